@@ -1,0 +1,289 @@
+"""Building blocks that run on PACKED token matrices ``[tokens, hidden]`` (no padding anywhere).
+
+Every block is a thin ``nn.Module`` holding parameters and calling the functional ops of
+``nmtgminor_b200.ops``; on a CUDA device with a flat parameter store attached the ops are the sm_100a
+kernels, otherwise their PyTorch restatements.  Sequences are described by ``PackedSeqs`` (cumulative
+offsets), which is what the variable-length attention kernel consumes.
+
+Functional counterparts in the reference: ``MultiHeadAttention`` (onmt/modules/attention.py:15-141),
+``SelfMultiheadAttn`` / ``EncdecMultiheadAttn`` (onmt/modules/optimized/self_attention.py:21-147,
+encdec_attention.py:10-156), ``FeedForward`` / ``PositionWiseFeedForward`` (onmt/modules/linear.py:123-160,
+onmt/modules/optimized/feed_forward.py:13-207), ``PrePostProcessing``
+(onmt/modules/pre_post_processing.py:10-82) and ``PositionalEncoding``
+(onmt/models/transformer_layers.py:354-442).
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+from typing import Optional
+
+import torch
+import torch.nn as nn
+
+from .. import ops
+
+
+@dataclass
+class PackedSeqs:
+    """A batch of sequences stored back to back.
+
+    tokens / positions: int64 ``[capacity]`` (rows past ``cu[-1]`` hold the padding id / position 0),
+    cu: int32 ``[B + 1]`` cumulative lengths, max_len: host upper bound on the longest sequence.
+    """
+    tokens: torch.Tensor
+    positions: torch.Tensor
+    cu: torch.Tensor
+    max_len: int
+    lengths: Optional[torch.Tensor] = None
+    extras: dict = field(default_factory=dict)
+
+    @property
+    def batch_size(self) -> int:
+        return self.cu.numel() - 1
+
+    def to(self, device, non_blocking=True):
+        mv = lambda t: t.to(device, non_blocking=non_blocking) if isinstance(t, torch.Tensor) else t
+        return PackedSeqs(mv(self.tokens), mv(self.positions), mv(self.cu), self.max_len, mv(self.lengths),
+                          {k: mv(v) for k, v in self.extras.items()})
+
+    @staticmethod
+    def from_padded(tokens_bt: torch.Tensor, lengths: torch.Tensor, capacity: Optional[int] = None, pad_idx: int = 0):
+        """Pack a right-padded ``[B, T]`` matrix given per-row lengths."""
+        B, T = tokens_bt.shape
+        lengths = lengths.to(torch.int64)
+        total = int(lengths.sum())
+        cap = capacity if capacity is not None else total
+        ar = torch.arange(T, device=tokens_bt.device)
+        mask = ar[None, :] < lengths[:, None]
+        toks = tokens_bt.new_full((cap,), pad_idx)
+        pos = tokens_bt.new_zeros((cap,))
+        toks[:total] = tokens_bt[mask]
+        pos[:total] = ar[None, :].expand(B, T)[mask]
+        cu = torch.zeros(B + 1, dtype=torch.int32, device=tokens_bt.device)
+        cu[1:] = torch.cumsum(lengths, 0).to(torch.int32)
+        return PackedSeqs(toks, pos, cu, int(lengths.max()) if B else 0, lengths)
+
+    def pad(self, x: torch.Tensor, time_first: bool = True):
+        """Packed ``[tokens, ...]`` -> padded ``[T, B, ...]`` (or ``[B, T, ...]``)."""
+        from ..ops.reference import pad_packed
+        out, _ = pad_packed(x, self.cu, self.max_len)
+        return out.transpose(0, 1).contiguous() if time_first else out
+
+
+def sinusoidal_table(n_pos: int, dim: int) -> torch.Tensor:
+    """tensor2tensor-style table: ``[sin(pos * w_i) | cos(pos * w_i)]`` with ``w_i = 10000^(-i/(dim/2-1))``."""
+    half = dim // 2
+    inc = math.log(10000.0) / max(half - 1, 1)
+    inv = torch.exp(torch.arange(half, dtype=torch.float32) * -inc)
+    ang = torch.arange(n_pos, dtype=torch.float32)[:, None] * inv[None, :]
+    return torch.cat([torch.sin(ang), torch.cos(ang)], dim=1)
+
+
+class LayerNorm(nn.Module):
+    def __init__(self, dim: int, eps: float = 1e-5):
+        super().__init__()
+        self.weight = nn.Parameter(torch.ones(dim))
+        self.bias = nn.Parameter(torch.zeros(dim))
+        self.eps = eps
+
+    def forward(self, x):
+        return ops.layer_norm(x, self.weight, self.bias, self.eps)
+
+
+class Linear(nn.Module):
+    """Affine map on packed rows with an optional fused epilogue (activation, dropout, residual)."""
+
+    def __init__(self, d_in: int, d_out: int, bias: bool = True, init_std: Optional[float] = None):
+        super().__init__()
+        self.weight = nn.Parameter(torch.empty(d_out, d_in))
+        self.bias = nn.Parameter(torch.zeros(d_out)) if bias else None
+        if init_std is None:
+            nn.init.xavier_uniform_(self.weight)
+        else:
+            nn.init.normal_(self.weight, 0.0, init_std)
+
+    def forward(self, x, act="none", dropout_p=0.0, residual=None):
+        return ops.linear(x, self.weight, self.bias, act, dropout_p, residual, self.training)
+
+
+class Embedding(nn.Module):
+    """Token embedding * scale + (sinusoidal | learned) position row, then dropout, in one kernel."""
+
+    def __init__(self, vocab: int, dim: int, pad_idx: int = 0, scale: Optional[float] = None, max_pos: int = 1024,
+                 learned_pos: bool = False, pos_offset: int = 0, use_pos: bool = True):
+        super().__init__()
+        self.weight = nn.Parameter(torch.empty(vocab, dim))
+        nn.init.normal_(self.weight, 0.0, dim ** -0.5)
+        with torch.no_grad():
+            self.weight[pad_idx].zero_()
+        self.pad_idx = pad_idx
+        self.scale = math.sqrt(dim) if scale is None else scale
+        self.learned_pos = learned_pos
+        self.pos_offset = pos_offset
+        self.use_pos = use_pos
+        if use_pos:
+            if learned_pos:
+                self.pos = nn.Parameter(torch.empty(max_pos + pos_offset, dim))
+                nn.init.normal_(self.pos, 0.0, 0.02)
+            else:
+                self.register_buffer("pos", sinusoidal_table(max_pos, dim), persistent=False)
+                self._pos_work = None
+
+    def renew(self, n_pos: int):
+        if self.use_pos and not self.learned_pos and n_pos > self.pos.shape[0]:
+            self.pos = sinusoidal_table(n_pos, self.pos.shape[1]).to(self.pos.device)
+            self._pos_work = None
+
+    def _pos_table(self, device):
+        if not self.use_pos:
+            return None
+        if self.learned_pos:
+            return self.pos
+        if device.type != "cuda":
+            return self.pos
+        if self._pos_work is None or self._pos_work.device != device:
+            self._pos_work = self.pos.to(device=device, dtype=torch.bfloat16)
+        return self._pos_work
+
+    def forward(self, seqs: PackedSeqs, dropout_p: float = 0.0):
+        pos = seqs.positions + self.pos_offset if (self.use_pos and self.pos_offset) else seqs.positions
+        return ops.embedding(seqs.tokens, self.weight, pos if self.use_pos else None, self._pos_table(seqs.tokens.device),
+                             self.scale, dropout_p, self.training, self.pad_idx, pos_trainable=self.learned_pos)
+
+
+class SelfAttention(nn.Module):
+    """Fused-QKV self-attention sub-layer: ``residual + D(out(attn(qkv(x))))``."""
+
+    def __init__(self, dim: int, heads: int, attn_dropout: float = 0.0, bias: bool = False, causal: bool = False):
+        super().__init__()
+        self.dim, self.heads, self.attn_dropout, self.causal = dim, heads, attn_dropout, causal
+        self.qkv = Linear(dim, 3 * dim, bias=bias)
+        self.out = Linear(dim, dim, bias=bias)
+
+    def forward(self, x, seqs: PackedSeqs, residual=None, dropout_p: float = 0.0):
+        ctx = ops.self_attention(self.qkv(x), seqs.cu, self.heads, seqs.max_len, self.causal, self.attn_dropout,
+                                 self.training)
+        return self.out(ctx, dropout_p=dropout_p, residual=residual)
+
+    # -- incremental decoding: x [B, H] is ONE new position per hypothesis --------------------------
+    def step(self, x, cache: dict):
+        H, h = self.dim, self.heads
+        qkv = self.qkv(x)
+        q, k, v = qkv[:, :H], qkv[:, H:2 * H], qkv[:, 2 * H:]
+        B = x.shape[0]
+        if "k" not in cache:
+            cache["k"], cache["v"] = k.view(B, 1, H), v.view(B, 1, H)
+        else:
+            cache["k"] = torch.cat([cache["k"], k.view(B, 1, H)], 1)
+            cache["v"] = torch.cat([cache["v"], v.view(B, 1, H)], 1)
+        ctx = _cached_attention(q, cache["k"], cache["v"], h, None)
+        return self.out(ctx)
+
+
+class CrossAttention(nn.Module):
+    """Encoder-decoder attention sub-layer with a fused key/value projection of the encoder states."""
+
+    def __init__(self, dim: int, heads: int, attn_dropout: float = 0.0, bias: bool = False, kv_dim: Optional[int] = None):
+        super().__init__()
+        self.dim, self.heads, self.attn_dropout = dim, heads, attn_dropout
+        self.q = Linear(dim, dim, bias=bias)
+        self.kv = Linear(kv_dim or dim, 2 * dim, bias=bias)
+        self.out = Linear(dim, dim, bias=bias)
+
+    def forward(self, x, seqs: PackedSeqs, memory, mem_seqs: PackedSeqs, residual=None, dropout_p: float = 0.0):
+        ctx = ops.cross_attention(self.q(x), self.kv(memory), seqs.cu, mem_seqs.cu, self.heads, seqs.max_len,
+                                  mem_seqs.max_len, self.attn_dropout, self.training)
+        return self.out(ctx, dropout_p=dropout_p, residual=residual)
+
+    def precompute(self, memory_padded):
+        """memory_padded [B, Ts, H] -> cached keys / values [B, Ts, H] for incremental decoding."""
+        B, T, Hm = memory_padded.shape
+        kv = self.kv(memory_padded.reshape(B * T, Hm)).view(B, T, 2 * self.dim)
+        return kv[..., :self.dim].contiguous(), kv[..., self.dim:].contiguous()
+
+    def step(self, x, cache: dict, mem_mask):
+        q = self.q(x)
+        ctx = _cached_attention(q, cache["c_k"], cache["c_v"], self.heads, mem_mask)
+        return self.out(ctx)
+
+
+def _cached_attention(q, k, v, heads, key_pad_mask):
+    """Single-position attention over cached keys.  q [B, H]; k, v [B, T, H]; key_pad_mask [B, T] True = pad."""
+    B, T, H = k.shape
+    d = H // heads
+    qh = q.view(B, heads, 1, d).float()
+    kh = k.view(B, T, heads, d).permute(0, 2, 1, 3).float()
+    vh = v.view(B, T, heads, d).permute(0, 2, 1, 3).float()
+    s = torch.matmul(qh, kh.transpose(-1, -2)) * (d ** -0.5)
+    if key_pad_mask is not None:
+        s = s.masked_fill(key_pad_mask[:, None, None, :], float("-inf"))
+    p = torch.softmax(s, dim=-1)
+    return torch.matmul(p, vh).reshape(B, H).to(q.dtype)
+
+
+class FeedForward(nn.Module):
+    """``residual + D(fc2(D(act(fc1(x)))))`` executed as two GEMMs with fused epilogues."""
+
+    def __init__(self, dim: int, inner: int, dropout: float = 0.0, activation: str = "relu"):
+        super().__init__()
+        self.fc1 = Linear(dim, inner)
+        self.fc2 = Linear(inner, dim)
+        self.dropout = dropout
+        self.activation = activation
+
+    def forward(self, x, residual=None, dropout_p: float = 0.0):
+        return ops.mlp(x, self.fc1.weight, self.fc1.bias, self.fc2.weight, self.fc2.bias, self.activation, self.dropout,
+                       dropout_p, residual, self.training)
+
+
+class EncoderLayer(nn.Module):
+    """Pre-LN block: x += D(SelfAttn(LN(x))); x += D(FFN(LN(x))), with optional stochastic depth."""
+
+    def __init__(self, dim, heads, inner, dropout=0.1, attn_dropout=0.1, activation="relu", attn_bias=False,
+                 death_rate=0.0, ffn_dropout=None):
+        super().__init__()
+        self.attn_norm = LayerNorm(dim)
+        self.attn = SelfAttention(dim, heads, attn_dropout, bias=attn_bias)
+        self.ffn_norm = LayerNorm(dim)
+        self.ffn = FeedForward(dim, inner, dropout if ffn_dropout is None else ffn_dropout, activation)
+        self.dropout = dropout
+        self.death_rate = death_rate
+
+    def forward(self, x, seqs: PackedSeqs):
+        if self.training and self.death_rate > 0 and torch.rand(1).item() < self.death_rate:
+            return x
+        x = self.attn(self.attn_norm(x), seqs, residual=x, dropout_p=self.dropout)
+        return self.ffn(self.ffn_norm(x), residual=x, dropout_p=self.dropout)
+
+
+class DecoderLayer(nn.Module):
+    """Pre-LN block with causal self-attention, encoder-decoder attention and FFN."""
+
+    def __init__(self, dim, heads, inner, dropout=0.1, attn_dropout=0.1, activation="relu", attn_bias=False,
+                 death_rate=0.0, ffn_dropout=None, ignore_source=False):
+        super().__init__()
+        self.self_norm = LayerNorm(dim)
+        self.self_attn = SelfAttention(dim, heads, attn_dropout, bias=attn_bias, causal=True)
+        self.ignore_source = ignore_source
+        if not ignore_source:
+            self.cross_norm = LayerNorm(dim)
+            self.cross_attn = CrossAttention(dim, heads, attn_dropout, bias=attn_bias)
+        self.ffn_norm = LayerNorm(dim)
+        self.ffn = FeedForward(dim, inner, dropout if ffn_dropout is None else ffn_dropout, activation)
+        self.dropout = dropout
+        self.death_rate = death_rate
+
+    def forward(self, x, seqs: PackedSeqs, memory, mem_seqs: PackedSeqs):
+        if self.training and self.death_rate > 0 and torch.rand(1).item() < self.death_rate:
+            return x
+        x = self.self_attn(self.self_norm(x), seqs, residual=x, dropout_p=self.dropout)
+        if not self.ignore_source:
+            x = self.cross_attn(self.cross_norm(x), seqs, memory, mem_seqs, residual=x, dropout_p=self.dropout)
+        return self.ffn(self.ffn_norm(x), residual=x, dropout_p=self.dropout)
+
+    def step(self, x, cache: dict, mem_mask):
+        x = x + self.self_attn.step(self.self_norm(x), cache)
+        if not self.ignore_source:
+            x = x + self.cross_attn.step(self.cross_norm(x), cache, mem_mask)
+        return self.ffn(self.ffn_norm(x), residual=x)

@@ -1,0 +1,213 @@
+"""Encoder-decoder Transformer (the ``-model transformer`` family) on packed variable-length batches.
+
+Pre-LN layers, tensor2tensor sinusoidal positions added to ``sqrt(d) *`` word embeddings, optional joined
+source/target embeddings and tied output projection, stochastic depth (``death_rate`` growing linearly
+with depth), incremental decoding with per-layer key/value caches.  The forward pass never materialises
+padded ``[T, B, H]`` activations or ``[T, B, V]`` logits in training: the trainer asks for the fused
+``loss`` directly.  ``hidden`` / ``logprobs`` in the reference's padded layout are produced on request for
+API parity.
+
+Reference behaviour: onmt/models/transformers.py:48-223 (encoder), :226-510 (decoder, ``step`` :393),
+:513-830 (``Transformer.forward`` :548, ``decode`` :685, ``step`` :754, ``create_decoder_state`` :792),
+:833-999 (decoding state, ``_reorder_incremental_state`` :967); generator onmt/modules/base_seq2seq.py:8-47.
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict, Optional
+
+import torch
+import torch.nn as nn
+
+from .. import ops
+from .layers import DecoderLayer, Embedding, EncoderLayer, LayerNorm, PackedSeqs
+
+
+def _expected_death_rates(n_layers: int, death_rate: float):
+    return [(i + 1) / n_layers * death_rate for i in range(n_layers)]
+
+
+class TransformerEncoder(nn.Module):
+    def __init__(self, opt, embed: Embedding):
+        super().__init__()
+        n = opt.encoder_layers if getattr(opt, "encoder_layers", -1) > 0 else opt.layers
+        self.embed = embed
+        self.emb_dropout = opt.emb_dropout
+        rates = _expected_death_rates(n, getattr(opt, "death_rate", 0.0))
+        self.layers = nn.ModuleList([
+            EncoderLayer(opt.model_size, opt.n_heads, opt.inner_size, opt.dropout, opt.attn_dropout, opt.ffn_activation,
+                         attn_bias=getattr(opt, "attn_bias", False), death_rate=rates[i],
+                         ffn_dropout=opt.ffn_dropout if getattr(opt, "ffn_dropout", -1) >= 0 else None)
+            for i in range(n)])
+        self.final_norm = LayerNorm(opt.model_size)
+
+    def forward(self, src: PackedSeqs):
+        x = self.embed(src, self.emb_dropout)
+        for layer in self.layers:
+            x = layer(x, src)
+        return self.final_norm(x)
+
+
+class TransformerDecoder(nn.Module):
+    def __init__(self, opt, embed: Embedding, ignore_source: bool = False):
+        super().__init__()
+        self.embed = embed
+        self.emb_dropout = opt.emb_dropout
+        rates = _expected_death_rates(opt.layers, getattr(opt, "death_rate", 0.0))
+        self.layers = nn.ModuleList([
+            DecoderLayer(opt.model_size, opt.n_heads, opt.inner_size, opt.dropout, opt.attn_dropout, opt.ffn_activation,
+                         attn_bias=getattr(opt, "attn_bias", False), death_rate=rates[i],
+                         ffn_dropout=opt.ffn_dropout if getattr(opt, "ffn_dropout", -1) >= 0 else None,
+                         ignore_source=ignore_source)
+            for i in range(opt.layers)])
+        self.final_norm = LayerNorm(opt.model_size)
+
+    def forward(self, tgt: PackedSeqs, memory, src: PackedSeqs):
+        x = self.embed(tgt, self.emb_dropout)
+        for layer in self.layers:
+            x = layer(x, tgt, memory, src)
+        return self.final_norm(x)
+
+    def step(self, tokens, position: int, state: "DecodingState"):
+        """tokens [B] (last generated symbol of every hypothesis) -> hidden [B, H]."""
+        B = tokens.shape[0]
+        seqs = PackedSeqs(tokens, torch.full_like(tokens, position), torch.arange(B + 1, dtype=torch.int32, device=tokens.device), 1)
+        self.embed.renew(position + 1)
+        x = self.embed(seqs, 0.0)
+        for i, layer in enumerate(self.layers):
+            x = layer.step(x, state.buffers[i], state.src_pad_mask)
+        return self.final_norm(x)
+
+
+class Generator(nn.Module):
+    """hidden -> vocabulary logits (weight optionally tied to the target embedding)."""
+
+    def __init__(self, dim: int, vocab: int, bias: bool = True):
+        super().__init__()
+        self.weight = nn.Parameter(torch.empty(vocab, dim))
+        nn.init.normal_(self.weight, 0.0, dim ** -0.5)
+        self.bias = nn.Parameter(torch.zeros(vocab)) if bias else None
+
+    def forward(self, hidden, log_softmax: bool = False):
+        logits = ops.linear(hidden, self.weight, self.bias, "none", 0.0, None, False)
+        return torch.log_softmax(logits.float(), dim=-1) if log_softmax else logits
+
+
+class DecodingState:
+    """Encoder output (padded once, repeated per beam) plus per-layer key/value caches.
+
+    ``buffers[i]`` holds ``k``/``v`` (self-attention, grown by one position per step) and ``c_k``/``c_v``
+    (projected encoder states, computed once).  ``reorder`` re-indexes every tensor along the hypothesis
+    dimension, which is what beam search needs after each step.
+    """
+
+    def __init__(self, context_padded, src_pad_mask, n_layers: int, beam_size: int):
+        self.beam_size = beam_size
+        self.context = context_padded.repeat_interleave(beam_size, 0) if beam_size > 1 else context_padded
+        self.src_pad_mask = src_pad_mask.repeat_interleave(beam_size, 0) if beam_size > 1 else src_pad_mask
+        self.buffers = [dict() for _ in range(n_layers)]
+        self.position = 0
+
+    def reorder(self, index):
+        self.context = self.context.index_select(0, index)
+        self.src_pad_mask = self.src_pad_mask.index_select(0, index)
+        for buf in self.buffers:
+            for k in list(buf.keys()):
+                buf[k] = buf[k].index_select(0, index)
+
+    _reorder_incremental_state = reorder  # reference spelling
+
+
+class Transformer(nn.Module):
+    """``NMTModel`` for text-to-text translation."""
+
+    def __init__(self, opt, dicts):
+        super().__init__()
+        self.opt = opt
+        src_vocab, tgt_vocab = dicts["src"].size(), dicts["tgt"].size()
+        self.pad_idx = getattr(opt, "pad_idx", 0)
+        max_pos = getattr(opt, "max_position_length", 1024)
+        tgt_embed = Embedding(tgt_vocab, opt.model_size, self.pad_idx, max_pos=max_pos)
+        if getattr(opt, "join_embedding", False):
+            assert src_vocab == tgt_vocab, "joined embeddings need one shared vocabulary"
+            src_embed = Embedding(src_vocab, opt.model_size, self.pad_idx, max_pos=max_pos)
+            src_embed.weight = tgt_embed.weight
+        else:
+            src_embed = Embedding(src_vocab, opt.model_size, self.pad_idx, max_pos=max_pos)
+        self.encoder = TransformerEncoder(opt, src_embed)
+        self.decoder = TransformerDecoder(opt, tgt_embed)
+        self.generator = Generator(opt.model_size, tgt_vocab)
+        if getattr(opt, "tie_weights", False):
+            self.tie_weights()
+        self.label_smoothing = getattr(opt, "label_smoothing", 0.0)
+
+    # -- weight sharing --------------------------------------------------------------------------
+    def tie_weights(self):
+        self.generator.weight = self.decoder.embed.weight
+
+    def share_enc_dec_embedding(self):
+        self.encoder.embed.weight = self.decoder.embed.weight
+
+    # -- training / scoring ----------------------------------------------------------------------
+    def forward(self, batch, return_logits: bool = False, compute_loss: bool = True, grad_scale=None, **_unused) -> Dict:
+        """``batch`` provides ``packed_source()``, ``packed_target_input()`` and ``packed_target_output()``."""
+        src = batch.packed_source()
+        tgt = batch.packed_target_input()
+        labels = batch.packed_target_output()
+        context = self.encoder(src)
+        hidden = self.decoder(tgt, context, src)
+        out = {"hidden_packed": hidden, "context_packed": context, "src": src, "tgt": tgt, "target": labels}
+        if compute_loss:
+            loss, correct, row_loss = ops.generator_cross_entropy(
+                hidden, self.generator.weight, self.generator.bias, labels,
+                self.label_smoothing if self.training else 0.0, self.pad_idx, grad_scale)
+            out.update(loss=loss, correct=correct, row_loss=row_loss)
+        if return_logits:
+            logits = self.generator(hidden)
+            out["logprobs"] = tgt.pad(logits)       # [T, B, V] (logits, as in the reference)
+            out["hidden"] = tgt.pad(hidden)         # [T, B, H]
+            out["context"] = src.pad(context)
+        return out
+
+    def post_backward(self, output_dict=None):
+        return None
+
+    @torch.no_grad()
+    def decode(self, batch):
+        """Gold scoring: per-sentence sum of target log-probabilities ``[B]`` and per-token scores."""
+        was_training = self.training
+        self.eval()
+        out = self.forward(batch, compute_loss=True)
+        tgt = out["tgt"]
+        tok_scores = -out["row_loss"]
+        padded = tgt.pad(tok_scores[:, None]).squeeze(-1)   # [T, B]
+        self.train(was_training)
+        return batch.get("target_output"), padded.sum(0), padded
+
+    # -- incremental decoding --------------------------------------------------------------------
+    @torch.no_grad()
+    def create_decoder_state(self, batch, beam_size: int = 1, **_unused) -> DecodingState:
+        src = batch.packed_source()
+        context = self.encoder(src)
+        ctx_padded = src.pad(context, time_first=False)                    # [B, Ts, H]
+        lengths = (src.cu[1:] - src.cu[:-1]).to(torch.int64)
+        pad_mask = torch.arange(ctx_padded.shape[1], device=ctx_padded.device)[None, :] >= lengths[:, None]
+        state = DecodingState(ctx_padded, pad_mask, len(self.decoder.layers), beam_size)
+        for i, layer in enumerate(self.decoder.layers):
+            if not layer.ignore_source:
+                ck, cv = layer.cross_attn.precompute(state.context)
+                state.buffers[i]["c_k"], state.buffers[i]["c_v"] = ck, cv
+        return state
+
+    @torch.no_grad()
+    def step(self, input_t, state: DecodingState) -> Dict:
+        """input_t ``[B*beam, t]`` (all symbols so far) -> ``log_prob [B*beam, V]`` fp32 for the next symbol."""
+        tokens = input_t[:, -1].contiguous()
+        hidden = self.decoder.step(tokens, input_t.shape[1] - 1, state)
+        logits = self.generator(hidden)
+        state.position += 1
+        return {"log_prob": torch.log_softmax(logits.float(), dim=-1), "hidden": hidden, "coverage": None}
+
+    def renew_buffer(self, new_len: int):
+        self.encoder.embed.renew(new_len)
+        self.decoder.embed.renew(new_len)

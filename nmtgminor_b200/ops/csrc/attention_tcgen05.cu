@@ -1,0 +1,611 @@
+// Variable-length (packed) multi-head attention for sm_100a, head_dim 64, forward and backward, on
+// tcgen05 tensor cores with TMEM accumulators and TMA-fed 128-byte-swizzled shared-memory tiles.
+//
+// Sequences are packed along the token dimension and described by cumulative offsets (cu_seqlens), so
+// key padding never exists; self-attention (optionally causal) and encoder-decoder attention (separate
+// query / key offsets) use the same kernels.  One CTA = one (128-query tile, head, sequence) in forward
+// and one (128-key tile, head, sequence) in backward.  Thread t of the CTA owns TMEM lane t = tile row
+// t, so the softmax needs no cross-thread reduction.
+//
+// forward:   S = Q K^T (UMMA, K-major x K-major) -> online softmax in registers -> P (bf16, swizzled
+//            smem) -> O_tile = P V (UMMA, V consumed MN-major straight from its [keys, d] TMA tile).
+// backward:  S, dP = dO V^T recomputed per query tile; dV += P^T dO, dK += dS^T Q accumulate in TMEM
+//            over query tiles (A operands read MN-major from the same smem that holds P / dS);
+//            dQ = dS K per tile (written directly when the sequence has a single key tile, else
+//            accumulated in an fp32 buffer with vector red.add).
+// Dropout on P is regenerated from Philox counters in backward; nothing but the row log-sum-exp is saved.
+//
+// Replaces the reference's cuBLAS-strided-batched + warp-softmax attention extensions
+// (onmt/modules/extensions/multihead_attn/self_multihead_attn_cuda.cu:23-612, encdec_multihead_attn_
+// bias_cuda.cu:22-612, softmax_apex.h) and its bundled FlashAttention-v1 mma.sync kernels
+// (onmt/modules/extensions/flashattn/src/fmha_fprop_kernel_1xN.h, fmha_dgrad_kernel_1xN_loop.h).
+#include "b200_ptx.cuh"
+#include "ops_api.h"
+
+namespace b200 {
+
+bool cached_tmap(CUtensorMap* out, const void* base, long rows, long cols, long ld, int br, int bc);
+
+constexpr int kHd = 64;          // head dimension
+constexpr int kTile = 128;       // query / key tile
+constexpr int kTileBytes = kTile * kHd * 2;   // 16 KB : one [128 x 64] bf16 tile
+constexpr int kPBytes = kTile * kTile * 2;    // 32 KB : P or dS as two [128 x 64] slabs
+constexpr float kNegBig = -1.0e30f;
+
+struct AttnArgs {
+  const int* cu_q;
+  const int* cu_k;
+  int num_heads;
+  int causal;
+  float scale;
+  float dropout_p;
+  unsigned long long seed, stream_id;
+  const unsigned long long* seed_dev;
+  int kstride;            // multiple of 16, >= longest key sequence: dropout counter stride per query row
+  __nv_bfloat16* out; int ld_out;       // fwd: O ; bwd: unused
+  float* lse; long lse_stride;          // [heads, lse_stride]
+  __nv_bfloat16* p_debug; long p_stride_row;  // optional [heads, total_q, kstride] dropped probabilities
+  // backward
+  const __nv_bfloat16* o; int ld_o;
+  const __nv_bfloat16* d_o; int ld_do;
+  __nv_bfloat16* dq; int ld_dq;
+  __nv_bfloat16* dk; int ld_dk;
+  __nv_bfloat16* dv; int ld_dv;
+  float* dq_acc; int ld_dqacc;          // fp32 accumulation buffer for multi-key-tile sequences
+  int total_q;
+  int* status;
+};
+
+// nk UMMA k-steps reading A from a_addr (+ k * a_step bytes) and B from b_addr (+ k * b_step bytes)
+__device__ __forceinline__ void umma_steps(uint32_t d_tmem, uint32_t a_addr, uint32_t a_lbo, uint32_t a_step,
+                                           uint32_t b_addr, uint32_t b_lbo, uint32_t b_step, uint32_t idesc, int nk,
+                                           bool accumulate_first) {
+  const uint64_t adesc = make_smem_desc_sw128(a_addr, a_lbo, 1024);
+  const uint64_t bdesc = make_smem_desc_sw128(b_addr, b_lbo, 1024);
+  for (int k = 0; k < nk; ++k)
+    umma_bf16(d_tmem, adesc + static_cast<uint64_t>((k * a_step) >> 4), bdesc + static_cast<uint64_t>((k * b_step) >> 4),
+              idesc, (accumulate_first || k > 0) ? 1u : 0u);
+}
+
+__device__ __forceinline__ float keep_factor(const Philox& rng, unsigned long long stream, unsigned long long idx,
+                                             uint32_t thr8, float keep_scale, uint4& cache, unsigned long long& cache_ctr) {
+  const unsigned long long ctr = idx >> 4;
+  if (ctr != cache_ctr) {
+    cache = rng(ctr, stream);
+    cache_ctr = ctr;
+  }
+  const int e = static_cast<int>(idx & 15);
+  const uint32_t w = philox_word(cache, e >> 2);
+  const uint32_t byte = (w >> ((e & 3) * 8)) & 0xFFu;
+  return byte >= thr8 ? keep_scale : 0.f;
+}
+
+// ---------------------------------------------------------------------------------------------------
+// forward
+// ---------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(128)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                const __grid_constant__ CUtensorMap tmap_v, const AttnArgs p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sK = sQ + kTileBytes;
+  uint8_t* sV = sK + kTileBytes;
+  uint8_t* sP = sV + kTileBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + kPBytes);  // [0]=Q [1]=KV [2]=MMA
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3);
+  volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int b = blockIdx.z, h = blockIdx.y, qt = blockIdx.x;
+  const int q_begin = p.cu_q[b], q_end = p.cu_q[b + 1];
+  const int k_begin = p.cu_k[b], k_len = p.cu_k[b + 1] - k_begin;
+  const int q0 = q_begin + qt * kTile;
+  if (q0 >= q_end) return;  // uniform for the CTA, before any barrier or TMEM use
+  const int q_rows = min(kTile, q_end - q0);
+  const int t = threadIdx.x, warp = t >> 5;
+
+  if (t == 0) {
+    mbar_init(&bars[0], 1);
+    mbar_init(&bars[1], 1);
+    mbar_init(&bars[2], 1);
+    *abort_word = 0;
+    mbar_fence_init();
+  }
+  if (warp == 0) tmem_alloc(tmem_slot, 256);
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tS = tmem_base;         // 128 columns
+  const uint32_t tO = tmem_base + 128;   // 64 columns
+  const uint32_t lane_sel = static_cast<uint32_t>(warp * 32) << 16;
+
+  if (t == 0) {
+    mbar_expect_tx(&bars[0], kTileBytes);
+    tma_load_2d(sQ, &tmap_q, &bars[0], h * kHd, q0);
+  }
+  const uint32_t idesc_s = make_idesc_bf16(kTile, kTile, 0, 0);
+  const uint32_t idesc_o = make_idesc_bf16(kTile, kHd, 0, 1);
+
+  float m_run = kNegBig, l_run = 0.f;
+  float o_acc[kHd];
+#pragma unroll
+  for (int j = 0; j < kHd; ++j) o_acc[j] = 0.f;
+
+  const int q_pos = qt * kTile + t;  // position inside the sequence
+  int num_kt = (k_len + kTile - 1) / kTile;
+  if (p.causal) num_kt = min(num_kt, (qt * kTile + q_rows + kTile - 1) / kTile);
+  const bool do_drop = p.dropout_p > 0.f;
+  const Philox rng(p.seed + ((do_drop && p.seed_dev) ? *p.seed_dev : 0ull));
+  const uint32_t thr8 = static_cast<uint32_t>(p.dropout_p * 256.0f + 0.5f);
+  const float keep_scale = do_drop ? 256.0f / static_cast<float>(256 - thr8) : 1.f;
+  const unsigned long long dstream = (p.stream_id << 16) | static_cast<unsigned long long>(h);
+  uint32_t ph_kv = 0, ph_mma = 0;
+  bool ok = true;
+
+  for (int kt = 0; kt < num_kt && ok; ++kt) {
+    if (t == 0) {
+      mbar_expect_tx(&bars[1], 2 * kTileBytes);
+      tma_load_2d(sK, &tmap_k, &bars[1], h * kHd, k_begin + kt * kTile);
+      tma_load_2d(sV, &tmap_v, &bars[1], h * kHd, k_begin + kt * kTile);
+      if (kt == 0) ok = mbar_wait(&bars[0], 0, abort_word, p.status, kTimeoutTmaFull);
+      if (ok) ok = mbar_wait(&bars[1], ph_kv, abort_word, p.status, kTimeoutTmaFull);
+      if (ok) {
+        tc_fence_after_sync();
+        umma_steps(tS, smem_u32(sQ), 16, 32, smem_u32(sK), 16, 32, idesc_s, kHd / 16, false);
+        umma_commit(&bars[2]);
+      }
+    }
+    ph_kv ^= 1;
+    if (!mbar_wait(&bars[2], ph_mma, abort_word, p.status, kTimeoutTmemFull)) { ok = false; break; }
+    ph_mma ^= 1;
+    tc_fence_after_sync();
+
+    // ---- softmax over this key tile: two passes over the 128 score columns of my row -----------
+    const int kcols = min(kTile, k_len - kt * kTile);
+    float tile_max = kNegBig;
+#pragma unroll 1
+    for (int c = 0; c < 4; ++c) {
+      uint32_t r[32];
+      tmem_ld32(tS + lane_sel + c * 32, r);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const int col = c * 32 + j;
+        const bool valid = col < kcols && (!p.causal || kt * kTile + col <= q_pos);
+        const float s = valid ? __uint_as_float(r[j]) * p.scale : kNegBig;
+        tile_max = fmaxf(tile_max, s);
+      }
+    }
+    const float m_new = fmaxf(m_run, tile_max);
+    const float alpha = __expf(m_run - m_new);
+    float row_sum = 0.f;
+    uint4 rc = make_uint4(0, 0, 0, 0);
+    unsigned long long rc_ctr = ~0ull;
+#pragma unroll 1
+    for (int c = 0; c < 4; ++c) {
+      uint32_t r[32];
+      tmem_ld32(tS + lane_sel + c * 32, r);
+      tmem_ld_wait();
+      float pv[32];
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const int col = c * 32 + j;
+        const bool valid = col < kcols && (!p.causal || kt * kTile + col <= q_pos);
+        const float e = valid ? __expf(__uint_as_float(r[j]) * p.scale - m_new) : 0.f;
+        row_sum += e;
+        pv[j] = e;
+      }
+      if (do_drop) {
+        const unsigned long long base = static_cast<unsigned long long>(q0 + t) * p.kstride + kt * kTile + c * 32;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) pv[j] *= keep_factor(rng, dstream, base + j, thr8, keep_scale, rc, rc_ctr);
+      }
+      // bf16, swizzled K-major slabs of 64 keys
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        uint4 o;
+        __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) o2[j] = __floats2bfloat162_rn(pv[g * 8 + 2 * j], pv[g * 8 + 2 * j + 1]);
+        const int chunk = c * 4 + g;  // 16-byte chunk index along the 128 keys
+        *reinterpret_cast<uint4*>(sP + (chunk >> 3) * kTileBytes + sw128_offset(t, chunk & 7)) = o;
+      }
+    }
+    l_run = l_run * alpha + row_sum;
+    m_run = m_new;
+    tc_fence_before_sync();
+    fence_async_smem();
+    __syncthreads();
+    if (t == 0) {
+      tc_fence_after_sync();
+      // O_tile = P V : A = P (K-major, two slabs of 4 k-steps), B = V (MN-major, 16 keys per k-step)
+      umma_steps(tO, smem_u32(sP), 16, 32, smem_u32(sV), 8192, 2048, idesc_o, 4, false);
+      umma_steps(tO, smem_u32(sP) + kTileBytes, 16, 32, smem_u32(sV) + 4 * 2048, 8192, 2048, idesc_o, 4, true);
+      umma_commit(&bars[2]);
+    }
+    if (!mbar_wait(&bars[2], ph_mma, abort_word, p.status, kTimeoutTmemFull)) { ok = false; break; }
+    ph_mma ^= 1;
+    tc_fence_after_sync();
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+      uint32_t r[32];
+      tmem_ld32(tO + lane_sel + c * 32, r);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 32; ++j) o_acc[c * 32 + j] = o_acc[c * 32 + j] * alpha + __uint_as_float(r[j]);
+    }
+    tc_fence_before_sync();
+    __syncthreads();  // K, V, P shared-memory tiles and both TMEM regions are free again
+  }
+
+  if (ok && t < q_rows) {
+    const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+    __nv_bfloat16* orow = p.out + static_cast<size_t>(q0 + t) * p.ld_out + h * kHd;
+#pragma unroll
+    for (int g = 0; g < 8; ++g) {
+      uint4 o;
+      __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) o2[j] = __floats2bfloat162_rn(o_acc[g * 8 + 2 * j] * inv, o_acc[g * 8 + 2 * j + 1] * inv);
+      reinterpret_cast<uint4*>(orow)[g] = o;
+    }
+    if (p.lse) p.lse[static_cast<size_t>(h) * p.lse_stride + q0 + t] = l_run > 0.f ? m_run + __logf(l_run) : 0.f;
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_word) {
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 0) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 256);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------
+// backward
+// ---------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(128)
+attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
+                const AttnArgs p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sK = smem;
+  uint8_t* sV = sK + kTileBytes;
+  uint8_t* sQ = sV + kTileBytes;
+  uint8_t* sDO = sQ + kTileBytes;
+  uint8_t* sP = sDO + kTileBytes;
+  uint8_t* sDS = sP + kPBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sDS + kPBytes);  // [0]=KV [1]=Q,dO [2]=MMA
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3);
+  volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int b = blockIdx.z, h = blockIdx.y, kt = blockIdx.x;
+  const int q_begin = p.cu_q[b], q_len = p.cu_q[b + 1] - q_begin;
+  const int k_begin = p.cu_k[b], k_len = p.cu_k[b + 1] - k_begin;
+  const int k0 = k_begin + kt * kTile;
+  if (kt * kTile >= k_len) return;
+  const int k_rows = min(kTile, k_len - kt * kTile);
+  const bool single_kt = k_len <= kTile;
+  const int t = threadIdx.x, warp = t >> 5;
+
+  if (t == 0) {
+    mbar_init(&bars[0], 1);
+    mbar_init(&bars[1], 1);
+    mbar_init(&bars[2], 1);
+    *abort_word = 0;
+    mbar_fence_init();
+  }
+  if (warp == 0) tmem_alloc(tmem_slot, 512);
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tS = tmem_base, tDP = tmem_base + 128, tDQ = tmem_base + 256, tDK = tmem_base + 320,
+                 tDV = tmem_base + 384;
+  const uint32_t lane_sel = static_cast<uint32_t>(warp * 32) << 16;
+
+  if (t == 0) {
+    mbar_expect_tx(&bars[0], 2 * kTileBytes);
+    tma_load_2d(sK, &tmap_k, &bars[0], h * kHd, k0);
+    tma_load_2d(sV, &tmap_v, &bars[0], h * kHd, k0);
+  }
+  const uint32_t idesc_s = make_idesc_bf16(kTile, kTile, 0, 0);    // S, dP : K-major x K-major, N = 128
+  const uint32_t idesc_dq = make_idesc_bf16(kTile, kHd, 0, 1);     // dQ    : K-major A, MN-major B, N = 64
+  const uint32_t idesc_dkv = make_idesc_bf16(kTile, kHd, 1, 1);    // dK,dV : MN-major A and B, N = 64
+
+  const bool do_drop = p.dropout_p > 0.f;
+  const Philox rng(p.seed + ((do_drop && p.seed_dev) ? *p.seed_dev : 0ull));
+  const uint32_t thr8 = static_cast<uint32_t>(p.dropout_p * 256.0f + 0.5f);
+  const float keep_scale = do_drop ? 256.0f / static_cast<float>(256 - thr8) : 1.f;
+  const unsigned long long dstream = (p.stream_id << 16) | static_cast<unsigned long long>(h);
+
+  const int num_qt = (q_len + kTile - 1) / kTile;
+  const int qt_first = p.causal ? (kt * kTile) / kTile : 0;  // query tiles before the key tile see none of it
+  uint32_t ph_q = 0, ph_mma = 0;
+  bool ok = true;
+  bool first = true;
+
+  for (int qt = qt_first; qt < num_qt && ok; ++qt) {
+    const int q0 = q_begin + qt * kTile;
+    const int q_rows = min(kTile, q_len - qt * kTile);
+    if (t == 0) {
+      mbar_expect_tx(&bars[1], 2 * kTileBytes);
+      tma_load_2d(sQ, &tmap_q, &bars[1], h * kHd, q0);
+      tma_load_2d(sDO, &tmap_do, &bars[1], h * kHd, q0);
+      if (first) ok = mbar_wait(&bars[0], 0, abort_word, p.status, kTimeoutTmaFull);
+      if (ok) ok = mbar_wait(&bars[1], ph_q, abort_word, p.status, kTimeoutTmaFull);
+      if (ok) {
+        tc_fence_after_sync();
+        umma_steps(tS, smem_u32(sQ), 16, 32, smem_u32(sK), 16, 32, idesc_s, kHd / 16, false);
+        umma_steps(tDP, smem_u32(sDO), 16, 32, smem_u32(sV), 16, 32, idesc_s, kHd / 16, false);
+        umma_commit(&bars[2]);
+      }
+    }
+    ph_q ^= 1;
+    // D = rowsum(dO * O) and the saved log-sum-exp of my query row (overlaps the MMAs)
+    const bool row_ok = t < q_rows;
+    float Drow = 0.f, lse = 0.f;
+    if (row_ok) {
+      const uint4* orow = reinterpret_cast<const uint4*>(p.o + static_cast<size_t>(q0 + t) * p.ld_o + h * kHd);
+      const uint4* drow = reinterpret_cast<const uint4*>(p.d_o + static_cast<size_t>(q0 + t) * p.ld_do + h * kHd);
+#pragma unroll
+      for (int g = 0; g < 8; ++g) {
+        uint4 a = orow[g], d = drow[g];
+        const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&a);
+        const __nv_bfloat162* d2 = reinterpret_cast<const __nv_bfloat162*>(&d);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float2 x = __bfloat1622float2(a2[j]), y = __bfloat1622float2(d2[j]);
+          Drow += x.x * y.x + x.y * y.y;
+        }
+      }
+      lse = p.lse[static_cast<size_t>(h) * p.lse_stride + q0 + t];
+    }
+    if (!mbar_wait(&bars[2], ph_mma, abort_word, p.status, kTimeoutTmemFull)) { ok = false; break; }
+    ph_mma ^= 1;
+    tc_fence_after_sync();
+
+    const int q_pos = qt * kTile + t;
+    uint4 rc = make_uint4(0, 0, 0, 0);
+    unsigned long long rc_ctr = ~0ull;
+#pragma unroll 1
+    for (int c = 0; c < 4; ++c) {
+      uint32_t rs[32], rd[32];
+      tmem_ld32(tS + lane_sel + c * 32, rs);
+      tmem_ld32(tDP + lane_sel + c * 32, rd);
+      tmem_ld_wait();
+      float pd[32], ds[32];
+      const unsigned long long base = static_cast<unsigned long long>(q0 + t) * p.kstride + kt * kTile + c * 32;
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const int col = c * 32 + j;
+        const bool valid = row_ok && col < k_rows && (!p.causal || kt * kTile + col <= q_pos);
+        const float pr = valid ? __expf(__uint_as_float(rs[j]) * p.scale - lse) : 0.f;
+        float kf = 1.f;
+        if (do_drop) kf = keep_factor(rng, dstream, base + j, thr8, keep_scale, rc, rc_ctr);
+        pd[j] = pr * kf;
+        ds[j] = pr * (__uint_as_float(rd[j]) * kf - Drow) * p.scale;
+      }
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        uint4 o1, o2v;
+        __nv_bfloat162* a2 = reinterpret_cast<__nv_bfloat162*>(&o1);
+        __nv_bfloat162* b2 = reinterpret_cast<__nv_bfloat162*>(&o2v);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          a2[j] = __floats2bfloat162_rn(pd[g * 8 + 2 * j], pd[g * 8 + 2 * j + 1]);
+          b2[j] = __floats2bfloat162_rn(ds[g * 8 + 2 * j], ds[g * 8 + 2 * j + 1]);
+        }
+        const int chunk = c * 4 + g;
+        const uint32_t off = (chunk >> 3) * kTileBytes + sw128_offset(t, chunk & 7);
+        *reinterpret_cast<uint4*>(sP + off) = o1;
+        *reinterpret_cast<uint4*>(sDS + off) = o2v;
+      }
+    }
+    tc_fence_before_sync();
+    fence_async_smem();
+    __syncthreads();
+    if (t == 0) {
+      tc_fence_after_sync();
+      // dV += P^T dO : A = P read MN-major (M = keys: two 64-key slabs, LBO = slab size), K = 128 query rows
+      umma_steps(tDV, smem_u32(sP), kTileBytes, 2048, smem_u32(sDO), 8192, 2048, idesc_dkv, 8, !first);
+      // dK += dS^T Q
+      umma_steps(tDK, smem_u32(sDS), kTileBytes, 2048, smem_u32(sQ), 8192, 2048, idesc_dkv, 8, !first);
+      // dQ = dS K : A = dS K-major (two slabs of 4 k-steps), B = K tile MN-major
+      umma_steps(tDQ, smem_u32(sDS), 16, 32, smem_u32(sK), 8192, 2048, idesc_dq, 4, false);
+      umma_steps(tDQ, smem_u32(sDS) + kTileBytes, 16, 32, smem_u32(sK) + 4 * 2048, 8192, 2048, idesc_dq, 4, true);
+      umma_commit(&bars[2]);
+    }
+    first = false;
+    if (!mbar_wait(&bars[2], ph_mma, abort_word, p.status, kTimeoutTmemFull)) { ok = false; break; }
+    ph_mma ^= 1;
+    tc_fence_after_sync();
+#pragma unroll 1
+    for (int c = 0; c < 2; ++c) {
+      uint32_t r[32];
+      tmem_ld32(tDQ + lane_sel + c * 32, r);
+      tmem_ld_wait();
+      if (row_ok) {
+        if (single_kt) {
+          __nv_bfloat16* drow = p.dq + static_cast<size_t>(q0 + t) * p.ld_dq + h * kHd + c * 32;
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            uint4 o;
+            __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              o2[j] = __floats2bfloat162_rn(__uint_as_float(r[g * 8 + 2 * j]), __uint_as_float(r[g * 8 + 2 * j + 1]));
+            reinterpret_cast<uint4*>(drow)[g] = o;
+          }
+        } else {
+          float* arow = p.dq_acc + static_cast<size_t>(q0 + t) * p.ld_dqacc + h * kHd + c * 32;
+#pragma unroll
+          for (int g = 0; g < 8; ++g)
+            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(arow + g * 4),
+                         "f"(__uint_as_float(r[g * 4])), "f"(__uint_as_float(r[g * 4 + 1])),
+                         "f"(__uint_as_float(r[g * 4 + 2])), "f"(__uint_as_float(r[g * 4 + 3]))
+                         : "memory");
+        }
+      }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+  }
+
+  // dK, dV of my key row
+  if (ok && !first) {
+#pragma unroll 1
+    for (int which = 0; which < 2; ++which) {
+      __nv_bfloat16* dst = which == 0 ? p.dk : p.dv;
+      const int ld = which == 0 ? p.ld_dk : p.ld_dv;
+      const uint32_t tsrc = which == 0 ? tDK : tDV;
+#pragma unroll 1
+      for (int c = 0; c < 2; ++c) {
+        uint32_t r[32];
+        tmem_ld32(tsrc + lane_sel + c * 32, r);
+        tmem_ld_wait();
+        if (t < k_rows) {
+          __nv_bfloat16* drow = dst + static_cast<size_t>(k0 + t) * ld + h * kHd + c * 32;
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            uint4 o;
+            __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              o2[j] = __floats2bfloat162_rn(__uint_as_float(r[g * 8 + 2 * j]), __uint_as_float(r[g * 8 + 2 * j + 1]));
+            reinterpret_cast<uint4*>(drow)[g] = o;
+          }
+        }
+      }
+    }
+  } else if (ok && t < k_rows) {
+    // no query tile attends to this key tile: zero gradients
+    for (int which = 0; which < 2; ++which) {
+      __nv_bfloat16* dst = which == 0 ? p.dk : p.dv;
+      const int ld = which == 0 ? p.ld_dk : p.ld_dv;
+      uint4 z = make_uint4(0, 0, 0, 0);
+      for (int g = 0; g < 8; ++g) reinterpret_cast<uint4*>(dst + static_cast<size_t>(k0 + t) * ld + h * kHd)[g] = z;
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_word) {
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 0) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// dq (bf16) = dq_acc (fp32) for rows of sequences with more than one key tile
+__global__ void attn_dq_convert_kernel(const float* __restrict__ acc, int ld_acc, __nv_bfloat16* __restrict__ dq, int ld_dq,
+                                       const int* __restrict__ cu_q, const int* __restrict__ cu_k, int width) {
+  const int b = blockIdx.y;
+  if (cu_k[b + 1] - cu_k[b] <= kTile) return;
+  const int q_begin = cu_q[b], q_end = cu_q[b + 1];
+  const int w4 = width >> 2;
+  for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < static_cast<long>(q_end - q_begin) * w4;
+       i += static_cast<long>(gridDim.x) * blockDim.x) {
+    const int r = q_begin + static_cast<int>(i / w4), c = static_cast<int>(i % w4) * 4;
+    float4 v = *reinterpret_cast<const float4*>(acc + static_cast<size_t>(r) * ld_acc + c);
+    __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+    uint2 o;
+    o.x = *reinterpret_cast<uint32_t*>(&lo);
+    o.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(dq + static_cast<size_t>(r) * ld_dq + c) = o;
+  }
+}
+
+constexpr int kFwdSmem = 3 * kTileBytes + kPBytes + 64 + 1024;
+constexpr int kBwdSmem = 4 * kTileBytes + 2 * kPBytes + 64 + 1024;
+
+}  // namespace b200
+
+using namespace b200;
+
+static const char* check_ptr(const void* p, int ld) {
+  if ((reinterpret_cast<uintptr_t>(p) & 15) || (ld % 8)) return "attention: tensors must be 16-byte aligned with ld % 8 == 0";
+  return nullptr;
+}
+
+const char* nmtg_attn_fwd(const AttnDesc* d, cudaStream_t stream) {
+  if (d->batch <= 0 || d->num_heads <= 0) return nullptr;
+  if (d->head_dim != kHd) return "attention: only head_dim 64 is implemented";
+  const char* e;
+  if ((e = check_ptr(d->q, d->ld_q)) || (e = check_ptr(d->k, d->ld_k)) || (e = check_ptr(d->v, d->ld_v)) ||
+      (e = check_ptr(d->out, d->ld_out)))
+    return e;
+  const int width = d->num_heads * kHd;
+  CUtensorMap tq, tk, tv;
+  if (!cached_tmap(&tq, d->q, d->total_q, width, d->ld_q, kTile, kHd)) return "attention: tensor map (q) failed";
+  if (!cached_tmap(&tk, d->k, d->total_k, width, d->ld_k, kTile, kHd)) return "attention: tensor map (k) failed";
+  if (!cached_tmap(&tv, d->v, d->total_k, width, d->ld_v, kTile, kHd)) return "attention: tensor map (v) failed";
+  AttnArgs a = {};
+  a.cu_q = d->cu_q; a.cu_k = d->cu_k; a.num_heads = d->num_heads; a.causal = d->causal; a.scale = d->scale;
+  a.dropout_p = d->dropout_p; a.seed = d->seed; a.stream_id = d->stream_id; a.seed_dev = d->seed_dev; a.kstride = d->kstride;
+  a.out = reinterpret_cast<__nv_bfloat16*>(d->out); a.ld_out = d->ld_out;
+  a.lse = d->lse; a.lse_stride = d->lse_stride;
+  a.p_debug = nullptr; a.total_q = d->total_q; a.status = d->status;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t ce = cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kFwdSmem);
+    if (ce != cudaSuccess) return cudaGetErrorString(ce);
+    configured = true;
+  }
+  dim3 grid((d->max_q + kTile - 1) / kTile, d->num_heads, d->batch);
+  attn_fwd_kernel<<<grid, 128, kFwdSmem, stream>>>(tq, tk, tv, a);
+  cudaError_t ce = cudaGetLastError();
+  return ce == cudaSuccess ? nullptr : cudaGetErrorString(ce);
+}
+
+const char* nmtg_attn_bwd(const AttnDesc* d, cudaStream_t stream) {
+  if (d->batch <= 0 || d->num_heads <= 0) return nullptr;
+  if (d->head_dim != kHd) return "attention: only head_dim 64 is implemented";
+  const char* e;
+  if ((e = check_ptr(d->q, d->ld_q)) || (e = check_ptr(d->k, d->ld_k)) || (e = check_ptr(d->v, d->ld_v)) ||
+      (e = check_ptr(d->out, d->ld_out)) || (e = check_ptr(d->d_out, d->ld_dout)) || (e = check_ptr(d->dq, d->ld_dq)) ||
+      (e = check_ptr(d->dk, d->ld_dk)) || (e = check_ptr(d->dv, d->ld_dv)))
+    return e;
+  if (d->max_k > kTile && !d->dq_acc) return "attention backward: sequences above 128 keys need the fp32 dq buffer";
+  const int width = d->num_heads * kHd;
+  CUtensorMap tq, tk, tv, tdo;
+  if (!cached_tmap(&tq, d->q, d->total_q, width, d->ld_q, kTile, kHd)) return "attention: tensor map (q) failed";
+  if (!cached_tmap(&tk, d->k, d->total_k, width, d->ld_k, kTile, kHd)) return "attention: tensor map (k) failed";
+  if (!cached_tmap(&tv, d->v, d->total_k, width, d->ld_v, kTile, kHd)) return "attention: tensor map (v) failed";
+  if (!cached_tmap(&tdo, d->d_out, d->total_q, width, d->ld_dout, kTile, kHd)) return "attention: tensor map (dO) failed";
+  AttnArgs a = {};
+  a.cu_q = d->cu_q; a.cu_k = d->cu_k; a.num_heads = d->num_heads; a.causal = d->causal; a.scale = d->scale;
+  a.dropout_p = d->dropout_p; a.seed = d->seed; a.stream_id = d->stream_id; a.seed_dev = d->seed_dev; a.kstride = d->kstride;
+  a.lse = d->lse; a.lse_stride = d->lse_stride;
+  a.o = reinterpret_cast<const __nv_bfloat16*>(d->out); a.ld_o = d->ld_out;
+  a.d_o = reinterpret_cast<const __nv_bfloat16*>(d->d_out); a.ld_do = d->ld_dout;
+  a.dq = reinterpret_cast<__nv_bfloat16*>(d->dq); a.ld_dq = d->ld_dq;
+  a.dk = reinterpret_cast<__nv_bfloat16*>(d->dk); a.ld_dk = d->ld_dk;
+  a.dv = reinterpret_cast<__nv_bfloat16*>(d->dv); a.ld_dv = d->ld_dv;
+  a.dq_acc = d->dq_acc; a.ld_dqacc = d->ld_dqacc;
+  a.total_q = d->total_q; a.status = d->status;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t ce = cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kBwdSmem);
+    if (ce != cudaSuccess) return cudaGetErrorString(ce);
+    configured = true;
+  }
+  dim3 grid((d->max_k + kTile - 1) / kTile, d->num_heads, d->batch);
+  attn_bwd_kernel<<<grid, 128, kBwdSmem, stream>>>(tq, tk, tv, tdo, a);
+  cudaError_t ce = cudaGetLastError();
+  if (ce != cudaSuccess) return cudaGetErrorString(ce);
+  if (d->max_k > kTile) {
+    dim3 g2(64, d->batch);
+    attn_dq_convert_kernel<<<g2, 256, 0, stream>>>(d->dq_acc, d->ld_dqacc, reinterpret_cast<__nv_bfloat16*>(d->dq), d->ld_dq,
+                                                   d->cu_q, d->cu_k, width);
+    ce = cudaGetLastError();
+    if (ce != cudaSuccess) return cudaGetErrorString(ce);
+  }
+  return nullptr;
+}

@@ -1,0 +1,246 @@
+// Memory-bound element-wise kernels for sm_100a (16-byte vector accesses, grid sized to the SM count):
+//   * dropout_add:      y = residual + dropout(x)           (mask regenerated from Philox, never stored)
+//   * masked_scale:     dx = dy * keep / (1-p)              (same counters as the forward op)
+//   * embed_fwd / bwd:  gather * scale + position row, dropout; backward scatter-adds into fp32 grads
+//   * colsum:           column sums of a bf16 matrix (bias gradients) accumulated into fp32
+// The dropout convention is shared with the GEMM epilogue: element e of the op with stream id s keeps
+// its value iff byte (e & 15) of Philox(counter = e >> 4, stream = s) is >= round(256 p); the keep scale
+// is 256 / (256 - round(256 p)).
+//
+// Counterpart of the reference's fused_dropout_add_cuda (onmt/modules/extensions/dropout_add/
+// dropout.h:21-160) and of the PyTorch embedding/position code in onmt/models/transformers.py:163-207.
+#include "b200_ptx.cuh"
+#include "ops_api.h"
+
+namespace b200 {
+
+int num_sms();
+
+__device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    float2 t = __bfloat1622float2(h[j]);
+    f[2 * j] = t.x;
+    f[2 * j + 1] = t.y;
+  }
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  uint4 o;
+  __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) o2[j] = __floats2bfloat162_rn(f[2 * j], f[2 * j + 1]);
+  return o;
+}
+
+// One thread handles 16 consecutive elements (two 16-byte vectors) = one Philox call.
+__global__ void dropout_add_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ res,
+                                   __nv_bfloat16* __restrict__ y, long n16, float p, unsigned long long seed,
+                                   unsigned long long stream_id, const unsigned long long* seed_dev) {
+  const Philox rng(seed + (seed_dev ? *seed_dev : 0ull));
+  const uint32_t thr8 = static_cast<uint32_t>(p * 256.0f + 0.5f);
+  const float scale = 256.0f / static_cast<float>(256 - thr8);
+  for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < n16;
+       i += static_cast<long>(gridDim.x) * blockDim.x) {
+    uint4 rnd = rng(static_cast<uint64_t>(i), stream_id);
+    const uint32_t w[4] = {rnd.x, rnd.y, rnd.z, rnd.w};
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      float f[8], r[8];
+      unpack8(reinterpret_cast<const uint4*>(x)[2 * i + h], f);
+      if (res) unpack8(reinterpret_cast<const uint4*>(res)[2 * i + h], r);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int e = h * 8 + j;
+        uint32_t byte = (w[e >> 2] >> ((e & 3) * 8)) & 0xFFu;
+        float v = byte >= thr8 ? f[j] * scale : 0.f;
+        f[j] = res ? v + r[j] : v;
+      }
+      reinterpret_cast<uint4*>(y)[2 * i + h] = pack8(f);
+    }
+  }
+}
+
+__global__ void embed_fwd_kernel(const int64_t* __restrict__ tokens, const int64_t* __restrict__ positions,
+                                 const __nv_bfloat16* __restrict__ table, const __nv_bfloat16* __restrict__ pos_table,
+                                 __nv_bfloat16* __restrict__ out, int rows, int hidden, int vocab, int max_pos,
+                                 float scale, float p, unsigned long long seed, unsigned long long stream_id,
+                                 const unsigned long long* seed_dev) {
+  const Philox rng(seed + (seed_dev ? *seed_dev : 0ull));
+  const uint32_t thr8 = static_cast<uint32_t>(p * 256.0f + 0.5f);
+  const float keep_scale = 256.0f / static_cast<float>(256 - thr8);
+  const int n16 = hidden >> 4;
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    long tok = tokens[row];
+    if (tok < 0 || tok >= vocab) tok = 0;
+    long pos = positions ? positions[row] : 0;
+    if (pos < 0) pos = 0;
+    if (pos >= max_pos) pos = max_pos - 1;
+    const uint4* tr = reinterpret_cast<const uint4*>(table + static_cast<size_t>(tok) * hidden);
+    const uint4* pr = pos_table ? reinterpret_cast<const uint4*>(pos_table + static_cast<size_t>(pos) * hidden) : nullptr;
+    uint4* orow = reinterpret_cast<uint4*>(out + static_cast<size_t>(row) * hidden);
+    for (int c = threadIdx.x; c < n16; c += blockDim.x) {
+      uint4 rnd = make_uint4(~0u, ~0u, ~0u, ~0u);
+      if (p > 0.f) rnd = rng(static_cast<uint64_t>(row) * n16 + c, stream_id);
+      const uint32_t w[4] = {rnd.x, rnd.y, rnd.z, rnd.w};
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        float f[8], q[8];
+        unpack8(__ldg(tr + 2 * c + h), f);
+        if (pr) unpack8(__ldg(pr + 2 * c + h), q);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int e = h * 8 + j;
+          float v = f[j] * scale + (pr ? q[j] : 0.f);
+          if (p > 0.f) {
+            uint32_t byte = (w[e >> 2] >> ((e & 3) * 8)) & 0xFFu;
+            v = byte >= thr8 ? v * keep_scale : 0.f;
+          }
+          f[j] = v;
+        }
+        orow[2 * c + h] = pack8(f);
+      }
+    }
+  }
+}
+
+// dTable[tok] += scale * keep * dy[row]   (fp32, vector red.add); optional dPos[pos] += keep * dy[row]
+__global__ void embed_bwd_kernel(const int64_t* __restrict__ tokens, const int64_t* __restrict__ positions,
+                                 const __nv_bfloat16* __restrict__ dy, float* __restrict__ dtable,
+                                 float* __restrict__ dpos, int rows, int hidden, int vocab, int max_pos, float scale,
+                                 float p, unsigned long long seed, unsigned long long stream_id,
+                                 const unsigned long long* seed_dev, int pad_idx) {
+  const Philox rng(seed + (seed_dev ? *seed_dev : 0ull));
+  const uint32_t thr8 = static_cast<uint32_t>(p * 256.0f + 0.5f);
+  const float keep_scale = 256.0f / static_cast<float>(256 - thr8);
+  const int n16 = hidden >> 4;
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    long tok = tokens[row];
+    if (tok < 0 || tok >= vocab || tok == pad_idx) continue;
+    long pos = positions ? positions[row] : 0;
+    if (pos < 0) pos = 0;
+    if (pos >= max_pos) pos = max_pos - 1;
+    const uint4* dr = reinterpret_cast<const uint4*>(dy + static_cast<size_t>(row) * hidden);
+    float* trow = dtable + static_cast<size_t>(tok) * hidden;
+    float* prow = dpos ? dpos + static_cast<size_t>(pos) * hidden : nullptr;
+    for (int c = threadIdx.x; c < n16; c += blockDim.x) {
+      uint4 rnd = make_uint4(~0u, ~0u, ~0u, ~0u);
+      if (p > 0.f) rnd = rng(static_cast<uint64_t>(row) * n16 + c, stream_id);
+      const uint32_t w[4] = {rnd.x, rnd.y, rnd.z, rnd.w};
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        float f[8];
+        unpack8(dr[2 * c + h], f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int e = h * 8 + j;
+          if (p > 0.f) {
+            uint32_t byte = (w[e >> 2] >> ((e & 3) * 8)) & 0xFFu;
+            f[j] = byte >= thr8 ? f[j] * keep_scale : 0.f;
+          }
+        }
+#pragma unroll
+        for (int g = 0; g < 2; ++g) {
+          float* t = trow + c * 16 + h * 8 + g * 4;
+          asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(t), "f"(f[g * 4] * scale),
+                       "f"(f[g * 4 + 1] * scale), "f"(f[g * 4 + 2] * scale), "f"(f[g * 4 + 3] * scale)
+                       : "memory");
+          if (prow) {
+            float* q = prow + c * 16 + h * 8 + g * 4;
+            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(q), "f"(f[g * 4]), "f"(f[g * 4 + 1]),
+                         "f"(f[g * 4 + 2]), "f"(f[g * 4 + 3])
+                         : "memory");
+          }
+        }
+      }
+    }
+  }
+}
+
+// out[c] += sum_r x[r, c]; CTA tile: 32 rows-lanes x 64 columns, rows strided over the grid's y dimension
+__global__ void colsum_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ out, int rows, int cols,
+                              long ld) {
+  __shared__ float part[8][64];
+  const int c0 = blockIdx.x * 64;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 8 warps
+  float a0 = 0.f, a1 = 0.f;
+  const int c = c0 + tx * 2;
+  if (c < cols) {
+    for (int r = blockIdx.y * 8 + ty; r < rows; r += gridDim.y * 8) {
+      __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(x + static_cast<size_t>(r) * ld + c);
+      float2 f = __bfloat1622float2(v);
+      a0 += f.x;
+      a1 += f.y;
+    }
+  }
+  part[ty][tx * 2] = a0;
+  part[ty][tx * 2 + 1] = a1;
+  __syncthreads();
+  if (threadIdx.x < 64 && c0 + threadIdx.x < cols) {
+    float s = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) s += part[w][threadIdx.x];
+    atomicAdd(out + c0 + threadIdx.x, s);
+  }
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+static const char* last_err() {
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? nullptr : cudaGetErrorString(e);
+}
+
+const char* nmtg_dropout_add(const void* x, const void* residual, void* y, long n, float p, unsigned long long seed,
+                             unsigned long long stream_id, const unsigned long long* seed_dev, cudaStream_t stream) {
+  if (n <= 0) return nullptr;
+  if (n % 16) return "dropout_add: element count must be a multiple of 16";
+  const long n16 = n / 16;
+  long blocks = (n16 + 255) / 256;
+  const long cap = static_cast<long>(num_sms()) * 8;
+  if (blocks > cap) blocks = cap;
+  dropout_add_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(
+      reinterpret_cast<const __nv_bfloat16*>(x), reinterpret_cast<const __nv_bfloat16*>(residual),
+      reinterpret_cast<__nv_bfloat16*>(y), n16, p, seed, stream_id, seed_dev);
+  return last_err();
+}
+
+const char* nmtg_embed_fwd(const int64_t* tokens, const int64_t* positions, const void* table, const void* pos_table,
+                           void* out, int rows, int hidden, int vocab, int max_pos, float scale, float p,
+                           unsigned long long seed, unsigned long long stream_id, const unsigned long long* seed_dev,
+                           cudaStream_t stream) {
+  if (rows <= 0) return nullptr;
+  if (hidden % 16) return "embed: hidden size must be a multiple of 16";
+  int grid = rows < num_sms() * 8 ? rows : num_sms() * 8;
+  embed_fwd_kernel<<<grid, 64, 0, stream>>>(tokens, positions, reinterpret_cast<const __nv_bfloat16*>(table),
+                                            reinterpret_cast<const __nv_bfloat16*>(pos_table),
+                                            reinterpret_cast<__nv_bfloat16*>(out), rows, hidden, vocab, max_pos, scale,
+                                            p, seed, stream_id, seed_dev);
+  return last_err();
+}
+
+const char* nmtg_embed_bwd(const int64_t* tokens, const int64_t* positions, const void* dy, float* dtable, float* dpos,
+                           int rows, int hidden, int vocab, int max_pos, float scale, float p, unsigned long long seed,
+                           unsigned long long stream_id, const unsigned long long* seed_dev, int pad_idx,
+                           cudaStream_t stream) {
+  if (rows <= 0) return nullptr;
+  if (hidden % 16) return "embed: hidden size must be a multiple of 16";
+  int grid = rows < num_sms() * 8 ? rows : num_sms() * 8;
+  embed_bwd_kernel<<<grid, 64, 0, stream>>>(tokens, positions, reinterpret_cast<const __nv_bfloat16*>(dy), dtable, dpos,
+                                            rows, hidden, vocab, max_pos, scale, p, seed, stream_id, seed_dev, pad_idx);
+  return last_err();
+}
+
+const char* nmtg_colsum(const void* x, float* out, int rows, int cols, long ld, cudaStream_t stream) {
+  if (rows <= 0 || cols <= 0) return nullptr;
+  if (cols % 2 || ld % 2) return "colsum: column count and leading dimension must be even";
+  dim3 grid((cols + 63) / 64, 1);
+  int gy = (num_sms() * 4) / grid.x;
+  if (gy < 1) gy = 1;
+  if (gy > (rows + 7) / 8) gy = (rows + 7) / 8;
+  grid.y = gy;
+  colsum_kernel<<<grid, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(x), out, rows, cols, ld);
+  return last_err();
+}

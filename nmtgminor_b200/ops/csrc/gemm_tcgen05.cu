@@ -1,0 +1,547 @@
+// Persistent warp-specialised bf16 GEMM for sm_100a: TMA -> shared memory (128-byte swizzle) ->
+// tcgen05.mma with fp32 accumulators in TMEM -> fused epilogue read back with tcgen05.ld.
+//
+//   C[M,N] = epilogue( alpha * sum_k A(m,k) * B(n,k) )
+//
+// A and B may each be stored "K-major" (row = M/N index, K contiguous; the layout of activations X[M,K]
+// and of Linear weights W[N,K]) or "MN-major" (row = K index, M/N contiguous), so the same mainloop
+// serves forward (X W^T), data-gradient (dY W) and weight-gradient (dY^T X) products without any
+// transposed copy.  Roles: warp 0 = TMA producer, warp 1 = UMMA issuer (owns TMEM), warps 2..5 =
+// epilogue.  Two accumulator buffers in TMEM let the epilogue of tile i overlap the mainloop of tile
+// i+1.  Optional split-K (weight gradients of small matrices) accumulates with vector red.add into an
+// fp32 output.
+//
+// Replaces the cuBLAS / cuBLASLt GEMM + separate element-wise kernels of the reference
+// (onmt/modules/extensions/mlp/mlp_relu_cuda.cu:82-190,445-1292; mlp_blaslt/mlp_gelu_cuda.cu:212-471;
+// multihead_attn/self_multihead_attn_cuda.cu:91,284; dropout_add/dropout.h:21-160).
+#include "b200_ptx.cuh"
+#include "ops_api.h"
+
+#include <mutex>
+#include <unordered_map>
+#include <string>
+#include <cstring>
+#include <cstdio>
+
+namespace b200 {
+
+constexpr int BM = 128;
+constexpr int BK = 64;
+constexpr int kGemmThreads = 192;
+
+template <int BN>
+struct GemmSmem {
+  static constexpr int kStages = (BN == 256) ? 4 : 6;
+  static constexpr int kABytes = BM * BK * 2;
+  static constexpr int kBBytes = BN * BK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kBarOffset = kStages * kStageBytes;
+  static constexpr int kTotal = kBarOffset + 256 + 1024;  // barriers + alignment slack
+};
+
+struct GemmArgs {
+  int M, N, K;
+  int a_mn_major, b_mn_major;
+  int split_k;             // >= 1; > 1 requires out_fp32 and atomic accumulation
+  float alpha;
+  const __nv_bfloat16* bias;      // [N] or null
+  const __nv_bfloat16* residual;  // [M, ld_res] or null, added last
+  int ld_res;
+  const __nv_bfloat16* aux;       // [M, ld_aux] activation-backward operand or null
+  int ld_aux;
+  void* out;
+  int ld_out;
+  int out_fp32;
+  int accumulate;          // fp32 output only: out += result
+  __nv_bfloat16* preact;   // optional [M, ld_out]: value after bias, before activation
+  int act;
+  float dropout_p;
+  unsigned long long seed, stream_id;
+  const unsigned long long* seed_dev;
+  int* status;
+};
+
+__device__ __forceinline__ float gelu_f(float x) { return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f)); }
+__device__ __forceinline__ float gelu_grad(float x) {
+  float cdf = 0.5f * (1.0f + erff(x * 0.70710678118654752f));
+  float pdf = 0.3989422804014327f * __expf(-0.5f * x * x);
+  return cdf + x * pdf;
+}
+__device__ __forceinline__ float sigmoid_f(float x) { return 1.0f / (1.0f + __expf(-x)); }
+
+template <int BN>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                    const GemmArgs p) {
+  using S = GemmSmem<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + S::kBarOffset);
+  uint64_t* empty_bar = full_bar + S::kStages;
+  uint64_t* tmem_full = empty_bar + S::kStages;
+  uint64_t* tmem_empty = tmem_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_m = (p.M + BM - 1) / BM;
+  const int num_n = (p.N + BN - 1) / BN;
+  const int num_kb_total = (p.K + BK - 1) / BK;
+  const int kb_per_split = (num_kb_total + p.split_k - 1) / p.split_k;
+  const int num_tiles = num_m * num_n * p.split_k;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < S::kStages; ++i) {
+      mbar_init(&full_bar[i], 1);
+      mbar_init(&empty_bar[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&tmem_full[i], 1);
+      mbar_init(&tmem_empty[i], 128);
+    }
+    *abort_word = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, 2 * BN);
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------- TMA producer -------------------------------------------
+    if (lane == 0) {
+      tma_prefetch_desc(&tmap_a);
+      tma_prefetch_desc(&tmap_b);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int mn = tile % (num_m * num_n);
+        const int ks = tile / (num_m * num_n);
+        const int m0 = (mn % num_m) * BM;
+        const int n0 = (mn / num_m) * BN;
+        const int kb_begin = ks * kb_per_split;
+        const int kb_end = min(kb_begin + kb_per_split, num_kb_total);
+        for (int kb = kb_begin; kb < kb_end; ++kb) {  // an empty split range issues nothing
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_word, p.status, kTimeoutSmemEmpty)) {
+            ok = false;
+            break;
+          }
+          uint8_t* sa = smem + stage * S::kStageBytes;
+          uint8_t* sb = sa + S::kABytes;
+          mbar_expect_tx(&full_bar[stage], S::kStageBytes);
+          if (!p.a_mn_major) {
+            tma_load_2d(sa, &tmap_a, &full_bar[stage], kb * BK, m0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j)
+              tma_load_2d(sa + j * (BK * 128), &tmap_a, &full_bar[stage], m0 + j * 64, kb * BK);
+          }
+          if (!p.b_mn_major) {
+            tma_load_2d(sb, &tmap_b, &full_bar[stage], kb * BK, n0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              tma_load_2d(sb + j * (BK * 128), &tmap_b, &full_bar[stage], n0 + j * 64, kb * BK);
+          }
+          if (++stage == S::kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------- UMMA issuer ---------------------------------------------
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc_bf16(BM, BN, p.a_mn_major, p.b_mn_major);
+      const uint32_t a_lbo = p.a_mn_major ? BK * 128 : 16, b_lbo = p.b_mn_major ? BK * 128 : 16;
+      const uint32_t a_kstep = p.a_mn_major ? (16 * 128) >> 4 : 32 >> 4;  // descriptor units of 16 B
+      const uint32_t b_kstep = p.b_mn_major ? (16 * 128) >> 4 : 32 >> 4;
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int ks = tile / (num_m * num_n);
+        const int kb_begin = ks * kb_per_split;
+        const int kb_end = min(kb_begin + kb_per_split, num_kb_total);
+        if (kb_begin >= kb_end) continue;  // empty split range: no accumulator is produced
+        const int acc = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1, abort_word, p.status, kTimeoutTmemEmpty)) break;
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = kb_begin; kb < kb_end; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, abort_word, p.status, kTimeoutTmaFull)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t sa = smem_u32(smem + stage * S::kStageBytes);
+          const uint32_t sb = sa + S::kABytes;
+          const uint64_t adesc = make_smem_desc_sw128(sa, a_lbo, 1024);
+          const uint64_t bdesc = make_smem_desc_sw128(sb, b_lbo, 1024);
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            umma_bf16(d_tmem, adesc + static_cast<uint64_t>(k * a_kstep), bdesc + static_cast<uint64_t>(k * b_kstep),
+                      idesc, (kb > kb_begin || k > 0) ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[stage]);
+          if (++stage == S::kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (ok) umma_commit(&tmem_full[acc]);
+        ++it;
+      }
+    }
+  } else {
+    // ------------------------------- epilogue (4 warps) --------------------------------------
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    const bool do_drop = p.dropout_p > 0.f;
+    const Philox rng(p.seed + ((do_drop && p.seed_dev) ? *p.seed_dev : 0ull));
+    const uint32_t thr8 = static_cast<uint32_t>(p.dropout_p * 256.0f + 0.5f);
+    const float keep_scale = do_drop ? 256.0f / static_cast<float>(256 - thr8) : 1.0f;
+    int it = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+      const int mn = tile % (num_m * num_n);
+      const int m0 = (mn % num_m) * BM;
+      const int n0 = (mn / num_m) * BN;
+      {
+        const int kb_begin = (tile / (num_m * num_n)) * kb_per_split;
+        if (kb_begin >= min(kb_begin + kb_per_split, num_kb_total)) continue;
+      }
+      const int acc = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      if (!mbar_wait(&tmem_full[acc], acc_phase, abort_word, p.status, kTimeoutTmemFull)) break;
+      tc_fence_after_sync();
+      const int row = m0 + q * 32 + lane;
+      const bool row_ok = row < p.M;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        const int col0 = n0 + c * 32;
+        if (col0 >= p.N) break;  // warp-uniform
+        uint32_t r[32];
+        tmem_ld32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN + c * 32, r);
+        tmem_ld_wait();
+        if (!row_ok) continue;
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
+        const bool full_cols = (col0 + 32 <= p.N);
+        if (p.bias) {
+          if (full_cols) {
+            const uint4* bp = reinterpret_cast<const uint4*>(p.bias + col0);
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              uint4 b = __ldg(bp + g);
+              const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&b);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                float2 f = __bfloat1622float2(b2[j]);
+                v[g * 8 + 2 * j] += f.x;
+                v[g * 8 + 2 * j + 1] += f.y;
+              }
+            }
+          } else {
+            for (int j = 0; j < 32; ++j)
+              if (col0 + j < p.N) v[j] += __bfloat162float(p.bias[col0 + j]);
+          }
+        }
+        if (p.preact) {
+          __nv_bfloat16* pp = p.preact + static_cast<size_t>(row) * p.ld_out + col0;
+          if (full_cols) {
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              uint4 o;
+              __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) o2[j] = __floats2bfloat162_rn(v[g * 8 + 2 * j], v[g * 8 + 2 * j + 1]);
+              reinterpret_cast<uint4*>(pp)[g] = o;
+            }
+          } else {
+            for (int j = 0; j < 32; ++j)
+              if (col0 + j < p.N) pp[j] = __float2bfloat16(v[j]);
+          }
+        }
+        // activation (forward) or activation-gradient (backward; aux holds h or z)
+        if (p.act >= kActReluBwd) {
+          const __nv_bfloat16* ap = p.aux + static_cast<size_t>(row) * p.ld_aux + col0;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            float a = (col0 + j < p.N) ? __bfloat162float(ap[j]) : 0.f;
+            float g;
+            if (p.act == kActReluBwd) g = a > 0.f ? 1.f : 0.f;  // aux = relu output (after dropout)
+            else if (p.act == kActGeluBwd) g = gelu_grad(a);
+            else { float s = sigmoid_f(a); g = s * (1.f + a * (1.f - s)); }
+            v[j] *= g;
+          }
+        } else if (p.act == kActRelu) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.f);
+        } else if (p.act == kActGelu) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = gelu_f(v[j]);
+        } else if (p.act == kActSilu) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = v[j] * sigmoid_f(v[j]);
+        }
+        if (do_drop) {
+          // element index = row * N + col; 16 consecutive elements share one Philox call (one byte each)
+          const unsigned long long e0 = static_cast<unsigned long long>(row) * p.N + col0;
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            uint4 rnd = rng((e0 >> 4) + h, p.stream_id);
+            const uint32_t w[4] = {rnd.x, rnd.y, rnd.z, rnd.w};
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              uint32_t byte = (w[j >> 2] >> ((j & 3) * 8)) & 0xFFu;
+              v[h * 16 + j] = byte >= thr8 ? v[h * 16 + j] * keep_scale : 0.f;
+            }
+          }
+        }
+        if (p.residual) {
+          const __nv_bfloat16* rp = p.residual + static_cast<size_t>(row) * p.ld_res + col0;
+          if (full_cols) {
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              uint4 b = reinterpret_cast<const uint4*>(rp)[g];
+              const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&b);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                float2 f = __bfloat1622float2(b2[j]);
+                v[g * 8 + 2 * j] += f.x;
+                v[g * 8 + 2 * j + 1] += f.y;
+              }
+            }
+          } else {
+            for (int j = 0; j < 32; ++j)
+              if (col0 + j < p.N) v[j] += __bfloat162float(rp[j]);
+          }
+        }
+        if (p.out_fp32) {
+          float* op = reinterpret_cast<float*>(p.out) + static_cast<size_t>(row) * p.ld_out + col0;
+          if (p.split_k > 1) {
+            if (full_cols) {
+#pragma unroll
+              for (int g = 0; g < 8; ++g)
+                asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(op + g * 4), "f"(v[g * 4]),
+                             "f"(v[g * 4 + 1]), "f"(v[g * 4 + 2]), "f"(v[g * 4 + 3])
+                             : "memory");
+            } else {
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < p.N) atomicAdd(op + j, v[j]);
+            }
+          } else if (full_cols) {
+#pragma unroll
+            for (int g = 0; g < 8; ++g) {
+              float4 o = make_float4(v[g * 4], v[g * 4 + 1], v[g * 4 + 2], v[g * 4 + 3]);
+              if (p.accumulate) {
+                float4 old = reinterpret_cast<float4*>(op)[g];
+                o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+              }
+              reinterpret_cast<float4*>(op)[g] = o;
+            }
+          } else {
+            for (int j = 0; j < 32; ++j)
+              if (col0 + j < p.N) op[j] = p.accumulate ? op[j] + v[j] : v[j];
+          }
+        } else {
+          __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<size_t>(row) * p.ld_out + col0;
+          if (full_cols) {
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              uint4 o;
+              __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) o2[j] = __floats2bfloat162_rn(v[g * 8 + 2 * j], v[g * 8 + 2 * j + 1]);
+              reinterpret_cast<uint4*>(op)[g] = o;
+            }
+          } else {
+            for (int j = 0; j < 32; ++j)
+              if (col0 + j < p.N) op[j] = __float2bfloat16(v[j]);
+          }
+        }
+      }
+      tc_fence_before_sync();
+      mbar_arrive(&tmem_empty[acc]);
+      ++it;
+    }
+  }
+
+  // ------------------------------- teardown ------------------------------------------------------
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_word) {
+    // give copies that may still be in flight a bounded time to land before shared memory is released
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 2 * BN);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// host side
+// ------------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres);
+    if (e == cudaSuccess && qres == cudaDriverEntryPointSuccess) fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  });
+  return fn;
+}
+
+// 2-D bf16 row-major tensor [rows, cols] with leading dimension ld (elements); box = [box_rows, box_cols].
+bool make_tmap_bf16_2d(CUtensorMap* out, const void* base, long rows, long cols, long ld, int box_rows,
+                       int box_cols) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(box_cols), static_cast<cuuint32_t>(box_rows)};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+struct TmapKey {
+  const void* base;
+  long rows, cols, ld;
+  int br, bc;
+  bool operator==(const TmapKey& o) const {
+    return base == o.base && rows == o.rows && cols == o.cols && ld == o.ld && br == o.br && bc == o.bc;
+  }
+};
+struct TmapKeyHash {
+  size_t operator()(const TmapKey& k) const {
+    size_t h = reinterpret_cast<size_t>(k.base);
+    h = h * 1000003u ^ static_cast<size_t>(k.rows);
+    h = h * 1000003u ^ static_cast<size_t>(k.cols);
+    h = h * 1000003u ^ static_cast<size_t>(k.ld);
+    h = h * 1000003u ^ static_cast<size_t>(k.br * 1024 + k.bc);
+    return h;
+  }
+};
+
+bool cached_tmap(CUtensorMap* out, const void* base, long rows, long cols, long ld, int br, int bc) {
+  static std::unordered_map<TmapKey, CUtensorMap, TmapKeyHash> cache;
+  static std::mutex mu;
+  TmapKey k{base, rows, cols, ld, br, bc};
+  {
+    std::lock_guard<std::mutex> g(mu);
+    auto it = cache.find(k);
+    if (it != cache.end()) {
+      *out = it->second;
+      return true;
+    }
+  }
+  if (!make_tmap_bf16_2d(out, base, rows, cols, ld, br, bc)) return false;
+  std::lock_guard<std::mutex> g(mu);
+  if (cache.size() > 8192) cache.clear();
+  cache.emplace(k, *out);
+  return true;
+}
+
+static int g_num_sms = 0;
+int num_sms() {
+  if (!g_num_sms) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  return g_num_sms;
+}
+
+template <int BN>
+static const char* launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& args, int grid,
+                               cudaStream_t stream) {
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         GemmSmem<BN>::kTotal);
+    if (e != cudaSuccess) return cudaGetErrorString(e);
+    configured = true;
+  }
+  gemm_tcgen05_kernel<BN><<<grid, kGemmThreads, GemmSmem<BN>::kTotal, stream>>>(ta, tb, args);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? nullptr : cudaGetErrorString(e);
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+// Returns nullptr on success, else a static error string.
+const char* nmtg_gemm_bf16(const GemmDesc* d, cudaStream_t stream) {
+  if (d->M <= 0 || d->N <= 0 || d->K <= 0) return nullptr;
+  if ((d->lda % 8) || (d->ldb % 8)) return "gemm: leading dimensions must be multiples of 8 elements";
+  if ((reinterpret_cast<uintptr_t>(d->a) & 15) || (reinterpret_cast<uintptr_t>(d->b) & 15))
+    return "gemm: operand base addresses must be 16-byte aligned";
+  if (d->dropout_p > 0.f && (d->N % 16)) return "gemm: dropout epilogue needs N % 16 == 0";
+  if ((d->ld_out % 8) || (reinterpret_cast<uintptr_t>(d->out) & 15)) return "gemm: output must be 16-byte aligned";
+  GemmArgs a;
+  a.M = d->M; a.N = d->N; a.K = d->K;
+  a.a_mn_major = d->a_mn_major; a.b_mn_major = d->b_mn_major;
+  a.alpha = d->alpha;
+  a.bias = reinterpret_cast<const __nv_bfloat16*>(d->bias);
+  a.residual = reinterpret_cast<const __nv_bfloat16*>(d->residual); a.ld_res = d->ld_res;
+  a.aux = reinterpret_cast<const __nv_bfloat16*>(d->aux); a.ld_aux = d->ld_aux;
+  a.out = d->out; a.ld_out = d->ld_out; a.out_fp32 = d->out_fp32; a.accumulate = d->accumulate;
+  a.preact = reinterpret_cast<__nv_bfloat16*>(d->preact);
+  a.act = d->act; a.dropout_p = d->dropout_p; a.seed = d->seed; a.stream_id = d->stream_id; a.seed_dev = d->seed_dev;
+  a.status = d->status;
+
+  // tile width: 256 when it does not waste a wave, else 128
+  const int sms = num_sms();
+  const int num_m = (d->M + BM - 1) / BM;
+  int bn = 256;
+  if (d->N <= 128 || ((d->N % 256) != 0 && (d->N % 128) == 0)) bn = 128;
+  {
+    long t256 = static_cast<long>(num_m) * ((d->N + 255) / 256), t128 = static_cast<long>(num_m) * ((d->N + 127) / 128);
+    auto waves_eff = [&](long t) { long w = (t + sms - 1) / sms; return static_cast<double>(t) / (w * sms); };
+    if (bn == 256 && waves_eff(t128) > waves_eff(t256) + 0.15) bn = 128;
+  }
+  if (d->force_bn == 128 || d->force_bn == 256) bn = d->force_bn;
+  const int num_n = (d->N + bn - 1) / bn;
+  const int num_kb = (d->K + BK - 1) / BK;
+  int split = 1;
+  if (d->split_k > 0) split = d->split_k;
+  else if (d->out_fp32 && d->allow_split_k) {
+    long tiles = static_cast<long>(num_m) * num_n;
+    while (tiles * split * 2 <= sms && num_kb / (split * 2) >= 8) split *= 2;
+  }
+  if (split > 1 && !d->out_fp32) return "gemm: split-K needs an fp32 output";
+  if (split > num_kb) split = num_kb;
+  a.split_k = split;
+
+  CUtensorMap ta, tb;
+  bool ok;
+  if (!d->a_mn_major) ok = cached_tmap(&ta, d->a, d->M, d->K, d->lda, BM, BK);
+  else ok = cached_tmap(&ta, d->a, d->K, d->M, d->lda, BK, 64);
+  if (!ok) return "gemm: cuTensorMapEncodeTiled failed for A";
+  if (!d->b_mn_major) ok = cached_tmap(&tb, d->b, d->N, d->K, d->ldb, bn, BK);
+  else ok = cached_tmap(&tb, d->b, d->K, d->N, d->ldb, BK, 64);
+  if (!ok) return "gemm: cuTensorMapEncodeTiled failed for B";
+
+  long tiles = static_cast<long>(num_m) * num_n * split;
+  int grid = static_cast<int>(tiles < sms ? tiles : sms);
+  if (bn == 256) return launch_gemm<256>(ta, tb, a, grid, stream);
+  return launch_gemm<128>(ta, tb, a, grid, stream);
+}

@@ -1,0 +1,116 @@
+// C launch interface of the sm_100a kernels.  Pointers are device pointers; every launcher enqueues on
+// `stream` and returns nullptr on success or a static error string.  No launcher allocates memory.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+enum NmtgAct : int {
+  kActNone = 0,
+  kActRelu = 1,
+  kActGelu = 2,   // erf form
+  kActSilu = 3,
+  kActReluBwd = 5,  // out = acc * 1[aux > 0]           (aux = ReLU output, after dropout)
+  kActGeluBwd = 6,  // out = acc * gelu'(aux)           (aux = pre-activation)
+  kActSiluBwd = 7,  // out = acc * silu'(aux)
+};
+
+struct GemmDesc {
+  // C[M,N] = epilogue(alpha * sum_k A(m,k) B(n,k)).  K-major operand: row index = M/N, leading dimension
+  // ld over K.  MN-major operand (x_mn_major = 1): stored [K, M/N] with ld over M/N.
+  const void* a; int lda; int a_mn_major;
+  const void* b; int ldb; int b_mn_major;
+  int M, N, K;
+  float alpha;
+  const void* bias;       // bf16 [N] or null
+  const void* residual;   // bf16 [M, ld_res] or null
+  int ld_res;
+  const void* aux;        // bf16 [M, ld_aux] for the *Bwd activations
+  int ld_aux;
+  void* out; int ld_out; int out_fp32; int accumulate;
+  void* preact;           // optional bf16 [M, ld_out]
+  int act;
+  float dropout_p; unsigned long long seed, stream_id;
+  const unsigned long long* seed_dev;  // optional device word added to seed (lets graph replays draw new masks)
+  int split_k;            // 0 = automatic (only when allow_split_k), else forced
+  int allow_split_k;
+  int force_bn;           // 0 = automatic, 128 or 256
+  int* status;            // device int, 0 = ok
+};
+
+const char* nmtg_gemm_bf16(const GemmDesc* d, cudaStream_t stream);
+
+// LayerNorm over the last dimension of bf16 x[rows, hidden]; mean/rstd (fp32 [rows]) may be null in fwd.
+const char* nmtg_layernorm_fwd(const void* x, const void* gamma, const void* beta, void* y, float* mean, float* rstd,
+                               int rows, int hidden, float eps, cudaStream_t stream);
+// dx = LN'(dy) (+ dres if given); dgamma/dbeta (fp32 [hidden]) are ACCUMULATED into.
+const char* nmtg_layernorm_bwd(const void* dy, const void* x, const float* mean, const float* rstd, const void* gamma,
+                               const void* dres, void* dx, float* dgamma, float* dbeta, int rows, int hidden,
+                               cudaStream_t stream);
+
+// Label-smoothed softmax cross-entropy over bf16 logits[rows, vocab] (leading dimension ld).  When
+// write_grad != 0 the logits are overwritten with grad_scale * dloss/dlogit (grad_scale = *grad_scale_ptr
+// * grad_scale_val, pointer optional).  row_loss / row_lse / loss_sum / correct_sum are optional; the two
+// sums are ACCUMULATED into.  Rows whose label equals pad_idx contribute nothing and get a zero gradient.
+const char* nmtg_xent_fused(void* logits, const int64_t* labels, float* row_loss, float* row_lse, float* loss_sum,
+                            float* correct_sum, int rows, int vocab, long ld, float smoothing, int pad_idx,
+                            const float* grad_scale_ptr, float grad_scale_val, int write_grad, cudaStream_t stream);
+
+// y = (residual ? residual : 0) + dropout(x) over n bf16 elements (n % 16 == 0).  The backward of the
+// dropout branch is the same call with x = dy, residual = null.
+const char* nmtg_dropout_add(const void* x, const void* residual, void* y, long n, float p, unsigned long long seed,
+                             unsigned long long stream_id, const unsigned long long* seed_dev, cudaStream_t stream);
+// out[r] = dropout(table[tokens[r]] * scale + pos_table[positions[r]])  (pos_table / positions optional)
+const char* nmtg_embed_fwd(const int64_t* tokens, const int64_t* positions, const void* table, const void* pos_table,
+                           void* out, int rows, int hidden, int vocab, int max_pos, float scale, float p,
+                           unsigned long long seed, unsigned long long stream_id, const unsigned long long* seed_dev,
+                           cudaStream_t stream);
+// fp32 dtable / dpos (dpos optional) are ACCUMULATED into; rows whose token is pad_idx are skipped.
+const char* nmtg_embed_bwd(const int64_t* tokens, const int64_t* positions, const void* dy, float* dtable, float* dpos,
+                           int rows, int hidden, int vocab, int max_pos, float scale, float p, unsigned long long seed,
+                           unsigned long long stream_id, const unsigned long long* seed_dev, int pad_idx,
+                           cudaStream_t stream);
+// out[c] += sum over rows of bf16 x[r, c]
+const char* nmtg_colsum(const void* x, float* out, int rows, int cols, long ld, cudaStream_t stream);
+
+// Per-step optimiser scalars, kept in device memory (16 floats) so captured graphs can be replayed.
+struct NmtgAdamHyper {
+  float lr, beta1, beta2, eps;
+  float weight_decay, bias_correction1, bias_correction2, grad_scale;
+  float max_grad_norm;
+  int decoupled_wd;   // 1 = AdamW, 0 = L2 added to the gradient
+  int zero_grad;      // 1 = clear the gradient buffer after use
+  int pad0, pad1, pad2, pad3, pad4;
+};
+// out_sq += sum g^2 ; *out_nonfinite |= 1 when a non-finite partial sum is met
+const char* nmtg_sq_norm(const float* g, long n, float* out_sq, int* out_nonfinite, cudaStream_t stream);
+// One Adam(W) step over flat fp32 buffers (n % 4 == 0); work_bf16 (optional) receives the refreshed copy.
+const char* nmtg_adamw_flat(float* master, void* work_bf16, float* grad, float* m, float* v, long n,
+                            const NmtgAdamHyper* hyper_dev, const float* grad_sq, const int* nonfinite,
+                            cudaStream_t stream);
+const char* nmtg_cast_f32_bf16(const float* src, void* dst, long n, cudaStream_t stream);
+
+// Packed variable-length attention, head_dim 64.  q rows of sequence b are [cu_q[b], cu_q[b+1]) and its
+// key/value rows [cu_k[b], cu_k[b+1]); head h occupies columns [64h, 64h+64) of each tensor.
+struct AttnDesc {
+  const void* q; int ld_q;
+  const void* k; int ld_k;
+  const void* v; int ld_v;
+  void* out; int ld_out;              // forward output; backward input (O)
+  float* lse; long lse_stride;        // [heads, lse_stride] row log-sum-exp
+  const int* cu_q; const int* cu_k;   // device int32 [batch + 1]
+  int batch, num_heads, head_dim;
+  int max_q, max_k;                   // upper bounds on sequence lengths (grid sizing)
+  int total_q, total_k;               // rows of the q / kv tensors
+  int causal; float scale;
+  float dropout_p; unsigned long long seed, stream_id; int kstride;
+  const unsigned long long* seed_dev;
+  // backward only
+  const void* d_out; int ld_dout;
+  void* dq; int ld_dq;
+  void* dk; int ld_dk;
+  void* dv; int ld_dv;
+  float* dq_acc; int ld_dqacc;        // zero-initialised fp32 [total_q, heads*64]; needed when max_k > 128
+  int* status;
+};
+const char* nmtg_attn_fwd(const AttnDesc* d, cudaStream_t stream);
+const char* nmtg_attn_bwd(const AttnDesc* d, cudaStream_t stream);

@@ -1,0 +1,160 @@
+"""Training-step engine: host batch in, loss out, everything in between enqueued on one CUDA stream.
+
+One ``TrainEngine.train_step(batch)`` call performs: async host-to-device copy of the packed integer
+tensors from pinned memory, forward through the fused kernels, backward (weight gradients accumulate
+straight into the flat fp32 buffer), optional data-parallel reduction of that buffer, and the flat
+Adam(W) update.  With ``cuda_graph=True`` and batches of static packed capacity, forward + backward +
+update are captured ONCE into a CUDA graph and replayed per step (inputs are copied into static buffers,
+per-step scalars live in device memory, dropout masks advance through a device-resident seed word), which
+removes per-kernel launch and Python overhead from the step.
+
+The reference's equivalent loop is ``Trainer.train_epoch`` (onmt/train_utils/mp_trainer.py:743-1016):
+``Batch.cuda`` -> autocast forward -> loss -> ``GradScaler.scale(loss).backward()`` (DDP all-reduce inside)
+-> unscale / normalise / clip -> ``optim.step`` -> ``zero_grad``.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .. import ops
+from ..models.layers import PackedSeqs
+from ..parallel.flat import FlatParameterStore
+from .optim import Optim
+
+
+class _StaticInputs:
+    """Device buffers with fixed addresses that a captured graph reads its batch from."""
+
+    def __init__(self, batch, device):
+        src, tgt = batch.packed_source(), batch.packed_target_input()
+        mk = lambda t: torch.empty_like(t, device=device)
+        self.src = PackedSeqs(mk(src.tokens), mk(src.positions), mk(src.cu), src.max_len)
+        self.tgt = PackedSeqs(mk(tgt.tokens), mk(tgt.positions), mk(tgt.cu), tgt.max_len)
+        self.labels = mk(batch.packed_target_output())
+
+    def signature(self):
+        return (self.src.tokens.numel(), self.src.cu.numel(), self.src.max_len, self.tgt.tokens.numel(),
+                self.tgt.cu.numel(), self.tgt.max_len)
+
+    @staticmethod
+    def signature_of(batch):
+        s, t = batch.packed_source(), batch.packed_target_input()
+        return (s.tokens.numel(), s.cu.numel(), s.max_len, t.tokens.numel(), t.cu.numel(), t.max_len)
+
+    def load(self, batch):
+        s, t = batch.packed_source(), batch.packed_target_input()
+        self.src.tokens.copy_(s.tokens, non_blocking=True)
+        self.src.positions.copy_(s.positions, non_blocking=True)
+        self.src.cu.copy_(s.cu, non_blocking=True)
+        self.tgt.tokens.copy_(t.tokens, non_blocking=True)
+        self.tgt.positions.copy_(t.positions, non_blocking=True)
+        self.tgt.cu.copy_(t.cu, non_blocking=True)
+        self.labels.copy_(batch.packed_target_output(), non_blocking=True)
+
+    # Batch protocol used by the models
+    def packed_source(self):
+        return self.src
+
+    def packed_target_input(self):
+        return self.tgt
+
+    def packed_target_output(self):
+        return self.labels
+
+
+class TrainEngine:
+    def __init__(self, model: torch.nn.Module, opt, device=None, reducer=None, cuda_graph: bool = False,
+                 grad_scale: float = 1.0):
+        self.model = model
+        self.opt = opt
+        self.device = torch.device(device) if device is not None else torch.device(
+            "cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
+        self.on_gpu = self.device.type == "cuda"
+        self.store = FlatParameterStore(model, self.device)
+        for b in model.buffers():
+            b.data = b.data.to(self.device)
+        self.optim = Optim(opt)
+        self.optim.set_parameters(model.parameters(), self.store)
+        self.reducer = reducer            # callable(flat_grad) -> None, data-parallel gradient reduction
+        self.grad_scale = grad_scale
+        self.use_graph = bool(cuda_graph) and self.on_gpu
+        self._graph = None
+        self._static: Optional[_StaticInputs] = None
+        self._static_loss = None
+        self._static_correct = None
+        self.kernel_launches_per_step = 0
+
+    # ---------------------------------------------------------------------------------------------
+    def _forward_backward(self, batch):
+        ops.reset_stream_counter()
+        out = self.model(batch)
+        out["loss"].backward()
+        if not self.optim.fused:
+            pass
+        else:
+            self.store.gather_autograd_grads()   # parameters touched by unfused ops, if any
+        return out["loss"].detach(), out["correct"].detach()
+
+    def _eager_step(self, batch):
+        if self.on_gpu:
+            batch = batch.cuda(self.device, hot_only=True)
+        n0 = ops.LAUNCHES[0]
+        loss, correct = self._forward_backward(batch)
+        if self.reducer is not None:
+            self.reducer(self.store.grad)
+        self.optim.step(self.grad_scale)
+        if not self.optim.fused:
+            self.optim.zero_grad()
+        self.kernel_launches_per_step = ops.LAUNCHES[0] - n0
+        return loss, correct
+
+    def _capture(self, batch):
+        self._static = _StaticInputs(batch, self.device)
+        self._static.load(batch)
+        torch.cuda.synchronize()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(2):      # warm-up outside capture: allocator pools, tensor-map cache, lazy inits
+                self._forward_backward(self._static)
+                if self.reducer is not None:
+                    self.reducer(self.store.grad)
+                self.optim._step += 1
+                self.optim.write_hyper(self.grad_scale)
+                self.optim.launch_fused()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        self._graph = torch.cuda.CUDAGraph()
+        n0 = ops.LAUNCHES[0]
+        with torch.cuda.graph(self._graph):
+            ops.advance_device_seed(self.device.index)
+            loss, correct = self._forward_backward(self._static)
+            if self.reducer is not None:
+                self.reducer(self.store.grad)
+            self.optim.launch_fused()
+        self.kernel_launches_per_step = ops.LAUNCHES[0] - n0   # every replay re-runs exactly these launches
+        self._static_loss, self._static_correct = loss, correct
+
+    def train_step(self, batch):
+        """Runs one optimiser update on ``batch`` (host tensors, ideally pinned).  Returns (loss_sum, n_correct)
+        as 1-element device tensors; reading them is the only synchronisation point."""
+        self.model.train()
+        if not (self.use_graph and self.optim.fused):
+            return self._eager_step(batch)
+        if self._graph is None or self._static.signature() != _StaticInputs.signature_of(batch):
+            self._capture(batch)
+        self._static.load(batch)
+        self.optim._step += 1
+        self.optim.write_hyper(self.grad_scale)
+        self._graph.replay()
+        return self._static_loss, self._static_correct
+
+    @torch.no_grad()
+    def eval_step(self, batch):
+        self.model.eval()
+        if self.on_gpu:
+            batch = batch.cuda(self.device, hot_only=True)
+        out = self.model(batch)
+        return out["loss"], out["correct"]

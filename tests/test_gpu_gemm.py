@@ -1,0 +1,122 @@
+"""tcgen05 GEMM against fp32 matmul: operand layouts, ragged shapes, epilogues, split-K."""
+import pytest
+import torch
+
+from nmtgminor_b200 import ops
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _rel_err(got, want):
+    got, want = got.float(), want.float()
+    return ((got - want).abs().max() / (want.abs().max() + 1e-6)).item()
+
+
+def _status_ok():
+    s = ops.check_status()
+    assert s == 0, "kernel status word = %d (a bounded wait timed out)" % s
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 512), (1000, 1032, 264), (8192, 1024, 1024), (77, 3072, 1024),
+                                   (300, 128, 4096), (4096, 32000, 1024)])
+def test_gemm_k_major(M, N, K):
+    torch.manual_seed(0)
+    a = torch.randn(M, K, device=DEV).bfloat16()
+    b = torch.randn(N, K, device=DEV).bfloat16()
+    out = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+    ops.gemm(a, b, out)
+    torch.cuda.synchronize()
+    _status_ok()
+    want = a.float() @ b.float().t()
+    assert _rel_err(out, want) < 1e-2
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, True), (True, False), (True, True)])
+@pytest.mark.parametrize("M,N,K", [(128, 128, 128), (512, 1024, 640), (1000, 264, 1000), (1024, 4096, 8192)])
+def test_gemm_mn_major(a_mn, b_mn, M, N, K):
+    torch.manual_seed(1)
+    A = torch.randn(M, K, device=DEV).bfloat16()
+    B = torch.randn(N, K, device=DEV).bfloat16()
+    a = A.t().contiguous() if a_mn else A
+    b = B.t().contiguous() if b_mn else B
+    out = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+    ops.gemm(a, b, out, a_mn_major=a_mn, b_mn_major=b_mn)
+    torch.cuda.synchronize()
+    _status_ok()
+    assert _rel_err(out, A.float() @ B.float().t()) < 1e-2
+
+
+@pytest.mark.parametrize("force_bn", [128, 256])
+def test_gemm_tile_widths(force_bn):
+    torch.manual_seed(2)
+    a = torch.randn(640, 512, device=DEV).bfloat16()
+    b = torch.randn(768, 512, device=DEV).bfloat16()
+    out = torch.empty(640, 768, device=DEV, dtype=torch.bfloat16)
+    ops.gemm(a, b, out, force_bn=force_bn)
+    _status_ok()
+    assert _rel_err(out, a.float() @ b.float().t()) < 1e-2
+
+
+@pytest.mark.parametrize("act", [0, 1, 2, 3])
+def test_gemm_bias_act_residual_preact(act):
+    torch.manual_seed(3)
+    M, N, K = 513, 1024, 256
+    a = torch.randn(M, K, device=DEV).bfloat16()
+    b = (torch.randn(N, K, device=DEV) / 16).bfloat16()
+    bias = torch.randn(N, device=DEV).bfloat16()
+    res = torch.randn(M, N, device=DEV).bfloat16()
+    out = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+    pre = torch.empty_like(out)
+    ops.gemm(a, b, out, bias=bias, residual=res, preact=pre, act=act)
+    _status_ok()
+    z = a.float() @ b.float().t() + bias.float()
+    f = [lambda t: t, torch.relu, torch.nn.functional.gelu, torch.nn.functional.silu][act]
+    assert _rel_err(pre, z) < 1e-2
+    assert _rel_err(out, f(z) + res.float()) < 1.5e-2
+
+
+def test_gemm_dropout_epilogue_matches_dropout_kernel():
+    torch.manual_seed(4)
+    M, N, K = 256, 512, 128
+    a = torch.randn(M, K, device=DEV).bfloat16()
+    b = torch.randn(N, K, device=DEV).bfloat16()
+    plain = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+    dropped = torch.empty_like(plain)
+    ops.gemm(a, b, plain)
+    ops.gemm(a, b, dropped, dropout_p=0.25, seed=99, stream_id=3)
+    same_mask = ops.ext().dropout_add(plain, None, 0.25, 99, 3)
+    _status_ok()
+    assert _rel_err(dropped, same_mask) < 1e-2
+    frac = (dropped == 0).float().mean().item()
+    assert abs(frac - 0.25) < 0.02
+
+
+@pytest.mark.parametrize("act,name", [(5, "relu"), (6, "gelu"), (7, "silu")])
+def test_gemm_activation_backward_epilogue(act, name):
+    torch.manual_seed(5)
+    M, N, K = 384, 1024, 256
+    dy = torch.randn(M, K, device=DEV).bfloat16()
+    w = (torch.randn(K, N, device=DEV) / 16).bfloat16()     # dgrad: dh = dy @ w  (w stored [K_red, N])
+    aux = torch.randn(M, N, device=DEV).bfloat16()
+    out = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+    ops.gemm(dy, w, out, b_mn_major=True, aux=aux, act=act)
+    _status_ok()
+    dh = dy.float() @ w.float()
+    x = aux.float().requires_grad_(True)
+    f = {"relu": torch.relu, "gelu": torch.nn.functional.gelu, "silu": torch.nn.functional.silu}[name]
+    f(x).sum().backward()
+    assert _rel_err(out, dh * x.grad) < 1.5e-2
+
+
+@pytest.mark.parametrize("split_k", [0, 1, 4])
+def test_gemm_wgrad_fp32_accumulate_split_k(split_k):
+    torch.manual_seed(6)
+    tokens, n_out, k_in = 4000, 1024, 1024
+    dy = torch.randn(tokens, n_out, device=DEV).bfloat16()
+    x = torch.randn(tokens, k_in, device=DEV).bfloat16()
+    acc = torch.ones(n_out, k_in, device=DEV)
+    ops.gemm(dy, x, acc, a_mn_major=True, b_mn_major=True, accumulate=True, allow_split_k=True, split_k=split_k)
+    _status_ok()
+    want = dy.float().t() @ x.float() + 1.0
+    assert _rel_err(acc, want) < 5e-3
