@@ -1,0 +1,81 @@
+"""Text -> id tensors, optionally with worker processes over byte ranges of the input file.
+
+Each worker seeks to its byte offset, realigns to the next line start, converts lines to id tensors with the
+given dictionary and returns them with their sizes; results are concatenated in file order.  Counterpart of
+the reference's ``Binarizer`` (onmt/data/binarizer.py:19-237) and ``Tokenizer`` (onmt/data/tokenizer.py:22-68).
+"""
+from __future__ import annotations
+
+import multiprocessing as mp
+import os
+from typing import Callable, List, Optional, Tuple
+
+import torch
+
+from .. import constants as C
+
+
+class Tokenizer:
+    """Whitespace (word) or character tokenisation, optional lower-casing; callable on a line."""
+
+    def __init__(self, input_type: str = "word", lower: bool = False):
+        self.input_type, self.lower = input_type, lower
+
+    def __call__(self, line: str) -> List[str]:
+        line = line.strip()
+        if self.lower:
+            line = line.lower()
+        if self.input_type == "word":
+            return line.split()
+        if self.input_type == "char":
+            return list(line)
+        raise ValueError("unknown input type %r" % self.input_type)
+
+    tokenize = __call__
+
+
+def find_offsets(path: str, n_chunks: int) -> List[int]:
+    size = os.path.getsize(path)
+    offs = [0]
+    with open(path, "rb") as fh:
+        for i in range(1, n_chunks):
+            fh.seek(size * i // n_chunks)
+            fh.readline()                      # move to the next line start
+            offs.append(min(fh.tell(), size))
+    offs.append(size)
+    return offs
+
+
+def binarize_range(path: str, vocab, tokenizer: Callable, start: int, end: int, bos_word: Optional[str],
+                   eos_word: Optional[str], external=None) -> Tuple[List[torch.Tensor], List[int]]:
+    data, sizes = [], []
+    with open(path, "rb") as fh:
+        fh.seek(start)
+        while fh.tell() < end:
+            raw = fh.readline()
+            if not raw:
+                break
+            line = raw.decode("utf-8")
+            if external is not None:
+                ids = torch.tensor(external(line.strip()), dtype=torch.int64)
+            else:
+                ids = vocab.convert_to_idx(tokenizer(line), C.UNK_WORD, bos_word, eos_word)
+            data.append(ids)
+            sizes.append(int(ids.numel()))
+    return data, sizes
+
+
+def binarize_file(path: str, vocab, tokenizer: Optional[Callable] = None, bos_word: Optional[str] = None,
+                  eos_word: Optional[str] = None, num_workers: int = 1, external=None):
+    tokenizer = tokenizer or Tokenizer()
+    if num_workers <= 1 or external is not None:
+        data, sizes = binarize_range(path, vocab, tokenizer, 0, os.path.getsize(path), bos_word, eos_word, external)
+        return {"data": data, "sizes": sizes}
+    offs = find_offsets(path, num_workers)
+    with mp.get_context("spawn").Pool(num_workers) as pool:
+        jobs = [pool.apply_async(binarize_range, (path, vocab, tokenizer, offs[i], offs[i + 1], bos_word, eos_word))
+                for i in range(num_workers)]
+        parts = [j.get() for j in jobs]
+    data = [t for p in parts for t in p[0]]
+    sizes = [s for p in parts for s in p[1]]
+    return {"data": data, "sizes": sizes}

@@ -1,0 +1,200 @@
+"""Per-kernel micro-benchmarks on the shapes of the Transformer-big training step.
+
+    python -m nmtgminor_b200.ops.bench_kernels [--json out.json] [--only gemm,attn,...]
+
+Each kernel is timed with CUDA events after warm-up; between timed launches a 256 MB buffer is rewritten so
+the 126 MB L2 starts cold.  GEMMs report TFLOP/s next to ``torch.matmul`` (cuBLAS) on the same shape as a
+yardstick; memory-bound kernels report GB/s of their algorithmic traffic.  When ``MEASURED_PEAKS.json`` sits
+at the repository root the fractions "of measured" peak are printed as well.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+import torch
+
+from .. import ops
+
+_FLUSH = None
+
+
+def _flush_l2():
+    global _FLUSH
+    if _FLUSH is None:
+        _FLUSH = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    _FLUSH.add_(1)
+
+
+def time_ms(fn, iters=10, warmup=3, flush=True):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    total = 0.0
+    for _ in range(iters):
+        if flush:
+            _flush_l2()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        total += e0.elapsed_time(e1)
+    return total / iters
+
+
+def peaks():
+    root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    try:
+        with open(os.path.join(root, "MEASURED_PEAKS.json")) as fh:
+            p = json.load(fh)
+        return p["bf16_tflops"], p["hbm_gbs"], "measured"
+    except (OSError, KeyError, ValueError):
+        return 1590.0, 6650.0, "fallback"
+
+
+def bench_gemm(rows):
+    T, H, F, V = 8192, 1024, 4096, 32000
+    dev = "cuda"
+    shapes = [
+        ("qkv fwd", T, 3 * H, H, False, False, "bf16"), ("out fwd", T, H, H, False, False, "bf16"),
+        ("fc1 fwd", T, F, H, False, False, "bf16"), ("fc2 fwd", T, H, F, False, False, "bf16"),
+        ("generator fwd", T, V, H, False, False, "bf16"),
+        ("fc1 dgrad", T, H, F, False, True, "bf16"), ("fc2 dgrad", T, F, H, False, True, "bf16"),
+        ("qkv dgrad", T, H, 3 * H, False, True, "bf16"), ("generator dgrad", T, H, V, False, True, "bf16"),
+        ("fc1 wgrad", F, H, T, True, True, "fp32"), ("fc2 wgrad", H, F, T, True, True, "fp32"),
+        ("out wgrad", H, H, T, True, True, "fp32"), ("qkv wgrad", 3 * H, H, T, True, True, "fp32"),
+        ("generator wgrad", V, H, T, True, True, "fp32"),
+    ]
+    for name, M, N, K, a_mn, b_mn, odt in shapes:
+        a = torch.randn((K, M) if a_mn else (M, K), device=dev).bfloat16()
+        b = torch.randn((K, N) if b_mn else (N, K), device=dev).bfloat16()
+        out = torch.zeros(M, N, device=dev, dtype=torch.float32 if odt == "fp32" else torch.bfloat16)
+        acc = odt == "fp32"
+        ms = time_ms(lambda: ops.gemm(a, b, out, a_mn_major=a_mn, b_mn_major=b_mn, accumulate=acc, allow_split_k=acc))
+        A = a.t() if a_mn else a
+        Bt = b if b_mn else b.t()
+        ref = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+        ms_ref = time_ms(lambda: torch.matmul(A, Bt, out=ref))
+        fl = 2.0 * M * N * K
+        rows.append({"kernel": "gemm " + name, "shape": [M, N, K], "ms": ms, "tflops": fl / ms / 1e9,
+                     "cublas_ms": ms_ref, "cublas_tflops": fl / ms_ref / 1e9})
+
+
+def bench_mlp_epilogues(rows):
+    T, H, F = 8192, 1024, 4096
+    x = torch.randn(T, H, device="cuda").bfloat16()
+    w1 = torch.randn(F, H, device="cuda").bfloat16()
+    b1 = torch.randn(F, device="cuda").bfloat16()
+    h = torch.empty(T, F, device="cuda", dtype=torch.bfloat16)
+    res = torch.randn(T, H, device="cuda").bfloat16()
+    w2 = torch.randn(H, F, device="cuda").bfloat16()
+    b2 = torch.randn(H, device="cuda").bfloat16()
+    y = torch.empty(T, H, device="cuda", dtype=torch.bfloat16)
+    fl = 2.0 * T * H * F
+    ms = time_ms(lambda: ops.gemm(x, w1, h, bias=b1, act=1, dropout_p=0.1, seed=1, stream_id=1))
+    rows.append({"kernel": "gemm fc1 + bias + relu + dropout", "shape": [T, F, H], "ms": ms, "tflops": fl / ms / 1e9})
+    ms = time_ms(lambda: ops.gemm(h, w2, y, bias=b2, residual=res, dropout_p=0.1, seed=1, stream_id=2))
+    rows.append({"kernel": "gemm fc2 + bias + dropout + residual", "shape": [T, H, F], "ms": ms, "tflops": fl / ms / 1e9})
+    ms = time_ms(lambda: ops.gemm(y, w2, h, b_mn_major=True, aux=h, act=5, alpha=1.1))
+    rows.append({"kernel": "gemm fc2 dgrad + relu'", "shape": [T, F, H], "ms": ms, "tflops": fl / ms / 1e9})
+
+
+def bench_elementwise(rows):
+    T, H, V = 8192, 1024, 32000
+    e = ops.ext()
+    x = torch.randn(T, H, device="cuda").bfloat16()
+    g = torch.ones(H, device="cuda").bfloat16()
+    b = torch.zeros(H, device="cuda").bfloat16()
+    ms = time_ms(lambda: e.layernorm_fwd(x, g, b, 1e-5))
+    rows.append({"kernel": "layernorm fwd", "shape": [T, H], "ms": ms, "gbs": 2 * T * H * 2 / ms / 1e6})
+    y, mean, rstd = e.layernorm_fwd(x, g, b, 1e-5)
+    dg, db = torch.zeros(H, device="cuda"), torch.zeros(H, device="cuda")
+    ms = time_ms(lambda: e.layernorm_bwd(x, x, mean, rstd, g, x, dg, db))
+    rows.append({"kernel": "layernorm bwd (+residual grad)", "shape": [T, H], "ms": ms, "gbs": 4 * T * H * 2 / ms / 1e6})
+    ms = time_ms(lambda: e.dropout_add(x, x, 0.1, 1, 1))
+    rows.append({"kernel": "dropout_add", "shape": [T, H], "ms": ms, "gbs": 3 * T * H * 2 / ms / 1e6})
+    logits = torch.randn(T, V, device="cuda").bfloat16()
+    labels = torch.randint(1, V, (T,), device="cuda")
+    ls = torch.zeros(1, device="cuda")
+    ms = time_ms(lambda: e.xent_fused(logits, labels, 0.1, 0, ls, None, None, 1.0, True), iters=5)
+    rows.append({"kernel": "xent fwd+bwd fused", "shape": [T, V], "ms": ms, "gbs": 2 * T * V * 2 / ms / 1e6})
+    n = 209_087_744 // 4 * 4
+    master, grad, m, v = (torch.zeros(n, device="cuda") for _ in range(4))
+    work = torch.zeros(n, device="cuda", dtype=torch.bfloat16)
+    hyper = torch.zeros(16)
+    hyper[0], hyper[1], hyper[2], hyper[3], hyper[5], hyper[6], hyper[7] = 1e-3, 0.9, 0.997, 1e-9, 0.1, 0.003, 1.0
+    hyper = hyper.cuda()
+    sq = torch.zeros(1, device="cuda")
+    bad = torch.zeros(1, device="cuda", dtype=torch.int32)
+    ms = time_ms(lambda: e.sq_norm(grad, sq, bad), iters=5)
+    rows.append({"kernel": "grad sq-norm (209M)", "shape": [n], "ms": ms, "gbs": n * 4 / ms / 1e6})
+    ms = time_ms(lambda: e.adamw_flat(master, work, grad, m, v, hyper, sq, bad), iters=5)
+    rows.append({"kernel": "adamw flat (209M)", "shape": [n], "ms": ms, "gbs": n * (4 * 4 + 4 * 4 + 2) / ms / 1e6})
+
+
+def bench_attention(rows):
+    import numpy as np
+    rng = np.random.RandomState(0)
+    lens = []
+    while sum(lens) < 8192 - 100:
+        lens.append(int(rng.randint(20, 101)))
+    n = sum(lens)
+    cap = (n + 127) // 128 * 128
+    heads, W = 16, 1024
+    cu = torch.zeros(len(lens) + 1, dtype=torch.int32)
+    cu[1:] = torch.tensor(lens).cumsum(0)
+    cu = cu.cuda()
+    qkv = torch.randn(cap, 3 * W, device="cuda").bfloat16()
+    out = torch.zeros(cap, W, device="cuda", dtype=torch.bfloat16)
+    lse = torch.empty(heads, cap, device="cuda")
+    e = ops.ext()
+    q, k, v = qkv[:, :W], qkv[:, W:2 * W], qkv[:, 2 * W:]
+    for causal in (False, True):
+        ms = time_ms(lambda: e.attn_fwd(q, k, v, out, lse, cu, cu, heads, 100, 100, causal, 0.125, 0.1, 1, 1))
+        fl = sum(4.0 * L * L * 64 * heads for L in lens)
+        rows.append({"kernel": "attention fwd causal=%s (%d seqs, %d tokens)" % (causal, len(lens), n), "ms": ms,
+                     "tflops": fl / ms / 1e9})
+        dqkv = torch.zeros_like(qkv)
+        dout = torch.randn_like(out)
+        ms = time_ms(lambda: e.attn_bwd(q, k, v, out, lse, dout, dqkv[:, :W], dqkv[:, W:2 * W], dqkv[:, 2 * W:], None, cu, cu,
+                                        heads, 100, 100, causal, 0.125, 0.1, 1, 1))
+        rows.append({"kernel": "attention bwd causal=%s" % causal, "ms": ms, "tflops": 2.5 * fl / ms / 1e9})
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--json", default=None)
+    ap.add_argument("--only", default="gemm,mlp,elementwise,attn")
+    args = ap.parse_args()
+    rows = []
+    which = set(args.only.split(","))
+    if "gemm" in which:
+        bench_gemm(rows)
+    if "mlp" in which:
+        bench_mlp_epilogues(rows)
+    if "elementwise" in which:
+        bench_elementwise(rows)
+    if "attn" in which:
+        bench_attention(rows)
+    tf_peak, bw_peak, kind = peaks()
+    for r in rows:
+        line = "%-48s %8.3f ms" % (r["kernel"], r["ms"])
+        if "tflops" in r:
+            line += "  %7.1f TFLOP/s (%.2f of %s bf16 peak)" % (r["tflops"], r["tflops"] / tf_peak, kind)
+        if "cublas_tflops" in r:
+            line += "   cuBLAS %7.1f TFLOP/s" % r["cublas_tflops"]
+        if "gbs" in r:
+            line += "  %7.1f GB/s (%.2f of %s HBM peak)" % (r["gbs"], r["gbs"] / bw_peak, kind)
+        print(line)
+    status = ops.check_status()
+    print("kernel status word:", status)
+    if args.json:
+        with open(args.json, "w") as fh:
+            json.dump({"rows": rows, "status": status, "peaks": {"bf16_tflops": tf_peak, "hbm_gbs": bw_peak, "kind": kind}}, fh, indent=1)
+
+
+if __name__ == "__main__":
+    main()

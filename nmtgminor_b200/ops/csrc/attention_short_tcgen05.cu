@@ -1,0 +1,533 @@
+// Persistent, warp-specialised, software-pipelined attention for sequences that fit ONE 128-row tile
+// (query and key length <= 128: every sentence-level translation batch).  A work item is one
+// (sequence, head) pair; each CTA (one per SM) walks a strided list of items and overlaps, across items,
+//   TMA loads of Q / K / V (/ dO)        - producer warp, multi-slot shared-memory ring
+//   tcgen05 MMAs into TMEM               - MMA warp, issues S(i+1) before the second-stage MMAs of item i
+//   softmax / dS math and the epilogues  - 128-thread groups, thread t = tile row t = TMEM lane t
+// so that per-item latencies (global loads, MMA completion, TMEM reads) are hidden instead of summed, which
+// is what dominates when a sentence has only 20..100 tokens.
+//
+// forward : two softmax groups alternate items (TMEM: S0 S1 | O0 O1), three Q/K/V slots.
+// backward: one group (TMEM: S dP | dQ dK dV), two Q/K/V/dO slots; P and dS are staged once in shared
+//           memory and consumed K-major (dQ = dS K) and MN-major (dV = P^T dO, dK = dS^T Q).
+// MMA reduction lengths are trimmed to the real sequence lengths (multiples of 16).
+// Same numerics, dropout counters and interfaces as the general kernels in attention_tcgen05.cu.
+#include "attention_common.cuh"
+
+namespace b200 {
+
+int num_sms();
+
+struct Item {
+  int q0, q_len, k0, k_len, h;
+  bool valid;
+};
+
+__device__ __forceinline__ Item get_item(const AttnArgs& p, int item) {
+  Item it;
+  const int b = item / p.num_heads;
+  it.h = item - b * p.num_heads;
+  it.q0 = p.cu_q[b];
+  it.q_len = p.cu_q[b + 1] - it.q0;
+  it.k0 = p.cu_k[b];
+  it.k_len = p.cu_k[b + 1] - it.k0;
+  it.valid = it.q_len > 0 && it.k_len > 0 && it.q_len <= kTile && it.k_len <= kTile;
+  return it;
+}
+
+// ---------------------------------------------------------------------------------------------------
+// forward
+// ---------------------------------------------------------------------------------------------------
+constexpr int kFwdSlots = 3;
+constexpr int kFwdSlotBytes = 3 * kTileBytes;
+constexpr int kFwdShortThreads = 384;
+constexpr int kFwdShortSmem = kFwdSlots * kFwdSlotBytes + 2 * kPBytes + 256 + 1024;
+
+__global__ void __launch_bounds__(kFwdShortThreads, 1)
+attn_fwd_short_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                      const __grid_constant__ CUtensorMap tmap_v, const AttnArgs p, const int num_items) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sSlots = smem;
+  uint8_t* sP = smem + kFwdSlots * kFwdSlotBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + 2 * kPBytes);
+  uint64_t* slot_full = bars;
+  uint64_t* slot_empty = bars + 3;
+  uint64_t* s_full = bars + 6;
+  uint64_t* s_empty = bars + 8;
+  uint64_t* p_full = bars + 10;
+  uint64_t* o_full = bars + 12;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
+  volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < 3; ++i) { mbar_init(&slot_full[i], 1); mbar_init(&slot_empty[i], 1); }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&s_full[i], 1);
+      mbar_init(&s_empty[i], 128);
+      mbar_init(&p_full[i], 128);
+      mbar_init(&o_full[i], 1);
+    }
+    *abort_word = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, 512);
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int it = 0;
+      for (int item = blockIdx.x; item < num_items; item += gridDim.x) {
+        const Item w = get_item(p, item);
+        if (!w.valid) continue;
+        const int slot = it % kFwdSlots;
+        if (!mbar_wait(&slot_empty[slot], ((it / kFwdSlots) & 1) ^ 1, abort_word, p.status, kTimeoutSmemEmpty)) break;
+        uint8_t* s = sSlots + slot * kFwdSlotBytes;
+        mbar_expect_tx(&slot_full[slot], kFwdSlotBytes);
+        tma_load_2d(s, &tmap_q, &slot_full[slot], w.h * kHd, w.q0);
+        tma_load_2d(s + kTileBytes, &tmap_k, &slot_full[slot], w.h * kHd, w.k0);
+        tma_load_2d(s + 2 * kTileBytes, &tmap_v, &slot_full[slot], w.h * kHd, w.k0);
+        ++it;
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc_s = make_idesc_bf16(kTile, kTile, 0, 0);
+      const uint32_t idesc_o = make_idesc_bf16(kTile, kHd, 0, 1);
+      int it = 0;
+      bool have_prev = false, ok = true;
+      int prev_it = 0, prev_klen = 0;
+      auto issue_pv = [&](int j, int k_len) -> bool {
+        const int g = j & 1, slot = j % kFwdSlots;
+        if (!mbar_wait(&p_full[g], (j >> 1) & 1, abort_word, p.status, kTimeoutTmemEmpty)) return false;
+        tc_fence_after_sync();
+        const uint32_t pa = smem_u32(sP + g * kPBytes);
+        const uint32_t va = smem_u32(sSlots + slot * kFwdSlotBytes + 2 * kTileBytes);
+        const uint32_t tO = tmem_base + 256 + g * kHd;
+        const int nk = (k_len + 15) >> 4;
+        for (int k = 0; k < nk; ++k) {
+          const uint64_t ad = make_smem_desc_sw128(pa + (k >> 2) * kTileBytes + (k & 3) * 32, 16, 1024);
+          const uint64_t bd = make_smem_desc_sw128(va + k * 2048, 8192, 1024);
+          umma_bf16(tO, ad, bd, idesc_o, k > 0 ? 1u : 0u);
+        }
+        umma_commit(&o_full[g]);
+        umma_commit(&slot_empty[slot]);
+        return true;
+      };
+      for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
+        const Item w = get_item(p, item);
+        if (!w.valid) continue;
+        const int slot = it % kFwdSlots, g = it & 1;
+        if (!mbar_wait(&slot_full[slot], (it / kFwdSlots) & 1, abort_word, p.status, kTimeoutTmaFull)) { ok = false; break; }
+        if (!mbar_wait(&s_empty[g], ((it >> 1) & 1) ^ 1, abort_word, p.status, kTimeoutTmemEmpty)) { ok = false; break; }
+        tc_fence_after_sync();
+        const uint32_t qa = smem_u32(sSlots + slot * kFwdSlotBytes);
+        umma_steps(tmem_base + g * kTile, qa, 16, 32, qa + kTileBytes, 16, 32, idesc_s, kHd / 16, false);
+        umma_commit(&s_full[g]);
+        if (have_prev) ok = issue_pv(prev_it, prev_klen);
+        have_prev = true;
+        prev_it = it;
+        prev_klen = w.k_len;
+        ++it;
+      }
+      if (ok && have_prev) issue_pv(prev_it, prev_klen);
+    }
+  } else if (warp >= 4) {
+    const int g = (warp - 4) >> 2;
+    const int t = (warp & 3) * 32 + lane;
+    const uint32_t lane_sel = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const uint32_t tS = tmem_base + g * kTile, tO = tmem_base + 256 + g * kHd;
+    uint8_t* myP = sP + g * kPBytes;
+    const bool do_drop = p.dropout_p > 0.f;
+    const Philox rng(p.seed + ((do_drop && p.seed_dev) ? *p.seed_dev : 0ull));
+    const uint32_t thr8 = static_cast<uint32_t>(p.dropout_p * 256.0f + 0.5f);
+    const float keep_scale = do_drop ? 256.0f / static_cast<float>(256 - thr8) : 1.f;
+    int it = 0;
+    for (int item = blockIdx.x; item < num_items; item += gridDim.x) {
+      const Item w = get_item(p, item);
+      if (!w.valid) continue;
+      const int my = ((it & 1) == g);
+      const uint32_t ph = (it >> 1) & 1;
+      ++it;
+      if (!my) continue;
+      if (!mbar_wait(&s_full[g], ph, abort_word, p.status, kTimeoutTmemFull)) break;
+      tc_fence_after_sync();
+      const bool warp_active = (warp & 3) * 32 < w.q_len;
+      const int nchunks = (w.k_len + 31) >> 5;
+      float row_sum = 0.f, row_max = kNegBig;
+      if (warp_active) {
+        for (int c = 0; c < nchunks; ++c) {
+          uint32_t r[32];
+          tmem_ld32(tS + lane_sel + c * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int col = c * 32 + j;
+            const bool valid = col < w.k_len && (!p.causal || col <= t);
+            row_max = fmaxf(row_max, valid ? __uint_as_float(r[j]) * p.scale : kNegBig);
+          }
+        }
+        const unsigned long long dstream = (p.stream_id << 16) | static_cast<unsigned long long>(w.h);
+        uint4 rc = make_uint4(0, 0, 0, 0);
+        unsigned long long rc_ctr = ~0ull;
+        for (int c = 0; c < nchunks; ++c) {
+          uint32_t r[32];
+          tmem_ld32(tS + lane_sel + c * 32, r);
+          tmem_ld_wait();
+          float pv[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int col = c * 32 + j;
+            const bool valid = col < w.k_len && (!p.causal || col <= t);
+            const float e = valid ? __expf(__uint_as_float(r[j]) * p.scale - row_max) : 0.f;
+            row_sum += e;
+            pv[j] = e;
+          }
+          if (do_drop) {
+            const unsigned long long base = static_cast<unsigned long long>(w.q0 + t) * p.kstride + c * 32;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) pv[j] *= keep_factor(rng, dstream, base + j, thr8, keep_scale, rc, rc_ctr);
+          }
+#pragma unroll
+          for (int g4 = 0; g4 < 4; ++g4) {
+            uint4 o;
+            __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) o2[j] = __floats2bfloat162_rn(pv[g4 * 8 + 2 * j], pv[g4 * 8 + 2 * j + 1]);
+            const int chunk = c * 4 + g4;
+            *reinterpret_cast<uint4*>(myP + (chunk >> 3) * kTileBytes + sw128_offset(t, chunk & 7)) = o;
+          }
+        }
+      }
+      tc_fence_before_sync();
+      fence_async_smem();
+      mbar_arrive(&p_full[g]);
+      mbar_arrive(&s_empty[g]);
+      if (!mbar_wait(&o_full[g], ph, abort_word, p.status, kTimeoutTmemFull)) break;
+      tc_fence_after_sync();
+      if (warp_active) {
+        const float inv = row_sum > 0.f ? 1.f / row_sum : 0.f;
+        __nv_bfloat16* orow = p.out + static_cast<size_t>(w.q0 + t) * p.ld_out + w.h * kHd;
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          uint32_t r[32];
+          tmem_ld32(tO + lane_sel + c * 32, r);
+          tmem_ld_wait();
+          if (t < w.q_len) {
+#pragma unroll
+            for (int g4 = 0; g4 < 4; ++g4) {
+              uint4 o;
+              __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+              for (int j = 0; j < 4; ++j)
+                o2[j] = __floats2bfloat162_rn(__uint_as_float(r[g4 * 8 + 2 * j]) * inv, __uint_as_float(r[g4 * 8 + 2 * j + 1]) * inv);
+              reinterpret_cast<uint4*>(orow + c * 32)[g4] = o;
+            }
+          }
+        }
+        if (t < w.q_len && p.lse)
+          p.lse[static_cast<size_t>(w.h) * p.lse_stride + w.q0 + t] = row_sum > 0.f ? row_max + __logf(row_sum) : 0.f;
+      }
+      tc_fence_before_sync();
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_word) {
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------
+// backward
+// ---------------------------------------------------------------------------------------------------
+constexpr int kBwdSlots = 2;
+constexpr int kBwdSlotBytes = 4 * kTileBytes;   // Q, K, V, dO
+constexpr int kBwdShortThreads = 256;
+constexpr int kBwdShortSmem = kBwdSlots * kBwdSlotBytes + 2 * kPBytes + 256 + 1024;
+
+__global__ void __launch_bounds__(kBwdShortThreads, 1)
+attn_bwd_short_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                      const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
+                      const AttnArgs p, const int num_items) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sSlots = smem;
+  uint8_t* sP = smem + kBwdSlots * kBwdSlotBytes;
+  uint8_t* sDS = sP + kPBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sDS + kPBytes);
+  uint64_t* slot_full = bars;        // [2]
+  uint64_t* slot_empty = bars + 2;   // [2]
+  uint64_t* sdp_full = bars + 4;
+  uint64_t* sdp_empty = bars + 5;
+  uint64_t* pds_full = bars + 6;
+  uint64_t* grads_full = bars + 7;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < 2; ++i) { mbar_init(&slot_full[i], 1); mbar_init(&slot_empty[i], 1); }
+    mbar_init(sdp_full, 1);
+    mbar_init(sdp_empty, 128);
+    mbar_init(pds_full, 128);
+    mbar_init(grads_full, 1);
+    *abort_word = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, 512);
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tS = tmem_base, tDP = tmem_base + 128, tDQ = tmem_base + 256, tDK = tmem_base + 320,
+                 tDV = tmem_base + 384;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int it = 0;
+      for (int item = blockIdx.x; item < num_items; item += gridDim.x) {
+        const Item w = get_item(p, item);
+        if (!w.valid) continue;
+        const int slot = it & 1;
+        if (!mbar_wait(&slot_empty[slot], ((it >> 1) & 1) ^ 1, abort_word, p.status, kTimeoutSmemEmpty)) break;
+        uint8_t* s = sSlots + slot * kBwdSlotBytes;
+        mbar_expect_tx(&slot_full[slot], kBwdSlotBytes);
+        tma_load_2d(s, &tmap_q, &slot_full[slot], w.h * kHd, w.q0);
+        tma_load_2d(s + kTileBytes, &tmap_k, &slot_full[slot], w.h * kHd, w.k0);
+        tma_load_2d(s + 2 * kTileBytes, &tmap_v, &slot_full[slot], w.h * kHd, w.k0);
+        tma_load_2d(s + 3 * kTileBytes, &tmap_do, &slot_full[slot], w.h * kHd, w.q0);
+        ++it;
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc_s = make_idesc_bf16(kTile, kTile, 0, 0);
+      const uint32_t idesc_dq = make_idesc_bf16(kTile, kHd, 0, 1);
+      const uint32_t idesc_dkv = make_idesc_bf16(kTile, kHd, 1, 1);
+      int it = 0;
+      bool have_prev = false, ok = true;
+      int prev_it = 0, prev_q = 0, prev_k = 0;
+      auto issue_grads = [&](int j, int q_len, int k_len) -> bool {
+        const int slot = j & 1;
+        if (!mbar_wait(pds_full, j & 1, abort_word, p.status, kTimeoutTmemEmpty)) return false;
+        tc_fence_after_sync();
+        const uint32_t base = smem_u32(sSlots + slot * kBwdSlotBytes);
+        const uint32_t qa = base, ka = base + kTileBytes, doa = base + 3 * kTileBytes;
+        const uint32_t pa = smem_u32(sP), dsa = smem_u32(sDS);
+        const int nkq = (q_len + 15) >> 4, nkk = (k_len + 15) >> 4;
+        // dV = P^T dO, dK = dS^T Q : A read MN-major (keys = M, two 64-key slabs), reduction over query rows
+        umma_steps(tDV, pa, kTileBytes, 2048, doa, 8192, 2048, idesc_dkv, nkq, false);
+        umma_steps(tDK, dsa, kTileBytes, 2048, qa, 8192, 2048, idesc_dkv, nkq, false);
+        // dQ = dS K : A K-major (slab per 64 keys), B = K tile MN-major, reduction over keys
+        for (int k = 0; k < nkk; ++k) {
+          const uint64_t ad = make_smem_desc_sw128(dsa + (k >> 2) * kTileBytes + (k & 3) * 32, 16, 1024);
+          const uint64_t bd = make_smem_desc_sw128(ka + k * 2048, 8192, 1024);
+          umma_bf16(tDQ, ad, bd, idesc_dq, k > 0 ? 1u : 0u);
+        }
+        umma_commit(grads_full);
+        umma_commit(&slot_empty[slot]);
+        return true;
+      };
+      for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
+        const Item w = get_item(p, item);
+        if (!w.valid) continue;
+        const int slot = it & 1;
+        if (!mbar_wait(&slot_full[slot], (it >> 1) & 1, abort_word, p.status, kTimeoutTmaFull)) { ok = false; break; }
+        if (!mbar_wait(sdp_empty, (it & 1) ^ 1, abort_word, p.status, kTimeoutTmemEmpty)) { ok = false; break; }
+        tc_fence_after_sync();
+        const uint32_t base = smem_u32(sSlots + slot * kBwdSlotBytes);
+        umma_steps(tS, base, 16, 32, base + kTileBytes, 16, 32, idesc_s, kHd / 16, false);                       // Q K^T
+        umma_steps(tDP, base + 3 * kTileBytes, 16, 32, base + 2 * kTileBytes, 16, 32, idesc_s, kHd / 16, false);  // dO V^T
+        umma_commit(sdp_full);
+        if (have_prev) ok = issue_grads(prev_it, prev_q, prev_k);
+        have_prev = true;
+        prev_it = it;
+        prev_q = w.q_len;
+        prev_k = w.k_len;
+        ++it;
+      }
+      if (ok && have_prev) issue_grads(prev_it, prev_q, prev_k);
+    }
+  } else if (warp >= 4) {
+    const int t = (warp & 3) * 32 + lane;
+    const uint32_t lane_sel = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const bool do_drop = p.dropout_p > 0.f;
+    const Philox rng(p.seed + ((do_drop && p.seed_dev) ? *p.seed_dev : 0ull));
+    const uint32_t thr8 = static_cast<uint32_t>(p.dropout_p * 256.0f + 0.5f);
+    const float keep_scale = do_drop ? 256.0f / static_cast<float>(256 - thr8) : 1.f;
+    int it = 0;
+    for (int item = blockIdx.x; item < num_items; item += gridDim.x) {
+      const Item w = get_item(p, item);
+      if (!w.valid) continue;
+      const uint32_t ph = it & 1;
+      ++it;
+      const bool row_ok = t < w.q_len;
+      float Drow = 0.f, lse = 0.f;
+      if (row_ok) {   // overlaps the S / dP MMAs
+        const uint4* orow = reinterpret_cast<const uint4*>(p.o + static_cast<size_t>(w.q0 + t) * p.ld_o + w.h * kHd);
+        const uint4* drow = reinterpret_cast<const uint4*>(p.d_o + static_cast<size_t>(w.q0 + t) * p.ld_do + w.h * kHd);
+#pragma unroll
+        for (int g4 = 0; g4 < 8; ++g4) {
+          uint4 a = orow[g4], d = drow[g4];
+          const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&a);
+          const __nv_bfloat162* d2 = reinterpret_cast<const __nv_bfloat162*>(&d);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            float2 x = __bfloat1622float2(a2[j]), y = __bfloat1622float2(d2[j]);
+            Drow += x.x * y.x + x.y * y.y;
+          }
+        }
+        lse = p.lse[static_cast<size_t>(w.h) * p.lse_stride + w.q0 + t];
+      }
+      if (!mbar_wait(sdp_full, ph, abort_word, p.status, kTimeoutTmemFull)) break;
+      tc_fence_after_sync();
+      const int nchunks = (w.k_len + 31) >> 5;
+      const int q_rows16 = ((w.q_len + 15) >> 4) << 4;   // rows the MN-major MMAs will read
+      const bool warp_writes = (warp & 3) * 32 < q_rows16;
+      if (warp_writes) {
+        const unsigned long long dstream = (p.stream_id << 16) | static_cast<unsigned long long>(w.h);
+        uint4 rc = make_uint4(0, 0, 0, 0);
+        unsigned long long rc_ctr = ~0ull;
+        for (int c = 0; c < nchunks; ++c) {
+          uint32_t rs[32], rd[32];
+          tmem_ld32(tS + lane_sel + c * 32, rs);
+          tmem_ld32(tDP + lane_sel + c * 32, rd);
+          tmem_ld_wait();
+          float pd[32], ds[32];
+          const unsigned long long base = static_cast<unsigned long long>(w.q0 + t) * p.kstride + c * 32;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int col = c * 32 + j;
+            const bool valid = row_ok && col < w.k_len && (!p.causal || col <= t);
+            const float pr = valid ? __expf(__uint_as_float(rs[j]) * p.scale - lse) : 0.f;
+            float kf = 1.f;
+            if (do_drop) kf = keep_factor(rng, dstream, base + j, thr8, keep_scale, rc, rc_ctr);
+            pd[j] = pr * kf;
+            ds[j] = pr * (__uint_as_float(rd[j]) * kf - Drow) * p.scale;
+          }
+#pragma unroll
+          for (int g4 = 0; g4 < 4; ++g4) {
+            uint4 o1, o2v;
+            __nv_bfloat162* a2 = reinterpret_cast<__nv_bfloat162*>(&o1);
+            __nv_bfloat162* b2 = reinterpret_cast<__nv_bfloat162*>(&o2v);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              a2[j] = __floats2bfloat162_rn(pd[g4 * 8 + 2 * j], pd[g4 * 8 + 2 * j + 1]);
+              b2[j] = __floats2bfloat162_rn(ds[g4 * 8 + 2 * j], ds[g4 * 8 + 2 * j + 1]);
+            }
+            const int chunk = c * 4 + g4;
+            const uint32_t off = (chunk >> 3) * kTileBytes + sw128_offset(t, chunk & 7);
+            *reinterpret_cast<uint4*>(sP + off) = o1;
+            *reinterpret_cast<uint4*>(sDS + off) = o2v;
+          }
+        }
+      }
+      tc_fence_before_sync();
+      fence_async_smem();
+      mbar_arrive(pds_full);
+      mbar_arrive(sdp_empty);
+      if (!mbar_wait(grads_full, ph, abort_word, p.status, kTimeoutTmemFull)) break;
+      tc_fence_after_sync();
+      // dQ row t (queries), dK / dV row t (keys)
+      if ((warp & 3) * 32 < w.q_len) {
+#pragma unroll 1
+        for (int c = 0; c < 2; ++c) {
+          uint32_t r[32];
+          tmem_ld32(tDQ + lane_sel + c * 32, r);
+          tmem_ld_wait();
+          if (row_ok) {
+            __nv_bfloat16* drow = p.dq + static_cast<size_t>(w.q0 + t) * p.ld_dq + w.h * kHd + c * 32;
+#pragma unroll
+            for (int g4 = 0; g4 < 4; ++g4) {
+              uint4 o;
+              __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+              for (int j = 0; j < 4; ++j)
+                o2[j] = __floats2bfloat162_rn(__uint_as_float(r[g4 * 8 + 2 * j]), __uint_as_float(r[g4 * 8 + 2 * j + 1]));
+              reinterpret_cast<uint4*>(drow)[g4] = o;
+            }
+          }
+        }
+      }
+      if ((warp & 3) * 32 < w.k_len) {
+#pragma unroll 1
+        for (int which = 0; which < 2; ++which) {
+          __nv_bfloat16* dst = which == 0 ? p.dk : p.dv;
+          const int ld = which == 0 ? p.ld_dk : p.ld_dv;
+          const uint32_t tsrc = which == 0 ? tDK : tDV;
+#pragma unroll 1
+          for (int c = 0; c < 2; ++c) {
+            uint32_t r[32];
+            tmem_ld32(tsrc + lane_sel + c * 32, r);
+            tmem_ld_wait();
+            if (t < w.k_len) {
+              __nv_bfloat16* drow = dst + static_cast<size_t>(w.k0 + t) * ld + w.h * kHd + c * 32;
+#pragma unroll
+              for (int g4 = 0; g4 < 4; ++g4) {
+                uint4 o;
+                __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                  o2[j] = __floats2bfloat162_rn(__uint_as_float(r[g4 * 8 + 2 * j]), __uint_as_float(r[g4 * 8 + 2 * j + 1]));
+                reinterpret_cast<uint4*>(drow)[g4] = o;
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before_sync();
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_word) {
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+const char* launch_attn_fwd_short(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttnArgs& a,
+                                  int num_items, cudaStream_t stream) {
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t ce = cudaFuncSetAttribute(attn_fwd_short_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kFwdShortSmem);
+    if (ce != cudaSuccess) return cudaGetErrorString(ce);
+    configured = true;
+  }
+  const int grid = num_items < num_sms() ? num_items : num_sms();
+  attn_fwd_short_kernel<<<grid, kFwdShortThreads, kFwdShortSmem, stream>>>(tq, tk, tv, a, num_items);
+  cudaError_t ce = cudaGetLastError();
+  return ce == cudaSuccess ? nullptr : cudaGetErrorString(ce);
+}
+
+const char* launch_attn_bwd_short(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tdo,
+                                  const AttnArgs& a, int num_items, cudaStream_t stream) {
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t ce = cudaFuncSetAttribute(attn_bwd_short_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kBwdShortSmem);
+    if (ce != cudaSuccess) return cudaGetErrorString(ce);
+    configured = true;
+  }
+  const int grid = num_items < num_sms() ? num_items : num_sms();
+  attn_bwd_short_kernel<<<grid, kBwdShortThreads, kBwdShortSmem, stream>>>(tq, tk, tv, tdo, a, num_items);
+  cudaError_t ce = cudaGetLastError();
+  return ce == cudaSuccess ? nullptr : cudaGetErrorString(ce);
+}
+
+}  // namespace b200

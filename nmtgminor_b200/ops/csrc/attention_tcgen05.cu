@@ -19,66 +19,9 @@
 // (onmt/modules/extensions/multihead_attn/self_multihead_attn_cuda.cu:23-612, encdec_multihead_attn_
 // bias_cuda.cu:22-612, softmax_apex.h) and its bundled FlashAttention-v1 mma.sync kernels
 // (onmt/modules/extensions/flashattn/src/fmha_fprop_kernel_1xN.h, fmha_dgrad_kernel_1xN_loop.h).
-#include "b200_ptx.cuh"
-#include "ops_api.h"
+#include "attention_common.cuh"
 
 namespace b200 {
-
-bool cached_tmap(CUtensorMap* out, const void* base, long rows, long cols, long ld, int br, int bc);
-
-constexpr int kHd = 64;          // head dimension
-constexpr int kTile = 128;       // query / key tile
-constexpr int kTileBytes = kTile * kHd * 2;   // 16 KB : one [128 x 64] bf16 tile
-constexpr int kPBytes = kTile * kTile * 2;    // 32 KB : P or dS as two [128 x 64] slabs
-constexpr float kNegBig = -1.0e30f;
-
-struct AttnArgs {
-  const int* cu_q;
-  const int* cu_k;
-  int num_heads;
-  int causal;
-  float scale;
-  float dropout_p;
-  unsigned long long seed, stream_id;
-  const unsigned long long* seed_dev;
-  int kstride;            // multiple of 16, >= longest key sequence: dropout counter stride per query row
-  __nv_bfloat16* out; int ld_out;       // fwd: O ; bwd: unused
-  float* lse; long lse_stride;          // [heads, lse_stride]
-  __nv_bfloat16* p_debug; long p_stride_row;  // optional [heads, total_q, kstride] dropped probabilities
-  // backward
-  const __nv_bfloat16* o; int ld_o;
-  const __nv_bfloat16* d_o; int ld_do;
-  __nv_bfloat16* dq; int ld_dq;
-  __nv_bfloat16* dk; int ld_dk;
-  __nv_bfloat16* dv; int ld_dv;
-  float* dq_acc; int ld_dqacc;          // fp32 accumulation buffer for multi-key-tile sequences
-  int total_q;
-  int* status;
-};
-
-// nk UMMA k-steps reading A from a_addr (+ k * a_step bytes) and B from b_addr (+ k * b_step bytes)
-__device__ __forceinline__ void umma_steps(uint32_t d_tmem, uint32_t a_addr, uint32_t a_lbo, uint32_t a_step,
-                                           uint32_t b_addr, uint32_t b_lbo, uint32_t b_step, uint32_t idesc, int nk,
-                                           bool accumulate_first) {
-  const uint64_t adesc = make_smem_desc_sw128(a_addr, a_lbo, 1024);
-  const uint64_t bdesc = make_smem_desc_sw128(b_addr, b_lbo, 1024);
-  for (int k = 0; k < nk; ++k)
-    umma_bf16(d_tmem, adesc + static_cast<uint64_t>((k * a_step) >> 4), bdesc + static_cast<uint64_t>((k * b_step) >> 4),
-              idesc, (accumulate_first || k > 0) ? 1u : 0u);
-}
-
-__device__ __forceinline__ float keep_factor(const Philox& rng, unsigned long long stream, unsigned long long idx,
-                                             uint32_t thr8, float keep_scale, uint4& cache, unsigned long long& cache_ctr) {
-  const unsigned long long ctr = idx >> 4;
-  if (ctr != cache_ctr) {
-    cache = rng(ctr, stream);
-    cache_ctr = ctr;
-  }
-  const int e = static_cast<int>(idx & 15);
-  const uint32_t w = philox_word(cache, e >> 2);
-  const uint32_t byte = (w >> ((e & 3) * 8)) & 0xFFu;
-  return byte >= thr8 ? keep_scale : 0.f;
-}
 
 // ---------------------------------------------------------------------------------------------------
 // forward
@@ -527,7 +470,17 @@ constexpr int kBwdSmem = 4 * kTileBytes + 2 * kPBytes + 64 + 1024;
 
 }  // namespace b200
 
+namespace b200 {
+const char* launch_attn_fwd_short(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttnArgs& a,
+                                  int num_items, cudaStream_t stream);
+const char* launch_attn_bwd_short(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tdo,
+                                  const AttnArgs& a, int num_items, cudaStream_t stream);
+}  // namespace b200
+
 using namespace b200;
+
+static int g_attn_variant = 0;   // 0 = automatic, 1 = always the general multi-tile kernels
+void nmtg_set_attention_variant(int v) { g_attn_variant = v; }
 
 static const char* check_ptr(const void* p, int ld) {
   if ((reinterpret_cast<uintptr_t>(p) & 15) || (ld % 8)) return "attention: tensors must be 16-byte aligned with ld % 8 == 0";
@@ -552,6 +505,8 @@ const char* nmtg_attn_fwd(const AttnDesc* d, cudaStream_t stream) {
   a.out = reinterpret_cast<__nv_bfloat16*>(d->out); a.ld_out = d->ld_out;
   a.lse = d->lse; a.lse_stride = d->lse_stride;
   a.p_debug = nullptr; a.total_q = d->total_q; a.status = d->status;
+  if (g_attn_variant == 0 && d->max_q <= kTile && d->max_k <= kTile)
+    return launch_attn_fwd_short(tq, tk, tv, a, d->batch * d->num_heads, stream);
   static bool configured = false;
   if (!configured) {
     cudaError_t ce = cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kFwdSmem);
@@ -590,6 +545,8 @@ const char* nmtg_attn_bwd(const AttnDesc* d, cudaStream_t stream) {
   a.dv = reinterpret_cast<__nv_bfloat16*>(d->dv); a.ld_dv = d->ld_dv;
   a.dq_acc = d->dq_acc; a.ld_dqacc = d->ld_dqacc;
   a.total_q = d->total_q; a.status = d->status;
+  if (g_attn_variant == 0 && d->max_q <= kTile && d->max_k <= kTile)
+    return launch_attn_bwd_short(tq, tk, tv, tdo, a, d->batch * d->num_heads, stream);
   static bool configured = false;
   if (!configured) {
     cudaError_t ce = cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kBwdSmem);

@@ -148,6 +148,7 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
 
 // 32 lanes x 32 consecutive fp32 columns -> 32 registers per thread (thread t = TMEM lane base+t).
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  __syncwarp();  // the load is warp-collective (.sync.aligned): reconverge after divergent code first
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
       "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "

@@ -302,6 +302,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("cast_f32_bf16", &cast_f32_bf16);
   m.def("attn_fwd", &attn_fwd);
   m.def("attn_bwd", &attn_bwd);
+  m.def("set_attention_variant", [](int64_t v) { nmtg_set_attention_variant(static_cast<int>(v)); });
   m.def("batch_allocate", &batch_allocate);
   m.def("get_seed_tensor", &get_seed_tensor);
   m.def("read_status", &read_status);

@@ -184,6 +184,33 @@ __global__ void colsum_kernel(const __nv_bfloat16* __restrict__ x, float* __rest
   }
 }
 
+// Wide variant: a warp covers 256 consecutive columns with 16-byte loads (cols % 8 == 0, ld % 8 == 0)
+__global__ void colsum_wide_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ out, int rows, int cols,
+                                   long ld) {
+  __shared__ float part[8][256];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int c0 = blockIdx.x * 256 + lane * 8;
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  if (c0 < cols) {
+    for (int r = blockIdx.y * 8 + warp; r < rows; r += gridDim.y * 8) {
+      float f[8];
+      unpack8(*reinterpret_cast<const uint4*>(x + static_cast<size_t>(r) * ld + c0), f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += f[j];
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) part[warp][lane * 8 + j] = acc[j];
+  __syncthreads();
+  const int c = blockIdx.x * 256 + threadIdx.x;
+  if (c < cols) {
+    float s = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) s += part[w][threadIdx.x];
+    atomicAdd(out + c, s);
+  }
+}
+
 }  // namespace b200
 
 using namespace b200;
@@ -236,6 +263,15 @@ const char* nmtg_embed_bwd(const int64_t* tokens, const int64_t* positions, cons
 const char* nmtg_colsum(const void* x, float* out, int rows, int cols, long ld, cudaStream_t stream) {
   if (rows <= 0 || cols <= 0) return nullptr;
   if (cols % 2 || ld % 2) return "colsum: column count and leading dimension must be even";
+  if (cols % 8 == 0 && ld % 8 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+    dim3 g((cols + 255) / 256, 1);
+    int gy = (num_sms() * 4) / g.x;
+    if (gy < 1) gy = 1;
+    if (gy > (rows + 7) / 8) gy = (rows + 7) / 8;
+    g.y = gy;
+    colsum_wide_kernel<<<g, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(x), out, rows, cols, ld);
+    return last_err();
+  }
   dim3 grid((cols + 63) / 64, 1);
   int gy = (num_sms() * 4) / grid.x;
   if (gy < 1) gy = 1;

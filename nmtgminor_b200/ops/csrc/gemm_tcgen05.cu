@@ -27,7 +27,8 @@ namespace b200 {
 
 constexpr int BM = 128;
 constexpr int BK = 64;
-constexpr int kGemmThreads = 192;
+constexpr int kEpilogueWarps = 8;   // two warps per TMEM lane quarter, interleaved over 32-column chunks
+constexpr int kGemmThreads = 32 * (2 + kEpilogueWarps);
 
 template <int BN>
 struct GemmSmem {
@@ -98,7 +99,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&tmem_full[i], 1);
-      mbar_init(&tmem_empty[i], 128);
+      mbar_init(&tmem_empty[i], 32 * kEpilogueWarps);
     }
     *abort_word = 0;
     mbar_fence_init();
@@ -200,8 +201,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       }
     }
   } else {
-    // ------------------------------- epilogue (4 warps) --------------------------------------
-    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    // ------------------------------- epilogue (8 warps) --------------------------------------
+    const int q = warp & 3;             // TMEM lane quarter this warp may read
+    const int chunk_par = (warp - 2) >> 2;  // 0 / 1: which interleaved half of the column chunks
     const bool do_drop = p.dropout_p > 0.f;
     const Philox rng(p.seed + ((do_drop && p.seed_dev) ? *p.seed_dev : 0ull));
     const uint32_t thr8 = static_cast<uint32_t>(p.dropout_p * 256.0f + 0.5f);
@@ -222,7 +224,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       const int row = m0 + q * 32 + lane;
       const bool row_ok = row < p.M;
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int c = chunk_par; c < BN / 32; c += kEpilogueWarps / 4) {
         const int col0 = n0 + c * 32;
         if (col0 >= p.N) break;  // warp-uniform
         uint32_t r[32];
@@ -271,9 +273,26 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         // activation (forward) or activation-gradient (backward; aux holds h or z)
         if (p.act >= kActReluBwd) {
           const __nv_bfloat16* ap = p.aux + static_cast<size_t>(row) * p.ld_aux + col0;
+          float av[32];
+          if (full_cols && (p.ld_aux & 7) == 0) {
+#pragma unroll
+            for (int g4 = 0; g4 < 4; ++g4) {
+              uint4 u = reinterpret_cast<const uint4*>(ap)[g4];
+              const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                float2 f = __bfloat1622float2(u2[j]);
+                av[g4 * 8 + 2 * j] = f.x;
+                av[g4 * 8 + 2 * j + 1] = f.y;
+              }
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) av[j] = (col0 + j < p.N) ? __bfloat162float(ap[j]) : 0.f;
+          }
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
-            float a = (col0 + j < p.N) ? __bfloat162float(ap[j]) : 0.f;
+            const float a = av[j];
             float g;
             if (p.act == kActReluBwd) g = a > 0.f ? 1.f : 0.f;  // aux = relu output (after dropout)
             else if (p.act == kActGeluBwd) g = gelu_grad(a);

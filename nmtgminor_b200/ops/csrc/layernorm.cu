@@ -108,6 +108,13 @@ ln_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restr
   __syncthreads();
   float* wg = s_acc + warp * 2 * hidden;  // lanes own disjoint columns: plain read-modify-write
   float* wb = wg + hidden;
+  // narrow rows keep the affine-gradient partial sums in registers; wide rows use the shared-memory slice
+  constexpr bool kRegAcc = VPL <= 4;
+  float ag[kRegAcc ? VPL : 1][8], ab[kRegAcc ? VPL : 1][8];
+#pragma unroll
+  for (int i = 0; i < (kRegAcc ? VPL : 1); ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) ag[i][j] = ab[i][j] = 0.f;
 
   for (int row = blockIdx.x * kLnWarps + warp; row < rows; row += gridDim.x * kLnWarps) {
     const uint4* dyr = reinterpret_cast<const uint4*>(dy + static_cast<size_t>(row) * hidden);
@@ -129,11 +136,18 @@ ln_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restr
           float xh0 = (xv.x - mu) * rs, xh1 = (xv.y - mu) * rs;
           xh[i][2 * j] = xh0;
           xh[i][2 * j + 1] = xh1;
-          const int c = vi * 8 + 2 * j;
-          wg[c] += d.x * xh0;
-          wg[c + 1] += d.y * xh1;
-          wb[c] += d.x;
-          wb[c + 1] += d.y;
+          if constexpr (kRegAcc) {
+            ag[i][2 * j] += d.x * xh0;
+            ag[i][2 * j + 1] += d.y * xh1;
+            ab[i][2 * j] += d.x;
+            ab[i][2 * j + 1] += d.y;
+          } else {
+            const int c = vi * 8 + 2 * j;
+            wg[c] += d.x * xh0;
+            wg[c + 1] += d.y * xh1;
+            wb[c] += d.x;
+            wb[c + 1] += d.y;
+          }
           float t0 = d.x * gf.x, t1 = d.y * gf.y;
           dyg[i][2 * j] = t0;
           dyg[i][2 * j + 1] = t1;
@@ -173,6 +187,19 @@ ln_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restr
           o2[j] = __floats2bfloat162_rn(d0, d1);
         }
         dxr[vi] = o;
+      }
+    }
+  }
+  if constexpr (kRegAcc) {
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      const int vi = lane + i * 32;
+      if (vi < nvec) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          wg[vi * 8 + j] = ag[i][j];
+          wb[vi * 8 + j] = ab[i][j];
+        }
       }
     }
   }

@@ -114,3 +114,5 @@ struct AttnDesc {
 };
 const char* nmtg_attn_fwd(const AttnDesc* d, cudaStream_t stream);
 const char* nmtg_attn_bwd(const AttnDesc* d, cudaStream_t stream);
+// 0 = choose automatically (persistent single-tile kernels when max_q, max_k <= 128), 1 = general kernels only
+void nmtg_set_attention_variant(int v);

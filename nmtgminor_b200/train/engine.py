@@ -89,7 +89,8 @@ class TrainEngine:
     # ---------------------------------------------------------------------------------------------
     def _forward_backward(self, batch):
         ops.reset_stream_counter()
-        out = self.model(batch)
+        # the loss gradient is written pre-scaled by the kernel (scale 1): no [tokens, V] rescale pass in backward
+        out = self.model(batch, grad_scale=1.0)
         out["loss"].backward()
         if not self.optim.fused:
             pass
@@ -97,16 +98,17 @@ class TrainEngine:
             self.store.gather_autograd_grads()   # parameters touched by unfused ops, if any
         return out["loss"].detach(), out["correct"].detach()
 
-    def _eager_step(self, batch):
+    def _eager_step(self, batch, update: bool = True):
         if self.on_gpu:
             batch = batch.cuda(self.device, hot_only=True)
         n0 = ops.LAUNCHES[0]
         loss, correct = self._forward_backward(batch)
-        if self.reducer is not None:
-            self.reducer(self.store.grad)
-        self.optim.step(self.grad_scale)
-        if not self.optim.fused:
-            self.optim.zero_grad()
+        if update:
+            if self.reducer is not None:
+                self.reducer(self.store.grad)
+            self.optim.step(self.grad_scale)
+            if not self.optim.fused:
+                self.optim.zero_grad()
         self.kernel_launches_per_step = ops.LAUNCHES[0] - n0
         return loss, correct
 
@@ -137,12 +139,13 @@ class TrainEngine:
         self.kernel_launches_per_step = ops.LAUNCHES[0] - n0   # every replay re-runs exactly these launches
         self._static_loss, self._static_correct = loss, correct
 
-    def train_step(self, batch):
-        """Runs one optimiser update on ``batch`` (host tensors, ideally pinned).  Returns (loss_sum, n_correct)
-        as 1-element device tensors; reading them is the only synchronisation point."""
+    def train_step(self, batch, update: bool = True):
+        """Forward + backward on ``batch`` (host tensors, ideally pinned) and, when ``update`` is set, gradient
+        reduction + one optimiser update (``update=False`` only accumulates gradients).  Returns (loss_sum,
+        n_correct) as 1-element device tensors; reading them is the only synchronisation point."""
         self.model.train()
-        if not (self.use_graph and self.optim.fused):
-            return self._eager_step(batch)
+        if not (self.use_graph and self.optim.fused) or not update:
+            return self._eager_step(batch, update)
         if self._graph is None or self._static.signature() != _StaticInputs.signature_of(batch):
             self._capture(batch)
         self._static.load(batch)

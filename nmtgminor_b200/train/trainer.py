@@ -1,0 +1,235 @@
+"""Per-rank trainer: builds the model, runs epochs, validates, checkpoints, logs.
+
+One process per GPU.  The step itself is ``TrainEngine.train_step`` (fused kernels, flat optimiser, optional
+CUDA graph); this class adds what surrounds it: process-group set-up, data iterators sharded by rank,
+gradient accumulation over ``update_frequency`` micro-batches, token-normalised gradients
+(``-normalize_gradient``), periodic validation and checkpointing (``-save_every``, ``-keep_save_files``,
+``-save_metrics``), rank-0 logging of perplexity / learning rate / tokens per second, heartbeat for the
+failure watchdog, and resume from a checkpoint (model, optimiser moments, update count, iterator position).
+
+Reference behaviour: onmt/train_utils/mp_trainer.py:152-414 (set-up), :512-560 (save), :562-671 (eval),
+:673-1160 (train_epoch), :1519-1690 (run).
+"""
+from __future__ import annotations
+
+import math
+import os
+import time
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from .. import ops
+from ..data.iterator import DataIterator, MultiDataIterator
+from ..models.factory import build_model
+from ..parallel.ddp import broadcast_parameters, make_reducer
+from ..utils.logging import Logger
+from .checkpoint import checkpoint_name, load_model_state, prune_checkpoints, save_checkpoint
+from .engine import TrainEngine
+
+
+def _is_list(x):
+    return isinstance(x, (list, tuple))
+
+
+class Trainer:
+    def __init__(self, device, dicts, opt, constants=None, setup_optimizer: bool = True, init_distributed: bool = True):
+        self.opt = opt
+        self.dicts = dicts
+        self.constants = constants
+        self.world_size = len(opt.gpus) if getattr(opt, "gpus", None) else int(os.environ.get("WORLD_SIZE", "1"))
+        self.rank = int(os.environ.get("RANK", device if isinstance(device, int) else 0)) if self.world_size > 1 else 0
+        self.cuda = torch.cuda.is_available() and (getattr(opt, "gpus", None) not in (None, [], [-1]))
+        if self.cuda:
+            local = int(os.environ.get("LOCAL_RANK", device if isinstance(device, int) else 0))
+            torch.cuda.set_device(local)
+            self.device = torch.device("cuda", local)
+        else:
+            self.device = torch.device("cpu")
+        if self.world_size > 1 and init_distributed and not dist.is_initialized():
+            os.environ.setdefault("MASTER_ADDR", getattr(opt, "master_addr", "127.0.0.1") or "127.0.0.1")
+            os.environ.setdefault("MASTER_PORT", str(getattr(opt, "master_port", "8888")))
+            dist.init_process_group("nccl" if self.cuda else "gloo", rank=self.rank, world_size=self.world_size)
+        self.log = Logger(self.rank == 0)
+        torch.manual_seed(getattr(opt, "seed", 9999))
+        ops.manual_seed(getattr(opt, "seed", 9999) + 7919 * self.rank)
+
+        self.log("[INFO] Building model ...")
+        self.model = build_model(opt, dicts, constants=constants)
+        n_params = sum(p.numel() for p in self.model.parameters() if p.requires_grad)
+        self.log("[INFO] Total number of trainable parameters: %d" % n_params)
+        checkpoint = None
+        if getattr(opt, "load_from", ""):
+            from .checkpoint import load_checkpoint
+            checkpoint = load_checkpoint(opt.load_from)
+            load_model_state(self.model, checkpoint["model"], verbose=self.rank == 0)
+        self._resume_checkpoint = checkpoint
+
+        grad_scale = 1.0
+        self.engine = TrainEngine(self.model, opt, self.device, reducer=None,
+                                  cuda_graph=getattr(opt, "cuda_graph", False) and getattr(opt, "update_frequency", 1) == 1,
+                                  grad_scale=grad_scale)
+        if self.world_size > 1:
+            mode = "nccl" if getattr(opt, "nccl_ddp", False) else "fused"
+            self.engine.reducer = make_reducer(self.world_size, mode, self.engine.store, self.engine.optim)
+            broadcast_parameters(self.engine.store)
+        self.optim = self.engine.optim
+        if checkpoint is not None and not getattr(opt, "reset_optim", False) and checkpoint.get("optim") is not None:
+            try:
+                self.optim.load_state_dict(checkpoint["optim"])
+            except Exception as exc:  # noqa: BLE001
+                self.log("[WARN] optimiser state not restored: %r" % (exc,))
+        self.start_time = time.time()
+        self.watchdog = None
+        if getattr(opt, "watchdog_timeout", 0) and self.world_size > 1:
+            from ..utils.watchdog import Heartbeat
+            self.watchdog = Heartbeat(self.rank, self.world_size, timeout=opt.watchdog_timeout)
+
+    # ------------------------------------------------------------------------------------------
+    def is_main(self):
+        return self.rank == 0
+
+    def _all_reduce_scalars(self, values):
+        if self.world_size <= 1:
+            return values
+        t = torch.tensor(values, dtype=torch.float64, device=self.device)
+        dist.all_reduce(t)
+        return t.tolist()
+
+    def _iterator(self, data, epoch, seed_offset=0, shuffle=True):
+        kw = dict(seed=getattr(self.opt, "seed", 9999) + seed_offset, num_workers=getattr(self.opt, "num_workers", 0),
+                  epoch=epoch, buffer_size=getattr(self.opt, "buffer_size", 0), num_shards=self.world_size,
+                  shard_id=self.rank, split_even=True, pin_memory=self.cuda, shuffle=shuffle)
+        if _is_list(data):
+            return MultiDataIterator(list(data), **kw)
+        return DataIterator(data, **kw)
+
+    # ------------------------------------------------------------------------------------------
+    @torch.no_grad()
+    def eval(self, data):
+        """Validation loss per target token and token accuracy over all ranks."""
+        if data is None:
+            return float("nan"), 0.0
+        self.model.eval()
+        tot_loss = tot_words = tot_correct = 0.0
+        for ds in (data if _is_list(data) else [data]):
+            it = DataIterator(ds, num_shards=self.world_size, shard_id=self.rank, split_even=False, shuffle=False,
+                              pin_memory=self.cuda).next_epoch_itr()
+            for batch in it:
+                loss, correct = self.engine.eval_step(batch)
+                tot_loss += float(loss)
+                tot_correct += float(correct)
+                tot_words += batch.tgt_size
+        tot_loss, tot_words, tot_correct = self._all_reduce_scalars([tot_loss, tot_words, tot_correct])
+        self.model.train()
+        return tot_loss / max(tot_words, 1.0), tot_correct / max(tot_words, 1.0)
+
+    def save(self, epoch: float, valid_ppl: float, itr=None, accuracy: float = 0.0):
+        if not self.is_main():
+            return None
+        opt = self.opt
+        metric = getattr(opt, "save_metrics", "ppl")
+        value = valid_ppl if metric in ("ppl", "perplexity") else (1.0 - accuracy if metric == "accuracy" else valid_ppl)
+        name = checkpoint_name(opt.save_model, "ppl", value, epoch)
+        os.makedirs(os.path.dirname(os.path.abspath(name)), exist_ok=True)
+        save_checkpoint(name, self.model, self.dicts, opt, epoch, self.optim, itr.state_dict() if itr is not None else None)
+        prune_checkpoints(opt.save_model, getattr(opt, "keep_save_files", 5), "ppl")
+        self.log("[INFO] Saved checkpoint %s" % name)
+        return name
+
+    # ------------------------------------------------------------------------------------------
+    def train_epoch(self, train_data, valid_data, epoch: int, resume_itr_state=None):
+        opt = self.opt
+        iterator = self._iterator(train_data, epoch)
+        if resume_itr_state is not None:
+            iterator.load_state_dict(resume_itr_state)
+        epoch_itr = iterator.next_epoch_itr()
+        n_batches = len(iterator)
+        update_frequency = max(1, getattr(opt, "update_frequency", 1))
+        log_interval = max(1, getattr(opt, "log_interval", 100))
+        report = {"loss": 0.0, "tgt": 0.0, "src": 0.0, "sents": 0.0}
+        epoch_loss = epoch_words = 0.0
+        pending = []          # device loss tensors of the current logging window (read once per window)
+        acc_words = 0
+        t_window = time.time()
+        counter = 0
+        self.model.train()
+        for i, batch in enumerate(epoch_itr):
+            counter += 1
+            update = counter >= update_frequency or i == n_batches - 1
+            acc_words += batch.tgt_size
+            if update and getattr(opt, "normalize_gradient", False):
+                total_words = self._all_reduce_scalars([float(acc_words)])[0]
+                self.engine.grad_scale = 1.0 / max(total_words, 1.0)
+            loss, _ = self.engine.train_step(batch, update=update)
+            pending.append(loss if self.engine.use_graph is False else loss.clone())
+            report["tgt"] += batch.tgt_size
+            report["src"] += batch.src_size
+            report["sents"] += batch.size
+            if update:
+                counter, acc_words = 0, 0
+                if self.watchdog is not None:
+                    self.watchdog.beat(self.optim._step)
+                n_up = self.optim._step
+                save_every = getattr(opt, "save_every", 0)
+                if save_every and save_every > 0 and n_up % save_every == 0:
+                    vloss, vacc = self.eval(valid_data)
+                    vppl = math.exp(min(vloss, 100)) if vloss == vloss else float("nan")
+                    self.log("Validation perplexity: %g  accuracy: %.4f" % (vppl, vacc))
+                    self.save(epoch - 1 + (i + 1) / max(n_batches, 1), vppl, iterator, vacc)
+                max_step = getattr(opt, "max_step", 0)
+                if max_step and n_up >= max_step:
+                    self.log("[INFO] Reached the maximum number of updates (%d)" % max_step)
+                    break
+            if (i + 1) % log_interval == 0 or i == n_batches - 1:
+                window_loss = float(torch.stack([p.reshape(()) for p in pending]).sum()) if pending else 0.0
+                pending = []
+                vals = self._all_reduce_scalars([window_loss, report["tgt"], report["src"]])
+                dt = max(time.time() - t_window, 1e-9)
+                epoch_loss += vals[0]
+                epoch_words += vals[1]
+                status = ops.check_status() if self.cuda and ops.extension_available() else 0
+                if status:
+                    raise RuntimeError("a device kernel gave up waiting (status %d); aborting the run" % status)
+                self.log("Epoch %2d, %5d/%5d; ppl: %8.2f ; lr: %.7f ; num updates: %7d ; %5.0f src tok/s; %5.0f tgt tok/s; %s elapsed"
+                         % (epoch, i + 1, n_batches, math.exp(min(vals[0] / max(vals[1], 1.0), 100)), self.optim.current_lr(),
+                            self.optim._step, vals[2] / dt, vals[1] / dt, _fmt_time(time.time() - self.start_time)))
+                report = {"loss": 0.0, "tgt": 0.0, "src": 0.0, "sents": 0.0}
+                t_window = time.time()
+        return epoch_loss / max(epoch_words, 1.0), iterator
+
+    def run(self, checkpoint=None, train_data=None, valid_data=None):
+        opt = self.opt
+        checkpoint = checkpoint if checkpoint is not None else self._resume_checkpoint
+        start_epoch, resume_itr = 1, None
+        if checkpoint is not None and not getattr(opt, "reset_optim", False):
+            start_epoch = int(math.floor(checkpoint.get("epoch", 0))) + 1
+            resume_itr = checkpoint.get("itr")
+            if resume_itr is not None and resume_itr.get("iterations_in_epoch", 0) > 0:
+                start_epoch = int(resume_itr.get("epoch", start_epoch))
+        if getattr(opt, "run_validation_before_training", False) or getattr(opt, "max_step", 1) is not None and getattr(opt, "max_step", 1) < 0:
+            vloss, vacc = self.eval(valid_data)
+            self.log("Validation perplexity: %g  accuracy: %.4f" % (math.exp(min(vloss, 100)), vacc))
+        self.start_time = time.time()
+        last = None
+        for epoch in range(start_epoch, start_epoch + getattr(opt, "epochs", 1)):
+            train_loss, iterator = self.train_epoch(train_data, valid_data, epoch, resume_itr)
+            resume_itr = None
+            self.log("Train perplexity: %g" % math.exp(min(train_loss, 100)))
+            vloss, vacc = self.eval(valid_data)
+            vppl = math.exp(min(vloss, 100)) if vloss == vloss else float("nan")
+            self.log("Validation perplexity: %g  accuracy: %.4f" % (vppl, vacc))
+            last = self.save(float(epoch), vppl if vppl == vppl else math.exp(min(train_loss, 100)), None, vacc)
+            self.optim.update_epoch(epoch)
+            max_step = getattr(opt, "max_step", 0)
+            if max_step and self.optim._step >= max_step:
+                break
+        if self.watchdog is not None:
+            self.watchdog.stop()
+        return last
+
+
+def _fmt_time(sec: float) -> str:
+    sec = int(sec)
+    return "%02d:%02d:%02d" % (sec // 3600, (sec // 60) % 60, sec % 60)

@@ -9,6 +9,14 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda"
 
 
+@pytest.fixture(params=[0, 1], ids=["auto", "general"])
+def variant(request):
+    """0 = automatic choice (persistent single-tile kernels up to 128 tokens), 1 = general kernels only."""
+    ops.ext().set_attention_variant(request.param)
+    yield request.param
+    ops.ext().set_attention_variant(0)
+
+
 def _cu(lengths):
     cu = torch.zeros(len(lengths) + 1, dtype=torch.int32)
     cu[1:] = torch.tensor(lengths).cumsum(0)
@@ -20,9 +28,10 @@ def _err(a, b):
     return ((a - b).abs().max() / (b.abs().max() + 1e-6)).item()
 
 
-@pytest.mark.parametrize("lengths", [[5], [128], [20, 100, 37, 64, 1], [129, 200, 77], [300, 17]])
+@pytest.mark.parametrize("lengths", [[5], [128], [20, 100, 37, 64, 1], [16, 17, 31, 32, 33, 63, 64, 65, 96, 97, 127, 2, 3],
+                                     [129, 200, 77], [300, 17], [0, 12, 0, 40]])
 @pytest.mark.parametrize("causal", [False, True])
-def test_self_attention_fwd_bwd(lengths, causal):
+def test_self_attention_fwd_bwd(lengths, causal, variant):
     torch.manual_seed(0)
     heads, W = 4, 256
     n = sum(lengths)
@@ -48,8 +57,9 @@ def test_self_attention_fwd_bwd(lengths, causal):
         assert g[n:].abs().max().item() == 0
 
 
-@pytest.mark.parametrize("lq,lk", [([7, 30], [50, 3]), ([100, 64, 12], [128, 129, 260]), ([140], [20])])
-def test_cross_attention_fwd_bwd(lq, lk):
+@pytest.mark.parametrize("lq,lk", [([7, 30], [50, 3]), ([100, 64, 12, 33], [128, 17, 99, 1]), ([100, 64, 12], [128, 129, 260]),
+                                   ([140], [20])])
+def test_cross_attention_fwd_bwd(lq, lk, variant):
     torch.manual_seed(1)
     heads, W = 2, 128
     nq, nk = sum(lq), sum(lk)
@@ -69,7 +79,28 @@ def test_cross_attention_fwd_bwd(lq, lk):
     assert _err(kv.grad, kv32.grad) < 3e-2
 
 
-def test_attention_dropout_is_replayed_in_backward():
+def test_many_items_per_cta_pipeline():
+    """More (sequence, head) items than SMs so every persistent CTA walks several items."""
+    torch.manual_seed(5)
+    import numpy as np
+    rng = np.random.RandomState(0)
+    lengths = [int(v) for v in rng.randint(1, 101, size=200)]
+    heads, W = 8, 512
+    n = sum(lengths)
+    cu = _cu(lengths)
+    qkv = torch.randn(n, 3 * W, device=DEV).bfloat16().requires_grad_(True)
+    out = ops.self_attention(qkv, cu, heads, 100, causal=True, dropout_p=0.0, training=True)
+    dout = torch.randn(n, W, device=DEV).bfloat16()
+    out.backward(dout)
+    assert ops.check_status() == 0
+    q32 = qkv.detach().float().requires_grad_(True)
+    o_ref = ref.attention(q32[:, :W], q32[:, W:2 * W], q32[:, 2 * W:], cu, cu, heads, True, 0.0)
+    o_ref.backward(dout.float())
+    assert _err(out, o_ref) < 2e-2
+    assert _err(qkv.grad, q32.grad) < 3e-2
+
+
+def test_attention_dropout_is_replayed_in_backward(variant):
     """With dropout the op must stay a deterministic function of (seed, stream): finite differences of the
     forward agree with the analytic backward only if backward regenerates the forward mask."""
     torch.manual_seed(2)
