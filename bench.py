@@ -182,14 +182,8 @@ def run_ours(args, rank, local, world):
     d = synthetic_dict(VOCAB)
     model = Transformer(opt, {"src": d, "tgt": d})
     n_params = sum(p.numel() for p in model.parameters())
-    reducer = None
-    if world > 1:
-        from nmtgminor_b200.parallel.ddp import make_reducer
-        reducer = make_reducer(world, mode=args.ddp)
-    engine = TrainEngine(model, opt, device="cuda:%d" % local, reducer=reducer, cuda_graph=not args.no_graph)
-    if world > 1:
-        from nmtgminor_b200.parallel.ddp import broadcast_parameters
-        broadcast_parameters(engine.store)
+    engine = TrainEngine(model, opt, device="cuda:%d" % local, cuda_graph=not args.no_graph,
+                         ddp=(args.ddp if world > 1 else None))
 
     groups = sentence_groups(N_DISTINCT_BATCHES, seed=1000 + rank)
     up = lambda v: (v + 127) // 128 * 128

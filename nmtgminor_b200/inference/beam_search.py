@@ -153,7 +153,7 @@ def beam_search(model, batch, cfg: BeamConfig, prefix_tokens: Optional[torch.Ten
             new_pos = pos_scores[src_rows].view(B, C, T + 2).clone()
             new_pos[:, :, step + 1] = lprobs.view(B, K, V)[torch.arange(B, device=device)[:, None], cand_beam, cand_tok]
             all_scores = torch.cat([fin_scores, new_scores], 1)
-            order = all_scores.argsort(1, descending=True, stable=True)[:, :K]
+            order = all_scores.argsort(dim=1, descending=True, stable=True)[:, :K]
             gather3 = order[:, :, None].expand(-1, -1, T + 2)
             fin_tokens = torch.cat([fin_tokens, new_tok], 1).gather(1, gather3)
             fin_pos = torch.cat([fin_pos, new_pos], 1).gather(1, gather3)
@@ -177,7 +177,8 @@ def beam_search(model, batch, cfg: BeamConfig, prefix_tokens: Optional[torch.Ten
         # ---- stopping ------------------------------------------------------------------------------
         best_possible = scores[:, 0] / ((float(T + 1) ** cfg.alpha) if (cfg.normalize and cfg.alpha > 0) else 1.0)
         worst_fin = fin_scores[:, K - 1]
-        done = done | ((fin_count >= K) & ((best_possible <= worst_fin) | ~cfg.normalize)) | ~torch.isfinite(scores[:, 0])
+        stop_early = (best_possible <= worst_fin) if cfg.normalize else torch.ones_like(done)
+        done = done | ((fin_count >= K) & stop_early) | ~torch.isfinite(scores[:, 0])
         scores = torch.where(done[:, None], torch.full_like(scores, float("-inf")), scores)
         if bool(done.all()):
             break

@@ -49,18 +49,15 @@ __device__ __forceinline__ void umma_steps(uint32_t d_tmem, uint32_t a_addr, uin
               idesc, (accumulate_first || k > 0) ? 1u : 0u);
 }
 
-__device__ __forceinline__ float keep_factor(const Philox& rng, unsigned long long stream, unsigned long long idx,
-                                             uint32_t thr8, float keep_scale, uint4& cache, unsigned long long& cache_ctr) {
-  const unsigned long long ctr = idx >> 4;
-  if (ctr != cache_ctr) {
-    cache = rng(ctr, stream);
-    cache_ctr = ctr;
+// Dropout factors (0 or keep scale) for 32 consecutive probabilities starting at element index `base`
+// (a multiple of 4): multiplies pv[] in place.
+__device__ __forceinline__ void apply_dropout32(const DropRng& rng, unsigned long long base, float (&pv)[32]) {
+#pragma unroll
+  for (int g = 0; g < 8; ++g) {
+    const uint32_t w = rng.word((base >> 2) + g);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) pv[g * 4 + j] = rng.keep(w, j) ? pv[g * 4 + j] * rng.scale : 0.f;
   }
-  const int e = static_cast<int>(idx & 15);
-  const uint32_t w = philox_word(cache, e >> 2);
-  const uint32_t byte = (w >> ((e & 3) * 8)) & 0xFFu;
-  return byte >= thr8 ? keep_scale : 0.f;
 }
-
 
 }  // namespace b200

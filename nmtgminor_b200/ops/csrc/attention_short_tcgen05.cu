@@ -19,8 +19,8 @@ namespace b200 {
 int num_sms();
 
 struct Item {
-  int q0, q_len, k0, k_len, h;
-  bool valid;
+  int q0 = 0, q_len = 0, k0 = 0, k_len = 0, h = 0;
+  bool valid = false;
 };
 
 __device__ __forceinline__ Item get_item(const AttnArgs& p, int item) {
@@ -40,7 +40,7 @@ __device__ __forceinline__ Item get_item(const AttnArgs& p, int item) {
 // ---------------------------------------------------------------------------------------------------
 constexpr int kFwdSlots = 3;
 constexpr int kFwdSlotBytes = 3 * kTileBytes;
-constexpr int kFwdShortThreads = 384;
+constexpr int kFwdShortThreads = 320;   // warps 0-3 / 4-7: softmax groups, warp 8: TMA producer, warp 9: MMA issuer
 constexpr int kFwdShortSmem = kFwdSlots * kFwdSlotBytes + 2 * kPBytes + 256 + 1024;
 
 __global__ void __launch_bounds__(kFwdShortThreads, 1)
@@ -72,13 +72,13 @@ attn_fwd_short_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
     *abort_word = 0;
     mbar_fence_init();
   }
-  if (warp == 1) tmem_alloc(tmem_slot, 512);
+  if (warp == 9) tmem_alloc(tmem_slot, 512);
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 0) {
+  if (warp == 8) {
     if (lane == 0) {
       int it = 0;
       for (int item = blockIdx.x; item < num_items; item += gridDim.x) {
@@ -94,7 +94,7 @@ attn_fwd_short_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
         ++it;
       }
     }
-  } else if (warp == 1) {
+  } else if (warp == 9) {
     if (lane == 0) {
       const uint32_t idesc_s = make_idesc_bf16(kTile, kTile, 0, 0);
       const uint32_t idesc_o = make_idesc_bf16(kTile, kHd, 0, 1);
@@ -136,19 +136,21 @@ attn_fwd_short_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
       }
       if (ok && have_prev) issue_pv(prev_it, prev_klen);
     }
-  } else if (warp >= 4) {
-    const int g = (warp - 4) >> 2;
+  } else if (warp < 8) {
+    const int g = warp >> 2;
     const int t = (warp & 3) * 32 + lane;
     const uint32_t lane_sel = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t tS = tmem_base + g * kTile, tO = tmem_base + 256 + g * kHd;
     uint8_t* myP = sP + g * kPBytes;
     const bool do_drop = p.dropout_p > 0.f;
-    const Philox rng(p.seed + ((do_drop && p.seed_dev) ? *p.seed_dev : 0ull));
-    const uint32_t thr8 = static_cast<uint32_t>(p.dropout_p * 256.0f + 0.5f);
-    const float keep_scale = do_drop ? 256.0f / static_cast<float>(256 - thr8) : 1.f;
+    const unsigned long long seed = p.seed + ((do_drop && p.seed_dev) ? *p.seed_dev : 0ull);
     int it = 0;
-    for (int item = blockIdx.x; item < num_items; item += gridDim.x) {
-      const Item w = get_item(p, item);
+    int item = blockIdx.x;
+    Item nxt = item < num_items ? get_item(p, item) : Item{};
+    while (item < num_items) {
+      const Item w = nxt;
+      item += gridDim.x;
+      if (item < num_items) nxt = get_item(p, item);   // loads for the next item overlap this item's work
       if (!w.valid) continue;
       const int my = ((it & 1) == g);
       const uint32_t ph = (it >> 1) & 1;
@@ -160,46 +162,59 @@ attn_fwd_short_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
       const int nchunks = (w.k_len + 31) >> 5;
       float row_sum = 0.f, row_max = kNegBig;
       if (warp_active) {
-        for (int c = 0; c < nchunks; ++c) {
-          uint32_t r[32];
-          tmem_ld32(tS + lane_sel + c * 32, r);
+        const DropRng rng(seed, (p.stream_id << 16) | static_cast<unsigned long long>(w.h), p.dropout_p);
+        // two column chunks (64 scores) per round: both TMEM loads are in flight before the single wait
+#pragma unroll 1
+        for (int c0 = 0; c0 < nchunks; c0 += 2) {
+          uint32_t r0[32], r1[32];
+          tmem_ld32(tS + lane_sel + c0 * 32, r0);
+          if (c0 + 1 < nchunks) tmem_ld32(tS + lane_sel + (c0 + 1) * 32, r1);
           tmem_ld_wait();
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
-            const int col = c * 32 + j;
+            const int col = c0 * 32 + j;
             const bool valid = col < w.k_len && (!p.causal || col <= t);
-            row_max = fmaxf(row_max, valid ? __uint_as_float(r[j]) * p.scale : kNegBig);
+            row_max = fmaxf(row_max, valid ? __uint_as_float(r0[j]) * p.scale : kNegBig);
+          }
+          if (c0 + 1 < nchunks) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const int col = (c0 + 1) * 32 + j;
+              const bool valid = col < w.k_len && (!p.causal || col <= t);
+              row_max = fmaxf(row_max, valid ? __uint_as_float(r1[j]) * p.scale : kNegBig);
+            }
           }
         }
-        const unsigned long long dstream = (p.stream_id << 16) | static_cast<unsigned long long>(w.h);
-        uint4 rc = make_uint4(0, 0, 0, 0);
-        unsigned long long rc_ctr = ~0ull;
-        for (int c = 0; c < nchunks; ++c) {
-          uint32_t r[32];
-          tmem_ld32(tS + lane_sel + c * 32, r);
+#pragma unroll 1
+        for (int c0 = 0; c0 < nchunks; c0 += 2) {
+          uint32_t r0[32], r1[32];
+          tmem_ld32(tS + lane_sel + c0 * 32, r0);
+          if (c0 + 1 < nchunks) tmem_ld32(tS + lane_sel + (c0 + 1) * 32, r1);
           tmem_ld_wait();
-          float pv[32];
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int col = c * 32 + j;
-            const bool valid = col < w.k_len && (!p.causal || col <= t);
-            const float e = valid ? __expf(__uint_as_float(r[j]) * p.scale - row_max) : 0.f;
-            row_sum += e;
-            pv[j] = e;
-          }
-          if (do_drop) {
-            const unsigned long long base = static_cast<unsigned long long>(w.q0 + t) * p.kstride + c * 32;
+          for (int half = 0; half < 2; ++half) {
+            const int c = c0 + half;
+            if (c >= nchunks) break;
+            float pv[32];
 #pragma unroll
-            for (int j = 0; j < 32; ++j) pv[j] *= keep_factor(rng, dstream, base + j, thr8, keep_scale, rc, rc_ctr);
-          }
+            for (int j = 0; j < 32; ++j) {
+              const int col = c * 32 + j;
+              const bool valid = col < w.k_len && (!p.causal || col <= t);
+              const float sv = __uint_as_float(half == 0 ? r0[j] : r1[j]);
+              const float e = valid ? __expf(sv * p.scale - row_max) : 0.f;
+              row_sum += e;
+              pv[j] = e;
+            }
+            if (do_drop) apply_dropout32(rng, static_cast<unsigned long long>(w.q0 + t) * p.kstride + c * 32, pv);
 #pragma unroll
-          for (int g4 = 0; g4 < 4; ++g4) {
-            uint4 o;
-            __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+            for (int g4 = 0; g4 < 4; ++g4) {
+              uint4 o;
+              __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
 #pragma unroll
-            for (int j = 0; j < 4; ++j) o2[j] = __floats2bfloat162_rn(pv[g4 * 8 + 2 * j], pv[g4 * 8 + 2 * j + 1]);
-            const int chunk = c * 4 + g4;
-            *reinterpret_cast<uint4*>(myP + (chunk >> 3) * kTileBytes + sw128_offset(t, chunk & 7)) = o;
+              for (int j = 0; j < 4; ++j) o2[j] = __floats2bfloat162_rn(pv[g4 * 8 + 2 * j], pv[g4 * 8 + 2 * j + 1]);
+              const int chunk = c * 4 + g4;
+              *reinterpret_cast<uint4*>(myP + (chunk >> 3) * kTileBytes + sw128_offset(t, chunk & 7)) = o;
+            }
           }
         }
       }
@@ -212,25 +227,25 @@ attn_fwd_short_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
       if (warp_active) {
         const float inv = row_sum > 0.f ? 1.f / row_sum : 0.f;
         __nv_bfloat16* orow = p.out + static_cast<size_t>(w.q0 + t) * p.ld_out + w.h * kHd;
+        uint32_t r0[32], r1[32];
+        tmem_ld32(tO + lane_sel, r0);
+        tmem_ld32(tO + lane_sel + 32, r1);
+        tmem_ld_wait();
+        if (t < w.q_len) {
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          uint32_t r[32];
-          tmem_ld32(tO + lane_sel + c * 32, r);
-          tmem_ld_wait();
-          if (t < w.q_len) {
+          for (int g4 = 0; g4 < 8; ++g4) {
+            uint4 o;
+            __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
 #pragma unroll
-            for (int g4 = 0; g4 < 4; ++g4) {
-              uint4 o;
-              __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
-#pragma unroll
-              for (int j = 0; j < 4; ++j)
-                o2[j] = __floats2bfloat162_rn(__uint_as_float(r[g4 * 8 + 2 * j]) * inv, __uint_as_float(r[g4 * 8 + 2 * j + 1]) * inv);
-              reinterpret_cast<uint4*>(orow + c * 32)[g4] = o;
+            for (int j = 0; j < 4; ++j) {
+              const int e = (g4 & 3) * 8 + 2 * j;
+              const float a = __uint_as_float(g4 < 4 ? r0[e] : r1[e]), b = __uint_as_float(g4 < 4 ? r0[e + 1] : r1[e + 1]);
+              o2[j] = __floats2bfloat162_rn(a * inv, b * inv);
             }
+            reinterpret_cast<uint4*>(orow)[g4] = o;
           }
+          if (p.lse) p.lse[static_cast<size_t>(w.h) * p.lse_stride + w.q0 + t] = row_sum > 0.f ? row_max + __logf(row_sum) : 0.f;
         }
-        if (t < w.q_len && p.lse)
-          p.lse[static_cast<size_t>(w.h) * p.lse_stride + w.q0 + t] = row_sum > 0.f ? row_max + __logf(row_sum) : 0.f;
       }
       tc_fence_before_sync();
     }
@@ -242,7 +257,7 @@ attn_fwd_short_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
     for (int i = 0; i < 2000; ++i) __nanosleep(1000);
     __syncthreads();
   }
-  if (warp == 1) {
+  if (warp == 9) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, 512);
   }
@@ -253,7 +268,7 @@ attn_fwd_short_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
 // ---------------------------------------------------------------------------------------------------
 constexpr int kBwdSlots = 2;
 constexpr int kBwdSlotBytes = 4 * kTileBytes;   // Q, K, V, dO
-constexpr int kBwdShortThreads = 256;
+constexpr int kBwdShortThreads = 192;   // warps 0-3: math group, warp 4: TMA producer, warp 5: MMA issuer
 constexpr int kBwdShortSmem = kBwdSlots * kBwdSlotBytes + 2 * kPBytes + 256 + 1024;
 
 __global__ void __launch_bounds__(kBwdShortThreads, 1)
@@ -285,7 +300,7 @@ attn_bwd_short_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
     *abort_word = 0;
     mbar_fence_init();
   }
-  if (warp == 1) tmem_alloc(tmem_slot, 512);
+  if (warp == 5) tmem_alloc(tmem_slot, 512);
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
@@ -293,7 +308,7 @@ attn_bwd_short_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
   const uint32_t tS = tmem_base, tDP = tmem_base + 128, tDQ = tmem_base + 256, tDK = tmem_base + 320,
                  tDV = tmem_base + 384;
 
-  if (warp == 0) {
+  if (warp == 4) {
     if (lane == 0) {
       int it = 0;
       for (int item = blockIdx.x; item < num_items; item += gridDim.x) {
@@ -310,7 +325,7 @@ attn_bwd_short_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
         ++it;
       }
     }
-  } else if (warp == 1) {
+  } else if (warp == 5) {
     if (lane == 0) {
       const uint32_t idesc_s = make_idesc_bf16(kTile, kTile, 0, 0);
       const uint32_t idesc_dq = make_idesc_bf16(kTile, kHd, 0, 1);
@@ -359,16 +374,18 @@ attn_bwd_short_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
       }
       if (ok && have_prev) issue_grads(prev_it, prev_q, prev_k);
     }
-  } else if (warp >= 4) {
-    const int t = (warp & 3) * 32 + lane;
-    const uint32_t lane_sel = static_cast<uint32_t>((warp & 3) * 32) << 16;
+  } else if (warp < 4) {
+    const int t = warp * 32 + lane;
+    const uint32_t lane_sel = static_cast<uint32_t>(warp * 32) << 16;
     const bool do_drop = p.dropout_p > 0.f;
-    const Philox rng(p.seed + ((do_drop && p.seed_dev) ? *p.seed_dev : 0ull));
-    const uint32_t thr8 = static_cast<uint32_t>(p.dropout_p * 256.0f + 0.5f);
-    const float keep_scale = do_drop ? 256.0f / static_cast<float>(256 - thr8) : 1.f;
+    const unsigned long long seed = p.seed + ((do_drop && p.seed_dev) ? *p.seed_dev : 0ull);
     int it = 0;
-    for (int item = blockIdx.x; item < num_items; item += gridDim.x) {
-      const Item w = get_item(p, item);
+    int item = blockIdx.x;
+    Item nxt = item < num_items ? get_item(p, item) : Item{};
+    while (item < num_items) {
+      const Item w = nxt;
+      item += gridDim.x;
+      if (item < num_items) nxt = get_item(p, item);
       if (!w.valid) continue;
       const uint32_t ph = it & 1;
       ++it;
@@ -377,59 +394,72 @@ attn_bwd_short_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
       if (row_ok) {   // overlaps the S / dP MMAs
         const uint4* orow = reinterpret_cast<const uint4*>(p.o + static_cast<size_t>(w.q0 + t) * p.ld_o + w.h * kHd);
         const uint4* drow = reinterpret_cast<const uint4*>(p.d_o + static_cast<size_t>(w.q0 + t) * p.ld_do + w.h * kHd);
+        uint4 a[8], d[8];
+#pragma unroll
+        for (int g4 = 0; g4 < 8; ++g4) { a[g4] = orow[g4]; d[g4] = drow[g4]; }
+        lse = p.lse[static_cast<size_t>(w.h) * p.lse_stride + w.q0 + t];
 #pragma unroll
         for (int g4 = 0; g4 < 8; ++g4) {
-          uint4 a = orow[g4], d = drow[g4];
-          const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&a);
-          const __nv_bfloat162* d2 = reinterpret_cast<const __nv_bfloat162*>(&d);
+          const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&a[g4]);
+          const __nv_bfloat162* d2 = reinterpret_cast<const __nv_bfloat162*>(&d[g4]);
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             float2 x = __bfloat1622float2(a2[j]), y = __bfloat1622float2(d2[j]);
             Drow += x.x * y.x + x.y * y.y;
           }
         }
-        lse = p.lse[static_cast<size_t>(w.h) * p.lse_stride + w.q0 + t];
       }
       if (!mbar_wait(sdp_full, ph, abort_word, p.status, kTimeoutTmemFull)) break;
       tc_fence_after_sync();
       const int nchunks = (w.k_len + 31) >> 5;
       const int q_rows16 = ((w.q_len + 15) >> 4) << 4;   // rows the MN-major MMAs will read
-      const bool warp_writes = (warp & 3) * 32 < q_rows16;
+      const bool warp_writes = warp * 32 < q_rows16;
       if (warp_writes) {
-        const unsigned long long dstream = (p.stream_id << 16) | static_cast<unsigned long long>(w.h);
-        uint4 rc = make_uint4(0, 0, 0, 0);
-        unsigned long long rc_ctr = ~0ull;
-        for (int c = 0; c < nchunks; ++c) {
-          uint32_t rs[32], rd[32];
-          tmem_ld32(tS + lane_sel + c * 32, rs);
-          tmem_ld32(tDP + lane_sel + c * 32, rd);
-          tmem_ld_wait();
-          float pd[32], ds[32];
-          const unsigned long long base = static_cast<unsigned long long>(w.q0 + t) * p.kstride + c * 32;
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int col = c * 32 + j;
-            const bool valid = row_ok && col < w.k_len && (!p.causal || col <= t);
-            const float pr = valid ? __expf(__uint_as_float(rs[j]) * p.scale - lse) : 0.f;
-            float kf = 1.f;
-            if (do_drop) kf = keep_factor(rng, dstream, base + j, thr8, keep_scale, rc, rc_ctr);
-            pd[j] = pr * kf;
-            ds[j] = pr * (__uint_as_float(rd[j]) * kf - Drow) * p.scale;
+        const DropRng rng(seed, (p.stream_id << 16) | static_cast<unsigned long long>(w.h), p.dropout_p);
+#pragma unroll 1
+        for (int c0 = 0; c0 < nchunks; c0 += 2) {
+          uint32_t rs0[32], rd0[32], rs1[32], rd1[32];
+          tmem_ld32(tS + lane_sel + c0 * 32, rs0);
+          tmem_ld32(tDP + lane_sel + c0 * 32, rd0);
+          if (c0 + 1 < nchunks) {
+            tmem_ld32(tS + lane_sel + (c0 + 1) * 32, rs1);
+            tmem_ld32(tDP + lane_sel + (c0 + 1) * 32, rd1);
           }
+          tmem_ld_wait();
 #pragma unroll
-          for (int g4 = 0; g4 < 4; ++g4) {
-            uint4 o1, o2v;
-            __nv_bfloat162* a2 = reinterpret_cast<__nv_bfloat162*>(&o1);
-            __nv_bfloat162* b2 = reinterpret_cast<__nv_bfloat162*>(&o2v);
+          for (int half = 0; half < 2; ++half) {
+            const int c = c0 + half;
+            if (c >= nchunks) break;
+            float kf[32];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              a2[j] = __floats2bfloat162_rn(pd[g4 * 8 + 2 * j], pd[g4 * 8 + 2 * j + 1]);
-              b2[j] = __floats2bfloat162_rn(ds[g4 * 8 + 2 * j], ds[g4 * 8 + 2 * j + 1]);
+            for (int j = 0; j < 32; ++j) kf[j] = 1.f;
+            if (do_drop) apply_dropout32(rng, static_cast<unsigned long long>(w.q0 + t) * p.kstride + c * 32, kf);
+            float pd[32], ds[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const int col = c * 32 + j;
+              const bool valid = row_ok && col < w.k_len && (!p.causal || col <= t);
+              const float sv = __uint_as_float(half == 0 ? rs0[j] : rs1[j]);
+              const float dv = __uint_as_float(half == 0 ? rd0[j] : rd1[j]);
+              const float pr = valid ? __expf(sv * p.scale - lse) : 0.f;
+              pd[j] = pr * kf[j];
+              ds[j] = pr * (dv * kf[j] - Drow) * p.scale;
             }
-            const int chunk = c * 4 + g4;
-            const uint32_t off = (chunk >> 3) * kTileBytes + sw128_offset(t, chunk & 7);
-            *reinterpret_cast<uint4*>(sP + off) = o1;
-            *reinterpret_cast<uint4*>(sDS + off) = o2v;
+#pragma unroll
+            for (int g4 = 0; g4 < 4; ++g4) {
+              uint4 o1, o2v;
+              __nv_bfloat162* a2 = reinterpret_cast<__nv_bfloat162*>(&o1);
+              __nv_bfloat162* b2 = reinterpret_cast<__nv_bfloat162*>(&o2v);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                a2[j] = __floats2bfloat162_rn(pd[g4 * 8 + 2 * j], pd[g4 * 8 + 2 * j + 1]);
+                b2[j] = __floats2bfloat162_rn(ds[g4 * 8 + 2 * j], ds[g4 * 8 + 2 * j + 1]);
+              }
+              const int chunk = c * 4 + g4;
+              const uint32_t off = (chunk >> 3) * kTileBytes + sw128_offset(t, chunk & 7);
+              *reinterpret_cast<uint4*>(sP + off) = o1;
+              *reinterpret_cast<uint4*>(sDS + off) = o2v;
+            }
           }
         }
       }
@@ -439,49 +469,50 @@ attn_bwd_short_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
       mbar_arrive(sdp_empty);
       if (!mbar_wait(grads_full, ph, abort_word, p.status, kTimeoutTmemFull)) break;
       tc_fence_after_sync();
-      // dQ row t (queries), dK / dV row t (keys)
-      if ((warp & 3) * 32 < w.q_len) {
-#pragma unroll 1
-        for (int c = 0; c < 2; ++c) {
-          uint32_t r[32];
-          tmem_ld32(tDQ + lane_sel + c * 32, r);
-          tmem_ld_wait();
-          if (row_ok) {
-            __nv_bfloat16* drow = p.dq + static_cast<size_t>(w.q0 + t) * p.ld_dq + w.h * kHd + c * 32;
+      // dQ row t (queries), dK / dV row t (keys): all TMEM loads of a row are issued before one wait
+      const bool q_warp = warp * 32 < w.q_len, k_warp = warp * 32 < w.k_len;
+      if (q_warp) {
+        uint32_t r0[32], r1[32];
+        tmem_ld32(tDQ + lane_sel, r0);
+        tmem_ld32(tDQ + lane_sel + 32, r1);
+        tmem_ld_wait();
+        if (row_ok) {
+          __nv_bfloat16* drow = p.dq + static_cast<size_t>(w.q0 + t) * p.ld_dq + w.h * kHd;
 #pragma unroll
-            for (int g4 = 0; g4 < 4; ++g4) {
-              uint4 o;
-              __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+          for (int g4 = 0; g4 < 8; ++g4) {
+            uint4 o;
+            __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
 #pragma unroll
-              for (int j = 0; j < 4; ++j)
-                o2[j] = __floats2bfloat162_rn(__uint_as_float(r[g4 * 8 + 2 * j]), __uint_as_float(r[g4 * 8 + 2 * j + 1]));
-              reinterpret_cast<uint4*>(drow)[g4] = o;
+            for (int j = 0; j < 4; ++j) {
+              const int e = (g4 & 3) * 8 + 2 * j;
+              o2[j] = __floats2bfloat162_rn(__uint_as_float(g4 < 4 ? r0[e] : r1[e]), __uint_as_float(g4 < 4 ? r0[e + 1] : r1[e + 1]));
             }
+            reinterpret_cast<uint4*>(drow)[g4] = o;
           }
         }
       }
-      if ((warp & 3) * 32 < w.k_len) {
+      if (k_warp) {
 #pragma unroll 1
         for (int which = 0; which < 2; ++which) {
           __nv_bfloat16* dst = which == 0 ? p.dk : p.dv;
           const int ld = which == 0 ? p.ld_dk : p.ld_dv;
           const uint32_t tsrc = which == 0 ? tDK : tDV;
-#pragma unroll 1
-          for (int c = 0; c < 2; ++c) {
-            uint32_t r[32];
-            tmem_ld32(tsrc + lane_sel + c * 32, r);
-            tmem_ld_wait();
-            if (t < w.k_len) {
-              __nv_bfloat16* drow = dst + static_cast<size_t>(w.k0 + t) * ld + w.h * kHd + c * 32;
+          uint32_t r0[32], r1[32];
+          tmem_ld32(tsrc + lane_sel, r0);
+          tmem_ld32(tsrc + lane_sel + 32, r1);
+          tmem_ld_wait();
+          if (t < w.k_len) {
+            __nv_bfloat16* drow = dst + static_cast<size_t>(w.k0 + t) * ld + w.h * kHd;
 #pragma unroll
-              for (int g4 = 0; g4 < 4; ++g4) {
-                uint4 o;
-                __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+            for (int g4 = 0; g4 < 8; ++g4) {
+              uint4 o;
+              __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
 #pragma unroll
-                for (int j = 0; j < 4; ++j)
-                  o2[j] = __floats2bfloat162_rn(__uint_as_float(r[g4 * 8 + 2 * j]), __uint_as_float(r[g4 * 8 + 2 * j + 1]));
-                reinterpret_cast<uint4*>(drow)[g4] = o;
+              for (int j = 0; j < 4; ++j) {
+                const int e = (g4 & 3) * 8 + 2 * j;
+                o2[j] = __floats2bfloat162_rn(__uint_as_float(g4 < 4 ? r0[e] : r1[e]), __uint_as_float(g4 < 4 ? r0[e + 1] : r1[e + 1]));
               }
+              reinterpret_cast<uint4*>(drow)[g4] = o;
             }
           }
         }
@@ -496,7 +527,7 @@ attn_bwd_short_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
     for (int i = 0; i < 2000; ++i) __nanosleep(1000);
     __syncthreads();
   }
-  if (warp == 1) {
+  if (warp == 5) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, 512);
   }

@@ -13,7 +13,7 @@
 //            over query tiles (A operands read MN-major from the same smem that holds P / dS);
 //            dQ = dS K per tile (written directly when the sequence has a single key tile, else
 //            accumulated in an fp32 buffer with vector red.add).
-// Dropout on P is regenerated from Philox counters in backward; nothing but the row log-sum-exp is saved.
+// Dropout on P is regenerated from its counters in backward; nothing but the row log-sum-exp is saved.
 //
 // Replaces the reference's cuBLAS-strided-batched + warp-softmax attention extensions
 // (onmt/modules/extensions/multihead_attn/self_multihead_attn_cuda.cu:23-612, encdec_multihead_attn_
@@ -79,10 +79,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   int num_kt = (k_len + kTile - 1) / kTile;
   if (p.causal) num_kt = min(num_kt, (qt * kTile + q_rows + kTile - 1) / kTile);
   const bool do_drop = p.dropout_p > 0.f;
-  const Philox rng(p.seed + ((do_drop && p.seed_dev) ? *p.seed_dev : 0ull));
-  const uint32_t thr8 = static_cast<uint32_t>(p.dropout_p * 256.0f + 0.5f);
-  const float keep_scale = do_drop ? 256.0f / static_cast<float>(256 - thr8) : 1.f;
-  const unsigned long long dstream = (p.stream_id << 16) | static_cast<unsigned long long>(h);
+  const DropRng rng(p.seed + ((do_drop && p.seed_dev) ? *p.seed_dev : 0ull),
+                    (p.stream_id << 16) | static_cast<unsigned long long>(h), p.dropout_p);
   uint32_t ph_kv = 0, ph_mma = 0;
   bool ok = true;
 
@@ -123,8 +121,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     const float m_new = fmaxf(m_run, tile_max);
     const float alpha = __expf(m_run - m_new);
     float row_sum = 0.f;
-    uint4 rc = make_uint4(0, 0, 0, 0);
-    unsigned long long rc_ctr = ~0ull;
 #pragma unroll 1
     for (int c = 0; c < 4; ++c) {
       uint32_t r[32];
@@ -141,8 +137,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       }
       if (do_drop) {
         const unsigned long long base = static_cast<unsigned long long>(q0 + t) * p.kstride + kt * kTile + c * 32;
-#pragma unroll
-        for (int j = 0; j < 32; ++j) pv[j] *= keep_factor(rng, dstream, base + j, thr8, keep_scale, rc, rc_ctr);
+        apply_dropout32(rng, base, pv);
       }
       // bf16, swizzled K-major slabs of 64 keys
 #pragma unroll
@@ -261,10 +256,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   const uint32_t idesc_dkv = make_idesc_bf16(kTile, kHd, 1, 1);    // dK,dV : MN-major A and B, N = 64
 
   const bool do_drop = p.dropout_p > 0.f;
-  const Philox rng(p.seed + ((do_drop && p.seed_dev) ? *p.seed_dev : 0ull));
-  const uint32_t thr8 = static_cast<uint32_t>(p.dropout_p * 256.0f + 0.5f);
-  const float keep_scale = do_drop ? 256.0f / static_cast<float>(256 - thr8) : 1.f;
-  const unsigned long long dstream = (p.stream_id << 16) | static_cast<unsigned long long>(h);
+  const DropRng rng(p.seed + ((do_drop && p.seed_dev) ? *p.seed_dev : 0ull),
+                    (p.stream_id << 16) | static_cast<unsigned long long>(h), p.dropout_p);
 
   const int num_qt = (q_len + kTile - 1) / kTile;
   const int qt_first = p.causal ? (kt * kTile) / kTile : 0;  // query tiles before the key tile see none of it
@@ -313,25 +306,24 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     tc_fence_after_sync();
 
     const int q_pos = qt * kTile + t;
-    uint4 rc = make_uint4(0, 0, 0, 0);
-    unsigned long long rc_ctr = ~0ull;
 #pragma unroll 1
     for (int c = 0; c < 4; ++c) {
       uint32_t rs[32], rd[32];
       tmem_ld32(tS + lane_sel + c * 32, rs);
       tmem_ld32(tDP + lane_sel + c * 32, rd);
       tmem_ld_wait();
-      float pd[32], ds[32];
+      float pd[32], ds[32], kf[32];
       const unsigned long long base = static_cast<unsigned long long>(q0 + t) * p.kstride + kt * kTile + c * 32;
+#pragma unroll
+      for (int j = 0; j < 32; ++j) kf[j] = 1.f;
+      if (do_drop) apply_dropout32(rng, base, kf);
 #pragma unroll
       for (int j = 0; j < 32; ++j) {
         const int col = c * 32 + j;
         const bool valid = row_ok && col < k_rows && (!p.causal || kt * kTile + col <= q_pos);
         const float pr = valid ? __expf(__uint_as_float(rs[j]) * p.scale - lse) : 0.f;
-        float kf = 1.f;
-        if (do_drop) kf = keep_factor(rng, dstream, base + j, thr8, keep_scale, rc, rc_ctr);
-        pd[j] = pr * kf;
-        ds[j] = pr * (__uint_as_float(rd[j]) * kf - Drow) * p.scale;
+        pd[j] = pr * kf[j];
+        ds[j] = pr * (__uint_as_float(rd[j]) * kf[j] - Drow) * p.scale;
       }
 #pragma unroll
       for (int g = 0; g < 4; ++g) {

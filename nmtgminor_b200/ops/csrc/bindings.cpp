@@ -280,6 +280,76 @@ void attn_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& o
   ck(nmtg_attn_bwd(&d, cur_stream()));
 }
 
+// ---- symmetric (IPC-exportable) memory and the peer-memory optimiser step ---------------------------------
+Tensor symm_alloc(int64_t nbytes, int64_t device) {
+  c10::cuda::CUDAGuard guard(static_cast<c10::DeviceIndex>(device));
+  void* ptr = nullptr;
+  cudaError_t e = cudaMalloc(&ptr, static_cast<size_t>(nbytes));
+  TORCH_CHECK(e == cudaSuccess, "cudaMalloc of ", nbytes, " bytes failed: ", cudaGetErrorString(e));
+  cudaMemset(ptr, 0, static_cast<size_t>(nbytes));
+  cudaDeviceSynchronize();
+  auto opts = torch::TensorOptions().dtype(torch::kUInt8).device(torch::kCUDA, static_cast<c10::DeviceIndex>(device));
+  return torch::from_blob(ptr, {nbytes}, [](void* p) { cudaFree(p); }, opts);
+}
+
+py::bytes ipc_get_handle(const Tensor& t) {
+  cudaIpcMemHandle_t h;
+  cudaError_t e = cudaIpcGetMemHandle(&h, t.data_ptr());
+  TORCH_CHECK(e == cudaSuccess, "cudaIpcGetMemHandle failed: ", cudaGetErrorString(e));
+  return py::bytes(reinterpret_cast<const char*>(&h), sizeof(h));
+}
+
+int64_t ipc_open_handle(const std::string& bytes, int64_t device) {
+  TORCH_CHECK(bytes.size() == sizeof(cudaIpcMemHandle_t), "bad IPC handle size");
+  c10::cuda::CUDAGuard guard(static_cast<c10::DeviceIndex>(device));
+  cudaIpcMemHandle_t h;
+  memcpy(&h, bytes.data(), sizeof(h));
+  void* ptr = nullptr;
+  cudaError_t e = cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess);
+  TORCH_CHECK(e == cudaSuccess, "cudaIpcOpenMemHandle failed: ", cudaGetErrorString(e));
+  return reinterpret_cast<int64_t>(ptr);
+}
+
+void ipc_close_handle(int64_t ptr) { cudaIpcCloseMemHandle(reinterpret_cast<void*>(ptr)); }
+
+NmtgPeerTable make_table(int64_t rank, const std::vector<int64_t>& grads, const std::vector<int64_t>& works,
+                         const std::vector<int64_t>& flags, const std::vector<int64_t>& partials, const OptTensor& norm_out) {
+  NmtgPeerTable t = {};
+  t.rank = static_cast<int>(rank);
+  t.world = static_cast<int>(grads.size());
+  TORCH_CHECK(t.world >= 1 && t.world <= 16 && works.size() == grads.size() && flags.size() == grads.size() &&
+              partials.size() == grads.size(), "peer table: inconsistent sizes");
+  for (int i = 0; i < t.world; ++i) {
+    t.grads[i] = reinterpret_cast<float*>(grads[i]);
+    t.works[i] = reinterpret_cast<unsigned short*>(works[i]);
+    t.flags[i] = reinterpret_cast<int*>(flags[i]);
+    t.partials[i] = reinterpret_cast<float*>(partials[i]);
+  }
+  t.norm_out = norm_out.has_value() ? norm_out->data_ptr<float>() : nullptr;
+  return t;
+}
+
+void allreduce_adamw(int64_t rank, const std::vector<int64_t>& grads, const std::vector<int64_t>& works,
+                     const std::vector<int64_t>& flags, const std::vector<int64_t>& partials, Tensor& reduced, Tensor& sq,
+                     Tensor& nonfinite, Tensor& master, Tensor& m, Tensor& v, const Tensor& hyper, int64_t slice_begin,
+                     int64_t slice_len, int64_t total_len, Tensor& epoch, const OptTensor& norm_out) {
+  need_f32(reduced, "reduced"); need_f32(sq, "sq"); need_f32(master, "master"); need_f32(m, "m"); need_f32(v, "v");
+  need_f32(hyper, "hyper");
+  TORCH_CHECK(reduced.numel() >= slice_len && master.numel() >= slice_len && m.numel() >= slice_len && v.numel() >= slice_len);
+  c10::cuda::CUDAGuard guard(master.device());
+  NmtgPeerTable t = make_table(rank, grads, works, flags, partials, norm_out);
+  ck(nmtg_allreduce_adamw(&t, reduced.data_ptr<float>(), sq.data_ptr<float>(), nonfinite.data_ptr<int>(), master.data_ptr<float>(),
+                          m.data_ptr<float>(), v.data_ptr<float>(), reinterpret_cast<const NmtgAdamHyper*>(hyper.data_ptr<float>()),
+                          slice_begin, slice_len, total_len, epoch.data_ptr<int>(), status_ptr(master), cur_stream()));
+}
+
+void peer_wait_row(int64_t rank, const std::vector<int64_t>& flags, int64_t row, int64_t epoch, const Tensor& like) {
+  std::vector<int64_t> zeros(flags.size(), 0);
+  c10::cuda::CUDAGuard guard(like.device());
+  NmtgPeerTable t = make_table(rank, zeros, zeros, flags, zeros, c10::nullopt);
+  ck(nmtg_peer_wait_row(&t, static_cast<int>(row), static_cast<int>(epoch), status_ptr(like), cur_stream()));
+}
+
 int64_t read_status(int64_t device) {
   Tensor& s = status_tensor(static_cast<int>(device));
   return s.cpu().item<int>();
@@ -290,6 +360,7 @@ void clear_status(int64_t device) { status_tensor(static_cast<int>(device)).zero
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", &gemm);
+  m.def("set_gemm_variant", [](int64_t v) { nmtg_set_gemm_variant(static_cast<int>(v)); });
   m.def("layernorm_fwd", &layernorm_fwd);
   m.def("layernorm_bwd", &layernorm_bwd);
   m.def("xent_fused", &xent_fused);
@@ -305,6 +376,12 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("set_attention_variant", [](int64_t v) { nmtg_set_attention_variant(static_cast<int>(v)); });
   m.def("batch_allocate", &batch_allocate);
   m.def("get_seed_tensor", &get_seed_tensor);
+  m.def("symm_alloc", &symm_alloc);
+  m.def("ipc_get_handle", &ipc_get_handle);
+  m.def("ipc_open_handle", &ipc_open_handle);
+  m.def("ipc_close_handle", &ipc_close_handle);
+  m.def("allreduce_adamw", &allreduce_adamw);
+  m.def("peer_wait_row", &peer_wait_row);
   m.def("read_status", &read_status);
   m.def("clear_status", &clear_status);
 }

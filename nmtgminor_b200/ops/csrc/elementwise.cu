@@ -1,11 +1,11 @@
 // Memory-bound element-wise kernels for sm_100a (16-byte vector accesses, grid sized to the SM count):
-//   * dropout_add:      y = residual + dropout(x)           (mask regenerated from Philox, never stored)
+//   * dropout_add:      y = residual + dropout(x)           (mask regenerated from counters, never stored)
 //   * masked_scale:     dx = dy * keep / (1-p)              (same counters as the forward op)
 //   * embed_fwd / bwd:  gather * scale + position row, dropout; backward scatter-adds into fp32 grads
 //   * colsum:           column sums of a bf16 matrix (bias gradients) accumulated into fp32
 // The dropout convention is shared with the GEMM epilogue: element e of the op with stream id s keeps
-// its value iff byte (e & 15) of Philox(counter = e >> 4, stream = s) is >= round(256 p); the keep scale
-// is 256 / (256 - round(256 p)).
+// its value iff byte (e & 3) of DropRng(seed, s).word(e >> 2) is >= round(256 p); the keep scale is
+// 256 / (256 - round(256 p)).
 //
 // Counterpart of the reference's fused_dropout_add_cuda (onmt/modules/extensions/dropout_add/
 // dropout.h:21-160) and of the PyTorch embedding/position code in onmt/models/transformers.py:163-207.
@@ -33,28 +33,26 @@ __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
   return o;
 }
 
-// One thread handles 16 consecutive elements (two 16-byte vectors) = one Philox call.
+// One thread handles 16 consecutive elements (two 16-byte vectors, four hash words).
 __global__ void dropout_add_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ res,
                                    __nv_bfloat16* __restrict__ y, long n16, float p, unsigned long long seed,
                                    unsigned long long stream_id, const unsigned long long* seed_dev) {
-  const Philox rng(seed + (seed_dev ? *seed_dev : 0ull));
-  const uint32_t thr8 = static_cast<uint32_t>(p * 256.0f + 0.5f);
-  const float scale = 256.0f / static_cast<float>(256 - thr8);
+  const DropRng rng(seed + (seed_dev ? *seed_dev : 0ull), stream_id, p);
   for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < n16;
        i += static_cast<long>(gridDim.x) * blockDim.x) {
-    uint4 rnd = rng(static_cast<uint64_t>(i), stream_id);
-    const uint32_t w[4] = {rnd.x, rnd.y, rnd.z, rnd.w};
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
       float f[8], r[8];
       unpack8(reinterpret_cast<const uint4*>(x)[2 * i + h], f);
       if (res) unpack8(reinterpret_cast<const uint4*>(res)[2 * i + h], r);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const int e = h * 8 + j;
-        uint32_t byte = (w[e >> 2] >> ((e & 3) * 8)) & 0xFFu;
-        float v = byte >= thr8 ? f[j] * scale : 0.f;
-        f[j] = res ? v + r[j] : v;
+      for (int g = 0; g < 2; ++g) {
+        const uint32_t w = rng.word(static_cast<unsigned long long>(i) * 4 + h * 2 + g);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float v = rng.keep(w, j) ? f[g * 4 + j] * rng.scale : 0.f;
+          f[g * 4 + j] = res ? v + r[g * 4 + j] : v;
+        }
       }
       reinterpret_cast<uint4*>(y)[2 * i + h] = pack8(f);
     }
@@ -66,9 +64,7 @@ __global__ void embed_fwd_kernel(const int64_t* __restrict__ tokens, const int64
                                  __nv_bfloat16* __restrict__ out, int rows, int hidden, int vocab, int max_pos,
                                  float scale, float p, unsigned long long seed, unsigned long long stream_id,
                                  const unsigned long long* seed_dev) {
-  const Philox rng(seed + (seed_dev ? *seed_dev : 0ull));
-  const uint32_t thr8 = static_cast<uint32_t>(p * 256.0f + 0.5f);
-  const float keep_scale = 256.0f / static_cast<float>(256 - thr8);
+  const DropRng rng(seed + (seed_dev ? *seed_dev : 0ull), stream_id, p);
   const int n16 = hidden >> 4;
   for (int row = blockIdx.x; row < rows; row += gridDim.x) {
     long tok = tokens[row];
@@ -80,23 +76,21 @@ __global__ void embed_fwd_kernel(const int64_t* __restrict__ tokens, const int64
     const uint4* pr = pos_table ? reinterpret_cast<const uint4*>(pos_table + static_cast<size_t>(pos) * hidden) : nullptr;
     uint4* orow = reinterpret_cast<uint4*>(out + static_cast<size_t>(row) * hidden);
     for (int c = threadIdx.x; c < n16; c += blockDim.x) {
-      uint4 rnd = make_uint4(~0u, ~0u, ~0u, ~0u);
-      if (p > 0.f) rnd = rng(static_cast<uint64_t>(row) * n16 + c, stream_id);
-      const uint32_t w[4] = {rnd.x, rnd.y, rnd.z, rnd.w};
+      const unsigned long long w0 = (static_cast<unsigned long long>(row) * n16 + c) * 4;
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
         float f[8], q[8];
         unpack8(__ldg(tr + 2 * c + h), f);
         if (pr) unpack8(__ldg(pr + 2 * c + h), q);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const int e = h * 8 + j;
-          float v = f[j] * scale + (pr ? q[j] : 0.f);
-          if (p > 0.f) {
-            uint32_t byte = (w[e >> 2] >> ((e & 3) * 8)) & 0xFFu;
-            v = byte >= thr8 ? v * keep_scale : 0.f;
+        for (int g = 0; g < 2; ++g) {
+          const uint32_t w = p > 0.f ? rng.word(w0 + h * 2 + g) : 0xFFFFFFFFu;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            float v = f[g * 4 + j] * scale + (pr ? q[g * 4 + j] : 0.f);
+            if (p > 0.f) v = rng.keep(w, j) ? v * rng.scale : 0.f;
+            f[g * 4 + j] = v;
           }
-          f[j] = v;
         }
         orow[2 * c + h] = pack8(f);
       }
@@ -110,9 +104,7 @@ __global__ void embed_bwd_kernel(const int64_t* __restrict__ tokens, const int64
                                  float* __restrict__ dpos, int rows, int hidden, int vocab, int max_pos, float scale,
                                  float p, unsigned long long seed, unsigned long long stream_id,
                                  const unsigned long long* seed_dev, int pad_idx) {
-  const Philox rng(seed + (seed_dev ? *seed_dev : 0ull));
-  const uint32_t thr8 = static_cast<uint32_t>(p * 256.0f + 0.5f);
-  const float keep_scale = 256.0f / static_cast<float>(256 - thr8);
+  const DropRng rng(seed + (seed_dev ? *seed_dev : 0ull), stream_id, p);
   const int n16 = hidden >> 4;
   for (int row = blockIdx.x; row < rows; row += gridDim.x) {
     long tok = tokens[row];
@@ -124,19 +116,17 @@ __global__ void embed_bwd_kernel(const int64_t* __restrict__ tokens, const int64
     float* trow = dtable + static_cast<size_t>(tok) * hidden;
     float* prow = dpos ? dpos + static_cast<size_t>(pos) * hidden : nullptr;
     for (int c = threadIdx.x; c < n16; c += blockDim.x) {
-      uint4 rnd = make_uint4(~0u, ~0u, ~0u, ~0u);
-      if (p > 0.f) rnd = rng(static_cast<uint64_t>(row) * n16 + c, stream_id);
-      const uint32_t w[4] = {rnd.x, rnd.y, rnd.z, rnd.w};
+      const unsigned long long w0 = (static_cast<unsigned long long>(row) * n16 + c) * 4;
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
         float f[8];
         unpack8(dr[2 * c + h], f);
+        if (p > 0.f) {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const int e = h * 8 + j;
-          if (p > 0.f) {
-            uint32_t byte = (w[e >> 2] >> ((e & 3) * 8)) & 0xFFu;
-            f[j] = byte >= thr8 ? f[j] * keep_scale : 0.f;
+          for (int g = 0; g < 2; ++g) {
+            const uint32_t w = rng.word(w0 + h * 2 + g);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) f[g * 4 + j] = rng.keep(w, j) ? f[g * 4 + j] * rng.scale : 0.f;
           }
         }
 #pragma unroll

@@ -1,0 +1,264 @@
+// CTA-pair bf16 GEMM for sm_100a: two CTAs of a cluster (two SMs) cooperate on one 256 x BN output tile
+// with tcgen05.mma.cta_group::2.  Each CTA loads its own 128 rows of A and its own HALF of the B tile, so
+// per SM the shared-memory traffic (TMA writes + UMMA operand reads) per flop drops by a third compared
+// with the single-CTA kernel, which is what keeps the tensor pipe fed at large tile sizes.
+//
+//   rank 0 (leader): TMA producer + UMMA issuer for the pair + epilogue of rows [m0, m0 + 128)
+//   rank 1         : TMA producer for its operand halves       + epilogue of rows [m0 + 128, m0 + 256)
+//
+// Synchronisation (all mbarriers live in shared memory; remote ones are addressed through the cluster
+// window, no broadcast forms are used anywhere):
+//   full[s]       on the leader, count 1 + 2 x stage bytes: both CTAs' TMA loads complete_tx on it
+//   empty[s]      on each CTA, signalled by two tcgen05.commit of the leader (local + peer address)
+//   tmem_full[a]  on each CTA, same two-commit scheme after the last k-block of a tile
+//   tmem_empty[a] on the leader, count 2 x 256: every epilogue thread of both CTAs arrives (peer: remote arrive)
+// Every wait is bounded; all exits go through the final cluster barrier so a CTA never leaves while its peer
+// may still touch its shared memory.
+#include "gemm_common.cuh"
+
+namespace b200 {
+
+bool cached_tmap(CUtensorMap* out, const void* base, long rows, long cols, long ld, int br, int bc);
+int num_sms();
+
+constexpr int kPairThreads = 32 * (2 + kEpilogueWarps);
+
+template <int BN>
+struct PairSmem {
+  static constexpr int kABytes = BM * BK * 2;            // 16 KB : this CTA's 128 rows of A
+  static constexpr int kBBytes = (BN / 2) * BK * 2;      // this CTA's half of the B tile
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kStages = (BN == 256) ? 6 : 8;
+  static constexpr int kBarOffset = kStages * kStageBytes;
+  static constexpr int kTotal = kBarOffset + 512 + 1024;
+};
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// TMA load into THIS CTA's shared memory that reports its bytes to an mbarrier of either CTA of the pair
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* m, uint32_t bar_cluster_addr, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar_cluster_addr), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void umma_bf16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar_cluster_addr) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster_addr) : "memory");
+}
+
+template <int BN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const GemmArgs p) {
+  using S = PairSmem<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + S::kBarOffset);
+  uint64_t* empty_bar = full_bar + S::kStages;
+  uint64_t* tmem_full = empty_bar + S::kStages;
+  uint64_t* tmem_empty = tmem_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  const int num_m = (p.M + 2 * BM - 1) / (2 * BM);
+  const int num_n = (p.N + BN - 1) / BN;
+  const int num_kb_total = (p.K + BK - 1) / BK;
+  const int kb_per_split = (num_kb_total + p.split_k - 1) / p.split_k;   // host guarantees no split is empty
+  const int num_mn = num_m * num_n;
+  const int num_tiles = num_mn * p.split_k;
+  const int cluster_id = blockIdx.x >> 1, num_clusters = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < S::kStages; ++i) {
+      mbar_init(&full_bar[i], 1);
+      mbar_init(&empty_bar[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&tmem_full[i], 1);
+      mbar_init(&tmem_empty[i], 2 * 32 * kEpilogueWarps);
+    }
+    *abort_word = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(2 * BN) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();      // barriers of both CTAs are initialised and TMEM is allocated before anyone proceeds
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------- TMA producer (both CTAs) --------------------------------
+    if (lane == 0) {
+      tma_prefetch_desc(&tmap_a);
+      tma_prefetch_desc(&tmap_b);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+        const int mn = tile % num_mn, ks = tile / num_mn;
+        const int m0 = (mn % num_m) * (2 * BM) + static_cast<int>(rank) * BM;   // my 128 rows of the pair tile
+        const int n0 = (mn / num_m) * BN + static_cast<int>(rank) * (BN / 2);   // my half of the B tile
+        const int kb_begin = ks * kb_per_split, kb_end = min(kb_begin + kb_per_split, num_kb_total);
+        for (int kb = kb_begin; kb < kb_end; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_word, p.status, kTimeoutSmemEmpty)) { ok = false; break; }
+          uint8_t* sa = smem + stage * S::kStageBytes;
+          uint8_t* sb = sa + S::kABytes;
+          const uint32_t bar = map_to_cta(smem_u32(&full_bar[stage]), 0);   // the leader's barrier
+          if (leader) mbar_expect_tx(&full_bar[stage], 2 * S::kStageBytes);
+          if (!p.a_mn_major) {
+            tma_load_2d_pair(sa, &tmap_a, bar, kb * BK, m0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j) tma_load_2d_pair(sa + j * (BK * 128), &tmap_a, bar, m0 + j * 64, kb * BK);
+          }
+          if (!p.b_mn_major) {
+            tma_load_2d_pair(sb, &tmap_b, bar, kb * BK, n0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 128; ++j) tma_load_2d_pair(sb + j * (BK * 128), &tmap_b, bar, n0 + j * 64, kb * BK);
+          }
+          if (++stage == S::kStages) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------- UMMA issuer (leader only) -------------------------------
+    if (leader && lane == 0) {
+      const uint32_t idesc = make_idesc_bf16(2 * BM, BN, p.a_mn_major, p.b_mn_major);
+      const uint32_t a_lbo = p.a_mn_major ? BK * 128 : 16, b_lbo = p.b_mn_major ? BK * 128 : 16;
+      const uint32_t a_kstep = p.a_mn_major ? (16 * 128) >> 4 : 32 >> 4;
+      const uint32_t b_kstep = p.b_mn_major ? (16 * 128) >> 4 : 32 >> 4;
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters, ++it) {
+        const int acc = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1, abort_word, p.status, kTimeoutTmemEmpty)) break;
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        const int ks = tile / num_mn;
+        const int kb_begin = ks * kb_per_split, kb_end = min(kb_begin + kb_per_split, num_kb_total);
+        for (int kb = kb_begin; kb < kb_end; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, abort_word, p.status, kTimeoutTmaFull)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t sa = smem_u32(smem + stage * S::kStageBytes);
+          const uint32_t sb = sa + S::kABytes;
+          const uint64_t adesc = make_smem_desc_sw128(sa, a_lbo, 1024);
+          const uint64_t bdesc = make_smem_desc_sw128(sb, b_lbo, 1024);
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k)
+            umma_bf16_pair(d_tmem, adesc + static_cast<uint64_t>(k * a_kstep), bdesc + static_cast<uint64_t>(k * b_kstep), idesc,
+                           (kb > kb_begin || k > 0) ? 1u : 0u);
+          umma_commit_pair(map_to_cta(smem_u32(&empty_bar[stage]), 0));
+          umma_commit_pair(map_to_cta(smem_u32(&empty_bar[stage]), 1));
+          if (++stage == S::kStages) { stage = 0; phase ^= 1; }
+        }
+        if (ok) {
+          umma_commit_pair(map_to_cta(smem_u32(&tmem_full[acc]), 0));
+          umma_commit_pair(map_to_cta(smem_u32(&tmem_full[acc]), 1));
+        }
+      }
+    }
+  } else {
+    // ------------------------------- epilogue (8 warps, both CTAs) ---------------------------
+    const int q = warp & 3;
+    const int chunk_par = (warp - 2) >> 2;
+    const bool do_drop = p.dropout_p > 0.f;
+    const DropRng rng(p.seed + ((do_drop && p.seed_dev) ? *p.seed_dev : 0ull), p.stream_id, p.dropout_p);
+    int it = 0;
+    for (int tile = cluster_id; tile < num_tiles; tile += num_clusters, ++it) {
+      const int mn = tile % num_mn;
+      const int m0 = (mn % num_m) * (2 * BM) + static_cast<int>(rank) * BM;
+      const int n0 = (mn / num_m) * BN;
+      const int acc = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      if (!mbar_wait(&tmem_full[acc], acc_phase, abort_word, p.status, kTimeoutTmemFull)) break;
+      tc_fence_after_sync();
+      const int row = m0 + q * 32 + lane;
+      const bool row_ok = row < p.M;
+#pragma unroll 1
+      for (int c = chunk_par; c < BN / 32; c += kEpilogueWarps / 4) {
+        const int col0 = n0 + c * 32;
+        if (col0 >= p.N) break;
+        gemm_epilogue_chunk(p, rng, do_drop, row, row_ok, col0, tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN + c * 32);
+      }
+      tc_fence_before_sync();
+      mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty[acc]), 0));
+    }
+  }
+
+  // ------------------------------- teardown --------------------------------------------------------
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_word) {
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+    __syncthreads();
+  }
+  cluster_sync_all();      // the peer may still signal barriers in my shared memory until it gets here
+  if (warp == 1) {
+    tc_fence_after_sync();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * BN) : "memory");
+  }
+}
+
+template <int BN>
+static const char* launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& args, int grid, cudaStream_t stream) {
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, PairSmem<BN>::kTotal);
+    if (e != cudaSuccess) return cudaGetErrorString(e);
+    configured = true;
+  }
+  gemm_pair_kernel<BN><<<grid, kPairThreads, PairSmem<BN>::kTotal, stream>>>(ta, tb, args);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? nullptr : cudaGetErrorString(e);
+}
+
+// CTA-pair path; BN = 256 or 128; a.split_k splits must all be non-empty.  Returns nullptr on success.
+const char* launch_gemm_pair(const GemmDesc* d, const GemmArgs& a, int bn, cudaStream_t stream) {
+  CUtensorMap ta, tb;
+  bool ok;
+  if (!d->a_mn_major) ok = cached_tmap(&ta, d->a, d->M, d->K, d->lda, BM, BK);
+  else ok = cached_tmap(&ta, d->a, d->K, d->M, d->lda, BK, 64);
+  if (!ok) return "gemm: cuTensorMapEncodeTiled failed for A";
+  if (!d->b_mn_major) ok = cached_tmap(&tb, d->b, d->N, d->K, d->ldb, bn / 2, BK);
+  else ok = cached_tmap(&tb, d->b, d->K, d->N, d->ldb, BK, 64);
+  if (!ok) return "gemm: cuTensorMapEncodeTiled failed for B";
+  const long tiles = static_cast<long>((d->M + 2 * BM - 1) / (2 * BM)) * ((d->N + bn - 1) / bn) * a.split_k;
+  const int max_clusters = num_sms() / 2;
+  const int clusters = static_cast<int>(tiles < max_clusters ? tiles : max_clusters);
+  if (bn == 256) return launch_pair<256>(ta, tb, a, clusters * 2, stream);
+  return launch_pair<128>(ta, tb, a, clusters * 2, stream);
+}
+
+}  // namespace b200

@@ -14,8 +14,7 @@
 // Replaces the cuBLAS / cuBLASLt GEMM + separate element-wise kernels of the reference
 // (onmt/modules/extensions/mlp/mlp_relu_cuda.cu:82-190,445-1292; mlp_blaslt/mlp_gelu_cuda.cu:212-471;
 // multihead_attn/self_multihead_attn_cuda.cu:91,284; dropout_add/dropout.h:21-160).
-#include "b200_ptx.cuh"
-#include "ops_api.h"
+#include "gemm_common.cuh"
 
 #include <mutex>
 #include <unordered_map>
@@ -25,9 +24,6 @@
 
 namespace b200 {
 
-constexpr int BM = 128;
-constexpr int BK = 64;
-constexpr int kEpilogueWarps = 8;   // two warps per TMEM lane quarter, interleaved over 32-column chunks
 constexpr int kGemmThreads = 32 * (2 + kEpilogueWarps);
 
 template <int BN>
@@ -39,36 +35,6 @@ struct GemmSmem {
   static constexpr int kBarOffset = kStages * kStageBytes;
   static constexpr int kTotal = kBarOffset + 256 + 1024;  // barriers + alignment slack
 };
-
-struct GemmArgs {
-  int M, N, K;
-  int a_mn_major, b_mn_major;
-  int split_k;             // >= 1; > 1 requires out_fp32 and atomic accumulation
-  float alpha;
-  const __nv_bfloat16* bias;      // [N] or null
-  const __nv_bfloat16* residual;  // [M, ld_res] or null, added last
-  int ld_res;
-  const __nv_bfloat16* aux;       // [M, ld_aux] activation-backward operand or null
-  int ld_aux;
-  void* out;
-  int ld_out;
-  int out_fp32;
-  int accumulate;          // fp32 output only: out += result
-  __nv_bfloat16* preact;   // optional [M, ld_out]: value after bias, before activation
-  int act;
-  float dropout_p;
-  unsigned long long seed, stream_id;
-  const unsigned long long* seed_dev;
-  int* status;
-};
-
-__device__ __forceinline__ float gelu_f(float x) { return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f)); }
-__device__ __forceinline__ float gelu_grad(float x) {
-  float cdf = 0.5f * (1.0f + erff(x * 0.70710678118654752f));
-  float pdf = 0.3989422804014327f * __expf(-0.5f * x * x);
-  return cdf + x * pdf;
-}
-__device__ __forceinline__ float sigmoid_f(float x) { return 1.0f / (1.0f + __expf(-x)); }
 
 template <int BN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
@@ -205,9 +171,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     const int q = warp & 3;             // TMEM lane quarter this warp may read
     const int chunk_par = (warp - 2) >> 2;  // 0 / 1: which interleaved half of the column chunks
     const bool do_drop = p.dropout_p > 0.f;
-    const Philox rng(p.seed + ((do_drop && p.seed_dev) ? *p.seed_dev : 0ull));
-    const uint32_t thr8 = static_cast<uint32_t>(p.dropout_p * 256.0f + 0.5f);
-    const float keep_scale = do_drop ? 256.0f / static_cast<float>(256 - thr8) : 1.0f;
+    const DropRng rng(p.seed + ((do_drop && p.seed_dev) ? *p.seed_dev : 0ull), p.stream_id, p.dropout_p);
     int it = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
       const int mn = tile % (num_m * num_n);
@@ -227,164 +191,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       for (int c = chunk_par; c < BN / 32; c += kEpilogueWarps / 4) {
         const int col0 = n0 + c * 32;
         if (col0 >= p.N) break;  // warp-uniform
-        uint32_t r[32];
-        tmem_ld32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN + c * 32, r);
-        tmem_ld_wait();
-        if (!row_ok) continue;
-        float v[32];
-#pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
-        const bool full_cols = (col0 + 32 <= p.N);
-        if (p.bias) {
-          if (full_cols) {
-            const uint4* bp = reinterpret_cast<const uint4*>(p.bias + col0);
-#pragma unroll
-            for (int g = 0; g < 4; ++g) {
-              uint4 b = __ldg(bp + g);
-              const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&b);
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                float2 f = __bfloat1622float2(b2[j]);
-                v[g * 8 + 2 * j] += f.x;
-                v[g * 8 + 2 * j + 1] += f.y;
-              }
-            }
-          } else {
-            for (int j = 0; j < 32; ++j)
-              if (col0 + j < p.N) v[j] += __bfloat162float(p.bias[col0 + j]);
-          }
-        }
-        if (p.preact) {
-          __nv_bfloat16* pp = p.preact + static_cast<size_t>(row) * p.ld_out + col0;
-          if (full_cols) {
-#pragma unroll
-            for (int g = 0; g < 4; ++g) {
-              uint4 o;
-              __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
-#pragma unroll
-              for (int j = 0; j < 4; ++j) o2[j] = __floats2bfloat162_rn(v[g * 8 + 2 * j], v[g * 8 + 2 * j + 1]);
-              reinterpret_cast<uint4*>(pp)[g] = o;
-            }
-          } else {
-            for (int j = 0; j < 32; ++j)
-              if (col0 + j < p.N) pp[j] = __float2bfloat16(v[j]);
-          }
-        }
-        // activation (forward) or activation-gradient (backward; aux holds h or z)
-        if (p.act >= kActReluBwd) {
-          const __nv_bfloat16* ap = p.aux + static_cast<size_t>(row) * p.ld_aux + col0;
-          float av[32];
-          if (full_cols && (p.ld_aux & 7) == 0) {
-#pragma unroll
-            for (int g4 = 0; g4 < 4; ++g4) {
-              uint4 u = reinterpret_cast<const uint4*>(ap)[g4];
-              const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&u);
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                float2 f = __bfloat1622float2(u2[j]);
-                av[g4 * 8 + 2 * j] = f.x;
-                av[g4 * 8 + 2 * j + 1] = f.y;
-              }
-            }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) av[j] = (col0 + j < p.N) ? __bfloat162float(ap[j]) : 0.f;
-          }
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const float a = av[j];
-            float g;
-            if (p.act == kActReluBwd) g = a > 0.f ? 1.f : 0.f;  // aux = relu output (after dropout)
-            else if (p.act == kActGeluBwd) g = gelu_grad(a);
-            else { float s = sigmoid_f(a); g = s * (1.f + a * (1.f - s)); }
-            v[j] *= g;
-          }
-        } else if (p.act == kActRelu) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.f);
-        } else if (p.act == kActGelu) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = gelu_f(v[j]);
-        } else if (p.act == kActSilu) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = v[j] * sigmoid_f(v[j]);
-        }
-        if (do_drop) {
-          // element index = row * N + col; 16 consecutive elements share one Philox call (one byte each)
-          const unsigned long long e0 = static_cast<unsigned long long>(row) * p.N + col0;
-#pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            uint4 rnd = rng((e0 >> 4) + h, p.stream_id);
-            const uint32_t w[4] = {rnd.x, rnd.y, rnd.z, rnd.w};
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              uint32_t byte = (w[j >> 2] >> ((j & 3) * 8)) & 0xFFu;
-              v[h * 16 + j] = byte >= thr8 ? v[h * 16 + j] * keep_scale : 0.f;
-            }
-          }
-        }
-        if (p.residual) {
-          const __nv_bfloat16* rp = p.residual + static_cast<size_t>(row) * p.ld_res + col0;
-          if (full_cols) {
-#pragma unroll
-            for (int g = 0; g < 4; ++g) {
-              uint4 b = reinterpret_cast<const uint4*>(rp)[g];
-              const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&b);
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                float2 f = __bfloat1622float2(b2[j]);
-                v[g * 8 + 2 * j] += f.x;
-                v[g * 8 + 2 * j + 1] += f.y;
-              }
-            }
-          } else {
-            for (int j = 0; j < 32; ++j)
-              if (col0 + j < p.N) v[j] += __bfloat162float(rp[j]);
-          }
-        }
-        if (p.out_fp32) {
-          float* op = reinterpret_cast<float*>(p.out) + static_cast<size_t>(row) * p.ld_out + col0;
-          if (p.split_k > 1) {
-            if (full_cols) {
-#pragma unroll
-              for (int g = 0; g < 8; ++g)
-                asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(op + g * 4), "f"(v[g * 4]),
-                             "f"(v[g * 4 + 1]), "f"(v[g * 4 + 2]), "f"(v[g * 4 + 3])
-                             : "memory");
-            } else {
-              for (int j = 0; j < 32; ++j)
-                if (col0 + j < p.N) atomicAdd(op + j, v[j]);
-            }
-          } else if (full_cols) {
-#pragma unroll
-            for (int g = 0; g < 8; ++g) {
-              float4 o = make_float4(v[g * 4], v[g * 4 + 1], v[g * 4 + 2], v[g * 4 + 3]);
-              if (p.accumulate) {
-                float4 old = reinterpret_cast<float4*>(op)[g];
-                o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
-              }
-              reinterpret_cast<float4*>(op)[g] = o;
-            }
-          } else {
-            for (int j = 0; j < 32; ++j)
-              if (col0 + j < p.N) op[j] = p.accumulate ? op[j] + v[j] : v[j];
-          }
-        } else {
-          __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<size_t>(row) * p.ld_out + col0;
-          if (full_cols) {
-#pragma unroll
-            for (int g = 0; g < 4; ++g) {
-              uint4 o;
-              __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
-#pragma unroll
-              for (int j = 0; j < 4; ++j) o2[j] = __floats2bfloat162_rn(v[g * 8 + 2 * j], v[g * 8 + 2 * j + 1]);
-              reinterpret_cast<uint4*>(op)[g] = o;
-            }
-          } else {
-            for (int j = 0; j < 32; ++j)
-              if (col0 + j < p.N) op[j] = __float2bfloat16(v[j]);
-          }
-        }
+        gemm_epilogue_chunk(p, rng, do_drop, row, row_ok, col0,
+                            tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN + c * 32);
       }
       tc_fence_before_sync();
       mbar_arrive(&tmem_empty[acc]);
@@ -505,7 +313,13 @@ static const char* launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, con
 
 }  // namespace b200
 
+namespace b200 {
+const char* launch_gemm_pair(const GemmDesc* d, const GemmArgs& a, int bn, cudaStream_t stream);
+}
 using namespace b200;
+
+static int g_gemm_variant = 0;   // 0 = automatic, 1 = single-CTA kernel only, 2 = CTA-pair kernel whenever M > 128
+void nmtg_set_gemm_variant(int v) { g_gemm_variant = v; }
 
 // Returns nullptr on success, else a static error string.
 const char* nmtg_gemm_bf16(const GemmDesc* d, cudaStream_t stream) {
@@ -513,7 +327,7 @@ const char* nmtg_gemm_bf16(const GemmDesc* d, cudaStream_t stream) {
   if ((d->lda % 8) || (d->ldb % 8)) return "gemm: leading dimensions must be multiples of 8 elements";
   if ((reinterpret_cast<uintptr_t>(d->a) & 15) || (reinterpret_cast<uintptr_t>(d->b) & 15))
     return "gemm: operand base addresses must be 16-byte aligned";
-  if (d->dropout_p > 0.f && (d->N % 16)) return "gemm: dropout epilogue needs N % 16 == 0";
+  if (d->dropout_p > 0.f && (d->N % 4)) return "gemm: dropout epilogue needs N % 4 == 0";
   if ((d->ld_out % 8) || (reinterpret_cast<uintptr_t>(d->out) & 15)) return "gemm: output must be 16-byte aligned";
   GemmArgs a;
   a.M = d->M; a.N = d->N; a.K = d->K;
@@ -527,8 +341,29 @@ const char* nmtg_gemm_bf16(const GemmDesc* d, cudaStream_t stream) {
   a.act = d->act; a.dropout_p = d->dropout_p; a.seed = d->seed; a.stream_id = d->stream_id; a.seed_dev = d->seed_dev;
   a.status = d->status;
 
-  // tile width: 256 when it does not waste a wave, else 128
   const int sms = num_sms();
+  const int num_kb = (d->K + BK - 1) / BK;
+  auto fix_split = [&](int split) {   // largest split <= requested whose last part is not empty
+    if (split > num_kb) split = num_kb;
+    while (split > 1 && (split - 1) * ((num_kb + split - 1) / split) >= num_kb) --split;
+    return split < 1 ? 1 : split;
+  };
+  // ---- CTA-pair kernel (256-row tiles): the default for everything but very small M ----------------
+  if (g_gemm_variant != 1 && d->M > BM) {
+    int bn = (d->N > 128) ? 256 : 128;
+    if (d->force_bn == 128 || d->force_bn == 256) bn = d->force_bn;
+    const long tiles = static_cast<long>((d->M + 2 * BM - 1) / (2 * BM)) * ((d->N + bn - 1) / bn);
+    int split = 1;
+    if (d->split_k > 0) split = d->split_k;
+    else if (d->out_fp32 && d->allow_split_k) {
+      const int clusters = sms / 2;
+      while (tiles * split * 2 <= clusters && num_kb / (split * 2) >= 8) split *= 2;
+    }
+    if (split > 1 && !d->out_fp32) return "gemm: split-K needs an fp32 output";
+    a.split_k = fix_split(split);
+    return launch_gemm_pair(d, a, bn, stream);
+  }
+  // ---- single-CTA kernel: tile width 256 when it does not waste a wave, else 128 -------------------
   const int num_m = (d->M + BM - 1) / BM;
   int bn = 256;
   if (d->N <= 128 || ((d->N % 256) != 0 && (d->N % 128) == 0)) bn = 128;
@@ -539,7 +374,6 @@ const char* nmtg_gemm_bf16(const GemmDesc* d, cudaStream_t stream) {
   }
   if (d->force_bn == 128 || d->force_bn == 256) bn = d->force_bn;
   const int num_n = (d->N + bn - 1) / bn;
-  const int num_kb = (d->K + BK - 1) / BK;
   int split = 1;
   if (d->split_k > 0) split = d->split_k;
   else if (d->out_fp32 && d->allow_split_k) {
@@ -547,8 +381,7 @@ const char* nmtg_gemm_bf16(const GemmDesc* d, cudaStream_t stream) {
     while (tiles * split * 2 <= sms && num_kb / (split * 2) >= 8) split *= 2;
   }
   if (split > 1 && !d->out_fp32) return "gemm: split-K needs an fp32 output";
-  if (split > num_kb) split = num_kb;
-  a.split_k = split;
+  a.split_k = fix_split(split);
 
   CUtensorMap ta, tb;
   bool ok;

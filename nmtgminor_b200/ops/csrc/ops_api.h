@@ -38,6 +38,8 @@ struct GemmDesc {
 };
 
 const char* nmtg_gemm_bf16(const GemmDesc* d, cudaStream_t stream);
+// 0 = automatic (CTA-pair kernel when M > 128), 1 = single-CTA kernel only, 2 = same as 0
+void nmtg_set_gemm_variant(int v);
 
 // LayerNorm over the last dimension of bf16 x[rows, hidden]; mean/rstd (fp32 [rows]) may be null in fwd.
 const char* nmtg_layernorm_fwd(const void* x, const void* gamma, const void* beta, void* y, float* mean, float* rstd,
@@ -116,3 +118,23 @@ const char* nmtg_attn_fwd(const AttnDesc* d, cudaStream_t stream);
 const char* nmtg_attn_bwd(const AttnDesc* d, cudaStream_t stream);
 // 0 = choose automatically (persistent single-tile kernels when max_q, max_k <= 128), 1 = general kernels only
 void nmtg_set_attention_variant(int v);
+
+// ---- peer-memory data parallelism ------------------------------------------------------------------------
+// Pointers of every rank's symmetric buffers as seen from THIS process (own buffers: local pointers; peers:
+// pointers obtained by opening their IPC handles).  flags[r]: int [3][16] epochs, partials[r]: float [2][16].
+struct NmtgPeerTable {
+  int rank, world;
+  float* grads[16];
+  unsigned short* works[16];   // bf16 parameter copies
+  int* flags[16];
+  float* partials[16];
+  float* norm_out;             // optional local float: global gradient norm of the step (-1 when skipped)
+};
+// reduce-scatter of slice [slice_begin, slice_begin + slice_len) + Adam(W) on it + all-gather of the bf16
+// parameters + clearing of the local gradient buffer; reduced / sq / nonfinite are local scratch buffers.
+// *epoch_dev (device int, starts at 1) is the barrier epoch; the last kernel of the step advances it.
+const char* nmtg_allreduce_adamw(const NmtgPeerTable* t, float* reduced, float* sq, int* nonfinite, float* master, float* m,
+                                 float* v, const NmtgAdamHyper* hyper_dev, long slice_begin, long slice_len, long total_len,
+                                 int* epoch_dev, int* status, cudaStream_t stream);
+// waits (bounded) on one flag row; used to exercise the timeout path
+const char* nmtg_peer_wait_row(const NmtgPeerTable* t, int row, int epoch, int* status, cudaStream_t stream);

@@ -35,7 +35,7 @@ class FlatParameterStore:
     """Owns the flat master / working / gradient buffers of a model."""
 
     def __init__(self, module: torch.nn.Module, device=None, work_dtype=torch.bfloat16,
-                 allocator: Optional[Callable[[int, torch.dtype], torch.Tensor]] = None,
+                 allocator=None,   # callable(numel, dtype) -> tensor, or {'master' | 'grad' | 'work': callable}
                  pad_total_to: int = ALIGN):
         params = _unique_params(p for p in module.parameters())
         self.params = params
@@ -46,10 +46,12 @@ class FlatParameterStore:
             self.offsets.append(off)
             off += (p.numel() + ALIGN - 1) // ALIGN * ALIGN
         self.total = (off + pad_total_to - 1) // pad_total_to * pad_total_to if off else 0
-        alloc = allocator or (lambda n, dt: torch.zeros(n, dtype=dt, device=self.device))
-        self.master = alloc(self.total, torch.float32)
-        self.grad = alloc(self.total, torch.float32)
-        self.work = alloc(self.total, work_dtype) if self.device.type == "cuda" else None
+        default = lambda n, dt: torch.zeros(n, dtype=dt, device=self.device)
+        allocs = allocator if isinstance(allocator, dict) else {"master": allocator, "grad": allocator, "work": allocator}
+        pick = lambda name: allocs.get(name) or default
+        self.master = pick("master")(self.total, torch.float32)
+        self.grad = pick("grad")(self.total, torch.float32)
+        self.work = pick("work")(self.total, work_dtype) if self.device.type == "cuda" else None
         self.trainable_mask = None
         for p, o in zip(params, self.offsets):
             n = p.numel()

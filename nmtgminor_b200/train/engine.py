@@ -66,17 +66,47 @@ class _StaticInputs:
 
 class TrainEngine:
     def __init__(self, model: torch.nn.Module, opt, device=None, reducer=None, cuda_graph: bool = False,
-                 grad_scale: float = 1.0):
+                 grad_scale: float = 1.0, ddp: Optional[str] = None):
+        """``ddp``: None (single process or an explicit ``reducer`` callable), ``"nccl"`` (all-reduce of the flat
+        gradient buffer through torch.distributed) or ``"fused"`` (peer-memory reduce-scatter + sharded Adam(W) +
+        all-gather kernels; needs an initialised process group on one node)."""
         self.model = model
         self.opt = opt
         self.device = torch.device(device) if device is not None else torch.device(
             "cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
         self.on_gpu = self.device.type == "cuda"
-        self.store = FlatParameterStore(model, self.device)
+        import torch.distributed as dist
+        world = dist.get_world_size() if (dist.is_available() and dist.is_initialized()) else 1
+        self.world_size = world
+        heap = None
+        ptrs = {}
+        if ddp == "fused" and world > 1 and self.on_gpu and ops.extension_available():
+            from ..parallel.symmetric import SymmetricHeap
+            heap = SymmetricHeap(self.device)
+
+            def symm(name):
+                def alloc(n, dt):
+                    t, p = heap.alloc(n, dt)
+                    ptrs[name] = p
+                    return t
+                return alloc
+            self.store = FlatParameterStore(model, self.device, allocator={"grad": symm("grad"), "work": symm("work")},
+                                            pad_total_to=256 * world)
+        else:
+            self.store = FlatParameterStore(model, self.device, pad_total_to=256 * max(world, 1))
         for b in model.buffers():
             b.data = b.data.to(self.device)
         self.optim = Optim(opt)
         self.optim.set_parameters(model.parameters(), self.store)
+        if world > 1 and reducer is None and ddp is not None:
+            from ..parallel.ddp import NcclReducer, broadcast_parameters
+            broadcast_parameters(self.store)
+            if heap is not None and self.optim.fused:
+                from ..parallel.symmetric import FusedAllReduceAdam
+                reducer = FusedAllReduceAdam(self.store, self.optim, heap, ptrs["grad"], ptrs["work"])
+                self.optim.attach_distributed(reducer)
+            else:
+                reducer = NcclReducer(world)
         self.reducer = reducer            # callable(flat_grad) -> None, data-parallel gradient reduction
         self.grad_scale = grad_scale
         self.use_graph = bool(cuda_graph) and self.on_gpu

@@ -127,8 +127,16 @@ class Optim:
         ints[10] = 1 if zero_grad else 0
         self.hyper.copy_(h, non_blocking=True)
 
+    def attach_distributed(self, fused_reducer) -> None:
+        """Route the fused update through the peer-memory kernels (sharded master slice and moments)."""
+        self.distributed = fused_reducer
+        self.exp_avg = self.exp_avg_sq = None      # the replicated moments are not needed any more
+
     def launch_fused(self):
         """Enqueue norm + update kernels (graph-capturable: reads only device-resident scalars)."""
+        if getattr(self, "distributed", None) is not None:
+            self.distributed.launch()
+            return
         s = self.store
         self.grad_sq.zero_()
         self.nonfinite.zero_()
@@ -159,6 +167,8 @@ class Optim:
 
     def grad_norm(self) -> float:
         """Global gradient norm of the last fused step (after unscaling), or of ``p.grad`` tensors."""
+        if self.fused and getattr(self, "distributed", None) is not None:
+            return float(self.distributed.norm.item())
         if self.fused:
             return float(self.grad_sq.sqrt().item()) * float(self._hyper_host[7])
         sq = sum(float(p.grad.float().pow(2).sum()) for p in self.params if p.grad is not None)
@@ -173,7 +183,9 @@ class Optim:
 
     # -- state ------------------------------------------------------------------------------------
     def state_dict(self):
-        if self.fused:
+        if self.fused and getattr(self, "distributed", None) is not None:
+            sd = {"fused": True, "sharded": self.distributed.state_dict()}
+        elif self.fused:
             sd = {"fused": True, "exp_avg": self.exp_avg.cpu(), "exp_avg_sq": self.exp_avg_sq.cpu()}
         else:
             sd = self.optimizer.state_dict()
@@ -185,8 +197,17 @@ class Optim:
         sd = dict(sd)
         self._step = sd.pop("_step", 0)
         self._epoch_decay = sd.pop("_epoch_decay", 1.0)
-        if self.fused:
-            if sd.get("fused"):
+        if self.fused and getattr(self, "distributed", None) is not None:
+            sh = sd.get("sharded")
+            d = self.distributed
+            if sh is not None and sh["begin"] == d.begin and sh["length"] == d.length:
+                d.exp_avg.copy_(sh["exp_avg"])
+                d.exp_avg_sq.copy_(sh["exp_avg_sq"])
+            elif "exp_avg" in sd:
+                d.exp_avg.copy_(sd["exp_avg"][d.begin:d.begin + d.length])
+                d.exp_avg_sq.copy_(sd["exp_avg_sq"][d.begin:d.begin + d.length])
+        elif self.fused:
+            if sd.get("fused") and "exp_avg" in sd:
                 self.exp_avg.copy_(sd["exp_avg"])
                 self.exp_avg_sq.copy_(sd["exp_avg_sq"])
             elif "state" in sd:

@@ -23,7 +23,6 @@ import torch.distributed as dist
 from .. import ops
 from ..data.iterator import DataIterator, MultiDataIterator
 from ..models.factory import build_model
-from ..parallel.ddp import broadcast_parameters, make_reducer
 from ..utils.logging import Logger
 from .checkpoint import checkpoint_name, load_model_state, prune_checkpoints, save_checkpoint
 from .engine import TrainEngine
@@ -67,13 +66,12 @@ class Trainer:
         self._resume_checkpoint = checkpoint
 
         grad_scale = 1.0
+        ddp = None
+        if self.world_size > 1:
+            ddp = "nccl" if (getattr(opt, "nccl_ddp", False) or not self.cuda) else "fused"
         self.engine = TrainEngine(self.model, opt, self.device, reducer=None,
                                   cuda_graph=getattr(opt, "cuda_graph", False) and getattr(opt, "update_frequency", 1) == 1,
-                                  grad_scale=grad_scale)
-        if self.world_size > 1:
-            mode = "nccl" if getattr(opt, "nccl_ddp", False) else "fused"
-            self.engine.reducer = make_reducer(self.world_size, mode, self.engine.store, self.engine.optim)
-            broadcast_parameters(self.engine.store)
+                                  grad_scale=grad_scale, ddp=ddp)
         self.optim = self.engine.optim
         if checkpoint is not None and not getattr(opt, "reset_optim", False) and checkpoint.get("optim") is not None:
             try:
@@ -126,6 +124,9 @@ class Trainer:
         return tot_loss / max(tot_words, 1.0), tot_correct / max(tot_words, 1.0)
 
     def save(self, epoch: float, valid_ppl: float, itr=None, accuracy: float = 0.0):
+        dist_opt = getattr(self.optim, "distributed", None)
+        if dist_opt is not None:
+            dist_opt.gather_master()      # collective: every rank refreshes its full fp32 copy from the slice owners
         if not self.is_main():
             return None
         opt = self.opt

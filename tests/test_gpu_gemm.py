@@ -8,6 +8,14 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda"
 
 
+@pytest.fixture(params=[0, 1], ids=["pair", "single"], autouse=True)
+def gemm_variant(request):
+    """0 = automatic (CTA-pair kernel for M > 128), 1 = single-CTA kernel only."""
+    ops.ext().set_gemm_variant(request.param)
+    yield request.param
+    ops.ext().set_gemm_variant(0)
+
+
 def _rel_err(got, want):
     got, want = got.float(), want.float()
     return ((got - want).abs().max() / (want.abs().max() + 1e-6)).item()

@@ -1,0 +1,90 @@
+#!/usr/bin/env python
+"""Training entry point: one process per GPU.
+
+    python train_distributed.py -data <prefix> -data_format raw|bin|mmap -save_model <path> -gpus 0 1 2 3 ...
+
+Loads the preprocessed corpus, builds token-budget ``Dataset`` objects, then either runs the trainer in this
+process (one GPU / CPU) or spawns one process per listed GPU (``torch.multiprocessing.spawn``), each of which
+joins a NCCL process group over 127.0.0.1.  When launched under ``torchrun`` (RANK / WORLD_SIZE in the
+environment) no processes are spawned and the environment's rank is used.
+Reference flow: train_distributed.py:118-727.
+"""
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+import numpy as np
+import torch
+
+from nmtgminor_b200.constants import Constants
+from nmtgminor_b200.data.dataset import Dataset
+from nmtgminor_b200.data.mmap_dataset import MMapIndexedDataset
+from nmtgminor_b200.options import make_parser
+
+
+def _dataset_from(split, opt, dicts, training):
+    if split is None or (split.get("src") is None and split.get("tgt") is None):
+        return None
+    return Dataset(split.get("src"), split.get("tgt"), split.get("src_sizes"), split.get("tgt_sizes"), split.get("src_lang"),
+                   split.get("tgt_lang"), split.get("src_atb"), split.get("tgt_atb"),
+                   batch_size_words=opt.batch_size_words, batch_size_frames=getattr(opt, "batch_size_frames", 10 ** 12),
+                   batch_size_sents=opt.batch_size_sents if opt.batch_size_sents > 0 else 10 ** 9,
+                   multiplier=opt.batch_size_multiplier, data_type=getattr(opt, "encoder_type", "text") if getattr(opt, "encoder_type", "text") != "text" else "text",
+                   max_src_len=opt.max_src_length if training else 10 ** 9, max_tgt_len=(opt.max_tgt_length + 2) if training else 10 ** 9,
+                   cleaning=training, verbose=True)
+
+
+def load_data(opt):
+    fmt = opt.data_format
+    if fmt in ("raw", "bin"):
+        blob = torch.load(opt.data + ".train.pt", map_location="cpu", weights_only=False)
+        dicts = blob["dicts"]
+        train, valid = blob["train"], blob.get("valid")
+    elif fmt in ("mmap", "mmem"):
+        dicts = torch.load(opt.data + ".dict.pt", map_location="cpu", weights_only=False)
+
+        def side(split):
+            out = {}
+            for s in ("src", "tgt", "src_lang", "tgt_lang"):
+                prefix = "%s.%s.%s" % (opt.data, split, s)
+                out[s] = MMapIndexedDataset(prefix) if MMapIndexedDataset.exists(prefix) else None
+            for s in ("src", "tgt"):
+                f = "%s.%s.%s_sizes.npy" % (opt.data, split, s)
+                out[s + "_sizes"] = np.load(f) if os.path.exists(f) else None
+            return out
+        train, valid = side("train"), side("valid")
+    else:
+        raise NotImplementedError("data format %r" % fmt)
+    return dicts, _dataset_from(train, opt, dicts, True), _dataset_from(valid, opt, dicts, False)
+
+
+def run_process(rank, opt):
+    from nmtgminor_b200.train.trainer import Trainer
+    if len(opt.gpus) > 1 and "RANK" not in os.environ:
+        os.environ["RANK"] = str(rank)
+        os.environ["LOCAL_RANK"] = str(opt.gpus[rank])
+        os.environ["WORLD_SIZE"] = str(len(opt.gpus))
+    os.environ.setdefault("MASTER_ADDR", opt.master_addr or "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", str(opt.master_port or 8888))
+    dicts, train_data, valid_data = load_data(opt)
+    if getattr(opt, "patch_vocab_multiplier", 1) > 1 and "tgt" in dicts:
+        dicts["tgt"].patch(opt.patch_vocab_multiplier)
+    constants = Constants.from_dicts(opt, dicts)
+    trainer = Trainer(opt.gpus[rank] if opt.gpus else -1, dicts, opt, constants)
+    trainer.run(train_data=train_data, valid_data=valid_data)
+
+
+def cli_main(argv=None):
+    opt = make_parser().parse_args(argv)
+    if "WORLD_SIZE" in os.environ and int(os.environ["WORLD_SIZE"]) > 1:
+        opt.gpus = list(range(int(os.environ["WORLD_SIZE"])))
+        run_process(int(os.environ["RANK"]), opt)
+    elif len(opt.gpus) <= 1:
+        run_process(0, opt)
+    else:
+        torch.multiprocessing.spawn(run_process, nprocs=len(opt.gpus), args=(opt,))
+
+
+if __name__ == "__main__":
+    cli_main()
