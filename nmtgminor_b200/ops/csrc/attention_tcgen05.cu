@@ -558,3 +558,90 @@ const char* nmtg_attn_bwd(const AttnDesc* d, cudaStream_t stream) {
   }
   return nullptr;
 }
+
+// ---------------------------------------------------------------------------------------------------
+// Backward pass with a built-in accumulation buffer (see attention_noalloc.h for the contract).
+// ---------------------------------------------------------------------------------------------------
+#include "attention_noalloc.h"
+#include <cstdio>
+
+namespace b200 {
+bool make_tmap_bf16_2d(CUtensorMap* out, const void* base, long rows, long cols, long ld, int box_rows, int box_cols);
+}
+
+// The fp32 dQ accumulation buffer of the no-allocation entry point.  In host code this name is only a handle
+// for cudaGetSymbolAddress, never a pointer that a kernel may receive.
+static __device__ __align__(256) float g_attn_noalloc_scratch[NMTG_ATTN_NOALLOC_MAX_FLOATS];
+static float* g_attn_noalloc_ptr[64] = {};   // device address of the array, per device ordinal
+
+static int noalloc_fail(int code, const char* msg, char* err, int err_len) {
+  if (err && err_len > 0) snprintf(err, static_cast<size_t>(err_len), "%s", msg);
+  return code;
+}
+
+extern "C" int nmtg_attn_bwd_noalloc(const void* q, int ld_q, const void* k, int ld_k, const void* v, int ld_v, const void* out,
+                                     int ld_out, const float* lse, long lse_stride, const void* d_out, int ld_dout, void* dq,
+                                     int ld_dq, void* dk, int ld_dk, void* dv, int ld_dv, const int* cu_q, const int* cu_k,
+                                     int batch, int num_heads, int max_q, int max_k, int total_q, int total_k, int causal,
+                                     float scale, float dropout_p, unsigned long long seed, unsigned long long stream_id,
+                                     int* status, cudaStream_t stream, char* err, int err_len) {
+  if (batch <= 0 || num_heads <= 0 || total_q <= 0 || total_k <= 0) return 0;
+  const void* ptrs[] = {q, k, v, out, d_out, dq, dk, dv};
+  const int lds[] = {ld_q, ld_k, ld_v, ld_out, ld_dout, ld_dq, ld_dk, ld_dv};
+  for (int i = 0; i < 8; ++i)
+    if (!ptrs[i] || (reinterpret_cast<uintptr_t>(ptrs[i]) & 15) || (lds[i] % 8))
+      return noalloc_fail(1, "attention: tensors must be non-null, 16-byte aligned, with leading dimensions % 8 == 0", err, err_len);
+  if (!lse || !cu_q || !cu_k) return noalloc_fail(1, "attention: lse / cu_q / cu_k must not be null", err, err_len);
+  const int width = num_heads * kHd;
+  const bool needs_buffer = max_k > kTile;
+  const long need = static_cast<long>(total_q) * width;
+  if (needs_buffer && need > NMTG_ATTN_NOALLOC_MAX_FLOATS) {
+    char msg[200];
+    snprintf(msg, sizeof(msg), "attention backward without allocation: total_q * heads * 64 = %ld floats exceeds the built-in "
+             "buffer of %ld floats", need, static_cast<long>(NMTG_ATTN_NOALLOC_MAX_FLOATS));
+    return noalloc_fail(2, msg, err, err_len);
+  }
+  int dev = 0;
+  cudaError_t ce = cudaGetDevice(&dev);
+  if (ce != cudaSuccess || dev < 0 || dev >= 64) return noalloc_fail(3, "cudaGetDevice failed", err, err_len);
+  if (!g_attn_noalloc_ptr[dev]) {   // first call on this device: resolve the array's device address
+    float* p = nullptr;
+    ce = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_attn_noalloc_scratch);
+    if (ce != cudaSuccess || !p) return noalloc_fail(3, cudaGetErrorString(ce), err, err_len);
+    g_attn_noalloc_ptr[dev] = p;
+  }
+  float* scratch = g_attn_noalloc_ptr[dev];
+  if (needs_buffer) {   // the array still holds the previous call's sums
+    ce = cudaMemsetAsync(scratch, 0, static_cast<size_t>(need) * sizeof(float), stream);
+    if (ce != cudaSuccess) return noalloc_fail(3, cudaGetErrorString(ce), err, err_len);
+  }
+  CUtensorMap tq, tk, tv, tdo;
+  if (!make_tmap_bf16_2d(&tq, q, total_q, width, ld_q, kTile, kHd) || !make_tmap_bf16_2d(&tk, k, total_k, width, ld_k, kTile, kHd) ||
+      !make_tmap_bf16_2d(&tv, v, total_k, width, ld_v, kTile, kHd) || !make_tmap_bf16_2d(&tdo, d_out, total_q, width, ld_dout, kTile, kHd))
+    return noalloc_fail(3, "attention: cuTensorMapEncodeTiled failed", err, err_len);
+  AttnArgs a = {};
+  a.cu_q = cu_q; a.cu_k = cu_k; a.num_heads = num_heads; a.causal = causal; a.scale = scale;
+  a.dropout_p = dropout_p; a.seed = seed; a.stream_id = stream_id; a.seed_dev = nullptr;
+  a.kstride = (max_k + 15) / 16 * 16;
+  a.lse = const_cast<float*>(lse); a.lse_stride = lse_stride;
+  a.o = reinterpret_cast<const __nv_bfloat16*>(out); a.ld_o = ld_out;
+  a.d_o = reinterpret_cast<const __nv_bfloat16*>(d_out); a.ld_do = ld_dout;
+  a.dq = reinterpret_cast<__nv_bfloat16*>(dq); a.ld_dq = ld_dq;
+  a.dk = reinterpret_cast<__nv_bfloat16*>(dk); a.ld_dk = ld_dk;
+  a.dv = reinterpret_cast<__nv_bfloat16*>(dv); a.ld_dv = ld_dv;
+  a.dq_acc = scratch; a.ld_dqacc = width;
+  a.total_q = total_q; a.status = status;
+  ce = cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kBwdSmem);
+  if (ce != cudaSuccess) return noalloc_fail(3, cudaGetErrorString(ce), err, err_len);
+  dim3 grid((max_k + kTile - 1) / kTile, num_heads, batch);
+  attn_bwd_kernel<<<grid, 128, kBwdSmem, stream>>>(tq, tk, tv, tdo, a);
+  ce = cudaGetLastError();
+  if (ce != cudaSuccess) return noalloc_fail(3, cudaGetErrorString(ce), err, err_len);
+  if (needs_buffer) {
+    dim3 g2(64, batch);
+    attn_dq_convert_kernel<<<g2, 256, 0, stream>>>(scratch, width, reinterpret_cast<__nv_bfloat16*>(dq), ld_dq, cu_q, cu_k, width);
+    ce = cudaGetLastError();
+    if (ce != cudaSuccess) return noalloc_fail(3, cudaGetErrorString(ce), err, err_len);
+  }
+  return 0;
+}

@@ -1,0 +1,100 @@
+"""The attention backward entry point that brings its own scratch memory.
+
+Some hosts of these kernels cannot hand over freshly allocated device memory: a server whose memory manager owns
+the whole GPU, a plug-in inside another runtime's pool, code between the begin and end of a stream capture.  For
+them ``nmtg_attn_bwd_noalloc`` (declared in ``ops/csrc/attention_noalloc.h``) keeps the fp32 dQ accumulation buffer
+in a fixed array inside the library.  This test calls it through its exported C symbol, twice in a row on
+different data (the array is shared and keeps the previous call's contents, so the second call checks that stale
+sums are cleared), and compares with the regular entry point, which gets its buffer from the caller.  It also
+checks that a problem larger than the built-in buffer is refused with a message instead of being launched.
+
+The file name sorts last on purpose: a run that stops at the first failure has then already run everything else.
+"""
+import ctypes
+import os
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+HEADS, W = 2, 128
+MAX_FLOATS = 4 << 20
+
+
+def _lib():
+    from nmtgminor_b200 import ops
+    ops.ext()                                    # builds / loads the extension and its dependencies
+    lib = ctypes.CDLL(os.path.join(os.path.dirname(ops.__file__), "_nmtg_b200_C.so"))
+    fn = lib.nmtg_attn_bwd_noalloc
+    P, I, L = ctypes.c_void_p, ctypes.c_int, ctypes.c_long
+    fn.argtypes = [P, I, P, I, P, I, P, I, P, L, P, I, P, I, P, I, P, I, P, P, I, I, I, I, I, I, I, ctypes.c_float,
+                   ctypes.c_float, ctypes.c_ulonglong, ctypes.c_ulonglong, P, P, ctypes.c_char_p, I]
+    fn.restype = I
+    return fn
+
+
+def _case(seed, lengths):
+    from nmtgminor_b200 import ops
+    torch.manual_seed(seed)
+    dev = "cuda"
+    n = sum(lengths)
+    cu = torch.zeros(len(lengths) + 1, dtype=torch.int32)
+    cu[1:] = torch.tensor(lengths).cumsum(0)
+    cu = cu.to(dev)
+    qkv = torch.randn(n, 3 * W, device=dev).bfloat16()
+    q, k, v = qkv[:, :W], qkv[:, W:2 * W], qkv[:, 2 * W:]
+    out = torch.zeros(n, W, device=dev, dtype=torch.bfloat16)
+    lse = torch.empty(HEADS, n, device=dev)
+    mx = max(lengths)
+    scale = 0.125
+    ops.ext().attn_fwd(q, k, v, out, lse, cu, cu, HEADS, mx, mx, True, scale, 0.0, 1, 1)
+    d_out = torch.randn(n, W, device=dev).bfloat16()
+    return dict(n=n, cu=cu, qkv=qkv, q=q, k=k, v=v, out=out, lse=lse, d_out=d_out, mx=mx, scale=scale)
+
+
+def _regular(c):
+    from nmtgminor_b200 import ops
+    g = torch.zeros_like(c["qkv"])
+    acc = torch.zeros(c["n"], W, device="cuda")
+    ops.ext().attn_bwd(c["q"], c["k"], c["v"], c["out"], c["lse"], c["d_out"], g[:, :W], g[:, W:2 * W], g[:, 2 * W:], acc, c["cu"],
+                       c["cu"], HEADS, c["mx"], c["mx"], True, c["scale"], 0.0, 1, 1)
+    return g
+
+
+def _noalloc(fn, c, total_q=None):
+    g = torch.zeros_like(c["qkv"])
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    err = ctypes.create_string_buffer(256)
+    ld = 3 * W
+    ptr = lambda t: ctypes.c_void_p(t.data_ptr())
+    rc = fn(ptr(c["q"]), ld, ptr(c["k"]), ld, ptr(c["v"]), ld, ptr(c["out"]), W, ptr(c["lse"]), c["lse"].stride(0), ptr(c["d_out"]), W,
+            ptr(g[:, :W]), ld, ptr(g[:, W:2 * W]), ld, ptr(g[:, 2 * W:]), ld, ptr(c["cu"]), ptr(c["cu"]), c["cu"].numel() - 1, HEADS,
+            c["mx"], c["mx"], c["n"] if total_q is None else total_q, c["n"], 1, c["scale"], 0.0, 1, 1, ptr(status),
+            ctypes.c_void_p(torch.cuda.current_stream().cuda_stream), err, 256)
+    return rc, g, status, err.value.decode()
+
+
+def _rel(a, b):
+    a, b = a.float(), b.float()
+    return ((a - b).abs().max() / (b.abs().max() + 1e-6)).item()
+
+
+def test_noalloc_entry_point_matches_regular_one_twice_in_a_row():
+    fn = _lib()
+    for seed, lengths in ((0, [300, 17, 140]), (1, [200, 260])):      # > 128 keys: the scratch buffer is in play
+        c = _case(seed, lengths)
+        want = _regular(c)
+        rc, got, status, msg = _noalloc(fn, c)
+        torch.cuda.synchronize()
+        assert rc == 0, msg
+        assert int(status.item()) == 0
+        assert _rel(got, want) < 3e-2, "call with seed %d differs from the regular entry point" % seed
+
+
+def test_noalloc_entry_point_rejects_oversized_problems():
+    fn = _lib()
+    c = _case(2, [150])
+    too_many_rows = MAX_FLOATS // W + 1
+    rc, _, _, msg = _noalloc(fn, c, total_q=too_many_rows)
+    assert rc == 2 and "exceeds the built-in buffer" in msg
