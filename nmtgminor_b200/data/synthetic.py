@@ -74,3 +74,20 @@ def token_budget_batches(vocab: int, min_len: int, max_len: int, tokens_per_batc
             b.packed_source().max_len = m_s
             b.packed_target_input().max_len = m_t
     return out
+
+
+def synthetic_audio_batch(n: int, vocab: int, kind: str = "wav", min_len: int = 4000, max_len: int = 8000, n_feats: int = 80,
+                          tgt_min: int = 5, tgt_max: int = 20, seed: int = 1, fixed_frames: int = 0) -> Batch:
+    """Speech batch: raw 16 kHz waveforms ~N(0, 0.1) (``kind='wav'``) or feature matrices ~N(0, 1) (``kind='feats'``:
+    log-mel / filterbank frames; ``fixed_frames`` > 0 gives every utterance that many frames, as Whisper's 30 s windows)."""
+    rng = np.random.RandomState(seed)
+    src, tgt = [], []
+    for _ in range(n):
+        L = fixed_frames if fixed_frames > 0 else int(rng.randint(min_len, max_len + 1))
+        if kind == "wav":
+            src.append(torch.from_numpy((rng.randn(L, 1) * 0.1).astype(np.float32)))
+        else:
+            src.append(torch.from_numpy(rng.randn(L, n_feats).astype(np.float32)))
+        lt = int(rng.randint(tgt_min, tgt_max + 1))
+        tgt.append(torch.from_numpy(np.concatenate([[C.BOS], rng.randint(4, vocab, size=lt), [C.EOS]]).astype(np.int64)))
+    return collate(src, tgt, src_type="audio", padded=True, packed=True, round_to=16)

@@ -66,8 +66,8 @@ def _load_builders():
         return _t.Transformer(opt, dicts)
 
     import importlib
-    for mod in ("relative_transformer", "speech", "wav2vec2", "mbart", "whisper", "deltalm", "conformer", "lstm",
-                "transformer_xl", "classifier", "pretrain_transformer", "multilingual", "discourse", "universal"):
+    for mod in ("pretrained", "relative_transformer", "conformer", "lstm", "transformer_xl", "classifier", "multilingual",
+                "discourse", "research"):
         try:
             m = importlib.import_module("." + mod, __package__)
         except ModuleNotFoundError as exc:

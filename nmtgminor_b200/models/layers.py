@@ -238,10 +238,11 @@ class FeedForward(nn.Module):
 
 
 class EncoderLayer(nn.Module):
-    """Pre-LN block: x += D(SelfAttn(LN(x))); x += D(FFN(LN(x))), with optional stochastic depth."""
+    """Self-attention + FFN block.  Pre-LN: x += D(Attn(LN(x))); x += D(FFN(LN(x))).  Post-LN (``post_norm``):
+    x = LN(x + D(Attn(x))); x = LN(x + D(FFN(x))).  Optional stochastic depth (``death_rate``)."""
 
     def __init__(self, dim, heads, inner, dropout=0.1, attn_dropout=0.1, activation="relu", attn_bias=False,
-                 death_rate=0.0, ffn_dropout=None):
+                 death_rate=0.0, ffn_dropout=None, post_norm=False):
         super().__init__()
         self.attn_norm = LayerNorm(dim)
         self.attn = SelfAttention(dim, heads, attn_dropout, bias=attn_bias)
@@ -249,41 +250,92 @@ class EncoderLayer(nn.Module):
         self.ffn = FeedForward(dim, inner, dropout if ffn_dropout is None else ffn_dropout, activation)
         self.dropout = dropout
         self.death_rate = death_rate
+        self.post_norm = post_norm
 
     def forward(self, x, seqs: PackedSeqs):
         if self.training and self.death_rate > 0 and torch.rand(1).item() < self.death_rate:
             return x
+        if self.post_norm:
+            x = self.attn_norm(self.attn(x, seqs, residual=x, dropout_p=self.dropout))
+            return self.ffn_norm(self.ffn(x, residual=x, dropout_p=self.dropout))
         x = self.attn(self.attn_norm(x), seqs, residual=x, dropout_p=self.dropout)
         return self.ffn(self.ffn_norm(x), residual=x, dropout_p=self.dropout)
 
 
 class DecoderLayer(nn.Module):
-    """Pre-LN block with causal self-attention, encoder-decoder attention and FFN."""
+    """Causal self-attention, encoder-decoder attention and FFN (pre- or post-LN).  ``interleaved_ffn`` adds a
+    second FFN between the two attentions (the DeltaLM decoder layout)."""
 
     def __init__(self, dim, heads, inner, dropout=0.1, attn_dropout=0.1, activation="relu", attn_bias=False,
-                 death_rate=0.0, ffn_dropout=None, ignore_source=False):
+                 death_rate=0.0, ffn_dropout=None, ignore_source=False, post_norm=False, interleaved_ffn=False,
+                 kv_dim=None):
         super().__init__()
+        fd = dropout if ffn_dropout is None else ffn_dropout
         self.self_norm = LayerNorm(dim)
         self.self_attn = SelfAttention(dim, heads, attn_dropout, bias=attn_bias, causal=True)
         self.ignore_source = ignore_source
+        if interleaved_ffn:
+            self.mid_norm = LayerNorm(dim)
+            self.mid_ffn = FeedForward(dim, inner, fd, activation)
+        self.interleaved_ffn = interleaved_ffn
         if not ignore_source:
             self.cross_norm = LayerNorm(dim)
-            self.cross_attn = CrossAttention(dim, heads, attn_dropout, bias=attn_bias)
+            self.cross_attn = CrossAttention(dim, heads, attn_dropout, bias=attn_bias, kv_dim=kv_dim)
         self.ffn_norm = LayerNorm(dim)
-        self.ffn = FeedForward(dim, inner, dropout if ffn_dropout is None else ffn_dropout, activation)
+        self.ffn = FeedForward(dim, inner, fd, activation)
         self.dropout = dropout
         self.death_rate = death_rate
+        self.post_norm = post_norm
 
     def forward(self, x, seqs: PackedSeqs, memory, mem_seqs: PackedSeqs):
         if self.training and self.death_rate > 0 and torch.rand(1).item() < self.death_rate:
             return x
-        x = self.self_attn(self.self_norm(x), seqs, residual=x, dropout_p=self.dropout)
+        p = self.dropout
+        if self.post_norm:
+            x = self.self_norm(self.self_attn(x, seqs, residual=x, dropout_p=p))
+            if self.interleaved_ffn:
+                x = self.mid_norm(self.mid_ffn(x, residual=x, dropout_p=p))
+            if not self.ignore_source:
+                x = self.cross_norm(self.cross_attn(x, seqs, memory, mem_seqs, residual=x, dropout_p=p))
+            return self.ffn_norm(self.ffn(x, residual=x, dropout_p=p))
+        x = self.self_attn(self.self_norm(x), seqs, residual=x, dropout_p=p)
+        if self.interleaved_ffn:
+            x = self.mid_ffn(self.mid_norm(x), residual=x, dropout_p=p)
         if not self.ignore_source:
-            x = self.cross_attn(self.cross_norm(x), seqs, memory, mem_seqs, residual=x, dropout_p=self.dropout)
-        return self.ffn(self.ffn_norm(x), residual=x, dropout_p=self.dropout)
+            x = self.cross_attn(self.cross_norm(x), seqs, memory, mem_seqs, residual=x, dropout_p=p)
+        return self.ffn(self.ffn_norm(x), residual=x, dropout_p=p)
 
     def step(self, x, cache: dict, mem_mask):
+        if self.post_norm:
+            x = self.self_norm(x + self.self_attn.step(x, cache))
+            if self.interleaved_ffn:
+                x = self.mid_norm(self.mid_ffn(x, residual=x))
+            if not self.ignore_source:
+                x = self.cross_norm(x + self.cross_attn.step(x, cache, mem_mask))
+            return self.ffn_norm(self.ffn(x, residual=x))
         x = x + self.self_attn.step(self.self_norm(x), cache)
+        if self.interleaved_ffn:
+            x = self.mid_ffn(self.mid_norm(x), residual=x)
         if not self.ignore_source:
             x = x + self.cross_attn.step(self.cross_norm(x), cache, mem_mask)
         return self.ffn(self.ffn_norm(x), residual=x)
+
+
+def pack_padded(x_bt, lengths, capacity=None):
+    """Right-padded ``[B, T, ...]`` + lengths -> packed ``[N, ...]`` and a ``PackedSeqs`` descriptor (tokens unused)."""
+    B, T = x_bt.shape[0], x_bt.shape[1]
+    lengths = lengths.to(torch.int64).clamp(max=T)
+    ar = torch.arange(T, device=x_bt.device)
+    mask = ar[None, :] < lengths[:, None]
+    packed = x_bt[mask]
+    total = packed.shape[0]
+    cap = capacity if capacity is not None else total
+    if cap > total:
+        packed = torch.cat([packed, packed.new_zeros((cap - total,) + tuple(packed.shape[1:]))], 0)
+    cu = torch.zeros(B + 1, dtype=torch.int32, device=x_bt.device)
+    cu[1:] = torch.cumsum(lengths, 0).to(torch.int32)
+    pos = ar[None, :].expand(B, T)[mask]
+    if cap > total:
+        pos = torch.cat([pos, pos.new_zeros(cap - total)])
+    seqs = PackedSeqs(torch.ones(cap, dtype=torch.int64, device=x_bt.device), pos, cu, int(T), lengths)
+    return packed, seqs

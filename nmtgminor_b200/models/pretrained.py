@@ -1,0 +1,278 @@
+"""Model families built around pretrained-style encoders / decoders, all on the packed fused layers:
+
+* ``PretrainedStyleDecoder`` - mBART / mBART-50 / BART / M2M-100 / Whisper / DeltaLM decoders as one configurable stack
+  (learned or sinusoidal positions with offset, embedding LayerNorm, pre- or post-LN, GELU/ReLU, biases, optional
+  interleaved FFN for DeltaLM, tied output projection);
+* ``PretrainedStyleEncoder`` - the matching text encoders (mBART / BART / M2M-100 / DeltaLM);
+* composite models registered under the reference's names: ``wav2vec2_bert`` (speech encoder + pretrained-style
+  decoder, optional CTC head), ``wav2vec2_transformer``, ``whisper``, ``speech_transformer``,
+  ``pretrain_transformer`` (text encoder + decoder of a chosen family), ``deltalm``.
+
+Sizes come from the reference's json configs when given (``-enc_config_file`` / ``-dec_config_file``, Hugging Face style
+keys), else from the training options.  Reference: pretrain_module/modeling_mbart.py:1598-2276 (encoder, decoder,
+``step``), onmt/models/deltalm/transformer_decoder.py:21-423, onmt/models/whisper/whisper_decoder.py:341-827,
+onmt/models/speech_recognizer/wav2vec2.py:522-1376 (``Wav2vecTransformer``, ``Wav2vecBERT``),
+onmt/model_factory.py:146-731.
+"""
+from __future__ import annotations
+
+import json
+import math
+from types import SimpleNamespace
+from typing import Optional
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from .. import ops
+from .layers import DecoderLayer, Embedding, EncoderLayer, LayerNorm, PackedSeqs
+from .speech_encoders import SpeechTransformerEncoder, Wav2Vec2Encoder, WhisperEncoder
+from .transformer import DecodingState, Generator, Seq2SeqBase
+
+FAMILY_DEFAULTS = {
+    # learned positions, position offset, embedding LayerNorm, final LayerNorm, pre-LN, scale embeddings, activation
+    "mbart": dict(learned_pos=True, pos_offset=2, emb_norm=True, final_norm=True, pre_norm=True, scale=True, act="gelu"),
+    "mbart50": dict(learned_pos=True, pos_offset=2, emb_norm=True, final_norm=True, pre_norm=True, scale=True, act="gelu"),
+    "bart": dict(learned_pos=True, pos_offset=2, emb_norm=True, final_norm=False, pre_norm=False, scale=False, act="gelu"),
+    "m2m100": dict(learned_pos=False, pos_offset=2, emb_norm=False, final_norm=True, pre_norm=True, scale=True, act="relu"),
+    "m2m": dict(learned_pos=False, pos_offset=2, emb_norm=False, final_norm=True, pre_norm=True, scale=True, act="relu"),
+    "deltalm": dict(learned_pos=True, pos_offset=2, emb_norm=True, final_norm=False, pre_norm=False, scale=True, act="gelu",
+                    interleaved=True),
+    "whisper": dict(learned_pos=True, pos_offset=0, emb_norm=False, final_norm=True, pre_norm=True, scale=False, act="gelu"),
+    "bert": dict(learned_pos=True, pos_offset=0, emb_norm=True, final_norm=False, pre_norm=False, scale=False, act="gelu"),
+    "roberta": dict(learned_pos=True, pos_offset=2, emb_norm=True, final_norm=False, pre_norm=False, scale=False, act="gelu"),
+}
+
+
+def load_json_config(path: Optional[str]) -> SimpleNamespace:
+    if not path:
+        return SimpleNamespace()
+    with open(path) as fh:
+        return SimpleNamespace(**json.load(fh))
+
+
+def _cfg(cfg, names, default):
+    for n in names:
+        if hasattr(cfg, n):
+            return getattr(cfg, n)
+    return default
+
+
+class PretrainedStyleDecoder(nn.Module):
+    def __init__(self, family: str, vocab: int, dim: int, layers: int, heads: int, ffn: int, dropout=0.1, attn_dropout=0.0,
+                 max_positions=1024, pad_idx=1, layerdrop=0.0, kv_dim=None):
+        super().__init__()
+        f = FAMILY_DEFAULTS[family]
+        self.family = family
+        self.embed = Embedding(vocab, dim, pad_idx, scale=math.sqrt(dim) if f["scale"] else 1.0, max_pos=max_positions,
+                               learned_pos=f["learned_pos"], pos_offset=f["pos_offset"])
+        self.emb_norm = LayerNorm(dim) if f["emb_norm"] else None
+        self.layers = nn.ModuleList([
+            DecoderLayer(dim, heads, ffn, dropout, attn_dropout, f["act"], attn_bias=True, death_rate=layerdrop,
+                         post_norm=not f["pre_norm"], interleaved_ffn=f.get("interleaved", False), kv_dim=kv_dim)
+            for _ in range(layers)])
+        self.final_norm = LayerNorm(dim) if f["final_norm"] else None
+        self.dropout = dropout
+
+    def _embed(self, seqs: PackedSeqs):
+        if self.emb_norm is None:
+            return self.embed(seqs, self.dropout)
+        return ops.dropout_add(self.emb_norm(self.embed(seqs, 0.0)), None, self.dropout, self.training)
+
+    def forward(self, tgt: PackedSeqs, memory, src: PackedSeqs):
+        x = self._embed(tgt)
+        for layer in self.layers:
+            x = layer(x, tgt, memory, src)
+        return self.final_norm(x) if self.final_norm is not None else x
+
+    def step(self, tokens, position: int, state: DecodingState):
+        B = tokens.shape[0]
+        seqs = PackedSeqs(tokens, torch.full_like(tokens, position), torch.arange(B + 1, dtype=torch.int32, device=tokens.device), 1)
+        x = self.embed(seqs, 0.0)
+        if self.emb_norm is not None:
+            x = self.emb_norm(x)
+        for i, layer in enumerate(self.layers):
+            x = layer.step(x, state.buffers[i], state.src_pad_mask)
+        return self.final_norm(x) if self.final_norm is not None else x
+
+
+class PretrainedStyleEncoder(nn.Module):
+    def __init__(self, family: str, vocab: int, dim: int, layers: int, heads: int, ffn: int, dropout=0.1, attn_dropout=0.0,
+                 max_positions=1024, pad_idx=1, layerdrop=0.0, embed: Optional[Embedding] = None):
+        super().__init__()
+        f = FAMILY_DEFAULTS[family]
+        self.embed = embed or Embedding(vocab, dim, pad_idx, scale=math.sqrt(dim) if f["scale"] else 1.0,
+                                        max_pos=max_positions, learned_pos=f["learned_pos"], pos_offset=f["pos_offset"])
+        self.emb_norm = LayerNorm(dim) if f["emb_norm"] else None
+        self.layers = nn.ModuleList([EncoderLayer(dim, heads, ffn, dropout, attn_dropout, f["act"], attn_bias=True,
+                                                  death_rate=layerdrop, post_norm=not f["pre_norm"]) for _ in range(layers)])
+        self.final_norm = LayerNorm(dim) if f["final_norm"] else None
+        self.dropout = dropout
+
+    def forward(self, src: PackedSeqs):
+        x = self.embed(src, 0.0 if self.emb_norm is not None else self.dropout)
+        if self.emb_norm is not None:
+            x = ops.dropout_add(self.emb_norm(x), None, self.dropout, self.training)
+        for layer in self.layers:
+            x = layer(x, src)
+        return self.final_norm(x) if self.final_norm is not None else x
+
+
+def _decoder_family(opt) -> str:
+    name = (getattr(opt, "dec_pretrained_model", "") or "").lower()
+    for fam in ("mbart50", "mbart", "deltalm", "m2m100", "m2m", "bart", "roberta", "bert", "whisper"):
+        if fam in name:
+            return fam
+    return "mbart50"
+
+
+def _encoder_family(opt) -> str:
+    name = (getattr(opt, "enc_pretrained_model", "") or "").lower()
+    for fam in ("mbart50", "mbart", "deltalm", "m2m100", "m2m", "bart", "roberta", "bert"):
+        if fam in name:
+            return fam
+    return "mbart50"
+
+
+def build_pretrained_decoder(opt, vocab: int, family: Optional[str] = None, kv_dim=None) -> PretrainedStyleDecoder:
+    fam = family or _decoder_family(opt)
+    cfg = load_json_config(getattr(opt, "dec_config_file", ""))
+    dim = _cfg(cfg, ["d_model", "decoder_embed_dim", "hidden_size"], opt.model_size)
+    return PretrainedStyleDecoder(
+        fam, _cfg(cfg, ["vocab_size"], vocab), dim,
+        _cfg(cfg, ["decoder_layers", "num_hidden_layers"], opt.layers),
+        _cfg(cfg, ["decoder_attention_heads", "num_attention_heads"], opt.n_heads),
+        _cfg(cfg, ["decoder_ffn_dim", "decoder_ffn_embed_dim", "intermediate_size"], opt.inner_size),
+        dropout=opt.dropout, attn_dropout=opt.attn_dropout,
+        max_positions=_cfg(cfg, ["max_position_embeddings", "max_target_positions"], 1024),
+        pad_idx=_cfg(cfg, ["pad_token_id"], getattr(opt, "pad_idx", 1)), layerdrop=getattr(opt, "death_rate", 0.0), kv_dim=kv_dim)
+
+
+class SpeechToTextModel(Seq2SeqBase):
+    """Audio encoder + text decoder with optional CTC head on the encoder states (``-ctc_loss``)."""
+
+    def __init__(self, opt, encoder: nn.Module, decoder: nn.Module, vocab: int, generator_bias: bool = True, tie: bool = True):
+        super().__init__()
+        self.opt = opt
+        self.encoder, self.decoder = encoder, decoder
+        dim = decoder.embed.weight.shape[1]
+        self.generator = Generator(dim, vocab, bias=generator_bias)
+        if tie:
+            self.tie_weights()
+        self.pad_idx = decoder.embed.pad_idx
+        self.label_smoothing = getattr(opt, "label_smoothing", 0.0)
+        self.ctc_weight = getattr(opt, "ctc_loss", 0.0)
+        if self.ctc_weight > 0:
+            self.ctc_linear = nn.Linear(encoder.dim, vocab)
+
+    def encode(self, batch):
+        return self.encoder(batch.get("source"))
+
+    def auxiliary_losses(self, batch, context, src, out):
+        if self.ctc_weight <= 0 or not self.training:
+            return None
+        logits = src.pad(self.ctc_linear(context.float()))                   # [T, B, V]
+        lengths = (src.cu[1:] - src.cu[:-1]).to(torch.int64)
+        targets = batch.get("target_output").t()                              # [B, U]
+        tgt_len = (targets != self.pad_idx).sum(-1)
+        lp = F.log_softmax(logits.float(), -1)
+        ctc = F.ctc_loss(lp, targets, lengths[:targets.shape[0]], tgt_len, blank=self.pad_idx, reduction="sum", zero_infinity=True)
+        out["ctc_loss"], out["n_ctc_targets"] = ctc.detach(), int(tgt_len.sum())
+        return self.ctc_weight * ctc
+
+
+class TextToTextPretrained(Seq2SeqBase):
+    """``pretrain_transformer``: pretrained-style text encoder + decoder (mBART, DeltaLM, M2M-100, BART ...)."""
+
+    def __init__(self, opt, dicts):
+        super().__init__()
+        self.opt = opt
+        src_vocab, tgt_vocab = dicts["src"].size(), dicts["tgt"].size()
+        efam, dfam = _encoder_family(opt), _decoder_family(opt)
+        ecfg = load_json_config(getattr(opt, "enc_config_file", ""))
+        dim = _cfg(ecfg, ["d_model", "encoder_embed_dim", "hidden_size"], opt.model_size)
+        n_enc = opt.encoder_layers if getattr(opt, "encoder_layers", -1) > 0 else opt.layers
+        self.encoder = PretrainedStyleEncoder(
+            efam, _cfg(ecfg, ["vocab_size"], src_vocab), dim, _cfg(ecfg, ["encoder_layers", "num_hidden_layers"], n_enc),
+            _cfg(ecfg, ["encoder_attention_heads", "num_attention_heads"], opt.n_heads),
+            _cfg(ecfg, ["encoder_ffn_dim", "encoder_ffn_embed_dim", "intermediate_size"], opt.inner_size), opt.dropout,
+            opt.attn_dropout, pad_idx=getattr(opt, "pad_idx", 1), layerdrop=getattr(opt, "death_rate", 0.0))
+        self.decoder = build_pretrained_decoder(opt, tgt_vocab, dfam, kv_dim=dim)
+        self.generator = Generator(self.decoder.embed.weight.shape[1], self.decoder.embed.weight.shape[0], bias=False)
+        self.tie_weights()
+        if getattr(opt, "join_embedding", False) and self.encoder.embed.weight.shape == self.decoder.embed.weight.shape:
+            self.encoder.embed.weight = self.decoder.embed.weight
+        self.pad_idx = self.decoder.embed.pad_idx
+        self.label_smoothing = getattr(opt, "label_smoothing", 0.0)
+
+    def encode(self, batch):
+        src = batch.packed_source()
+        return self.encoder(src), src
+
+
+def _wav2vec_from_opt(opt) -> Wav2Vec2Encoder:
+    cfg = load_json_config(getattr(opt, "enc_config_file", ""))
+    name = (getattr(opt, "enc_pretrained_model", "") or "wav2vec2").lower()
+    base = "base" in name
+    return Wav2Vec2Encoder(
+        dim=_cfg(cfg, ["encoder_embed_dim", "hidden_size"], 768 if base else 1024),
+        layers=_cfg(cfg, ["encoder_layers", "num_hidden_layers"], 12 if base else 24),
+        heads=_cfg(cfg, ["encoder_attention_heads", "num_attention_heads"], 12 if base else 16),
+        ffn=_cfg(cfg, ["encoder_ffn_embed_dim", "intermediate_size"], 3072 if base else 4096),
+        dropout=getattr(opt, "enc_pretrain_hidden_dropout", opt.dropout) if hasattr(opt, "enc_pretrain_hidden_dropout") else opt.dropout,
+        attn_dropout=opt.attn_dropout, layer_norm_first=_cfg(cfg, ["layer_norm_first"], not base),
+        extractor_mode=_cfg(cfg, ["extractor_mode"], "default" if base else "layer_norm"),
+        conv_bias=_cfg(cfg, ["conv_bias"], not base),
+        mask_prob=getattr(opt, "wav2vec_spec_augment_mask_prob", 0.0) if hasattr(opt, "wav2vec_spec_augment_mask_prob") else 0.0,
+        layerdrop=getattr(opt, "death_rate", 0.0) / 2,
+        freeze_extractor=not getattr(opt, "unfreeze_feature_extractor", False))
+
+
+def _whisper_sizes(opt):
+    cfg = load_json_config(getattr(opt, "dec_config_file", "") or getattr(opt, "enc_config_file", ""))
+    return dict(dim=_cfg(cfg, ["d_model"], opt.model_size), enc_layers=_cfg(cfg, ["encoder_layers"], opt.layers),
+                dec_layers=_cfg(cfg, ["decoder_layers"], opt.layers), heads=_cfg(cfg, ["encoder_attention_heads"], opt.n_heads),
+                ffn=_cfg(cfg, ["encoder_ffn_dim"], opt.inner_size), n_mels=_cfg(cfg, ["num_mel_bins"], getattr(opt, "num_mel_bin", 80) or 80),
+                src_pos=_cfg(cfg, ["max_source_positions"], 1500), tgt_pos=_cfg(cfg, ["max_target_positions"], 448),
+                vocab=_cfg(cfg, ["vocab_size"], None), pad=_cfg(cfg, ["pad_token_id"], getattr(opt, "pad_idx", 0)))
+
+
+def register_builders(register):
+    @register("wav2vec2_bert", "quantize_wav2vec2_bert", "quantize_wav2vec2_mbart50")
+    def _wav2vec_bert(opt, dicts):
+        enc = _wav2vec_from_opt(opt)
+        dec = build_pretrained_decoder(opt, dicts["tgt"].size(), kv_dim=enc.dim)
+        return SpeechToTextModel(opt, enc, dec, dec.embed.weight.shape[0], generator_bias=False)
+
+    @register("wav2vec2_transformer")
+    def _wav2vec_transformer(opt, dicts):
+        from .transformer import TransformerDecoder
+        enc = _wav2vec_from_opt(opt)
+        embed = Embedding(dicts["tgt"].size(), opt.model_size, getattr(opt, "pad_idx", 0))
+        dec = TransformerDecoder(opt, embed)
+        if enc.dim != opt.model_size:
+            for layer in dec.layers:
+                layer.cross_attn.kv = type(layer.cross_attn.kv)(enc.dim, 2 * opt.model_size, bias=layer.cross_attn.kv.bias is not None)
+        return SpeechToTextModel(opt, enc, dec, dicts["tgt"].size())
+
+    @register("whisper")
+    def _whisper(opt, dicts):
+        s = _whisper_sizes(opt)
+        vocab = s["vocab"] or dicts["tgt"].size()
+        enc = WhisperEncoder(s["n_mels"], s["dim"], s["enc_layers"], s["heads"], s["ffn"], s["src_pos"], opt.dropout, opt.attn_dropout)
+        dec = PretrainedStyleDecoder("whisper", vocab, s["dim"], s["dec_layers"], s["heads"], s["ffn"], opt.dropout,
+                                     opt.attn_dropout, max_positions=s["tgt_pos"], pad_idx=s["pad"])
+        return SpeechToTextModel(opt, enc, dec, vocab, generator_bias=False)
+
+    @register("speech_transformer", "hybrid_transformer")
+    def _speech_transformer(opt, dicts):
+        from .transformer import TransformerDecoder
+        enc = SpeechTransformerEncoder(opt, getattr(opt, "input_size", 40))
+        embed = Embedding(dicts["tgt"].size(), opt.model_size, getattr(opt, "pad_idx", 0))
+        dec = TransformerDecoder(opt, embed)
+        return SpeechToTextModel(opt, enc, dec, dicts["tgt"].size())
+
+    @register("pretrain_transformer", "deltalm", "mbart", "mbart50", "m2m100")
+    def _pretrain_transformer(opt, dicts):
+        return TextToTextPretrained(opt, dicts)

@@ -1,0 +1,242 @@
+"""Speech encoders on packed frames: wav2vec 2.0 family (wav2vec2 / HuBERT / WavLM-style), Whisper, and the
+plain speech Transformer front-ends (linear projection of stacked filterbanks or 2 x Conv2d subsampling).
+
+All encoders take the batch's ``source`` tensor ``[T, B, 1 + F]`` (channel 0 = 1 for real frames / samples, 0 for
+padding; the rest are features or the raw waveform), run their convolutional front-end on the padded batch
+(cuDNN through PyTorch), then drop the padding once and run every Transformer layer on packed
+``[frames, hidden]`` matrices with the variable-length attention kernel - the "unpad once" execution that the
+reference only reaches when its fp16 flash path is available
+(onmt/models/speech_recognizer/fairseq_wav2vec2/wav2vec2.py:998-1034).
+
+Reference behaviour: wav2vec2 ``Wav2Vec2Model`` / ``ConvFeatureExtractionModel`` / ``TransformerEncoder``
+(fairseq_wav2vec2/wav2vec2.py:91-731, :733-811, :814-1142), wrapper ``FairseqWav2Vec``
+(onmt/models/speech_recognizer/wav2vec2.py:165-519), HuBERT / WavLM wrappers (hubert.py:93, wavlm.py:56);
+``WhisperEncoder`` (onmt/models/whisper/whisper_encoder.py:545-744); speech Transformer front-ends
+(onmt/models/transformers.py:90-147).
+"""
+from __future__ import annotations
+
+import math
+from typing import List, Optional, Tuple
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from .. import ops
+from .layers import EncoderLayer, LayerNorm, Linear, PackedSeqs, pack_padded, sinusoidal_table
+
+W2V_LARGE_CONV = [(512, 10, 5)] + [(512, 3, 2)] * 4 + [(512, 2, 2)] * 2
+
+
+def split_audio_batch(source):
+    """``[T, B, 1 + F]`` -> features ``[B, T, F]``, lengths ``[B]``."""
+    mask = source[:, :, 0] > 0
+    lengths = mask.sum(0).to(torch.int64)
+    return source[:, :, 1:].transpose(0, 1).contiguous(), lengths
+
+
+def compute_mask_spans(B: int, T: int, lengths, mask_prob: float, mask_length: int, generator=None):
+    """SpecAugment-style time masks: for each utterance ~mask_prob * len / mask_length spans of mask_length frames."""
+    mask = torch.zeros(B, T, dtype=torch.bool)
+    for b in range(B):
+        L = int(lengths[b])
+        n = int(mask_prob * L / max(mask_length, 1) + torch.rand(1, generator=generator).item())
+        if n <= 0 or L <= mask_length:
+            continue
+        starts = torch.randint(0, L - mask_length + 1, (n,), generator=generator)
+        for s in starts.tolist():
+            mask[b, s:s + mask_length] = True
+    return mask
+
+
+class ConvFeatureExtractor(nn.Module):
+    """7-layer strided Conv1d stack over the raw waveform (total stride 320).  ``mode='layer_norm'`` normalises every
+    layer's channels; ``mode='default'`` applies GroupNorm on the first layer only."""
+
+    def __init__(self, conv_layers=W2V_LARGE_CONV, mode: str = "layer_norm", conv_bias: bool = False):
+        super().__init__()
+        self.specs = list(conv_layers)
+        self.mode = mode
+        self.convs = nn.ModuleList()
+        self.norms = nn.ModuleList()
+        c_in = 1
+        for i, (c, k, s) in enumerate(self.specs):
+            conv = nn.Conv1d(c_in, c, k, stride=s, bias=conv_bias)
+            nn.init.kaiming_normal_(conv.weight)
+            self.convs.append(conv)
+            if mode == "layer_norm":
+                self.norms.append(nn.LayerNorm(c))
+            elif i == 0:
+                self.norms.append(nn.GroupNorm(c, c))
+            else:
+                self.norms.append(nn.Identity())
+            c_in = c
+        self.out_dim = c_in
+
+    def output_lengths(self, lengths):
+        for _, k, s in self.specs:
+            lengths = torch.div(lengths - k, s, rounding_mode="floor") + 1
+        return lengths.clamp(min=0)
+
+    def forward(self, wav):          # [B, samples] -> [B, T', C]
+        x = wav.unsqueeze(1)
+        for conv, norm in zip(self.convs, self.norms):
+            x = conv(x)
+            if isinstance(norm, nn.LayerNorm):
+                x = norm(x.transpose(1, 2)).transpose(1, 2)
+            else:
+                x = norm(x)
+            x = F.gelu(x)
+        return x.transpose(1, 2)
+
+
+class ConvPositionalEmbedding(nn.Module):
+    """Grouped Conv1d (k = 128, 16 groups) with weight normalisation + GELU, added to the frame embeddings."""
+
+    def __init__(self, dim: int, kernel: int = 128, groups: int = 16):
+        super().__init__()
+        conv = nn.Conv1d(dim, dim, kernel, padding=kernel // 2, groups=groups)
+        nn.init.normal_(conv.weight, 0, math.sqrt(4.0 / (kernel * dim)))
+        nn.init.zeros_(conv.bias)
+        self.conv = nn.utils.parametrizations.weight_norm(conv, name="weight", dim=2)
+        self.trim = 1 if kernel % 2 == 0 else 0
+
+    def forward(self, x_bt):          # [B, T, C]
+        y = self.conv(x_bt.transpose(1, 2))
+        if self.trim:
+            y = y[:, :, :-self.trim]
+        return F.gelu(y).transpose(1, 2)
+
+
+class Wav2Vec2Encoder(nn.Module):
+    """wav2vec 2.0 encoder: conv feature extractor -> LayerNorm -> projection -> time masking -> conv positions ->
+    Transformer layers on packed frames.  ``layer_norm_first`` (the *large* recipe) uses pre-LN layers with a final
+    LayerNorm, otherwise post-LN layers after an input LayerNorm."""
+
+    def __init__(self, dim=1024, layers=24, heads=16, ffn=4096, dropout=0.1, attn_dropout=0.1, activation="gelu",
+                 layer_norm_first=True, extractor_mode="layer_norm", conv_layers=W2V_LARGE_CONV, conv_bias=False,
+                 mask_prob=0.0, mask_length=10, layerdrop=0.0, freeze_extractor=True, pos_kernel=128, pos_groups=16,
+                 dropout_input=0.0):
+        super().__init__()
+        self.extractor = ConvFeatureExtractor(conv_layers, extractor_mode, conv_bias)
+        self.freeze_extractor = freeze_extractor
+        if freeze_extractor:
+            for p in self.extractor.parameters():
+                p.requires_grad_(False)
+        self.feat_norm = nn.LayerNorm(self.extractor.out_dim)
+        self.post_extract_proj = nn.Linear(self.extractor.out_dim, dim)
+        self.dropout_input = dropout_input
+        self.mask_emb = nn.Parameter(torch.empty(dim).uniform_())
+        self.mask_prob, self.mask_length = mask_prob, mask_length
+        self.pos_conv = ConvPositionalEmbedding(dim, pos_kernel, pos_groups)
+        self.layer_norm_first = layer_norm_first
+        self.input_norm = LayerNorm(dim)      # applied before the layers (post-LN recipe) or after them (pre-LN)
+        self.layers = nn.ModuleList([
+            EncoderLayer(dim, heads, ffn, dropout, attn_dropout, activation, attn_bias=True, death_rate=layerdrop,
+                         post_norm=not layer_norm_first) for _ in range(layers)])
+        self.dim = dim
+
+    def forward(self, source) -> Tuple[torch.Tensor, PackedSeqs]:
+        feats, lengths = split_audio_batch(source)
+        wav = feats[:, :, 0].float()
+        if self.freeze_extractor:
+            with torch.no_grad():
+                x = self.extractor(wav)
+        else:
+            x = self.extractor(wav)
+        out_len = self.extractor.output_lengths(lengths).clamp(max=x.shape[1])
+        x = self.post_extract_proj(self.feat_norm(x))
+        if self.dropout_input > 0:
+            x = F.dropout(x, self.dropout_input, self.training)
+        B, T, _ = x.shape
+        valid = torch.arange(T, device=x.device)[None, :] < out_len[:, None]
+        if self.training and self.mask_prob > 0:
+            m = compute_mask_spans(B, T, out_len.cpu(), self.mask_prob, self.mask_length).to(x.device)
+            x = torch.where(m.unsqueeze(-1), self.mask_emb.to(x.dtype).expand_as(x), x)
+        x = x * valid.unsqueeze(-1)
+        x = x + self.pos_conv(x)
+        packed, seqs = pack_padded(x, out_len)
+        packed = packed.to(torch.bfloat16) if (packed.is_cuda and ops.fused_param(self.input_norm.weight)) else packed
+        if not self.layer_norm_first:
+            packed = self.input_norm(packed)
+        for layer in self.layers:
+            packed = layer(packed, seqs)
+        if self.layer_norm_first:
+            packed = self.input_norm(packed)
+        return packed, seqs
+
+
+class WhisperEncoder(nn.Module):
+    """Whisper audio encoder: Conv1d(mels -> d, k3) + GELU, Conv1d(d -> d, k3, stride 2) + GELU, fixed sinusoidal
+    positions, pre-LN layers, final LayerNorm.  Accepts any number of mel bins (the reference hard-codes 128 + 1)."""
+
+    def __init__(self, n_mels=80, dim=1280, layers=32, heads=20, ffn=5120, max_positions=1500, dropout=0.0,
+                 attn_dropout=0.0, layerdrop=0.0):
+        super().__init__()
+        self.conv1 = nn.Conv1d(n_mels, dim, 3, padding=1)
+        self.conv2 = nn.Conv1d(dim, dim, 3, stride=2, padding=1)
+        self.register_buffer("positions", sinusoidal_table(max_positions, dim), persistent=False)
+        self.layers = nn.ModuleList([EncoderLayer(dim, heads, ffn, dropout, attn_dropout, "gelu", attn_bias=True,
+                                                  death_rate=layerdrop) for _ in range(layers)])
+        self.final_norm = LayerNorm(dim)
+        self.n_mels, self.dim = n_mels, dim
+
+    def forward(self, source):
+        feats, lengths = split_audio_batch(source)           # [B, T, n_mels]
+        assert feats.shape[-1] == self.n_mels, "expected %d mel bins (+1 padding channel), got %d" % (self.n_mels, feats.shape[-1])
+        x = F.gelu(self.conv1(feats.transpose(1, 2).float()))
+        x = F.gelu(self.conv2(x)).transpose(1, 2)             # [B, T/2, d]
+        out_len = torch.div(lengths + 1, 2, rounding_mode="floor").clamp(max=x.shape[1])
+        if x.shape[1] > self.positions.shape[0]:
+            self.positions = sinusoidal_table(x.shape[1], self.dim).to(x.device)
+        x = x + self.positions[:x.shape[1]].to(x.dtype)
+        packed, seqs = pack_padded(x, out_len)
+        packed = packed.to(torch.bfloat16) if (packed.is_cuda and ops.fused_param(self.final_norm.weight)) else packed
+        for layer in self.layers:
+            packed = layer(packed, seqs)
+        return self.final_norm(packed), seqs
+
+
+class SpeechTransformerEncoder(nn.Module):
+    """Filterbank encoder of the ``speech_transformer`` family: linear projection of (stacked) frames, or two
+    stride-2 Conv2d layers (x4 subsampling) followed by a projection, then sinusoidal positions and pre-LN layers."""
+
+    def __init__(self, opt, input_size: int):
+        super().__init__()
+        dim = opt.model_size
+        self.cnn = bool(getattr(opt, "cnn_downsampling", False))
+        self.channels = getattr(opt, "upsampling", 1) if False else 1
+        if self.cnn:
+            self.conv = nn.Sequential(nn.Conv2d(1, 32, 3, stride=2, padding=1), nn.ReLU(), nn.BatchNorm2d(32),
+                                      nn.Conv2d(32, 32, 3, stride=2, padding=1), nn.ReLU(), nn.BatchNorm2d(32))
+            feat = ((input_size + 1) // 2 + 1) // 2 * 32
+            self.proj = nn.Linear(feat, dim)
+        else:
+            self.proj = nn.Linear(input_size, dim)
+        n = opt.encoder_layers if getattr(opt, "encoder_layers", -1) > 0 else opt.layers
+        self.register_buffer("positions", sinusoidal_table(getattr(opt, "max_position_length", 2048), dim), persistent=False)
+        self.layers = nn.ModuleList([EncoderLayer(dim, opt.n_heads, opt.inner_size, opt.dropout, opt.attn_dropout,
+                                                  opt.ffn_activation) for _ in range(n)])
+        self.final_norm = LayerNorm(dim)
+        self.emb_dropout = opt.emb_dropout
+        self.dim = dim
+
+    def forward(self, source):
+        feats, lengths = split_audio_batch(source)
+        if self.cnn:
+            x = self.conv(feats.unsqueeze(1).float())                     # [B, 32, T/4, F/4]
+            x = x.permute(0, 2, 1, 3).reshape(x.shape[0], x.shape[2], -1)
+            lengths = torch.div(torch.div(lengths + 1, 2, rounding_mode="floor") + 1, 2, rounding_mode="floor")
+        else:
+            x = feats.float()
+        x = self.proj(x) * math.sqrt(self.dim)
+        if x.shape[1] > self.positions.shape[0]:
+            self.positions = sinusoidal_table(x.shape[1], self.dim).to(x.device)
+        x = x + self.positions[:x.shape[1]].to(x.dtype)
+        x = F.dropout(x, self.emb_dropout, self.training)
+        packed, seqs = pack_padded(x, lengths.clamp(max=x.shape[1]))
+        packed = packed.to(torch.bfloat16) if (packed.is_cuda and ops.fused_param(self.final_norm.weight)) else packed
+        for layer in self.layers:
+            packed = layer(packed, seqs)
+        return self.final_norm(packed), seqs

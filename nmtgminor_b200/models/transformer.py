@@ -118,7 +118,92 @@ class DecodingState:
     _reorder_incremental_state = reorder  # reference spelling
 
 
-class Transformer(nn.Module):
+class Seq2SeqBase(nn.Module):
+    """Shared behaviour of every encoder-decoder model: fused training loss, gold scoring, incremental decoding.
+
+    Subclasses provide ``encode(batch) -> (context_packed [Ns, H], src PackedSeqs)``, ``self.decoder`` (forward on
+    packed targets + ``step``) and ``self.generator``; everything trainers and translators call lives here
+    (model contract of the reference: onmt/models/transformers.py:548-830, onmt/modules/base_seq2seq.py:50-150).
+    """
+
+    pad_idx = 0
+    label_smoothing = 0.0
+
+    def encode(self, batch):
+        raise NotImplementedError
+
+    def auxiliary_losses(self, batch, context, src, out):
+        """Hook for CTC / language-id / contrastive terms; returns a tensor to add to the loss or None."""
+        return None
+
+    def forward(self, batch, return_logits: bool = False, compute_loss: bool = True, grad_scale=None, **_unused) -> Dict:
+        context, src = self.encode(batch)
+        tgt = batch.packed_target_input()
+        labels = batch.packed_target_output()
+        hidden = self.decoder(tgt, context, src)
+        out = {"hidden_packed": hidden, "context_packed": context, "src": src, "tgt": tgt, "target": labels}
+        if compute_loss:
+            loss, correct, row_loss = ops.generator_cross_entropy(
+                hidden, self.generator.weight, self.generator.bias, labels,
+                self.label_smoothing if self.training else 0.0, self.pad_idx, grad_scale)
+            out.update(loss=loss, correct=correct, row_loss=row_loss)
+            aux = self.auxiliary_losses(batch, context, src, out)
+            if aux is not None:
+                out["nmt_loss"] = out["loss"]
+                out["loss"] = out["loss"] + aux
+        if return_logits:
+            logits = self.generator(hidden)
+            out["logprobs"] = tgt.pad(logits)       # [T, B, V] (logits, as in the reference)
+            out["hidden"] = tgt.pad(hidden)         # [T, B, H]
+            out["context"] = src.pad(context)
+        return out
+
+    def post_backward(self, output_dict=None):
+        return None
+
+    def tie_weights(self):
+        self.generator.weight = self.decoder.embed.weight
+
+    @torch.no_grad()
+    def decode(self, batch):
+        """Gold scoring: per-sentence sum of target log-probabilities ``[B]`` and per-token scores ``[T, B]``."""
+        was_training = self.training
+        self.eval()
+        out = self.forward(batch, compute_loss=True)
+        padded = out["tgt"].pad((-out["row_loss"])[:, None]).squeeze(-1)
+        self.train(was_training)
+        return batch.get("target_output"), padded.sum(0), padded
+
+    @torch.no_grad()
+    def create_decoder_state(self, batch, beam_size: int = 1, **_unused) -> DecodingState:
+        context, src = self.encode(batch)
+        ctx_padded = src.pad(context, time_first=False)                    # [B, Ts, H]
+        lengths = (src.cu[1:] - src.cu[:-1]).to(torch.int64)
+        pad_mask = torch.arange(ctx_padded.shape[1], device=ctx_padded.device)[None, :] >= lengths[:, None]
+        state = DecodingState(ctx_padded, pad_mask, len(self.decoder.layers), beam_size)
+        for i, layer in enumerate(self.decoder.layers):
+            if not getattr(layer, "ignore_source", False):
+                ck, cv = layer.cross_attn.precompute(state.context)
+                state.buffers[i]["c_k"], state.buffers[i]["c_v"] = ck, cv
+        return state
+
+    @torch.no_grad()
+    def step(self, input_t, state: DecodingState) -> Dict:
+        """input_t ``[B*beam, t]`` (all symbols so far) -> ``log_prob [B*beam, V]`` fp32 for the next symbol."""
+        tokens = input_t[:, -1].contiguous()
+        hidden = self.decoder.step(tokens, input_t.shape[1] - 1, state)
+        logits = self.generator(hidden)
+        state.position += 1
+        return {"log_prob": torch.log_softmax(logits.float(), dim=-1), "hidden": hidden, "coverage": None}
+
+    def renew_buffer(self, new_len: int):
+        for m in (getattr(self, "encoder", None), getattr(self, "decoder", None)):
+            emb = getattr(m, "embed", None)
+            if emb is not None and hasattr(emb, "renew"):
+                emb.renew(new_len)
+
+
+class Transformer(Seq2SeqBase):
     """``NMTModel`` for text-to-text translation."""
 
     def __init__(self, opt, dicts):
@@ -141,73 +226,9 @@ class Transformer(nn.Module):
             self.tie_weights()
         self.label_smoothing = getattr(opt, "label_smoothing", 0.0)
 
-    # -- weight sharing --------------------------------------------------------------------------
-    def tie_weights(self):
-        self.generator.weight = self.decoder.embed.weight
-
     def share_enc_dec_embedding(self):
         self.encoder.embed.weight = self.decoder.embed.weight
 
-    # -- training / scoring ----------------------------------------------------------------------
-    def forward(self, batch, return_logits: bool = False, compute_loss: bool = True, grad_scale=None, **_unused) -> Dict:
-        """``batch`` provides ``packed_source()``, ``packed_target_input()`` and ``packed_target_output()``."""
+    def encode(self, batch):
         src = batch.packed_source()
-        tgt = batch.packed_target_input()
-        labels = batch.packed_target_output()
-        context = self.encoder(src)
-        hidden = self.decoder(tgt, context, src)
-        out = {"hidden_packed": hidden, "context_packed": context, "src": src, "tgt": tgt, "target": labels}
-        if compute_loss:
-            loss, correct, row_loss = ops.generator_cross_entropy(
-                hidden, self.generator.weight, self.generator.bias, labels,
-                self.label_smoothing if self.training else 0.0, self.pad_idx, grad_scale)
-            out.update(loss=loss, correct=correct, row_loss=row_loss)
-        if return_logits:
-            logits = self.generator(hidden)
-            out["logprobs"] = tgt.pad(logits)       # [T, B, V] (logits, as in the reference)
-            out["hidden"] = tgt.pad(hidden)         # [T, B, H]
-            out["context"] = src.pad(context)
-        return out
-
-    def post_backward(self, output_dict=None):
-        return None
-
-    @torch.no_grad()
-    def decode(self, batch):
-        """Gold scoring: per-sentence sum of target log-probabilities ``[B]`` and per-token scores."""
-        was_training = self.training
-        self.eval()
-        out = self.forward(batch, compute_loss=True)
-        tgt = out["tgt"]
-        tok_scores = -out["row_loss"]
-        padded = tgt.pad(tok_scores[:, None]).squeeze(-1)   # [T, B]
-        self.train(was_training)
-        return batch.get("target_output"), padded.sum(0), padded
-
-    # -- incremental decoding --------------------------------------------------------------------
-    @torch.no_grad()
-    def create_decoder_state(self, batch, beam_size: int = 1, **_unused) -> DecodingState:
-        src = batch.packed_source()
-        context = self.encoder(src)
-        ctx_padded = src.pad(context, time_first=False)                    # [B, Ts, H]
-        lengths = (src.cu[1:] - src.cu[:-1]).to(torch.int64)
-        pad_mask = torch.arange(ctx_padded.shape[1], device=ctx_padded.device)[None, :] >= lengths[:, None]
-        state = DecodingState(ctx_padded, pad_mask, len(self.decoder.layers), beam_size)
-        for i, layer in enumerate(self.decoder.layers):
-            if not layer.ignore_source:
-                ck, cv = layer.cross_attn.precompute(state.context)
-                state.buffers[i]["c_k"], state.buffers[i]["c_v"] = ck, cv
-        return state
-
-    @torch.no_grad()
-    def step(self, input_t, state: DecodingState) -> Dict:
-        """input_t ``[B*beam, t]`` (all symbols so far) -> ``log_prob [B*beam, V]`` fp32 for the next symbol."""
-        tokens = input_t[:, -1].contiguous()
-        hidden = self.decoder.step(tokens, input_t.shape[1] - 1, state)
-        logits = self.generator(hidden)
-        state.position += 1
-        return {"log_prob": torch.log_softmax(logits.float(), dim=-1), "hidden": hidden, "coverage": None}
-
-    def renew_buffer(self, new_len: int):
-        self.encoder.embed.renew(new_len)
-        self.decoder.embed.renew(new_len)
+        return self.encoder(src), src
