@@ -75,10 +75,10 @@ def beam_search(model, batch, cfg: BeamConfig, prefix_tokens: Optional[torch.Ten
     """Decode every sentence of ``batch``; returns ``n_best`` hypotheses per sentence (best first)."""
     K = cfg.beam_size
     state = model.create_decoder_state(batch, K)
-    src = batch.packed_source()
-    B = src.batch_size
-    device = src.tokens.device
-    src_len = (src.cu[1:] - src.cu[:-1]).to(torch.float32)
+    # batch size / source lengths come from the encoder output, so audio batches (no packed source) work too
+    device = state.context.device
+    B = state.context.shape[0] // K
+    src_len = (~state.src_pad_mask).sum(1)[::K].to(torch.float32)
     if cfg.dynamic_max_len:
         max_len_per = (cfg.len_a * src_len + cfg.len_b).clamp(max=cfg.max_len).long()
     else:
@@ -202,8 +202,8 @@ def beam_search(model, batch, cfg: BeamConfig, prefix_tokens: Optional[torch.Ten
 @torch.no_grad()
 def greedy_search(model, batch, max_len: int = 256, bos: int = 2, eos: int = 3, pad: int = 0) -> List[List[int]]:
     state = model.create_decoder_state(batch, 1)
-    B = batch.packed_source().batch_size
-    device = batch.packed_source().tokens.device
+    B = state.context.shape[0]
+    device = state.context.device
     tokens = torch.full((B, max_len + 2), pad, dtype=torch.long, device=device)
     tokens[:, 0] = bos
     finished = torch.zeros(B, dtype=torch.bool, device=device)

@@ -1,0 +1,147 @@
+"""Multilingual translation models (``-model multilingual_translator`` / ``translator``): language embeddings added to the
+token embeddings, language-factorised weights (MFW: every Linear weight is modulated by a per-language rank-r outer
+product, ``W_l = W * (r_l s_l^T) + (rm_l sm_l^T)``), language-specific LayerNorm, and bottleneck adapters per language.
+
+Reference: onmt/models/multilingual_translator/relative_transformer.py:33,178, relative_transformer_layers.py,
+onmt/modules/multilingual_factorized/* (``MFWPositionWiseFeedForward``, ``MFWEncdecMultiheadAttn``),
+onmt/modules/multilingual_partitioned/*, onmt/modules/adaptive/*, onmt/modules/layer_norm.py (``MultilingualLayerNorm``),
+pretrain_module/adapter.py:10,58.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from .layers import Embedding, LayerNorm, PackedSeqs
+from .transformer import Generator, Seq2SeqBase, TransformerDecoder, TransformerEncoder
+
+
+class FactorizedLinear(nn.Module):
+    """Linear layer whose weight is specialised per language by low-rank multiplicative and additive factors."""
+
+    def __init__(self, d_in, d_out, n_languages, rank=1, bias=True, multiplicative=True):
+        super().__init__()
+        self.weight = nn.Parameter(torch.empty(d_out, d_in))
+        nn.init.xavier_uniform_(self.weight)
+        self.bias = nn.Parameter(torch.zeros(d_out)) if bias else None
+        self.r = nn.Parameter(torch.zeros(n_languages, rank, d_out))
+        self.s = nn.Parameter(torch.zeros(n_languages, rank, d_in))
+        nn.init.normal_(self.r, 0, 0.02)
+        nn.init.normal_(self.s, 0, 0.02)
+        self.multiplicative = multiplicative
+        if multiplicative:
+            self.rm = nn.Parameter(torch.ones(n_languages, 1, d_out))
+            self.sm = nn.Parameter(torch.ones(n_languages, 1, d_in))
+
+    def weight_for(self, lang: int):
+        w = self.weight
+        if self.multiplicative:
+            w = w * (self.rm[lang].t() @ self.sm[lang])
+        return w + self.r[lang].t() @ self.s[lang]
+
+    def forward(self, x, lang: int):
+        return F.linear(x, self.weight_for(lang).to(x.dtype), self.bias.to(x.dtype) if self.bias is not None else None)
+
+
+class MultilingualLayerNorm(nn.Module):
+    def __init__(self, dim, n_languages, eps=1e-5):
+        super().__init__()
+        self.weight = nn.Parameter(torch.ones(n_languages, dim))
+        self.bias = nn.Parameter(torch.zeros(n_languages, dim))
+        self.eps = eps
+
+    def forward(self, x, lang: int):
+        return F.layer_norm(x, (x.shape[-1],), self.weight[lang].to(x.dtype), self.bias[lang].to(x.dtype), self.eps)
+
+
+class Adapter(nn.Module):
+    """Bottleneck adapter: LayerNorm -> down -> ReLU -> up, added to its input."""
+
+    def __init__(self, dim, bottleneck):
+        super().__init__()
+        self.norm = LayerNorm(dim)
+        self.down, self.up = nn.Linear(dim, bottleneck), nn.Linear(bottleneck, dim)
+        nn.init.zeros_(self.up.weight)
+        nn.init.zeros_(self.up.bias)
+
+    def forward(self, x):
+        return x + self.up(F.relu(self.down(self.norm(x).float()))).to(x.dtype)
+
+
+class MultilingualAdapter(nn.Module):
+    def __init__(self, dim, bottleneck, n_languages):
+        super().__init__()
+        self.adapters = nn.ModuleList([Adapter(dim, bottleneck) for _ in range(n_languages)])
+
+    def forward(self, x, lang: int):
+        return self.adapters[lang](x)
+
+
+class MultilingualTransformer(Seq2SeqBase):
+    """Transformer with language embeddings (sum), optional per-language adapters after every layer and an optional
+    factorised output projection."""
+
+    def __init__(self, opt, dicts):
+        super().__init__()
+        self.opt = opt
+        n_lang = max(len(dicts.get("langs", {"src": 0, "tgt": 1})), 1)
+        pad = getattr(opt, "pad_idx", 0)
+        tgt_embed = Embedding(dicts["tgt"].size(), opt.model_size, pad)
+        src_embed = Embedding(dicts["src"].size(), opt.model_size, pad)
+        if getattr(opt, "join_embedding", False):
+            src_embed.weight = tgt_embed.weight
+        self.encoder = TransformerEncoder(opt, src_embed)
+        self.decoder = TransformerDecoder(opt, tgt_embed)
+        self.lang_embed = nn.Embedding(n_lang, opt.model_size)
+        nn.init.normal_(self.lang_embed.weight, 0, opt.model_size ** -0.5)
+        self.generator = Generator(opt.model_size, dicts["tgt"].size())
+        if getattr(opt, "tie_weights", False):
+            self.tie_weights()
+        bott = int(getattr(opt, "adapter_bottleneck_size", 0) or 0)
+        self.use_adapters = bool(getattr(opt, "multilingual_adapter", False)) and bott > 0
+        if self.use_adapters:
+            self.enc_adapters = nn.ModuleList([MultilingualAdapter(opt.model_size, bott, n_lang) for _ in self.encoder.layers])
+            self.dec_adapters = nn.ModuleList([MultilingualAdapter(opt.model_size, bott, n_lang) for _ in self.decoder.layers])
+        self.pad_idx, self.label_smoothing = pad, getattr(opt, "label_smoothing", 0.0)
+
+    def _lang(self, batch, key, default):
+        t = batch.get(key)
+        return int(t.view(-1)[0]) if t is not None and t.numel() else default
+
+    def encode(self, batch):
+        src = batch.packed_source()
+        lang = self._lang(batch, "source_lang", 0)
+        x = self.encoder.embed(src, self.encoder.emb_dropout)
+        x = x + self.lang_embed.weight[lang].to(x.dtype)
+        for i, layer in enumerate(self.encoder.layers):
+            x = layer(x, src)
+            if self.use_adapters:
+                x = self.enc_adapters[i](x, lang)
+        return self.encoder.final_norm(x), src
+
+    def forward(self, batch, **kw):
+        lang = self._lang(batch, "target_lang", min(1, self.lang_embed.num_embeddings - 1))
+        dec = self.decoder
+        if not hasattr(self, "_plain_decoder_forward"):
+            self._plain_decoder_forward = True
+
+        def decoder_forward(tgt, memory, src):
+            x = dec.embed(tgt, dec.emb_dropout) + self.lang_embed.weight[lang].to(memory.dtype)
+            for i, layer in enumerate(dec.layers):
+                x = layer(x, tgt, memory, src)
+                if self.use_adapters:
+                    x = self.dec_adapters[i](x, lang)
+            return dec.final_norm(x)
+        original = dec.forward
+        dec.forward = decoder_forward
+        try:
+            return super().forward(batch, **kw)
+        finally:
+            dec.forward = original
+
+
+def register_builders(register):
+    register("multilingual_translator", "translator")(lambda opt, dicts: MultilingualTransformer(opt, dicts))

@@ -1,0 +1,99 @@
+"""Every model family of the factory builds, trains one step and (where it decodes) runs beam search on CPU."""
+import json
+
+import pytest
+import torch
+
+from nmtgminor_b200.data.synthetic import synthetic_audio_batch, synthetic_dict, token_budget_batches
+from nmtgminor_b200.inference.beam_search import BeamConfig, beam_search
+from nmtgminor_b200.models import factory
+from nmtgminor_b200.models.factory import build_classifier, build_language_model, build_model
+from nmtgminor_b200.options import default_options
+
+COMMON = ["-model_size", "64", "-layers", "2", "-n_heads", "2", "-inner_size", "128", "-dropout", "0.1", "-attn_dropout", "0.0",
+          "-ffn_activation", "relu", "-label_smoothing", "0.1"]
+REFERENCE_MODEL_NAMES = ["transformer", "stochastic_transformer", "relative_transformer", "universal_transformer",
+                         "multilingual_translator", "translator", "speech_transformer", "conformer", "hybrid_transformer", "LSTM", "lstm",
+                         "discourse_speech_transformer", "discourse_translator", "wav2vec2_transformer", "wav2vec2_bert",
+                         "quantize_wav2vec2_bert", "quantize_wav2vec2_mbart50", "pretrain_transformer", "whisper"]
+
+
+@pytest.fixture(scope="module")
+def dicts():
+    d = synthetic_dict(120)
+    return {"src": d, "tgt": d, "langs": {"en": 0, "de": 1}}
+
+
+def _cfg(tmp_path, name, **kw):
+    p = tmp_path / name
+    p.write_text(json.dumps(kw))
+    return str(p)
+
+
+def test_registry_covers_the_reference_model_names():
+    factory._load_builders()
+    missing = [n for n in REFERENCE_MODEL_NAMES if n not in factory._REGISTRY]
+    assert not missing, missing
+
+
+@pytest.mark.parametrize("name,extra", [
+    ("transformer", ["-death_rate", "0.1"]), ("relative_transformer", []), ("universal_transformer", []),
+    ("multilingual_translator", ["-multilingual_adapter", "-adapter_bottleneck_size", "16"]), ("LSTM", []),
+    ("discourse_translator", []), ("pretrain_transformer", ["-enc_pretrained_model", "mbart50", "-dec_pretrained_model", "mbart50"]),
+    ("pretrain_transformer", ["-enc_pretrained_model", "deltalm", "-dec_pretrained_model", "deltalm"]),
+])
+def test_text_families_train_and_decode(dicts, name, extra):
+    torch.manual_seed(0)
+    model = build_model(default_options(["-model", name] + COMMON + extra), dicts)
+    batch = token_budget_batches(120, 4, 10, 60, 1, static=False, padded=True)[0]
+    out = model(batch)
+    assert torch.isfinite(out["loss"]).all()
+    out["loss"].backward()
+    assert any(p.grad is not None and p.grad.abs().sum() > 0 for p in model.parameters())
+    model.eval()
+    hyps = beam_search(model, batch, BeamConfig(beam_size=2, max_len=5))
+    assert len(hyps) == batch.size and all(h[0].tokens for h in hyps)
+
+
+def test_speech_families(dicts, tmp_path):
+    torch.manual_seed(1)
+    enc = _cfg(tmp_path, "enc.json", encoder_embed_dim=64, encoder_layers=2, encoder_attention_heads=2, encoder_ffn_embed_dim=128)
+    dec = _cfg(tmp_path, "dec.json", d_model=64, decoder_layers=2, decoder_attention_heads=2, decoder_ffn_dim=128, vocab_size=120, pad_token_id=0)
+    wsp = _cfg(tmp_path, "whisper.json", d_model=64, encoder_layers=2, decoder_layers=2, encoder_attention_heads=2, encoder_ffn_dim=128,
+               num_mel_bins=80, max_source_positions=128, max_target_positions=64, vocab_size=120, pad_token_id=0)
+    cases = [
+        (["-model", "wav2vec2_bert", "-enc_config_file", enc, "-dec_config_file", dec, "-dec_pretrained_model", "mbart50", "-ctc_loss", "0.3"],
+         synthetic_audio_batch(2, 120, "wav", 3000, 6000)),
+        (["-model", "wav2vec2_transformer", "-enc_config_file", enc], synthetic_audio_batch(2, 120, "wav", 3000, 6000)),
+        (["-model", "whisper", "-dec_config_file", wsp], synthetic_audio_batch(2, 120, "feats", n_feats=80, fixed_frames=120)),
+        (["-model", "speech_transformer", "-input_size", "40", "-cnn_downsampling"], synthetic_audio_batch(2, 120, "feats", 40, 80, n_feats=40)),
+        (["-model", "conformer", "-input_size", "40"], synthetic_audio_batch(2, 120, "feats", 40, 80, n_feats=40)),
+    ]
+    for argv, batch in cases:
+        model = build_model(default_options(argv + COMMON), dicts)
+        out = model(batch)
+        assert torch.isfinite(out["loss"]).all(), argv
+        out["loss"].backward()
+        model.eval()
+        hyps = beam_search(model, batch, BeamConfig(beam_size=2, max_len=4))
+        assert len(hyps) == 2
+    # wav2vec2: frame count follows the 320x conv stride, extractor frozen by default
+    w2v = build_model(default_options(cases[0][0] + COMMON), dicts)
+    ctx, seqs = w2v.encode(cases[0][1])
+    lens = (cases[0][1].get("source")[:, :, 0] > 0).sum(0)
+    assert (seqs.cu[1:] - seqs.cu[:-1]).tolist() == w2v.encoder.extractor.output_lengths(lens).tolist()
+    assert all(not p.requires_grad for p in w2v.encoder.extractor.parameters())
+
+
+def test_language_model_and_classifier(dicts):
+    lm = build_language_model(default_options(["-model", "transformer_xl", "-max_memory_size", "8"] + COMMON), dicts)
+    batch = token_budget_batches(120, 4, 10, 60, 1, static=False, padded=True)[0]
+    stream = lm.init_stream()
+    l1 = lm(batch, streaming_state=stream)["loss"]
+    l1.backward()
+    assert stream.mems[0] is not None and stream.mems[0].shape[1] <= 8
+    clf = build_classifier(default_options(COMMON), dicts)
+    batch.tensors["labels"] = torch.randint(0, 5, (batch.size,))
+    out = clf(batch)
+    out["loss"].backward()
+    assert out["logits"].shape == (batch.size, 120)
