@@ -65,6 +65,14 @@ class _EnsembleState:
     def __init__(self, states):
         self.states = states
 
+    @property
+    def context(self):
+        return self.states[0].context
+
+    @property
+    def src_pad_mask(self):
+        return self.states[0].src_pad_mask
+
     def reorder(self, index):
         for s in self.states:
             s.reorder(index)
