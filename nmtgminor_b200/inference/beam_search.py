@@ -42,6 +42,7 @@ class BeamConfig:
     sampling: bool = False
     sampling_temperature: float = 1.0
     vocab_mask: Optional[torch.Tensor] = None   # bool [V], True = allowed
+    fused_step: bool = True     # CUDA: fused log-softmax + top-k kernel when no constraint needs full log-probabilities
 
 
 @dataclass
@@ -67,6 +68,45 @@ def _block_ngrams(tokens, step, lprobs, n, pad):
     rows = torch.arange(R, device=tokens.device)[:, None].expand_as(banned)
     lprobs[rows[match], banned[match]] = float("-inf")
     return lprobs
+
+
+def _masked_topk(lprobs, cfg, step, max_rows, prefix_tokens, banned_first, tokens, scores, B, K):
+    """Reference step: apply the length / prefix / n-gram constraints to ``lprobs`` [R, V] and pick 2K candidates."""
+    device = lprobs.device
+    R = B * K
+    V = lprobs.shape[1]
+    lprobs[:, cfg.pad] = float("-inf")
+    if cfg.vocab_mask is not None:
+        lprobs.masked_fill_(~cfg.vocab_mask[None, :].to(device), float("-inf"))
+    if step < cfg.min_len:
+        lprobs[:, cfg.eos] = float("-inf")
+    force_eos = (step >= max_rows)                             # at the length limit only EOS may follow
+    if force_eos.any():
+        keep = lprobs[:, cfg.eos].clone()
+        lprobs[force_eos] = float("-inf")
+        lprobs[force_eos, cfg.eos] = keep[force_eos]
+    if prefix_tokens is not None and step < prefix_tokens.shape[1]:
+        want = prefix_tokens[:, step].repeat_interleave(K)
+        forced = want != cfg.pad
+        if forced.any():
+            keep = lprobs.gather(1, want[:, None]).squeeze(1)
+            lprobs[forced] = float("-inf")
+            lprobs[forced, want[forced]] = keep[forced]
+    if banned_first is not None and step == 0:
+        lprobs[:, banned_first] = float("-inf")
+    lprobs = _block_ngrams(tokens, step, lprobs, cfg.no_repeat_ngram_size, cfg.pad)
+
+    cand = scores[:, :, None] + lprobs.view(B, K, V)            # [B, K, V]
+    flat = cand.view(B, K * V)
+    if cfg.sampling and step > 0:
+        probs = torch.softmax(lprobs.view(B, K, V) / cfg.sampling_temperature, -1)
+        samp = torch.multinomial(probs.view(R, V), 2).view(B, K * 2)
+        beam_of = torch.arange(K, device=device).repeat_interleave(2)[None, :].expand(B, -1)
+        top_idx = beam_of * V + samp
+        top_scores = flat.gather(1, top_idx)
+    else:
+        top_scores, top_idx = flat.topk(min(2 * K, K * V), dim=1)
+    return top_scores, top_idx, V
 
 
 @torch.no_grad()
@@ -99,41 +139,31 @@ def beam_search(model, batch, cfg: BeamConfig, prefix_tokens: Optional[torch.Ten
     base = (torch.arange(B, device=device) * K)[:, None]
     max_rows = max_len_per.repeat_interleave(K)
 
-    for step in range(T + 1):
-        out = model.step(tokens[:, :step + 1], state)
-        lprobs = out["log_prob"].float()                           # [R, V]
-        V = lprobs.shape[1]
-        lprobs[:, cfg.pad] = float("-inf")
-        if cfg.vocab_mask is not None:
-            lprobs.masked_fill_(~cfg.vocab_mask[None, :].to(device), float("-inf"))
-        if step < cfg.min_len:
-            lprobs[:, cfg.eos] = float("-inf")
-        force_eos = (step >= max_rows)                             # at the length limit only EOS may follow
-        if force_eos.any():
-            keep = lprobs[:, cfg.eos].clone()
-            lprobs[force_eos] = float("-inf")
-            lprobs[force_eos, cfg.eos] = keep[force_eos]
-        if prefix_tokens is not None and step < prefix_tokens.shape[1]:
-            want = prefix_tokens[:, step].repeat_interleave(K)
-            forced = want != cfg.pad
-            if forced.any():
-                keep = lprobs.gather(1, want[:, None]).squeeze(1)
-                lprobs[forced] = float("-inf")
-                lprobs[forced, want[forced]] = keep[forced]
-        if banned_first is not None and step == 0:
-            lprobs[:, banned_first] = float("-inf")
-        lprobs = _block_ngrams(tokens, step, lprobs, cfg.no_repeat_ngram_size, cfg.pad)
+    if hasattr(state, "set_cache_capacity") and device.type == "cuda":
+        state.set_cache_capacity(T + 2)
+    # fused step: log-softmax, masks and the per-sentence top-2K in two kernels, no [R, V] log-probabilities
+    fused = (device.type == "cuda" and cfg.fused_step and getattr(model, "supports_logits_step", False)
+             and not cfg.sampling and cfg.no_repeat_ngram_size <= 0 and cfg.vocab_mask is None and 2 * K <= 64)
 
-        cand = scores[:, :, None] + lprobs.view(B, K, V)            # [B, K, V]
-        flat = cand.view(B, K * V)
-        if cfg.sampling and step > 0:
-            probs = torch.softmax(lprobs.view(B, K, V) / cfg.sampling_temperature, -1)
-            samp = torch.multinomial(probs.view(R, V), 2).view(B, K * 2)
-            beam_of = torch.arange(K, device=device).repeat_interleave(2)[None, :].expand(B, -1)
-            top_idx = beam_of * V + samp
-            top_scores = flat.gather(1, top_idx)
+    for step in range(T + 1):
+        use_fused = (fused and not (prefix_tokens is not None and step < prefix_tokens.shape[1])
+                     and not (banned_first is not None and step == 0))
+        if use_fused:
+            from .. import ops
+            logits = model.step(tokens[:, :step + 1], state, logits_only=True)["logits"]
+            V = logits.shape[1]
+            if logits.dtype not in (torch.float32, torch.bfloat16):
+                logits = logits.float()
+            top_scores, top_idx, _ = ops.ext().beam_topk(logits.contiguous(), scores.reshape(-1).contiguous(),
+                                                         (step >= max_rows).to(torch.uint8), K, cfg.pad, cfg.eos,
+                                                         step < cfg.min_len)
+            lprobs = None
         else:
-            top_scores, top_idx = flat.topk(min(2 * K, K * V), dim=1)
+            top_scores = None
+            out = model.step(tokens[:, :step + 1], state)
+            lprobs = out["log_prob"].float()                       # [R, V]
+        if lprobs is not None:
+            top_scores, top_idx, V = _masked_topk(lprobs, cfg, step, max_rows, prefix_tokens, banned_first, tokens, scores, B, K)
         cand_beam = top_idx // V
         cand_tok = top_idx % V
         C = top_scores.shape[1]
@@ -151,7 +181,7 @@ def beam_search(model, batch, cfg: BeamConfig, prefix_tokens: Optional[torch.Ten
             new_tok = tokens[src_rows].view(B, C, T + 2).clone()
             new_tok[:, :, step + 1] = cfg.eos
             new_pos = pos_scores[src_rows].view(B, C, T + 2).clone()
-            new_pos[:, :, step + 1] = lprobs.view(B, K, V)[torch.arange(B, device=device)[:, None], cand_beam, cand_tok]
+            new_pos[:, :, step + 1] = top_scores - scores.gather(1, cand_beam)
             all_scores = torch.cat([fin_scores, new_scores], 1)
             order = all_scores.argsort(dim=1, descending=True, stable=True)[:, :K]
             gather3 = order[:, :, None].expand(-1, -1, T + 2)

@@ -172,6 +172,16 @@ class SelfAttention(nn.Module):
         qkv = self.qkv(x)
         q, k, v = qkv[:, :H], qkv[:, H:2 * H], qkv[:, 2 * H:]
         B = x.shape[0]
+        if _fused_decode(qkv, H, h) and cache.get("cap"):
+            # preallocated [rows, cap, H] caches: append in place, attend with the single-query kernel
+            pos = cache.get("pos", 0)
+            if "k" not in cache:
+                for name in ("k", "v", "k_spare", "v_spare"):
+                    cache[name] = torch.empty(B, cache["cap"], H, dtype=qkv.dtype, device=qkv.device)
+            ops.ext().cache_append(k, v, cache["k"], cache["v"], pos)
+            ctx = ops.ext().decode_attn(q, cache["k"], cache["v"], None, pos + 1, h, (H // h) ** -0.5)
+            cache["pos"] = pos + 1
+            return self.out(ctx)
         if "k" not in cache:
             cache["k"], cache["v"] = k.view(B, 1, H), v.view(B, 1, H)
         else:
@@ -179,6 +189,10 @@ class SelfAttention(nn.Module):
             cache["v"] = torch.cat([cache["v"], v.view(B, 1, H)], 1)
         ctx = _cached_attention(q, cache["k"], cache["v"], h, None)
         return self.out(ctx)
+
+
+def _fused_decode(t, dim, heads) -> bool:
+    return t.is_cuda and t.dtype == torch.bfloat16 and dim // heads == 64
 
 
 class CrossAttention(nn.Module):
@@ -204,7 +218,15 @@ class CrossAttention(nn.Module):
 
     def step(self, x, cache: dict, mem_mask):
         q = self.q(x)
-        ctx = _cached_attention(q, cache["c_k"], cache["c_v"], self.heads, mem_mask)
+        ck, cv = cache["c_k"], cache["c_v"]
+        if "c_len" in cache and _fused_decode(q, self.dim, self.heads):
+            # one cache row per sentence, shared by its hypotheses
+            ctx = ops.ext().decode_attn(q, ck, cv, cache["c_len"], ck.shape[1], self.heads, (self.dim // self.heads) ** -0.5)
+            return self.out(ctx)
+        if ck.shape[0] != q.shape[0]:
+            rep = q.shape[0] // ck.shape[0]
+            ck, cv = ck.repeat_interleave(rep, 0), cv.repeat_interleave(rep, 0)
+        ctx = _cached_attention(q, ck, cv, self.heads, mem_mask)
         return self.out(ctx)
 
 

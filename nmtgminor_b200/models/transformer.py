@@ -108,12 +108,30 @@ class DecodingState:
         self.buffers = [dict() for _ in range(n_layers)]
         self.position = 0
 
+    def set_cache_capacity(self, cap: int):
+        """Ask the self-attention layers for preallocated ``[rows, cap, H]`` key/value caches (CUDA bf16 path)."""
+        for buf in self.buffers:
+            buf["cap"] = int(cap)
+
     def reorder(self, index):
+        rows = index.numel()
         self.context = self.context.index_select(0, index)
         self.src_pad_mask = self.src_pad_mask.index_select(0, index)
         for buf in self.buffers:
+            if "k_spare" in buf:
+                # preallocated caches: copy only the filled prefix of every row into the spare buffers and swap
+                filled = buf.get("pos", 0) * buf["k"].shape[2]
+                ops.ext().gather_rows(buf["k"], buf["k_spare"], index, filled)
+                ops.ext().gather_rows(buf["v"], buf["v_spare"], index, filled)
+                buf["k"], buf["k_spare"] = buf["k_spare"], buf["k"]
+                buf["v"], buf["v_spare"] = buf["v_spare"], buf["v"]
             for k in list(buf.keys()):
-                buf[k] = buf[k].index_select(0, index)
+                val = buf[k]
+                if k in ("k", "v", "k_spare", "v_spare") and "k_spare" in buf:
+                    continue
+                # per-sentence entries (encoder-decoder caches shared by the hypotheses) keep their order
+                if torch.is_tensor(val) and val.dim() > 0 and val.shape[0] == rows:
+                    buf[k] = val.index_select(0, index)
 
     _reorder_incremental_state = reorder  # reference spelling
 
@@ -181,19 +199,28 @@ class Seq2SeqBase(nn.Module):
         lengths = (src.cu[1:] - src.cu[:-1]).to(torch.int64)
         pad_mask = torch.arange(ctx_padded.shape[1], device=ctx_padded.device)[None, :] >= lengths[:, None]
         state = DecodingState(ctx_padded, pad_mask, len(self.decoder.layers), beam_size)
+        shared = ctx_padded.is_cuda and ctx_padded.dtype == torch.bfloat16 and beam_size > 1
         for i, layer in enumerate(self.decoder.layers):
             if not getattr(layer, "ignore_source", False):
-                ck, cv = layer.cross_attn.precompute(state.context)
+                # on the GPU the projected encoder states are kept once per sentence, not once per hypothesis
+                ck, cv = layer.cross_attn.precompute(ctx_padded if shared else state.context)
                 state.buffers[i]["c_k"], state.buffers[i]["c_v"] = ck, cv
+                if ctx_padded.is_cuda and ctx_padded.dtype == torch.bfloat16:
+                    state.buffers[i]["c_len"] = lengths.to(torch.int32).contiguous()
         return state
 
+    supports_logits_step = True
+
     @torch.no_grad()
-    def step(self, input_t, state: DecodingState) -> Dict:
-        """input_t ``[B*beam, t]`` (all symbols so far) -> ``log_prob [B*beam, V]`` fp32 for the next symbol."""
+    def step(self, input_t, state: DecodingState, logits_only: bool = False) -> Dict:
+        """input_t ``[B*beam, t]`` (all symbols so far) -> ``log_prob [B*beam, V]`` fp32 for the next symbol
+        (``logits_only``: raw ``logits`` instead, for the fused log-softmax + top-k beam kernel)."""
         tokens = input_t[:, -1].contiguous()
         hidden = self.decoder.step(tokens, input_t.shape[1] - 1, state)
         logits = self.generator(hidden)
         state.position += 1
+        if logits_only:
+            return {"logits": logits, "hidden": hidden, "coverage": None}
         return {"log_prob": torch.log_softmax(logits.float(), dim=-1), "hidden": hidden, "coverage": None}
 
     def renew_buffer(self, new_len: int):

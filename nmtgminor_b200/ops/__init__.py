@@ -164,6 +164,15 @@ def gemm(a, b, out, *, a_mn_major=False, b_mn_major=False, bias=None, residual=N
     return out
 
 
+def empty_rows(rows: int, cols: int, device, dtype=torch.bfloat16):
+    """[rows, cols] tensor whose row stride is rounded up to 16 bytes (kernels need aligned rows; e.g. vocabulary
+    sizes that are not multiples of 8).  The result is a column slice of a wider buffer when padding is needed."""
+    mult = 16 // torch.empty((), dtype=dtype).element_size()
+    padded = (cols + mult - 1) // mult * mult
+    t = torch.empty((rows, padded), dtype=dtype, device=device)
+    return t if padded == cols else t[:, :cols]
+
+
 def _keep_scale(p: float) -> float:
     """Dropout is byte-granular on the device: keep probability (256 - round(256 p)) / 256."""
     if p <= 0.0:
@@ -177,8 +186,8 @@ class _LinearFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w, bias, residual, gw, gb, act, dropout_p, seed, stream_id, need_input_grad):
         M, N = x.shape[0], w.shape[0]
-        y = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
-        z = torch.empty_like(y) if act != 0 else None  # pre-activation, needed by act'
+        y = empty_rows(M, N, x.device)
+        z = empty_rows(M, N, x.device) if act != 0 else None  # pre-activation, needed by act'
         gemm(x, w, y, bias=bias, residual=residual, preact=z, act=act, dropout_p=dropout_p, seed=seed,
              stream_id=stream_id)
         ctx.save_for_backward(x, w, z)
@@ -190,7 +199,12 @@ class _LinearFn(torch.autograd.Function):
     def backward(ctx, dy):
         x, w, z = ctx.saved_tensors
         act, p, seed, sid, has_res, has_bias, need_dx = ctx.cfg
-        dy = dy.contiguous()
+        if dy.shape[1] % 8:
+            padded = empty_rows(dy.shape[0], dy.shape[1], dy.device)
+            padded.copy_(dy)
+            dy = padded
+        else:
+            dy = dy.contiguous()
         dz = ext().dropout_add(dy, None, p, seed, sid) if p > 0.0 else dy  # regenerates the forward mask
         if act != 0:
             dz = _act_backward(dz, z, act)
@@ -230,7 +244,7 @@ def linear(x, weight, bias=None, act="none", dropout_p=0.0, residual=None, train
         need_dx = x.requires_grad
         xin = (x if x.dtype == torch.bfloat16 else x.to(torch.bfloat16)).contiguous()
         if not torch.is_grad_enabled() or not (need_dx or gw is not None):
-            y = torch.empty((x.shape[0], weight.shape[0]), dtype=torch.bfloat16, device=x.device)
+            y = empty_rows(x.shape[0], weight.shape[0], x.device)
             return gemm(xin, weight.work, y, bias=b, residual=residual, act=act_id, dropout_p=p, seed=_Rng.seed,
                         stream_id=sid)
         return _LinearFn.apply(xin, weight.work, b, residual, gw, gb, act_id, p, _Rng.seed, sid, need_dx)
@@ -542,7 +556,7 @@ def cross_entropy(logits, labels, smoothing=0.0, pad_idx=0):
 
     On the fused path ``logits`` (bf16, 2-D) is consumed: its storage is overwritten with the gradient.
     """
-    if logits.is_cuda and logits.dtype == torch.bfloat16 and extension_available() and logits.shape[1] % 8 == 0:
+    if logits.is_cuda and logits.dtype == torch.bfloat16 and extension_available() and logits.stride(0) % 8 == 0 and logits.stride(1) == 1:
         labels = labels.contiguous()
         if torch.is_grad_enabled() and logits.requires_grad:
             return _XentFn.apply(logits, labels, float(smoothing), int(pad_idx))
@@ -564,7 +578,7 @@ class _GeneratorXentFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, h, w, bias, gw, gb, labels, smoothing, pad_idx, grad_scale):
         rows, V = h.shape[0], w.shape[0]
-        logits = torch.empty((rows, V), dtype=torch.bfloat16, device=h.device)
+        logits = empty_rows(rows, V, h.device)
         gemm(h, w, logits, bias=bias)
         loss_sum = torch.zeros(1, dtype=torch.float32, device=h.device)
         correct = torch.zeros(1, dtype=torch.float32, device=h.device)
@@ -601,7 +615,7 @@ def generator_cross_entropy(h, weight, bias, labels, smoothing=0.0, pad_idx=0, g
         if torch.is_grad_enabled():
             return _GeneratorXentFn.apply(hin, weight.work, b, gw, gb, labels.contiguous(), float(smoothing), int(pad_idx),
                                           grad_scale)
-        logits = torch.empty((h.shape[0], weight.shape[0]), dtype=torch.bfloat16, device=h.device)
+        logits = empty_rows(h.shape[0], weight.shape[0], h.device)
         gemm(hin, weight.work, logits, bias=b)
         return cross_entropy(logits, labels, smoothing, pad_idx)
     logits = ref.linear(h, weight, bias, 0, 0.0, None)

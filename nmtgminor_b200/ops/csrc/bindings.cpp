@@ -358,7 +358,10 @@ void clear_status(int64_t device) { status_tensor(static_cast<int>(device)).zero
 
 }  // namespace
 
+void bind_sequence_ops(pybind11::module& m);   // bindings_seq.cpp
+
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  bind_sequence_ops(m);
   m.def("gemm", &gemm);
   m.def("set_gemm_variant", [](int64_t v) { nmtg_set_gemm_variant(static_cast<int>(v)); });
   m.def("layernorm_fwd", &layernorm_fwd);
