@@ -154,7 +154,7 @@ def beam_search(model, batch, cfg: BeamConfig, prefix_tokens: Optional[torch.Ten
             V = logits.shape[1]
             if logits.dtype not in (torch.float32, torch.bfloat16):
                 logits = logits.float()
-            top_scores, top_idx, _ = ops.ext().beam_topk(logits.contiguous(), scores.reshape(-1).contiguous(),
+            top_scores, top_idx, _ = ops.ext().beam_topk(logits, scores.reshape(-1).contiguous(),
                                                          (step >= max_rows).to(torch.uint8), K, cfg.pad, cfg.eos,
                                                          step < cfg.min_len)
             lprobs = None

@@ -163,7 +163,7 @@ Tensor softmax_dropout_bwd(const Tensor& dyd, const Tensor& y, double scale, dou
 
 std::vector<Tensor> beam_topk(const Tensor& logits, const Tensor& scores, const OptTensor& force_eos, int64_t K, int64_t pad,
                               int64_t eos, bool ban_eos) {
-  TORCH_CHECK(logits.is_cuda() && logits.is_contiguous() && logits.dim() == 2);
+  TORCH_CHECK(logits.is_cuda() && logits.dim() == 2 && logits.stride(1) == 1);
   need(scores, at::kFloat, "scores");
   c10::cuda::CUDAGuard guard(logits.device());
   const int R = logits.size(0), V = logits.size(1);
@@ -178,7 +178,7 @@ std::vector<Tensor> beam_topk(const Tensor& logits, const Tensor& scores, const 
   Tensor lse = torch::empty({R}, fo), cv = torch::empty({R, 2 * K}, fo);
   Tensor ci = torch::empty({R, 2 * K}, fo.dtype(torch::kInt));
   Tensor os = torch::empty({B, 2 * K}, fo), oi = torch::empty({B, 2 * K}, fo.dtype(torch::kLong));
-  ck(nmtg_beam_topk(logits.data_ptr(), dtype_code(logits), scores.data_ptr<float>(), fe, lse.data_ptr<float>(),
+  ck(nmtg_beam_topk(logits.data_ptr(), logits.stride(0), dtype_code(logits), scores.data_ptr<float>(), fe, lse.data_ptr<float>(),
                     cv.data_ptr<float>(), ci.data_ptr<int>(), os.data_ptr<float>(), reinterpret_cast<long*>(oi.data_ptr<int64_t>()),
                     B, static_cast<int>(K), V, static_cast<int>(pad), static_cast<int>(eos), ban_eos, cur_stream()));
   return {os, oi, lse};

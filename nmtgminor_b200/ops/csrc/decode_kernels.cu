@@ -63,15 +63,31 @@ __device__ __forceinline__ float block_reduce(float v, float* red, bool is_max) 
 }
 
 // Stage 1: one block per hypothesis row.  cand[r, 0:2K] = best 2K of scores[r] + masked log-softmax(logits[r]).
-template <typename T>
-__global__ void beam_row_topk_kernel(const T* __restrict__ logits, const float* __restrict__ scores,
+// kStage: the row is first copied into shared memory, so the 2K + 2 passes over it never leave the SM.
+template <typename T, bool kStage>
+__global__ void beam_row_topk_kernel(const T* __restrict__ logits, long ld, const float* __restrict__ scores,
                                      const uint8_t* __restrict__ force_eos, float* __restrict__ row_lse,
                                      float* __restrict__ cand_val, int* __restrict__ cand_idx, int K2, int V, int pad, int eos,
                                      int ban_eos) {
+  extern __shared__ __align__(16) uint8_t stage_raw[];
   __shared__ float redf[32];
   __shared__ Best redb[32];
   const int r = blockIdx.x;
-  const T* x = logits + static_cast<long>(r) * V;
+  const T* x = logits + static_cast<long>(r) * ld;
+  if (kStage) {
+    T* st = reinterpret_cast<T*>(stage_raw);
+    constexpr int kPer = 16 / sizeof(T);
+    if ((ld % kPer) == 0 && (reinterpret_cast<uintptr_t>(logits) & 15) == 0) {
+      const int nvec = V / kPer;
+      for (int i = threadIdx.x; i < nvec; i += blockDim.x)
+        reinterpret_cast<uint4*>(st)[i] = reinterpret_cast<const uint4*>(x)[i];
+      for (int v = nvec * kPer + threadIdx.x; v < V; v += blockDim.x) st[v] = x[v];
+    } else {
+      for (int v = threadIdx.x; v < V; v += blockDim.x) st[v] = x[v];
+    }
+    __syncthreads();
+    x = st;
+  }
   float mx = -INFINITY;
   for (int v = threadIdx.x; v < V; v += blockDim.x) mx = fmaxf(mx, ldv(x + v));
   mx = block_reduce(mx, redf, true);
@@ -82,25 +98,99 @@ __global__ void beam_row_topk_kernel(const T* __restrict__ logits, const float* 
   if (threadIdx.x == 0) row_lse[r] = lse;
   const float base = scores[r] - lse;
   const bool only_eos = force_eos && force_eos[r];
-  Best prev{INFINITY, -1};
-  for (int j = 0; j < K2; ++j) {
-    Best mine{-INFINITY, 0x7fffffff};
-    for (int v = threadIdx.x; v < V; v += blockDim.x) {
-      float val = ldv(x + v) + base;
-      if (v == pad || (only_eos && v != eos) || (ban_eos && !only_eos && v == eos)) val = -INFINITY;
-      if (val != val) val = -INFINITY;
-      if (after(val, v, prev)) {
-        Best c{val, v};
-        if (better(c, mine)) mine = c;
+  float* cv = cand_val + static_cast<long>(r) * K2;
+  int* ci = cand_idx + static_cast<long>(r) * K2;
+  if (only_eos || base == -INFINITY) {
+    // one live candidate (or none): no search needed
+    for (int j = threadIdx.x; j < K2; j += blockDim.x) {
+      const bool live = only_eos && j == 0 && base != -INFINITY;
+      cv[j] = live ? ldv(x + eos) + base : -INFINITY;
+      ci[j] = live ? eos : (j == eos ? (eos + K2) % V : j);
+    }
+    return;
+  }
+  if constexpr (kStage) {
+    // The masks are written into the staged copy, so the selection passes compare raw values only.
+    T* st = reinterpret_cast<T*>(stage_raw);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      if (pad >= 0 && pad < V) st[pad] = static_cast<T>(-INFINITY);
+      if (ban_eos && eos >= 0 && eos < V) st[eos] = static_cast<T>(-INFINITY);
+    }
+    __syncthreads();
+    constexpr int kPer = 16 / sizeof(T);
+    const int nvec = V / kPer;
+    Best prev{INFINITY, -1};
+    for (int j = 0; j < K2; ++j) {
+      Best mine{-INFINITY, 0x7fffffff};
+      for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+        const uint4 u = reinterpret_cast<const uint4*>(st)[i];
+        const T* e = reinterpret_cast<const T*>(&u);
+#pragma unroll
+        for (int k = 0; k < kPer; ++k) {
+          const float f = static_cast<float>(e[k]);
+          if (f > mine.v || (f == mine.v && mine.i == 0x7fffffff)) {
+            const int v = i * kPer + k;
+            if (after(f, v, prev)) { mine.v = f; mine.i = v; }
+          }
+        }
+      }
+      for (int v = nvec * kPer + threadIdx.x; v < V; v += blockDim.x) {
+        const float f = static_cast<float>(st[v]);
+        if ((f > mine.v || (f == mine.v && v < mine.i)) && after(f, v, prev)) { mine.v = f; mine.i = v; }
+      }
+      const Best b = block_best(mine, redb);
+      if (threadIdx.x == 0) {
+        cv[j] = b.v + base;
+        ci[j] = b.i == 0x7fffffff ? 0 : b.i;
+      }
+      prev = b;
+    }
+  } else {
+    Best prev{INFINITY, -1};
+    for (int j = 0; j < K2; ++j) {
+      Best mine{-INFINITY, 0x7fffffff};
+      for (int v = threadIdx.x; v < V; v += blockDim.x) {
+        float val = ldv(x + v);
+        if (v == pad || (ban_eos && v == eos)) val = -INFINITY;
+        if (val != val) val = -INFINITY;
+        if (after(val, v, prev)) {
+          Best c{val, v};
+          if (better(c, mine)) mine = c;
+        }
+      }
+      const Best b = block_best(mine, redb);
+      if (threadIdx.x == 0) {
+        cv[j] = b.v + base;
+        ci[j] = b.i == 0x7fffffff ? 0 : b.i;
+      }
+      prev = b;
+    }
+  }
+}
+
+template <typename T>
+const char* launch_row_topk(const T* logits, long ld, const float* scores, const uint8_t* force_eos, float* row_lse,
+                            float* cand_val, int* cand_idx, int R, int K2, int V, int pad, int eos, int ban_eos,
+                            cudaStream_t stream) {
+  const int threads = V >= 8192 ? 512 : (V >= 1024 ? 256 : 64);
+  const size_t need = static_cast<size_t>(V) * sizeof(T) + 16;
+  if (need <= 200 * 1024) {
+    if (need > 48 * 1024) {
+      static bool configured = false;
+      if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(beam_row_topk_kernel<T, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        if (e != cudaSuccess) return cudaGetErrorString(e);
+        configured = true;
       }
     }
-    const Best b = block_best(mine, redb);
-    if (threadIdx.x == 0) {
-      cand_val[static_cast<long>(r) * K2 + j] = b.v;
-      cand_idx[static_cast<long>(r) * K2 + j] = b.i == 0x7fffffff ? 0 : b.i;
-    }
-    prev = b;
+    beam_row_topk_kernel<T, true><<<R, threads, need, stream>>>(logits, ld, scores, force_eos, row_lse, cand_val, cand_idx, K2, V,
+                                                                 pad, eos, ban_eos);
+  } else {
+    beam_row_topk_kernel<T, false><<<R, threads, 0, stream>>>(logits, ld, scores, force_eos, row_lse, cand_val, cand_idx, K2, V,
+                                                              pad, eos, ban_eos);
   }
+  return nullptr;
 }
 
 // Stage 2: one block per sentence; merge K rows of 2K candidates into the best 2K (sorted, best first).
@@ -247,21 +337,22 @@ using namespace b200;
 
 extern "C" {
 
-const char* nmtg_beam_topk(const void* logits, int dtype, const float* scores, const uint8_t* force_eos, float* row_lse,
-                           float* cand_val, int* cand_idx, float* out_scores, long* out_index, int B, int K, int V,
-                           int pad, int eos, int ban_eos, cudaStream_t stream) {
+const char* nmtg_beam_topk(const void* logits, long ld, int dtype, const float* scores, const uint8_t* force_eos,
+                           float* row_lse, float* cand_val, int* cand_idx, float* out_scores, long* out_index, int B, int K,
+                           int V, int pad, int eos, int ban_eos, cudaStream_t stream) {
   if (B <= 0 || K <= 0 || V <= 0) return nullptr;
   const int K2 = 2 * K;
   if (K2 > V) return "beam_topk: vocabulary smaller than twice the beam";
+  if (ld < V) return "beam_topk: row stride smaller than the vocabulary";
   const int R = B * K;
-  const int threads = V >= 8192 ? 512 : (V >= 1024 ? 256 : 64);
+  const char* err;
   if (dtype == 0)
-    beam_row_topk_kernel<float><<<R, threads, 0, stream>>>(static_cast<const float*>(logits), scores, force_eos, row_lse,
-                                                           cand_val, cand_idx, K2, V, pad, eos, ban_eos);
+    err = launch_row_topk<float>(static_cast<const float*>(logits), ld, scores, force_eos, row_lse, cand_val, cand_idx, R, K2, V,
+                                 pad, eos, ban_eos, stream);
   else
-    beam_row_topk_kernel<__nv_bfloat16><<<R, threads, 0, stream>>>(static_cast<const __nv_bfloat16*>(logits), scores,
-                                                                   force_eos, row_lse, cand_val, cand_idx, K2, V, pad, eos,
-                                                                   ban_eos);
+    err = launch_row_topk<__nv_bfloat16>(static_cast<const __nv_bfloat16*>(logits), ld, scores, force_eos, row_lse, cand_val,
+                                         cand_idx, R, K2, V, pad, eos, ban_eos, stream);
+  if (err) return err;
   beam_merge_kernel<<<B, K * K2 >= 256 ? 256 : 64, 0, stream>>>(cand_val, cand_idx, out_scores, out_index, K, K2, V);
   return launch_err();
 }

@@ -28,7 +28,7 @@ constexpr int kGemmThreads = 32 * (2 + kEpilogueWarps);
 
 template <int BN>
 struct GemmSmem {
-  static constexpr int kStages = (BN == 256) ? 4 : 6;
+  static constexpr int kStages = (BN == 256) ? 4 : (BN == 128 ? 6 : 8);
   static constexpr int kABytes = BM * BK * 2;
   static constexpr int kBBytes = BN * BK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
@@ -348,6 +348,30 @@ const char* nmtg_gemm_bf16(const GemmDesc* d, cudaStream_t stream) {
     while (split > 1 && (split - 1) * ((num_kb + split - 1) / split) >= num_kb) --split;
     return split < 1 ? 1 : split;
   };
+  // ---- skinny problems (incremental decoding: a few hundred rows): the weight matrix is streamed once, so the
+  // only lever is the number of CTAs pulling it in; take the widest tile that still gives every SM a tile,
+  // down to 64 columns
+  const bool skinny = g_gemm_variant == 0 && d->M <= 512 && !d->out_fp32 && d->force_bn == 0 && d->split_k <= 1;
+  if (skinny) {
+    const int num_m = (d->M + BM - 1) / BM;
+    int bn = 64;
+    if (static_cast<long>(num_m) * ((d->N + 255) / 256) >= sms) bn = 256;
+    else if (static_cast<long>(num_m) * ((d->N + 127) / 128) >= sms) bn = 128;
+    a.split_k = 1;
+    CUtensorMap ta, tb;
+    bool ok;
+    if (!d->a_mn_major) ok = cached_tmap(&ta, d->a, d->M, d->K, d->lda, BM, BK);
+    else ok = cached_tmap(&ta, d->a, d->K, d->M, d->lda, BK, 64);
+    if (!ok) return "gemm: cuTensorMapEncodeTiled failed for A";
+    if (!d->b_mn_major) ok = cached_tmap(&tb, d->b, d->N, d->K, d->ldb, bn, BK);
+    else ok = cached_tmap(&tb, d->b, d->K, d->N, d->ldb, BK, 64);
+    if (!ok) return "gemm: cuTensorMapEncodeTiled failed for B";
+    const long tiles = static_cast<long>(num_m) * ((d->N + bn - 1) / bn);
+    const int grid = static_cast<int>(tiles < sms ? tiles : sms);
+    if (bn == 256) return launch_gemm<256>(ta, tb, a, grid, stream);
+    if (bn == 128) return launch_gemm<128>(ta, tb, a, grid, stream);
+    return launch_gemm<64>(ta, tb, a, grid, stream);
+  }
   // ---- CTA-pair kernel (256-row tiles): the default for everything but very small M ----------------
   if (g_gemm_variant != 1 && d->M > BM) {
     int bn = (d->N > 128) ? 256 : 128;

@@ -61,13 +61,13 @@ const char* nmtg_softmax_dropout_bwd(const void* dyd, const void* y, void* dx, i
                                      cudaStream_t stream);
 
 // ---- beam search step ---------------------------------------------------------------------------------------
-// logits: [R = B*K, V] (dtype 0 fp32 / 1 bf16).  For every row: lp = log_softmax(logits) with pad -> -inf,
+// logits: [R = B*K, V], rows `ld` elements apart (dtype 0 fp32 / 1 bf16).  For every row: lp = log_softmax(logits) with pad -> -inf,
 // eos -> -inf when step < min_len, everything but eos -> -inf when force_eos[r]; then per sentence the best
 // 2K of (scores[r] + lp[r, v]) over its K rows.  out_scores / out_index: [B, 2K]; index = k * V + v.
 // row_lse: fp32 [R] scratch, cand_*: scratch [R, 2K].
-const char* nmtg_beam_topk(const void* logits, int dtype, const float* scores, const uint8_t* force_eos, float* row_lse,
-                           float* cand_val, int* cand_idx, float* out_scores, long* out_index, int B, int K, int V,
-                           int pad, int eos, int ban_eos, cudaStream_t stream);
+const char* nmtg_beam_topk(const void* logits, long ld, int dtype, const float* scores, const uint8_t* force_eos,
+                           float* row_lse, float* cand_val, int* cand_idx, float* out_scores, long* out_index, int B, int K,
+                           int V, int pad, int eos, int ban_eos, cudaStream_t stream);
 // dst[r, 0:copy_bytes] = src[index[r], 0:copy_bytes] for rows `row_stride_bytes` apart (both multiples of 16).
 const char* nmtg_gather_rows(const void* src, void* dst, const long* index, int rows, long row_stride_bytes,
                              long copy_bytes, cudaStream_t stream);

@@ -128,3 +128,25 @@ def test_gemm_wgrad_fp32_accumulate_split_k(split_k):
     _status_ok()
     want = dy.float().t() @ x.float() + 1.0
     assert _rel_err(acc, want) < 5e-3
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 1024, 1024), (256, 1000, 512), (64, 4096, 1024), (256, 32000, 1024)])
+def test_gemm_decode_shapes_bias_and_transposed_weight(M, N, K):
+    """Few-row problems take 64-column tiles (many CTAs stream the weight matrix); bias epilogue, ragged N."""
+    torch.manual_seed(0)
+    a = torch.randn(M, K, device=DEV).bfloat16()
+    w = torch.randn(N, K, device=DEV).bfloat16()
+    bias = torch.randn(N, device=DEV).bfloat16()
+    out = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+    ops.gemm(a, w, out, bias=bias, act=1)
+    torch.cuda.synchronize()
+    _status_ok()
+    want = torch.relu(a.float() @ w.float().t() + bias.float())
+    assert _rel_err(out, want) < 1e-2
+    wt = w.t().contiguous()                      # [K, N]: the same weights stored N-contiguous
+    if N % 8 == 0:
+        out2 = torch.empty_like(out)
+        ops.gemm(a, wt, out2, b_mn_major=True, bias=bias, act=1)
+        torch.cuda.synchronize()
+        _status_ok()
+        assert _rel_err(out2, want) < 1e-2
