@@ -60,7 +60,7 @@ def load_data(opt):
 
 
 def run_process(rank, opt):
-    from nmtgminor_b200.train.trainer import Trainer
+    from nmtgminor_b200.train.research import select_trainer
     if len(opt.gpus) > 1 and "RANK" not in os.environ:
         os.environ["RANK"] = str(rank)
         os.environ["LOCAL_RANK"] = str(opt.gpus[rank])
@@ -71,7 +71,7 @@ def run_process(rank, opt):
     if getattr(opt, "patch_vocab_multiplier", 1) > 1 and "tgt" in dicts:
         dicts["tgt"].patch(opt.patch_vocab_multiplier)
     constants = Constants.from_dicts(opt, dicts)
-    trainer = Trainer(opt.gpus[rank] if opt.gpus else -1, dicts, opt, constants)
+    trainer = select_trainer(opt)(opt.gpus[rank] if opt.gpus else -1, dicts, opt, constants)
     trainer.run(train_data=train_data, valid_data=valid_data)
 
 
