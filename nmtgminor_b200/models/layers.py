@@ -146,10 +146,17 @@ class Embedding(nn.Module):
             self._pos_work = self.pos.to(device=device, dtype=torch.bfloat16)
         return self._pos_work
 
+    word_dropout = 0.0      # probability of dropping a whole vocabulary entry for one batch (training only)
+
     def forward(self, seqs: PackedSeqs, dropout_p: float = 0.0):
         pos = seqs.positions + self.pos_offset if (self.use_pos and self.pos_offset) else seqs.positions
-        return ops.embedding(seqs.tokens, self.weight, pos if self.use_pos else None, self._pos_table(seqs.tokens.device),
-                             self.scale, dropout_p, self.training, self.pad_idx, pos_trainable=self.learned_pos)
+        tokens, scale = seqs.tokens, self.scale
+        if self.training and self.word_dropout > 0:
+            from ..modules.dropout import word_dropout_tokens
+            tokens, mult = word_dropout_tokens(tokens, self.weight.shape[0], self.word_dropout, self.pad_idx)
+            scale = scale * mult
+        return ops.embedding(tokens, self.weight, pos if self.use_pos else None, self._pos_table(seqs.tokens.device),
+                             scale, dropout_p, self.training, self.pad_idx, pos_trainable=self.learned_pos)
 
 
 class SelfAttention(nn.Module):
@@ -259,6 +266,16 @@ class FeedForward(nn.Module):
                        dropout_p, residual, self.training)
 
 
+def _sub(layer, fn, inp, residual, p, seqs, *args):
+    """Sub-layer output + residual.  Element-wise dropout rides in the producing kernel; with ``layer.variational``
+    the mask is shared along time instead and applied outside the kernel."""
+    if getattr(layer, "variational", False) and layer.training and p > 0:
+        from ..modules.dropout import variational_dropout
+        y = fn(inp, *args, residual=None, dropout_p=0.0)
+        return residual + variational_dropout(y, p, True, cu=seqs.cu)
+    return fn(inp, *args, residual=residual, dropout_p=p)
+
+
 class EncoderLayer(nn.Module):
     """Self-attention + FFN block.  Pre-LN: x += D(Attn(LN(x))); x += D(FFN(LN(x))).  Post-LN (``post_norm``):
     x = LN(x + D(Attn(x))); x = LN(x + D(FFN(x))).  Optional stochastic depth (``death_rate``)."""
@@ -277,11 +294,12 @@ class EncoderLayer(nn.Module):
     def forward(self, x, seqs: PackedSeqs):
         if self.training and self.death_rate > 0 and torch.rand(1).item() < self.death_rate:
             return x
+        p = self.dropout
         if self.post_norm:
-            x = self.attn_norm(self.attn(x, seqs, residual=x, dropout_p=self.dropout))
-            return self.ffn_norm(self.ffn(x, residual=x, dropout_p=self.dropout))
-        x = self.attn(self.attn_norm(x), seqs, residual=x, dropout_p=self.dropout)
-        return self.ffn(self.ffn_norm(x), residual=x, dropout_p=self.dropout)
+            x = self.attn_norm(_sub(self, self.attn, x, x, p, seqs, seqs))
+            return self.ffn_norm(_sub(self, self.ffn, x, x, p, seqs))
+        x = _sub(self, self.attn, self.attn_norm(x), x, p, seqs, seqs)
+        return _sub(self, self.ffn, self.ffn_norm(x), x, p, seqs)
 
 
 class DecoderLayer(nn.Module):
@@ -314,18 +332,18 @@ class DecoderLayer(nn.Module):
             return x
         p = self.dropout
         if self.post_norm:
-            x = self.self_norm(self.self_attn(x, seqs, residual=x, dropout_p=p))
+            x = self.self_norm(_sub(self, self.self_attn, x, x, p, seqs, seqs))
             if self.interleaved_ffn:
-                x = self.mid_norm(self.mid_ffn(x, residual=x, dropout_p=p))
+                x = self.mid_norm(_sub(self, self.mid_ffn, x, x, p, seqs))
             if not self.ignore_source:
-                x = self.cross_norm(self.cross_attn(x, seqs, memory, mem_seqs, residual=x, dropout_p=p))
-            return self.ffn_norm(self.ffn(x, residual=x, dropout_p=p))
-        x = self.self_attn(self.self_norm(x), seqs, residual=x, dropout_p=p)
+                x = self.cross_norm(_sub(self, self.cross_attn, x, x, p, seqs, seqs, memory, mem_seqs))
+            return self.ffn_norm(_sub(self, self.ffn, x, x, p, seqs))
+        x = _sub(self, self.self_attn, self.self_norm(x), x, p, seqs, seqs)
         if self.interleaved_ffn:
-            x = self.mid_ffn(self.mid_norm(x), residual=x, dropout_p=p)
+            x = _sub(self, self.mid_ffn, self.mid_norm(x), x, p, seqs)
         if not self.ignore_source:
-            x = self.cross_attn(self.cross_norm(x), seqs, memory, mem_seqs, residual=x, dropout_p=p)
-        return self.ffn(self.ffn_norm(x), residual=x, dropout_p=p)
+            x = _sub(self, self.cross_attn, self.cross_norm(x), x, p, seqs, seqs, memory, mem_seqs)
+        return _sub(self, self.ffn, self.ffn_norm(x), x, p, seqs)
 
     def step(self, x, cache: dict, mem_mask):
         if self.post_norm:

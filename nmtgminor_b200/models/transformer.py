@@ -20,7 +20,17 @@ import torch
 import torch.nn as nn
 
 from .. import ops
+from ..modules.dropout import checkpointed
 from .layers import DecoderLayer, Embedding, EncoderLayer, LayerNorm, PackedSeqs
+
+
+def _apply_regularisation_options(stack, opt):
+    """``-variational_dropout`` (time-shared masks on the residual branches), ``-word_dropout`` (vocabulary-level
+    dropout in the embedding) and ``-checkpointing N`` (recompute the first N layers in backward) for a layer stack."""
+    stack.checkpointing = int(getattr(opt, "checkpointing", 0) or 0)
+    for layer in stack.layers:
+        layer.variational = bool(getattr(opt, "variational_dropout", False))
+    stack.embed.word_dropout = float(getattr(opt, "word_dropout", 0.0) or 0.0)
 
 
 def _expected_death_rates(n_layers: int, death_rate: float):
@@ -40,11 +50,15 @@ class TransformerEncoder(nn.Module):
                          ffn_dropout=opt.ffn_dropout if getattr(opt, "ffn_dropout", -1) >= 0 else None)
             for i in range(n)])
         self.final_norm = LayerNorm(opt.model_size)
+        _apply_regularisation_options(self, opt)
 
     def forward(self, src: PackedSeqs):
         x = self.embed(src, self.emb_dropout)
-        for layer in self.layers:
-            x = layer(x, src)
+        for i, layer in enumerate(self.layers):
+            if self.training and i < self.checkpointing:
+                x = checkpointed(layer, x, src)
+            else:
+                x = layer(x, src)
         return self.final_norm(x)
 
 
@@ -61,11 +75,15 @@ class TransformerDecoder(nn.Module):
                          ignore_source=ignore_source)
             for i in range(opt.layers)])
         self.final_norm = LayerNorm(opt.model_size)
+        _apply_regularisation_options(self, opt)
 
     def forward(self, tgt: PackedSeqs, memory, src: PackedSeqs):
         x = self.embed(tgt, self.emb_dropout)
-        for layer in self.layers:
-            x = layer(x, tgt, memory, src)
+        for i, layer in enumerate(self.layers):
+            if self.training and i < self.checkpointing:
+                x = checkpointed(layer, x, tgt, memory, src)
+            else:
+                x = layer(x, tgt, memory, src)
         return self.final_norm(x)
 
     def step(self, tokens, position: int, state: "DecodingState"):
@@ -154,9 +172,18 @@ class Seq2SeqBase(nn.Module):
         """Hook for CTC / language-id / contrastive terms; returns a tensor to add to the loss or None."""
         return None
 
+    switchout = 0.0
+
+    def _switchout(self, seqs: PackedSeqs, vocab: int) -> PackedSeqs:
+        from ..modules.dropout import switchout_packed
+        return PackedSeqs(switchout_packed(seqs.tokens, seqs.cu, vocab, self.switchout), seqs.positions, seqs.cu, seqs.max_len,
+                          seqs.lengths, seqs.extras)
+
     def forward(self, batch, return_logits: bool = False, compute_loss: bool = True, grad_scale=None, **_unused) -> Dict:
         context, src = self.encode(batch)
         tgt = batch.packed_target_input()
+        if self.training and self.switchout > 0:
+            tgt = self._switchout(tgt, self.generator.weight.shape[0])
         labels = batch.packed_target_output()
         hidden = self.decoder(tgt, context, src)
         out = {"hidden_packed": hidden, "context_packed": context, "src": src, "tgt": tgt, "target": labels}
@@ -252,10 +279,13 @@ class Transformer(Seq2SeqBase):
         if getattr(opt, "tie_weights", False):
             self.tie_weights()
         self.label_smoothing = getattr(opt, "label_smoothing", 0.0)
+        self.switchout = float(getattr(opt, "switchout", 0.0) or 0.0)
 
     def share_enc_dec_embedding(self):
         self.encoder.embed.weight = self.decoder.embed.weight
 
     def encode(self, batch):
         src = batch.packed_source()
+        if self.training and self.switchout > 0:
+            src = self._switchout(src, self.encoder.embed.weight.shape[0])
         return self.encoder(src), src
