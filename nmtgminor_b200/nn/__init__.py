@@ -1,0 +1,2 @@
+from .blocks import *  # noqa: F401,F403
+from .builders import *  # noqa: F401,F403
