@@ -80,6 +80,8 @@ class ConvFeatureExtractor(nn.Module):
         return lengths.clamp(min=0)
 
     def forward(self, wav):          # [B, samples] -> [B, T', C]
+        if wav.is_cuda and len(self.convs) > 1 and ops.fused_param(self.convs[1].weight):
+            return self._forward_gemm(wav)
         x = wav.unsqueeze(1)
         for conv, norm in zip(self.convs, self.norms):
             x = conv(x)
@@ -89,6 +91,26 @@ class ConvFeatureExtractor(nn.Module):
                 x = norm(x)
             x = F.gelu(x)
         return x.transpose(1, 2)
+
+
+    def _forward_gemm(self, wav):
+        """Channels-last path: the single-channel first layer stays a library convolution, every later layer is one
+        tcgen05 GEMM over overlapping rows (``ops.conv.conv1d``) with GELU in its epilogue when no norm intervenes."""
+        from ..ops.conv import conv1d
+        conv, norm = self.convs[0], self.norms[0]
+        x = F.conv1d(wav.unsqueeze(1).to(conv.weight.dtype), conv.weight, conv.bias, stride=conv.stride[0])
+        if isinstance(norm, nn.LayerNorm):
+            x = F.gelu(norm(x.transpose(1, 2)))
+        else:
+            x = F.gelu(norm(x)).transpose(1, 2)
+        x = x.to(torch.bfloat16)
+        for conv, norm in zip(self.convs[1:], self.norms[1:]):
+            if isinstance(norm, nn.LayerNorm):
+                x = conv1d(x, conv.weight, conv.bias, conv.stride[0], "none")
+                x = F.gelu(F.layer_norm(x.float(), norm.normalized_shape, norm.weight.float(), norm.bias.float(), norm.eps)).to(torch.bfloat16)
+            else:
+                x = conv1d(x, conv.weight, conv.bias, conv.stride[0], "gelu")
+        return x
 
 
 class ConvPositionalEmbedding(nn.Module):

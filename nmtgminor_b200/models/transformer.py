@@ -164,6 +164,7 @@ class Seq2SeqBase(nn.Module):
 
     pad_idx = 0
     label_smoothing = 0.0
+    generator_chunk_rows = 0      # > 0: output projection + loss over this many rows at a time (no [rows, V] logits)
 
     def encode(self, batch):
         raise NotImplementedError
@@ -190,7 +191,8 @@ class Seq2SeqBase(nn.Module):
         if compute_loss:
             loss, correct, row_loss = ops.generator_cross_entropy(
                 hidden, self.generator.weight, self.generator.bias, labels,
-                self.label_smoothing if self.training else 0.0, self.pad_idx, grad_scale)
+                self.label_smoothing if self.training else 0.0, self.pad_idx, grad_scale,
+                chunk_rows=self.generator_chunk_rows if self.training else 0)
             out.update(loss=loss, correct=correct, row_loss=row_loss)
             aux = self.auxiliary_losses(batch, context, src, out)
             if aux is not None:
@@ -280,6 +282,7 @@ class Transformer(Seq2SeqBase):
             self.tie_weights()
         self.label_smoothing = getattr(opt, "label_smoothing", 0.0)
         self.switchout = float(getattr(opt, "switchout", 0.0) or 0.0)
+        self.generator_chunk_rows = int(getattr(opt, "generator_chunk_rows", 0) or 0)
 
     def share_enc_dec_embedding(self):
         self.encoder.embed.weight = self.decoder.embed.weight

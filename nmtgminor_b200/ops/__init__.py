@@ -605,13 +605,54 @@ class _GeneratorXentFn(torch.autograd.Function):
         return (dh,) + (None,) * 8
 
 
-def generator_cross_entropy(h, weight, bias, labels, smoothing=0.0, pad_idx=0, grad_scale=None):
-    """Output projection + label-smoothed CE.  Returns (loss_sum, n_correct, row_loss)."""
+class _GeneratorXentChunkedFn(torch.autograd.Function):
+    """``_GeneratorXentFn`` without the ``[rows, V]`` buffer: the rows are processed ``chunk`` at a time through one
+    ``[chunk, V]`` scratch that stays in L2 between its four uses (logits GEMM -> fused CE in place -> dH GEMM ->
+    dW GEMM), so the logits never travel to HBM.  Gradients are produced during the forward call (the CE kernel
+    writes them anyway), which is why a ``grad_scale`` must be given: the upstream gradient is taken to be 1."""
+
+    @staticmethod
+    def forward(ctx, h, w, bias, gw, gb, labels, smoothing, pad_idx, grad_scale, chunk):
+        rows, V = h.shape[0], w.shape[0]
+        scratch = empty_rows(chunk, V, h.device)
+        loss_sum = torch.zeros(1, dtype=torch.float32, device=h.device)
+        correct = torch.zeros(1, dtype=torch.float32, device=h.device)
+        gs_t = grad_scale if isinstance(grad_scale, torch.Tensor) else None
+        gs_v = 1.0 if gs_t is not None else float(grad_scale)
+        dh = torch.empty_like(h)
+        row_losses = []
+        for r0 in range(0, rows, chunk):
+            r1 = min(r0 + chunk, rows)
+            lg = scratch[:r1 - r0]
+            gemm(h[r0:r1], w, lg, bias=bias)
+            row_losses.append(ext().xent_fused(lg, labels[r0:r1], smoothing, pad_idx, loss_sum, correct, gs_t, gs_v, True))
+            gemm(lg, w, dh[r0:r1], b_mn_major=True)
+            if gw is not None:
+                gemm(lg, h[r0:r1], gw, a_mn_major=True, b_mn_major=True, accumulate=True, allow_split_k=True)
+            if gb is not None:
+                ext().colsum(lg, gb)
+        row_loss = torch.cat(row_losses) if len(row_losses) > 1 else row_losses[0]
+        ctx.save_for_backward(dh)
+        ctx.mark_non_differentiable(correct, row_loss)
+        return loss_sum, correct, row_loss
+
+    @staticmethod
+    def backward(ctx, g_loss, _g1, _g2):
+        (dh,) = ctx.saved_tensors
+        return (dh,) + (None,) * 9
+
+
+def generator_cross_entropy(h, weight, bias, labels, smoothing=0.0, pad_idx=0, grad_scale=None, chunk_rows: int = 0):
+    """Output projection + label-smoothed CE.  Returns (loss_sum, n_correct, row_loss).  ``chunk_rows`` > 0 (with a
+    ``grad_scale``) selects the chunked variant that keeps the logits out of HBM."""
     if fused_param(weight) and h.is_cuda:
         b = bias.work if bias is not None else None
         gw = weight.main_grad if weight.requires_grad else None
         gb = bias.main_grad if (bias is not None and bias.requires_grad) else None
         hin = (h if h.dtype == torch.bfloat16 else h.to(torch.bfloat16)).contiguous()
+        if torch.is_grad_enabled() and chunk_rows > 0 and grad_scale is not None and h.shape[0] > chunk_rows:
+            return _GeneratorXentChunkedFn.apply(hin, weight.work, b, gw, gb, labels.contiguous(), float(smoothing),
+                                                 int(pad_idx), grad_scale, int(chunk_rows))
         if torch.is_grad_enabled():
             return _GeneratorXentFn.apply(hin, weight.work, b, gw, gb, labels.contiguous(), float(smoothing), int(pad_idx),
                                           grad_scale)

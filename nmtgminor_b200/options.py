@@ -23,6 +23,8 @@ EXTRA_TRAIN_FLAGS = [
     ("nccl_ddp", "flag", False, {}),             # baseline switch: NCCL all-reduce of the flat gradient buffer
     ("watchdog_timeout", "float", 0.0, {}),      # seconds without a heartbeat before a rank is declared dead
     ("trace_nvtx", "flag", False, {}),           # NVTX ranges around layers / buckets
+    ("generator_chunk_rows", "int", 0, {}),      # output projection + loss this many rows at a time (logits stay in L2)
+    ("fused_conv", "flag", False, {}),           # speech front-end convolutions through the tcgen05 GEMM (implicit im2col)
 ]
 
 

@@ -94,3 +94,25 @@ def test_checkpointing_replays_fused_dropout_masks():
     assert abs(losses[0] - losses[1]) < 1e-3 * abs(losses[0])
     denom = grads[0].abs().max().item()
     assert (grads[0] - grads[1]).abs().max().item() / denom < 2e-2
+
+
+def test_chunked_generator_loss_matches_unchunked():
+    """Rows processed 512 at a time through one scratch buffer give the loss and gradients of the one-shot path."""
+    d = synthetic_dict(2000)
+    batch = token_budget_batches(2000, 5, 40, 1500, 1, seed=4, static=True, padded=False)[0]
+    res = []
+    for extra in ([], ["-generator_chunk_rows", "512"]):
+        torch.manual_seed(0)
+        model = Transformer(_opt(extra), {"src": d, "tgt": d}).train()
+        store = FlatParameterStore(model, "cuda")
+        for b in model.buffers():
+            b.data = b.data.cuda()
+        out = model(copy.deepcopy(batch).cuda("cuda", hot_only=True), grad_scale=1.0)
+        out["loss"].backward()
+        torch.cuda.synchronize()
+        res.append((out["loss"].item(), out["correct"].item(), store.grad.clone(), out["row_loss"].clone()))
+    assert ops.check_status() == 0
+    assert abs(res[0][0] - res[1][0]) < 1e-3 * abs(res[0][0]) and res[0][1] == res[1][1]
+    assert torch.allclose(res[0][3], res[1][3], atol=1e-3)
+    denom = res[0][2].abs().max().item()
+    assert (res[0][2] - res[1][2]).abs().max().item() / denom < 2e-2
