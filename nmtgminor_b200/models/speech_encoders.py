@@ -110,7 +110,7 @@ class ConvFeatureExtractor(nn.Module):
                 x = F.gelu(F.layer_norm(x.float(), norm.normalized_shape, norm.weight.float(), norm.bias.float(), norm.eps)).to(torch.bfloat16)
             else:
                 x = conv1d(x, conv.weight, conv.bias, conv.stride[0], "gelu")
-        return x
+        return x.float()      # the modules that follow (feature LayerNorm, projection) hold fp32 parameters
 
 
 class ConvPositionalEmbedding(nn.Module):
@@ -207,8 +207,13 @@ class WhisperEncoder(nn.Module):
     def forward(self, source):
         feats, lengths = split_audio_batch(source)           # [B, T, n_mels]
         assert feats.shape[-1] == self.n_mels, "expected %d mel bins (+1 padding channel), got %d" % (self.n_mels, feats.shape[-1])
-        x = F.gelu(self.conv1(feats.transpose(1, 2).float()))
-        x = F.gelu(self.conv2(x)).transpose(1, 2)             # [B, T/2, d]
+        if feats.is_cuda and ops.fused_param(self.conv1.weight) and self.n_mels % 8 == 0:
+            from ..ops.conv import conv1d                       # both stem layers as GEMMs with GELU in the epilogue
+            x = conv1d(feats, self.conv1.weight, self.conv1.bias, 1, "gelu", padding=1)
+            x = conv1d(x, self.conv2.weight, self.conv2.bias, 2, "gelu", padding=1)
+        else:
+            x = F.gelu(self.conv1(feats.transpose(1, 2).float()))
+            x = F.gelu(self.conv2(x)).transpose(1, 2)             # [B, T/2, d]
         out_len = torch.div(lengths + 1, 2, rounding_mode="floor").clamp(max=x.shape[1])
         if x.shape[1] > self.positions.shape[0]:
             self.positions = sinusoidal_table(x.shape[1], self.dim).to(x.device)
