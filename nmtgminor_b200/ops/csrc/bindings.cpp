@@ -343,6 +343,37 @@ void allreduce_adamw(int64_t rank, const std::vector<int64_t>& grads, const std:
                           slice_begin, slice_len, total_len, epoch.data_ptr<int>(), status_ptr(master), cur_stream()));
 }
 
+void fsdp_gather(int64_t rank, const std::vector<int64_t>& works, Tensor& dst, int64_t shard_off, int64_t piece_len,
+                 int64_t unit_len, int64_t ctas) {
+  need_bf16(dst, "dst");
+  TORCH_CHECK(dst.is_contiguous() && dst.numel() >= unit_len, "fsdp_gather: staging buffer too small");
+  std::vector<int64_t> zeros(works.size(), 0);
+  c10::cuda::CUDAGuard guard(dst.device());
+  NmtgPeerTable t = make_table(rank, zeros, works, zeros, zeros, c10::nullopt);
+  ck(nmtg_fsdp_gather(&t, dst.data_ptr(), shard_off, piece_len, unit_len, static_cast<int>(ctas), cur_stream()));
+}
+
+void fsdp_step(int64_t rank, const std::vector<int64_t>& grads, const std::vector<int64_t>& works, const std::vector<int64_t>& flags,
+               const std::vector<int64_t>& partials, const std::vector<int64_t>& shard_off, const std::vector<int64_t>& global_begin,
+               const std::vector<int64_t>& piece_len, Tensor& reduced, Tensor& sq, Tensor& nonfinite, Tensor& master, Tensor& m,
+               Tensor& v, const Tensor& hyper, int64_t shard_len, int64_t total_len, Tensor& epoch, const OptTensor& norm_out) {
+  need_f32(reduced, "reduced"); need_f32(sq, "sq"); need_f32(master, "master"); need_f32(m, "m"); need_f32(v, "v");
+  need_f32(hyper, "hyper");
+  TORCH_CHECK(reduced.numel() >= shard_len && master.numel() >= shard_len && m.numel() >= shard_len && v.numel() >= shard_len);
+  TORCH_CHECK(shard_off.size() == global_begin.size() && shard_off.size() == piece_len.size() && shard_off.size() <= kFsdpMaxUnits);
+  c10::cuda::CUDAGuard guard(master.device());
+  NmtgPeerTable t = make_table(rank, grads, works, flags, partials, norm_out);
+  NmtgFsdpPieces pc = {};
+  pc.n = static_cast<int>(shard_off.size());
+  for (int u = 0; u < pc.n; ++u) {
+    pc.shard_off[u] = shard_off[u]; pc.global_begin[u] = global_begin[u]; pc.len[u] = piece_len[u];
+    TORCH_CHECK(shard_off[u] + piece_len[u] <= shard_len && global_begin[u] + piece_len[u] <= total_len, "fsdp_step: piece out of range");
+  }
+  ck(nmtg_fsdp_step(&t, &pc, reduced.data_ptr<float>(), sq.data_ptr<float>(), nonfinite.data_ptr<int>(), master.data_ptr<float>(),
+                    m.data_ptr<float>(), v.data_ptr<float>(), reinterpret_cast<const NmtgAdamHyper*>(hyper.data_ptr<float>()), shard_len,
+                    total_len, epoch.data_ptr<int>(), status_ptr(master), cur_stream()));
+}
+
 void peer_wait_row(int64_t rank, const std::vector<int64_t>& flags, int64_t row, int64_t epoch, const Tensor& like) {
   std::vector<int64_t> zeros(flags.size(), 0);
   c10::cuda::CUDAGuard guard(like.device());
@@ -384,6 +415,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("ipc_open_handle", &ipc_open_handle);
   m.def("ipc_close_handle", &ipc_close_handle);
   m.def("allreduce_adamw", &allreduce_adamw);
+  m.def("fsdp_gather", &fsdp_gather);
+  m.def("fsdp_step", &fsdp_step);
   m.def("peer_wait_row", &peer_wait_row);
   m.def("read_status", &read_status);
   m.def("clear_status", &clear_status);

@@ -28,51 +28,11 @@
 #include <cuda_bf16.h>
 #include <stdint.h>
 #include "ops_api.h"
+#include "peer_sync.cuh"
 
 namespace b200 {
 
 int num_sms();
-
-constexpr int kMaxRanks = 16;
-constexpr unsigned kFlagPolls = 1u << 22;
-
-__device__ __forceinline__ void st_release_sys(int* p, int v) {
-  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ int ld_acquire_sys(const int* p) {
-  int v;
-  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ float ld_relaxed_sys_f32(const float* p) {
-  float v;
-  asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
-  return v;
-}
-
-// Thread i < n publishes `epoch` in slot `rank` of peer i's flag row, then waits until slot i of the local
-// row reaches `epoch`.  Returns false for the whole CTA when any wait ran out of polls.
-__device__ bool peer_barrier(const NmtgPeerTable& t, int row, int epoch, int* status) {
-  __shared__ int s_fail;
-  if (threadIdx.x == 0) s_fail = 0;
-  __syncthreads();
-  if (threadIdx.x < t.world) {
-    __threadfence_system();
-    st_release_sys(t.flags[threadIdx.x] + row * kMaxRanks + t.rank, epoch);
-    const int* mine = t.flags[t.rank] + row * kMaxRanks + threadIdx.x;
-    bool ok = false;
-    for (unsigned i = 0; i < kFlagPolls; ++i) {
-      if (ld_acquire_sys(mine) >= epoch) { ok = true; break; }
-      if (i > 64) __nanosleep(i > 4096 ? 256 : 32);
-    }
-    if (!ok) {
-      s_fail = 1;
-      if (status) atomicCAS(status, 0, 5 /* kTimeoutPeerFlag */);
-    }
-  }
-  __syncthreads();
-  return s_fail == 0;
-}
 
 __global__ void __launch_bounds__(512)
 reduce_slice_kernel(const NmtgPeerTable t, float* __restrict__ reduced, float* __restrict__ sq_out, int* __restrict__ nonfinite,
@@ -225,6 +185,11 @@ const char* nmtg_allreduce_adamw(const NmtgPeerTable* t, float* reduced, float* 
   update_slice_kernel<<<num_sms() * 2, 512, 0, stream>>>(*t, reduced, master, m, v, hyper_dev, sq, nonfinite, slice_begin, slice_len,
                                                          total_len, epoch_dev, status);
   if ((e = err_str())) return e;
+  finish_step_kernel<<<1, 32, 0, stream>>>(*t, epoch_dev, status);
+  return err_str();
+}
+
+const char* nmtg_peer_finish_step(const NmtgPeerTable* t, int* epoch_dev, int* status, cudaStream_t stream) {
   finish_step_kernel<<<1, 32, 0, stream>>>(*t, epoch_dev, status);
   return err_str();
 }

@@ -136,5 +136,26 @@ struct NmtgPeerTable {
 const char* nmtg_allreduce_adamw(const NmtgPeerTable* t, float* reduced, float* sq, int* nonfinite, float* master, float* m,
                                  float* v, const NmtgAdamHyper* hyper_dev, long slice_begin, long slice_len, long total_len,
                                  int* epoch_dev, int* status, cudaStream_t stream);
+// the closing barrier of a step (row 2) + epoch advance, shared by the data-parallel and the fully sharded step
+const char* nmtg_peer_finish_step(const NmtgPeerTable* t, int* epoch_dev, int* status, cudaStream_t stream);
+
+// ---- fully sharded data parallelism ----------------------------------------------------------------------------
+// Unit u of the flat parameter space is cut into `world` pieces; this rank's piece is `len[u]` elements at
+// `global_begin[u]` of the flat space and at `shard_off[u]` of the shard-ordered buffers (bf16 parameters in
+// works[rank], fp32 master / moments / reduced gradients).
+constexpr int kFsdpMaxUnits = 96;
+struct NmtgFsdpPieces {
+  int n;
+  long shard_off[kFsdpMaxUnits];
+  long global_begin[kFsdpMaxUnits];
+  long len[kFsdpMaxUnits];
+};
+// dst[0:unit_len] (bf16) <- the unit's pieces pulled from every rank's shard (works[p] + shard_off, piece_len each)
+const char* nmtg_fsdp_gather(const NmtgPeerTable* t, void* dst, long shard_off, long piece_len, long unit_len, int ctas,
+                             cudaStream_t stream);
+// reduce-scatter of the full gradient buffers into shard order + Adam(W) on the shard + closing barrier
+const char* nmtg_fsdp_step(const NmtgPeerTable* t, const NmtgFsdpPieces* pieces, float* reduced, float* sq, int* nonfinite,
+                           float* master, float* m, float* v, const NmtgAdamHyper* hyper_dev, long shard_len, long total_len,
+                           int* epoch_dev, int* status, cudaStream_t stream);
 // waits (bounded) on one flag row; used to exercise the timeout path
 const char* nmtg_peer_wait_row(const NmtgPeerTable* t, int row, int epoch, int* status, cudaStream_t stream);

@@ -80,7 +80,8 @@ class TrainEngine:
         self.world_size = world
         heap = None
         ptrs = {}
-        if ddp == "fused" and world > 1 and self.on_gpu and ops.extension_available():
+        fsdp = ddp == "fsdp" and self.on_gpu and ops.extension_available()
+        if (fsdp or (ddp == "fused" and world > 1)) and self.on_gpu and ops.extension_available():
             from ..parallel.symmetric import SymmetricHeap
             heap = SymmetricHeap(self.device)
 
@@ -90,7 +91,9 @@ class TrainEngine:
                     ptrs[name] = p
                     return t
                 return alloc
-            self.store = FlatParameterStore(model, self.device, allocator={"grad": symm("grad"), "work": symm("work")},
+            # fully sharded: no replicated bf16 copy; layers read gathered weights from staging buffers
+            work_alloc = (lambda n, dt: None) if fsdp else symm("work")
+            self.store = FlatParameterStore(model, self.device, allocator={"grad": symm("grad"), "work": work_alloc},
                                             pad_total_to=256 * world)
         else:
             self.store = FlatParameterStore(model, self.device, pad_total_to=256 * max(world, 1))
@@ -98,7 +101,16 @@ class TrainEngine:
             b.data = b.data.to(self.device)
         self.optim = Optim(opt)
         self.optim.set_parameters(model.parameters(), self.store)
-        if world > 1 and reducer is None and ddp is not None:
+        if fsdp:
+            from ..parallel.ddp import broadcast_parameters
+            from ..parallel.fsdp import FullyShardedAdam
+            if world > 1:
+                broadcast_parameters(self.store)
+            assert self.optim.fused, "-fsdp needs the fused Adam(W) path"
+            reducer = FullyShardedAdam(model, self.store, self.optim, heap, ptrs["grad"])
+            self.optim.attach_distributed(reducer)
+            cuda_graph = False
+        elif world > 1 and reducer is None and ddp is not None:
             from ..parallel.ddp import NcclReducer, broadcast_parameters
             broadcast_parameters(self.store)
             if heap is not None and self.optim.fused:

@@ -69,6 +69,8 @@ class Trainer:
         ddp = None
         if self.world_size > 1:
             ddp = "nccl" if (getattr(opt, "nccl_ddp", False) or not self.cuda) else "fused"
+        if getattr(opt, "fsdp", False) and self.cuda:
+            ddp = "fsdp"
         self.engine = TrainEngine(self.model, opt, self.device, reducer=None,
                                   cuda_graph=getattr(opt, "cuda_graph", False) and getattr(opt, "update_frequency", 1) == 1,
                                   grad_scale=grad_scale, ddp=ddp)

@@ -164,3 +164,76 @@ def test_two_gpu_training_with_fused_ddp():
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     _run(_worker_train, 2)
+
+
+def _small_opt(extra=()):
+    from nmtgminor_b200.options import default_options
+    return default_options(["-model_size", "256", "-layers", "3", "-n_heads", "4", "-inner_size", "1024", "-tie_weights",
+                            "-join_embedding", "-ffn_activation", "relu", "-label_smoothing", "0.1", "-optim", "adam",
+                            "-learning_rate", "1e-3", "-update_method", "regular", "-dropout", "0.0", "-attn_dropout", "0.0",
+                            "-emb_dropout", "0.0", "-weight_decay", "0.01"] + list(extra))
+
+
+def _train_losses(ddp, rank, steps=8, seed_off=0):
+    from nmtgminor_b200.data.synthetic import synthetic_dict, token_budget_batches
+    from nmtgminor_b200.models.transformer import Transformer
+    from nmtgminor_b200.train.engine import TrainEngine
+    torch.manual_seed(1)
+    d = synthetic_dict(2000)
+    model = Transformer(_small_opt(), {"src": d, "tgt": d})
+    eng = TrainEngine(model, _small_opt(), device="cuda:%d" % rank, cuda_graph=False, ddp=ddp)
+    batches = [b.pin_memory() for b in token_budget_batches(2000, 5, 40, 1024, 4, seed=5 + seed_off, static=True)]
+    losses = []
+    for it in range(steps):
+        loss, _ = eng.train_step(batches[it % len(batches)])
+        losses.append(loss.item())
+    torch.cuda.synchronize()
+    return eng, losses
+
+
+def test_fsdp_single_rank_matches_plain_engine():
+    """World size 1 exercises the whole sharded path (units, staging buffers, gather hooks, sharded Adam)."""
+    from nmtgminor_b200 import ops
+    _, plain = _train_losses(None, 0)
+    eng, sharded = _train_losses("fsdp", 0)
+    assert ops.check_status() == 0
+    fs = eng.optim.distributed
+    assert len([u for u in fs.units if u.slot >= 0]) == 6 and fs.store.work is None
+    for a, b in zip(plain, sharded):
+        assert abs(a - b) < 2e-3 * abs(a), (plain, sharded)
+    assert sharded[-1] < sharded[0]
+    fs.gather_master()
+    assert torch.isfinite(eng.store.master).all()
+
+
+def _worker_fsdp(rank, world, port, q):
+    try:
+        _init(rank, world, port)
+        from nmtgminor_b200 import ops
+        eng_f, fused = _train_losses("fused", rank, seed_off=rank)
+        eng_s, sharded = _train_losses("fsdp", rank, seed_off=rank)
+        assert ops.check_status() == 0
+        for a, b in zip(fused, sharded):
+            assert abs(a - b) < 5e-3 * abs(a), (fused, sharded)
+        # the sharded master weights, gathered, equal the data-parallel run's weights
+        eng_f.optim.distributed.gather_master()
+        eng_s.optim.distributed.gather_master()
+        # Adam moves every weight by about lr per step, so rounding-level gradient differences can flip single steps
+        delta = (eng_f.store.master - eng_s.store.master).abs()
+        assert delta.max().item() < 2e-2 and delta.mean().item() < 5e-4, (delta.max().item(), delta.mean().item())
+        rep = eng_s.optim.distributed.memory_report()
+        assert rep["bf16_shard"] * world <= rep["replicated_bf16_would_be"] * 1.05 + 4096 * world
+        q.put((rank, "ok", sharded[-1]))
+    except Exception:  # noqa: BLE001
+        import traceback
+        q.put((rank, "fail", traceback.format_exc()))
+    finally:
+        if dist.is_initialized():
+            dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_fsdp_matches_fused_data_parallel(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip("needs %d GPUs" % world)
+    _run(_worker_fsdp, world)
