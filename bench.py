@@ -183,7 +183,7 @@ def run_ours(args, rank, local, world):
     model = Transformer(opt, {"src": d, "tgt": d})
     n_params = sum(p.numel() for p in model.parameters())
     engine = TrainEngine(model, opt, device="cuda:%d" % local, cuda_graph=not args.no_graph,
-                         ddp=(args.ddp if world > 1 else None))
+                         ddp=(args.ddp if (world > 1 or args.ddp == "fsdp") else None))
 
     groups = sentence_groups(N_DISTINCT_BATCHES, seed=1000 + rank)
     up = lambda v: (v + 127) // 128 * 128
@@ -223,7 +223,7 @@ def run_ours(args, rank, local, world):
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "ours",
             "config": {"model": "transformer-big 6+6 d1024 h16 ffn4096 relu vocab32000 tied", "global_batch": int(round(total_tok / args.steps)),
                        "global_batch_unit": "target tokens", "seq_len": "uniform[20,100]", "parallelism": "dp%d" % world,
-                       "optimizer": "adamw", "params": n_params, "cuda_graph": not args.no_graph, "ddp": args.ddp if world > 1 else None,
+                       "optimizer": "adamw", "params": n_params, "cuda_graph": not args.no_graph, "ddp": args.ddp if (world > 1 or args.ddp == "fsdp") else None,
                        "l2": "per-step working set (weights + optimizer state + activations, several GB) exceeds the 126 MB L2; no flush"},
             "clocks": clocks,
             "e2e": {"value": total_tok_e2e / (ms_e2e / 1e3), "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,
@@ -287,7 +287,8 @@ def main():
     ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--ddp", default="fused", choices=["fused", "nccl"], help="gradient reduction for N > 1")
+    ap.add_argument("--ddp", default="fused", choices=["fused", "nccl", "fsdp"],
+                    help="N > 1: peer-memory reduction fused with the optimiser, NCCL all-reduce, or fully sharded parameters")
     ap.add_argument("--no-graph", action="store_true", help="run the step eagerly instead of replaying a CUDA graph")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
