@@ -68,7 +68,17 @@ class RelativeSelfAttention(nn.Module):
     def forward(self, x, seqs: PackedSeqs, memory: Optional[torch.Tensor] = None, residual=None, dropout_p: float = 0.0):
         """x packed [N, H].  ``memory`` [B, M, H] (padded) is prepended to keys/values (streaming / Transformer-XL)."""
         H, h, d = self.dim, self.heads, self.hd
-        qkv = seqs.pad(self.qkv(x), time_first=False).float()          # [B, T, 3H]
+        qkv_packed = self.qkv(x)
+        if ((memory is None or memory.shape[1] == 0) and qkv_packed.is_cuda and qkv_packed.dtype == torch.bfloat16 and d == 64
+                and int(seqs.max_len) <= 128):
+            # packed kernel: scores, relative shift (index arithmetic), softmax, dropout and value product per (sequence, head)
+            from ..ops.rel_attention import rel_self_attention
+            T = int(seqs.max_len)
+            r = self.pos(self._positions(T, T, x.device).to(torch.bfloat16))
+            ctx = rel_self_attention(qkv_packed, r.to(torch.bfloat16), self.r_w_bias, self.r_r_bias, seqs.cu, h, T, T - 1, self.causal,
+                                     self.attn_dropout, self.training)
+            return self.out(ctx, dropout_p=dropout_p, residual=residual)
+        qkv = seqs.pad(qkv_packed, time_first=False).float()          # [B, T, 3H]
         B, T, _ = qkv.shape
         q, k, v = qkv[..., :H], qkv[..., H:2 * H], qkv[..., 2 * H:]
         lengths = (seqs.cu[1:] - seqs.cu[:-1]).to(torch.int64)

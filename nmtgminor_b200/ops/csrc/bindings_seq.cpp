@@ -224,9 +224,43 @@ void cache_append(const Tensor& k_new, const Tensor& v_new, Tensor& k_cache, Ten
                        static_cast<int>(pos), cur_stream()));
 }
 
+std::vector<Tensor> rel_attn_fwd(const Tensor& qkv, const Tensor& r, const Tensor& u, const Tensor& w, const Tensor& cu, int64_t heads,
+                                 int64_t max_len, int64_t r_center, bool causal, double scale, double p, int64_t seed, int64_t stream_id) {
+  need(qkv, at::kBFloat16, "qkv"); need(r, at::kBFloat16, "r"); need(u, at::kFloat, "u"); need(w, at::kFloat, "w"); need(cu, at::kInt, "cu");
+  TORCH_CHECK(qkv.dim() == 2 && qkv.size(1) == 3 * heads * 64 && r.dim() == 2 && r.size(1) == heads * 64 && u.numel() == heads * 64 && w.numel() == heads * 64);
+  c10::cuda::CUDAGuard guard(qkv.device());
+  const int N = qkv.size(0), B = cu.numel() - 1;
+  Tensor out = torch::zeros({N, heads * 64}, qkv.options());
+  Tensor lse = torch::zeros({heads, N}, qkv.options().dtype(torch::kFloat));
+  ck(nmtg_rel_attn_fwd(qkv.data_ptr(), r.data_ptr(), u.data_ptr<float>(), w.data_ptr<float>(), cu.data_ptr<int>(), out.data_ptr(),
+                       lse.data_ptr<float>(), B, N, static_cast<int>(heads), static_cast<int>(max_len), static_cast<int>(r_center),
+                       static_cast<int>(r.size(0)), causal, static_cast<float>(scale), static_cast<float>(p),
+                       static_cast<unsigned long long>(seed), static_cast<unsigned long long>(stream_id), cur_stream()));
+  return {out, lse};
+}
+
+std::vector<Tensor> rel_attn_bwd(const Tensor& qkv, const Tensor& r, const Tensor& u, const Tensor& w, const Tensor& cu, const Tensor& lse,
+                                 const Tensor& dctx, int64_t heads, int64_t max_len, int64_t r_center, bool causal, double scale, double p,
+                                 int64_t seed, int64_t stream_id) {
+  need(dctx, at::kBFloat16, "dctx"); need(lse, at::kFloat, "lse");
+  c10::cuda::CUDAGuard guard(qkv.device());
+  const int N = qkv.size(0), B = cu.numel() - 1;
+  auto f32 = qkv.options().dtype(torch::kFloat);
+  Tensor dqkv = torch::zeros_like(qkv), dr = torch::zeros({r.size(0), r.size(1)}, f32), du = torch::zeros({heads, 64}, f32),
+         dw = torch::zeros({heads, 64}, f32);
+  ck(nmtg_rel_attn_bwd(qkv.data_ptr(), r.data_ptr(), u.data_ptr<float>(), w.data_ptr<float>(), cu.data_ptr<int>(), lse.data_ptr<float>(),
+                       dctx.data_ptr(), dqkv.data_ptr(), dr.data_ptr<float>(), du.data_ptr<float>(), dw.data_ptr<float>(), B, N,
+                       static_cast<int>(heads), static_cast<int>(max_len), static_cast<int>(r_center), static_cast<int>(r.size(0)), causal,
+                       static_cast<float>(scale), static_cast<float>(p), static_cast<unsigned long long>(seed),
+                       static_cast<unsigned long long>(stream_id), cur_stream()));
+  return {dqkv, dr, du, dw};
+}
+
 }  // namespace
 
 void bind_sequence_ops(pybind11::module& m) {
+  m.def("rel_attn_fwd", &rel_attn_fwd);
+  m.def("rel_attn_bwd", &rel_attn_bwd);
   m.def("joint_fwd", &joint_fwd);
   m.def("joint_bwd", &joint_bwd);
   m.def("rnnt_loss_fwd", &rnnt_loss_fwd);

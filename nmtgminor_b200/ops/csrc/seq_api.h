@@ -81,4 +81,16 @@ const char* nmtg_decode_attn(const void* q, long q_ld, const void* k_cache, cons
 // cache[r, pos, :] = new[r, :] for k and v (new rows `ld` elements apart, heads * 64 elements each).
 const char* nmtg_cache_append(const void* k_new, const void* v_new, long ld, void* k_cache, void* v_cache, int R, int heads,
                               int cap, int pos, cudaStream_t stream);
+
+// ---- relative-position (Transformer-XL) self-attention on packed sequences of at most 128 tokens ---------------
+// qkv: bf16 [N, 3 * heads * 64]; r: bf16 [L, heads * 64], row r_center - d = projected embedding of distance d;
+// u / w: fp32 [heads, 64] content / position biases; cu: int32 [B + 1]; out: bf16 [N, heads * 64]; lse: fp32 [heads, N].
+const char* nmtg_rel_attn_fwd(const void* qkv, const void* r, const float* u, const float* w, const int* cu, void* out, float* lse,
+                              int B, int N, int heads, int max_len, int r_center, int L, int causal, float scale, float p,
+                              unsigned long long seed, unsigned long long stream_id, cudaStream_t stream);
+// dqkv: bf16 [N, 3H] (rows of the sequences are overwritten); dr [L, H], du, dw [heads, 64]: fp32, ACCUMULATED into.
+const char* nmtg_rel_attn_bwd(const void* qkv, const void* r, const float* u, const float* w, const int* cu, const float* lse,
+                              const void* dctx, void* dqkv, float* dr, float* du, float* dw, int B, int N, int heads, int max_len,
+                              int r_center, int L, int causal, float scale, float p, unsigned long long seed,
+                              unsigned long long stream_id, cudaStream_t stream);
 }
