@@ -28,6 +28,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=2)
     ap.add_argument("--vocab", type=int, default=32000)
     ap.add_argument("--plain", action="store_true", help="PyTorch log-softmax / top-k instead of the fused beam kernel")
+    ap.add_argument("--no-graph", action="store_true", help="launch the decoding step kernel by kernel instead of replaying CUDA graphs")
     args = ap.parse_args()
 
     from nmtgminor_b200 import ops
@@ -50,7 +51,8 @@ def main():
         b.data = b.data.to(dev)
     model.renew_buffer(max(args.src_len, args.max_len) + 4)
     g = torch.Generator().manual_seed(1)
-    cfg = BeamConfig(beam_size=args.beam, n_best=1, max_len=args.max_len, min_len=args.max_len, fused_step=not args.plain)
+    cfg = BeamConfig(beam_size=args.beam, n_best=1, max_len=args.max_len, min_len=args.max_len, fused_step=not args.plain,
+                     cuda_graph=not args.no_graph)
 
     def one():
         src = [torch.randint(4, args.vocab, (args.src_len,), generator=g) for _ in range(args.batch)]
@@ -72,7 +74,7 @@ def main():
                       "ms_per_batch": 1e3 * dt / args.steps, "ms_per_decode_step": 1e3 * dt / args.steps / (args.max_len + 1),
                       "tokens": toks, "gpu_launches": ops.LAUNCHES[0], "status": ops.check_status(),
                       "config": {"model": "transformer-big", "batch": args.batch, "beam": args.beam, "src_len": args.src_len,
-                                 "max_len": args.max_len, "vocab": args.vocab, "fused_step": not args.plain},
+                                 "max_len": args.max_len, "vocab": args.vocab, "fused_step": not args.plain, "cuda_graph": not (args.no_graph or args.plain)},
                       "dtype": "bf16", "data": "synthetic"}))
 
 

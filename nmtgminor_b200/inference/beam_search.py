@@ -43,6 +43,7 @@ class BeamConfig:
     sampling_temperature: float = 1.0
     vocab_mask: Optional[torch.Tensor] = None   # bool [V], True = allowed
     fused_step: bool = True     # CUDA: fused log-softmax + top-k kernel when no constraint needs full log-probabilities
+    cuda_graph: bool = True     # CUDA + fused_step: replay the decoder step (embedding ... top-k) as a captured graph
 
 
 @dataclass
@@ -109,6 +110,100 @@ def _masked_topk(lprobs, cfg, step, max_rows, prefix_tokens, banned_first, token
     return top_scores, top_idx, V
 
 
+class _GraphedStep:
+    """One decoding step (embedding, decoder layers over the preallocated caches, output projection, fused
+    log-softmax + top-k) as CUDA graphs.  The cache write position and the token positions live on the device and are
+    advanced inside the graph; hypothesis reordering swaps every layer's cache with its spare buffer, so there is one
+    graph per swap parity.  The first steps (cache allocation, warm-up, steps that must not emit EOS) run eagerly
+    through the same code."""
+
+    def __init__(self, model, state, cfg, K: int, R: int):
+        dev = state.context.device
+        self.model, self.state, self.cfg, self.K = model, state, cfg, K
+        cap = state.buffers[0].get("cap", 0)
+        emb = getattr(model.decoder, "embed", None)
+        if emb is not None and hasattr(emb, "renew"):
+            before = id(getattr(emb, "pos", None))
+            emb.renew(cap + 2)
+            if id(getattr(emb, "pos", None)) != before:
+                model.__dict__.pop("_decode_pools", None)      # graphs captured against the old position table are stale
+        # Buffers and captured graphs are pooled on the model and reused by later batches of the same geometry
+        # (rows, cache capacity, padded source length): the projected encoder states of a new batch are copied into
+        # the pooled encoder-decoder caches, so the pointers recorded in the graphs stay valid.
+        cross = [b for b in state.buffers if "c_k" in b and "c_len" in b]
+        src_cap = (max(b["c_k"].shape[1] for b in cross) + 15) // 16 * 16 if cross else 0
+        n_sent = cross[0]["c_k"].shape[0] if cross else 0
+        key = (R, cap, n_sent, src_cap, len(state.buffers), str(dev), cfg.pad, cfg.eos)
+        pools = model.__dict__.setdefault("_decode_pools", {})
+        pool = pools.get(key)
+        if pool is None:
+            if len(pools) >= 4:
+                pools.pop(next(iter(pools)))
+            pool = pools[key] = {"graphs": {}, "layers": [dict() for _ in state.buffers], "eager_steps": 0,
+                                 "tok": torch.zeros(R, dtype=torch.long, device=dev), "pos_t": torch.zeros(R, dtype=torch.long, device=dev),
+                                 "scores": torch.zeros(R, dtype=torch.float32, device=dev),
+                                 "force": torch.zeros(R, dtype=torch.uint8, device=dev),
+                                 "pos_dev": torch.zeros(1, dtype=torch.int32, device=dev)}
+        self.pool = pool
+        self.tok, self.pos_t, self.scores, self.force = pool["tok"], pool["pos_t"], pool["scores"], pool["force"]
+        self.graphs = pool["graphs"]
+        self.pos_t.zero_()
+        pool["pos_dev"].zero_()
+        state.pos_dev = pool["pos_dev"]
+        for buf, keep in zip(state.buffers, pool["layers"]):
+            buf["pos_dev"] = pool["pos_dev"]
+            if "c_k" in buf and "c_len" in buf:
+                if "c_k" not in keep:
+                    H = buf["c_k"].shape[2]
+                    keep["c_k"] = torch.zeros(n_sent, src_cap, H, dtype=buf["c_k"].dtype, device=dev)
+                    keep["c_v"] = torch.zeros_like(keep["c_k"])
+                    keep["c_len"] = torch.zeros(n_sent, dtype=torch.int32, device=dev)
+                ts = buf["c_k"].shape[1]
+                keep["c_k"][:, :ts].copy_(buf["c_k"])
+                keep["c_v"][:, :ts].copy_(buf["c_v"])
+                keep["c_len"].copy_(buf["c_len"])
+                buf["c_k"], buf["c_v"], buf["c_len"] = keep["c_k"], keep["c_v"], keep["c_len"]
+            if "k" in keep:       # self-attention caches of an earlier batch: same pointers, contents are overwritten
+                buf["k"], buf["v"], buf["k_spare"], buf["v_spare"] = keep["k"], keep["v"], keep["k_spare"], keep["v_spare"]
+
+    def _body(self, ban_eos: bool):
+        from .. import ops
+        hidden = self.model.decoder.step_static(self.tok, self.pos_t, self.state)
+        logits = self.model.generator(hidden)
+        if logits.dtype not in (torch.float32, torch.bfloat16):
+            logits = logits.float()
+        ts, ti, _ = ops.ext().beam_topk(logits, self.scores, self.force, self.K, self.cfg.pad, self.cfg.eos, ban_eos)
+        self.state.pos_dev.add_(1)
+        self.pos_t.add_(1)
+        return ts, ti, logits.shape[1]
+
+    def run(self, last_tokens, scores, force_eos, ban_eos: bool, step: int):
+        self.tok.copy_(last_tokens)
+        self.scores.copy_(scores)
+        # control byte per row: 1 = only EOS may follow (length limit), 2 = EOS banned (minimum length), 0 = free
+        self.force.copy_(force_eos)
+        if ban_eos:
+            self.force.add_(2).clamp_(max=2).sub_(force_eos.to(torch.uint8))      # 0 -> 2, 1 -> 1
+        key = self.state.buffers[0]["k"].data_ptr() if "k" in self.state.buffers[0] else None
+        if key is None or self.pool["eager_steps"] < 2:
+            self.pool["eager_steps"] += 1
+            out = self._body(False)
+            for buf, keep in zip(self.state.buffers, self.pool["layers"]):
+                if "k" in buf and "k" not in keep:        # caches allocated by the first step: keep them for later batches
+                    keep.update(k=buf["k"], v=buf["v"], k_spare=buf["k_spare"], v_spare=buf["v_spare"])
+            return out
+        entry = self.graphs.get(key)
+        if entry is None:
+            g = torch.cuda.CUDAGraph()
+            torch.cuda.synchronize()
+            with torch.cuda.graph(g):
+                out = self._body(False)
+            # capture records the launches without running them: replay once for this step's result
+            self.graphs[key] = entry = (g, out)
+        entry[0].replay()
+        return entry[1]
+
+
 @torch.no_grad()
 def beam_search(model, batch, cfg: BeamConfig, prefix_tokens: Optional[torch.Tensor] = None,
                 banned_first: Optional[torch.Tensor] = None) -> List[List[Hypothesis]]:
@@ -145,10 +240,18 @@ def beam_search(model, batch, cfg: BeamConfig, prefix_tokens: Optional[torch.Ten
     fused = (device.type == "cuda" and cfg.fused_step and getattr(model, "supports_logits_step", False)
              and not cfg.sampling and cfg.no_repeat_ngram_size <= 0 and cfg.vocab_mask is None and 2 * K <= 64)
 
+    graphed = None
+    if (fused and cfg.cuda_graph and prefix_tokens is None and banned_first is None and hasattr(state, "enable_device_positions")
+            and hasattr(getattr(model, "decoder", None), "step_static")):
+        graphed = _GraphedStep(model, state, cfg, K, R)
+
     for step in range(T + 1):
         use_fused = (fused and not (prefix_tokens is not None and step < prefix_tokens.shape[1])
                      and not (banned_first is not None and step == 0))
-        if use_fused:
+        if graphed is not None:
+            top_scores, top_idx, V = graphed.run(tokens[:, step], scores.reshape(-1), step >= max_rows, step < cfg.min_len, step)
+            lprobs = None
+        elif use_fused:
             from .. import ops
             logits = model.step(tokens[:, :step + 1], state, logits_only=True)["logits"]
             V = logits.shape[1]
@@ -173,7 +276,8 @@ def beam_search(model, batch, cfg: BeamConfig, prefix_tokens: Optional[torch.Ten
         is_eos &= ~done[:, None]
 
         # ---- finalize: merge EOS candidates into the sorted table of finished hypotheses ---------
-        if is_eos.any():
+        # on a GPU the merge runs whenever EOS is possible instead of asking the device (`any()` would stall the host)
+        if step >= cfg.min_len and (device.type == "cuda" or bool(is_eos.any())):
             length = step + 1                                      # symbols after BOS, including EOS
             norm = (float(length) ** cfg.alpha) if (cfg.normalize and cfg.alpha > 0) else 1.0
             new_scores = torch.where(is_eos, top_scores / norm, torch.full_like(top_scores, float("-inf")))
@@ -210,7 +314,7 @@ def beam_search(model, batch, cfg: BeamConfig, prefix_tokens: Optional[torch.Ten
         stop_early = (best_possible <= worst_fin) if cfg.normalize else torch.ones_like(done)
         done = done | ((fin_count >= K) & stop_early) | ~torch.isfinite(scores[:, 0])
         scores = torch.where(done[:, None], torch.full_like(scores, float("-inf")), scores)
-        if bool(done.all()):
+        if (device.type != "cuda" or step % 4 == 3 or step == T) and bool(done.all()):
             break
 
     fin_scores_c, fin_tokens_c, fin_len_c, fin_pos_c = fin_scores.cpu(), fin_tokens.cpu(), fin_len.cpu(), fin_pos.cpu()

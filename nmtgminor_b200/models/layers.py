@@ -174,7 +174,7 @@ class SelfAttention(nn.Module):
         return self.out(ctx, dropout_p=dropout_p, residual=residual)
 
     # -- incremental decoding: x [B, H] is ONE new position per hypothesis --------------------------
-    def step(self, x, cache: dict):
+    def step(self, x, cache: dict, residual=None):
         H, h = self.dim, self.heads
         qkv = self.qkv(x)
         q, k, v = qkv[:, :H], qkv[:, H:2 * H], qkv[:, 2 * H:]
@@ -185,17 +185,23 @@ class SelfAttention(nn.Module):
             if "k" not in cache:
                 for name in ("k", "v", "k_spare", "v_spare"):
                     cache[name] = torch.empty(B, cache["cap"], H, dtype=qkv.dtype, device=qkv.device)
-            ops.ext().cache_append(k, v, cache["k"], cache["v"], pos)
-            ctx = ops.ext().decode_attn(q, cache["k"], cache["v"], None, pos + 1, h, (H // h) ** -0.5)
-            cache["pos"] = pos + 1
-            return self.out(ctx)
+            pos_dev = cache.get("pos_dev")
+            if pos_dev is not None:
+                # the write position lives on the device (advanced once per step by the caller): graph-replayable
+                ops.ext().cache_append(k, v, cache["k"], cache["v"], 0, pos_dev)
+                ctx = ops.ext().decode_attn(q, cache["k"], cache["v"], None, cache["cap"], h, (H // h) ** -0.5, pos_dev, 1)
+            else:
+                ops.ext().cache_append(k, v, cache["k"], cache["v"], pos)
+                ctx = ops.ext().decode_attn(q, cache["k"], cache["v"], None, pos + 1, h, (H // h) ** -0.5)
+                cache["pos"] = pos + 1
+            return self.out(ctx, residual=residual)
         if "k" not in cache:
             cache["k"], cache["v"] = k.view(B, 1, H), v.view(B, 1, H)
         else:
             cache["k"] = torch.cat([cache["k"], k.view(B, 1, H)], 1)
             cache["v"] = torch.cat([cache["v"], v.view(B, 1, H)], 1)
         ctx = _cached_attention(q, cache["k"], cache["v"], h, None)
-        return self.out(ctx)
+        return self.out(ctx, residual=residual)
 
 
 def _fused_decode(t, dim, heads) -> bool:
@@ -223,18 +229,18 @@ class CrossAttention(nn.Module):
         kv = self.kv(memory_padded.reshape(B * T, Hm)).view(B, T, 2 * self.dim)
         return kv[..., :self.dim].contiguous(), kv[..., self.dim:].contiguous()
 
-    def step(self, x, cache: dict, mem_mask):
+    def step(self, x, cache: dict, mem_mask, residual=None):
         q = self.q(x)
         ck, cv = cache["c_k"], cache["c_v"]
         if "c_len" in cache and _fused_decode(q, self.dim, self.heads):
             # one cache row per sentence, shared by its hypotheses
             ctx = ops.ext().decode_attn(q, ck, cv, cache["c_len"], ck.shape[1], self.heads, (self.dim // self.heads) ** -0.5)
-            return self.out(ctx)
+            return self.out(ctx, residual=residual)
         if ck.shape[0] != q.shape[0]:
             rep = q.shape[0] // ck.shape[0]
             ck, cv = ck.repeat_interleave(rep, 0), cv.repeat_interleave(rep, 0)
         ctx = _cached_attention(q, ck, cv, self.heads, mem_mask)
-        return self.out(ctx)
+        return self.out(ctx, residual=residual)
 
 
 def _cached_attention(q, k, v, heads, key_pad_mask):
@@ -353,11 +359,11 @@ class DecoderLayer(nn.Module):
             if not self.ignore_source:
                 x = self.cross_norm(x + self.cross_attn.step(x, cache, mem_mask))
             return self.ffn_norm(self.ffn(x, residual=x))
-        x = x + self.self_attn.step(self.self_norm(x), cache)
+        x = self.self_attn.step(self.self_norm(x), cache, residual=x)      # residual add in the GEMM epilogue
         if self.interleaved_ffn:
             x = self.mid_ffn(self.mid_norm(x), residual=x)
         if not self.ignore_source:
-            x = x + self.cross_attn.step(self.cross_norm(x), cache, mem_mask)
+            x = self.cross_attn.step(self.cross_norm(x), cache, mem_mask, residual=x)
         return self.ffn(self.ffn_norm(x), residual=x)
 
 

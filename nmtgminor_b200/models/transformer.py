@@ -96,6 +96,18 @@ class TransformerDecoder(nn.Module):
             x = layer.step(x, state.buffers[i], state.src_pad_mask)
         return self.final_norm(x)
 
+    def step_static(self, tokens, positions, state: "DecodingState"):
+        """``step`` with the positions given as a device tensor and no host-side bookkeeping, so that the whole call
+        can be captured in a CUDA graph (``state.enable_device_positions()`` must have been called)."""
+        B = tokens.shape[0]
+        cu = getattr(self, "_step_cu", None)
+        if cu is None or cu.numel() != B + 1 or cu.device != tokens.device:
+            cu = self._step_cu = torch.arange(B + 1, dtype=torch.int32, device=tokens.device)
+        x = self.embed(PackedSeqs(tokens, positions, cu, 1), 0.0)
+        for i, layer in enumerate(self.layers):
+            x = layer.step(x, state.buffers[i], state.src_pad_mask)
+        return self.final_norm(x)
+
 
 class Generator(nn.Module):
     """hidden -> vocabulary logits (weight optionally tied to the target embedding)."""
@@ -131,12 +143,26 @@ class DecodingState:
         for buf in self.buffers:
             buf["cap"] = int(cap)
 
-    def reorder(self, index):
-        rows = index.numel()
-        self.context = self.context.index_select(0, index)
-        self.src_pad_mask = self.src_pad_mask.index_select(0, index)
+    def enable_device_positions(self):
+        """Keep the write position of the self-attention caches in a device integer (``pos_dev``) that the caller
+        advances once per step, so that a decoding step can be captured in a CUDA graph and replayed."""
+        self.pos_dev = torch.zeros(1, dtype=torch.int32, device=self.context.device)
         for buf in self.buffers:
-            if "k_spare" in buf:
+            buf["pos_dev"] = self.pos_dev
+
+    def reorder(self, index, reorder_context: bool = True):
+        rows = index.numel()
+        if reorder_context:
+            self.context = self.context.index_select(0, index)
+            self.src_pad_mask = self.src_pad_mask.index_select(0, index)
+        for buf in self.buffers:
+            if "k_spare" in buf and buf.get("pos_dev") is not None:
+                H = buf["k"].shape[2]
+                ops.ext().gather_rows(buf["k"], buf["k_spare"], index, -1, buf["pos_dev"], H)
+                ops.ext().gather_rows(buf["v"], buf["v_spare"], index, -1, buf["pos_dev"], H)
+                buf["k"], buf["k_spare"] = buf["k_spare"], buf["k"]
+                buf["v"], buf["v_spare"] = buf["v_spare"], buf["v"]
+            elif "k_spare" in buf:
                 # preallocated caches: copy only the filled prefix of every row into the spare buffers and swap
                 filled = buf.get("pos", 0) * buf["k"].shape[2]
                 ops.ext().gather_rows(buf["k"], buf["k_spare"], index, filled)
@@ -145,7 +171,7 @@ class DecodingState:
                 buf["v"], buf["v_spare"] = buf["v_spare"], buf["v"]
             for k in list(buf.keys()):
                 val = buf[k]
-                if k in ("k", "v", "k_spare", "v_spare") and "k_spare" in buf:
+                if k == "pos_dev" or (k in ("k", "v", "k_spare", "v_spare") and "k_spare" in buf):
                     continue
                 # per-sentence entries (encoder-decoder caches shared by the hypotheses) keep their order
                 if torch.is_tensor(val) and val.dim() > 0 and val.shape[0] == rows:

@@ -184,7 +184,14 @@ std::vector<Tensor> beam_topk(const Tensor& logits, const Tensor& scores, const 
   return {os, oi, lse};
 }
 
-void gather_rows(const Tensor& src, Tensor& dst, const Tensor& index, int64_t copy_elems) {
+const int* dev_int(const OptTensor& t, const char* name) {
+  if (!t.has_value()) return nullptr;
+  need(*t, at::kInt, name);
+  return t->data_ptr<int>();
+}
+
+void gather_rows(const Tensor& src, Tensor& dst, const Tensor& index, int64_t copy_elems, const OptTensor& filled_dev,
+                 int64_t unit_elems) {
   TORCH_CHECK(src.is_cuda() && src.is_contiguous() && dst.is_contiguous() && src.sizes() == dst.sizes());
   need(index, at::kLong, "index");
   c10::cuda::CUDAGuard guard(src.device());
@@ -193,11 +200,12 @@ void gather_rows(const Tensor& src, Tensor& dst, const Tensor& index, int64_t co
   const long stride = src.numel() / src.size(0) * src.element_size();
   const long copy = copy_elems < 0 ? stride : copy_elems * src.element_size();
   ck(nmtg_gather_rows(src.data_ptr(), dst.data_ptr(), reinterpret_cast<const long*>(index.data_ptr<int64_t>()),
-                      static_cast<int>(rows), stride, copy, cur_stream()));
+                      static_cast<int>(rows), stride, copy, dev_int(filled_dev, "filled_dev"), unit_elems * src.element_size(),
+                      cur_stream()));
 }
 
 Tensor decode_attn(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache, const OptTensor& lengths, int64_t len,
-                   int64_t heads, double scale) {
+                   int64_t heads, double scale, const OptTensor& len_dev, int64_t len_add) {
   TORCH_CHECK(q.is_cuda() && q.scalar_type() == at::kBFloat16 && q.dim() == 2 && q.stride(1) == 1);
   need(k_cache, at::kBFloat16, "k_cache"); need(v_cache, at::kBFloat16, "v_cache");
   TORCH_CHECK(k_cache.dim() == 3 && k_cache.sizes() == v_cache.sizes() && k_cache.size(2) == heads * 64 && q.size(1) == heads * 64);
@@ -209,11 +217,12 @@ Tensor decode_attn(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache
   if (lengths.has_value()) { need(*lengths, at::kInt, "lengths"); TORCH_CHECK(lengths->numel() == k_cache.size(0)); lp = lengths->data_ptr<int>(); }
   Tensor out = torch::empty({R, heads * 64}, q.options());
   ck(nmtg_decode_attn(q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), lp, out.data_ptr(), R,
-                      static_cast<int>(heads), cap, static_cast<int>(len), kv_div, static_cast<float>(scale), cur_stream()));
+                      static_cast<int>(heads), cap, static_cast<int>(len), kv_div, static_cast<float>(scale),
+                      dev_int(len_dev, "len_dev"), static_cast<int>(len_add), cur_stream()));
   return out;
 }
 
-void cache_append(const Tensor& k_new, const Tensor& v_new, Tensor& k_cache, Tensor& v_cache, int64_t pos) {
+void cache_append(const Tensor& k_new, const Tensor& v_new, Tensor& k_cache, Tensor& v_cache, int64_t pos, const OptTensor& pos_dev) {
   TORCH_CHECK(k_new.is_cuda() && k_new.scalar_type() == at::kBFloat16 && k_new.dim() == 2 && k_new.stride(1) == 1);
   TORCH_CHECK(v_new.scalar_type() == at::kBFloat16 && v_new.stride(1) == 1 && v_new.stride(0) == k_new.stride(0) && v_new.sizes() == k_new.sizes());
   need(k_cache, at::kBFloat16, "k_cache"); need(v_cache, at::kBFloat16, "v_cache");
@@ -221,7 +230,7 @@ void cache_append(const Tensor& k_new, const Tensor& v_new, Tensor& k_cache, Ten
   c10::cuda::CUDAGuard guard(k_new.device());
   ck(nmtg_cache_append(k_new.data_ptr(), v_new.data_ptr(), k_new.stride(0), k_cache.data_ptr(), v_cache.data_ptr(),
                        static_cast<int>(k_new.size(0)), static_cast<int>(k_new.size(1) / 64), static_cast<int>(k_cache.size(1)),
-                       static_cast<int>(pos), cur_stream()));
+                       static_cast<int>(pos), dev_int(pos_dev, "pos_dev"), cur_stream()));
 }
 
 std::vector<Tensor> rel_attn_fwd(const Tensor& qkv, const Tensor& r, const Tensor& u, const Tensor& w, const Tensor& cu, int64_t heads,
@@ -272,7 +281,11 @@ void bind_sequence_ops(pybind11::module& m) {
   m.def("softmax_dropout_fwd", &softmax_dropout_fwd);
   m.def("softmax_dropout_bwd", &softmax_dropout_bwd);
   m.def("beam_topk", &beam_topk);
-  m.def("gather_rows", &gather_rows);
-  m.def("decode_attn", &decode_attn);
-  m.def("cache_append", &cache_append);
+  namespace py = pybind11;
+  m.def("gather_rows", &gather_rows, py::arg("src"), py::arg("dst"), py::arg("index"), py::arg("copy_elems"),
+        py::arg("filled_dev") = py::none(), py::arg("unit_elems") = 0);
+  m.def("decode_attn", &decode_attn, py::arg("q"), py::arg("k_cache"), py::arg("v_cache"), py::arg("lengths"), py::arg("len"),
+        py::arg("heads"), py::arg("scale"), py::arg("len_dev") = py::none(), py::arg("len_add") = 0);
+  m.def("cache_append", &cache_append, py::arg("k_new"), py::arg("v_new"), py::arg("k_cache"), py::arg("v_cache"), py::arg("pos"),
+        py::arg("pos_dev") = py::none());
 }

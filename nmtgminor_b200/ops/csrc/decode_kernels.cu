@@ -97,7 +97,10 @@ __global__ void beam_row_topk_kernel(const T* __restrict__ logits, long ld, cons
   const float lse = mx + __logf(s);
   if (threadIdx.x == 0) row_lse[r] = lse;
   const float base = scores[r] - lse;
-  const bool only_eos = force_eos && force_eos[r];
+  // per-row control byte: 1 = only EOS may follow, 2 = EOS is banned (same as ban_eos, but readable by a replayed graph)
+  const uint8_t fe = force_eos ? force_eos[r] : 0;
+  const bool only_eos = fe == 1;
+  if (fe == 2) ban_eos = 1;
   float* cv = cand_val + static_cast<long>(r) * K2;
   int* ci = cand_idx + static_cast<long>(r) * K2;
   if (only_eos || base == -INFINITY) {
@@ -222,7 +225,14 @@ __global__ void beam_merge_kernel(const float* __restrict__ cand_val, const int*
 }
 
 __global__ void gather_rows_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, const long* __restrict__ index,
-                                   int rows, long stride16, long copy16) {
+                                   int rows, long stride16, long copy16, const int* __restrict__ filled_dev, long unit16) {
+  // filled_dev (optional): number of `unit16`-sized units at the start of every row that hold data, read on the
+  // device so that a captured graph copies the right amount at every replay
+  if (filled_dev) {
+    const long want = static_cast<long>(*filled_dev) * unit16;
+    copy16 = want < stride16 ? want : stride16;
+  }
+  if (copy16 <= 0) return;
   const long total = static_cast<long>(rows) * copy16;
   for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < total;
        i += static_cast<long>(gridDim.x) * blockDim.x) {
@@ -233,7 +243,9 @@ __global__ void gather_rows_kernel(const uint4* __restrict__ src, uint4* __restr
 
 __global__ void cache_append_kernel(const __nv_bfloat16* __restrict__ k_new, const __nv_bfloat16* __restrict__ v_new, long ld,
                                     __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache, int R, int hid,
-                                    int cap, int pos) {
+                                    int cap, int pos, const int* __restrict__ pos_dev) {
+  if (pos_dev) pos = *pos_dev;
+  if (pos < 0 || pos >= cap) return;
   const int n16 = hid >> 3;
   const long total = static_cast<long>(R) * n16;
   for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < total;
@@ -250,14 +262,14 @@ __global__ void cache_append_kernel(const __nv_bfloat16* __restrict__ k_new, con
 __global__ void decode_attn_kernel(const __nv_bfloat16* __restrict__ q, long q_ld, const __nv_bfloat16* __restrict__ k_cache,
                                    const __nv_bfloat16* __restrict__ v_cache, const int* __restrict__ lengths,
                                    __nv_bfloat16* __restrict__ out, int R, int heads, int cap, int len_all, int kv_div,
-                                   float scale) {
+                                   float scale, const int* __restrict__ len_dev, int len_add) {
   extern __shared__ float probs[];
   const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
   const long item = blockIdx.x * static_cast<long>(blockDim.x >> 5) + wib;
   if (item >= static_cast<long>(R) * heads) return;
   const int r = static_cast<int>(item / heads), h = static_cast<int>(item % heads);
   const int kr = r / kv_div;
-  int len = lengths ? lengths[kr] : len_all;
+  int len = lengths ? lengths[kr] : (len_dev ? *len_dev + len_add : len_all);
   len = len < 0 ? 0 : (len > cap ? cap : len);
   float* p = probs + static_cast<long>(wib) * cap;
   const int hid = heads * 64;
@@ -358,7 +370,11 @@ const char* nmtg_beam_topk(const void* logits, long ld, int dtype, const float* 
 }
 
 const char* nmtg_gather_rows(const void* src, void* dst, const long* index, int rows, long row_stride_bytes,
-                             long copy_bytes, cudaStream_t stream) {
+                             long copy_bytes, const int* filled_dev, long unit_bytes, cudaStream_t stream) {
+  if (filled_dev) {
+    if (unit_bytes <= 0 || (unit_bytes % 16)) return "gather_rows: unit size must be a positive multiple of 16 bytes";
+    copy_bytes = row_stride_bytes;       // grid sized for the worst case; the kernel reads the real amount
+  }
   if (rows <= 0 || copy_bytes <= 0) return nullptr;
   if ((row_stride_bytes % 16) || (copy_bytes % 16) || copy_bytes > row_stride_bytes)
     return "gather_rows: sizes must be multiples of 16 bytes with copy <= stride";
@@ -367,12 +383,14 @@ const char* nmtg_gather_rows(const void* src, void* dst, const long* index, int 
   long blocks = (total + 255) / 256;
   if (blocks > 148 * 8) blocks = 148 * 8;
   gather_rows_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(static_cast<const uint4*>(src), static_cast<uint4*>(dst),
-                                                                        index, rows, row_stride_bytes / 16, copy_bytes / 16);
+                                                                        index, rows, row_stride_bytes / 16, copy_bytes / 16,
+                                                                        filled_dev, unit_bytes / 16);
   return launch_err();
 }
 
 const char* nmtg_decode_attn(const void* q, long q_ld, const void* k_cache, const void* v_cache, const int* lengths,
-                             void* out, int R, int heads, int cap, int len, int kv_div, float scale, cudaStream_t stream) {
+                             void* out, int R, int heads, int cap, int len, int kv_div, float scale, const int* len_dev,
+                             int len_add, cudaStream_t stream) {
   if (R <= 0 || heads <= 0) return nullptr;
   if (kv_div <= 0 || cap <= 0 || len > cap) return "decode_attn: bad cache geometry";
   if (q_ld % 8) return "decode_attn: query row stride must be a multiple of 8 elements";
@@ -386,14 +404,15 @@ const char* nmtg_decode_attn(const void* q, long q_ld, const void* k_cache, cons
   const long items = static_cast<long>(R) * heads;
   decode_attn_kernel<<<static_cast<unsigned>((items + warps - 1) / warps), warps * 32, smem, stream>>>(
       static_cast<const __nv_bfloat16*>(q), q_ld, static_cast<const __nv_bfloat16*>(k_cache),
-      static_cast<const __nv_bfloat16*>(v_cache), lengths, static_cast<__nv_bfloat16*>(out), R, heads, cap, len, kv_div, scale);
+      static_cast<const __nv_bfloat16*>(v_cache), lengths, static_cast<__nv_bfloat16*>(out), R, heads, cap, len, kv_div, scale,
+      len_dev, len_add);
   return launch_err();
 }
 
 const char* nmtg_cache_append(const void* k_new, const void* v_new, long ld, void* k_cache, void* v_cache, int R, int heads,
-                              int cap, int pos, cudaStream_t stream) {
+                              int cap, int pos, const int* pos_dev, cudaStream_t stream) {
   if (R <= 0) return nullptr;
-  if (pos < 0 || pos >= cap) return "cache_append: position outside the cache";
+  if (!pos_dev && (pos < 0 || pos >= cap)) return "cache_append: position outside the cache";
   if (ld % 8) return "cache_append: row stride must be a multiple of 8 elements";
   const int hid = heads * 64;
   const long total = static_cast<long>(R) * (hid / 8);
@@ -401,7 +420,7 @@ const char* nmtg_cache_append(const void* k_new, const void* v_new, long ld, voi
   if (blocks > 148 * 8) blocks = 148 * 8;
   cache_append_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
       static_cast<const __nv_bfloat16*>(k_new), static_cast<const __nv_bfloat16*>(v_new), ld,
-      static_cast<__nv_bfloat16*>(k_cache), static_cast<__nv_bfloat16*>(v_cache), R, hid, cap, pos);
+      static_cast<__nv_bfloat16*>(k_cache), static_cast<__nv_bfloat16*>(v_cache), R, hid, cap, pos, pos_dev);
   return launch_err();
 }
 

@@ -69,18 +69,23 @@ const char* nmtg_beam_topk(const void* logits, long ld, int dtype, const float* 
                            float* row_lse, float* cand_val, int* cand_idx, float* out_scores, long* out_index, int B, int K,
                            int V, int pad, int eos, int ban_eos, cudaStream_t stream);
 // dst[r, 0:copy_bytes] = src[index[r], 0:copy_bytes] for rows `row_stride_bytes` apart (both multiples of 16).
+// filled_dev (optional device int): copy filled_dev[0] * unit_bytes per row instead of copy_bytes, so that a captured
+// CUDA graph moves the right amount at every replay.
 const char* nmtg_gather_rows(const void* src, void* dst, const long* index, int rows, long row_stride_bytes,
-                             long copy_bytes, cudaStream_t stream);
+                             long copy_bytes, const int* filled_dev, long unit_bytes, cudaStream_t stream);
 
 // ---- single-query attention over a preallocated cache ------------------------------------------------------
 // q: bf16 [R, heads, 64]; k_cache / v_cache: bf16 [R / kv_div, cap, heads, 64] (kv_div > 1 shares one cache row
 // between the hypotheses of a sentence, as for encoder-decoder attention); lengths: int32 [R / kv_div] or null
 // (= all rows use `len`); out: bf16 [R, heads, 64].
+// len_dev (optional device int, used when lengths is null): the number of valid keys is len_dev[0] + len_add.
 const char* nmtg_decode_attn(const void* q, long q_ld, const void* k_cache, const void* v_cache, const int* lengths,
-                             void* out, int R, int heads, int cap, int len, int kv_div, float scale, cudaStream_t stream);
+                             void* out, int R, int heads, int cap, int len, int kv_div, float scale, const int* len_dev,
+                             int len_add, cudaStream_t stream);
 // cache[r, pos, :] = new[r, :] for k and v (new rows `ld` elements apart, heads * 64 elements each).
+// pos_dev (optional device int) overrides pos.
 const char* nmtg_cache_append(const void* k_new, const void* v_new, long ld, void* k_cache, void* v_cache, int R, int heads,
-                              int cap, int pos, cudaStream_t stream);
+                              int cap, int pos, const int* pos_dev, cudaStream_t stream);
 
 // ---- relative-position (Transformer-XL) self-attention on packed sequences of at most 128 tokens ---------------
 // qkv: bf16 [N, 3 * heads * 64]; r: bf16 [L, heads * 64], row r_center - d = projected embedding of distance d;

@@ -118,15 +118,16 @@ def test_fused_beam_search_matches_unfused_and_cpu():
     batch = collate(src, None, padded=True, packed=True, round_to=1)
     gbatch = copy.deepcopy(batch).cuda("cuda")
     res = {}
-    for name, fused in (("fused", True), ("plain", False)):
-        cfg = BeamConfig(beam_size=4, n_best=2, max_len=20, min_len=2, fused_step=fused)
+    for name, fused, graph in (("fused", True, False), ("graph", True, True), ("plain", False, False)):
+        cfg = BeamConfig(beam_size=4, n_best=2, max_len=20, min_len=2, fused_step=fused, cuda_graph=graph)
         res[name] = beam_search(gpu, gbatch, cfg)
     assert ops.check_status() == 0
-    for a, b in zip(res["fused"], res["plain"]):
-        assert [h.tokens for h in a] == [h.tokens for h in b]
-        for ha, hb in zip(a, b):
-            assert abs(ha.score - hb.score) < 5e-2
-            assert len(ha.positional_scores) == len(ha.tokens)
+    for other in ("plain", "graph"):
+        for a, b in zip(res["fused"], res[other]):
+            assert [h.tokens for h in a] == [h.tokens for h in b], other
+            for ha, hb in zip(a, b):
+                assert abs(ha.score - hb.score) < 5e-2
+                assert len(ha.positional_scores) == len(ha.tokens)
     cpu = beam_search(model, batch, BeamConfig(beam_size=4, n_best=2, max_len=20, min_len=2))
     agree = sum(a[0].tokens == c[0].tokens for a, c in zip(res["fused"], cpu))
     assert agree >= 4, "best hypotheses differ between the bf16 GPU path and the fp32 CPU path"
