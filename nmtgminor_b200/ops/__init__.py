@@ -157,10 +157,12 @@ def advance_device_seed(device=None, by: int = 1) -> None:
 # GEMM primitives
 # ---------------------------------------------------------------------------------------------------
 def gemm(a, b, out, *, a_mn_major=False, b_mn_major=False, bias=None, residual=None, aux=None, preact=None, act=0,
-         dropout_p=0.0, seed=0, stream_id=0, alpha=1.0, accumulate=False, allow_split_k=False, split_k=0, force_bn=0):
-    """out[M,N] = epilogue(alpha * A B^T) on the tcgen05 kernel (see csrc/ops_api.h: GemmDesc)."""
+         dropout_p=0.0, seed=0, stream_id=0, alpha=1.0, accumulate=False, allow_split_k=False, split_k=0, force_bn=0,
+         mask=None):
+    """out[M,N] = epilogue(alpha * A B^T) on the tcgen05 kernel (see csrc/ops_api.h: GemmDesc).  ``mask`` (int32
+    [M, ceil(N/32)]) receives the sign bits of the output, or supplies them when ``act`` is the mask-backward id 8."""
     ext().gemm(a, a_mn_major, b, b_mn_major, out, bias, residual, aux, preact, int(act), float(dropout_p), int(seed),
-               int(stream_id), float(alpha), bool(accumulate), bool(allow_split_k), int(split_k), int(force_bn))
+               int(stream_id), float(alpha), bool(accumulate), bool(allow_split_k), int(split_k), int(force_bn), mask)
     return out
 
 
@@ -264,10 +266,13 @@ class _MlpFn(torch.autograd.Function):
         M = x.shape[0]
         h = torch.empty((M, w1.shape[0]), dtype=torch.bfloat16, device=x.device)
         z = torch.empty_like(h) if act != 1 else None
-        gemm(x, w1, h, bias=b1, preact=z, act=act, dropout_p=p1, seed=seed, stream_id=sid1)
+        # ReLU: the epilogue also writes one sign bit per element (ReLU and dropout mask in one), which is all the
+        # backward pass needs from h: 1/16 of the bytes of re-reading h
+        bits = torch.empty((M, (w1.shape[0] + 31) // 32), dtype=torch.int32, device=x.device) if act == 1 else None
+        gemm(x, w1, h, bias=b1, preact=z, act=act, dropout_p=p1, seed=seed, stream_id=sid1, mask=bits)
         y = torch.empty((M, w2.shape[0]), dtype=torch.bfloat16, device=x.device)
         gemm(h, w2, y, bias=b2, residual=residual, dropout_p=p2, seed=seed, stream_id=sid2)
-        ctx.save_for_backward(x, w1, w2, h, z)
+        ctx.save_for_backward(x, w1, w2, h, z if z is not None else bits)
         ctx.cfg = (act, p1, p2, seed, sid1, sid2, residual is not None)
         ctx.g = g
         return y
@@ -284,8 +289,8 @@ class _MlpFn(torch.autograd.Function):
         if gb2 is not None:
             ext().colsum(dz2, gb2)
         dz1 = torch.empty_like(h)
-        if act == 1:   # h > 0 already encodes ReLU and the dropout mask; only the keep scale is missing
-            gemm(dz2, w2, dz1, b_mn_major=True, aux=h, act=_ACT_BWD[1], alpha=_keep_scale(p1))
+        if act == 1:   # the sign bits encode ReLU and the dropout mask; only the keep scale is missing
+            gemm(dz2, w2, dz1, b_mn_major=True, act=8, mask=z, alpha=_keep_scale(p1))
         else:
             gemm(dz2, w2, dz1, b_mn_major=True, aux=z, act=_ACT_BWD[act], dropout_p=p1, seed=seed, stream_id=sid1)
         if gw1 is not None:

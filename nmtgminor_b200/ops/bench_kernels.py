@@ -99,7 +99,13 @@ def bench_mlp_epilogues(rows):
     ms = time_ms(lambda: ops.gemm(h, w2, y, bias=b2, residual=res, dropout_p=0.1, seed=1, stream_id=2))
     rows.append({"kernel": "gemm fc2 + bias + dropout + residual", "shape": [T, H, F], "ms": ms, "tflops": fl / ms / 1e9})
     ms = time_ms(lambda: ops.gemm(y, w2, h, b_mn_major=True, aux=h, act=5, alpha=1.1))
-    rows.append({"kernel": "gemm fc2 dgrad + relu'", "shape": [T, F, H], "ms": ms, "tflops": fl / ms / 1e9})
+    rows.append({"kernel": "gemm fc2 dgrad + relu' (aux = h)", "shape": [T, F, H], "ms": ms, "tflops": fl / ms / 1e9})
+    bits = torch.empty(T, F // 32, dtype=torch.int32, device="cuda")
+    ms = time_ms(lambda: ops.gemm(x, w1, h, bias=b1, act=1, dropout_p=0.1, seed=1, stream_id=1, mask=bits))
+    rows.append({"kernel": "gemm fc1 + bias + relu + dropout + sign bits", "shape": [T, F, H], "ms": ms, "tflops": fl / ms / 1e9})
+    dz = torch.empty(T, F, device="cuda", dtype=torch.bfloat16)
+    ms = time_ms(lambda: ops.gemm(y, w2, dz, b_mn_major=True, act=8, mask=bits, alpha=1.1))
+    rows.append({"kernel": "gemm fc2 dgrad + relu' (sign bits)", "shape": [T, F, H], "ms": ms, "tflops": fl / ms / 1e9})
 
 
 def bench_elementwise(rows):

@@ -25,6 +25,8 @@ struct GemmArgs {
   int out_fp32;
   int accumulate;          // fp32 output only: out += result
   __nv_bfloat16* preact;   // optional [M, ld_out]: value after bias, before activation
+  uint32_t* mask;          // optional [M, ld_mask] sign bits of the output (written, or read by kActMaskBwd)
+  int ld_mask;
   int act;
   float dropout_p;
   unsigned long long seed, stream_id;
@@ -48,7 +50,9 @@ __device__ __forceinline__ void gemm_epilogue_chunk(const GemmArgs& p, const Dro
     const bool full_cols = (col0 + 32 <= p.N);
     // global operands of the epilogue are requested BEFORE the TMEM load so their latency overlaps it
     uint4 aux_v[4], res_v[4];
-    const bool aux_vec = row_ok && full_cols && p.act >= kActReluBwd && (p.ld_aux & 7) == 0;
+    const bool aux_vec = row_ok && full_cols && p.act >= kActReluBwd && p.act != kActMaskBwd && (p.ld_aux & 7) == 0;
+    uint32_t mask_word = 0;
+    if (p.act == kActMaskBwd && row_ok) mask_word = p.mask[static_cast<size_t>(row) * p.ld_mask + (col0 >> 5)];
     const bool res_vec = row_ok && full_cols && p.residual != nullptr && (p.ld_res & 7) == 0;
     if (aux_vec) {
       const uint4* ap4 = reinterpret_cast<const uint4*>(p.aux + static_cast<size_t>(row) * p.ld_aux + col0);
@@ -103,7 +107,10 @@ __device__ __forceinline__ void gemm_epilogue_chunk(const GemmArgs& p, const Dro
       }
     }
     // activation (forward) or activation-gradient (backward; aux holds h or z)
-    if (p.act >= kActReluBwd) {
+    if (p.act == kActMaskBwd) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = ((mask_word >> j) & 1u) ? v[j] : 0.f;
+    } else if (p.act >= kActReluBwd) {
       const __nv_bfloat16* ap = p.aux + static_cast<size_t>(row) * p.ld_aux + col0;
       float av[32];
       if (aux_vec) {
@@ -150,6 +157,12 @@ __device__ __forceinline__ void gemm_epilogue_chunk(const GemmArgs& p, const Dro
 #pragma unroll
         for (int j = 0; j < 4; ++j) v[g * 4 + j] = rng.keep(w, j) ? v[g * 4 + j] * rng.scale : 0.f;
       }
+    }
+    if (p.mask && p.act != kActMaskBwd) {
+      uint32_t bits = 0;
+#pragma unroll
+      for (int j = 0; j < 32; ++j) bits |= (v[j] > 0.f ? 1u : 0u) << j;
+      p.mask[static_cast<size_t>(row) * p.ld_mask + (col0 >> 5)] = bits;
     }
     if (p.residual) {
       const __nv_bfloat16* rp = p.residual + static_cast<size_t>(row) * p.ld_res + col0;

@@ -338,6 +338,8 @@ const char* nmtg_gemm_bf16(const GemmDesc* d, cudaStream_t stream) {
   a.aux = reinterpret_cast<const __nv_bfloat16*>(d->aux); a.ld_aux = d->ld_aux;
   a.out = d->out; a.ld_out = d->ld_out; a.out_fp32 = d->out_fp32; a.accumulate = d->accumulate;
   a.preact = reinterpret_cast<__nv_bfloat16*>(d->preact);
+  a.mask = reinterpret_cast<uint32_t*>(d->mask); a.ld_mask = d->ld_mask;
+  if (d->act == kActMaskBwd && !d->mask) return "gemm: the mask-backward epilogue needs a mask";
   a.act = d->act; a.dropout_p = d->dropout_p; a.seed = d->seed; a.stream_id = d->stream_id; a.seed_dev = d->seed_dev;
   a.status = d->status;
 

@@ -12,6 +12,7 @@ enum NmtgAct : int {
   kActReluBwd = 5,  // out = acc * 1[aux > 0]           (aux = ReLU output, after dropout)
   kActGeluBwd = 6,  // out = acc * gelu'(aux)           (aux = pre-activation)
   kActSiluBwd = 7,  // out = acc * silu'(aux)
+  kActMaskBwd = 8,  // out = acc * bit(mask)              (mask = sign bits written by a forward epilogue)
 };
 
 struct GemmDesc {
@@ -28,6 +29,9 @@ struct GemmDesc {
   int ld_aux;
   void* out; int ld_out; int out_fp32; int accumulate;
   void* preact;           // optional bf16 [M, ld_out]
+  void* mask;             // optional uint32 [M, ld_mask]: bit j of word c = (output[row, 32 c + j] > 0); written by forward
+                          // epilogues (before the residual), read by kActMaskBwd
+  int ld_mask;
   int act;
   float dropout_p; unsigned long long seed, stream_id;
   const unsigned long long* seed_dev;  // optional device word added to seed (lets graph replays draw new masks)

@@ -150,3 +150,27 @@ def test_gemm_decode_shapes_bias_and_transposed_weight(M, N, K):
         torch.cuda.synchronize()
         _status_ok()
         assert _rel_err(out2, want) < 1e-2
+
+
+def test_gemm_sign_bit_mask_round_trip():
+    """Forward epilogue writes one sign bit per output; the mask-backward epilogue applies it to another product."""
+    torch.manual_seed(0)
+    M, N, K = 300, 1000, 256
+    a = torch.randn(M, K, device=DEV).bfloat16()
+    w = torch.randn(N, K, device=DEV).bfloat16()
+    out = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+    bits = torch.zeros(M, (N + 31) // 32, dtype=torch.int32, device=DEV)
+    ops.gemm(a, w, out, act=1, mask=bits)
+    torch.cuda.synchronize()
+    positive = out.float() > 0
+    cols = torch.arange(N, device=DEV)
+    got = ((bits[:, cols // 32] >> (cols % 32)) & 1).bool()
+    assert torch.equal(got, positive)
+    g = torch.randn(M, 64, device=DEV).bfloat16()
+    w2 = torch.randn(N, 64, device=DEV).bfloat16()
+    d = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+    ops.gemm(g, w2, d, act=8, mask=bits, alpha=1.25)
+    torch.cuda.synchronize()
+    _status_ok()
+    want = (g.float() @ w2.float().t()) * 1.25 * positive
+    assert _rel_err(d, want) < 1e-2
