@@ -29,7 +29,9 @@ struct PairSmem {
   static constexpr int kBBytes = (BN / 2) * BK * 2;      // this CTA's half of the B tile
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kStages = (BN == 256) ? 6 : 8;
-  static constexpr int kBarOffset = kStages * kStageBytes;
+  static constexpr int kStagingOffset = kStages * kStageBytes;          // 8 epilogue warps x [32 rows x 128 B]
+  static constexpr int kStagingBytes = kEpilogueWarps * 32 * 128;
+  static constexpr int kBarOffset = kStagingOffset + kStagingBytes;
   static constexpr int kTotal = kBarOffset + 512 + 1024;
 };
 
@@ -70,7 +72,8 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar_cluster_addr) {
 
 template <int BN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
-gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const GemmArgs p) {
+gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                 const __grid_constant__ CUtensorMap tmap_out, const GemmArgs p) {
   using S = PairSmem<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -206,15 +209,42 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       tc_fence_after_sync();
       const int row = m0 + q * 32 + lane;
       const bool row_ok = row < p.M;
+      if (p.tma_store) {
+        // 64-column groups: both 32-column halves go to this warp's staging tile, one TMA store per group writes
+        // full 128-byte lines (rows / columns outside the matrix are clipped by the copy engine)
+        uint8_t* stage = smem + S::kStagingOffset + (warp - 2) * (32 * 128);
 #pragma unroll 1
-      for (int c = chunk_par; c < BN / 32; c += kEpilogueWarps / 4) {
-        const int col0 = n0 + c * 32;
-        if (col0 >= p.N) break;
-        gemm_epilogue_chunk(p, rng, do_drop, row, row_ok, col0, tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN + c * 32);
+        for (int g = chunk_par; g < BN / 64; g += kEpilogueWarps / 4) {
+          const int col0 = n0 + g * 64;
+          if (col0 >= p.N || p.ablate == 2) break;
+          if (lane == 0) tma_store_wait_read();        // the previous store of this warp has drained its staging tile
+          __syncwarp();
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            if (col0 + half * 32 < p.N)
+              gemm_epilogue_chunk(p, rng, do_drop, row, row_ok, col0 + half * 32,
+                                  tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN + g * 64 + half * 32,
+                                  stage + lane * 128, half, lane);
+          }
+          fence_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_2d(&tmap_out, stage, col0, m0 + q * 32);
+            tma_store_commit();
+          }
+        }
+      } else {
+#pragma unroll 1
+        for (int c = chunk_par; c < BN / 32; c += kEpilogueWarps / 4) {
+          const int col0 = n0 + c * 32;
+          if (col0 >= p.N || p.ablate == 2) break;
+          gemm_epilogue_chunk(p, rng, do_drop, row, row_ok, col0, tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN + c * 32);
+        }
       }
       tc_fence_before_sync();
       mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty[acc]), 0));
     }
+    if (p.tma_store && lane == 0) tma_store_wait_all();   // staging must outlive the copies that read it
   }
 
   // ------------------------------- teardown --------------------------------------------------------
@@ -232,19 +262,22 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 }
 
 template <int BN>
-static const char* launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& args, int grid, cudaStream_t stream) {
+static const char* launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmArgs& args, int grid,
+                               cudaStream_t stream) {
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, PairSmem<BN>::kTotal);
     if (e != cudaSuccess) return cudaGetErrorString(e);
     configured = true;
   }
-  gemm_pair_kernel<BN><<<grid, kPairThreads, PairSmem<BN>::kTotal, stream>>>(ta, tb, args);
+  gemm_pair_kernel<BN><<<grid, kPairThreads, PairSmem<BN>::kTotal, stream>>>(ta, tb, tc, args);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? nullptr : cudaGetErrorString(e);
 }
 
 // CTA-pair path; BN = 256 or 128; a.split_k splits must all be non-empty.  Returns nullptr on success.
+int g_pair_tma_store = 1;     // set to 0 (gemm variant 20) to force per-thread global stores, for A/B measurements
+
 const char* launch_gemm_pair(const GemmDesc* d, const GemmArgs& a, int bn, cudaStream_t stream) {
   CUtensorMap ta, tb;
   bool ok;
@@ -254,11 +287,19 @@ const char* launch_gemm_pair(const GemmDesc* d, const GemmArgs& a, int bn, cudaS
   if (!d->b_mn_major) ok = cached_tmap(&tb, d->b, d->N, d->K, d->ldb, bn / 2, BK);
   else ok = cached_tmap(&tb, d->b, d->K, d->N, d->ldb, BK, 64);
   if (!ok) return "gemm: cuTensorMapEncodeTiled failed for B";
+  // bf16 results leave through shared memory + TMA stores when nothing else has to be written per element
+  GemmArgs args = a;
+  CUtensorMap tc = ta;
+  args.tma_store = 0;
+  if (!d->out_fp32 && a.split_k == 1 && d->preact == nullptr && (d->ld_out % 8) == 0 && g_pair_tma_store) {
+    if (cached_tmap(&tc, d->out, d->M, d->N, d->ld_out, 32, 64)) args.tma_store = 1;
+    else tc = ta;
+  }
   const long tiles = static_cast<long>((d->M + 2 * BM - 1) / (2 * BM)) * ((d->N + bn - 1) / bn) * a.split_k;
   const int max_clusters = num_sms() / 2;
   const int clusters = static_cast<int>(tiles < max_clusters ? tiles : max_clusters);
-  if (bn == 256) return launch_pair<256>(ta, tb, a, clusters * 2, stream);
-  return launch_pair<128>(ta, tb, a, clusters * 2, stream);
+  if (bn == 256) return launch_pair<256>(ta, tb, tc, args, clusters * 2, stream);
+  return launch_pair<128>(ta, tb, tc, args, clusters * 2, stream);
 }
 
 }  // namespace b200

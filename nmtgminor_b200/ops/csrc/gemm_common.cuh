@@ -32,6 +32,8 @@ struct GemmArgs {
   unsigned long long seed, stream_id;
   const unsigned long long* seed_dev;
   int* status;
+  int tma_store;           // bf16 output leaves through shared memory and TMA stores (CTA-pair kernel)
+  int ablate;              // profiling aid: 1 = read the accumulator but skip arithmetic and stores, 2 = skip the epilogue body
 };
 
 __device__ __forceinline__ float gelu_f(float x) { return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f)); }
@@ -45,8 +47,13 @@ __device__ __forceinline__ float sigmoid_f(float x) { return 1.0f / (1.0f + __ex
 // One thread = one accumulator row; processes columns [col0, col0 + 32) read from TMEM address `taddr`:
 // alpha, bias, optional pre-activation store, activation or activation gradient, dropout, residual, store
 // (bf16, fp32, fp32 accumulate, or fp32 red.add for split-K).  Warp-collective (contains a tcgen05.ld).
+// `stage_row` (optional): instead of writing bf16 results to global memory, place the 64-byte row fragment in a
+// shared-memory staging row laid out for a 128-byte-swizzled TMA store (logical 16-byte chunk j of row r sits at
+// chunk j ^ (r & 7)); `stage_half` selects the left / right 32 columns of the 64-column staging tile.
 __device__ __forceinline__ void gemm_epilogue_chunk(const GemmArgs& p, const DropRng& rng, const bool do_drop, const int row,
-                                                    const bool row_ok, const int col0, const uint32_t taddr) {
+                                                    const bool row_ok, const int col0, const uint32_t taddr,
+                                                    uint8_t* stage_row = nullptr, const int stage_half = 0,
+                                                    const int stage_r = 0) {
     const bool full_cols = (col0 + 32 <= p.N);
     // global operands of the epilogue are requested BEFORE the TMEM load so their latency overlaps it
     uint4 aux_v[4], res_v[4];
@@ -67,7 +74,7 @@ __device__ __forceinline__ void gemm_epilogue_chunk(const GemmArgs& p, const Dro
     uint32_t r[32];
     tmem_ld32(taddr, r);
     tmem_ld_wait();
-    if (!row_ok) return;
+    if (!row_ok || p.ablate == 1) return;
     float v[32];
 #pragma unroll
     for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
@@ -209,6 +216,15 @@ __device__ __forceinline__ void gemm_epilogue_chunk(const GemmArgs& p, const Dro
       } else {
         for (int j = 0; j < 32; ++j)
           if (col0 + j < p.N) op[j] = p.accumulate ? op[j] + v[j] : v[j];
+      }
+    } else if (stage_row != nullptr) {
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        uint4 o;
+        __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) o2[j] = __floats2bfloat162_rn(v[g * 8 + 2 * j], v[g * 8 + 2 * j + 1]);
+        *reinterpret_cast<uint4*>(stage_row + (((stage_half * 4 + g) ^ (stage_r & 7)) << 4)) = o;
       }
     } else {
       __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<size_t>(row) * p.ld_out + col0;

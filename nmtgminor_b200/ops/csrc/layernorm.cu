@@ -94,7 +94,7 @@ ln_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restri
 }
 
 template <int VPL>
-__global__ void __launch_bounds__(kLnWarps * 32)
+__global__ void __launch_bounds__(kLnWarps * 32, VPL <= 4 ? 4 : 1)
 ln_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
               const float* __restrict__ mean, const float* __restrict__ rstd,
               const __nv_bfloat16* __restrict__ gamma, const __nv_bfloat16* __restrict__ dres,
@@ -257,12 +257,20 @@ const char* nmtg_layernorm_bwd(const void* dy, const void* x, const float* mean,
   if (rows <= 0) return nullptr;
   if (hidden % 8) return "layernorm: hidden size must be a multiple of 8";
   int grid = (rows + kLnWarps - 1) / kLnWarps;
-  const int cap = num_sms() * 4;
-  if (grid > cap) grid = cap;
   const size_t smem = kLnWarps * 2 * static_cast<size_t>(hidden) * sizeof(float);
   return dispatch_vpl(hidden, [&](auto vpl) -> const char* {
     auto kern = ln_bwd_kernel<decltype(vpl)::value>;
     if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    // exactly one wave of resident CTAs: a partial second wave would leave most SMs idle while it runs
+    static int resident[16] = {0};
+    int& occ = resident[decltype(vpl)::value];
+    if (occ == 0) {
+      int n = 0;
+      if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, kLnWarps * 32, smem) != cudaSuccess || n < 1) n = 1;
+      occ = n;
+    }
+    const int cap = num_sms() * occ;
+    if (grid > cap) grid = cap;
     kern<<<grid, kLnWarps * 32, smem, stream>>>(
         reinterpret_cast<const __nv_bfloat16*>(dy), reinterpret_cast<const __nv_bfloat16*>(x), mean, rstd,
         reinterpret_cast<const __nv_bfloat16*>(gamma), reinterpret_cast<const __nv_bfloat16*>(dres),
