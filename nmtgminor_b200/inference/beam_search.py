@@ -41,6 +41,7 @@ class BeamConfig:
     pad: int = 0
     sampling: bool = False
     sampling_temperature: float = 1.0
+    diversity_rate: float = 0.0  # > 0: sibling-rank penalty (the k-th best continuation of a hypothesis loses k * rate)
     vocab_mask: Optional[torch.Tensor] = None   # bool [V], True = allowed
     fused_step: bool = True     # CUDA: fused log-softmax + top-k kernel when no constraint needs full log-probabilities
     cuda_graph: bool = True     # CUDA + fused_step: replay the decoder step (embedding ... top-k) as a captured graph
@@ -96,6 +97,11 @@ def _masked_topk(lprobs, cfg, step, max_rows, prefix_tokens, banned_first, token
     if banned_first is not None and step == 0:
         lprobs[:, banned_first] = float("-inf")
     lprobs = _block_ngrams(tokens, step, lprobs, cfg.no_repeat_ngram_size, cfg.pad)
+    if cfg.diversity_rate > 0 and step > 0:
+        # diverse beam search: only the best 2K continuations of a hypothesis can be selected, so ranking those suffices
+        top_v, top_i = lprobs.topk(min(2 * K, V), dim=1)
+        penalty = torch.arange(top_v.shape[1], device=device, dtype=lprobs.dtype) * cfg.diversity_rate
+        lprobs = lprobs.scatter(1, top_i, top_v - penalty[None, :])
 
     cand = scores[:, :, None] + lprobs.view(B, K, V)            # [B, K, V]
     flat = cand.view(B, K * V)
@@ -238,7 +244,8 @@ def beam_search(model, batch, cfg: BeamConfig, prefix_tokens: Optional[torch.Ten
         state.set_cache_capacity(T + 2)
     # fused step: log-softmax, masks and the per-sentence top-2K in two kernels, no [R, V] log-probabilities
     fused = (device.type == "cuda" and cfg.fused_step and getattr(model, "supports_logits_step", False)
-             and not cfg.sampling and cfg.no_repeat_ngram_size <= 0 and cfg.vocab_mask is None and 2 * K <= 64)
+             and not cfg.sampling and cfg.no_repeat_ngram_size <= 0 and cfg.vocab_mask is None and 2 * K <= 64
+             and cfg.diversity_rate <= 0)
 
     graphed = None
     if (fused and cfg.cuda_graph and prefix_tokens is None and banned_first is None and hasattr(state, "enable_device_positions")

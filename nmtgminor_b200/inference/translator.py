@@ -125,20 +125,45 @@ class Translator:
                               pad=self.pad, sampling=getattr(opt, "sampling", False))
 
     # ------------------------------------------------------------------------------------------
-    def build_data(self, src_sents: List[List[str]], tgt_sents: Optional[List[List[str]]] = None):
-        src = [self.src_dict.convert_to_idx(s, C.UNK_WORD) for s in src_sents]
+    def _lang_ids(self, n: int):
+        """Language-id tensors for multilingual models from ``-src_lang`` / ``-tgt_lang`` and the checkpoint's table."""
+        langs = self.dicts.get("langs") if isinstance(self.dicts, dict) else None
+        if not langs:
+            return None, None
+        pick = lambda name: torch.full((n,), int(langs.get(name, 0)), dtype=torch.long)
+        return pick(getattr(self.opt, "src_lang", "src")), pick(getattr(self.opt, "tgt_lang", "tgt"))
+
+    def build_data(self, src_sents, tgt_sents: Optional[List[List[str]]] = None):
+        """``src_sents``: token lists (text models) or ``[frames, features]`` tensors (audio models: ``-encoder_type
+        audio`` / ``-asr_format``; a leading channel of ones marks real frames, as in training batches)."""
+        audio = len(src_sents) > 0 and torch.is_tensor(src_sents[0])
+        if audio:
+            src = [f.float().view(f.shape[0], -1) for f in src_sents]     # collate adds the real-frame marker channel
+        else:
+            src = [self.src_dict.convert_to_idx(s, C.UNK_WORD) for s in src_sents]
         tgt = None
         if tgt_sents:
             tgt = [self.tgt_dict.convert_to_idx(t, C.UNK_WORD, C.BOS_WORD, C.EOS_WORD) for t in tgt_sents]
-        return collate(src, tgt, padded=True, packed=True, round_to=1)
+        sl, tl = self._lang_ids(len(src))
+        return collate(src, tgt, src_lang=sl, tgt_lang=tl, src_type="audio" if audio else "text", padded=True, packed=True, round_to=1)
 
-    def translate_batch(self, batch, prefix_tokens=None) -> List[List[Hypothesis]]:
+    def translate_batch(self, batch, prefix_tokens=None, banned_first=None) -> List[List[Hypothesis]]:
         if self.cuda:
             batch = batch.cuda(self.device)
-        return beam_search(self.model, batch, self.cfg, prefix_tokens)
+        return beam_search(self.model, batch, self.cfg, prefix_tokens, banned_first)
 
-    def translate(self, src_sents: List[List[str]], tgt_sents: Optional[List[List[str]]] = None, prefix: Optional[List[List[str]]] = None):
+    def translate(self, src_sents, tgt_sents: Optional[List[List[str]]] = None, prefix: Optional[List[List[str]]] = None,
+                  anti_prefix: Optional[List[str]] = None):
+        """``prefix``: tokens every hypothesis of sentence i must start with (``-prefix_string`` gives one prefix for
+        all sentences); ``anti_prefix``: tokens that may not open a hypothesis (``-anti_prefix_string``)."""
         batch = self.build_data(src_sents, tgt_sents)
+        if prefix is None and getattr(self.opt, "prefix_string", None):
+            prefix = [str(self.opt.prefix_string).split()] * len(src_sents)
+        if anti_prefix is None and getattr(self.opt, "anti_prefix_string", None):
+            anti_prefix = str(self.opt.anti_prefix_string).split()
+        banned_first = None
+        if anti_prefix:
+            banned_first = self.tgt_dict.convert_to_idx(anti_prefix, C.UNK_WORD).to(self.device)
         prefix_tokens = None
         if prefix:
             rows = [self.tgt_dict.convert_to_idx(p, C.UNK_WORD) for p in prefix]
@@ -154,7 +179,7 @@ class Translator:
             gold_score = sums.float().cpu().tolist()
             gold_words = batch.tgt_size
             allgold = per_tok.float().cpu().t().tolist()
-        hyps = self.translate_batch(batch, prefix_tokens)
+        hyps = self.translate_batch(batch, prefix_tokens, banned_first)
         pred_batch, pred_ids, pred_score, pred_pos, pred_len = [], [], [], [], []
         for h in hyps:
             ids = [x.tokens for x in h]

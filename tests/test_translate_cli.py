@@ -1,0 +1,58 @@
+"""translate.py end to end on CPU: text input with prefix / anti-prefix / diverse search, and audio (scp) input."""
+import json
+import os
+import sys
+
+import numpy as np
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+from nmtgminor_b200.data import audio
+from nmtgminor_b200.data.synthetic import synthetic_dict
+from nmtgminor_b200.models.factory import build_model
+from nmtgminor_b200.options import default_options
+from nmtgminor_b200.train.checkpoint import save_checkpoint
+import translate as translate_cli
+
+COMMON = ["-model_size", "32", "-layers", "1", "-n_heads", "2", "-inner_size", "64", "-ffn_activation", "relu"]
+
+
+def test_text_translation_with_prefix_antiprefix_and_diverse_search(tmp_path):
+    torch.manual_seed(0)
+    d = synthetic_dict(40)
+    opt = default_options(COMMON + ["-tie_weights", "-join_embedding"])
+    ck = str(tmp_path / "m.pt")
+    save_checkpoint(ck, build_model(opt, {"src": d, "tgt": d}), {"src": d, "tgt": d}, opt, 1.0)
+    src = tmp_path / "src.txt"
+    src.write_text("w1 w2 w3\nw4 w5\nw6\n")
+    out = tmp_path / "out.txt"
+    base = ["-model", ck, "-src", str(src), "-output", str(out), "-gpu", "-1", "-beam_size", "3", "-max_sent_length", "6", "-batch_size", "2"]
+    translate_cli.main(base)
+    plain = out.read_text().splitlines()
+    assert len(plain) == 3
+    translate_cli.main(base + ["-prefix_string", "w7 w8"])
+    assert all(l.startswith("w7 w8") for l in out.read_text().splitlines())
+    first = plain[0].split()[0]
+    translate_cli.main(base + ["-anti_prefix_string", first])
+    assert out.read_text().splitlines()[0].split()[:1] != [first]
+    translate_cli.main(base + ["-diverse_beamsearch", "-n_best", "3"])
+    assert len(out.read_text().splitlines()) == 3
+
+
+def test_audio_translation_from_scp(tmp_path):
+    torch.manual_seed(0)
+    d = synthetic_dict(40)
+    opt = default_options(["-model", "speech_transformer", "-input_size", "40"] + COMMON)
+    ck = str(tmp_path / "asr.pt")
+    save_checkpoint(ck, build_model(opt, {"tgt": d}), {"tgt": d}, opt, 1.0)
+    ark, scp = tmp_path / "feats.ark", tmp_path / "feats.scp"
+    with open(ark, "wb") as fh, open(scp, "w") as sf:
+        for i, n in enumerate((50, 37)):
+            off = audio.write_ark_matrix(fh, "utt%d" % i, np.random.RandomState(i).randn(n, 40).astype(np.float32))
+            sf.write("utt%d %s:%d\n" % (i, ark, off))
+    out = tmp_path / "hyp.txt"
+    translate_cli.main(["-model", ck, "-src", str(scp), "-output", str(out), "-gpu", "-1", "-beam_size", "2", "-max_sent_length", "5",
+                        "-encoder_type", "audio", "-asr_format", "scp", "-batch_size", "2"])
+    assert len(out.read_text().splitlines()) == 2

@@ -32,10 +32,45 @@ def get_sentence_from_tokens(tokens, input_type="word"):
     return "".join(tokens) if input_type == "char" else " ".join(tokens)
 
 
+class _Null:
+    def __enter__(self):
+        return None
+
+    def __exit__(self, *a):
+        return False
+
+
+def _audio_inputs(opt):
+    """Yields ``[frames, features]`` tensors for ``-encoder_type audio``."""
+    from nmtgminor_b200.data import audio
+    concat = int(str(getattr(opt, "concat", "1")).split("|")[0] or 1)
+    if getattr(opt, "asr_format", "scp") == "scp":
+        for _key, (path, offset) in audio.read_scp(opt.src).items():
+            feats = torch.from_numpy(audio.read_ark_matrix(path, offset)).float()
+            yield audio.stack_frames(feats, concat) if concat > 1 else feats
+    else:
+        with open(opt.src, encoding="utf-8") as fh:
+            for line in fh:
+                parts = line.split()
+                if not parts:
+                    continue
+                path = parts[-1] if len(parts) <= 2 else parts[1]
+                start = float(parts[2]) if len(parts) > 3 else 0.0
+                end = float(parts[3]) if len(parts) > 3 else 0.0
+                wav, _sr = audio.read_wav(path, start, end)
+                yield torch.from_numpy(wav).float().view(-1, 1)
+
+
 def main(argv=None):
     opt = make_translate_parser().parse_args(argv)
     opt.cuda = opt.gpu > -1 and torch.cuda.is_available()
-    translator = Translator(opt)
+    if getattr(opt, "streaming", False) or getattr(opt, "global_search", False):
+        from nmtgminor_b200.inference.scoring import StreamTranslator
+        translator = StreamTranslator(opt, context_tokens=getattr(opt, "max_memory_size", 0) and 8)
+    else:
+        translator = Translator(opt)
+    if getattr(opt, "diverse_beamsearch", False):
+        translator.cfg.diversity_rate = 0.5
     out = open(opt.output, "w", encoding="utf-8") if opt.output and opt.output != "stdout" else sys.stdout
     tgt_f = open(opt.tgt, encoding="utf-8") if getattr(opt, "tgt", None) else None
     pred_score_total = pred_words_total = gold_score_total = gold_words_total = 0.0
@@ -61,7 +96,8 @@ def main(argv=None):
             if tgt_batch:
                 gold_score_total += gold_score[b]
             if opt.verbose:
-                print("SENT %d: %s" % (count, " ".join(src_batch[b])))
+                if not torch.is_tensor(src_batch[b]):
+                    print("SENT %d: %s" % (count, " ".join(src_batch[b])))
                 print("PRED %d: %s" % (count, best))
                 print("PRED SCORE: %.4f" % pred_score[b][0])
                 if tgt_batch:
@@ -73,8 +109,21 @@ def main(argv=None):
         out.flush()
         src_batch, tgt_batch = [], []
 
-    with open(opt.src, encoding="utf-8") as src_f:
-        for line in src_f:
+    if getattr(opt, "encoder_type", "text") == "audio":
+        # audio input: a Kaldi scp of feature matrices (``-asr_format scp``) or a list of wav paths (``wav``), one
+        # utterance per line, in the order of the optional reference file
+        for feats in _audio_inputs(opt):
+            src_batch.append(feats)
+            if tgt_f is not None:
+                tgt_batch.append(tgt_f.readline().split())
+            if len(src_batch) >= opt.batch_size:
+                flush()
+        flush()
+        src_lines = []
+    else:
+        src_lines = open(opt.src, encoding="utf-8")
+    with src_lines if hasattr(src_lines, "close") else _Null() as src_f:
+        for line in (src_f or []):
             toks = line.split()
             if getattr(opt, "input_type", "word") == "char":
                 toks = list(line.strip())
