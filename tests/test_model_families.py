@@ -97,3 +97,25 @@ def test_language_model_and_classifier(dicts):
     out = clf(batch)
     out["loss"].backward()
     assert out["logits"].shape == (batch.size, 120)
+
+
+def test_state_space_encoder_and_backend_selection(dicts):
+    from nmtgminor_b200.models.mssm import TiedStateSpaceModel
+    torch.manual_seed(0)
+    ssm = TiedStateSpaceModel(8, heads=2, state=4, channels=1)
+    k = ssm.kernel(16)
+    assert k.shape == (1, 16, 8) and torch.isfinite(k).all()
+    # causal convolution: an impulse at t = 3 produces the kernel shifted by 3 (plus the skip term)
+    u = torch.zeros(1, 16, 8)
+    u[0, 3] = 1.0
+    y = ssm(u)
+    assert torch.allclose(y[0, :3], torch.zeros(3, 8), atol=1e-4)
+    assert torch.allclose(y[0, 4:10], k[0, 1:7], atol=1e-4)
+    for name, kind, feats in (("s4", "feats", 40), ("w2v-bert", "feats", 40), ("hubert_base", "wav", 1)):
+        argv = ["-model", "wav2vec2_transformer", "-enc_pretrained_model", name, "-input_size", str(feats)] + COMMON
+        model = build_model(default_options(argv), dicts)
+        batch = (synthetic_audio_batch(2, 120, "feats", 40, 80, n_feats=feats) if kind == "feats"
+                 else synthetic_audio_batch(2, 120, "wav", 3000, 5000))
+        out = model(batch)
+        assert torch.isfinite(out["loss"]).all(), name
+        out["loss"].backward()
