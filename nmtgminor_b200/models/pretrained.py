@@ -149,6 +149,47 @@ def build_pretrained_decoder(opt, vocab: int, family: Optional[str] = None, kv_d
         pad_idx=_cfg(cfg, ["pad_token_id"], getattr(opt, "pad_idx", 1)), layerdrop=getattr(opt, "death_rate", 0.0), kv_dim=kv_dim)
 
 
+def ctc_compress(context, seqs: PackedSeqs, logits, mode: str = "avg"):
+    """Collapse consecutive frames of a sequence that share the CTC arg-max symbol into one state.
+
+    ``mode``: ``avg`` (mean of the run), ``weighted`` (mean weighted by the probability of the predicted symbol) or
+    ``softmax`` (weights = softmax of those probabilities within the run).  Returns the compressed packed states and
+    their ``PackedSeqs`` (reference: onmt/models/speech_recognizer/ctc_compressor.py:11,
+    onmt/models/speech_recognizer/wav2vec2.py:993-1017)."""
+    N = context.shape[0]
+    cu = seqs.cu.long()
+    n_valid = int(cu[-1])
+    pred = logits.argmax(-1)
+    prob = torch.softmax(logits.float(), -1).gather(1, pred[:, None]).squeeze(1)
+    idx = torch.arange(N, device=context.device)
+    start = torch.ones(N, dtype=torch.bool, device=context.device)
+    start[1:] = pred[1:] != pred[:-1]
+    start[cu[:-1].clamp(max=N - 1)] = True                                  # a run never crosses a sentence boundary
+    valid = idx < n_valid
+    start &= valid
+    seg = torch.cumsum(start.long(), 0) - 1                                 # run index of every frame
+    n_seg = int(start.sum())
+    seg = seg.clamp(min=0)
+    if mode == "weighted":
+        w = prob
+    elif mode == "softmax":
+        e = torch.exp(prob - prob.max())
+        w = e
+    else:
+        w = torch.ones_like(prob)
+    w = w * valid
+    num = torch.zeros(n_seg, context.shape[1], dtype=torch.float32, device=context.device).index_add_(0, seg, context.float() * w[:, None])
+    den = torch.zeros(n_seg, dtype=torch.float32, device=context.device).index_add_(0, seg, w)
+    out = (num / den.clamp_min(1e-9)[:, None]).to(context.dtype)
+    sent = torch.bucketize(idx, cu[1:].contiguous(), right=True).clamp(max=cu.numel() - 2)
+    per_sent = torch.zeros(cu.numel() - 1, dtype=torch.long, device=context.device).index_add_(0, sent[start], torch.ones(n_seg, dtype=torch.long, device=context.device))
+    new_cu = torch.zeros_like(seqs.cu)
+    new_cu[1:] = torch.cumsum(per_sent, 0).to(seqs.cu.dtype)
+    positions = torch.arange(n_seg, device=context.device) - new_cu.long()[:-1].repeat_interleave(per_sent)
+    new_seqs = PackedSeqs(torch.zeros(n_seg, dtype=torch.long, device=context.device), positions, new_cu, int(per_sent.max()) if n_seg else 1)
+    return out, new_seqs
+
+
 class SpeechToTextModel(Seq2SeqBase):
     """Audio encoder + text decoder with optional CTC head on the encoder states (``-ctc_loss``)."""
 
@@ -167,11 +208,21 @@ class SpeechToTextModel(Seq2SeqBase):
             self.ctc_linear = nn.Linear(encoder.dim, vocab)
 
     def encode(self, batch):
-        return self.encoder(batch.get("source"))
+        context, src = self.encoder(batch.get("source"))
+        self._uncompressed = None
+        mode = str(getattr(self.opt, "ctc_compress", "None") or "None").lower()
+        if mode != "none" and self.ctc_weight > 0:
+            # merge runs of frames with the same CTC prediction before the decoder attends to them
+            self._uncompressed = (context, src)
+            logits = self.ctc_linear(context.float())
+            context, src = ctc_compress(context, src, logits, mode)
+        return context, src
 
     def auxiliary_losses(self, batch, context, src, out):
         if self.ctc_weight <= 0 or not self.training:
             return None
+        if getattr(self, "_uncompressed", None) is not None:
+            context, src = self._uncompressed              # the CTC loss is defined on the frame-level states
         logits = src.pad(self.ctc_linear(context.float()))                   # [T, B, V]
         lengths = (src.cu[1:] - src.cu[:-1]).to(torch.int64)
         targets = batch.get("target_output").t()                              # [B, U]

@@ -51,9 +51,18 @@ class TransformerEncoder(nn.Module):
             for i in range(n)])
         self.final_norm = LayerNorm(opt.model_size)
         _apply_regularisation_options(self, opt)
+        self.reversible = None
+        if getattr(opt, "src_reversible", False):
+            # activations are reconstructed in backward instead of stored (reference: onmt/reversible_models)
+            from .reversible import ReversibleStack
+            self.layers = nn.ModuleList()
+            self.reversible = ReversibleStack(n, opt.model_size, opt.n_heads, opt.inner_size, opt.dropout, opt.attn_dropout,
+                                              opt.ffn_activation)
 
     def forward(self, src: PackedSeqs):
         x = self.embed(src, self.emb_dropout)
+        if self.reversible is not None:
+            return self.reversible(x, src)
         for i, layer in enumerate(self.layers):
             if self.training and i < self.checkpointing:
                 x = checkpointed(layer, x, src)
@@ -76,9 +85,19 @@ class TransformerDecoder(nn.Module):
             for i in range(opt.layers)])
         self.final_norm = LayerNorm(opt.model_size)
         _apply_regularisation_options(self, opt)
+        self.reversible = None
+        if getattr(opt, "tgt_reversible", False) and not ignore_source:
+            from .reversible import ReversibleStack
+            self.n_layers = opt.layers
+            self.layers = nn.ModuleList()
+            self.reversible = ReversibleStack(opt.layers, opt.model_size, opt.n_heads, opt.inner_size, opt.dropout,
+                                              opt.attn_dropout, opt.ffn_activation, causal=True, cross=True)
+            self.layers = self.reversible.layers      # decoding state set-up walks the layers (cross-attention caches)
 
     def forward(self, tgt: PackedSeqs, memory, src: PackedSeqs):
         x = self.embed(tgt, self.emb_dropout)
+        if self.reversible is not None:
+            return self.reversible(x, tgt, memory, src)
         for i, layer in enumerate(self.layers):
             if self.training and i < self.checkpointing:
                 x = checkpointed(layer, x, tgt, memory, src)
@@ -92,6 +111,8 @@ class TransformerDecoder(nn.Module):
         seqs = PackedSeqs(tokens, torch.full_like(tokens, position), torch.arange(B + 1, dtype=torch.int32, device=tokens.device), 1)
         self.embed.renew(position + 1)
         x = self.embed(seqs, 0.0)
+        if self.reversible is not None:
+            return self.reversible.step(x, state.buffers, state.src_pad_mask)
         for i, layer in enumerate(self.layers):
             x = layer.step(x, state.buffers[i], state.src_pad_mask)
         return self.final_norm(x)
@@ -104,6 +125,8 @@ class TransformerDecoder(nn.Module):
         if cu is None or cu.numel() != B + 1 or cu.device != tokens.device:
             cu = self._step_cu = torch.arange(B + 1, dtype=torch.int32, device=tokens.device)
         x = self.embed(PackedSeqs(tokens, positions, cu, 1), 0.0)
+        if self.reversible is not None:
+            return self.reversible.step(x, state.buffers, state.src_pad_mask)
         for i, layer in enumerate(self.layers):
             x = layer.step(x, state.buffers[i], state.src_pad_mask)
         return self.final_norm(x)

@@ -27,6 +27,11 @@ NVCC_FLAGS = [
 ]
 
 
+def _extra_flags():
+    """``NMTG_DEBUG_BOUNDS=1`` compiles the index checks that record status 6 (bad argument) instead of clamping."""
+    return ["-DNMTG_DEBUG_BOUNDS"] if os.environ.get("NMTG_DEBUG_BOUNDS", "0") not in ("", "0") else []
+
+
 def _nvcc() -> str:
     cand = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
     if not os.path.exists(cand):
@@ -78,7 +83,7 @@ def build(verbose: bool = False, force: bool = False) -> str:
         src, obj = os.path.join(CSRC, f), os.path.join(OBJ_DIR, f + ".o")
         objs.append(obj)
         if force or _stale(src, obj, hdr):
-            jobs.append([nvcc] + NVCC_FLAGS + inc + ["-c", src, "-o", obj])
+            jobs.append([nvcc] + NVCC_FLAGS + _extra_flags() + inc + ["-c", src, "-o", obj])
     abi = int(getattr(torch._C, "_GLIBCXX_USE_CXX11_ABI", True))
     host_inc = ["-I" + p for p in ce.include_paths("cuda")] + ["-I" + sysconfig.get_paths()["include"]]
     for f in cpp:

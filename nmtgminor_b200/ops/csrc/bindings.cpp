@@ -396,6 +396,7 @@ void clear_status(int64_t device) { status_tensor(static_cast<int>(device)).zero
 }  // namespace
 
 void bind_sequence_ops(pybind11::module& m);   // bindings_seq.cpp
+extern "C" long nmtg_bounds_violations();
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   bind_sequence_ops(m);
@@ -427,6 +428,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("fsdp_gather", &fsdp_gather);
   m.def("fsdp_step", &fsdp_step);
   m.def("peer_wait_row", &peer_wait_row);
+  m.def("bounds_violations", []() { return static_cast<int64_t>(nmtg_bounds_violations()); });
   m.def("read_status", &read_status);
   m.def("clear_status", &clear_status);
 }

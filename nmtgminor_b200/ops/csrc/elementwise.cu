@@ -16,6 +16,15 @@ namespace b200 {
 
 int num_sms();
 
+// Debug build (-DNMTG_DEBUG_BOUNDS): out-of-range indices are counted (and still clamped, never trapped) so that a
+// test run can assert that no kernel ever saw one; the release build only clamps.
+#ifdef NMTG_DEBUG_BOUNDS
+__device__ unsigned int g_bounds_violations = 0;
+#define NMTG_BOUNDS_HIT() atomicAdd(&g_bounds_violations, 1u)
+#else
+#define NMTG_BOUNDS_HIT() ((void)0)
+#endif
+
 __device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
   const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
 #pragma unroll
@@ -68,10 +77,10 @@ __global__ void embed_fwd_kernel(const int64_t* __restrict__ tokens, const int64
   const int n16 = hidden >> 4;
   for (int row = blockIdx.x; row < rows; row += gridDim.x) {
     long tok = tokens[row];
-    if (tok < 0 || tok >= vocab) tok = 0;
+    if (tok < 0 || tok >= vocab) { NMTG_BOUNDS_HIT(); tok = 0; }
     long pos = positions ? positions[row] : 0;
     if (pos < 0) pos = 0;
-    if (pos >= max_pos) pos = max_pos - 1;
+    if (pos >= max_pos) { NMTG_BOUNDS_HIT(); pos = max_pos - 1; }
     const uint4* tr = reinterpret_cast<const uint4*>(table + static_cast<size_t>(tok) * hidden);
     const uint4* pr = pos_table ? reinterpret_cast<const uint4*>(pos_table + static_cast<size_t>(pos) * hidden) : nullptr;
     uint4* orow = reinterpret_cast<uint4*>(out + static_cast<size_t>(row) * hidden);
@@ -269,4 +278,15 @@ const char* nmtg_colsum(const void* x, float* out, int rows, int cols, long ld, 
   grid.y = gy;
   colsum_kernel<<<grid, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(x), out, rows, cols, ld);
   return last_err();
+}
+
+// Number of out-of-range indices seen by the kernels of this file since load; -1 when the checks are compiled out.
+extern "C" long nmtg_bounds_violations() {
+#ifdef NMTG_DEBUG_BOUNDS
+  unsigned int v = 0;
+  if (cudaMemcpyFromSymbol(&v, b200::g_bounds_violations, sizeof(v)) != cudaSuccess) return -2;
+  return static_cast<long>(v);
+#else
+  return -1;
+#endif
 }

@@ -130,10 +130,17 @@ class TrainEngine:
 
     # ---------------------------------------------------------------------------------------------
     def _forward_backward(self, batch):
+        from ..utils.tracing import nvtx_range
+        trace = bool(getattr(self.opt, "trace_nvtx", False))
+        if trace and not getattr(self, "_nvtx_hooks", None):
+            from ..utils.tracing import install_nvtx_hooks
+            self._nvtx_hooks = install_nvtx_hooks(self.model)
         ops.reset_stream_counter()
         # the loss gradient is written pre-scaled by the kernel (scale 1): no [tokens, V] rescale pass in backward
-        out = self.model(batch, grad_scale=1.0)
-        out["loss"].backward()
+        with nvtx_range("forward", trace):
+            out = self.model(batch, grad_scale=1.0)
+        with nvtx_range("backward", trace):
+            out["loss"].backward()
         if not self.optim.fused:
             pass
         else:
@@ -146,9 +153,11 @@ class TrainEngine:
         n0 = ops.LAUNCHES[0]
         loss, correct = self._forward_backward(batch)
         if update:
-            if self.reducer is not None:
-                self.reducer(self.store.grad)
-            self.optim.step(self.grad_scale)
+            from ..utils.tracing import nvtx_range
+            with nvtx_range("reduce+optimizer", bool(getattr(self.opt, "trace_nvtx", False))):
+                if self.reducer is not None:
+                    self.reducer(self.store.grad)
+                self.optim.step(self.grad_scale)
             if not self.optim.fused:
                 self.optim.zero_grad()
         self.kernel_launches_per_step = ops.LAUNCHES[0] - n0

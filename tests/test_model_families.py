@@ -119,3 +119,22 @@ def test_state_space_encoder_and_backend_selection(dicts):
         out = model(batch)
         assert torch.isfinite(out["loss"]).all(), name
         out["loss"].backward()
+
+
+def test_ctc_compression_merges_runs(dicts, tmp_path):
+    from nmtgminor_b200.models.layers import PackedSeqs
+    from nmtgminor_b200.models.pretrained import ctc_compress
+    ctx = torch.arange(7, dtype=torch.float32)[:, None].repeat(1, 2)
+    cu = torch.tensor([0, 4, 7], dtype=torch.int32)
+    seqs = PackedSeqs(torch.zeros(7, dtype=torch.long), torch.arange(7), cu, 4)
+    logits = torch.full((7, 3), -5.0)
+    for i, sym in enumerate([1, 1, 2, 2, 2, 0, 0]):      # runs: [0,1] [2,3] | [4] [5,6]  (the boundary splits the run of 2s)
+        logits[i, sym] = 5.0
+    out, new = ctc_compress(ctx, seqs, logits, "avg")
+    assert new.cu.tolist() == [0, 2, 4]
+    assert torch.allclose(out[:, 0], torch.tensor([0.5, 2.5, 4.0, 5.5]))
+    enc = _cfg(tmp_path, "enc2.json", encoder_embed_dim=64, encoder_layers=1, encoder_attention_heads=2, encoder_ffn_embed_dim=128)
+    model = build_model(default_options(["-model", "wav2vec2_transformer", "-enc_config_file", enc, "-ctc_loss", "0.3", "-ctc_compress", "avg"] + COMMON), dicts)
+    out = model(synthetic_audio_batch(2, 120, "wav", 3000, 5000))
+    out["loss"].backward()
+    assert torch.isfinite(out["loss"]) and out["src"].cu[-1] <= out["context_packed"].shape[0]
