@@ -130,15 +130,17 @@ def bench_elementwise(rows):
     n = 209_087_744 // 4 * 4
     master, grad, m, v = (torch.zeros(n, device="cuda") for _ in range(4))
     work = torch.zeros(n, device="cuda", dtype=torch.bfloat16)
+    master.normal_(0, 0.02), grad.normal_(0, 1e-3), m.normal_(0, 1e-4), v.uniform_(0, 1e-6)
     hyper = torch.zeros(16)
-    hyper[0], hyper[1], hyper[2], hyper[3], hyper[5], hyper[6], hyper[7] = 1e-3, 0.9, 0.997, 1e-9, 0.1, 0.003, 1.0
+    hyper[0], hyper[1], hyper[2], hyper[3], hyper[4], hyper[5], hyper[6], hyper[7], hyper[8] = 1e-3, 0.9, 0.997, 1e-9, 0.01, 0.1, 0.003, 1.0, 5.0
+    hyper.view(torch.int32)[9:11] = 1          # decoupled weight decay, clear the gradients: what the training step runs
     hyper = hyper.cuda()
     sq = torch.zeros(1, device="cuda")
     bad = torch.zeros(1, device="cuda", dtype=torch.int32)
     ms = time_ms(lambda: e.sq_norm(grad, sq, bad), iters=5)
     rows.append({"kernel": "grad sq-norm (209M)", "shape": [n], "ms": ms, "gbs": n * 4 / ms / 1e6})
     ms = time_ms(lambda: e.adamw_flat(master, work, grad, m, v, hyper, sq, bad), iters=5)
-    rows.append({"kernel": "adamw flat (209M)", "shape": [n], "ms": ms, "gbs": n * (4 * 4 + 4 * 4 + 2) / ms / 1e6})
+    rows.append({"kernel": "adamw flat (209M)", "shape": [n], "ms": ms, "gbs": n * (4 * 4 + 4 * 4 + 2) / ms / 1e6})   # reads p, g, m, v; writes p, g, m, v, bf16 p
 
 
 def bench_attention(rows):

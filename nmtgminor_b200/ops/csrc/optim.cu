@@ -66,8 +66,10 @@ __global__ void adamw_kernel(float* __restrict__ master, __nv_bfloat16* __restri
   for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < n4;
        i += static_cast<long>(gridDim.x) * blockDim.x) {
     float4 g4 = reinterpret_cast<float4*>(grad)[i];
-    if (h.zero_grad) reinterpret_cast<float4*>(grad)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (skip) continue;
+    if (skip) {
+      if (h.zero_grad) __stcs(reinterpret_cast<float4*>(grad) + i, make_float4(0.f, 0.f, 0.f, 0.f));
+      continue;
+    }
     float4 p4 = reinterpret_cast<float4*>(master)[i];
     float4 m4 = reinterpret_cast<float4*>(m)[i];
     float4 v4 = reinterpret_cast<float4*>(v)[i];
@@ -95,6 +97,9 @@ __global__ void adamw_kernel(float* __restrict__ master, __nv_bfloat16* __restri
       o.y = *reinterpret_cast<uint32_t*>(&hi);
       reinterpret_cast<uint2*>(work)[i] = o;
     }
+    // Clearing the gradient comes last and bypasses the usual write policy: a store to the line that was just
+    // loaded, issued before the other loads of the iteration, made the whole kernel four times slower.
+    if (h.zero_grad) __stcs(reinterpret_cast<float4*>(grad) + i, make_float4(0.f, 0.f, 0.f, 0.f));
   }
 }
 
