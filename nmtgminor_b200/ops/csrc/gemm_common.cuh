@@ -192,7 +192,8 @@ __device__ __forceinline__ void gemm_epilogue_chunk(const GemmArgs& p, const Dro
     }
     if (p.out_fp32) {
       float* op = reinterpret_cast<float*>(p.out) + static_cast<size_t>(row) * p.ld_out + col0;
-      if (p.split_k > 1) {
+      // accumulation into an existing fp32 buffer goes through the L2 reduction unit as well: no read round trip
+      if (p.split_k > 1 || p.accumulate) {
         if (full_cols) {
 #pragma unroll
           for (int g = 0; g < 8; ++g)
