@@ -1,2 +1,3 @@
 from .blocks import *  # noqa: F401,F403
 from .builders import *  # noqa: F401,F403
+from .unity import *  # noqa: F401,F403

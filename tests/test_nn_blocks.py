@@ -64,3 +64,21 @@ def test_llama_grouped_kv_and_generation():
     conv = N.convert_llama_state_dict(sd)
     keys = set(model.state_dict().keys())
     assert set(conv.keys()) <= keys, set(conv.keys()) - keys
+
+
+def test_unity_adaptor_shortens_sequences_and_masks():
+    torch.manual_seed(0)
+    adaptor = N.UnitYEncoderAdaptor(32, num_layers=1, num_heads=4, kernel_size=8, stride=8, dropout_p=0.0).eval()
+    x = torch.randn(2, 64, 32)
+    pad = torch.zeros(2, 64, dtype=torch.bool)
+    pad[1, 40:] = True
+    y, mask = adaptor(x, pad)
+    assert y.shape == (2, 9, 32) and mask.shape == (2, 9)
+    assert (~mask).sum(1).tolist() == [9, 6]
+
+    class Inner(torch.nn.Module):
+        def forward(self, feats, padding_mask=None):
+            return feats, padding_mask
+    enc = N.SeamlessSpeechEncoder(Inner(), adaptor)
+    z, m2 = enc(x, pad)
+    assert torch.allclose(z, y) and torch.equal(m2, mask)
