@@ -175,6 +175,13 @@ def empty_rows(rows: int, cols: int, device, dtype=torch.bfloat16):
     return t if padded == cols else t[:, :cols]
 
 
+def _track(x):
+    """Input of a fused autograd node whose only gradients go to parameters (written straight into ``main_grad``):
+    autograd records a node only if some tensor input requires grad, so an input that does not (frozen embeddings in
+    front of trainable adapters, say) is replaced by a detached leaf that does."""
+    return x if x.requires_grad else x.detach().requires_grad_(True)
+
+
 def _keep_scale(p: float) -> float:
     """Dropout is byte-granular on the device: keep probability (256 - round(256 p)) / 256."""
     if p <= 0.0:
@@ -249,7 +256,7 @@ def linear(x, weight, bias=None, act="none", dropout_p=0.0, residual=None, train
             y = empty_rows(x.shape[0], weight.shape[0], x.device)
             return gemm(xin, weight.work, y, bias=b, residual=residual, act=act_id, dropout_p=p, seed=_Rng.seed,
                         stream_id=sid)
-        return _LinearFn.apply(xin, weight.work, b, residual, gw, gb, act_id, p, _Rng.seed, sid, need_dx)
+        return _LinearFn.apply(_track(xin), weight.work, b, residual, gw, gb, act_id, p, _Rng.seed, sid, need_dx)
     return ref.linear(x, weight, bias, act_id, p, residual)
 
 
@@ -314,7 +321,7 @@ def mlp(x, w1, b1, w2, b2, act="relu", dropout_p=0.0, out_dropout_p=0.0, residua
         if torch.is_grad_enabled():
             g = tuple(getattr(t, "main_grad", None) if (t is not None and t.requires_grad) else None
                       for t in (w1, b1, w2, b2))
-            return _MlpFn.apply(xin, w1.work, b1.work if b1 is not None else None, w2.work,
+            return _MlpFn.apply(_track(xin), w1.work, b1.work if b1 is not None else None, w2.work,
                                 b2.work if b2 is not None else None, residual, g, act_id, p1, p2, _Rng.seed, sid1, sid2)
         h = torch.empty((x.shape[0], w1.shape[0]), dtype=torch.bfloat16, device=x.device)
         gemm(xin, w1.work, h, bias=b1.work if b1 is not None else None, act=act_id)
@@ -351,7 +358,7 @@ def layer_norm(x, weight, bias, eps=1e-5):
         if x2.dtype != torch.bfloat16:
             x2 = x2.to(torch.bfloat16)
         if torch.is_grad_enabled() and (x.requires_grad or weight.requires_grad):
-            y = _LayerNormFn.apply(x2, weight.work, bias.work, getattr(weight, "main_grad", None),
+            y = _LayerNormFn.apply(_track(x2), weight.work, bias.work, getattr(weight, "main_grad", None),
                                    getattr(bias, "main_grad", None), eps)
         else:
             y = ext().layernorm_fwd(x2, weight.work, bias.work, eps)[0]
@@ -656,10 +663,10 @@ def generator_cross_entropy(h, weight, bias, labels, smoothing=0.0, pad_idx=0, g
         gb = bias.main_grad if (bias is not None and bias.requires_grad) else None
         hin = (h if h.dtype == torch.bfloat16 else h.to(torch.bfloat16)).contiguous()
         if torch.is_grad_enabled() and chunk_rows > 0 and grad_scale is not None and h.shape[0] > chunk_rows:
-            return _GeneratorXentChunkedFn.apply(hin, weight.work, b, gw, gb, labels.contiguous(), float(smoothing),
+            return _GeneratorXentChunkedFn.apply(_track(hin), weight.work, b, gw, gb, labels.contiguous(), float(smoothing),
                                                  int(pad_idx), grad_scale, int(chunk_rows))
         if torch.is_grad_enabled():
-            return _GeneratorXentFn.apply(hin, weight.work, b, gw, gb, labels.contiguous(), float(smoothing), int(pad_idx),
+            return _GeneratorXentFn.apply(_track(hin), weight.work, b, gw, gb, labels.contiguous(), float(smoothing), int(pad_idx),
                                           grad_scale)
         logits = empty_rows(h.shape[0], weight.shape[0], h.device)
         gemm(hin, weight.work, logits, bias=b)

@@ -24,7 +24,13 @@ EXTRA_TRAIN_FLAGS = [
     ("watchdog_timeout", "float", 0.0, {}),      # seconds without a heartbeat before a rank is declared dead
     ("trace_nvtx", "flag", False, {}),           # NVTX ranges around layers / buckets
     ("generator_chunk_rows", "int", 0, {}),      # output projection + loss this many rows at a time (logits stay in L2)
-    ("fused_conv", "flag", False, {}),           # speech front-end convolutions through the tcgen05 GEMM (implicit im2col)
+    ("fused_conv", "flag", False, {}),
+    ("ema_decay", "float", 0.999, {}),           # decay of the parameter average kept with -ema
+    ("lora_rank", "int", 0, {}),                 # finetune_whisper.py: rank of the LoRA adapters (0 = full fine-tuning)
+    ("lora_alpha", "float", 16.0, {}),
+    ("teacher", "str", "", {}),                  # finetune_whisper.py: checkpoint of a teacher model for distillation
+    ("distill_alpha", "float", 0.5, {}),
+    ("distill_temperature", "float", 2.0, {}),           # speech front-end convolutions through the tcgen05 GEMM (implicit im2col)
 ]
 
 

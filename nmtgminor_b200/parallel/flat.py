@@ -38,6 +38,9 @@ class FlatParameterStore:
                  allocator=None,   # callable(numel, dtype) -> tensor, or {'master' | 'grad' | 'work': callable}
                  pad_total_to: int = ALIGN):
         params = _unique_params(p for p in module.parameters())
+        # trainable parameters first: the optimiser (and its state) then covers one contiguous prefix of the flat space,
+        # which is what makes adapter fine-tuning (a few trainable matrices in a frozen model) cheap
+        params = [p for p in params if p.requires_grad] + [p for p in params if not p.requires_grad]
         self.params = params
         self.device = torch.device(device) if device is not None else (params[0].device if params else torch.device("cpu"))
         self.offsets: List[int] = []
@@ -46,6 +49,12 @@ class FlatParameterStore:
             self.offsets.append(off)
             off += (p.numel() + ALIGN - 1) // ALIGN * ALIGN
         self.total = (off + pad_total_to - 1) // pad_total_to * pad_total_to if off else 0
+        n_train = 0
+        for p, o in zip(params, self.offsets):
+            if p.requires_grad:
+                n_train = o + (p.numel() + ALIGN - 1) // ALIGN * ALIGN
+        # length of the trainable prefix (whole buffer when nothing is frozen, so padding stays included)
+        self.trainable_total = self.total if all(p.requires_grad for p in params) else n_train
         default = lambda n, dt: torch.zeros(n, dtype=dt, device=self.device)
         allocs = allocator if isinstance(allocator, dict) else {"master": allocator, "grad": allocator, "work": allocator}
         pick = lambda name: allocs.get(name) or default

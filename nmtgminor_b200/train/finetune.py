@@ -174,3 +174,38 @@ class BatchEnsembleLinear(nn.Module):
             member = torch.arange(x.shape[0], device=x.device) * self.members // max(x.shape[0], 1)
         y = self.shared((x * self.r[member].to(x.dtype))) * self.s[member].to(x.dtype)
         return y if self.bias is None else y + self.bias[member].to(y.dtype)
+
+
+class DistillationWrapper(nn.Module):
+    """Presents ``student`` to the training engine with the distillation objective as its loss: the engine calls
+    ``wrapper(batch, grad_scale=...)`` and back-propagates ``out["loss"]``.  The teacher is held outside the module
+    tree, so it is neither trained nor saved."""
+
+    def __init__(self, student: nn.Module, teacher: nn.Module, alpha: float = 0.5, temperature: float = 2.0):
+        super().__init__()
+        self.student = student
+        self._teacher = [teacher.eval()]
+        self.alpha, self.temperature = alpha, temperature
+        for p in teacher.parameters():
+            p.requires_grad_(False)
+
+    def __getattr__(self, name):
+        try:
+            return super().__getattr__(name)
+        except AttributeError:
+            return getattr(super().__getattr__("student"), name)
+
+    def forward(self, batch, grad_scale=None, **kw):
+        if not self.training:
+            return self.student(batch, **kw)
+        with torch.no_grad():
+            t_out = self._teacher[0](batch, return_logits=True, compute_loss=False)
+        s_out = self.student(batch, return_logits=True, compute_loss=False)
+        tgt = s_out["tgt"]
+        unpad = lambda o: ops.reference.unpad_packed(o["logprobs"].transpose(0, 1), tgt.cu, tgt.tokens.shape[0])
+        s_logits, labels = unpad(s_out), s_out["target"]
+        loss = distillation_loss(s_logits, unpad(t_out), labels, getattr(self.student, "pad_idx", 0), self.alpha, self.temperature)
+        keep = labels != getattr(self.student, "pad_idx", 0)
+        correct = (s_logits.argmax(-1)[keep] == labels[keep]).sum().float().reshape(1)
+        s_out.update(loss=loss.reshape(1), correct=correct)
+        return s_out

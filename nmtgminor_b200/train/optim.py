@@ -78,8 +78,10 @@ class Optim:
         self.fused = fused
         if fused:
             dev = store.master.device
-            self.exp_avg = torch.zeros_like(store.master)
-            self.exp_avg_sq = torch.zeros_like(store.master)
+            # moments only for the trainable prefix of the flat space (frozen parameters sit behind it)
+            self.n_update = int(getattr(store, "trainable_total", store.total))
+            self.exp_avg = torch.zeros(self.n_update, dtype=torch.float32, device=dev)
+            self.exp_avg_sq = torch.zeros(self.n_update, dtype=torch.float32, device=dev)
             self.grad_sq = torch.zeros(1, dtype=torch.float32, device=dev)
             self.nonfinite = torch.zeros(1, dtype=torch.int32, device=dev)
             self.hyper = torch.zeros(16, dtype=torch.float32, device=dev)
@@ -141,8 +143,14 @@ class Optim:
         self.grad_sq.zero_()
         self.nonfinite.zero_()
         e = ops.ext()
-        e.sq_norm(s.grad, self.grad_sq, self.nonfinite)
-        e.adamw_flat(s.master, s.work, s.grad, self.exp_avg, self.exp_avg_sq, self.hyper, self.grad_sq, self.nonfinite)
+        n = self.n_update
+        if n == s.total:
+            e.sq_norm(s.grad, self.grad_sq, self.nonfinite)
+            e.adamw_flat(s.master, s.work, s.grad, self.exp_avg, self.exp_avg_sq, self.hyper, self.grad_sq, self.nonfinite)
+        elif n > 0:
+            e.sq_norm(s.grad[:n], self.grad_sq, self.nonfinite)
+            e.adamw_flat(s.master[:n], s.work[:n] if s.work is not None else None, s.grad[:n], self.exp_avg, self.exp_avg_sq,
+                         self.hyper, self.grad_sq, self.nonfinite)
 
     def step(self, grad_scale: float = 1.0, scaler=None):
         """One update.  ``grad_scale`` multiplies the raw gradients (1 / (loss scale * normaliser))."""

@@ -81,6 +81,16 @@ class Trainer:
             except Exception as exc:  # noqa: BLE001
                 self.log("[WARN] optimiser state not restored: %r" % (exc,))
         self.start_time = time.time()
+        # -ema: exponential moving average of the parameters (one vector op on the flat master buffer per update),
+        # used for validation and for the saved checkpoints
+        self.ema = None
+        if getattr(opt, "ema", False) and getattr(self.optim, "distributed", None) is None:
+            from .finetune import FlatEMA
+            self.ema = FlatEMA(self.engine.store, decay=getattr(opt, "ema_decay", 0.999) or 0.999)
+        lora_rank = int(getattr(opt, "lora_rank", 0) or 0)
+        if lora_rank > 0:
+            raise RuntimeError("apply LoRA before building the trainer: use nmtgminor_b200.train.finetune.apply_lora on the model "
+                               "returned by build_model (see finetune_whisper.py)")
         self.watchdog = None
         if getattr(opt, "watchdog_timeout", 0) and self.world_size > 1:
             from ..utils.watchdog import Heartbeat
@@ -111,6 +121,8 @@ class Trainer:
         """Validation loss per target token and token accuracy over all ranks."""
         if data is None:
             return float("nan"), 0.0
+        if self.ema is not None:
+            self.ema.swap_in()
         self.model.eval()
         tot_loss = tot_words = tot_correct = 0.0
         for ds in (data if _is_list(data) else [data]):
@@ -122,6 +134,8 @@ class Trainer:
                 tot_correct += float(correct)
                 tot_words += batch.tgt_size
         tot_loss, tot_words, tot_correct = self._all_reduce_scalars([tot_loss, tot_words, tot_correct])
+        if self.ema is not None:
+            self.ema.swap_out()
         self.model.train()
         return tot_loss / max(tot_words, 1.0), tot_correct / max(tot_words, 1.0)
 
@@ -131,6 +145,16 @@ class Trainer:
             dist_opt.gather_master()      # collective: every rank refreshes its full fp32 copy from the slice owners
         if not self.is_main():
             return None
+        opt = self.opt
+        if self.ema is not None:
+            self.ema.swap_in()
+        try:
+            return self._save_checkpoint_file(epoch, valid_ppl, itr, accuracy)
+        finally:
+            if self.ema is not None:
+                self.ema.swap_out()
+
+    def _save_checkpoint_file(self, epoch: float, valid_ppl: float, itr=None, accuracy: float = 0.0):
         opt = self.opt
         metric = getattr(opt, "save_metrics", "ppl")
         value = valid_ppl if metric in ("ppl", "perplexity") else (1.0 - accuracy if metric == "accuracy" else valid_ppl)
@@ -172,6 +196,8 @@ class Trainer:
             report["sents"] += batch.size
             if update:
                 counter, acc_words = 0, 0
+                if self.ema is not None:
+                    self.ema.update(self.optim._step)
                 if self.watchdog is not None:
                     self.watchdog.beat(self.optim._step)
                 n_up = self.optim._step

@@ -95,3 +95,21 @@ def test_lsh_perceiver_maxout_shapes_and_masks():
     x2[1, 8:] = 100.0
     assert a.shape == (2, 5, 32) and torch.allclose(a, lat(x2, pad), atol=1e-4)       # padded frames are ignored
     assert MaxOut(32, 7, 3)(x).shape == (2, 12, 7)
+
+
+def test_distillation_wrapper_trains_through_the_engine():
+    from nmtgminor_b200.train.engine import TrainEngine
+    student, teacher = _model(1), _model(2)
+    wrapper = FT.DistillationWrapper(student, teacher, alpha=0.5)
+    assert all(not p.requires_grad for p in teacher.parameters())
+    assert len(list(wrapper.parameters())) == len(list(student.parameters()))
+    opt = default_options(["-model_size", "32", "-layers", "1", "-n_heads", "2", "-inner_size", "64", "-optim", "adam", "-learning_rate",
+                           "0.01", "-update_method", "regular"])
+    eng = TrainEngine(wrapper, opt, device="cpu")
+    batch = token_budget_batches(60, 4, 10, 120, 1, seed=1, padded=False)[0]
+    first = eng.train_step(batch)[0].item()
+    for _ in range(8):
+        last = eng.train_step(batch)[0].item()
+    assert last < first
+    wrapper.eval()
+    assert "loss" in wrapper(batch)

@@ -140,3 +140,29 @@ def test_forward_is_bitwise_deterministic_for_a_seed():
     assert torch.equal(outs[0][1], outs[1][1]) and torch.allclose(outs[0][0], outs[1][0], rtol=1e-5)   # the sum uses atomics
     assert not torch.equal(outs[0][1], outs[2][1])
     assert ops.ext().bounds_violations() in (-1, 0)
+
+
+def test_lora_adapters_train_on_the_fused_path_and_leave_frozen_weights_alone():
+    from nmtgminor_b200.train import finetune as ft
+    from nmtgminor_b200.train.engine import TrainEngine
+    torch.manual_seed(0)
+    d = synthetic_dict(2000)
+    opt = _opt(["-weight_decay", "0.1"])
+    model = Transformer(opt, {"src": d, "tgt": d})
+    replaced = ft.apply_lora(model, r=8, alpha=16)
+    assert replaced
+    eng = TrainEngine(model, opt, device="cuda", cuda_graph=False)
+    store = eng.store
+    n_train = sum(p.numel() for p in model.parameters() if p.requires_grad)
+    assert 0 < store.trainable_total < store.total and eng.optim.exp_avg.numel() == store.trainable_total
+    assert store.trainable_total < n_train * 2 + 64 * len(replaced) * 4
+    frozen_before = store.master[store.trainable_total:].clone()
+    batches = [b.pin_memory() for b in token_budget_batches(2000, 5, 40, 1024, 2, seed=5, static=True)]
+    losses = []
+    for it in range(12):
+        loss, _ = eng.train_step(batches[it % 2])
+        losses.append(loss.item() / batches[it % 2].tgt_size)
+    torch.cuda.synchronize()
+    assert ops.check_status() == 0
+    assert torch.equal(store.master[store.trainable_total:], frozen_before)      # no update, no weight decay
+    assert losses[-1] < losses[0]
