@@ -67,7 +67,7 @@ def _load_builders():
 
     import importlib
     for mod in ("pretrained", "relative_transformer", "conformer", "lstm", "transformer_xl", "classifier", "multilingual",
-                "research"):
+                "research", "legacy"):
         try:
             m = importlib.import_module("." + mod, __package__)
         except ModuleNotFoundError as exc:

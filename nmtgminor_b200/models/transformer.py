@@ -110,7 +110,10 @@ class TransformerDecoder(nn.Module):
         B = tokens.shape[0]
         seqs = PackedSeqs(tokens, torch.full_like(tokens, position), torch.arange(B + 1, dtype=torch.int32, device=tokens.device), 1)
         self.embed.renew(position + 1)
-        x = self.embed(seqs, 0.0)
+        return self.run_layers_step(self.embed(seqs, 0.0), state)
+
+    def run_layers_step(self, x, state: "DecodingState"):
+        """One new position through the layer stack (subclasses with a different wiring override this)."""
         if self.reversible is not None:
             return self.reversible.step(x, state.buffers, state.src_pad_mask)
         for i, layer in enumerate(self.layers):
@@ -124,12 +127,7 @@ class TransformerDecoder(nn.Module):
         cu = getattr(self, "_step_cu", None)
         if cu is None or cu.numel() != B + 1 or cu.device != tokens.device:
             cu = self._step_cu = torch.arange(B + 1, dtype=torch.int32, device=tokens.device)
-        x = self.embed(PackedSeqs(tokens, positions, cu, 1), 0.0)
-        if self.reversible is not None:
-            return self.reversible.step(x, state.buffers, state.src_pad_mask)
-        for i, layer in enumerate(self.layers):
-            x = layer.step(x, state.buffers[i], state.src_pad_mask)
-        return self.final_norm(x)
+        return self.run_layers_step(self.embed(PackedSeqs(tokens, positions, cu, 1), 0.0), state)
 
 
 class Generator(nn.Module):

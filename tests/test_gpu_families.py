@@ -54,6 +54,7 @@ def _step_and_decode(model, batch, decode=True):
     ("multilingual_translator", ["-multilingual_adapter", "-adapter_bottleneck_size", "16"]), ("LSTM", []),
     ("discourse_translator", []), ("pretrain_transformer", ["-enc_pretrained_model", "mbart50", "-dec_pretrained_model", "mbart50"]),
     ("pretrain_transformer", ["-enc_pretrained_model", "deltalm", "-dec_pretrained_model", "deltalm"]),
+    ("dlcl_transformer", []), ("parallel_transformer", []), ("fctransformer", []), ("unified_transformer", []),
 ])
 def test_text_families_on_gpu(dicts, name, extra):
     torch.manual_seed(0)
