@@ -90,6 +90,11 @@ class LayerNorm(nn.Module):
     def forward(self, x):
         return ops.layer_norm(x, self.weight, self.bias, self.eps)
 
+    def with_residual(self, x):
+        """``(x, LN(x))``; use the first result as the residual of ``x + f(LN(x))`` so that backward sums the two
+        gradient paths inside the LayerNorm kernel."""
+        return ops.layer_norm_residual(x, self.weight, self.bias, self.eps)
+
 
 class Linear(nn.Module):
     """Affine map on packed rows with an optional fused epilogue (activation, dropout, residual)."""
@@ -304,8 +309,10 @@ class EncoderLayer(nn.Module):
         if self.post_norm:
             x = self.attn_norm(_sub(self, self.attn, x, x, p, seqs, seqs))
             return self.ffn_norm(_sub(self, self.ffn, x, x, p, seqs))
-        x = _sub(self, self.attn, self.attn_norm(x), x, p, seqs, seqs)
-        return _sub(self, self.ffn, self.ffn_norm(x), x, p, seqs)
+        x, h = self.attn_norm.with_residual(x)
+        x = _sub(self, self.attn, h, x, p, seqs, seqs)
+        x, h = self.ffn_norm.with_residual(x)
+        return _sub(self, self.ffn, h, x, p, seqs)
 
 
 class DecoderLayer(nn.Module):
@@ -344,12 +351,16 @@ class DecoderLayer(nn.Module):
             if not self.ignore_source:
                 x = self.cross_norm(_sub(self, self.cross_attn, x, x, p, seqs, seqs, memory, mem_seqs))
             return self.ffn_norm(_sub(self, self.ffn, x, x, p, seqs))
-        x = _sub(self, self.self_attn, self.self_norm(x), x, p, seqs, seqs)
+        x, h = self.self_norm.with_residual(x)
+        x = _sub(self, self.self_attn, h, x, p, seqs, seqs)
         if self.interleaved_ffn:
-            x = _sub(self, self.mid_ffn, self.mid_norm(x), x, p, seqs)
+            x, h = self.mid_norm.with_residual(x)
+            x = _sub(self, self.mid_ffn, h, x, p, seqs)
         if not self.ignore_source:
-            x = _sub(self, self.cross_attn, self.cross_norm(x), x, p, seqs, seqs, memory, mem_seqs)
-        return _sub(self, self.ffn, self.ffn_norm(x), x, p, seqs)
+            x, h = self.cross_norm.with_residual(x)
+            x = _sub(self, self.cross_attn, h, x, p, seqs, seqs, memory, mem_seqs)
+        x, h = self.ffn_norm.with_residual(x)
+        return _sub(self, self.ffn, h, x, p, seqs)
 
     def step(self, x, cache: dict, mem_mask):
         if self.post_norm:

@@ -351,6 +351,40 @@ class _LayerNormFn(torch.autograd.Function):
         return dx, None, None, None, None, None
 
 
+class _LayerNormResidualFn(torch.autograd.Function):
+    """Returns ``(x, LN(x))``.  The first output carries the residual stream past the sub-layer, so the gradients of
+    both uses of ``x`` arrive in one backward call and are summed inside the LayerNorm backward kernel instead of by a
+    separate element-wise add."""
+
+    @staticmethod
+    def forward(ctx, x, g, b, gg, gb, eps):
+        y, mean, rstd = ext().layernorm_fwd(x, g, b, eps)
+        ctx.save_for_backward(x, mean, rstd, g)
+        ctx.gg, ctx.gb = gg, gb
+        return x.view_as(x), y
+
+    @staticmethod
+    def backward(ctx, dres, dy):
+        if dy is None:
+            return dres, None, None, None, None, None
+        x, mean, rstd, g = ctx.saved_tensors
+        gg = ctx.gg if ctx.gg is not None else torch.zeros(x.shape[1], dtype=torch.float32, device=x.device)
+        gb = ctx.gb if ctx.gb is not None else torch.zeros(x.shape[1], dtype=torch.float32, device=x.device)
+        if dres is not None:
+            dres = dres.contiguous() if dres.dtype == torch.bfloat16 else dres.to(torch.bfloat16).contiguous()
+        dx = ext().layernorm_bwd(dy.contiguous(), x, mean, rstd, g, dres, gg, gb)
+        return dx, None, None, None, None, None
+
+
+def layer_norm_residual(x, weight, bias, eps=1e-5):
+    """``(x, LN(x))`` for a pre-norm residual block ``x + f(LN(x))``: pass the first result as the residual."""
+    if (fused_param(weight) and x.is_cuda and x.dim() == 2 and x.dtype == torch.bfloat16 and x.is_contiguous()
+            and x.shape[-1] <= 2048 and x.shape[-1] % 8 == 0 and torch.is_grad_enabled() and x.requires_grad):
+        return _LayerNormResidualFn.apply(x, weight.work, bias.work, getattr(weight, "main_grad", None),
+                                          getattr(bias, "main_grad", None), eps)
+    return x, layer_norm(x, weight, bias, eps)
+
+
 def layer_norm(x, weight, bias, eps=1e-5):
     if fused_param(weight) and x.is_cuda and x.shape[-1] <= 2048 and x.shape[-1] % 8 == 0:
         shp = x.shape
@@ -384,7 +418,7 @@ class _AttnFn(torch.autograd.Function):
             q, k, v = a[:, :W], a[:, W:2 * W], a[:, 2 * W:]
         else:
             q, k, v = a, b[:, :W], b[:, W:]
-        out = torch.zeros((q.shape[0], W), dtype=torch.bfloat16, device=q.device)
+        out = torch.empty((q.shape[0], W), dtype=torch.bfloat16, device=q.device)   # the kernel clears rows past the last sequence
         lse = torch.empty((heads, q.shape[0]), dtype=torch.float32, device=q.device)
         ext().attn_fwd(q, k, v, out, lse, cu_q, cu_k, heads, max_q, max_k, causal, scale, p, seed, sid)
         ctx.save_for_backward(a, b, out, lse, cu_q, cu_k)
@@ -396,13 +430,13 @@ class _AttnFn(torch.autograd.Function):
         a, b, out, lse, cu_q, cu_k = ctx.saved_tensors
         heads, max_q, max_k, causal, scale, p, seed, sid = ctx.cfg
         W = heads * 64
-        da = torch.zeros_like(a)
+        da = torch.empty_like(a)        # every sequence row is written by the kernel, the rest is cleared by it
         if b is None:
             q, k, v = a[:, :W], a[:, W:2 * W], a[:, 2 * W:]
             dq, dk, dv = da[:, :W], da[:, W:2 * W], da[:, 2 * W:]
             db = None
         else:
-            db = torch.zeros_like(b)
+            db = torch.empty_like(b)
             q, k, v = a, b[:, :W], b[:, W:]
             dq, dk, dv = da, db[:, :W], db[:, W:]
         dq_acc = torch.zeros((q.shape[0], W), dtype=torch.float32, device=q.device) if max_k > 128 else None
@@ -426,7 +460,7 @@ def _attn_dispatch(a, b, cu_q, cu_k, heads, max_q, max_k, causal, dropout_p, tra
             q, k, v = a[:, :W], a[:, W:2 * W], a[:, 2 * W:]
         else:
             q, k, v = a, b[:, :W], b[:, W:]
-        out = torch.zeros((q.shape[0], W), dtype=torch.bfloat16, device=q.device)
+        out = torch.empty((q.shape[0], W), dtype=torch.bfloat16, device=q.device)   # the kernel clears rows past the last sequence
         lse = torch.empty((heads, q.shape[0]), dtype=torch.float32, device=q.device)
         ext().attn_fwd(q, k, v, out, lse, cu_q, cu_k, heads, int(max_q), int(max_k), bool(causal), scale, p, _Rng.seed, sid)
         return out
@@ -454,7 +488,7 @@ def attention(q, k, v, cu_q, cu_k, heads, max_q, max_k, causal=False, dropout_p=
     p = float(dropout_p) if training else 0.0
     if q.is_cuda and d == 64 and q.dtype == torch.bfloat16 and not (torch.is_grad_enabled() and q.requires_grad):
         sid = next_stream() if p > 0 else 0
-        out = torch.zeros((q.shape[0], heads * 64), dtype=torch.bfloat16, device=q.device)
+        out = torch.empty((q.shape[0], heads * 64), dtype=torch.bfloat16, device=q.device)
         lse = torch.empty((heads, q.shape[0]), dtype=torch.float32, device=q.device)
         ext().attn_fwd(q, k, v, out, lse, cu_q, cu_k, heads, int(max_q), int(max_k), bool(causal), scale, p, _Rng.seed, sid)
         return out

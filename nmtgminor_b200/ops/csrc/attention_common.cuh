@@ -35,8 +35,37 @@ struct AttnArgs {
   __nv_bfloat16* dv; int ld_dv;
   float* dq_acc; int ld_dqacc;          // fp32 accumulation buffer for multi-key-tile sequences
   int total_q;
+  int total_k;            // allocated rows of q / k (>= cu[batch]): rows past the last sequence are cleared by the kernels
+  int batch;
   int* status;
 };
+
+// Clears rows [first_row, end_row) of a bf16 matrix (width a multiple of 8 columns, 16-byte aligned rows) with the
+// whole grid.  Those rows belong to no sequence, so nothing else in the kernel touches them and no ordering is
+// needed; callers can therefore hand the kernels uninitialised output buffers.
+__device__ __forceinline__ void zero_tail_rows(__nv_bfloat16* base, int ld, int width, int first_row, int end_row) {
+  if (base == nullptr || first_row >= end_row) return;
+  const long bid = blockIdx.x + static_cast<long>(gridDim.x) * (blockIdx.y + static_cast<long>(gridDim.y) * blockIdx.z);
+  const long nb = static_cast<long>(gridDim.x) * gridDim.y * gridDim.z;
+  const int vec = width >> 3;
+  const long total = static_cast<long>(end_row - first_row) * vec;
+  const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+  for (long i = bid * blockDim.x + threadIdx.x; i < total; i += nb * blockDim.x) {
+    const long r = first_row + i / vec;
+    const int c = static_cast<int>(i % vec) << 3;
+    *reinterpret_cast<uint4*>(base + r * ld + c) = z;
+  }
+}
+__device__ __forceinline__ void zero_tail_fwd(const AttnArgs& p) {
+  zero_tail_rows(p.out, p.ld_out, p.num_heads * 64, p.cu_q[p.batch], p.total_q);
+}
+__device__ __forceinline__ void zero_tail_bwd(const AttnArgs& p) {
+  const int w = p.num_heads * 64;
+  zero_tail_rows(p.dq, p.ld_dq, w, p.cu_q[p.batch], p.total_q);
+  const int k_end = p.cu_k[p.batch];
+  zero_tail_rows(p.dk, p.ld_dk, w, k_end, p.total_k);
+  zero_tail_rows(p.dv, p.ld_dv, w, k_end, p.total_k);
+}
 
 // nk UMMA k-steps reading A from a_addr (+ k * a_step bytes) and B from b_addr (+ k * b_step bytes)
 __device__ __forceinline__ void umma_steps(uint32_t d_tmem, uint32_t a_addr, uint32_t a_lbo, uint32_t a_step,

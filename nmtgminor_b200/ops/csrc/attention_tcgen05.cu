@@ -39,6 +39,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3);
   volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
+  zero_tail_fwd(p);
   const int b = blockIdx.z, h = blockIdx.y, qt = blockIdx.x;
   const int q_begin = p.cu_q[b], q_end = p.cu_q[b + 1];
   const int k_begin = p.cu_k[b], k_len = p.cu_k[b + 1] - k_begin;
@@ -221,6 +222,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3);
   volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
+  zero_tail_bwd(p);
   const int b = blockIdx.z, h = blockIdx.y, kt = blockIdx.x;
   const int q_begin = p.cu_q[b], q_len = p.cu_q[b + 1] - q_begin;
   const int k_begin = p.cu_k[b], k_len = p.cu_k[b + 1] - k_begin;
@@ -496,7 +498,7 @@ const char* nmtg_attn_fwd(const AttnDesc* d, cudaStream_t stream) {
   a.dropout_p = d->dropout_p; a.seed = d->seed; a.stream_id = d->stream_id; a.seed_dev = d->seed_dev; a.kstride = d->kstride;
   a.out = reinterpret_cast<__nv_bfloat16*>(d->out); a.ld_out = d->ld_out;
   a.lse = d->lse; a.lse_stride = d->lse_stride;
-  a.p_debug = nullptr; a.total_q = d->total_q; a.status = d->status;
+  a.p_debug = nullptr; a.total_q = d->total_q; a.total_k = d->total_k; a.batch = d->batch; a.status = d->status;
   if (g_attn_variant == 0 && d->max_q <= kTile && d->max_k <= kTile)
     return launch_attn_fwd_short(tq, tk, tv, a, d->batch * d->num_heads, stream);
   static bool configured = false;
@@ -536,7 +538,7 @@ const char* nmtg_attn_bwd(const AttnDesc* d, cudaStream_t stream) {
   a.dk = reinterpret_cast<__nv_bfloat16*>(d->dk); a.ld_dk = d->ld_dk;
   a.dv = reinterpret_cast<__nv_bfloat16*>(d->dv); a.ld_dv = d->ld_dv;
   a.dq_acc = d->dq_acc; a.ld_dqacc = d->ld_dqacc;
-  a.total_q = d->total_q; a.status = d->status;
+  a.total_q = d->total_q; a.total_k = d->total_k; a.batch = d->batch; a.status = d->status;
   if (g_attn_variant == 0 && d->max_q <= kTile && d->max_k <= kTile)
     return launch_attn_bwd_short(tq, tk, tv, tdo, a, d->batch * d->num_heads, stream);
   static bool configured = false;
@@ -630,7 +632,7 @@ extern "C" int nmtg_attn_bwd_noalloc(const void* q, int ld_q, const void* k, int
   a.dk = reinterpret_cast<__nv_bfloat16*>(dk); a.ld_dk = ld_dk;
   a.dv = reinterpret_cast<__nv_bfloat16*>(dv); a.ld_dv = ld_dv;
   a.dq_acc = scratch; a.ld_dqacc = width;
-  a.total_q = total_q; a.status = status;
+  a.total_q = total_q; a.total_k = total_k; a.batch = batch; a.status = status;
   ce = cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kBwdSmem);
   if (ce != cudaSuccess) return noalloc_fail(3, cudaGetErrorString(ce), err, err_len);
   dim3 grid((max_k + kTile - 1) / kTile, num_heads, batch);

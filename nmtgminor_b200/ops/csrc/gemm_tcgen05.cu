@@ -238,6 +238,13 @@ bool make_tmap_bf16_2d(CUtensorMap* out, const void* base, long rows, long cols,
                        int box_cols) {
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) return false;
+  // The encoder is a driver entry point and needs a current context.  A thread that has issued no runtime call yet
+  // (autograd's backward thread when the first thing it does is build a descriptor) has none: bind the primary one.
+  static thread_local bool context_bound = false;
+  if (!context_bound) {
+    cudaFree(nullptr);
+    context_bound = true;
+  }
   cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
   cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2};
   cuuint32_t box[2] = {static_cast<cuuint32_t>(box_cols), static_cast<cuuint32_t>(box_rows)};
@@ -245,6 +252,9 @@ bool make_tmap_bf16_2d(CUtensorMap* out, const void* base, long rows, long cols,
   CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    fprintf(stderr, "nmtgminor_b200: cuTensorMapEncodeTiled failed with CUresult %d (base %p, rows %ld, cols %ld, ld %ld, box %d x %d)\n",
+            static_cast<int>(r), base, rows, cols, ld, box_rows, box_cols);
   return r == CUDA_SUCCESS;
 }
 

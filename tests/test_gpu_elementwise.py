@@ -171,3 +171,32 @@ def test_adamw_skips_on_nonfinite():
     assert bad.item() == 1
     ops.ext().adamw_flat(master, None, grad, m, v, hyper.to(DEV), sq, bad)
     assert torch.equal(master, torch.ones(n, device=DEV)) and grad.abs().max().item() == 0.0
+
+
+def test_layernorm_residual_pair_sums_both_gradient_paths():
+    """``(x, LN(x))`` as one autograd node: d/dx of ``a * x + b * LN(x)`` matches the fp32 composition."""
+    from nmtgminor_b200.models.layers import LayerNorm
+    from nmtgminor_b200.parallel.flat import FlatParameterStore
+    torch.manual_seed(3)
+    ln = LayerNorm(512)
+    with torch.no_grad():
+        ln.weight.normal_(1.0, 0.2)
+        ln.bias.normal_(0.0, 0.2)
+    store = FlatParameterStore(ln, DEV)
+    x = torch.randn(300, 512, device=DEV).bfloat16().requires_grad_(True)
+    wa, wb = torch.randn(300, 512, device=DEV).bfloat16(), torch.randn(300, 512, device=DEV).bfloat16()
+    res, h = ln.with_residual(x)
+    assert type(h.grad_fn).__name__.startswith("_LayerNormResidualFn")
+    (res * wa + h * wb).sum().backward()
+    xf = x.detach().float().requires_grad_(True)
+    gf, bf = ln.weight.detach().float().requires_grad_(True), ln.bias.detach().float().requires_grad_(True)
+    hf = torch.nn.functional.layer_norm(xf, (512,), gf, bf, 1e-5)
+    (xf * wa.float() + hf * wb.float()).sum().backward()
+    _close(x.grad, xf.grad, 8e-2, 3e-2, "ln residual dx")
+    _close(ln.weight.main_grad, gf.grad, 0.02 * math.sqrt(300) + 0.05, 2e-2, "ln residual dgamma")
+    # only the residual path used: the gradient passes straight through
+    x2 = x.detach().clone().requires_grad_(True)
+    res2, _ = ln.with_residual(x2)
+    (res2 * wa).sum().backward()
+    assert torch.equal(x2.grad, wa)
+    del store
