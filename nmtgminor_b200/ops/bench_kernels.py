@@ -1,6 +1,6 @@
 """Per-kernel micro-benchmarks on the shapes of the Transformer-big training step.
 
-    python -m nmtgminor_b200.ops.bench_kernels [--json out.json] [--only gemm,attn,...]
+    python -m nmtgminor_b200.ops.bench_kernels [--json out.json] [--only gemm,attn,...]   (--only gemm_stalls: cycle breakdown of the CTA-pair GEMM)
 
 Each kernel is timed with CUDA events after warm-up; between timed launches a 256 MB buffer is rewritten so
 the 126 MB L2 starts cold.  GEMMs report TFLOP/s next to ``torch.matmul`` (cuBLAS) on the same shape as a
@@ -150,7 +150,7 @@ def bench_attention(rows):
     while sum(lens) < 8192 - 100:
         lens.append(int(rng.randint(20, 101)))
     n = sum(lens)
-    cap = (n + 127) // 128 * 128
+    cap = (n + 127) // 1216 * 128
     heads, W = 16, 1024
     cu = torch.zeros(len(lens) + 1, dtype=torch.int32)
     cu[1:] = torch.tensor(lens).cumsum(0)
@@ -172,6 +172,72 @@ def bench_attention(rows):
         rows.append({"kernel": "attention bwd causal=%s" % causal, "ms": ms, "tflops": 2.5 * fl / ms / 1e9})
 
 
+def bench_gemm_stalls():
+    """Where the CTA-pair GEMM spends its cycles: the traced build of the kernel counts, per cluster, how long the MMA
+    issuer waited for operands and for a free accumulator and how long the epilogue waited for a finished one; two
+    ablations (no epilogue, operand streaming without any MMA) bound what each part could reach alone."""
+    T, H, F = 8192, 1024, 4096
+    dev = "cuda"
+    mk = lambda *shape: torch.randn(*shape, device=dev).bfloat16()
+    x, w1, w2, wo, wq = mk(T, H), mk(F, H), mk(H, F), mk(H, H), mk(3 * H, H)
+    h = torch.empty(T, F, device=dev, dtype=torch.bfloat16)
+    y = torch.empty(T, H, device=dev, dtype=torch.bfloat16)
+    qkv = torch.empty(T, 3 * H, device=dev, dtype=torch.bfloat16)
+    b1, b2, res = mk(F), mk(H), mk(T, H)
+    bits = torch.empty(T, F // 32, dtype=torch.int32, device=dev)
+    gw, gwo = torch.zeros(F, H, device=dev), torch.zeros(H, H, device=dev)
+    trace = torch.zeros(16 * 128, dtype=torch.int64, device=dev)
+    cases = [
+        ("fc1 8192x4096x1024", 2.0 * T * H * F, lambda: ops.gemm(x, w1, h)),
+        ("fc1 + bias + relu + dropout + sign bits", 2.0 * T * H * F,
+         lambda: ops.gemm(x, w1, h, bias=b1, act=1, dropout_p=0.1, seed=1, stream_id=1, mask=bits)),
+        ("fc2 8192x1024x4096", 2.0 * T * H * F, lambda: ops.gemm(h, w2, y)),
+        ("fc2 + bias + dropout + residual", 2.0 * T * H * F,
+         lambda: ops.gemm(h, w2, y, bias=b2, residual=res, dropout_p=0.1, seed=1, stream_id=2)),
+        ("fc2 dgrad + sign bits 8192x4096x1024", 2.0 * T * H * F,
+         lambda: ops.gemm(y, w2, h, b_mn_major=True, act=8, mask=bits, alpha=1.1)),
+        ("out 8192x1024x1024", 2.0 * T * H * H, lambda: ops.gemm(x, wo, y)),
+        ("qkv 8192x3072x1024", 2.0 * T * H * 3 * H, lambda: ops.gemm(x, wq, qkv)),
+        ("fc1 wgrad 4096x1024x8192 (fp32 accumulate)", 2.0 * T * H * F,
+         lambda: ops.gemm(h, x, gw, a_mn_major=True, b_mn_major=True, accumulate=True, allow_split_k=True)),
+        ("out wgrad 1024x1024x8192 (fp32 accumulate)", 2.0 * T * H * H,
+         lambda: ops.gemm(y, x, gwo, a_mn_major=True, b_mn_major=True, accumulate=True, allow_split_k=True)),
+    ]
+
+    def traced(fn):
+        ops.ext().set_gemm_trace(trace)
+        trace.zero_()
+        fn()
+        torch.cuda.synchronize()
+        ops.ext().set_gemm_trace(None)
+        t = trace.view(128, 16).float()
+        return t[t[:, 0] > 0].mean(0)
+
+    print("%-44s %9s %8s | %12s %9s %9s %10s | %9s %10s" % ("kernel", "ms", "TFLOP/s", "issuer cyc", "wait acc", "wait ops",
+                                                             "first ops", "epi wait", "last epi") + "   per tile: drain / chunks / store issue")
+    for name, fl, fn in cases:
+        ms = time_ms(fn)              # timed with the production kernel; the traced variant runs once afterwards
+        m = traced(fn)
+        print("%-44s %9.4f %8.0f | %12.0f %8.1f%% %8.1f%% %10.0f | %8.1f%% %10.0f   %6.0f / %6.0f / %6.0f" % (
+            name, ms, fl / ms / 1e9, m[0], 100 * m[1] / m[0], 100 * m[2] / m[0], m[3], 100 * m[5] / m[4], m[6],
+            m[8] / m[7], m[9] / m[7], m[10] / m[7]))
+    for variant, label in ((12, "no epilogue"), (13, "operand streaming only (no MMA)")):
+        ops.ext().set_gemm_variant(variant)
+        ops.ext().set_gemm_trace(trace)          # the ablations exist in the traced kernel only
+        for name, fl, fn in (cases[0], cases[2], cases[5], cases[7]):
+            ms = time_ms(fn)
+            trace.zero_()
+            fn()
+            torch.cuda.synchronize()
+            t = trace.view(128, 16).float()
+            m = t[t[:, 0] > 0].mean(0)
+            print("%-34s %-44s %9.4f ms  %6.0f TFLOP/s-equivalent | issuer %8.0f cyc, waiting for operands %4.1f%%" % (
+                label, name, ms, fl / ms / 1e9, m[0], 100 * m[2] / m[0]))
+        ops.ext().set_gemm_trace(None)
+    ops.ext().set_gemm_variant(10)
+    print("kernel status word:", ops.check_status())
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--json", default=None)
@@ -179,6 +245,9 @@ def main():
     args = ap.parse_args()
     rows = []
     which = set(args.only.split(","))
+    if "gemm_stalls" in which:
+        bench_gemm_stalls()
+        return
     if "gemm" in which:
         bench_gemm(rows)
     if "mlp" in which:

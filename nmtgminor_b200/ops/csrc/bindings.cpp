@@ -405,6 +405,14 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         pybind11::arg("dropout_p"), pybind11::arg("seed"), pybind11::arg("stream_id"), pybind11::arg("alpha"), pybind11::arg("accumulate"),
         pybind11::arg("allow_split_k"), pybind11::arg("split_k"), pybind11::arg("force_bn"), pybind11::arg("mask") = pybind11::none());
   m.def("set_gemm_variant", [](int64_t v) { nmtg_set_gemm_variant(static_cast<int>(v)); });
+  m.def("set_gemm_trace", [](const OptTensor& buf) {
+    if (buf.has_value()) {
+      TORCH_CHECK(buf->is_cuda() && buf->scalar_type() == at::kLong && buf->is_contiguous() && buf->numel() >= 16 * 128);
+      nmtg_set_gemm_trace(reinterpret_cast<long long*>(buf->data_ptr<int64_t>()));
+    } else {
+      nmtg_set_gemm_trace(nullptr);
+    }
+  });
   m.def("layernorm_fwd", &layernorm_fwd);
   m.def("layernorm_bwd", &layernorm_bwd);
   m.def("xent_fused", &xent_fused);

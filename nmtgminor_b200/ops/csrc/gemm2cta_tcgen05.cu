@@ -70,7 +70,7 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar_cluster_addr) {
   asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster_addr) : "memory");
 }
 
-template <int BN>
+template <int BN, bool kTrace, uint32_t kFeat>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const __grid_constant__ CUtensorMap tmap_out, const GemmArgs p) {
@@ -163,25 +163,39 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
+      // cycle counters for p.trace: [0] issuer loop, [1] waiting for a free accumulator, [2] waiting for operands,
+      // [3] start of the loop until the first operands have landed
+      const long long t_begin = kTrace ? clock64() : 0;
+      long long t_wait_acc = 0, t_wait_ops = 0, t_first = 0;
       for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters, ++it) {
         const int acc = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
+        long long t0 = kTrace ? clock64() : 0;
         if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1, abort_word, p.status, kTimeoutTmemEmpty)) break;
+        if (kTrace) t_wait_acc += clock64() - t0;
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * BN;
         const int ks = tile / num_mn;
         const int kb_begin = ks * kb_per_split, kb_end = min(kb_begin + kb_per_split, num_kb_total);
         for (int kb = kb_begin; kb < kb_end; ++kb) {
+          t0 = kTrace ? clock64() : 0;
           if (!mbar_wait(&full_bar[stage], phase, abort_word, p.status, kTimeoutTmaFull)) { ok = false; break; }
+          if (kTrace) {
+            const long long t1 = clock64();
+            t_wait_ops += t1 - t0;
+            if (t_first == 0) t_first = t1 - t_begin;
+          }
           tc_fence_after_sync();
           const uint32_t sa = smem_u32(smem + stage * S::kStageBytes);
           const uint32_t sb = sa + S::kABytes;
           const uint64_t adesc = make_smem_desc_sw128(sa, a_lbo, 1024);
           const uint64_t bdesc = make_smem_desc_sw128(sb, b_lbo, 1024);
+          if (!kTrace || p.ablate != 3) {     // traced ablation 3: stream the operands only, no tensor-core work
 #pragma unroll
-          for (int k = 0; k < BK / 16; ++k)
-            umma_bf16_pair(d_tmem, adesc + static_cast<uint64_t>(k * a_kstep), bdesc + static_cast<uint64_t>(k * b_kstep), idesc,
-                           (kb > kb_begin || k > 0) ? 1u : 0u);
+            for (int k = 0; k < BK / 16; ++k)
+              umma_bf16_pair(d_tmem, adesc + static_cast<uint64_t>(k * a_kstep), bdesc + static_cast<uint64_t>(k * b_kstep), idesc,
+                             (kb > kb_begin || k > 0) ? 1u : 0u);
+          }
           umma_commit_pair(map_to_cta(smem_u32(&empty_bar[stage]), 0));
           umma_commit_pair(map_to_cta(smem_u32(&empty_bar[stage]), 1));
           if (++stage == S::kStages) { stage = 0; phase ^= 1; }
@@ -191,6 +205,13 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           umma_commit_pair(map_to_cta(smem_u32(&tmem_full[acc]), 1));
         }
       }
+      if (kTrace && p.trace) {
+        long long* tr = p.trace + cluster_id * 16;
+        tr[0] = clock64() - t_begin;
+        tr[1] = t_wait_acc;
+        tr[2] = t_wait_ops;
+        tr[3] = t_first;
+      }
     }
   } else {
     // ------------------------------- epilogue (8 warps, both CTAs) ---------------------------
@@ -199,52 +220,78 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     const bool do_drop = p.dropout_p > 0.f;
     const DropRng rng(p.seed + ((do_drop && p.seed_dev) ? *p.seed_dev : 0ull), p.stream_id, p.dropout_p);
     int it = 0;
+    // cycle counters for p.trace (first epilogue warp of the leader): [4] loop, [5] waiting for a finished accumulator,
+    // [6] the last tile's epilogue (the part no later main loop can hide), [7] tiles
+    const bool tracing = kTrace && p.trace != nullptr && leader && warp == 2 && lane == 0;
+    const long long e_begin = tracing ? clock64() : 0;
+    long long e_wait = 0, e_last = 0, e_drain = 0, e_chunks = 0, e_issue = 0;
     for (int tile = cluster_id; tile < num_tiles; tile += num_clusters, ++it) {
       const int mn = tile % num_mn;
       const int m0 = (mn % num_m) * (2 * BM) + static_cast<int>(rank) * BM;
       const int n0 = (mn / num_m) * BN;
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
+      const long long e0 = tracing ? clock64() : 0;
       if (!mbar_wait(&tmem_full[acc], acc_phase, abort_word, p.status, kTimeoutTmemFull)) break;
+      if (tracing) { e_last = clock64(); e_wait += e_last - e0; }
       tc_fence_after_sync();
       const int row = m0 + q * 32 + lane;
       const bool row_ok = row < p.M;
-      if (p.tma_store) {
+      if ((kFeat & kEpiBf16) && p.tma_store) {
         // 64-column groups: both 32-column halves go to this warp's staging tile, one TMA store per group writes
         // full 128-byte lines (rows / columns outside the matrix are clipped by the copy engine)
         uint8_t* stage = smem + S::kStagingOffset + (warp - 2) * (32 * 128);
 #pragma unroll 1
         for (int g = chunk_par; g < BN / 64; g += kEpilogueWarps / 4) {
           const int col0 = n0 + g * 64;
-          if (col0 >= p.N || p.ablate == 2) break;
+          if (col0 >= p.N || p.ablate >= 2) break;
+          const long long c0 = tracing ? clock64() : 0;
           if (lane == 0) tma_store_wait_read();        // the previous store of this warp has drained its staging tile
           __syncwarp();
+          const long long c1 = tracing ? clock64() : 0;
 #pragma unroll
           for (int half = 0; half < 2; ++half) {
             if (col0 + half * 32 < p.N)
-              gemm_epilogue_chunk(p, rng, do_drop, row, row_ok, col0 + half * 32,
+              gemm_epilogue_chunk<kFeat>(p, rng, do_drop, row, row_ok, col0 + half * 32,
                                   tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN + g * 64 + half * 32,
                                   stage + lane * 128, half, lane);
           }
+          const long long c2 = tracing ? clock64() : 0;
           fence_async_smem();
           __syncwarp();
           if (lane == 0) {
             tma_store_2d(&tmap_out, stage, col0, m0 + q * 32);
             tma_store_commit();
           }
+          if (tracing) {
+            e_drain += c1 - c0;
+            e_chunks += c2 - c1;
+            e_issue += clock64() - c2;
+          }
         }
       } else {
 #pragma unroll 1
         for (int c = chunk_par; c < BN / 32; c += kEpilogueWarps / 4) {
           const int col0 = n0 + c * 32;
-          if (col0 >= p.N || p.ablate == 2) break;
-          gemm_epilogue_chunk(p, rng, do_drop, row, row_ok, col0, tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN + c * 32);
+          if (col0 >= p.N || p.ablate >= 2) break;
+          gemm_epilogue_chunk<kFeat>(p, rng, do_drop, row, row_ok, col0, tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN + c * 32);
         }
       }
       tc_fence_before_sync();
       mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty[acc]), 0));
     }
     if (p.tma_store && lane == 0) tma_store_wait_all();   // staging must outlive the copies that read it
+    if (tracing) {
+      long long* tr = p.trace + cluster_id * 16;
+      const long long e_end = clock64();
+      tr[4] = e_end - e_begin;
+      tr[5] = e_wait;
+      tr[6] = e_end - e_last;
+      tr[7] = it;
+      tr[8] = e_drain;       // waiting for the previous TMA store to release the staging tile
+      tr[9] = e_chunks;      // accumulator loads, arithmetic, staging writes
+      tr[10] = e_issue;      // proxy fence + issuing the store
+    }
   }
 
   // ------------------------------- teardown --------------------------------------------------------
@@ -261,21 +308,22 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   }
 }
 
-template <int BN>
+template <int BN, bool kTrace, uint32_t kFeat>
 static const char* launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmArgs& args, int grid,
                                cudaStream_t stream) {
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, PairSmem<BN>::kTotal);
+    cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel<BN, kTrace, kFeat>, cudaFuncAttributeMaxDynamicSharedMemorySize, PairSmem<BN>::kTotal);
     if (e != cudaSuccess) return cudaGetErrorString(e);
     configured = true;
   }
-  gemm_pair_kernel<BN><<<grid, kPairThreads, PairSmem<BN>::kTotal, stream>>>(ta, tb, tc, args);
+  gemm_pair_kernel<BN, kTrace, kFeat><<<grid, kPairThreads, PairSmem<BN>::kTotal, stream>>>(ta, tb, tc, args);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? nullptr : cudaGetErrorString(e);
 }
 
 // CTA-pair path; BN = 256 or 128; a.split_k splits must all be non-empty.  Returns nullptr on success.
+int g_pair_generic_epilogue = 0;   // gemm variant 31: always run the general epilogue (30 = specialised, default)
 int g_pair_tma_store = 1;     // set to 0 (gemm variant 20) to force per-thread global stores, for A/B measurements
 
 const char* launch_gemm_pair(const GemmDesc* d, const GemmArgs& a, int bn, cudaStream_t stream) {
@@ -298,8 +346,22 @@ const char* launch_gemm_pair(const GemmDesc* d, const GemmArgs& a, int bn, cudaS
   const long tiles = static_cast<long>((d->M + 2 * BM - 1) / (2 * BM)) * ((d->N + bn - 1) / bn) * a.split_k;
   const int max_clusters = num_sms() / 2;
   const int clusters = static_cast<int>(tiles < max_clusters ? tiles : max_clusters);
-  if (bn == 256) return launch_pair<256>(ta, tb, tc, args, clusters * 2, stream);
-  return launch_pair<128>(ta, tb, tc, args, clusters * 2, stream);
+  if (bn != 256) return launch_pair<128, false, kEpiAll>(ta, tb, tc, args, clusters * 2, stream);
+  if (args.trace != nullptr) return launch_pair<256, true, kEpiAll>(ta, tb, tc, args, clusters * 2, stream);
+  // the specialised epilogues of the shapes a training step is made of; anything else takes the general kernel
+  constexpr uint32_t kPlain = kEpiBf16;
+  constexpr uint32_t kFc1 = kEpiBf16 | kEpiBias | kEpiActFwd | kEpiDrop | kEpiMaskOut;
+  constexpr uint32_t kOutRes = kEpiBf16 | kEpiBias | kEpiDrop | kEpiRes;
+  constexpr uint32_t kDgradMask = kEpiBf16 | kEpiMaskBwd;
+  constexpr uint32_t kAccum = kEpiF32;
+  const uint32_t need = g_pair_generic_epilogue ? kEpiAll : gemm_epilogue_features(args);
+  const int grid = clusters * 2;
+  if ((need & ~kPlain) == 0) return launch_pair<256, false, kPlain>(ta, tb, tc, args, grid, stream);
+  if ((need & ~kAccum) == 0) return launch_pair<256, false, kAccum>(ta, tb, tc, args, grid, stream);
+  if ((need & ~kDgradMask) == 0) return launch_pair<256, false, kDgradMask>(ta, tb, tc, args, grid, stream);
+  if ((need & ~kOutRes) == 0) return launch_pair<256, false, kOutRes>(ta, tb, tc, args, grid, stream);
+  if ((need & ~kFc1) == 0) return launch_pair<256, false, kFc1>(ta, tb, tc, args, grid, stream);
+  return launch_pair<256, false, kEpiAll>(ta, tb, tc, args, grid, stream);
 }
 
 }  // namespace b200

@@ -33,7 +33,9 @@ struct GemmArgs {
   const unsigned long long* seed_dev;
   int* status;
   int tma_store;           // bf16 output leaves through shared memory and TMA stores (CTA-pair kernel)
-  int ablate;              // profiling aid: 1 = read the accumulator but skip arithmetic and stores, 2 = skip the epilogue body
+  int ablate;              // profiling aid: 1 = read the accumulator but skip arithmetic and stores, 2 = skip the epilogue body,
+                           // 3 (traced kernel only) = also skip the MMAs: operand streaming alone
+  long long* trace;        // profiling aid: when set, the CTA-pair kernel writes up to 16 cycle counters per cluster (see gemm2cta_tcgen05.cu)
 };
 
 __device__ __forceinline__ float gelu_f(float x) { return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f)); }
@@ -50,6 +52,29 @@ __device__ __forceinline__ float sigmoid_f(float x) { return 1.0f / (1.0f + __ex
 // `stage_row` (optional): instead of writing bf16 results to global memory, place the 64-byte row fragment in a
 // shared-memory staging row laid out for a 128-byte-swizzled TMA store (logical 16-byte chunk j of row r sits at
 // chunk j ^ (r & 7)); `stage_half` selects the left / right 32 columns of the 64-column staging tile.
+// Feature bits of the epilogue.  A kernel instantiated with a mask contains only the code of those features (the
+// run-time checks inside still apply), which keeps the epilogue a short straight-line sequence: with everything
+// compiled in, each 32-column chunk jumps over a dozen large unused blocks and the warps wait on instruction fetch
+// rather than on arithmetic.  kEpiAll is the general kernel.
+constexpr uint32_t kEpiBias = 1u, kEpiPreact = 2u, kEpiActFwd = 4u, kEpiActBwd = 8u, kEpiMaskBwd = 16u, kEpiDrop = 32u,
+                   kEpiMaskOut = 64u, kEpiRes = 128u, kEpiF32 = 256u, kEpiBf16 = 512u, kEpiAll = 1023u;
+
+// Features a problem needs (host side).
+inline uint32_t gemm_epilogue_features(const GemmArgs& a) {
+  uint32_t f = 0;
+  if (a.bias) f |= kEpiBias;
+  if (a.preact) f |= kEpiPreact;
+  if (a.act == kActMaskBwd) f |= kEpiMaskBwd;
+  else if (a.act >= kActReluBwd) f |= kEpiActBwd;
+  else if (a.act != 0) f |= kEpiActFwd;
+  if (a.dropout_p > 0.f) f |= kEpiDrop;
+  if (a.mask && a.act != kActMaskBwd) f |= kEpiMaskOut;
+  if (a.residual) f |= kEpiRes;
+  f |= a.out_fp32 ? kEpiF32 : kEpiBf16;
+  return f;
+}
+
+template <uint32_t kFeat = kEpiAll>
 __device__ __forceinline__ void gemm_epilogue_chunk(const GemmArgs& p, const DropRng& rng, const bool do_drop, const int row,
                                                     const bool row_ok, const int col0, const uint32_t taddr,
                                                     uint8_t* stage_row = nullptr, const int stage_half = 0,
@@ -57,10 +82,10 @@ __device__ __forceinline__ void gemm_epilogue_chunk(const GemmArgs& p, const Dro
     const bool full_cols = (col0 + 32 <= p.N);
     // global operands of the epilogue are requested BEFORE the TMEM load so their latency overlaps it
     uint4 aux_v[4], res_v[4];
-    const bool aux_vec = row_ok && full_cols && p.act >= kActReluBwd && p.act != kActMaskBwd && (p.ld_aux & 7) == 0;
+    const bool aux_vec = (kFeat & kEpiActBwd) && row_ok && full_cols && p.act >= kActReluBwd && p.act != kActMaskBwd && (p.ld_aux & 7) == 0;
     uint32_t mask_word = 0;
-    if (p.act == kActMaskBwd && row_ok) mask_word = p.mask[static_cast<size_t>(row) * p.ld_mask + (col0 >> 5)];
-    const bool res_vec = row_ok && full_cols && p.residual != nullptr && (p.ld_res & 7) == 0;
+    if ((kFeat & kEpiMaskBwd) && p.act == kActMaskBwd && row_ok) mask_word = p.mask[static_cast<size_t>(row) * p.ld_mask + (col0 >> 5)];
+    const bool res_vec = (kFeat & kEpiRes) && row_ok && full_cols && p.residual != nullptr && (p.ld_res & 7) == 0;
     if (aux_vec) {
       const uint4* ap4 = reinterpret_cast<const uint4*>(p.aux + static_cast<size_t>(row) * p.ld_aux + col0);
 #pragma unroll
@@ -78,7 +103,7 @@ __device__ __forceinline__ void gemm_epilogue_chunk(const GemmArgs& p, const Dro
     float v[32];
 #pragma unroll
     for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
-    if (p.bias) {
+    if ((kFeat & kEpiBias) && p.bias) {
       if (full_cols) {
         const uint4* bp = reinterpret_cast<const uint4*>(p.bias + col0);
 #pragma unroll
@@ -97,7 +122,7 @@ __device__ __forceinline__ void gemm_epilogue_chunk(const GemmArgs& p, const Dro
           if (col0 + j < p.N) v[j] += __bfloat162float(p.bias[col0 + j]);
       }
     }
-    if (p.preact) {
+    if ((kFeat & kEpiPreact) && p.preact) {
       __nv_bfloat16* pp = p.preact + static_cast<size_t>(row) * p.ld_out + col0;
       if (full_cols) {
 #pragma unroll
@@ -114,10 +139,10 @@ __device__ __forceinline__ void gemm_epilogue_chunk(const GemmArgs& p, const Dro
       }
     }
     // activation (forward) or activation-gradient (backward; aux holds h or z)
-    if (p.act == kActMaskBwd) {
+    if ((kFeat & kEpiMaskBwd) && p.act == kActMaskBwd) {
 #pragma unroll
       for (int j = 0; j < 32; ++j) v[j] = ((mask_word >> j) & 1u) ? v[j] : 0.f;
-    } else if (p.act >= kActReluBwd) {
+    } else if ((kFeat & kEpiActBwd) && p.act >= kActReluBwd) {
       const __nv_bfloat16* ap = p.aux + static_cast<size_t>(row) * p.ld_aux + col0;
       float av[32];
       if (aux_vec) {
@@ -145,17 +170,17 @@ __device__ __forceinline__ void gemm_epilogue_chunk(const GemmArgs& p, const Dro
         else { float s = sigmoid_f(a); g = s * (1.f + a * (1.f - s)); }
         v[j] *= g;
       }
-    } else if (p.act == kActRelu) {
+    } else if ((kFeat & kEpiActFwd) && p.act == kActRelu) {
 #pragma unroll
       for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.f);
-    } else if (p.act == kActGelu) {
+    } else if ((kFeat & kEpiActFwd) && p.act == kActGelu) {
 #pragma unroll
       for (int j = 0; j < 32; ++j) v[j] = gelu_f(v[j]);
-    } else if (p.act == kActSilu) {
+    } else if ((kFeat & kEpiActFwd) && p.act == kActSilu) {
 #pragma unroll
       for (int j = 0; j < 32; ++j) v[j] = v[j] * sigmoid_f(v[j]);
     }
-    if (do_drop) {
+    if ((kFeat & kEpiDrop) && do_drop) {
       // element index = row * N + col; 4 consecutive elements share one hash word (one byte each)
       const unsigned long long w0 = (static_cast<unsigned long long>(row) * p.N + col0) >> 2;
 #pragma unroll
@@ -165,13 +190,13 @@ __device__ __forceinline__ void gemm_epilogue_chunk(const GemmArgs& p, const Dro
         for (int j = 0; j < 4; ++j) v[g * 4 + j] = rng.keep(w, j) ? v[g * 4 + j] * rng.scale : 0.f;
       }
     }
-    if (p.mask && p.act != kActMaskBwd) {
+    if ((kFeat & kEpiMaskOut) && p.mask && p.act != kActMaskBwd) {
       uint32_t bits = 0;
 #pragma unroll
       for (int j = 0; j < 32; ++j) bits |= (v[j] > 0.f ? 1u : 0u) << j;
       p.mask[static_cast<size_t>(row) * p.ld_mask + (col0 >> 5)] = bits;
     }
-    if (p.residual) {
+    if ((kFeat & kEpiRes) && p.residual) {
       const __nv_bfloat16* rp = p.residual + static_cast<size_t>(row) * p.ld_res + col0;
       if (res_vec) {
 #pragma unroll
@@ -190,7 +215,7 @@ __device__ __forceinline__ void gemm_epilogue_chunk(const GemmArgs& p, const Dro
           if (col0 + j < p.N) v[j] += __bfloat162float(rp[j]);
       }
     }
-    if (p.out_fp32) {
+    if ((kFeat & kEpiF32) && (p.out_fp32 || !(kFeat & kEpiBf16))) {
       float* op = reinterpret_cast<float*>(p.out) + static_cast<size_t>(row) * p.ld_out + col0;
       // accumulation into an existing fp32 buffer goes through the L2 reduction unit as well: no read round trip
       if (p.split_k > 1 || p.accumulate) {
@@ -218,6 +243,8 @@ __device__ __forceinline__ void gemm_epilogue_chunk(const GemmArgs& p, const Dro
         for (int j = 0; j < 32; ++j)
           if (col0 + j < p.N) op[j] = p.accumulate ? op[j] + v[j] : v[j];
       }
+    } else if (!(kFeat & kEpiBf16)) {
+      // fp32-only kernel asked for bf16 output: the host never selects this combination
     } else if (stage_row != nullptr) {
 #pragma unroll
       for (int g = 0; g < 4; ++g) {

@@ -329,12 +329,17 @@ const char* launch_gemm_pair(const GemmDesc* d, const GemmArgs& a, int bn, cudaS
 using namespace b200;
 
 static int g_gemm_variant = 0;   // 0 = automatic, 1 = single-CTA kernel only, 2 = CTA-pair kernel whenever M > 128
+static long long* g_gemm_trace = nullptr;   // see nmtg_set_gemm_trace
 static int g_gemm_ablate = 0;    // profiling aid, see GemmArgs::ablate; variants 10 / 11 / 12 select ablation 0 / 1 / 2
 namespace b200 {
 extern int g_pair_tma_store;
+extern int g_pair_generic_epilogue;
 }
+void nmtg_set_gemm_trace(long long* buf) { g_gemm_trace = buf; }
+
 void nmtg_set_gemm_variant(int v) {
-  if (v == 20 || v == 21) b200::g_pair_tma_store = v - 20;   // 20: per-thread stores, 21: TMA-store epilogue (default)
+  if (v == 30 || v == 31) b200::g_pair_generic_epilogue = v - 30;
+  else if (v == 20 || v == 21) b200::g_pair_tma_store = v - 20;   // 20: per-thread stores, 21: TMA-store epilogue (default)
   else if (v >= 10) g_gemm_ablate = v - 10;
   else g_gemm_variant = v;
 }
@@ -358,6 +363,7 @@ const char* nmtg_gemm_bf16(const GemmDesc* d, cudaStream_t stream) {
   a.preact = reinterpret_cast<__nv_bfloat16*>(d->preact);
   a.mask = reinterpret_cast<uint32_t*>(d->mask); a.ld_mask = d->ld_mask;
   a.ablate = g_gemm_ablate;
+  a.trace = g_gemm_trace;
   if (d->act == kActMaskBwd && !d->mask) return "gemm: the mask-backward epilogue needs a mask";
   a.act = d->act; a.dropout_p = d->dropout_p; a.seed = d->seed; a.stream_id = d->stream_id; a.seed_dev = d->seed_dev;
   a.status = d->status;

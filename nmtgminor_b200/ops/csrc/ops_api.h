@@ -44,6 +44,9 @@ struct GemmDesc {
 const char* nmtg_gemm_bf16(const GemmDesc* d, cudaStream_t stream);
 // 0 = automatic (CTA-pair kernel when M > 128), 1 = single-CTA kernel only, 2 = same as 0
 void nmtg_set_gemm_variant(int v);
+// Profiling aid: device buffer of 16 int64 per CTA pair (at least 16 * #SMs / 2 entries) that the CTA-pair GEMM fills with
+// cycle counters of its MMA issuer and of one epilogue warp; nullptr switches it off.
+void nmtg_set_gemm_trace(long long* buf);
 
 // LayerNorm over the last dimension of bf16 x[rows, hidden]; mean/rstd (fp32 [rows]) may be null in fwd.
 const char* nmtg_layernorm_fwd(const void* x, const void* gamma, const void* beta, void* y, float* mean, float* rstd,
