@@ -57,7 +57,8 @@ __device__ __forceinline__ float sigmoid_f(float x) { return 1.0f / (1.0f + __ex
 // compiled in, each 32-column chunk jumps over a dozen large unused blocks and the warps wait on instruction fetch
 // rather than on arithmetic.  kEpiAll is the general kernel.
 constexpr uint32_t kEpiBias = 1u, kEpiPreact = 2u, kEpiActFwd = 4u, kEpiActBwd = 8u, kEpiMaskBwd = 16u, kEpiDrop = 32u,
-                   kEpiMaskOut = 64u, kEpiRes = 128u, kEpiF32 = 256u, kEpiBf16 = 512u, kEpiAll = 1023u;
+                   kEpiMaskOut = 64u, kEpiRes = 128u, kEpiF32 = 256u, kEpiBf16 = 512u,
+                   kEpiRagged = 1024u /* N not a multiple of 64: partial column chunks */, kEpiAll = 2047u;
 
 // Features a problem needs (host side).
 inline uint32_t gemm_epilogue_features(const GemmArgs& a) {
@@ -71,6 +72,7 @@ inline uint32_t gemm_epilogue_features(const GemmArgs& a) {
   if (a.mask && a.act != kActMaskBwd) f |= kEpiMaskOut;
   if (a.residual) f |= kEpiRes;
   f |= a.out_fp32 ? kEpiF32 : kEpiBf16;
+  if (a.N % 64) f |= kEpiRagged;
   return f;
 }
 
@@ -79,7 +81,7 @@ __device__ __forceinline__ void gemm_epilogue_chunk(const GemmArgs& p, const Dro
                                                     const bool row_ok, const int col0, const uint32_t taddr,
                                                     uint8_t* stage_row = nullptr, const int stage_half = 0,
                                                     const int stage_r = 0) {
-    const bool full_cols = (col0 + 32 <= p.N);
+    const bool full_cols = !(kFeat & kEpiRagged) || (col0 + 32 <= p.N);
     // global operands of the epilogue are requested BEFORE the TMEM load so their latency overlaps it
     uint4 aux_v[4], res_v[4];
     const bool aux_vec = (kFeat & kEpiActBwd) && row_ok && full_cols && p.act >= kActReluBwd && p.act != kActMaskBwd && (p.ld_aux & 7) == 0;

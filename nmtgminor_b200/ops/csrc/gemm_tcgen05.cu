@@ -36,7 +36,7 @@ struct GemmSmem {
   static constexpr int kTotal = kBarOffset + 256 + 1024;  // barriers + alignment slack
 };
 
-template <int BN>
+template <int BN, uint32_t kFeat>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                     const GemmArgs p) {
@@ -191,7 +191,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       for (int c = chunk_par; c < BN / 32; c += kEpilogueWarps / 4) {
         const int col0 = n0 + c * 32;
         if (col0 >= p.N) break;  // warp-uniform
-        gemm_epilogue_chunk(p, rng, do_drop, row, row_ok, col0,
+        gemm_epilogue_chunk<kFeat>(p, rng, do_drop, row, row_ok, col0,
                             tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN + c * 32);
       }
       tc_fence_before_sync();
@@ -306,17 +306,17 @@ int num_sms() {
   return g_num_sms;
 }
 
-template <int BN>
+template <int BN, uint32_t kFeat = kEpiAll>
 static const char* launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& args, int grid,
                                cudaStream_t stream) {
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, kFeat>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          GemmSmem<BN>::kTotal);
     if (e != cudaSuccess) return cudaGetErrorString(e);
     configured = true;
   }
-  gemm_tcgen05_kernel<BN><<<grid, kGemmThreads, GemmSmem<BN>::kTotal, stream>>>(ta, tb, args);
+  gemm_tcgen05_kernel<BN, kFeat><<<grid, kGemmThreads, GemmSmem<BN>::kTotal, stream>>>(ta, tb, args);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? nullptr : cudaGetErrorString(e);
 }
@@ -395,6 +395,20 @@ const char* nmtg_gemm_bf16(const GemmDesc* d, cudaStream_t stream) {
     if (!ok) return "gemm: cuTensorMapEncodeTiled failed for B";
     const long tiles = static_cast<long>(num_m) * ((d->N + bn - 1) / bn);
     const int grid = static_cast<int>(tiles < sms ? tiles : sms);
+    // decoding steps are latency bound: short specialised epilogues (see gemm_common.cuh) for their two shapes
+    constexpr uint32_t kLinear = kEpiBf16 | kEpiBias | kEpiRes;
+    constexpr uint32_t kActivated = kEpiBf16 | kEpiBias | kEpiActFwd;
+    const uint32_t need = b200::g_pair_generic_epilogue ? kEpiAll : gemm_epilogue_features(a);
+    if ((need & ~kLinear) == 0) {
+      if (bn == 256) return launch_gemm<256, kLinear>(ta, tb, a, grid, stream);
+      if (bn == 128) return launch_gemm<128, kLinear>(ta, tb, a, grid, stream);
+      return launch_gemm<64, kLinear>(ta, tb, a, grid, stream);
+    }
+    if ((need & ~kActivated) == 0) {
+      if (bn == 256) return launch_gemm<256, kActivated>(ta, tb, a, grid, stream);
+      if (bn == 128) return launch_gemm<128, kActivated>(ta, tb, a, grid, stream);
+      return launch_gemm<64, kActivated>(ta, tb, a, grid, stream);
+    }
     if (bn == 256) return launch_gemm<256>(ta, tb, a, grid, stream);
     if (bn == 128) return launch_gemm<128>(ta, tb, a, grid, stream);
     return launch_gemm<64>(ta, tb, a, grid, stream);
