@@ -94,6 +94,33 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   const int num_mn = num_m * num_n;
   const int num_tiles = num_mn * p.split_k;
   const int cluster_id = blockIdx.x >> 1, num_clusters = gridDim.x >> 1;
+  // Work distribution.  Default: whole (tile, split) units dealt round-robin.  p.stream_k (fp32 accumulating output
+  // only): the (tile, k-block) pairs are laid end to end and every cluster takes one contiguous, equally long run of
+  // them, which may end in the middle of a tile; partial tiles meet in the output through the red.add epilogue, so
+  // no fix-up pass is needed and no cluster idles when the tile count is not a multiple of the cluster count.
+  const long sk_total = static_cast<long>(num_mn) * num_kb_total;
+  const long sk_per = sk_total / num_clusters, sk_rem = sk_total % num_clusters;
+  const long sk_begin = cluster_id * sk_per + (cluster_id < sk_rem ? cluster_id : sk_rem);
+  const long sk_end = sk_begin + sk_per + (cluster_id < sk_rem ? 1 : 0);
+  const long first_work = p.stream_k ? sk_begin : cluster_id;
+  auto next_work = [&](long& cursor, int& mn, int& kb_begin, int& kb_end) -> bool {
+    if (!p.stream_k) {
+      if (cursor >= num_tiles) return false;
+      const int tile = static_cast<int>(cursor);
+      mn = tile % num_mn;
+      kb_begin = (tile / num_mn) * kb_per_split;
+      kb_end = min(kb_begin + kb_per_split, num_kb_total);
+      cursor += num_clusters;
+      return true;
+    }
+    if (cursor >= sk_end) return false;
+    mn = static_cast<int>(cursor / num_kb_total);
+    kb_begin = static_cast<int>(cursor % num_kb_total);
+    const long left = sk_end - cursor;
+    kb_end = (kb_begin + left < num_kb_total) ? static_cast<int>(kb_begin + left) : num_kb_total;
+    cursor += kb_end - kb_begin;
+    return true;
+  };
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < S::kStages; ++i) {
@@ -125,11 +152,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
-        const int mn = tile % num_mn, ks = tile / num_mn;
+      long cursor = first_work;
+      int mn, kb_begin, kb_end;
+      while (ok && next_work(cursor, mn, kb_begin, kb_end)) {
         const int m0 = (mn % num_m) * (2 * BM) + static_cast<int>(rank) * BM;   // my 128 rows of the pair tile
         const int n0 = (mn / num_m) * BN + static_cast<int>(rank) * (BN / 2);   // my half of the B tile
-        const int kb_begin = ks * kb_per_split, kb_end = min(kb_begin + kb_per_split, num_kb_total);
         for (int kb = kb_begin; kb < kb_end; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_word, p.status, kTimeoutSmemEmpty)) { ok = false; break; }
           uint8_t* sa = smem + stage * S::kStageBytes;
@@ -167,7 +194,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       // [3] start of the loop until the first operands have landed
       const long long t_begin = kTrace ? clock64() : 0;
       long long t_wait_acc = 0, t_wait_ops = 0, t_first = 0;
-      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters, ++it) {
+      long cursor = first_work;
+      int mn, kb_begin, kb_end;
+      for (; ok && next_work(cursor, mn, kb_begin, kb_end); ++it) {
         const int acc = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
         long long t0 = kTrace ? clock64() : 0;
@@ -175,8 +204,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         if (kTrace) t_wait_acc += clock64() - t0;
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        const int ks = tile / num_mn;
-        const int kb_begin = ks * kb_per_split, kb_end = min(kb_begin + kb_per_split, num_kb_total);
         for (int kb = kb_begin; kb < kb_end; ++kb) {
           t0 = kTrace ? clock64() : 0;
           if (!mbar_wait(&full_bar[stage], phase, abort_word, p.status, kTimeoutTmaFull)) { ok = false; break; }
@@ -225,8 +252,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     const bool tracing = kTrace && p.trace != nullptr && leader && warp == 2 && lane == 0;
     const long long e_begin = tracing ? clock64() : 0;
     long long e_wait = 0, e_last = 0, e_drain = 0, e_chunks = 0, e_issue = 0;
-    for (int tile = cluster_id; tile < num_tiles; tile += num_clusters, ++it) {
-      const int mn = tile % num_mn;
+    long cursor = first_work;
+    int mn, kb_begin, kb_end;
+    for (; next_work(cursor, mn, kb_begin, kb_end); ++it) {
       const int m0 = (mn % num_m) * (2 * BM) + static_cast<int>(rank) * BM;
       const int n0 = (mn / num_m) * BN;
       const int acc = it & 1;
@@ -345,7 +373,7 @@ const char* launch_gemm_pair(const GemmDesc* d, const GemmArgs& a, int bn, cudaS
   }
   const long tiles = static_cast<long>((d->M + 2 * BM - 1) / (2 * BM)) * ((d->N + bn - 1) / bn) * a.split_k;
   const int max_clusters = num_sms() / 2;
-  const int clusters = static_cast<int>(tiles < max_clusters ? tiles : max_clusters);
+  const int clusters = a.stream_k ? max_clusters : static_cast<int>(tiles < max_clusters ? tiles : max_clusters);
   if (bn != 256) return launch_pair<128, false, kEpiAll>(ta, tb, tc, args, clusters * 2, stream);
   if (args.trace != nullptr) return launch_pair<256, true, kEpiAll>(ta, tb, tc, args, clusters * 2, stream);
   // the specialised epilogues of the shapes a training step is made of; anything else takes the general kernel

@@ -14,6 +14,7 @@ struct GemmArgs {
   int M, N, K;
   int a_mn_major, b_mn_major;
   int split_k;             // >= 1; > 1 requires out_fp32 and atomic accumulation
+  int stream_k;            // CTA-pair kernel, fp32 accumulating output: equal runs of (tile, k-block) pairs per cluster
   float alpha;
   const __nv_bfloat16* bias;      // [N] or null
   const __nv_bfloat16* residual;  // [M, ld_res] or null, added last
@@ -220,7 +221,7 @@ __device__ __forceinline__ void gemm_epilogue_chunk(const GemmArgs& p, const Dro
     if ((kFeat & kEpiF32) && (p.out_fp32 || !(kFeat & kEpiBf16))) {
       float* op = reinterpret_cast<float*>(p.out) + static_cast<size_t>(row) * p.ld_out + col0;
       // accumulation into an existing fp32 buffer goes through the L2 reduction unit as well: no read round trip
-      if (p.split_k > 1 || p.accumulate) {
+      if (p.split_k > 1 || p.accumulate || p.stream_k) {
         if (full_cols) {
 #pragma unroll
           for (int g = 0; g < 8; ++g)

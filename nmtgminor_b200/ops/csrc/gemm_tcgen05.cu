@@ -330,6 +330,7 @@ using namespace b200;
 
 static int g_gemm_variant = 0;   // 0 = automatic, 1 = single-CTA kernel only, 2 = CTA-pair kernel whenever M > 128
 static long long* g_gemm_trace = nullptr;   // see nmtg_set_gemm_trace
+static int g_stream_k = 1;       // gemm variant 40 switches the equal-run work split of weight gradients off, 41 on
 static int g_gemm_ablate = 0;    // profiling aid, see GemmArgs::ablate; variants 10 / 11 / 12 select ablation 0 / 1 / 2
 namespace b200 {
 extern int g_pair_tma_store;
@@ -338,7 +339,8 @@ extern int g_pair_generic_epilogue;
 void nmtg_set_gemm_trace(long long* buf) { g_gemm_trace = buf; }
 
 void nmtg_set_gemm_variant(int v) {
-  if (v == 30 || v == 31) b200::g_pair_generic_epilogue = v - 30;
+  if (v == 40 || v == 41) g_stream_k = v - 40;
+  else if (v == 30 || v == 31) b200::g_pair_generic_epilogue = v - 30;
   else if (v == 20 || v == 21) b200::g_pair_tma_store = v - 20;   // 20: per-thread stores, 21: TMA-store epilogue (default)
   else if (v >= 10) g_gemm_ablate = v - 10;
   else g_gemm_variant = v;
@@ -363,6 +365,7 @@ const char* nmtg_gemm_bf16(const GemmDesc* d, cudaStream_t stream) {
   a.preact = reinterpret_cast<__nv_bfloat16*>(d->preact);
   a.mask = reinterpret_cast<uint32_t*>(d->mask); a.ld_mask = d->ld_mask;
   a.ablate = g_gemm_ablate;
+  a.stream_k = 0;
   a.trace = g_gemm_trace;
   if (d->act == kActMaskBwd && !d->mask) return "gemm: the mask-backward epilogue needs a mask";
   a.act = d->act; a.dropout_p = d->dropout_p; a.seed = d->seed; a.stream_id = d->stream_id; a.seed_dev = d->seed_dev;
@@ -426,6 +429,18 @@ const char* nmtg_gemm_bf16(const GemmDesc* d, cudaStream_t stream) {
     }
     if (split > 1 && !d->out_fp32) return "gemm: split-K needs an fp32 output";
     a.split_k = fix_split(split);
+    // weight gradients (fp32, accumulating): when the tiles do not fill the clusters evenly, hand every cluster an
+    // equal run of k-blocks instead of whole tiles
+    // (measured: a gain where whole tiles leave a fifth or more of the clusters idle, and for many-wave problems such
+    // as the generator; a loss of 5-15 % from the extra partial-tile reductions where the tiles nearly fill a wave)
+    const int clusters = sms / 2;
+    const long units = tiles * a.split_k;
+    const double wave_fill = static_cast<double>(units) / (static_cast<double>((units + clusters - 1) / clusters) * clusters);
+    if (g_stream_k && d->out_fp32 && d->accumulate && d->allow_split_k && d->split_k <= 0 && (units % clusters) != 0 &&
+        tiles * num_kb / clusters >= 16 && (wave_fill < 0.8 || tiles >= 4L * clusters)) {
+      a.split_k = 1;
+      a.stream_k = 1;
+    }
     return launch_gemm_pair(d, a, bn, stream);
   }
   // ---- single-CTA kernel: tile width 256 when it does not waste a wave, else 128 -------------------

@@ -130,6 +130,25 @@ def test_gemm_wgrad_fp32_accumulate_split_k(split_k):
     assert _rel_err(acc, want) < 5e-3
 
 
+@pytest.mark.parametrize("tokens,n_out,k_in", [(8192, 3072, 1024), (8000, 4096, 1024), (5000, 1280, 768), (8192, 1024, 2048)])
+@pytest.mark.parametrize("stream_k", [1, 0])
+def test_gemm_wgrad_equal_runs_of_k_blocks(tokens, n_out, k_in, stream_k):
+    """Weight gradients whose tiles do not fill the CTA pairs evenly are split into equal runs of k-blocks that may
+    end inside a tile; the partial tiles meet in the fp32 output through reductions.  Same result either way."""
+    torch.manual_seed(7)
+    dy = torch.randn(tokens, n_out, device=DEV).bfloat16()
+    x = torch.randn(tokens, k_in, device=DEV).bfloat16()
+    acc = torch.full((n_out, k_in), 0.5, device=DEV)
+    ops.ext().set_gemm_variant(40 + stream_k)
+    try:
+        ops.gemm(dy, x, acc, a_mn_major=True, b_mn_major=True, accumulate=True, allow_split_k=True)
+    finally:
+        ops.ext().set_gemm_variant(41)
+    _status_ok()
+    want = dy.float().t() @ x.float() + 0.5
+    assert _rel_err(acc, want) < 5e-3
+
+
 @pytest.mark.parametrize("M,N,K", [(256, 1024, 1024), (256, 1000, 512), (64, 4096, 1024), (256, 32000, 1024)])
 def test_gemm_decode_shapes_bias_and_transposed_weight(M, N, K):
     """Few-row problems take 64-column tiles (many CTAs stream the weight matrix); bias epilogue, ragged N."""
