@@ -119,23 +119,34 @@ ln_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restr
   for (int row = blockIdx.x * kLnWarps + warp; row < rows; row += gridDim.x * kLnWarps) {
     const uint4* dyr = reinterpret_cast<const uint4*>(dy + static_cast<size_t>(row) * hidden);
     const uint4* xr = reinterpret_cast<const uint4*>(x + static_cast<size_t>(row) * hidden);
+    const uint4* rr = dres ? reinterpret_cast<const uint4*>(dres + static_cast<size_t>(row) * hidden) : nullptr;
+    // every global load of the row (dy, x and the residual-path gradient) is issued before anything waits on one;
+    // the operands stay packed in registers and are unpacked again in the second pass
+    uint4 av[VPL], bv[VPL], rv[VPL];
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      const int vi = lane + i * 32;
+      av[i] = bv[i] = rv[i] = make_uint4(0u, 0u, 0u, 0u);
+      if (vi < nvec) {
+        av[i] = dyr[vi];
+        bv[i] = xr[vi];
+        if (rr) rv[i] = rr[vi];
+      }
+    }
     const float mu = mean[row], rs = rstd[row];
-    float dyg[VPL][8], xh[VPL][8];
     float s1 = 0.f, s2 = 0.f;
 #pragma unroll
     for (int i = 0; i < VPL; ++i) {
       const int vi = lane + i * 32;
       if (vi < nvec) {
-        uint4 a = dyr[vi], b = xr[vi], g = __ldg(reinterpret_cast<const uint4*>(gamma) + vi);
-        const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&a);
-        const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&b);
+        const uint4 g = __ldg(reinterpret_cast<const uint4*>(gamma) + vi);
+        const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&av[i]);
+        const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&bv[i]);
         const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&g);
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           float2 d = __bfloat1622float2(a2[j]), xv = __bfloat1622float2(b2[j]), gf = __bfloat1622float2(g2[j]);
           float xh0 = (xv.x - mu) * rs, xh1 = (xv.y - mu) * rs;
-          xh[i][2 * j] = xh0;
-          xh[i][2 * j + 1] = xh1;
           if constexpr (kRegAcc) {
             ag[i][2 * j] += d.x * xh0;
             ag[i][2 * j + 1] += d.y * xh1;
@@ -149,41 +160,32 @@ ln_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restr
             wb[c + 1] += d.y;
           }
           float t0 = d.x * gf.x, t1 = d.y * gf.y;
-          dyg[i][2 * j] = t0;
-          dyg[i][2 * j + 1] = t1;
           s1 += t0 + t1;
           s2 += t0 * xh0 + t1 * xh1;
         }
-      } else {
-#pragma unroll
-        for (int j = 0; j < 8; ++j) dyg[i][j] = xh[i][j] = 0.f;
       }
     }
     s1 = warp_sum(s1) / hidden;
     s2 = warp_sum(s2) / hidden;
     uint4* dxr = reinterpret_cast<uint4*>(dx + static_cast<size_t>(row) * hidden);
-    const uint4* rr = dres ? reinterpret_cast<const uint4*>(dres + static_cast<size_t>(row) * hidden) : nullptr;
 #pragma unroll
     for (int i = 0; i < VPL; ++i) {
       const int vi = lane + i * 32;
       if (vi < nvec) {
-        float add[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        if (rr) {
-          uint4 r = rr[vi];
-          const __nv_bfloat162* r2 = reinterpret_cast<const __nv_bfloat162*>(&r);
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            float2 f = __bfloat1622float2(r2[j]);
-            add[2 * j] = f.x;
-            add[2 * j + 1] = f.y;
-          }
-        }
+        const uint4 g = __ldg(reinterpret_cast<const uint4*>(gamma) + vi);
+        const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&av[i]);
+        const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&bv[i]);
+        const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&g);
+        const __nv_bfloat162* r2 = reinterpret_cast<const __nv_bfloat162*>(&rv[i]);
         uint4 o;
         __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          float d0 = rs * (dyg[i][2 * j] - s1 - xh[i][2 * j] * s2) + add[2 * j];
-          float d1 = rs * (dyg[i][2 * j + 1] - s1 - xh[i][2 * j + 1] * s2) + add[2 * j + 1];
+          float2 d = __bfloat1622float2(a2[j]), xv = __bfloat1622float2(b2[j]), gf = __bfloat1622float2(g2[j]);
+          float2 add = __bfloat1622float2(r2[j]);       // zero when there is no residual-path gradient
+          float xh0 = (xv.x - mu) * rs, xh1 = (xv.y - mu) * rs;
+          float d0 = rs * (d.x * gf.x - s1 - xh0 * s2) + add.x;
+          float d1 = rs * (d.y * gf.y - s1 - xh1 * s2) + add.y;
           o2[j] = __floats2bfloat162_rn(d0, d1);
         }
         dxr[vi] = o;
