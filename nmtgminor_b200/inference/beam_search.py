@@ -7,7 +7,9 @@ continuations ending in EOS are moved into a per-sentence table of finished hypo
 are re-indexed accordingly.  A sentence stops when it has ``beam`` finished hypotheses and its best active
 score can no longer enter the table; the loop ends when all sentences stopped or ``max_len`` is reached.
 The batch is not shrunk when sentences finish (static shapes keep the step graph-capturable); finished
-sentences simply stop contributing.  One ``any()`` read per step is the only host synchronisation.
+sentences simply stop contributing.  On a GPU the loop reads from the device only every fourth step (the "all sentences done" flag), finished sentences
+are masked in between, and the decoder step is replayed as a CUDA graph (``BeamConfig.cuda_graph``); on the CPU one
+``any()`` per step skips the merge of finished hypotheses when no EOS was produced.
 
 Constraints supported: minimum length, maximum length (absolute or ``a * src_len + b``), length-normalised
 scores (``score / len^alpha``), n-gram blocking, forced target prefixes, banned first tokens, vocabulary
