@@ -258,7 +258,7 @@ __global__ void cache_append_kernel(const __nv_bfloat16* __restrict__ k_new, con
 }
 
 // One warp per (row, head).  Scores: one key per lane (the 128-byte key row is read with eight 16-byte loads);
-// values: two output dimensions per lane, probabilities broadcast from shared memory.
+// values: see the second half of the kernel (four positions per load instruction, probabilities from shared memory).
 __global__ void decode_attn_kernel(const __nv_bfloat16* __restrict__ q, long q_ld, const __nv_bfloat16* __restrict__ k_cache,
                                    const __nv_bfloat16* __restrict__ v_cache, const int* __restrict__ lengths,
                                    __nv_bfloat16* __restrict__ out, int R, int heads, int cap, int len_all, int kv_div,
@@ -320,26 +320,47 @@ __global__ void decode_attn_kernel(const __nv_bfloat16* __restrict__ q, long q_l
   for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
   __syncwarp();
   const float inv = sum > 0.f ? 1.f / sum : 0.f;
-  float2 acc = make_float2(0.f, 0.f);
-  int j = 0;
-  for (; j + 4 <= len; j += 4) {
-    float2 v[4];
+  // values: a 128-byte value row is read by eight lanes with one 16-byte load each, so one load instruction of the
+  // warp covers four cache positions; eight such loads (32 positions) are in flight before any is used.  Lane
+  // (sub, part) accumulates dimensions part*8 .. part*8+7 over positions sub, sub+4, ...; the four partial sums of a
+  // dimension are combined with two shuffles.
+  const int sub = lane >> 3, part = lane & 7;
+  float acc[8];
 #pragma unroll
-    for (int u = 0; u < 4; ++u)
-      v[u] = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(vb + static_cast<long>(j + u) * hid + 2 * lane));
+  for (int d = 0; d < 8; ++d) acc[d] = 0.f;
+  for (int j0 = 0; j0 < len; j0 += 32) {
+    uint4 v[8];
+    float pj[8];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      acc.x = fmaf(p[j + u], v[u].x, acc.x);
-      acc.y = fmaf(p[j + u], v[u].y, acc.y);
+    for (int u = 0; u < 8; ++u) {
+      const int j = j0 + u * 4 + sub;
+      const bool in = j < len;
+      v[u] = in ? *reinterpret_cast<const uint4*>(vb + static_cast<long>(j) * hid + part * 8) : make_uint4(0u, 0u, 0u, 0u);
+      pj[u] = in ? p[j] : 0.f;
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&v[u]);
+#pragma unroll
+      for (int d = 0; d < 4; ++d) {
+        const float2 t = __bfloat1622float2(h2[d]);
+        acc[2 * d] = fmaf(pj[u], t.x, acc[2 * d]);
+        acc[2 * d + 1] = fmaf(pj[u], t.y, acc[2 * d + 1]);
+      }
     }
   }
-  for (; j < len; ++j) {
-    const float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(vb + static_cast<long>(j) * hid + 2 * lane));
-    acc.x = fmaf(p[j], v.x, acc.x);
-    acc.y = fmaf(p[j], v.y, acc.y);
+#pragma unroll
+  for (int d = 0; d < 8; ++d) {
+    acc[d] += __shfl_xor_sync(0xffffffffu, acc[d], 8);
+    acc[d] += __shfl_xor_sync(0xffffffffu, acc[d], 16);
   }
-  *reinterpret_cast<__nv_bfloat162*>(out + (static_cast<long>(r) * heads + h) * 64 + 2 * lane) =
-      __floats2bfloat162_rn(acc.x * inv, acc.y * inv);
+  if (sub == 0) {
+    uint4 o;
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int d = 0; d < 4; ++d) o2[d] = __floats2bfloat162_rn(acc[2 * d] * inv, acc[2 * d + 1] * inv);
+    *reinterpret_cast<uint4*>(out + (static_cast<long>(r) * heads + h) * 64 + part * 8) = o;
+  }
 }
 
 }  // namespace
