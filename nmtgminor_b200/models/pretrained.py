@@ -265,8 +265,8 @@ class TextToTextPretrained(Seq2SeqBase):
 def _wav2vec_from_opt(opt):
     """Speech encoder chosen by substring of ``-enc_pretrained_model`` (reference: onmt/model_factory.py:247-272):
     ``s4`` -> state-space encoder on feature frames; ``w2vbert`` / ``w2v-bert`` / ``xeus`` -> Conformer-style encoder on
-    filterbank frames; ``hubert`` / ``wavlm`` / anything else -> the wav2vec 2.0 architecture on raw audio (HuBERT shares
-    it; WavLM's gated relative position bias is not modelled)."""
+    filterbank frames; ``hubert`` / anything else -> the wav2vec 2.0 architecture on raw audio (HuBERT shares it);
+    ``wavlm`` -> the same stack with the gated relative-position bias in every self-attention."""
     cfg = load_json_config(getattr(opt, "enc_config_file", ""))
     name = (getattr(opt, "enc_pretrained_model", "") or "wav2vec2").lower()
     if "s4" in name:
@@ -291,7 +291,9 @@ def _wav2vec_from_opt(opt):
         conv_bias=_cfg(cfg, ["conv_bias"], not base),
         mask_prob=getattr(opt, "wav2vec_spec_augment_mask_prob", 0.0) if hasattr(opt, "wav2vec_spec_augment_mask_prob") else 0.0,
         layerdrop=getattr(opt, "death_rate", 0.0) / 2,
-        freeze_extractor=not getattr(opt, "unfreeze_feature_extractor", False))
+        freeze_extractor=not getattr(opt, "unfreeze_feature_extractor", False),
+        gated_relative_position="wavlm" in name,
+        num_buckets=_cfg(cfg, ["num_buckets"], 320), max_distance=_cfg(cfg, ["max_distance"], 800))
 
 
 def _whisper_sizes(opt):

@@ -24,7 +24,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from .. import ops
-from .layers import EncoderLayer, LayerNorm, Linear, PackedSeqs, pack_padded, sinusoidal_table
+from .layers import EncoderLayer, LayerNorm, Linear, PackedSeqs, SelfAttention, pack_padded, sinusoidal_table
 
 W2V_LARGE_CONV = [(512, 10, 5)] + [(512, 3, 2)] * 4 + [(512, 2, 2)] * 2
 
@@ -131,6 +131,61 @@ class ConvPositionalEmbedding(nn.Module):
         return F.gelu(y).transpose(1, 2)
 
 
+class GatedRelPosSelfAttention(SelfAttention):
+    """WavLM self-attention: a bucketed relative-position bias (one ``[buckets, heads]`` table owned by the first
+    layer and shared by all) is added to the scores after being scaled, per query position and head, by a gate
+    computed from the query: ``g = a * (b * grep_a - 1) + 2`` with ``a, b = sigmoid(sum_4(W q))``.
+
+    The additive bias is not expressible in the packed tensor-core attention kernels, so this sub-layer pads the
+    fused projection and runs PyTorch's scaled-dot-product attention; projections stay on the fused GEMM path.
+    Reference: onmt/models/speech_recognizer/fairseq_wav2vec2/wavlm_modules.py:128-166 (buckets, bias), :236-256 (gate).
+    """
+
+    def __init__(self, dim, heads, attn_dropout=0.0, num_buckets=320, max_distance=800, table_owner=None):
+        super().__init__(dim, heads, attn_dropout, bias=True)
+        self.num_buckets, self.max_distance = num_buckets, max_distance
+        self.relative_attention_bias = nn.Embedding(num_buckets, heads) if table_owner is None else None
+        self._owner = [self if table_owner is None else table_owner]       # in a list: not a registered sub-module
+        self.grep_linear = nn.Linear(dim // heads, 8)
+        self.grep_a = nn.Parameter(torch.ones(1, heads, 1, 1))
+        self._bias_cache = None
+
+    def _buckets(self, rel):
+        nb = self.num_buckets // 2
+        out = (rel > 0).long() * nb
+        rel = rel.abs()
+        max_exact = nb // 2
+        large = max_exact + (torch.log(rel.float().clamp(min=1) / max_exact) / math.log(self.max_distance / max_exact)
+                             * (nb - max_exact)).long()
+        large = large.clamp(max=nb - 1)
+        return out + torch.where(rel < max_exact, rel, large)
+
+    def position_bias(self, T: int, device, key):
+        owner = self._owner[0]
+        if owner._bias_cache is not None and owner._bias_cache[0] == key:
+            return owner._bias_cache[1]
+        pos = torch.arange(T, device=device)
+        bias = owner.relative_attention_bias(owner._buckets(pos[None, :] - pos[:, None])).permute(2, 0, 1)    # [heads, T, T]
+        owner._bias_cache = (key, bias)
+        return bias
+
+    def forward(self, x, seqs: PackedSeqs, residual=None, dropout_p: float = 0.0):
+        from ..ops.reference import pad_packed, unpad_packed
+        H, h = self.dim, self.heads
+        qkv, valid = pad_packed(self.qkv(x), seqs.cu, seqs.max_len)               # [B, T, 3H]
+        B, T, _ = qkv.shape
+        q, k, v = (t.view(B, T, h, H // h).transpose(1, 2) for t in qkv.float().split(H, dim=-1))
+        gate = self.grep_linear(q).view(B, h, T, 2, 4).sum(-1)
+        ga, gb = torch.sigmoid(gate).chunk(2, dim=-1)
+        scale = ga * (gb * self.grep_a - 1.0) + 2.0                                 # [B, h, T, 1]
+        bias = scale * self.position_bias(T, x.device, (id(seqs), torch.is_grad_enabled()))[None].float()
+        bias = bias.masked_fill(~valid[:, None, None, :], float("-inf"))
+        ctx = F.scaled_dot_product_attention(q, k, v, attn_mask=bias, dropout_p=self.attn_dropout if self.training else 0.0)
+        ctx = ctx.transpose(1, 2).reshape(B, T, H) * valid.unsqueeze(-1)
+        ctx = unpad_packed(ctx, seqs.cu, x.shape[0]).to(x.dtype)
+        return self.out(ctx, dropout_p=dropout_p, residual=residual)
+
+
 class Wav2Vec2Encoder(nn.Module):
     """wav2vec 2.0 encoder: conv feature extractor -> LayerNorm -> projection -> time masking -> conv positions ->
     Transformer layers on packed frames.  ``layer_norm_first`` (the *large* recipe) uses pre-LN layers with a final
@@ -139,7 +194,7 @@ class Wav2Vec2Encoder(nn.Module):
     def __init__(self, dim=1024, layers=24, heads=16, ffn=4096, dropout=0.1, attn_dropout=0.1, activation="gelu",
                  layer_norm_first=True, extractor_mode="layer_norm", conv_layers=W2V_LARGE_CONV, conv_bias=False,
                  mask_prob=0.0, mask_length=10, layerdrop=0.0, freeze_extractor=True, pos_kernel=128, pos_groups=16,
-                 dropout_input=0.0):
+                 dropout_input=0.0, gated_relative_position=False, num_buckets=320, max_distance=800):
         super().__init__()
         self.extractor = ConvFeatureExtractor(conv_layers, extractor_mode, conv_bias)
         self.freeze_extractor = freeze_extractor
@@ -157,6 +212,11 @@ class Wav2Vec2Encoder(nn.Module):
         self.layers = nn.ModuleList([
             EncoderLayer(dim, heads, ffn, dropout, attn_dropout, activation, attn_bias=True, death_rate=layerdrop,
                          post_norm=not layer_norm_first) for _ in range(layers)])
+        if gated_relative_position:      # WavLM: every layer's attention gets the gated relative-position bias
+            owner = None
+            for layer in self.layers:
+                layer.attn = GatedRelPosSelfAttention(dim, heads, attn_dropout, num_buckets, max_distance, table_owner=owner)
+                owner = owner or layer.attn
         self.dim = dim
 
     def forward(self, source) -> Tuple[torch.Tensor, PackedSeqs]:

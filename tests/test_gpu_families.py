@@ -77,6 +77,8 @@ def test_speech_families_on_gpu(dicts, tmp_path):
         (["-model", "wav2vec2_bert", "-enc_config_file", enc, "-dec_config_file", dec, "-dec_pretrained_model", "mbart50", "-ctc_loss", "0.3"],
          synthetic_audio_batch(2, 120, "wav", 3000, 6000)),
         (["-model", "wav2vec2_transformer", "-enc_config_file", enc], synthetic_audio_batch(2, 120, "wav", 3000, 6000)),
+        (["-model", "wav2vec2_transformer", "-enc_config_file", enc, "-enc_pretrained_model", "wavlm"],
+         synthetic_audio_batch(2, 120, "wav", 3000, 6000)),
         (["-model", "whisper", "-dec_config_file", wsp], synthetic_audio_batch(2, 120, "feats", n_feats=80, fixed_frames=120)),
         (["-model", "speech_transformer", "-input_size", "40", "-cnn_downsampling"], synthetic_audio_batch(2, 120, "feats", 40, 80, n_feats=40)),
         (["-model", "conformer", "-input_size", "40"], synthetic_audio_batch(2, 120, "feats", 40, 80, n_feats=40)),

@@ -138,3 +138,41 @@ def test_ctc_compression_merges_runs(dicts, tmp_path):
     out = model(synthetic_audio_batch(2, 120, "wav", 3000, 5000))
     out["loss"].backward()
     assert torch.isfinite(out["loss"]) and out["src"].cu[-1] <= out["context_packed"].shape[0]
+
+
+def test_wavlm_gated_relative_position_bias(dicts, tmp_path):
+    """``-enc_pretrained_model wavlm`` puts the gated relative-position attention in every encoder layer; the table is
+    owned by the first layer, the sub-layer matches a direct statement of the formula, and it trains."""
+    from nmtgminor_b200.models.speech_encoders import GatedRelPosSelfAttention
+    from nmtgminor_b200.models.layers import PackedSeqs
+    torch.manual_seed(5)
+    enc = _cfg(tmp_path, "enc.json", encoder_embed_dim=64, encoder_layers=2, encoder_attention_heads=2, encoder_ffn_embed_dim=128,
+               num_buckets=32, max_distance=64)
+    model = build_model(default_options(["-model", "wav2vec2_transformer", "-enc_config_file", enc, "-enc_pretrained_model", "wavlm"]
+                                        + COMMON), dicts)
+    attns = [l.attn for l in model.encoder.layers]
+    assert all(isinstance(a, GatedRelPosSelfAttention) for a in attns)
+    assert attns[0].relative_attention_bias is not None and attns[1].relative_attention_bias is None
+    out = model(synthetic_audio_batch(2, 120, "wav", 3000, 6000))
+    assert torch.isfinite(out["loss"]).all()
+    out["loss"].backward()
+    assert attns[0].relative_attention_bias.weight.grad.abs().sum() > 0 and attns[1].grep_linear.weight.grad.abs().sum() > 0
+
+    # direct statement for one sequence
+    a = attns[0].eval()
+    T, H, h = 9, 64, 2
+    x = torch.randn(T, H)
+    seqs = PackedSeqs.from_padded(torch.ones(1, T, dtype=torch.long), torch.tensor([T]))
+    got = a(x, seqs)
+    qkv = a.qkv(x)
+    q, k, v = (t.view(T, h, H // h).transpose(0, 1) for t in qkv.split(H, -1))
+    pos = torch.arange(T)
+    bias = a.relative_attention_bias(a._buckets(pos[None, :] - pos[:, None])).permute(2, 0, 1)
+    g = torch.sigmoid(a.grep_linear(q).view(h, T, 2, 4).sum(-1))
+    gate = g[..., :1] * (g[..., 1:] * a.grep_a[0] - 1.0) + 2.0
+    p = torch.softmax(q @ k.transpose(1, 2) / (H // h) ** 0.5 + gate * bias, -1)
+    want = a.out((p @ v).transpose(0, 1).reshape(T, H))
+    assert torch.allclose(got, want, atol=1e-5)
+    # buckets: symmetric halves, exact for small offsets, saturating for large ones
+    b = a._buckets(torch.tensor([0, 1, -1, 5, -5, 1000, -1000]))
+    assert b[0] == 0 and b[1] == 16 + 1 and b[2] == 1 and b[5] == 31 and b[6] == 15
