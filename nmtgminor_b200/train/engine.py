@@ -121,6 +121,7 @@ class TrainEngine:
                 reducer = NcclReducer(world)
         self.reducer = reducer            # callable(flat_grad) -> None, data-parallel gradient reduction
         self.grad_scale = grad_scale
+        self.loss_weight = 1.0            # weight of the next batch's gradient (replay weighting in continual learning)
         self.use_graph = bool(cuda_graph) and self.on_gpu
         self._graph = None
         self._static: Optional[_StaticInputs] = None
@@ -138,7 +139,7 @@ class TrainEngine:
         ops.reset_stream_counter()
         # the loss gradient is written pre-scaled by the kernel (scale 1): no [tokens, V] rescale pass in backward
         with nvtx_range("forward", trace):
-            out = self.model(batch, grad_scale=1.0)
+            out = self.model(batch, grad_scale=float(getattr(self, "loss_weight", 1.0)))   # per-step weight of this batch's gradient
         with nvtx_range("backward", trace):
             out["loss"].backward()
         if not self.optim.fused:

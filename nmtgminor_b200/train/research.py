@@ -44,6 +44,7 @@ class Reservoir:
         self.dark_experience = dark_experience
         self.data: Dict[int, tuple] = {}
         self.extras: Dict[int, torch.Tensor] = {}
+        self.lambdas: Dict[int, float] = {}        # dual-primal learning: one Lagrange multiplier per memory slot
         self.num_observed = 0
         self.rng = random.Random(seed)
 
@@ -64,6 +65,7 @@ class Reservoir:
         self.num_observed += 1
         if slot is not None:
             self.data[slot] = sample
+            self.lambdas[slot] = 1.0               # a new sample starts with a fresh multiplier
             if extra is not None:
                 self.extras[slot] = extra.detach().cpu()
             else:
@@ -83,11 +85,12 @@ class Reservoir:
         return stats
 
     def state_dict(self):
-        return {"data": self.data, "extras": self.extras, "num_observed": self.num_observed, "unit": self.unit,
-                "update_method": self.update_method}
+        return {"data": self.data, "extras": self.extras, "lambdas": self.lambdas, "num_observed": self.num_observed,
+                "unit": self.unit, "update_method": self.update_method}
 
     def load_state_dict(self, sd):
         self.data, self.extras = sd["data"], sd.get("extras", {})
+        self.lambdas = sd.get("lambdas", {k: 1.0 for k in self.data})
         self.num_observed, self.unit, self.update_method = sd["num_observed"], sd["unit"], sd["update_method"]
 
 
@@ -218,6 +221,14 @@ class OCLTrainer(Trainer, _FlatAccess):
         self.agem = getattr(opt, "agem_training", False)
         self.agem_sum = getattr(opt, "agem_summation", False)
         self.projections = 0
+        # dual-primal learning (-dpl_training): replayed batches are weighted by a Lagrange multiplier per memory slot;
+        # every -dpl_count updates the multipliers move by lr * (loss per token - -dpl_epsilon), clamped at zero, so
+        # memory whose loss violates the constraint is replayed harder (reference: offline_cl_trainer.py:1141-1223)
+        self.dpl = bool(getattr(opt, "dpl_training", False))
+        self.dpl_epsilon = float(getattr(opt, "dpl_epsilon", 0.0) or 0.0)
+        self.dpl_every = max(1, int(getattr(opt, "dpl_count", 1) or 1))
+        self.dpl_lr = float(getattr(opt, "dpl_lr", 0.1) or 0.1)
+        self._dpl_counter = 0
 
     # one optimisation step on (new batch, memory batches)
     def train_step(self, batch, dataset_id: int = 0):
@@ -235,12 +246,38 @@ class OCLTrainer(Trainer, _FlatAccess):
                 g.add_(ref)
             self.set_flat_grad(g)
         else:
-            for _, _, mb in mem:
+            for slot, _, mb in mem:
+                eng.loss_weight = self.reservoir.lambdas.get(slot, 1.0) if self.dpl else 1.0
                 eng.train_step(mb, update=False)
+            eng.loss_weight = 1.0
             loss, correct = eng.train_step(batch, update=False)
         self._apply_update(batch.tgt_size + sum(mb.tgt_size for _, _, mb in mem))
         self.reservoir.add_sample((dataset_id, batch))
+        if self.dpl:
+            self._dpl_counter += 1
+            if self._dpl_counter >= self.dpl_every:
+                self.update_lambdas()
+                self._dpl_counter = 0
         return loss, correct
+
+    @torch.no_grad()
+    def update_lambdas(self, max_batches: int = 16):
+        """Dual ascent on the multipliers of (a sample of) the memory: ``lambda += lr * (loss per token - epsilon)``,
+        never below zero; the per-slot differences are summed over ranks first."""
+        slots = sorted(self.reservoir.data)
+        if len(slots) > max_batches:
+            slots = sorted(self.reservoir.rng.sample(slots, max_batches))
+        if not slots:
+            return
+        diffs = []
+        for s in slots:
+            _, mb = self.reservoir.data[s]
+            loss, _ = self.engine.eval_step(mb)
+            diffs.append(float(loss) / max(mb.tgt_size, 1) - self.dpl_epsilon)
+        diffs = self._all_reduce_scalars(diffs)
+        for s, d in zip(slots, diffs):
+            self.reservoir.lambdas[s] = max(0.0, self.reservoir.lambdas.get(s, 1.0) + self.dpl_lr * d / max(self.world_size, 1))
+        self.model.train()
 
     def _apply_update(self, n_words: int):
         eng = self.engine

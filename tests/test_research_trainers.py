@@ -94,3 +94,21 @@ def test_gem_meta_bayes_vat_offline_trainers_step():
     _run(R.VATTrainer, ["-ocl_training", "-vat_training", "1"], [_data(5)])
     tr = _run(R.OfflineCLTrainer, ["-offline_cl_training", "-ewc_importance", "10.0"], [_data(6), _data(7)])
     assert tr.ewc.anchor is not None and float(tr.ewc.fisher.sum()) > 0
+
+
+def test_dual_primal_learning_moves_the_memory_multipliers():
+    """``-dpl_training``: replayed batches are weighted by per-slot multipliers, which rise while the memory loss is
+    above ``-dpl_epsilon`` and are clamped at zero when it is far below."""
+    tr = _run(R.OCLTrainer, ["-ocl_training", "-dpl_training", "-dpl_epsilon", "0.0", "-dpl_count", "2"], [_data(11)])
+    lam = tr.reservoir.lambdas
+    assert set(lam) == set(tr.reservoir.data) and all(v >= 0 for v in lam.values())
+    assert any(v > 1.0 for v in lam.values())          # every loss is above a zero constraint
+    assert tr.engine.loss_weight == 1.0                 # the weight is reset after the replay batches
+    tr.dpl_epsilon = 1e6                               # constraint satisfied by a wide margin: multipliers fall to zero
+    for _ in range(40):
+        tr.update_lambdas()
+    assert max(tr.reservoir.lambdas.values()) == 0.0
+    sd = tr.reservoir.state_dict()
+    fresh = R.Reservoir(8)
+    fresh.load_state_dict(sd)
+    assert fresh.lambdas == tr.reservoir.lambdas
