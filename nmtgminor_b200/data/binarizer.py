@@ -79,3 +79,36 @@ def binarize_file(path: str, vocab, tokenizer: Optional[Callable] = None, bos_wo
     data = [t for p in parts for t in p[0]]
     sizes = [s for p in parts for s in p[1]]
     return {"data": data, "sizes": sizes}
+
+
+def binarize_speech_file(path: str, fmt: str = "wav", num_mel_bin: int = 0, concat: int = 1, sample_rate: int = 16000):
+    """Index an utterance list without copying the audio (reference: onmt/data/binarizer.py ``SpeechBinarizer``).
+
+    ``fmt == "wav"``: lines ``utt_id wav_path [start end]`` (seconds) -> entries ``(wav_path, start, end, sample_rate)``;
+    the size of an utterance is its number of samples (or of 10 ms feature frames when ``num_mel_bin > 0``).
+    ``fmt in ("scp", "kaldi")``: lines ``utt_id ark_path:offset`` -> entries ``(ark_path, offset)``; the size is the number
+    of frames after ``concat`` stacking.  Returns ``{"data": entries, "sizes": lengths}`` in file order."""
+    import wave
+    from .audio import read_ark_matrix
+    data, sizes = [], []
+    with open(path, encoding="utf-8") as fh:
+        for line in fh:
+            parts = line.split()
+            if not parts:
+                continue
+            if fmt == "wav":
+                wav_path = parts[1] if len(parts) > 1 else parts[0]
+                start, end = (float(parts[2]), float(parts[3])) if len(parts) >= 4 else (0.0, 0.0)
+                with wave.open(wav_path, "rb") as w:
+                    sr, frames = w.getframerate(), w.getnframes()
+                n = int(round((end - start) * sr)) if end > 0 else frames - int(round(start * sr))
+                n = max(min(n, frames), 0)
+                data.append((wav_path, start, end, sr))
+                sizes.append(n // (sr // 100) if num_mel_bin > 0 else n)
+            else:
+                loc = parts[1] if len(parts) > 1 else parts[0]
+                f, off = loc.rsplit(":", 1)
+                rows = read_ark_matrix(f, int(off)).shape[0]
+                data.append((f, int(off)))
+                sizes.append((rows + concat - 1) // concat)
+    return {"data": data, "sizes": sizes}

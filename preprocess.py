@@ -4,6 +4,9 @@
 Writes, for ``-save_data <name>``:
   * ``-format raw`` / ``bin``:  ``<name>.train.pt`` = {'dicts', 'type', 'train': {'src','tgt','src_sizes','tgt_sizes',
     'src_lang','tgt_lang'}, 'valid': {...}} (lists of id tensors);
+  * ``-asr -asr_format wav|scp -format wav|scp|scpmem``: ``<name>.dict.pt``, ``<name>.{wav,scp}_path.pt`` (utterance index
+    ``{'train': [...], 'valid': [...]}`` of ``(path, start, end, sample_rate)`` / ``(ark, offset)`` entries), memory-mapped
+    targets and ``*_sizes.npy``;
   * ``-format mmap`` / ``mmem``: ``<name>.dict.pt`` plus ``<name>.{train,valid}.{src,tgt,src_lang,tgt_lang}.{bin,idx}`` in
     the MMIDIDX layout and ``<name>.{train,valid}.{src,tgt}_sizes.npy``.
 Same option names and file layouts as the reference (preprocess.py:27-170 options, :1261-1265 save).
@@ -17,7 +20,7 @@ import numpy as np
 import torch
 
 from nmtgminor_b200 import constants as C
-from nmtgminor_b200.data.binarizer import Tokenizer, binarize_file
+from nmtgminor_b200.data.binarizer import Tokenizer, binarize_file, binarize_speech_file
 from nmtgminor_b200.data.mmap_dataset import best_dtype, write_dataset
 from nmtgminor_b200.dictionary import Dict
 from nmtgminor_b200.options import make_preprocess_parser
@@ -44,18 +47,65 @@ def init_vocab(name, files, vocab_file, size, tokenizer, lower=False):
 
 
 def make_data(src_file, tgt_file, src_dict, tgt_dict, opt, tokenizer):
-    src = binarize_file(src_file, src_dict, tokenizer, None, None, opt.num_threads) if src_file else None
+    if getattr(opt, "asr", False):
+        # audio source: an index of utterances (wav segments or Kaldi matrices), never the samples themselves
+        src = binarize_speech_file(src_file, getattr(opt, "asr_format", "wav") or "wav", getattr(opt, "num_mel_bin", 0) or 0,
+                                   getattr(opt, "concat", 1) or 1) if src_file else None
+    else:
+        src = binarize_file(src_file, src_dict, tokenizer, None, None, opt.num_threads) if src_file else None
     tgt = binarize_file(tgt_file, tgt_dict, tokenizer, C.BOS_WORD, C.EOS_WORD, opt.num_threads) if tgt_file else None
     n = len(src["data"]) if src else len(tgt["data"])
     keep = []
     for i in range(n):
         ls = src["sizes"][i] if src else 1
         lt = tgt["sizes"][i] - 2 if tgt else 1
-        if 0 < ls <= opt.src_seq_length and 0 < lt <= opt.tgt_seq_length:
+        src_ok = ls > 0 if getattr(opt, "asr", False) else 0 < ls <= opt.src_seq_length   # audio is not length-filtered here
+        if src_ok and 0 < lt <= opt.tgt_seq_length:
             keep.append(i)
     pick = lambda d: None if d is None else {"data": [d["data"][i] for i in keep], "sizes": [d["sizes"][i] for i in keep]}
     print("Prepared %d sentences (%d ignored due to length)" % (len(keep), n - len(keep)))
     return pick(src), pick(tgt)
+
+
+def write_multi_dataset(opt, dicts, langs, tokenizer):
+    """``-multi_dataset``: every (source file, target file) pair becomes its own data set in a sibling directory
+    ``train.<i>.<src lang>-<tgt lang>/data.*`` (``valid.<i>.…`` likewise) next to ``<save_data>.dict.pt``; the trainer
+    iterates them jointly (reference layout: train_distributed.py:487-545)."""
+    root = os.path.dirname(os.path.abspath(opt.save_data))
+    os.makedirs(root, exist_ok=True)
+    torch.save(dicts, opt.save_data + ".dict.pt")
+    asr = getattr(opt, "asr", False)
+    fmt = getattr(opt, "format", "mmap")
+    for split, s_arg, t_arg, sl_arg, tl_arg in (("train", opt.train_src, opt.train_tgt, getattr(opt, "train_src_lang", "src"),
+                                                 getattr(opt, "train_tgt_lang", "tgt")),
+                                                ("valid", opt.valid_src, opt.valid_tgt, getattr(opt, "valid_src_lang", "src"),
+                                                 getattr(opt, "valid_tgt_lang", "tgt"))):
+        sfiles = s_arg.split("|") if s_arg else []
+        tfiles = t_arg.split("|") if t_arg else []
+        slangs = (sl_arg or "src").split("|")
+        tlangs = (tl_arg or "tgt").split("|")
+        for i in range(max(len(sfiles), len(tfiles))):
+            sl = slangs[i] if i < len(slangs) else slangs[-1]
+            tl = tlangs[i] if i < len(tlangs) else tlangs[-1]
+            for l in (sl, tl):
+                langs.setdefault(l, len(langs))
+            s, t = make_data(sfiles[i] if i < len(sfiles) else None, tfiles[i] if i < len(tfiles) else None,
+                             dicts.get("src"), dicts["tgt"], opt, tokenizer)
+            d = os.path.join(root, "%s.%d.%s-%s" % (split, i, sl, tl))
+            os.makedirs(d, exist_ok=True)
+            if s is not None:
+                if asr:
+                    torch.save(s["data"], os.path.join(d, "data.scp_path.pt"))       # the reference uses this name for wav lists too
+                else:
+                    write_dataset(os.path.join(d, "data.src"), s["data"], best_dtype(dicts["src"].size()))
+                np.save(os.path.join(d, "data.src_sizes.npy"), np.asarray(s["sizes"]))
+            if t is not None:
+                write_dataset(os.path.join(d, "data.tgt"), t["data"], best_dtype(dicts["tgt"].size()))
+                np.save(os.path.join(d, "data.tgt_sizes.npy"), np.asarray(t["sizes"]))
+            write_dataset(os.path.join(d, "data.src_lang"), [torch.tensor([langs[sl]])], np.int32)
+            write_dataset(os.path.join(d, "data.tgt_lang"), [torch.tensor([langs[tl]])], np.int32)
+            print("Saved %s set %d (%s-%s, %s) to %s" % (split, i, sl, tl, fmt, d))
+    torch.save(dicts, opt.save_data + ".dict.pt")      # the language table may have grown
 
 
 def main(argv=None):
@@ -77,6 +127,9 @@ def main(argv=None):
         langs.setdefault(l, len(langs))
     dicts["langs"] = langs
     dicts["atbs"] = {"nothingness": 0}
+
+    if getattr(opt, "multi_dataset", False):
+        return write_multi_dataset(opt, dicts, langs, tokenizer)
 
     sets = {}
     for split, sfiles, tfiles in (("train", train_src, train_tgt),
@@ -113,8 +166,23 @@ def main(argv=None):
             for side in ("src_lang", "tgt_lang"):
                 write_dataset("%s.%s.%s" % (opt.save_data, split, side), sets[split][side], np.int32)
         print("Saved mmap data to %s.*" % opt.save_data)
+    elif fmt in ("wav", "scp", "scpmem"):
+        # audio: <name>.{wav,scp}_path.pt = {'train': entries, 'valid': entries}; targets memory-mapped; sizes as .npy
+        assert getattr(opt, "asr", False), "-format %s needs -asr (the source side is an utterance list)" % fmt
+        torch.save(dicts, opt.save_data + ".dict.pt")
+        torch.save({"train": sets["train"]["src"], "valid": sets["valid"]["src"]},
+                   opt.save_data + (".wav_path.pt" if fmt == "wav" else ".scp_path.pt"))
+        for split in ("train", "valid"):
+            if sets[split]["tgt"] is not None:
+                write_dataset("%s.%s.tgt" % (opt.save_data, split), sets[split]["tgt"], best_dtype(dicts["tgt"].size()))
+            for side in ("src", "tgt"):
+                if sets[split][side + "_sizes"] is not None:
+                    np.save("%s.%s.%s_sizes.npy" % (opt.save_data, split, side), np.asarray(sets[split][side + "_sizes"]))
+            for side in ("src_lang", "tgt_lang"):
+                write_dataset("%s.%s.%s" % (opt.save_data, split, side), sets[split][side], np.int32)
+        print("Saved %s utterance index and targets to %s.*" % (fmt, opt.save_data))
     else:
-        raise NotImplementedError("format %r: audio formats are handled by preprocess with -asr (scp / wav lists)" % fmt)
+        raise NotImplementedError("format %r" % fmt)
 
 
 if __name__ == "__main__":

@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Training entry point: one process per GPU.
 
-    python train_distributed.py -data <prefix> -data_format raw|bin|mmap -save_model <path> -gpus 0 1 2 3 ...
+    python train_distributed.py -data <prefix> -data_format raw|bin|mmap|wav|scp -save_model <path> -gpus 0 1 2 3 ...
 
 Loads the preprocessed corpus, builds token-budget ``Dataset`` objects, then either runs the trainer in this
 process (one GPU / CPU) or spawns one process per listed GPU (``torch.multiprocessing.spawn``), each of which
@@ -35,8 +35,44 @@ def _dataset_from(split, opt, dicts, training):
                    cleaning=training, verbose=True)
 
 
+def load_multi_datasets(opt):
+    """``-multi_dataset``: one data set per directory ``train.<i>.<langs>/data.*`` / ``valid.<i>.<langs>/data.*`` next to
+    ``<data>.dict.pt`` (reference: train_distributed.py:487-545); returns lists that the trainer iterates jointly."""
+    from nmtgminor_b200.data.audio import SCPDataset, WavDataset
+    dicts = torch.load(opt.data + ".dict.pt", map_location="cpu", weights_only=False)
+    root = os.path.dirname(os.path.abspath(opt.data))
+    fmt = opt.data_format
+    found = {"train": {}, "valid": {}}
+    for d in os.listdir(root):
+        parts = d.split(".")
+        if os.path.isdir(os.path.join(root, d)) and parts[0] in found and len(parts) > 1 and parts[1].isdigit():
+            found[parts[0]][int(parts[1])] = os.path.join(root, d)
+    if fmt in ("wav", "scp", "scpmem") and getattr(opt, "encoder_type", "text") == "text":
+        opt.encoder_type = "audio"
+
+    def one(d, training):
+        mm = lambda name: MMapIndexedDataset(os.path.join(d, name)) if MMapIndexedDataset.exists(os.path.join(d, name)) else None
+        if fmt in ("wav", "scp", "scpmem"):
+            entries = torch.load(os.path.join(d, "data.scp_path.pt"), map_location="cpu", weights_only=False)
+            proc = getattr(opt, "wav_processor", None)
+            src = (WavDataset(entries, proc if proc in ("fbank", "whisper") else None, getattr(opt, "num_mel_bin", 0) or 80)
+                   if fmt == "wav" else SCPDataset(entries, getattr(opt, "concat", 1) or 1))
+        else:
+            src = mm("data.src")
+        sizes = lambda name: np.load(os.path.join(d, name)) if os.path.exists(os.path.join(d, name)) else None
+        split = {"src": src, "tgt": mm("data.tgt"), "src_lang": mm("data.src_lang"), "tgt_lang": mm("data.tgt_lang"),
+                 "src_atb": mm("data.src_atb"), "tgt_atb": mm("data.tgt_atb"),
+                 "src_sizes": sizes("data.src_sizes.npy"), "tgt_sizes": sizes("data.tgt_sizes.npy")}
+        return _dataset_from(split, opt, dicts, training)
+    train = [one(d, True) for _, d in sorted(found["train"].items())]
+    valid = [one(d, False) for _, d in sorted(found["valid"].items())]
+    return dicts, train, (valid or None)
+
+
 def load_data(opt):
     fmt = opt.data_format
+    if getattr(opt, "multi_dataset", False):
+        return load_multi_datasets(opt)
     if fmt in ("raw", "bin"):
         blob = torch.load(opt.data + ".train.pt", map_location="cpu", weights_only=False)
         dicts = blob["dicts"]
@@ -47,6 +83,35 @@ def load_data(opt):
         def side(split):
             out = {}
             for s in ("src", "tgt", "src_lang", "tgt_lang"):
+                prefix = "%s.%s.%s" % (opt.data, split, s)
+                out[s] = MMapIndexedDataset(prefix) if MMapIndexedDataset.exists(prefix) else None
+            for s in ("src", "tgt"):
+                f = "%s.%s.%s_sizes.npy" % (opt.data, split, s)
+                out[s + "_sizes"] = np.load(f) if os.path.exists(f) else None
+            return out
+        train, valid = side("train"), side("valid")
+    elif fmt in ("wav", "scp", "scpmem"):
+        from nmtgminor_b200.data.audio import SCPDataset, WavDataset
+        dicts = torch.load(opt.data + ".dict.pt", map_location="cpu", weights_only=False)
+        index = torch.load(opt.data + (".wav_path.pt" if fmt == "wav" else ".scp_path.pt"), map_location="cpu", weights_only=False)
+        if getattr(opt, "encoder_type", "text") == "text":
+            opt.encoder_type = "audio"
+
+        def side(split):
+            entries = index.get(split)
+            if not entries:
+                return None
+            if fmt == "wav":
+                replace = getattr(opt, "wav_path_replace", None)
+                if replace and len(replace) == 2:
+                    entries = [(e[0].replace(replace[0], replace[1]),) + tuple(e[1:]) for e in entries]
+                proc = getattr(opt, "wav_processor", None)
+                src = WavDataset(entries, proc if proc in ("fbank", "whisper") else None, getattr(opt, "num_mel_bin", 0) or 80,
+                                 cache_size=getattr(opt, "data_cache_size", 64) or 64)
+            else:
+                src = SCPDataset(entries, getattr(opt, "concat", 1) or 1)
+            out = {"src": src}
+            for s in ("tgt", "src_lang", "tgt_lang"):
                 prefix = "%s.%s.%s" % (opt.data, split, s)
                 out[s] = MMapIndexedDataset(prefix) if MMapIndexedDataset.exists(prefix) else None
             for s in ("src", "tgt"):
