@@ -133,7 +133,7 @@ class Translator:
         pick = lambda name: torch.full((n,), int(langs.get(name, 0)), dtype=torch.long)
         return pick(getattr(self.opt, "src_lang", "src")), pick(getattr(self.opt, "tgt_lang", "tgt"))
 
-    def build_data(self, src_sents, tgt_sents: Optional[List[List[str]]] = None):
+    def build_data(self, src_sents, tgt_sents: Optional[List[List[str]]] = None, past_sents: Optional[List[List[str]]] = None):
         """``src_sents``: token lists (text models) or ``[frames, features]`` tensors (audio models: ``-encoder_type
         audio`` / ``-asr_format``; a leading channel of ones marks real frames, as in training batches)."""
         audio = len(src_sents) > 0 and torch.is_tensor(src_sents[0])
@@ -145,7 +145,12 @@ class Translator:
         if tgt_sents:
             tgt = [self.tgt_dict.convert_to_idx(t, C.UNK_WORD, C.BOS_WORD, C.EOS_WORD) for t in tgt_sents]
         sl, tl = self._lang_ids(len(src))
-        return collate(src, tgt, src_lang=sl, tgt_lang=tl, src_type="audio" if audio else "text", padded=True, packed=True, round_to=1)
+        past = None
+        if past_sents and not audio:
+            # an empty previous sentence (document start) is represented by a single padding symbol
+            past = [self.src_dict.convert_to_idx(p, C.UNK_WORD) if p else torch.tensor([C.PAD]) for p in past_sents]
+        return collate(src, tgt, src_lang=sl, tgt_lang=tl, src_type="audio" if audio else "text", padded=True, packed=True, round_to=1,
+                       past_src_data=past)
 
     def translate_batch(self, batch, prefix_tokens=None, banned_first=None) -> List[List[Hypothesis]]:
         if self.cuda:
@@ -153,10 +158,10 @@ class Translator:
         return beam_search(self.model, batch, self.cfg, prefix_tokens, banned_first)
 
     def translate(self, src_sents, tgt_sents: Optional[List[List[str]]] = None, prefix: Optional[List[List[str]]] = None,
-                  anti_prefix: Optional[List[str]] = None):
+                  anti_prefix: Optional[List[str]] = None, past_sents: Optional[List[List[str]]] = None):
         """``prefix``: tokens every hypothesis of sentence i must start with (``-prefix_string`` gives one prefix for
         all sentences); ``anti_prefix``: tokens that may not open a hypothesis (``-anti_prefix_string``)."""
-        batch = self.build_data(src_sents, tgt_sents)
+        batch = self.build_data(src_sents, tgt_sents, past_sents)
         if prefix is None and getattr(self.opt, "prefix_string", None):
             prefix = [str(self.opt.prefix_string).split()] * len(src_sents)
         if anti_prefix is None and getattr(self.opt, "anti_prefix_string", None):

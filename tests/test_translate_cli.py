@@ -56,3 +56,35 @@ def test_audio_translation_from_scp(tmp_path):
     translate_cli.main(["-model", ck, "-src", str(scp), "-output", str(out), "-gpu", "-1", "-beam_size", "2", "-max_sent_length", "5",
                         "-encoder_type", "audio", "-asr_format", "scp", "-batch_size", "2"])
     assert len(out.read_text().splitlines()) == 2
+
+
+def test_document_context_translation_with_past_src(tmp_path):
+    """``-past_src``: the previous source sentence reaches a document-context model and changes its output
+    distribution; data sets carry it through ``past_src_data``."""
+    from nmtgminor_b200.data.dataset import Dataset
+    from nmtgminor_b200.inference.translator import Translator
+    torch.manual_seed(3)
+    d = synthetic_dict(40)
+    opt = default_options(["-model", "discourse_translator"] + COMMON + ["-tie_weights", "-join_embedding"])
+    ck = str(tmp_path / "disc.pt")
+    save_checkpoint(ck, build_model(opt, {"src": d, "tgt": d}), {"src": d, "tgt": d}, opt, 1.0)
+    src, past, out = tmp_path / "src.txt", tmp_path / "past.txt", tmp_path / "out.txt"
+    src.write_text("w1 w2 w3\nw4 w5\nw6 w7\n")
+    past.write_text("\nw1 w2 w3\nw4 w5\n")                      # first line: document start
+    base = ["-model", ck, "-src", str(src), "-output", str(out), "-gpu", "-1", "-beam_size", "2", "-max_sent_length", "5", "-batch_size", "2"]
+    translate_cli.main(base + ["-past_src", str(past)])
+    assert len(out.read_text().splitlines()) == 3
+    tr = Translator(translate_cli.make_translate_parser().parse_args(base))
+    sents = [["w4", "w5"], ["w6", "w7"]]
+    b0 = tr.build_data(sents, [["w9"], ["w9"]])
+    b1 = tr.build_data(sents, [["w9"], ["w9"]], past_sents=[["w1", "w2", "w3"], ["w4", "w5"]])
+    assert b0.get("packed_past_source") is None and b1.get("packed_past_source").batch_size == 2
+    assert b1.get("past_source").shape == (3, 2)
+    _, s0, _ = tr.model.decode(b0)
+    _, s1, _ = tr.model.decode(b1)
+    assert not torch.allclose(s0, s1)
+    # training data sets hand the previous sentence to the batch as well
+    ids = [d.convert_to_idx(s, "<unk>") for s in sents]
+    tgt = [d.convert_to_idx(["w9"], "<unk>", "<s>", "</s>") for _ in sents]
+    ds = Dataset(ids, tgt, past_src_data=[ids[1], ids[0]], batch_size_words=64, cleaning=False)
+    assert ds.get_batch(0).get("packed_past_source") is not None

@@ -73,16 +73,20 @@ def main(argv=None):
         translator.cfg.diversity_rate = 0.5
     out = open(opt.output, "w", encoding="utf-8") if opt.output and opt.output != "stdout" else sys.stdout
     tgt_f = open(opt.tgt, encoding="utf-8") if getattr(opt, "tgt", None) else None
+    # -past_src: the previous source sentence of every line (document-context models); an empty line = document start
+    past_f = open(opt.past_src, encoding="utf-8") if getattr(opt, "past_src", None) else None
+    past_batch = []
     pred_score_total = pred_words_total = gold_score_total = gold_words_total = 0.0
     src_batch, tgt_batch, count = [], [], 0
     t0 = time.time()
 
     def flush():
-        nonlocal pred_score_total, pred_words_total, gold_score_total, gold_words_total, count, src_batch, tgt_batch
+        nonlocal pred_score_total, pred_words_total, gold_score_total, gold_words_total, count, src_batch, tgt_batch, past_batch
         if not src_batch:
             return
+        extra = {"past_sents": past_batch} if past_batch else {}
         pred_batch, pred_ids, pred_score, pred_pos, pred_len, gold_score, gold_words, allgold = translator.translate(
-            src_batch, tgt_batch if tgt_batch else None)
+            src_batch, tgt_batch if tgt_batch else None, **extra)
         for b in range(len(src_batch)):
             count += 1
             best = get_sentence_from_tokens(pred_batch[b][0], getattr(opt, "input_type", "word"))
@@ -107,7 +111,7 @@ def main(argv=None):
         if tgt_batch:
             gold_words_total += gold_words
         out.flush()
-        src_batch, tgt_batch = [], []
+        src_batch, tgt_batch, past_batch = [], [], []
 
     if getattr(opt, "encoder_type", "text") == "audio":
         # audio input: a Kaldi scp of feature matrices (``-asr_format scp``) or a list of wav paths (``wav``), one
@@ -130,6 +134,8 @@ def main(argv=None):
             src_batch.append(toks)
             if tgt_f is not None:
                 tgt_batch.append(tgt_f.readline().split())
+            if past_f is not None:
+                past_batch.append(past_f.readline().split())
             if len(src_batch) >= opt.batch_size:
                 flush()
     flush()
@@ -142,6 +148,8 @@ def main(argv=None):
         out.close()
     if tgt_f is not None:
         tgt_f.close()
+    if past_f is not None:
+        past_f.close()
 
 
 if __name__ == "__main__":
