@@ -112,3 +112,15 @@ def binarize_speech_file(path: str, fmt: str = "wav", num_mel_bin: int = 0, conc
                 data.append((f, int(off)))
                 sizes.append((rows + concat - 1) // concat)
     return {"data": data, "sizes": sizes}
+
+
+def load_external_tokenizer(name: str, lang: Optional[str] = None):
+    """``-external_tokenizer <name or path>``: a Hugging Face tokenizer turns a raw line into ids (with its own special
+    symbols), instead of the whitespace tokeniser + dictionary lookup.  ``name`` is a local directory or a model name that
+    is present in the local cache (nothing is downloaded).  Returns ``line -> list of ids``
+    (reference: onmt/data/binarizer.py, ``external_tokenizer`` branches)."""
+    from transformers import AutoTokenizer
+    tok = AutoTokenizer.from_pretrained(name, local_files_only=True)
+    if lang and hasattr(tok, "src_lang"):
+        tok.src_lang = lang
+    return lambda line: tok(line)["input_ids"]

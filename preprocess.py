@@ -47,13 +47,19 @@ def init_vocab(name, files, vocab_file, size, tokenizer, lower=False):
 
 
 def make_data(src_file, tgt_file, src_dict, tgt_dict, opt, tokenizer):
+    external = None
+    if getattr(opt, "external_tokenizer", ""):
+        from nmtgminor_b200.data.binarizer import load_external_tokenizer
+        external = load_external_tokenizer(opt.external_tokenizer)
     if getattr(opt, "asr", False):
         # audio source: an index of utterances (wav segments or Kaldi matrices), never the samples themselves
         src = binarize_speech_file(src_file, getattr(opt, "asr_format", "wav") or "wav", getattr(opt, "num_mel_bin", 0) or 0,
                                    getattr(opt, "concat", 1) or 1) if src_file else None
     else:
-        src = binarize_file(src_file, src_dict, tokenizer, None, None, opt.num_threads) if src_file else None
-    tgt = binarize_file(tgt_file, tgt_dict, tokenizer, C.BOS_WORD, C.EOS_WORD, opt.num_threads) if tgt_file else None
+        src = binarize_file(src_file, src_dict, tokenizer, None, None, opt.num_threads, external=external) if src_file else None
+    # an external tokenizer adds its own sentence delimiters
+    tgt = binarize_file(tgt_file, tgt_dict, tokenizer, None if external else C.BOS_WORD, None if external else C.EOS_WORD,
+                        opt.num_threads, external=external) if tgt_file else None
     n = len(src["data"]) if src else len(tgt["data"])
     keep = []
     for i in range(n):

@@ -107,3 +107,20 @@ def test_multi_dataset_directories(tmp_path):
     assert len(train) == 2 and len(valid) == 1
     b = train[1].get_batch(0)
     assert int(b.get("target_lang")[0]) == 2 and int(b.get("source_lang")[0]) == 0
+
+
+def test_external_tokenizer_from_a_local_directory(tmp_path):
+    """``-external_tokenizer <dir>``: ids come from a Hugging Face tokenizer stored locally."""
+    tokenizers = __import__("pytest").importorskip("tokenizers")
+    from transformers import PreTrainedTokenizerFast
+    from nmtgminor_b200.data.binarizer import binarize_file, load_external_tokenizer
+    vocab = {"<pad>": 0, "<unk>": 1, "<s>": 2, "</s>": 3, "hello": 4, "world": 5}
+    tk = tokenizers.Tokenizer(tokenizers.models.WordLevel(vocab, unk_token="<unk>"))
+    tk.pre_tokenizer = tokenizers.pre_tokenizers.Whitespace()
+    PreTrainedTokenizerFast(tokenizer_object=tk, unk_token="<unk>", pad_token="<pad>").save_pretrained(str(tmp_path / "tok"))
+    ext = load_external_tokenizer(str(tmp_path / "tok"))
+    assert ext("hello world foo") == [4, 5, 1]
+    f = tmp_path / "t.txt"
+    f.write_text("hello world\nworld\n")
+    out = binarize_file(str(f), None, None, None, None, 1, external=ext)
+    assert [t.tolist() for t in out["data"]] == [[4, 5], [5]] and out["sizes"] == [2, 1]
