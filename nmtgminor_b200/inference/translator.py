@@ -31,16 +31,20 @@ from .beam_search import BeamConfig, Hypothesis, beam_search
 class EnsembleModel(torch.nn.Module):
     """Presents several models as one for beam search by combining their next-token distributions."""
 
-    def __init__(self, models, op: str = "mean", weights: Optional[Sequence[float]] = None):
+    def __init__(self, models, op: str = "mean", weights: Optional[Sequence[float]] = None, sub_flags: Optional[Sequence[bool]] = None):
         super().__init__()
         self.models = torch.nn.ModuleList(models)
+        # members flagged here read the batch's ``sub_batch`` (``-sub_model`` / ``-sub_src``: e.g. a text model fed the
+        # transcript next to a speech model fed the audio) instead of the main batch
+        self.sub_flags = list(sub_flags) if sub_flags else [False] * len(models)
         self.op = op
         w = list(weights) if weights else [1.0] * len(models)
         s = sum(w)
         self.weights = [x / s for x in w]
 
     def create_decoder_state(self, batch, beam_size, **kw):
-        return _EnsembleState([m.create_decoder_state(batch, beam_size, **kw) for m in self.models])
+        pick = lambda sub: batch.sub_batch if (sub and getattr(batch, "sub_batch", None) is not None) else batch
+        return _EnsembleState([m.create_decoder_state(pick(sub), beam_size, **kw) for m, sub in zip(self.models, self.sub_flags)])
 
     def step(self, input_t, state):
         outs = [m.step(input_t, s)["log_prob"] for m, s in zip(self.models, state.states)]
@@ -90,14 +94,19 @@ class Translator:
         models = []
         self.src_dict = self.tgt_dict = None
         self.model_opts = []
-        for path in str(opt.model).split("|"):
+        main_paths = str(opt.model).split("|")
+        sub_paths = [p for p in str(getattr(opt, "sub_model", "") or "").split("|") if p]
+        self.sub_src_dict = None
+        for path in main_paths + sub_paths:
             ckpt = load_checkpoint(path)
             mopt = backward_compatible(ckpt["opt"])
             dicts = ckpt["dicts"]
-            if self.src_dict is None:
+            if self.src_dict is None and self.tgt_dict is None:
                 self.src_dict = dicts.get("src")
                 self.tgt_dict = dicts["tgt"]
                 self.dicts = dicts
+            if len(models) >= len(main_paths) and self.sub_src_dict is None:
+                self.sub_src_dict = dicts.get("src")            # source vocabulary of the first sub-model
             model = build_model(mopt, dicts, remove_pretrain=True)
             load_model_state(model, ckpt["model"])
             model.renew_buffer(getattr(opt, "max_sent_length", 256) + 2)
@@ -113,7 +122,8 @@ class Translator:
         weights = None
         if getattr(opt, "ensemble_weight", ""):
             weights = [float(x) for x in str(opt.ensemble_weight).split("|")]
-        self.model = models[0] if len(models) == 1 else EnsembleModel(models, getattr(opt, "ensemble_op", "mean"), weights)
+        self.model = models[0] if len(models) == 1 else EnsembleModel(
+            models, getattr(opt, "ensemble_op", "mean"), weights, [False] * len(main_paths) + [True] * len(sub_paths))
         self.bos = self.tgt_dict.lookup(getattr(opt, "bos_token", C.BOS_WORD), C.BOS) if hasattr(self.tgt_dict, "lookup") else C.BOS
         self.eos = self.tgt_dict.lookup(C.EOS_WORD, C.EOS) if hasattr(self.tgt_dict, "lookup") else C.EOS
         self.pad = C.PAD
@@ -155,13 +165,20 @@ class Translator:
     def translate_batch(self, batch, prefix_tokens=None, banned_first=None) -> List[List[Hypothesis]]:
         if self.cuda:
             batch = batch.cuda(self.device)
+            if getattr(batch, "sub_batch", None) is not None:
+                batch.sub_batch = batch.sub_batch.cuda(self.device)
         return beam_search(self.model, batch, self.cfg, prefix_tokens, banned_first)
 
     def translate(self, src_sents, tgt_sents: Optional[List[List[str]]] = None, prefix: Optional[List[List[str]]] = None,
-                  anti_prefix: Optional[List[str]] = None, past_sents: Optional[List[List[str]]] = None):
+                  anti_prefix: Optional[List[str]] = None, past_sents: Optional[List[List[str]]] = None,
+                  sub_src_sents: Optional[List[List[str]]] = None):
         """``prefix``: tokens every hypothesis of sentence i must start with (``-prefix_string`` gives one prefix for
         all sentences); ``anti_prefix``: tokens that may not open a hypothesis (``-anti_prefix_string``)."""
         batch = self.build_data(src_sents, tgt_sents, past_sents)
+        if sub_src_sents and self.sub_src_dict is not None:
+            # ``-sub_src``: the sub-models' own source side (same sentences, same order)
+            sub = [self.sub_src_dict.convert_to_idx(s, C.UNK_WORD) for s in sub_src_sents]
+            batch.sub_batch = collate(sub, None, src_type="text", padded=True, packed=True, round_to=1)
         if prefix is None and getattr(self.opt, "prefix_string", None):
             prefix = [str(self.opt.prefix_string).split()] * len(src_sents)
         if anti_prefix is None and getattr(self.opt, "anti_prefix_string", None):

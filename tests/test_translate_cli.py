@@ -88,3 +88,29 @@ def test_document_context_translation_with_past_src(tmp_path):
     tgt = [d.convert_to_idx(["w9"], "<unk>", "<s>", "</s>") for _ in sents]
     ds = Dataset(ids, tgt, past_src_data=[ids[1], ids[0]], batch_size_words=64, cleaning=False)
     assert ds.get_batch(0).get("packed_past_source") is not None
+
+
+def test_sub_model_reads_its_own_source(tmp_path):
+    """``-sub_model`` / ``-sub_src``: a second model joins the ensemble but encodes a different source file."""
+    from nmtgminor_b200.inference.translator import EnsembleModel, Translator
+    torch.manual_seed(4)
+    d = synthetic_dict(40)
+    dicts = {"src": d, "tgt": d}
+    opt = default_options(COMMON + ["-tie_weights", "-join_embedding"])
+    main_ck, sub_ck = str(tmp_path / "main.pt"), str(tmp_path / "sub.pt")
+    save_checkpoint(main_ck, build_model(opt, dicts), dicts, opt, 1.0)
+    save_checkpoint(sub_ck, build_model(opt, dicts), dicts, opt, 1.0)
+    src, sub, out = tmp_path / "src.txt", tmp_path / "sub.txt", tmp_path / "out.txt"
+    src.write_text("w1 w2 w3\nw4 w5\n")
+    sub.write_text("w9 w8\nw7 w6 w5 w4\n")
+    base = ["-model", main_ck, "-sub_model", sub_ck, "-src", str(src), "-output", str(out), "-gpu", "-1", "-beam_size", "2",
+            "-max_sent_length", "5", "-batch_size", "2"]
+    translate_cli.main(base + ["-sub_src", str(sub)])
+    assert len(out.read_text().splitlines()) == 2
+    tr = Translator(translate_cli.make_translate_parser().parse_args(base))
+    assert isinstance(tr.model, EnsembleModel) and tr.model.sub_flags == [False, True]
+    sents, other = [["w1", "w2", "w3"], ["w4", "w5"]], [["w9", "w8"], ["w7", "w6", "w5", "w4"]]
+    batch = tr.build_data(sents)
+    batch.sub_batch = tr.build_data(other)
+    state = tr.model.create_decoder_state(batch, 1)
+    assert state.states[0].context.shape[1] == 3 and state.states[1].context.shape[1] == 4     # each member saw its own source

@@ -76,15 +76,20 @@ def main(argv=None):
     # -past_src: the previous source sentence of every line (document-context models); an empty line = document start
     past_f = open(opt.past_src, encoding="utf-8") if getattr(opt, "past_src", None) else None
     past_batch = []
+    # -sub_src: the source side read by the -sub_model members of the ensemble, line by line parallel to -src
+    sub_f = open(opt.sub_src, encoding="utf-8") if getattr(opt, "sub_src", None) else None
+    sub_batch = []
     pred_score_total = pred_words_total = gold_score_total = gold_words_total = 0.0
     src_batch, tgt_batch, count = [], [], 0
     t0 = time.time()
 
     def flush():
-        nonlocal pred_score_total, pred_words_total, gold_score_total, gold_words_total, count, src_batch, tgt_batch, past_batch
+        nonlocal pred_score_total, pred_words_total, gold_score_total, gold_words_total, count, src_batch, tgt_batch, past_batch, sub_batch
         if not src_batch:
             return
         extra = {"past_sents": past_batch} if past_batch else {}
+        if sub_batch:
+            extra["sub_src_sents"] = sub_batch
         pred_batch, pred_ids, pred_score, pred_pos, pred_len, gold_score, gold_words, allgold = translator.translate(
             src_batch, tgt_batch if tgt_batch else None, **extra)
         for b in range(len(src_batch)):
@@ -111,7 +116,7 @@ def main(argv=None):
         if tgt_batch:
             gold_words_total += gold_words
         out.flush()
-        src_batch, tgt_batch, past_batch = [], [], []
+        src_batch, tgt_batch, past_batch, sub_batch = [], [], [], []
 
     if getattr(opt, "encoder_type", "text") == "audio":
         # audio input: a Kaldi scp of feature matrices (``-asr_format scp``) or a list of wav paths (``wav``), one
@@ -120,6 +125,8 @@ def main(argv=None):
             src_batch.append(feats)
             if tgt_f is not None:
                 tgt_batch.append(tgt_f.readline().split())
+            if sub_f is not None:
+                sub_batch.append(sub_f.readline().split())
             if len(src_batch) >= opt.batch_size:
                 flush()
         flush()
@@ -136,6 +143,8 @@ def main(argv=None):
                 tgt_batch.append(tgt_f.readline().split())
             if past_f is not None:
                 past_batch.append(past_f.readline().split())
+            if sub_f is not None:
+                sub_batch.append(sub_f.readline().split())
             if len(src_batch) >= opt.batch_size:
                 flush()
     flush()
@@ -150,6 +159,8 @@ def main(argv=None):
         tgt_f.close()
     if past_f is not None:
         past_f.close()
+    if sub_f is not None:
+        sub_f.close()
 
 
 if __name__ == "__main__":
