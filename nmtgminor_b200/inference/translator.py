@@ -117,6 +117,9 @@ class Translator:
                     b.data = b.data.to(self.device)
             for p in model.parameters():
                 p.requires_grad_(False)
+            if not self.cuda and int(getattr(opt, "dynamic_quantile", 0) or 0) == 1:
+                from ..models.layers import quantize_linears_for_cpu
+                quantize_linears_for_cpu(model)
             models.append(model)
             self.model_opts.append(mopt)
         weights = None

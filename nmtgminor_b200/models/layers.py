@@ -109,7 +109,34 @@ class Linear(nn.Module):
             nn.init.normal_(self.weight, 0.0, init_std)
 
     def forward(self, x, act="none", dropout_p=0.0, residual=None):
+        q = getattr(self, "_int8", None)
+        if q is not None and not self.training and not x.is_cuda:
+            # CPU inference with dynamically quantised weights (``-dynamic_quantile 1``)
+            from ..ops.reference import _act
+            y = _act(q(x.float()), ops.ACT_IDS[act] if not isinstance(act, int) else act).to(x.dtype)
+            return y if residual is None else y + residual
         return ops.linear(x, self.weight, self.bias, act, dropout_p, residual, self.training)
+
+
+def quantize_linears_for_cpu(model: nn.Module) -> int:
+    """Attach an int8 dynamically quantised twin (per-tensor weight scale, activations quantised on the fly) to every
+    ``Linear`` of ``model`` for CPU inference; returns how many were converted.  The fp32 weights stay in place, so the
+    model still runs on a GPU.  Counterpart of the reference's ``torch.quantization.quantize_dynamic`` call
+    (onmt/inference/fast_translator.py:176-190)."""
+    engines = torch.backends.quantized.supported_engines
+    torch.backends.quantized.engine = "fbgemm" if "fbgemm" in engines else ("qnnpack" if "qnnpack" in engines else engines[-1])
+    from torch.ao.nn.quantized.dynamic import Linear as QLinear
+    n = 0
+    for m in model.modules():
+        if isinstance(m, Linear):
+            ref = nn.Linear(m.weight.shape[1], m.weight.shape[0], bias=m.bias is not None)
+            ref.weight.data = m.weight.detach().float().cpu()
+            if m.bias is not None:
+                ref.bias.data = m.bias.detach().float().cpu()
+            ref.qconfig = torch.ao.quantization.default_dynamic_qconfig
+            object.__setattr__(m, "_int8", QLinear.from_float(ref))      # not a registered sub-module: checkpoints are unchanged
+            n += 1
+    return n
 
 
 class Embedding(nn.Module):

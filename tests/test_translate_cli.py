@@ -114,3 +114,24 @@ def test_sub_model_reads_its_own_source(tmp_path):
     batch.sub_batch = tr.build_data(other)
     state = tr.model.create_decoder_state(batch, 1)
     assert state.states[0].context.shape[1] == 3 and state.states[1].context.shape[1] == 4     # each member saw its own source
+
+
+def test_dynamic_quantisation_on_cpu(tmp_path):
+    """``-dynamic_quantile 1``: int8 linear layers on the CPU give nearly the same scores as fp32."""
+    from nmtgminor_b200.inference.translator import Translator
+    from nmtgminor_b200.models.layers import Linear
+    torch.manual_seed(6)
+    d = synthetic_dict(40)
+    dicts = {"src": d, "tgt": d}
+    opt = default_options(COMMON + ["-tie_weights", "-join_embedding"])
+    ck = str(tmp_path / "m.pt")
+    save_checkpoint(ck, build_model(opt, dicts), dicts, opt, 1.0)
+    base = ["-model", ck, "-src", "unused", "-gpu", "-1", "-beam_size", "2", "-max_sent_length", "5"]
+    plain = Translator(translate_cli.make_translate_parser().parse_args(base))
+    quant = Translator(translate_cli.make_translate_parser().parse_args(base + ["-dynamic_quantile", "1"]))
+    assert all(getattr(m, "_int8", None) is not None for m in quant.model.modules() if isinstance(m, Linear))
+    assert not any(k.endswith("_int8") or "_int8." in k for k in quant.model.state_dict())
+    sents, gold = [["w1", "w2", "w3"], ["w4", "w5"]], [["w2", "w3"], ["w6"]]
+    s_plain = plain.translate(sents, gold)[5]
+    s_quant = quant.translate(sents, gold)[5]
+    assert all(abs(a - b) < 0.05 * max(1.0, abs(a)) for a, b in zip(s_plain, s_quant)) and s_plain != s_quant
