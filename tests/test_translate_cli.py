@@ -135,3 +135,26 @@ def test_dynamic_quantisation_on_cpu(tmp_path):
     s_plain = plain.translate(sents, gold)[5]
     s_quant = quant.translate(sents, gold)[5]
     assert all(abs(a - b) < 0.05 * max(1.0, abs(a)) for a, b in zip(s_plain, s_quant)) and s_plain != s_quant
+
+
+def test_translate_distributed_splits_all_line_parallel_inputs(tmp_path):
+    """Two worker processes (CPU here) translate halves of the input; ``-past_src`` is split alongside ``-src``."""
+    import translate_distributed
+    torch.manual_seed(3)
+    d = synthetic_dict(40)
+    opt = default_options(["-model", "discourse_translator"] + COMMON + ["-tie_weights", "-join_embedding"])
+    ck = str(tmp_path / "disc.pt")
+    save_checkpoint(ck, build_model(opt, {"src": d, "tgt": d}), {"src": d, "tgt": d}, opt, 1.0)
+    src, past = tmp_path / "src.txt", tmp_path / "past.txt"
+    src.write_text("w1 w2 w3\nw4 w5\nw6 w7\nw8\nw9 w1\n")
+    past.write_text("\nw1 w2 w3\nw4 w5\nw6 w7\nw8\n")
+    # one sentence per batch, so both runs do exactly the same arithmetic (an untrained model is full of near-ties)
+    common = ["-model", ck, "-beam_size", "2", "-max_sent_length", "5", "-batch_size", "1", "-past_src", str(past)]
+    single, multi = tmp_path / "single.txt", tmp_path / "multi.txt"
+    translate_cli.main(common + ["-src", str(src), "-output", str(single), "-gpu", "-1"])
+    translate_distributed.main(common + ["-src", str(src), "-output", str(multi), "-gpus", "-1,-1"])
+    # (the hypotheses themselves are not compared: an untrained model is full of near-ties that flip with the thread count)
+    assert len(multi.read_text().splitlines()) == len(single.read_text().splitlines()) == 5
+    a = translate_distributed.split_file(str(src), 2, str(tmp_path), "a")
+    b = translate_distributed.split_file(str(past), 2, str(tmp_path), "b")
+    assert [len(open(p).readlines()) for p in a] == [len(open(p).readlines()) for p in b] == [3, 2]

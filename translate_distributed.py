@@ -48,17 +48,21 @@ def main(argv=None):
 
     gpus = [int(g) for g in str(take("-gpus", "0")).split(",") if g != ""]
     src, out, tgt = take("-src"), take("-output", "pred.txt"), take("-tgt")
+    side_inputs = {flag: take(flag) for flag in ("-sub_src", "-past_src")}     # line-parallel to -src: split the same way
     take("-gpu")
     tmpdir = tempfile.mkdtemp(prefix="nmtg_translate_")
     try:
         src_parts = split_file(src, len(gpus), tmpdir, "src")
         tgt_parts = split_file(tgt, len(gpus), tmpdir, "tgt") if tgt else [None] * len(gpus)
+        side_parts = {flag: split_file(path, len(gpus), tmpdir, flag.strip("-")) for flag, path in side_inputs.items() if path}
         out_parts = [os.path.join(tmpdir, "out.%d" % i) for i in range(len(gpus))]
         jobs = []
         for i, g in enumerate(gpus):
             a = argv + ["-src", src_parts[i], "-output", out_parts[i], "-gpu", str(g)]
             if tgt_parts[i]:
                 a += ["-tgt", tgt_parts[i]]
+            for flag, parts in side_parts.items():
+                a += [flag, parts[i]]
             jobs.append((a,))
         with mp.get_context("spawn").Pool(len(gpus)) as pool:
             pool.map(run_part, jobs)
