@@ -250,7 +250,24 @@ class Seq2SeqBase(nn.Module):
             out["logprobs"] = tgt.pad(logits)       # [T, B, V] (logits, as in the reference)
             out["hidden"] = tgt.pad(hidden)         # [T, B, H]
             out["context"] = src.pad(context)
+            lengths = (src.cu[1:] - src.cu[:-1]).to(torch.int64)
+            out["src_mask"] = torch.arange(src.max_len, device=lengths.device)[None, :] >= lengths[:, None]   # [B, Ts], True = padding
+            out["target_mask"] = batch.get("target_input_selfattn_mask") if hasattr(batch, "get") else None
+            out["softmaxed"] = False
         return out
+
+    def load_encoder_weights(self, pretrained, strict: bool = False):
+        """Copy the encoder of another model (a module, or a checkpoint's ``model`` state dict) into this one; used to
+        start a speech-translation or continual-learning run from a trained encoder
+        (reference: onmt/models/transformers.py ``load_encoder_weights``)."""
+        state = pretrained.state_dict() if isinstance(pretrained, nn.Module) else pretrained
+        if any(k.startswith("encoder.") for k in state):
+            state = {k[len("encoder."):]: v for k, v in state.items() if k.startswith("encoder.")}
+        return self.encoder.load_state_dict(state, strict=strict)
+
+    def init_stream(self):
+        """Streaming state for models with segment memories; models without one decode sentence by sentence."""
+        return None
 
     def post_backward(self, output_dict=None):
         return None

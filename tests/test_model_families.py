@@ -176,3 +176,22 @@ def test_wavlm_gated_relative_position_bias(dicts, tmp_path):
     # buckets: symmetric halves, exact for small offsets, saturating for large ones
     b = a._buckets(torch.tensor([0, 1, -1, 5, -5, 1000, -1000]))
     assert b[0] == 0 and b[1] == 16 + 1 and b[2] == 1 and b[5] == 31 and b[6] == 15
+
+
+def test_model_contract_extras(dicts):
+    """Output keys trainers of the reference read (``src_mask``, ``target_mask``, ``softmaxed``) and encoder transplant."""
+    torch.manual_seed(7)
+    opt = default_options(["-model", "transformer"] + COMMON)
+    a, b = build_model(opt, dicts), build_model(opt, dicts)
+    batch = token_budget_batches(120, 4, 10, 60, 1, static=False, padded=True)[0]
+    out = a(batch, return_logits=True)
+    T = batch.get("source").shape[0]
+    assert out["src_mask"].shape == (batch.size, T) and out["src_mask"].dtype == torch.bool
+    assert torch.equal(out["src_mask"], batch.get("src_selfattn_mask")) and out["softmaxed"] is False
+    assert out["logprobs"].shape[:2] == batch.get("target_input").shape
+    assert not torch.equal(a.encoder.layers[0].ffn.fc1.weight, b.encoder.layers[0].ffn.fc1.weight)
+    b.load_encoder_weights(a)
+    assert torch.equal(a.encoder.layers[0].ffn.fc1.weight, b.encoder.layers[0].ffn.fc1.weight)
+    b.load_encoder_weights({k: torch.zeros_like(v) for k, v in a.state_dict().items()})
+    assert float(b.encoder.layers[0].ffn.fc1.weight.abs().sum()) == 0 and float(b.decoder.layers[0].ffn.fc1.weight.abs().sum()) > 0
+    assert a.init_stream() is None
