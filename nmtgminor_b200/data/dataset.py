@@ -148,7 +148,8 @@ class Batch:
         for k, v in self.tensors.items():
             if isinstance(v, PackedSeqs):
                 n += v.tokens.numel() * 8 + v.positions.numel() * 8 + v.cu.numel() * 4
-            elif isinstance(v, torch.Tensor) and (not hot_only or k == "packed_target_output"):
+            elif isinstance(v, torch.Tensor) and (not hot_only or k == "packed_target_output"
+                                                  or self.tensors.get("src_type", "text") != "text"):
                 n += v.numel() * v.element_size()
         return n
 
@@ -161,7 +162,9 @@ class Batch:
                 self.tensors[k] = moved
                 self._packed[k] = moved
             elif isinstance(v, torch.Tensor):
-                if hot_only and k != "packed_target_output":
+                # text batches: the packed views are all the training step reads; audio batches are read through
+                # their padded tensors (frames, lengths, CTC labels), so everything moves
+                if hot_only and k != "packed_target_output" and self.tensors.get("src_type", "text") == "text":
                     continue
                 t = v.to(dev, non_blocking=non_blocking)
                 if fp16 and t.is_floating_point():

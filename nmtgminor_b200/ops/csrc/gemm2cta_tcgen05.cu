@@ -382,6 +382,9 @@ const char* launch_gemm_pair(const GemmDesc* d, const GemmArgs& a, int bn, cudaS
   constexpr uint32_t kOutRes = kEpiBf16 | kEpiBias | kEpiDrop | kEpiRes;
   constexpr uint32_t kDgradMask = kEpiBf16 | kEpiMaskBwd;
   constexpr uint32_t kAccum = kEpiF32;
+  // GELU / SiLU feed-forward blocks (speech and pretrained-decoder models) keep the pre-activation instead of sign bits
+  constexpr uint32_t kFc1Preact = kEpiBf16 | kEpiBias | kEpiActFwd | kEpiDrop | kEpiPreact;
+  constexpr uint32_t kDgradAct = kEpiBf16 | kEpiActBwd | kEpiDrop;
   const uint32_t need = g_pair_generic_epilogue ? kEpiAll : gemm_epilogue_features(args);
   const int grid = clusters * 2;
   if ((need & ~kPlain) == 0) return launch_pair<256, false, kPlain>(ta, tb, tc, args, grid, stream);
@@ -389,6 +392,8 @@ const char* launch_gemm_pair(const GemmDesc* d, const GemmArgs& a, int bn, cudaS
   if ((need & ~kDgradMask) == 0) return launch_pair<256, false, kDgradMask>(ta, tb, tc, args, grid, stream);
   if ((need & ~kOutRes) == 0) return launch_pair<256, false, kOutRes>(ta, tb, tc, args, grid, stream);
   if ((need & ~kFc1) == 0) return launch_pair<256, false, kFc1>(ta, tb, tc, args, grid, stream);
+  if ((need & ~kFc1Preact) == 0) return launch_pair<256, false, kFc1Preact>(ta, tb, tc, args, grid, stream);
+  if ((need & ~kDgradAct) == 0) return launch_pair<256, false, kDgradAct>(ta, tb, tc, args, grid, stream);
   return launch_pair<256, false, kEpiAll>(ta, tb, tc, args, grid, stream);
 }
 

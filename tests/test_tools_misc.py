@@ -27,3 +27,19 @@ def test_text_tools_and_autoencoder():
     first = Autoencoder(16, 8).loss(states[0]).item()
     ae = train_autoencoder(states, inner_size=8, epochs=40, lr=5e-3)
     assert ae.loss(states[0]).item() < first
+
+
+def test_speech_benchmark_dry_run(capsys):
+    """``bench_speech.py --tiny`` runs both speech configurations through the training engine on the CPU."""
+    import importlib.util
+    import json
+    import os
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    spec = importlib.util.spec_from_file_location("bench_speech", os.path.join(root, "bench_speech.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    for cfg in ("whisper_large_v2", "wav2vec2_mbart50"):
+        mod.main(["--config", cfg, "--tiny", "--steps", "1", "--warmup", "1"])
+        line = [l for l in capsys.readouterr().out.splitlines() if l.startswith("{")][-1]
+        out = json.loads(line)
+        assert out["value"] > 0 and out["audio_seconds_per_second"] > 0 and out["loss_per_token_after_warmup"] > 0
