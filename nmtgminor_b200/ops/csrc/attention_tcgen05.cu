@@ -214,12 +214,14 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sK = smem;
   uint8_t* sV = sK + kTileBytes;
-  uint8_t* sQ = sV + kTileBytes;
-  uint8_t* sDO = sQ + kTileBytes;
-  uint8_t* sP = sDO + kTileBytes;
+  uint8_t* sQ0 = sV + kTileBytes;         // Q / dO tiles are double-buffered: the next query tile is fetched while
+  uint8_t* sDO0 = sQ0 + kTileBytes;       // this one is being worked on
+  uint8_t* sQ1 = sDO0 + kTileBytes;
+  uint8_t* sDO1 = sQ1 + kTileBytes;
+  uint8_t* sP = sDO1 + kTileBytes;
   uint8_t* sDS = sP + kPBytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sDS + kPBytes);  // [0]=KV [1]=Q,dO [2]=MMA
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sDS + kPBytes);  // [0]=KV [1]=Q,dO buffer 0 [2]=MMA [3]=Q,dO buffer 1
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4);
   volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   zero_tail_bwd(p);
@@ -236,6 +238,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     mbar_init(&bars[0], 1);
     mbar_init(&bars[1], 1);
     mbar_init(&bars[2], 1);
+    mbar_init(&bars[3], 1);
     *abort_word = 0;
     mbar_fence_init();
   }
@@ -263,19 +266,31 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
 
   const int num_qt = (q_len + kTile - 1) / kTile;
   const int qt_first = p.causal ? (kt * kTile) / kTile : 0;  // query tiles before the key tile see none of it
-  uint32_t ph_q = 0, ph_mma = 0;
+  uint32_t ph_mma = 0;
   bool ok = true;
   bool first = true;
 
+  if (t == 0 && qt_first < num_qt) {
+    mbar_expect_tx(&bars[1], 2 * kTileBytes);
+    tma_load_2d(sQ0, &tmap_q, &bars[1], h * kHd, q_begin + qt_first * kTile);
+    tma_load_2d(sDO0, &tmap_do, &bars[1], h * kHd, q_begin + qt_first * kTile);
+  }
   for (int qt = qt_first; qt < num_qt && ok; ++qt) {
     const int q0 = q_begin + qt * kTile;
     const int q_rows = min(kTile, q_len - qt * kTile);
+    const int it = qt - qt_first, buf = it & 1;
+    uint8_t* sQ = buf ? sQ1 : sQ0;
+    uint8_t* sDO = buf ? sDO1 : sDO0;
     if (t == 0) {
-      mbar_expect_tx(&bars[1], 2 * kTileBytes);
-      tma_load_2d(sQ, &tmap_q, &bars[1], h * kHd, q0);
-      tma_load_2d(sDO, &tmap_do, &bars[1], h * kHd, q0);
+      if (qt + 1 < num_qt) {
+        // the other buffer was last read by the MMAs of the previous iteration, which have completed
+        uint64_t* nb = buf ? &bars[1] : &bars[3];
+        mbar_expect_tx(nb, 2 * kTileBytes);
+        tma_load_2d(buf ? sQ0 : sQ1, &tmap_q, nb, h * kHd, q0 + kTile);
+        tma_load_2d(buf ? sDO0 : sDO1, &tmap_do, nb, h * kHd, q0 + kTile);
+      }
       if (first) ok = mbar_wait(&bars[0], 0, abort_word, p.status, kTimeoutTmaFull);
-      if (ok) ok = mbar_wait(&bars[1], ph_q, abort_word, p.status, kTimeoutTmaFull);
+      if (ok) ok = mbar_wait(buf ? &bars[3] : &bars[1], (it >> 1) & 1, abort_word, p.status, kTimeoutTmaFull);
       if (ok) {
         tc_fence_after_sync();
         umma_steps(tS, smem_u32(sQ), 16, 32, smem_u32(sK), 16, 32, idesc_s, kHd / 16, false);
@@ -283,7 +298,6 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         umma_commit(&bars[2]);
       }
     }
-    ph_q ^= 1;
     // D = rowsum(dO * O) and the saved log-sum-exp of my query row (overlaps the MMAs)
     const bool row_ok = t < q_rows;
     float Drow = 0.f, lse = 0.f;
@@ -460,7 +474,7 @@ __global__ void attn_dq_convert_kernel(const float* __restrict__ acc, int ld_acc
 }
 
 constexpr int kFwdSmem = 3 * kTileBytes + kPBytes + 64 + 1024;
-constexpr int kBwdSmem = 4 * kTileBytes + 2 * kPBytes + 64 + 1024;
+constexpr int kBwdSmem = 6 * kTileBytes + 2 * kPBytes + 64 + 1024;
 
 }  // namespace b200
 
