@@ -206,7 +206,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
 // ---------------------------------------------------------------------------------------------------
 // backward
 // ---------------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(128)
+// 256 threads: two warpgroups own the same 128 rows (TMEM lanes) and split the columns of every tile between them, so
+// each scheduler has two warps to switch between while the other waits on TMEM loads and exponentials.
+__global__ void __launch_bounds__(256)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                 const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
                 const AttnArgs p) {
@@ -232,9 +234,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   if (kt * kTile >= k_len) return;
   const int k_rows = min(kTile, k_len - kt * kTile);
   const bool single_kt = k_len <= kTile;
-  const int t = threadIdx.x, warp = t >> 5;
+  const int t = threadIdx.x & 127, warp = t >> 5, grp = threadIdx.x >> 7;
+  const bool leader = threadIdx.x == 0;
 
-  if (t == 0) {
+  if (leader) {
     mbar_init(&bars[0], 1);
     mbar_init(&bars[1], 1);
     mbar_init(&bars[2], 1);
@@ -242,7 +245,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     *abort_word = 0;
     mbar_fence_init();
   }
-  if (warp == 0) tmem_alloc(tmem_slot, 512);
+  if (threadIdx.x < 32) tmem_alloc(tmem_slot, 512);
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
@@ -251,7 +254,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                  tDV = tmem_base + 384;
   const uint32_t lane_sel = static_cast<uint32_t>(warp * 32) << 16;
 
-  if (t == 0) {
+  if (leader) {
     mbar_expect_tx(&bars[0], 2 * kTileBytes);
     tma_load_2d(sK, &tmap_k, &bars[0], h * kHd, k0);
     tma_load_2d(sV, &tmap_v, &bars[0], h * kHd, k0);
@@ -270,7 +273,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   bool ok = true;
   bool first = true;
 
-  if (t == 0 && qt_first < num_qt) {
+  if (leader && qt_first < num_qt) {
     mbar_expect_tx(&bars[1], 2 * kTileBytes);
     tma_load_2d(sQ0, &tmap_q, &bars[1], h * kHd, q_begin + qt_first * kTile);
     tma_load_2d(sDO0, &tmap_do, &bars[1], h * kHd, q_begin + qt_first * kTile);
@@ -281,7 +284,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     const int it = qt - qt_first, buf = it & 1;
     uint8_t* sQ = buf ? sQ1 : sQ0;
     uint8_t* sDO = buf ? sDO1 : sDO0;
-    if (t == 0) {
+    if (leader) {
       if (qt + 1 < num_qt) {
         // the other buffer was last read by the MMAs of the previous iteration, which have completed
         uint64_t* nb = buf ? &bars[1] : &bars[3];
@@ -323,7 +326,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
 
     const int q_pos = qt * kTile + t;
 #pragma unroll 1
-    for (int c = 0; c < 4; ++c) {
+    for (int c = 2 * grp; c < 2 * grp + 2; ++c) {      // this warpgroup's 64 of the 128 key columns
       uint32_t rs[32], rd[32];
       tmem_ld32(tS + lane_sel + c * 32, rs);
       tmem_ld32(tDP + lane_sel + c * 32, rd);
@@ -360,7 +363,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     tc_fence_before_sync();
     fence_async_smem();
     __syncthreads();
-    if (t == 0) {
+    if (leader) {
       tc_fence_after_sync();
       // dV += P^T dO : A = P read MN-major (M = keys: two 64-key slabs, LBO = slab size), K = 128 query rows
       umma_steps(tDV, smem_u32(sP), kTileBytes, 2048, smem_u32(sDO), 8192, 2048, idesc_dkv, 8, !first);
@@ -376,7 +379,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     ph_mma ^= 1;
     tc_fence_after_sync();
 #pragma unroll 1
-    for (int c = 0; c < 2; ++c) {
+    for (int c = grp; c < grp + 1; ++c) {               // 32 of the 64 dQ columns per warpgroup
       uint32_t r[32];
       tmem_ld32(tDQ + lane_sel + c * 32, r);
       tmem_ld_wait();
@@ -415,7 +418,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       const int ld = which == 0 ? p.ld_dk : p.ld_dv;
       const uint32_t tsrc = which == 0 ? tDK : tDV;
 #pragma unroll 1
-      for (int c = 0; c < 2; ++c) {
+      for (int c = grp; c < grp + 1; ++c) {
         uint32_t r[32];
         tmem_ld32(tsrc + lane_sel + c * 32, r);
         tmem_ld_wait();
@@ -433,7 +436,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         }
       }
     }
-  } else if (ok && t < k_rows) {
+  } else if (ok && t < k_rows && grp == 0) {
     // no query tile attends to this key tile: zero gradients
     for (int which = 0; which < 2; ++which) {
       __nv_bfloat16* dst = which == 0 ? p.dk : p.dv;
@@ -448,7 +451,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     for (int i = 0; i < 2000; ++i) __nanosleep(1000);
     __syncthreads();
   }
-  if (warp == 0) {
+  if (threadIdx.x < 32) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, 512);
   }
@@ -562,7 +565,7 @@ const char* nmtg_attn_bwd(const AttnDesc* d, cudaStream_t stream) {
     configured = true;
   }
   dim3 grid((d->max_k + kTile - 1) / kTile, d->num_heads, d->batch);
-  attn_bwd_kernel<<<grid, 128, kBwdSmem, stream>>>(tq, tk, tv, tdo, a);
+  attn_bwd_kernel<<<grid, 256, kBwdSmem, stream>>>(tq, tk, tv, tdo, a);
   cudaError_t ce = cudaGetLastError();
   if (ce != cudaSuccess) return cudaGetErrorString(ce);
   if (d->max_k > kTile) {
@@ -650,7 +653,7 @@ extern "C" int nmtg_attn_bwd_noalloc(const void* q, int ld_q, const void* k, int
   ce = cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kBwdSmem);
   if (ce != cudaSuccess) return noalloc_fail(3, cudaGetErrorString(ce), err, err_len);
   dim3 grid((max_k + kTile - 1) / kTile, num_heads, batch);
-  attn_bwd_kernel<<<grid, 128, kBwdSmem, stream>>>(tq, tk, tv, tdo, a);
+  attn_bwd_kernel<<<grid, 256, kBwdSmem, stream>>>(tq, tk, tv, tdo, a);
   ce = cudaGetLastError();
   if (ce != cudaSuccess) return noalloc_fail(3, cudaGetErrorString(ce), err, err_len);
   if (needs_buffer) {
