@@ -104,8 +104,8 @@ def main(argv=None):
         loss = step(batches[i % len(batches)])
     first_loss = float(loss) / tokens[(args.warmup - 1) % len(batches)] if args.warmup else None
     if cuda:
-        peak0 = torch.cuda.max_memory_allocated() / 2 ** 30
         ms, ntok = B.timed_loop(step, batches, tokens, args.steps, world, read_loss=True)
+        peak0 = torch.cuda.max_memory_allocated() / 2 ** 30
         total_tok = B.sum_over_ranks(float(ntok), world)
         audio = B.sum_over_ranks(float(sum(secs[i % len(secs)] for i in range(args.steps))), world)
         from nmtgminor_b200 import ops
@@ -128,6 +128,8 @@ def main(argv=None):
                        "parallelism": "dp%d" % world, "ddp": args.ddp if (world > 1 or args.ddp == "fsdp") else None,
                        "timing": "end to end: pinned host batch -> device and loss read back every step"},
             "peak_memory_gib": peak0, "kernel_status": status, "loss_per_token_after_warmup": first_loss}), flush=True)
+    if world > 1 and torch.distributed.is_initialized():
+        torch.distributed.destroy_process_group()
 
 
 if __name__ == "__main__":
