@@ -158,11 +158,12 @@ def advance_device_seed(device=None, by: int = 1) -> None:
 # ---------------------------------------------------------------------------------------------------
 def gemm(a, b, out, *, a_mn_major=False, b_mn_major=False, bias=None, residual=None, aux=None, preact=None, act=0,
          dropout_p=0.0, seed=0, stream_id=0, alpha=1.0, accumulate=False, allow_split_k=False, split_k=0, force_bn=0,
-         mask=None):
+         mask=None, colsum=None):
     """out[M,N] = epilogue(alpha * A B^T) on the tcgen05 kernel (see csrc/ops_api.h: GemmDesc).  ``mask`` (int32
-    [M, ceil(N/32)]) receives the sign bits of the output, or supplies them when ``act`` is the mask-backward id 8."""
+    [M, ceil(N/32)]) receives the sign bits of the output, or supplies them when ``act`` is the mask-backward id 8.
+    ``colsum`` (fp32 [N]): the column sums of the bf16 output are added to it by the epilogue (bias gradients)."""
     ext().gemm(a, a_mn_major, b, b_mn_major, out, bias, residual, aux, preact, int(act), float(dropout_p), int(seed),
-               int(stream_id), float(alpha), bool(accumulate), bool(allow_split_k), int(split_k), int(force_bn), mask)
+               int(stream_id), float(alpha), bool(accumulate), bool(allow_split_k), int(split_k), int(force_bn), mask, colsum)
     return out
 
 
@@ -296,13 +297,16 @@ class _MlpFn(torch.autograd.Function):
         if gb2 is not None:
             ext().colsum(dz2, gb2)
         dz1 = torch.empty_like(h)
+        fused_gb1 = False
         if act == 1:   # the sign bits encode ReLU and the dropout mask; only the keep scale is missing
-            gemm(dz2, w2, dz1, b_mn_major=True, act=8, mask=z, alpha=_keep_scale(p1))
+            # with more than 128 rows the CTA-pair kernel runs, whose epilogue can also sum the columns (fc1 bias gradient)
+            fused_gb1 = gb1 is not None and dz2.shape[0] > 128 and dz1.shape[1] % 8 == 0
+            gemm(dz2, w2, dz1, b_mn_major=True, act=8, mask=z, alpha=_keep_scale(p1), colsum=gb1 if fused_gb1 else None)
         else:
             gemm(dz2, w2, dz1, b_mn_major=True, aux=z, act=_ACT_BWD[act], dropout_p=p1, seed=seed, stream_id=sid1)
         if gw1 is not None:
             gemm(dz1, x, gw1, a_mn_major=True, b_mn_major=True, accumulate=True, allow_split_k=True)
-        if gb1 is not None:
+        if gb1 is not None and not fused_gb1:
             ext().colsum(dz1, gb1)
         dx = torch.empty_like(x)
         gemm(dz1, w1, dx, b_mn_major=True)

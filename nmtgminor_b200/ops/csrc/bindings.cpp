@@ -62,7 +62,7 @@ Tensor get_seed_tensor(int64_t device) { return seed_tensor(static_cast<int>(dev
 void gemm(const Tensor& a, bool a_mn_major, const Tensor& b, bool b_mn_major, Tensor& out, const OptTensor& bias,
           const OptTensor& residual, const OptTensor& aux, const OptTensor& preact, int64_t act, double dropout_p,
           int64_t seed, int64_t stream_id, double alpha, bool accumulate, bool allow_split_k, int64_t split_k,
-          int64_t force_bn, const OptTensor& mask) {
+          int64_t force_bn, const OptTensor& mask, const OptTensor& colsum) {
   need_bf16(a, "a"); need_bf16(b, "b");
   need_rowmajor2d(a, "a"); need_rowmajor2d(b, "b"); need_rowmajor2d(out, "out");
   c10::cuda::CUDAGuard guard(a.device());
@@ -88,6 +88,11 @@ void gemm(const Tensor& a, bool a_mn_major, const Tensor& b, bool b_mn_major, Te
     TORCH_CHECK(mask->is_cuda() && mask->scalar_type() == at::kInt && mask->dim() == 2 && mask->stride(1) == 1 &&
                 mask->size(0) >= d.M && mask->size(1) * 32 >= d.N, "gemm: mask must be int32 [M, ceil(N / 32)]");
     d.mask = mask->data_ptr(); d.ld_mask = static_cast<int>(mask->stride(0));
+  }
+  if (colsum.has_value()) {
+    need_f32(*colsum, "colsum");
+    TORCH_CHECK(colsum->is_contiguous() && colsum->numel() >= d.N, "gemm: colsum must be fp32 [N]");
+    d.colsum = colsum->data_ptr<float>();
   }
   d.out = out.data_ptr(); d.ld_out = static_cast<int>(out.stride(0));
   TORCH_CHECK(out.is_cuda());
@@ -403,7 +408,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", &gemm, pybind11::arg("a"), pybind11::arg("a_mn_major"), pybind11::arg("b"), pybind11::arg("b_mn_major"), pybind11::arg("out"),
         pybind11::arg("bias"), pybind11::arg("residual"), pybind11::arg("aux"), pybind11::arg("preact"), pybind11::arg("act"),
         pybind11::arg("dropout_p"), pybind11::arg("seed"), pybind11::arg("stream_id"), pybind11::arg("alpha"), pybind11::arg("accumulate"),
-        pybind11::arg("allow_split_k"), pybind11::arg("split_k"), pybind11::arg("force_bn"), pybind11::arg("mask") = pybind11::none());
+        pybind11::arg("allow_split_k"), pybind11::arg("split_k"), pybind11::arg("force_bn"), pybind11::arg("mask") = pybind11::none(),
+        pybind11::arg("colsum") = pybind11::none());
   m.def("set_gemm_variant", [](int64_t v) { nmtg_set_gemm_variant(static_cast<int>(v)); });
   m.def("set_gemm_trace", [](const OptTensor& buf) {
     if (buf.has_value()) {

@@ -287,6 +287,21 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           const long long c2 = tracing ? clock64() : 0;
           fence_async_smem();
           __syncwarp();
+          if ((kFeat & kEpiColsum) && p.colsum) {
+            // column sums of the staged 32 x 64 tile: lane l owns columns 2l, 2l+1 (one 32-bit word per row; the
+            // swizzle keeps the 32 lanes on 32 different banks), rows outside the matrix are skipped
+            const int rows_here = min(32, p.M - (m0 + q * 32));
+            float s0 = 0.f, s1 = 0.f;
+            for (int r = 0; r < rows_here; ++r) {
+              const uint32_t w = *reinterpret_cast<const uint32_t*>(stage + r * 128 + ((((lane >> 2) ^ (r & 7)) << 4) | ((lane & 3) << 2)));
+              const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w));
+              s0 += f.x;
+              s1 += f.y;
+            }
+            const int c = col0 + 2 * lane;
+            if (c < p.N) atomicAdd(p.colsum + c, s0);
+            if (c + 1 < p.N) atomicAdd(p.colsum + c + 1, s1);
+          }
           if (lane == 0) {
             tma_store_2d(&tmap_out, stage, col0, m0 + q * 32);
             tma_store_commit();
@@ -367,10 +382,11 @@ const char* launch_gemm_pair(const GemmDesc* d, const GemmArgs& a, int bn, cudaS
   GemmArgs args = a;
   CUtensorMap tc = ta;
   args.tma_store = 0;
-  if (!d->out_fp32 && a.split_k == 1 && d->preact == nullptr && (d->ld_out % 8) == 0 && g_pair_tma_store) {
+  if (!d->out_fp32 && a.split_k == 1 && d->preact == nullptr && (d->ld_out % 8) == 0 && (g_pair_tma_store || a.colsum)) {
     if (cached_tmap(&tc, d->out, d->M, d->N, d->ld_out, 32, 64)) args.tma_store = 1;
     else tc = ta;
   }
+  if (a.colsum && !args.tma_store) return "gemm: the column-sum output needs the bf16 TMA-store epilogue (no split-K, no pre-activation)";
   const long tiles = static_cast<long>((d->M + 2 * BM - 1) / (2 * BM)) * ((d->N + bn - 1) / bn) * a.split_k;
   const int max_clusters = num_sms() / 2;
   const int clusters = a.stream_k ? max_clusters : static_cast<int>(tiles < max_clusters ? tiles : max_clusters);
@@ -380,7 +396,7 @@ const char* launch_gemm_pair(const GemmDesc* d, const GemmArgs& a, int bn, cudaS
   constexpr uint32_t kPlain = kEpiBf16;
   constexpr uint32_t kFc1 = kEpiBf16 | kEpiBias | kEpiActFwd | kEpiDrop | kEpiMaskOut;
   constexpr uint32_t kOutRes = kEpiBf16 | kEpiBias | kEpiDrop | kEpiRes;
-  constexpr uint32_t kDgradMask = kEpiBf16 | kEpiMaskBwd;
+  constexpr uint32_t kDgradMask = kEpiBf16 | kEpiMaskBwd | kEpiColsum;
   constexpr uint32_t kAccum = kEpiF32;
   // GELU / SiLU feed-forward blocks (speech and pretrained-decoder models) keep the pre-activation instead of sign bits
   constexpr uint32_t kFc1Preact = kEpiBf16 | kEpiBias | kEpiActFwd | kEpiDrop | kEpiPreact;

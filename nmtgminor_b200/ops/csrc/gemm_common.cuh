@@ -28,6 +28,7 @@ struct GemmArgs {
   __nv_bfloat16* preact;   // optional [M, ld_out]: value after bias, before activation
   uint32_t* mask;          // optional [M, ld_mask] sign bits of the output (written, or read by kActMaskBwd)
   int ld_mask;
+  float* colsum;           // optional fp32 [N]: += column sums of the stored bf16 output (TMA-store epilogue)
   int act;
   float dropout_p;
   unsigned long long seed, stream_id;
@@ -59,7 +60,8 @@ __device__ __forceinline__ float sigmoid_f(float x) { return 1.0f / (1.0f + __ex
 // rather than on arithmetic.  kEpiAll is the general kernel.
 constexpr uint32_t kEpiBias = 1u, kEpiPreact = 2u, kEpiActFwd = 4u, kEpiActBwd = 8u, kEpiMaskBwd = 16u, kEpiDrop = 32u,
                    kEpiMaskOut = 64u, kEpiRes = 128u, kEpiF32 = 256u, kEpiBf16 = 512u,
-                   kEpiRagged = 1024u /* N not a multiple of 64: partial column chunks */, kEpiAll = 2047u;
+                   kEpiRagged = 1024u /* N not a multiple of 64: partial column chunks */,
+                   kEpiColsum = 2048u /* column sums of the output, pair kernel only */, kEpiAll = 4095u;
 
 // Features a problem needs (host side).
 inline uint32_t gemm_epilogue_features(const GemmArgs& a) {
@@ -74,6 +76,7 @@ inline uint32_t gemm_epilogue_features(const GemmArgs& a) {
   if (a.residual) f |= kEpiRes;
   f |= a.out_fp32 ? kEpiF32 : kEpiBf16;
   if (a.N % 64) f |= kEpiRagged;
+  if (a.colsum) f |= kEpiColsum;
   return f;
 }
 

@@ -364,6 +364,7 @@ const char* nmtg_gemm_bf16(const GemmDesc* d, cudaStream_t stream) {
   a.out = d->out; a.ld_out = d->ld_out; a.out_fp32 = d->out_fp32; a.accumulate = d->accumulate;
   a.preact = reinterpret_cast<__nv_bfloat16*>(d->preact);
   a.mask = reinterpret_cast<uint32_t*>(d->mask); a.ld_mask = d->ld_mask;
+  a.colsum = d->colsum;
   a.ablate = g_gemm_ablate;
   a.stream_k = 0;
   a.trace = g_gemm_trace;
@@ -381,7 +382,7 @@ const char* nmtg_gemm_bf16(const GemmDesc* d, cudaStream_t stream) {
   // ---- skinny problems (incremental decoding: a few hundred rows): the weight matrix is streamed once, so the
   // only lever is the number of CTAs pulling it in; take the widest tile that still gives every SM a tile,
   // down to 64 columns
-  const bool skinny = g_gemm_variant == 0 && d->M <= 512 && !d->out_fp32 && d->force_bn == 0 && d->split_k <= 1;
+  const bool skinny = g_gemm_variant == 0 && d->M <= 512 && !d->out_fp32 && d->force_bn == 0 && d->split_k <= 1 && !d->colsum;
   if (skinny) {
     const int num_m = (d->M + BM - 1) / BM;
     int bn = 64;
@@ -417,7 +418,8 @@ const char* nmtg_gemm_bf16(const GemmDesc* d, cudaStream_t stream) {
     return launch_gemm<64>(ta, tb, a, grid, stream);
   }
   // ---- CTA-pair kernel (256-row tiles): the default for everything but very small M ----------------
-  if (g_gemm_variant != 1 && d->M > BM) {
+  if (d->colsum && d->M <= BM) return "gemm: the column-sum output needs more than 128 rows (CTA-pair kernel)";
+  if ((g_gemm_variant != 1 || d->colsum) && d->M > BM) {
     int bn = (d->N > 128) ? 256 : 128;
     if (d->force_bn == 128 || d->force_bn == 256) bn = d->force_bn;
     const long tiles = static_cast<long>((d->M + 2 * BM - 1) / (2 * BM)) * ((d->N + bn - 1) / bn);

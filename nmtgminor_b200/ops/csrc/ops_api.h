@@ -32,6 +32,8 @@ struct GemmDesc {
   void* mask;             // optional uint32 [M, ld_mask]: bit j of word c = (output[row, 32 c + j] > 0); written by forward
                           // epilogues (before the residual), read by kActMaskBwd
   int ld_mask;
+  float* colsum;          // optional fp32 [N]: column sums of the (bf16-rounded) output are ADDED here (bias gradient of the
+                          // layer whose output gradient this GEMM produces); CTA-pair kernel with the TMA-store epilogue only
   int act;
   float dropout_p; unsigned long long seed, stream_id;
   const unsigned long long* seed_dev;  // optional device word added to seed (lets graph replays draw new masks)

@@ -193,3 +193,21 @@ def test_gemm_sign_bit_mask_round_trip():
     _status_ok()
     want = (g.float() @ w2.float().t()) * 1.25 * positive
     assert _rel_err(d, want) < 1e-2
+
+
+@pytest.mark.parametrize("M,N,K", [(8192, 4096, 1024), (1000, 1024, 512), (300, 264, 256), (129, 64, 128)])
+def test_gemm_column_sums_in_the_epilogue(M, N, K):
+    """The sign-bit backward epilogue also adds the column sums of its bf16 output to an fp32 vector (bias gradient)."""
+    torch.manual_seed(9)
+    dy = torch.randn(M, K, device=DEV).bfloat16()
+    w = (torch.randn(K, N, device=DEV) * 0.05).bfloat16()            # [K, N]: B read MN-major, as in the fc2 data gradient
+    bits = torch.randint(-2 ** 31, 2 ** 31 - 1, (M, (N + 31) // 32), device=DEV, dtype=torch.int32)
+    out = ops.empty_rows(M, N, DEV)
+    gb = torch.full((N,), 0.25, device=DEV)
+    ops.gemm(dy, w, out, b_mn_major=True, act=8, mask=bits, alpha=1.1, colsum=gb)
+    _status_ok()
+    ref = torch.empty_like(out)
+    ops.gemm(dy, w, ref, b_mn_major=True, act=8, mask=bits, alpha=1.1)
+    assert torch.equal(out, ref)
+    want = ref.float().sum(0) + 0.25
+    assert (gb - want).abs().max().item() <= 2e-3 * max(1.0, want.abs().max().item())
