@@ -65,8 +65,8 @@ def extension_available() -> bool:
     return load_extension(build_if_missing=False) is not None
 
 
-_KERNEL_CALLS = {"gemm": 1, "layernorm_fwd": 1, "layernorm_bwd": 1, "xent_fused": 1, "dropout_add": 1, "embed_fwd": 1,
-                 "embed_bwd": 1, "colsum": 1, "sq_norm": 1, "adamw_flat": 1, "cast_f32_bf16": 1, "attn_fwd": 1,
+_KERNEL_CALLS = {"gemm": 1, "layernorm_fwd": 1, "layernorm_bwd": 1, "xent_fused": 1, "dropout_add": 1,
+                 "dropout_colsum": 1, "embed_fwd": 1, "embed_bwd": 1, "colsum": 1, "sq_norm": 1, "adamw_flat": 1, "cast_f32_bf16": 1, "attn_fwd": 1,
                  "attn_bwd": 1, "allreduce_adamw": 1}
 LAUNCHES = [0]   # kernels of this extension enqueued so far (Python-side count of launcher calls)
 
@@ -215,18 +215,29 @@ class _LinearFn(torch.autograd.Function):
             dy = padded
         else:
             dy = dy.contiguous()
-        dz = ext().dropout_add(dy, None, p, seed, sid) if p > 0.0 else dy  # regenerates the forward mask
+        want_gb = has_bias and ctx.gb is not None
+        fused_gb = want_gb and act == 0 and p > 0.0 and _colsum_fusable(dy)
+        if fused_gb:
+            dz = ext().dropout_colsum(dy, p, seed, sid, ctx.gb)  # regenerated mask and bias gradient in one pass
+        else:
+            dz = ext().dropout_add(dy, None, p, seed, sid) if p > 0.0 else dy  # regenerates the forward mask
         if act != 0:
             dz = _act_backward(dz, z, act)
         if ctx.gw is not None:
             gemm(dz, x, ctx.gw, a_mn_major=True, b_mn_major=True, accumulate=True, allow_split_k=True)
-        if has_bias and ctx.gb is not None:
+        if want_gb and not fused_gb:
             ext().colsum(dz, ctx.gb)
         dx = None
         if need_dx:
             dx = torch.empty((dy.shape[0], x.shape[1]), dtype=torch.bfloat16, device=dy.device)
             gemm(dz, w, dx, b_mn_major=True)
         return dx, None, None, (dy if has_res else None), None, None, None, None, None, None, None
+
+
+def _colsum_fusable(dy):
+    """The one-pass masked-gradient + bias-gradient kernel takes 16 * (8, 16, ..., 256) columns."""
+    n = dy.shape[1]
+    return dy.dim() == 2 and n % 128 == 0 and n <= 4096 and (n & (n - 1)) == 0
 
 
 def _act_backward(dh, z, act):
@@ -291,10 +302,14 @@ class _MlpFn(torch.autograd.Function):
         act, p1, p2, seed, sid1, sid2, has_res = ctx.cfg
         gw1, gb1, gw2, gb2 = ctx.g
         dy = dy.contiguous()
-        dz2 = ext().dropout_add(dy, None, p2, seed, sid2) if p2 > 0.0 else dy
+        fused_gb2 = gb2 is not None and p2 > 0.0 and _colsum_fusable(dy)
+        if fused_gb2:
+            dz2 = ext().dropout_colsum(dy, p2, seed, sid2, gb2)
+        else:
+            dz2 = ext().dropout_add(dy, None, p2, seed, sid2) if p2 > 0.0 else dy
         if gw2 is not None:
             gemm(dz2, h, gw2, a_mn_major=True, b_mn_major=True, accumulate=True, allow_split_k=True)
-        if gb2 is not None:
+        if gb2 is not None and not fused_gb2:
             ext().colsum(dz2, gb2)
         dz1 = torch.empty_like(h)
         fused_gb1 = False

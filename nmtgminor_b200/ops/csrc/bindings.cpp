@@ -169,6 +169,17 @@ Tensor dropout_add(const Tensor& x, const OptTensor& residual, double p, int64_t
   return y;
 }
 
+Tensor dropout_colsum(const Tensor& x, double p, int64_t seed, int64_t stream_id, Tensor& colsum) {
+  need_bf16(x, "x"); need_f32(colsum, "colsum");
+  TORCH_CHECK(x.dim() == 2 && x.is_contiguous() && colsum.is_contiguous() && colsum.numel() >= x.size(1));
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor y = torch::empty_like(x);
+  ck(nmtg_dropout_colsum(x.data_ptr(), y.data_ptr(), colsum.data_ptr<float>(), static_cast<int>(x.size(0)), static_cast<int>(x.size(1)),
+                         static_cast<float>(p), static_cast<unsigned long long>(seed), static_cast<unsigned long long>(stream_id),
+                         seed_ptr(x), cur_stream()));
+  return y;
+}
+
 Tensor embed_fwd(const Tensor& tokens, const OptTensor& positions, const Tensor& table, const OptTensor& pos_table,
                  double scale, double p, int64_t seed, int64_t stream_id) {
   need_bf16(table, "table");
@@ -423,6 +434,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("layernorm_bwd", &layernorm_bwd);
   m.def("xent_fused", &xent_fused);
   m.def("dropout_add", &dropout_add);
+  m.def("dropout_colsum", &dropout_colsum);
   m.def("embed_fwd", &embed_fwd);
   m.def("embed_bwd", &embed_bwd);
   m.def("colsum", &colsum);

@@ -68,6 +68,52 @@ __global__ void dropout_add_kernel(const __nv_bfloat16* __restrict__ x, const __
   }
 }
 
+// y = dropout-mask(x) (the mask of dropout_add with the same seed / stream) and colsum += column sums of y, in one
+// pass: backward of ``dropout(linear(x) + bias)`` needs both the masked gradient and the bias gradient.  A thread keeps
+// one group of 16 columns for all the rows it visits, so the partial sums stay in registers; the CTA's row slices are
+// combined in shared memory and every CTA ends with one atomic per column.
+template <int kGroups>     // 16-column groups per row; 256 % kGroups == 0
+__global__ void __launch_bounds__(256)
+dropout_colsum_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y, float* __restrict__ colsum, int rows,
+                      float p, unsigned long long seed, unsigned long long stream_id, const unsigned long long* seed_dev) {
+  constexpr int kRowsPerIter = 256 / kGroups;
+  __shared__ float part[kRowsPerIter][kGroups * 16 + 1];
+  const DropRng rng(seed + (seed_dev ? *seed_dev : 0ull), stream_id, p);
+  const int c = threadIdx.x % kGroups, rsub = threadIdx.x / kGroups;
+  float acc[16];
+#pragma unroll
+  for (int j = 0; j < 16; ++j) acc[j] = 0.f;
+  for (long row = static_cast<long>(blockIdx.x) * kRowsPerIter + rsub; row < rows; row += static_cast<long>(gridDim.x) * kRowsPerIter) {
+    const long i = row * kGroups + c;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      float f[8];
+      unpack8(reinterpret_cast<const uint4*>(x)[2 * i + h], f);
+#pragma unroll
+      for (int g = 0; g < 2; ++g) {
+        const uint32_t w = rng.word(static_cast<unsigned long long>(i) * 4 + h * 2 + g);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) f[g * 4 + j] = rng.keep(w, j) ? f[g * 4 + j] * rng.scale : 0.f;
+      }
+      const uint4 packed = pack8(f);
+      reinterpret_cast<uint4*>(y)[2 * i + h] = packed;
+      float back[8];
+      unpack8(packed, back);          // sum what was stored (bf16-rounded), as a separate pass over y would
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[h * 8 + j] += back[j];
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 16; ++j) part[rsub][c * 16 + j] = acc[j];
+  __syncthreads();
+  for (int col = threadIdx.x; col < kGroups * 16; col += 256) {
+    float s = 0.f;
+#pragma unroll
+    for (int r = 0; r < kRowsPerIter; ++r) s += part[r][col];
+    atomicAdd(colsum + col, s);
+  }
+}
+
 __global__ void embed_fwd_kernel(const int64_t* __restrict__ tokens, const int64_t* __restrict__ positions,
                                  const __nv_bfloat16* __restrict__ table, const __nv_bfloat16* __restrict__ pos_table,
                                  __nv_bfloat16* __restrict__ out, int rows, int hidden, int vocab, int max_pos,
@@ -230,6 +276,31 @@ const char* nmtg_dropout_add(const void* x, const void* residual, void* y, long 
   dropout_add_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(
       reinterpret_cast<const __nv_bfloat16*>(x), reinterpret_cast<const __nv_bfloat16*>(residual),
       reinterpret_cast<__nv_bfloat16*>(y), n16, p, seed, stream_id, seed_dev);
+  return last_err();
+}
+
+const char* nmtg_dropout_colsum(const void* x, void* y, float* colsum, int rows, int cols, float p, unsigned long long seed,
+                                unsigned long long stream_id, const unsigned long long* seed_dev, cudaStream_t stream) {
+  if (rows <= 0 || cols <= 0) return nullptr;
+  const int groups = cols / 16;
+  if (cols % 16 || groups > 256 || (256 % groups) != 0) return "dropout_colsum: columns must be 16 * a divisor of 256";
+  const int rows_per_iter = 256 / groups;
+  long blocks = (static_cast<long>(rows) + rows_per_iter - 1) / rows_per_iter;
+  const long cap = static_cast<long>(num_sms()) * 4;
+  if (blocks > cap) blocks = cap;
+  auto go = [&](auto tag) {
+    dropout_colsum_kernel<decltype(tag)::value><<<static_cast<int>(blocks), 256, 0, stream>>>(
+        reinterpret_cast<const __nv_bfloat16*>(x), reinterpret_cast<__nv_bfloat16*>(y), colsum, rows, p, seed, stream_id, seed_dev);
+  };
+  switch (groups) {
+    case 256: go(std::integral_constant<int, 256>()); break;
+    case 128: go(std::integral_constant<int, 128>()); break;
+    case 64: go(std::integral_constant<int, 64>()); break;
+    case 32: go(std::integral_constant<int, 32>()); break;
+    case 16: go(std::integral_constant<int, 16>()); break;
+    case 8: go(std::integral_constant<int, 8>()); break;
+    default: return "dropout_colsum: unsupported column count";
+  }
   return last_err();
 }
 

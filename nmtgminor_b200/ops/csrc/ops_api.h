@@ -68,6 +68,9 @@ const char* nmtg_xent_fused(void* logits, const int64_t* labels, float* row_loss
 
 // y = (residual ? residual : 0) + dropout(x) over n bf16 elements (n % 16 == 0).  The backward of the
 // dropout branch is the same call with x = dy, residual = null.
+// y = dropout-mask(x) with dropout_add's mask; colsum[cols] += column sums of y.  cols = 16 * (a divisor of 256).
+const char* nmtg_dropout_colsum(const void* x, void* y, float* colsum, int rows, int cols, float p, unsigned long long seed,
+                                unsigned long long stream_id, const unsigned long long* seed_dev, cudaStream_t stream);
 const char* nmtg_dropout_add(const void* x, const void* residual, void* y, long n, float p, unsigned long long seed,
                              unsigned long long stream_id, const unsigned long long* seed_dev, cudaStream_t stream);
 // out[r] = dropout(table[tokens[r]] * scale + pos_table[positions[r]])  (pos_table / positions optional)

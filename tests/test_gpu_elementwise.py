@@ -124,6 +124,20 @@ def test_colsum():
     _close(out, x.float().sum(0) + 1, 5e-2, 1e-3, "colsum")
 
 
+@pytest.mark.parametrize("rows,cols", [(1, 128), (37, 256), (1000, 1024), (8148, 1024), (513, 4096), (300, 512)])
+def test_dropout_colsum_matches_two_passes(rows, cols):
+    torch.manual_seed(2)
+    x = torch.randn(rows, cols, device=DEV).bfloat16()
+    want_y = ops.ext().dropout_add(x, None, 0.3, 99, 5)
+    want_sum = torch.full((cols,), 2.0, device=DEV)
+    ops.ext().colsum(want_y, want_sum)
+    got_sum = torch.full((cols,), 2.0, device=DEV)
+    got_y = ops.ext().dropout_colsum(x, 0.3, 99, 5, got_sum)
+    assert torch.equal(got_y, want_y)
+    _close(got_sum, want_y.float().sum(0) + 2, 1e-3 * math.sqrt(rows) + 1e-3, 1e-4, "dropout_colsum vs fp32")
+    _close(got_sum, want_sum, 5e-2, 1e-3, "dropout_colsum vs colsum")
+
+
 @pytest.mark.parametrize("decoupled,clip", [(True, 0.0), (False, 0.0), (True, 0.5)])
 def test_adamw_flat(decoupled, clip):
     torch.manual_seed(6)
