@@ -264,8 +264,8 @@ class TextToTextPretrained(Seq2SeqBase):
 
 def _wav2vec_from_opt(opt):
     """Speech encoder chosen by substring of ``-enc_pretrained_model`` (reference: onmt/model_factory.py:247-272):
-    ``s4`` -> state-space encoder on feature frames; ``w2vbert`` / ``w2v-bert`` / ``xeus`` -> Conformer-style encoder on
-    filterbank frames; ``hubert`` / anything else -> the wav2vec 2.0 architecture on raw audio (HuBERT shares it);
+    ``s4`` -> state-space encoder on feature frames; ``w2vbert`` / ``w2v-bert`` / ``xeus`` -> Conformer-Shaw encoder on
+    stacked filterbank frames (``models/w2vbert.py``); ``hubert`` / anything else -> the wav2vec 2.0 architecture on raw audio (HuBERT shares it);
     ``wavlm`` -> the same stack with the gated relative-position bias in every self-attention."""
     cfg = load_json_config(getattr(opt, "enc_config_file", ""))
     name = (getattr(opt, "enc_pretrained_model", "") or "wav2vec2").lower()
@@ -275,10 +275,8 @@ def _wav2vec_from_opt(opt):
                                    _cfg(cfg, ["encoder_layers"], opt.layers), _cfg(cfg, ["num_heads"], 4),
                                    _cfg(cfg, ["state_dim"], 32), opt.dropout)
     if "w2vbert" in name or "w2v-bert" in name or "xeus" in name:
-        from .conformer import ConformerEncoder
-        enc = ConformerEncoder(opt, getattr(opt, "input_size", 160))
-        enc.dim = opt.model_size
-        return enc
+        from .w2vbert import build_w2vbert_encoder
+        return build_w2vbert_encoder(opt, vars(cfg))
     base = "base" in name
     return Wav2Vec2Encoder(
         dim=_cfg(cfg, ["encoder_embed_dim", "hidden_size"], 768 if base else 1024),
