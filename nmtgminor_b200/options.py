@@ -53,17 +53,26 @@ def _add(parser: argparse.ArgumentParser, rows: Iterable) -> None:
         parser.add_argument(flag, **kw)
 
 
+def _md(parser) -> None:
+    """``-md``: print the options as Markdown (reference: onmt/markdown.py, wired in train.py / translate.py)."""
+    from .utils.markdown import add_md_help_argument
+    if not any("-md" in a.option_strings for a in parser._actions):
+        add_md_help_argument(parser)
+
+
 def make_parser(parser: Optional[argparse.ArgumentParser] = None) -> argparse.ArgumentParser:
     """Training parser (``train.py`` / ``train_distributed.py``)."""
     parser = parser or argparse.ArgumentParser(description="train")
     _add(parser, TRAIN_FLAGS)
     _add(parser, EXTRA_TRAIN_FLAGS)
+    _md(parser)
     return parser
 
 
 def make_translate_parser(parser: Optional[argparse.ArgumentParser] = None) -> argparse.ArgumentParser:
     parser = parser or argparse.ArgumentParser(description="translate")
     _add(parser, TRANSLATE_FLAGS)
+    _md(parser)
     return parser
 
 
