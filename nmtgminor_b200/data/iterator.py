@@ -156,9 +156,13 @@ class DataIterator:
 
 
 class MultiDataIterator:
-    """Interleaves several ``DataIterator`` objects; dataset i is drawn with probability ~ its length."""
+    """Interleaves several ``DataIterator`` objects; dataset i is drawn with probability ~ its length, so an epoch is
+    one pass over all of them.  With ``probabilities`` (e.g. equal weights) the source of every batch is drawn with
+    those weights and the epoch ends when the first data set runs out, with a schedule that changes every epoch
+    (reference: whisper/trainers/trainer_shuffle_ctc.py:231-239, equal-probability interleaving reseeded per call)."""
 
-    def __init__(self, datasets, seed: int = 1, dataset_ids=None, **kw):
+    def __init__(self, datasets, seed: int = 1, dataset_ids=None, probabilities=None, **kw):
+        self.probabilities = None if probabilities is None else [float(p) / sum(probabilities) for p in probabilities]
         ids = list(range(len(datasets))) if dataset_ids is None else list(dataset_ids)
         self.iterators = [DataIterator(datasets[i], seed=seed + 17 * i, **kw) for i in ids]
         self.seed = seed
@@ -168,12 +172,22 @@ class MultiDataIterator:
         self._pos = 0
 
     def __len__(self):
-        return sum(len(it) for it in self.iterators)
+        return len(self._schedule) if (self.probabilities is not None and self._schedule) else sum(len(it) for it in self.iterators)
 
     def next_epoch_itr(self, **kw):
         self._active = [it.next_epoch_itr(**kw) for it in self.iterators]
-        sched = [i for i, it in enumerate(self.iterators) for _ in range(len(it))]
-        np.random.RandomState(self.seed + self.epoch).shuffle(sched)
+        rng = np.random.RandomState(self.seed + self.epoch)
+        if self.probabilities is None:
+            sched = [i for i, it in enumerate(self.iterators) for _ in range(len(it))]
+            rng.shuffle(sched)
+        else:
+            left = [len(it) for it in self.iterators]
+            sched = []
+            for i in rng.choice(len(left), size=sum(left), p=self.probabilities).tolist():
+                if left[i] == 0:
+                    break               # first data set exhausted: the epoch ends here
+                left[i] -= 1
+                sched.append(i)
         self._schedule, self._pos = sched, 0
         self.epoch += 1
         return self

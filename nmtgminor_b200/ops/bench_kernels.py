@@ -1,6 +1,6 @@
 """Per-kernel micro-benchmarks on the shapes of the Transformer-big training step.
 
-    python -m nmtgminor_b200.ops.bench_kernels [--json out.json] [--only gemm,attn,...]   (--only gemm_stalls: cycle breakdown of the CTA-pair GEMM)
+    python -m nmtgminor_b200.ops.bench_kernels [--json out.json] [--only gemm,attn,attn_long,...]   (--only gemm_stalls: cycle breakdown of the CTA-pair GEMM)
 
 Each kernel is timed with CUDA events after warm-up; between timed launches a 256 MB buffer is rewritten so
 the 126 MB L2 starts cold.  GEMMs report TFLOP/s next to ``torch.matmul`` (cuBLAS) on the same shape as a
@@ -172,6 +172,35 @@ def bench_attention(rows):
         rows.append({"kernel": "attention bwd causal=%s" % causal, "ms": ms, "tflops": 2.5 * fl / ms / 1e9})
 
 
+def bench_attention_long(rows):
+    """The general multi-tile kernels on speech-length sequences: 8 x 1500 encoder frames with 20 heads (Whisper-large
+    encoder self-attention, no dropout) and 8 x 448 causal with dropout 0.1 (decoder self-attention)."""
+    e = ops.ext()
+    for L, heads, causal, p in ((1500, 20, False, 0.0), (448, 20, True, 0.1), (1000, 16, False, 0.1)):
+        B, W = 8, heads * 64
+        n = B * L
+        cap = (n + 127) // 128 * 128
+        cu = (torch.arange(B + 1, dtype=torch.int32) * L).cuda()
+        qkv = torch.randn(cap, 3 * W, device="cuda").bfloat16()
+        out = torch.zeros(cap, W, device="cuda", dtype=torch.bfloat16)
+        lse = torch.empty(heads, cap, device="cuda")
+        q, k, v = qkv[:, :W], qkv[:, W:2 * W], qkv[:, 2 * W:]
+        fl = 4.0 * L * L * 64 * heads * B * (0.5 if causal else 1.0)
+        ms = time_ms(lambda: e.attn_fwd(q, k, v, out, lse, cu, cu, heads, L, L, causal, 0.125, p, 1, 1))
+        rows.append({"kernel": "attention fwd %d x %d, %d heads, causal=%s, p=%.1f" % (B, L, heads, causal, p), "ms": ms,
+                     "tflops": fl / ms / 1e9})
+        dqkv = torch.zeros_like(qkv)
+        dout = torch.randn_like(out)
+        acc = torch.zeros(cap, W, device="cuda")
+
+        def bwd():
+            acc.zero_()
+            e.attn_bwd(q, k, v, out, lse, dout, dqkv[:, :W], dqkv[:, W:2 * W], dqkv[:, 2 * W:], acc, cu, cu, heads, L, L,
+                       causal, 0.125, p, 1, 1)
+        ms = time_ms(bwd)
+        rows.append({"kernel": "attention bwd (incl. clearing the dQ accumulator)", "ms": ms, "tflops": 2.5 * fl / ms / 1e9})
+
+
 def bench_gemm_stalls():
     """Where the CTA-pair GEMM spends its cycles: the traced build of the kernel counts, per cluster, how long the MMA
     issuer waited for operands and for a free accumulator and how long the epilogue waited for a finished one; two
@@ -256,6 +285,8 @@ def main():
         bench_elementwise(rows)
     if "attn" in which:
         bench_attention(rows)
+    if "attn_long" in which:
+        bench_attention_long(rows)
     tf_peak, bw_peak, kind = peaks()
     for r in rows:
         line = "%-48s %8.3f ms" % (r["kernel"], r["ms"])

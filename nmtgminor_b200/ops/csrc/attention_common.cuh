@@ -14,6 +14,12 @@ constexpr int kTileBytes = kTile * kHd * 2;   // 16 KB : one [128 x 64] bf16 til
 constexpr int kPBytes = kTile * kTile * 2;    // 32 KB : P or dS as two [128 x 64] slabs
 constexpr float kNegBig = -1.0e30f;
 
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 struct AttnArgs {
   const int* cu_q;
   const int* cu_k;

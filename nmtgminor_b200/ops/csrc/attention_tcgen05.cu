@@ -35,8 +35,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   uint8_t* sK = sQ + kTileBytes;
   uint8_t* sV = sK + kTileBytes;
   uint8_t* sP = sV + kTileBytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + kPBytes);  // [0]=Q [1]=KV [2]=MMA
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + kPBytes);  // [0]=Q [1]=K [2]=MMA [3]=V
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4);
   volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   zero_tail_fwd(p);
@@ -52,6 +52,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     mbar_init(&bars[0], 1);
     mbar_init(&bars[1], 1);
     mbar_init(&bars[2], 1);
+    mbar_init(&bars[3], 1);
     *abort_word = 0;
     mbar_fence_init();
   }
@@ -71,7 +72,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   const uint32_t idesc_s = make_idesc_bf16(kTile, kTile, 0, 0);
   const uint32_t idesc_o = make_idesc_bf16(kTile, kHd, 0, 1);
 
-  float m_run = kNegBig, l_run = 0.f;
+  float m_run = kNegBig, l_run = 0.f;          // running maximum in the base-2 domain, running sum
+  const float scale_log2 = p.scale * 1.4426950408889634f;
   float o_acc[kHd];
 #pragma unroll
   for (int j = 0; j < kHd; ++j) o_acc[j] = 0.f;
@@ -85,11 +87,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   uint32_t ph_kv = 0, ph_mma = 0;
   bool ok = true;
 
+  // The K tile of the next iteration is requested as soon as S = Q K^T of this one has been computed, the V tile as soon
+  // as O = P V has: both loads run under the softmax of the tile in between.
+  if (t == 0 && num_kt > 0) {
+    mbar_expect_tx(&bars[1], kTileBytes);
+    tma_load_2d(sK, &tmap_k, &bars[1], h * kHd, k_begin);
+    mbar_expect_tx(&bars[3], kTileBytes);
+    tma_load_2d(sV, &tmap_v, &bars[3], h * kHd, k_begin);
+  }
   for (int kt = 0; kt < num_kt && ok; ++kt) {
     if (t == 0) {
-      mbar_expect_tx(&bars[1], 2 * kTileBytes);
-      tma_load_2d(sK, &tmap_k, &bars[1], h * kHd, k_begin + kt * kTile);
-      tma_load_2d(sV, &tmap_v, &bars[1], h * kHd, k_begin + kt * kTile);
       if (kt == 0) ok = mbar_wait(&bars[0], 0, abort_word, p.status, kTimeoutTmaFull);
       if (ok) ok = mbar_wait(&bars[1], ph_kv, abort_word, p.status, kTimeoutTmaFull);
       if (ok) {
@@ -98,29 +105,39 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         umma_commit(&bars[2]);
       }
     }
-    ph_kv ^= 1;
     if (!mbar_wait(&bars[2], ph_mma, abort_word, p.status, kTimeoutTmemFull)) { ok = false; break; }
     ph_mma ^= 1;
     tc_fence_after_sync();
+    if (t == 0 && kt + 1 < num_kt) {       // the MMA that read sK has completed
+      mbar_expect_tx(&bars[1], kTileBytes);
+      tma_load_2d(sK, &tmap_k, &bars[1], h * kHd, k_begin + (kt + 1) * kTile);
+    }
 
     // ---- softmax over this key tile: two passes over the 128 score columns of my row -----------
+    // Scores stay in the base-2 domain (score * scale * log2 e), so one FMA + one ex2 makes a probability.  A tile whose
+    // 128 x 128 scores are all inside the sequence (and below the diagonal when causal) skips the per-element masks.
     const int kcols = min(kTile, k_len - kt * kTile);
+    const bool full = kcols == kTile && (!p.causal || kt < qt);
     float tile_max = kNegBig;
 #pragma unroll 1
     for (int c = 0; c < 4; ++c) {
       uint32_t r[32];
       tmem_ld32(tS + lane_sel + c * 32, r);
       tmem_ld_wait();
+      if (full) {
 #pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        const int col = c * 32 + j;
-        const bool valid = col < kcols && (!p.causal || kt * kTile + col <= q_pos);
-        const float s = valid ? __uint_as_float(r[j]) * p.scale : kNegBig;
-        tile_max = fmaxf(tile_max, s);
+        for (int j = 0; j < 32; ++j) tile_max = fmaxf(tile_max, __uint_as_float(r[j]));
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const int col = c * 32 + j;
+          const bool valid = col < kcols && (!p.causal || kt * kTile + col <= q_pos);
+          tile_max = fmaxf(tile_max, valid ? __uint_as_float(r[j]) : kNegBig);
+        }
       }
     }
-    const float m_new = fmaxf(m_run, tile_max);
-    const float alpha = __expf(m_run - m_new);
+    const float m_new = fmaxf(m_run, tile_max * scale_log2);    // scale > 0: the maximum commutes with the scaling
+    const float alpha = ex2_approx(m_run - m_new);
     float row_sum = 0.f;
 #pragma unroll 1
     for (int c = 0; c < 4; ++c) {
@@ -128,13 +145,21 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       tmem_ld32(tS + lane_sel + c * 32, r);
       tmem_ld_wait();
       float pv[32];
+      if (full) {
 #pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        const int col = c * 32 + j;
-        const bool valid = col < kcols && (!p.causal || kt * kTile + col <= q_pos);
-        const float e = valid ? __expf(__uint_as_float(r[j]) * p.scale - m_new) : 0.f;
-        row_sum += e;
-        pv[j] = e;
+        for (int j = 0; j < 32; ++j) {
+          pv[j] = ex2_approx(fmaf(__uint_as_float(r[j]), scale_log2, -m_new));
+          row_sum += pv[j];
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const int col = c * 32 + j;
+          const bool valid = col < kcols && (!p.causal || kt * kTile + col <= q_pos);
+          const float e = valid ? ex2_approx(fmaf(__uint_as_float(r[j]), scale_log2, -m_new)) : 0.f;
+          row_sum += e;
+          pv[j] = e;
+        }
       }
       if (do_drop) {
         const unsigned long long base = static_cast<unsigned long long>(q0 + t) * p.kstride + kt * kTile + c * 32;
@@ -157,15 +182,22 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     fence_async_smem();
     __syncthreads();
     if (t == 0) {
-      tc_fence_after_sync();
-      // O_tile = P V : A = P (K-major, two slabs of 4 k-steps), B = V (MN-major, 16 keys per k-step)
-      umma_steps(tO, smem_u32(sP), 16, 32, smem_u32(sV), 8192, 2048, idesc_o, 4, false);
-      umma_steps(tO, smem_u32(sP) + kTileBytes, 16, 32, smem_u32(sV) + 4 * 2048, 8192, 2048, idesc_o, 4, true);
-      umma_commit(&bars[2]);
+      if (mbar_wait(&bars[3], ph_kv, abort_word, p.status, kTimeoutTmaFull)) {
+        tc_fence_after_sync();
+        // O_tile = P V : A = P (K-major, two slabs of 4 k-steps), B = V (MN-major, 16 keys per k-step)
+        umma_steps(tO, smem_u32(sP), 16, 32, smem_u32(sV), 8192, 2048, idesc_o, 4, false);
+        umma_steps(tO, smem_u32(sP) + kTileBytes, 16, 32, smem_u32(sV) + 4 * 2048, 8192, 2048, idesc_o, 4, true);
+        umma_commit(&bars[2]);
+      }
     }
+    ph_kv ^= 1;
     if (!mbar_wait(&bars[2], ph_mma, abort_word, p.status, kTimeoutTmemFull)) { ok = false; break; }
     ph_mma ^= 1;
     tc_fence_after_sync();
+    if (t == 0 && kt + 1 < num_kt) {       // the MMA that read sV has completed
+      mbar_expect_tx(&bars[3], kTileBytes);
+      tma_load_2d(sV, &tmap_v, &bars[3], h * kHd, k_begin + (kt + 1) * kTile);
+    }
 #pragma unroll
     for (int c = 0; c < 2; ++c) {
       uint32_t r[32];
@@ -189,7 +221,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       for (int j = 0; j < 4; ++j) o2[j] = __floats2bfloat162_rn(o_acc[g * 8 + 2 * j] * inv, o_acc[g * 8 + 2 * j + 1] * inv);
       reinterpret_cast<uint4*>(orow)[g] = o;
     }
-    if (p.lse) p.lse[static_cast<size_t>(h) * p.lse_stride + q0 + t] = l_run > 0.f ? m_run + __logf(l_run) : 0.f;
+    if (p.lse) p.lse[static_cast<size_t>(h) * p.lse_stride + q0 + t] = l_run > 0.f ? (m_run + __log2f(l_run)) * 0.6931471805599453f : 0.f;
   }
   tc_fence_before_sync();
   __syncthreads();
@@ -263,6 +295,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   const uint32_t idesc_dq = make_idesc_bf16(kTile, kHd, 0, 1);     // dQ    : K-major A, MN-major B, N = 64
   const uint32_t idesc_dkv = make_idesc_bf16(kTile, kHd, 1, 1);    // dK,dV : MN-major A and B, N = 64
 
+  const float scale_log2 = p.scale * 1.4426950408889634f;
   const bool do_drop = p.dropout_p > 0.f;
   const DropRng rng(p.seed + ((do_drop && p.seed_dev) ? *p.seed_dev : 0ull),
                     (p.stream_id << 16) | static_cast<unsigned long long>(h), p.dropout_p);
@@ -325,24 +358,38 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     tc_fence_after_sync();
 
     const int q_pos = qt * kTile + t;
+    // P = 2^(S * scale * log2 e - lse * log2 e); dS is kept WITHOUT the softmax scale (dQ and dK are scaled when they
+    // leave TMEM: 64 multiplies per row instead of 128 per row and tile).  A tile with all 128 x 128 scores inside both
+    // sequences (and below the diagonal when causal) and no dropout takes the branch without per-element masks.
+    const bool full = q_rows == kTile && k_rows == kTile && (!p.causal || kt < qt);
+    const float lse2 = lse * 1.4426950408889634f;
 #pragma unroll 1
     for (int c = 2 * grp; c < 2 * grp + 2; ++c) {      // this warpgroup's 64 of the 128 key columns
       uint32_t rs[32], rd[32];
       tmem_ld32(tS + lane_sel + c * 32, rs);
       tmem_ld32(tDP + lane_sel + c * 32, rd);
       tmem_ld_wait();
-      float pd[32], ds[32], kf[32];
-      const unsigned long long base = static_cast<unsigned long long>(q0 + t) * p.kstride + kt * kTile + c * 32;
+      float pd[32], ds[32];
+      if (full && !do_drop) {
 #pragma unroll
-      for (int j = 0; j < 32; ++j) kf[j] = 1.f;
-      if (do_drop) apply_dropout32(rng, base, kf);
+        for (int j = 0; j < 32; ++j) {
+          pd[j] = ex2_approx(fmaf(__uint_as_float(rs[j]), scale_log2, -lse2));
+          ds[j] = pd[j] * (__uint_as_float(rd[j]) - Drow);
+        }
+      } else {
+        float kf[32];
+        const unsigned long long base = static_cast<unsigned long long>(q0 + t) * p.kstride + kt * kTile + c * 32;
 #pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        const int col = c * 32 + j;
-        const bool valid = row_ok && col < k_rows && (!p.causal || kt * kTile + col <= q_pos);
-        const float pr = valid ? __expf(__uint_as_float(rs[j]) * p.scale - lse) : 0.f;
-        pd[j] = pr * kf[j];
-        ds[j] = pr * (__uint_as_float(rd[j]) * kf[j] - Drow) * p.scale;
+        for (int j = 0; j < 32; ++j) kf[j] = 1.f;
+        if (do_drop) apply_dropout32(rng, base, kf);
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const int col = c * 32 + j;
+          const bool valid = row_ok && col < k_rows && (!p.causal || kt * kTile + col <= q_pos);
+          const float pr = valid ? ex2_approx(fmaf(__uint_as_float(rs[j]), scale_log2, -lse2)) : 0.f;
+          pd[j] = pr * kf[j];
+          ds[j] = pr * (__uint_as_float(rd[j]) * kf[j] - Drow);
+        }
       }
 #pragma unroll
       for (int g = 0; g < 4; ++g) {
@@ -392,7 +439,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
 #pragma unroll
             for (int j = 0; j < 4; ++j)
-              o2[j] = __floats2bfloat162_rn(__uint_as_float(r[g * 8 + 2 * j]), __uint_as_float(r[g * 8 + 2 * j + 1]));
+              o2[j] = __floats2bfloat162_rn(__uint_as_float(r[g * 8 + 2 * j]) * p.scale, __uint_as_float(r[g * 8 + 2 * j + 1]) * p.scale);
             reinterpret_cast<uint4*>(drow)[g] = o;
           }
         } else {
@@ -400,8 +447,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
 #pragma unroll
           for (int g = 0; g < 8; ++g)
             asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(arow + g * 4),
-                         "f"(__uint_as_float(r[g * 4])), "f"(__uint_as_float(r[g * 4 + 1])),
-                         "f"(__uint_as_float(r[g * 4 + 2])), "f"(__uint_as_float(r[g * 4 + 3]))
+                         "f"(__uint_as_float(r[g * 4]) * p.scale), "f"(__uint_as_float(r[g * 4 + 1]) * p.scale),
+                         "f"(__uint_as_float(r[g * 4 + 2]) * p.scale), "f"(__uint_as_float(r[g * 4 + 3]) * p.scale)
                          : "memory");
         }
       }
@@ -424,13 +471,14 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         tmem_ld_wait();
         if (t < k_rows) {
           __nv_bfloat16* drow = dst + static_cast<size_t>(k0 + t) * ld + h * kHd + c * 32;
+          const float osc = which == 0 ? p.scale : 1.f;     // dK carries the softmax scale that dS left out
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
             uint4 o;
             __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
 #pragma unroll
             for (int j = 0; j < 4; ++j)
-              o2[j] = __floats2bfloat162_rn(__uint_as_float(r[g * 8 + 2 * j]), __uint_as_float(r[g * 8 + 2 * j + 1]));
+              o2[j] = __floats2bfloat162_rn(__uint_as_float(r[g * 8 + 2 * j]) * osc, __uint_as_float(r[g * 8 + 2 * j + 1]) * osc);
             reinterpret_cast<uint4*>(drow)[g] = o;
           }
         }

@@ -166,6 +166,23 @@ class Trainer:
         return name
 
     # ------------------------------------------------------------------------------------------
+    def _guarded_step(self, batch, update: bool):
+        """One engine step; a batch that runs the device out of memory is dropped (its partial gradients with it) and
+        training goes on, as in the reference (onmt/train_utils/mp_trainer.py: "out of memory" handling of the step;
+        whisper/trainers/trainer_shuffle_ctc.py:169-177).  With several ranks the other ranks are already waiting in
+        the gradient exchange of this step, so there the error is raised."""
+        try:
+            return self.engine.train_step(batch, update=update)[0]
+        except torch.cuda.OutOfMemoryError:
+            if self.world_size > 1:
+                raise
+            self.oom_skipped = getattr(self, "oom_skipped", 0) + 1
+            self.log("[WARNING] out of device memory on a batch of %d source / %d target tokens; batch skipped (%d so far)"
+                     % (batch.src_size, batch.tgt_size, self.oom_skipped))
+            self.optim.zero_grad()
+            torch.cuda.empty_cache()
+            return torch.zeros((), device=self.engine.device if self.cuda else "cpu")
+
     def train_epoch(self, train_data, valid_data, epoch: int, resume_itr_state=None):
         opt = self.opt
         iterator = self._iterator(train_data, epoch)
@@ -189,7 +206,7 @@ class Trainer:
             if update and getattr(opt, "normalize_gradient", False):
                 total_words = self._all_reduce_scalars([float(acc_words)])[0]
                 self.engine.grad_scale = 1.0 / max(total_words, 1.0)
-            loss, _ = self.engine.train_step(batch, update=update)
+            loss = self._guarded_step(batch, update)
             pending.append(loss if self.engine.use_graph is False else loss.clone())
             report["tgt"] += batch.tgt_size
             report["src"] += batch.src_size

@@ -103,6 +103,40 @@ def test_buffered_and_multi_iterators():
     assert sum(1 for _ in m.next_epoch_itr()) == len(a) + len(b)
 
 
+def test_multi_iterator_equal_probability_interleave():
+    a, b = synthetic_dataset(100, 50, 3, 10, 100, seed=1), synthetic_dataset(60, 50, 3, 10, 100, seed=2)
+    m = MultiDataIterator([a, b], seed=3, probabilities=[1, 1])
+    n1 = sum(1 for _ in m.next_epoch_itr())
+    first = list(m._schedule)
+    assert 0 < n1 <= len(a) + len(b) and n1 == len(m)
+    assert min(first.count(0), first.count(1)) > 0 and (first.count(0) == len(a) or first.count(1) == len(b))
+    m.next_epoch_itr()
+    assert m._schedule != first                     # reseeded per epoch
+
+
+def test_trainer_skips_a_batch_that_runs_out_of_memory():
+    from types import SimpleNamespace
+    from nmtgminor_b200.train.trainer import Trainer
+    calls = {"zero": 0}
+
+    class _Engine:
+        device = "cpu"
+
+        def train_step(self, batch, update=True):
+            raise torch.cuda.OutOfMemoryError("CUDA out of memory (simulated on the host)")
+
+    tr = Trainer.__new__(Trainer)
+    tr.engine, tr.world_size, tr.cuda = _Engine(), 1, False
+    tr.optim = SimpleNamespace(zero_grad=lambda: calls.__setitem__("zero", calls["zero"] + 1))
+    tr.log = lambda msg: None
+    loss = tr._guarded_step(SimpleNamespace(src_size=5, tgt_size=7), True)
+    assert float(loss) == 0.0 and calls["zero"] == 1 and tr.oom_skipped == 1
+    tr.world_size = 2
+    import pytest
+    with pytest.raises(torch.cuda.OutOfMemoryError):
+        tr._guarded_step(SimpleNamespace(src_size=5, tgt_size=7), True)
+
+
 def test_mmap_and_legacy_indexed_roundtrip(tmp_path):
     items = [torch.randint(0, 60000, (n,)) for n in (3, 1, 17, 5)]
     prefix = str(tmp_path / "corpus")
