@@ -199,6 +199,15 @@ def bench_attention_long(rows):
                        causal, 0.125, p, 1, 1)
         ms = time_ms(bwd)
         rows.append({"kernel": "attention bwd (incl. clearing the dQ accumulator)", "ms": ms, "tflops": 2.5 * fl / ms / 1e9})
+        # the library kernels on the same problem (padded [B, H, L, 64] layout, which favours them: no packing work)
+        import torch.nn.functional as F
+        qs, ks, vs = (torch.randn(B, heads, L, 64, device="cuda", dtype=torch.bfloat16, requires_grad=True) for _ in range(3))
+        ms = time_ms(lambda: F.scaled_dot_product_attention(qs, ks, vs, dropout_p=p, is_causal=causal))
+        rows.append({"kernel": "  torch SDPA fwd, same shape", "ms": ms, "tflops": fl / ms / 1e9})
+        o = F.scaled_dot_product_attention(qs, ks, vs, dropout_p=p, is_causal=causal)
+        go = torch.randn_like(o)
+        ms = time_ms(lambda: torch.autograd.grad(o, (qs, ks, vs), go, retain_graph=True))
+        rows.append({"kernel": "  torch SDPA bwd, same shape", "ms": ms, "tflops": 2.5 * fl / ms / 1e9})
 
 
 def bench_gemm_stalls():

@@ -7,6 +7,7 @@
 namespace b200 {
 
 bool cached_tmap(CUtensorMap* out, const void* base, long rows, long cols, long ld, int br, int bc);
+bool cached_tmap_f32(CUtensorMap* out, const void* base, long rows, long cols, long ld, int br, int bc);
 
 constexpr int kHd = 64;          // head dimension
 constexpr int kTile = 128;       // query / key tile
@@ -40,6 +41,8 @@ struct AttnArgs {
   __nv_bfloat16* dk; int ld_dk;
   __nv_bfloat16* dv; int ld_dv;
   float* dq_acc; int ld_dqacc;          // fp32 accumulation buffer for multi-key-tile sequences
+  const float* delta;                   // rowsum(dO * O), laid out like lse; null: computed in the kernel per tile
+  int dq_tma;                           // 1: dQ tiles are added to dq_acc by TMA reductions (tensor map given to the kernel)
   int total_q;
   int total_k;            // allocated rows of q / k (>= cu[batch]): rows past the last sequence are cleared by the kernels
   int batch;

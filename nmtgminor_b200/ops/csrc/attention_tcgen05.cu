@@ -243,7 +243,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
 __global__ void __launch_bounds__(256)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                 const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
-                const AttnArgs p) {
+                const __grid_constant__ CUtensorMap tmap_dq, const AttnArgs p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sK = smem;
@@ -254,7 +254,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   uint8_t* sDO1 = sQ1 + kTileBytes;
   uint8_t* sP = sDO1 + kTileBytes;
   uint8_t* sDS = sP + kPBytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sDS + kPBytes);  // [0]=KV [1]=Q,dO buffer 0 [2]=MMA [3]=Q,dO buffer 1
+  uint8_t* sDQ = sDS + kPBytes;           // fp32 dQ staging: one [128 x 32] 128-byte-swizzled slab per warpgroup
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sDQ + 2 * kTileBytes);  // [0]=KV [1]=Q,dO buffer 0 [2]=MMA [3]=Q,dO buffer 1
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4);
   volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -338,17 +339,21 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     const bool row_ok = t < q_rows;
     float Drow = 0.f, lse = 0.f;
     if (row_ok) {
-      const uint4* orow = reinterpret_cast<const uint4*>(p.o + static_cast<size_t>(q0 + t) * p.ld_o + h * kHd);
-      const uint4* drow = reinterpret_cast<const uint4*>(p.d_o + static_cast<size_t>(q0 + t) * p.ld_do + h * kHd);
+      if (p.delta) {
+        Drow = p.delta[static_cast<size_t>(h) * p.lse_stride + q0 + t];
+      } else {
+        const uint4* orow = reinterpret_cast<const uint4*>(p.o + static_cast<size_t>(q0 + t) * p.ld_o + h * kHd);
+        const uint4* drow = reinterpret_cast<const uint4*>(p.d_o + static_cast<size_t>(q0 + t) * p.ld_do + h * kHd);
 #pragma unroll
-      for (int g = 0; g < 8; ++g) {
-        uint4 a = orow[g], d = drow[g];
-        const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&a);
-        const __nv_bfloat162* d2 = reinterpret_cast<const __nv_bfloat162*>(&d);
+        for (int g = 0; g < 8; ++g) {
+          uint4 a = orow[g], d = drow[g];
+          const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&a);
+          const __nv_bfloat162* d2 = reinterpret_cast<const __nv_bfloat162*>(&d);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          float2 x = __bfloat1622float2(a2[j]), y = __bfloat1622float2(d2[j]);
-          Drow += x.x * y.x + x.y * y.y;
+          for (int j = 0; j < 4; ++j) {
+            float2 x = __bfloat1622float2(a2[j]), y = __bfloat1622float2(d2[j]);
+            Drow += x.x * y.x + x.y * y.y;
+          }
         }
       }
       lse = p.lse[static_cast<size_t>(h) * p.lse_stride + q0 + t];
@@ -407,6 +412,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         *reinterpret_cast<uint4*>(sDS + off) = o2v;
       }
     }
+    if (t == 0) tma_store_wait_read();                 // last tile's dQ slab has been read by its reduction
     tc_fence_before_sync();
     fence_async_smem();
     __syncthreads();
@@ -430,7 +436,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       uint32_t r[32];
       tmem_ld32(tDQ + lane_sel + c * 32, r);
       tmem_ld_wait();
-      if (row_ok) {
+      if (row_ok || (!single_kt && p.dq_tma)) {      // rows past the sequence hold exact zeros: harmless in the tile sum
         if (single_kt) {
           __nv_bfloat16* drow = p.dq + static_cast<size_t>(q0 + t) * p.ld_dq + h * kHd + c * 32;
 #pragma unroll
@@ -441,6 +447,16 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             for (int j = 0; j < 4; ++j)
               o2[j] = __floats2bfloat162_rn(__uint_as_float(r[g * 8 + 2 * j]) * p.scale, __uint_as_float(r[g * 8 + 2 * j + 1]) * p.scale);
             reinterpret_cast<uint4*>(drow)[g] = o;
+          }
+        } else if (p.dq_tma) {
+          // my 32 values go to the staging slab of my warpgroup (conflict-free thanks to the swizzle); one thread per
+          // warpgroup hands the slab to the TMA unit after the barrier below: whole 128-byte lines reach the L2 reduction
+          // units, where a row-per-thread red.add sends 16-byte fragments of 32 different lines per instruction
+#pragma unroll
+          for (int g = 0; g < 8; ++g) {
+            float4 o = make_float4(__uint_as_float(r[g * 4]) * p.scale, __uint_as_float(r[g * 4 + 1]) * p.scale,
+                                   __uint_as_float(r[g * 4 + 2]) * p.scale, __uint_as_float(r[g * 4 + 3]) * p.scale);
+            *reinterpret_cast<float4*>(sDQ + grp * kTileBytes + sw128_offset(t, g)) = o;
           }
         } else {
           float* arow = p.dq_acc + static_cast<size_t>(q0 + t) * p.ld_dqacc + h * kHd + c * 32;
@@ -454,8 +470,14 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       }
     }
     tc_fence_before_sync();
+    if (!single_kt && p.dq_tma) fence_async_smem();
     __syncthreads();
+    if (!single_kt && p.dq_tma && t == 0) {          // one thread per warpgroup: dq_acc[q0 .. q0+127, my 32 columns] += slab
+      tma_reduce_add_2d(&tmap_dq, sDQ + grp * kTileBytes, h * kHd + grp * 32, q0);
+      tma_store_commit();
+    }
   }
+  if (t == 0) tma_store_wait_all();                  // the slabs must outlive the reductions that read them
 
   // dK, dV of my key row
   if (ok && !first) {
@@ -505,6 +527,30 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   }
 }
 
+// delta[h, row] = sum_j dO[row, h*64 + j] * O[row, h*64 + j]; one thread per (row, head), neighbours read neighbouring
+// 128-byte runs
+__global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o, int ld_o, const __nv_bfloat16* __restrict__ d_o, int ld_do,
+                                  float* __restrict__ delta, long stride, int total_q, int heads) {
+  const long i = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= static_cast<long>(total_q) * heads) return;
+  const int row = static_cast<int>(i / heads), h = static_cast<int>(i % heads);
+  const uint4* orow = reinterpret_cast<const uint4*>(o + static_cast<size_t>(row) * ld_o + h * kHd);
+  const uint4* drow = reinterpret_cast<const uint4*>(d_o + static_cast<size_t>(row) * ld_do + h * kHd);
+  float acc = 0.f;
+#pragma unroll
+  for (int g = 0; g < 8; ++g) {
+    uint4 a = orow[g], d = drow[g];
+    const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&a);
+    const __nv_bfloat162* d2 = reinterpret_cast<const __nv_bfloat162*>(&d);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float2 x = __bfloat1622float2(a2[j]), y = __bfloat1622float2(d2[j]);
+      acc += x.x * y.x + x.y * y.y;
+    }
+  }
+  delta[static_cast<size_t>(h) * stride + row] = acc;
+}
+
 // dq (bf16) = dq_acc (fp32) for rows of sequences with more than one key tile
 __global__ void attn_dq_convert_kernel(const float* __restrict__ acc, int ld_acc, __nv_bfloat16* __restrict__ dq, int ld_dq,
                                        const int* __restrict__ cu_q, const int* __restrict__ cu_k, int width) {
@@ -525,7 +571,7 @@ __global__ void attn_dq_convert_kernel(const float* __restrict__ acc, int ld_acc
 }
 
 constexpr int kFwdSmem = 3 * kTileBytes + kPBytes + 64 + 1024;
-constexpr int kBwdSmem = 6 * kTileBytes + 2 * kPBytes + 64 + 1024;
+constexpr int kBwdSmem = 8 * kTileBytes + 2 * kPBytes + 64 + 1024;
 
 }  // namespace b200
 
@@ -612,8 +658,19 @@ const char* nmtg_attn_bwd(const AttnDesc* d, cudaStream_t stream) {
     if (ce != cudaSuccess) return cudaGetErrorString(ce);
     configured = true;
   }
+  if (d->delta && d->max_k > kTile) {
+    const long n = static_cast<long>(d->total_q) * d->num_heads;
+    attn_delta_kernel<<<static_cast<int>((n + 255) / 256), 256, 0, stream>>>(a.o, a.ld_o, a.d_o, a.ld_do, d->delta, d->lse_stride,
+                                                                            d->total_q, d->num_heads);
+    a.delta = d->delta;
+  }
+  CUtensorMap tdq = tq;       // placeholder when the reductions go through red.add
+  a.dq_tma = 0;
+  if (d->dq_acc && d->max_k > kTile && (reinterpret_cast<uintptr_t>(d->dq_acc) & 15) == 0 && d->ld_dqacc % 4 == 0 &&
+      cached_tmap_f32(&tdq, d->dq_acc, d->total_q, width, d->ld_dqacc, kTile, 32))
+    a.dq_tma = 1;
   dim3 grid((d->max_k + kTile - 1) / kTile, d->num_heads, d->batch);
-  attn_bwd_kernel<<<grid, 256, kBwdSmem, stream>>>(tq, tk, tv, tdo, a);
+  attn_bwd_kernel<<<grid, 256, kBwdSmem, stream>>>(tq, tk, tv, tdo, tdq, a);
   cudaError_t ce = cudaGetLastError();
   if (ce != cudaSuccess) return cudaGetErrorString(ce);
   if (d->max_k > kTile) {
@@ -700,8 +757,10 @@ extern "C" int nmtg_attn_bwd_noalloc(const void* q, int ld_q, const void* k, int
   a.total_q = total_q; a.total_k = total_k; a.batch = batch; a.status = status;
   ce = cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kBwdSmem);
   if (ce != cudaSuccess) return noalloc_fail(3, cudaGetErrorString(ce), err, err_len);
+  CUtensorMap tdq = tq;       // placeholder when no accumulation buffer is needed
+  a.dq_tma = (needs_buffer && cached_tmap_f32(&tdq, scratch, total_q, width, width, kTile, 32)) ? 1 : 0;
   dim3 grid((max_k + kTile - 1) / kTile, num_heads, batch);
-  attn_bwd_kernel<<<grid, 256, kBwdSmem, stream>>>(tq, tk, tv, tdo, a);
+  attn_bwd_kernel<<<grid, 256, kBwdSmem, stream>>>(tq, tk, tv, tdo, tdq, a);
   ce = cudaGetLastError();
   if (ce != cudaSuccess) return noalloc_fail(3, cudaGetErrorString(ce), err, err_len);
   if (needs_buffer) {

@@ -299,6 +299,11 @@ void attn_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& o
     need_f32(*dq_acc, "dq_acc"); need_rowmajor2d(*dq_acc, "dq_acc");
     d.dq_acc = dq_acc->data_ptr<float>(); d.ld_dqacc = static_cast<int>(dq_acc->stride(0));
   }
+  Tensor delta;
+  if (max_k > 128) {
+    delta = torch::empty_like(lse);
+    d.delta = delta.data_ptr<float>();
+  }
   ck(nmtg_attn_bwd(&d, cur_stream()));
 }
 

@@ -234,8 +234,14 @@ static EncodeTiledFn get_encode_fn() {
 }
 
 // 2-D bf16 row-major tensor [rows, cols] with leading dimension ld (elements); box = [box_rows, box_cols].
+static bool make_tmap_2d(CUtensorMap* out, const void* base, long rows, long cols, long ld, int box_rows, int box_cols,
+                         bool f32);
 bool make_tmap_bf16_2d(CUtensorMap* out, const void* base, long rows, long cols, long ld, int box_rows,
                        int box_cols) {
+  return make_tmap_2d(out, base, rows, cols, ld, box_rows, box_cols, false);
+}
+static bool make_tmap_2d(CUtensorMap* out, const void* base, long rows, long cols, long ld, int box_rows, int box_cols,
+                         bool f32) {
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) return false;
   // The encoder is a driver entry point and needs a current context.  A thread that has issued no runtime call yet
@@ -246,10 +252,10 @@ bool make_tmap_bf16_2d(CUtensorMap* out, const void* base, long rows, long cols,
     context_bound = true;
   }
   cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
-  cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * (f32 ? 4 : 2)};
   cuuint32_t box[2] = {static_cast<cuuint32_t>(box_cols), static_cast<cuuint32_t>(box_rows)};
   cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+  CUresult r = fn(out, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS)
@@ -290,6 +296,26 @@ bool cached_tmap(CUtensorMap* out, const void* base, long rows, long cols, long 
     }
   }
   if (!make_tmap_bf16_2d(out, base, rows, cols, ld, br, bc)) return false;
+  std::lock_guard<std::mutex> g(mu);
+  if (cache.size() > 8192) cache.clear();
+  cache.emplace(k, *out);
+  return true;
+}
+
+// fp32 matrix, 128-byte-swizzled boxes (box_cols * 4 bytes <= 128); same cache, told apart by a negated column box
+bool cached_tmap_f32(CUtensorMap* out, const void* base, long rows, long cols, long ld, int br, int bc) {
+  static std::unordered_map<TmapKey, CUtensorMap, TmapKeyHash> cache;
+  static std::mutex mu;
+  TmapKey k{base, rows, cols, ld, br, -bc};
+  {
+    std::lock_guard<std::mutex> g(mu);
+    auto it = cache.find(k);
+    if (it != cache.end()) {
+      *out = it->second;
+      return true;
+    }
+  }
+  if (!make_tmap_2d(out, base, rows, cols, ld, br, bc, true)) return false;
   std::lock_guard<std::mutex> g(mu);
   if (cache.size() > 8192) cache.clear();
   cache.emplace(k, *out);

@@ -124,6 +124,8 @@ struct AttnDesc {
   void* dk; int ld_dk;
   void* dv; int ld_dv;
   float* dq_acc; int ld_dqacc;        // zero-initialised fp32 [total_q, heads*64]; needed when max_k > 128
+  float* delta;                       // optional scratch, fp32 [heads, lse_stride]: the backward pass of sequences above 128
+                                      // keys fills it with rowsum(dO * O) once instead of recomputing it per key tile
   int* status;
 };
 const char* nmtg_attn_fwd(const AttnDesc* d, cudaStream_t stream);
