@@ -4,8 +4,9 @@
 // Sequences are packed along the token dimension and described by cumulative offsets (cu_seqlens), so
 // key padding never exists; self-attention (optionally causal) and encoder-decoder attention (separate
 // query / key offsets) use the same kernels.  One CTA = one (128-query tile, head, sequence) in forward
-// and one (128-key tile, head, sequence) in backward.  Thread t of the CTA owns TMEM lane t = tile row
-// t, so the softmax needs no cross-thread reduction.
+// and one (128-key tile, head, sequence) in backward.  Two warpgroups of 128 threads each: thread t of a
+// warpgroup owns TMEM lane t = tile row t and half of that row's columns, so the softmax needs one
+// shared-memory exchange of the row maximum per tile and no shuffles.
 //
 // forward:   S = Q K^T (UMMA, K-major x K-major) -> online softmax in registers -> P (bf16, swizzled
 //            smem) -> O_tile = P V (UMMA, V consumed MN-major straight from its [keys, d] TMA tile).
@@ -26,7 +27,9 @@ namespace b200 {
 // ---------------------------------------------------------------------------------------------------
 // forward
 // ---------------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(128)
+// 256 threads: two warpgroups own the same 128 query rows (TMEM lanes) and split the 128 score columns and the 64 output
+// columns between them, so every scheduler has four warps (two CTAs per SM) to hide TMEM loads and exponentials behind.
+__global__ void __launch_bounds__(256, 2)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                 const __grid_constant__ CUtensorMap tmap_v, const AttnArgs p) {
   extern __shared__ uint8_t smem_raw[];
@@ -35,7 +38,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   uint8_t* sK = sQ + kTileBytes;
   uint8_t* sV = sK + kTileBytes;
   uint8_t* sP = sV + kTileBytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + kPBytes);  // [0]=Q [1]=K [2]=MMA [3]=V
+  float* sRed = reinterpret_cast<float*>(sP + kPBytes);        // [2][128]: row maxima / row sums of the two warpgroups
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sRed + 2 * kTile);  // [0]=Q [1]=K [2]=MMA [3]=V
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4);
   volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -46,9 +50,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   const int q0 = q_begin + qt * kTile;
   if (q0 >= q_end) return;  // uniform for the CTA, before any barrier or TMEM use
   const int q_rows = min(kTile, q_end - q0);
-  const int t = threadIdx.x, warp = t >> 5;
+  const int t = threadIdx.x & 127, warp = t >> 5, grp = threadIdx.x >> 7;
+  const bool leader = threadIdx.x == 0;
 
-  if (t == 0) {
+  if (leader) {
     mbar_init(&bars[0], 1);
     mbar_init(&bars[1], 1);
     mbar_init(&bars[2], 1);
@@ -56,7 +61,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     *abort_word = 0;
     mbar_fence_init();
   }
-  if (warp == 0) tmem_alloc(tmem_slot, 256);
+  if (threadIdx.x < 32) tmem_alloc(tmem_slot, 256);
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
@@ -65,18 +70,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   const uint32_t tO = tmem_base + 128;   // 64 columns
   const uint32_t lane_sel = static_cast<uint32_t>(warp * 32) << 16;
 
-  if (t == 0) {
+  if (leader) {
     mbar_expect_tx(&bars[0], kTileBytes);
     tma_load_2d(sQ, &tmap_q, &bars[0], h * kHd, q0);
   }
   const uint32_t idesc_s = make_idesc_bf16(kTile, kTile, 0, 0);
   const uint32_t idesc_o = make_idesc_bf16(kTile, kHd, 0, 1);
 
-  float m_run = kNegBig, l_run = 0.f;          // running maximum in the base-2 domain, running sum
+  float m_run = kNegBig, l_run = 0.f;          // running maximum in the base-2 domain, running sum of my 64 columns
   const float scale_log2 = p.scale * 1.4426950408889634f;
-  float o_acc[kHd];
+  float o_acc[32];                             // my warpgroup's 32 of the 64 output columns
 #pragma unroll
-  for (int j = 0; j < kHd; ++j) o_acc[j] = 0.f;
+  for (int j = 0; j < 32; ++j) o_acc[j] = 0.f;
 
   const int q_pos = qt * kTile + t;  // position inside the sequence
   int num_kt = (k_len + kTile - 1) / kTile;
@@ -89,14 +94,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
 
   // The K tile of the next iteration is requested as soon as S = Q K^T of this one has been computed, the V tile as soon
   // as O = P V has: both loads run under the softmax of the tile in between.
-  if (t == 0 && num_kt > 0) {
+  if (leader && num_kt > 0) {
     mbar_expect_tx(&bars[1], kTileBytes);
     tma_load_2d(sK, &tmap_k, &bars[1], h * kHd, k_begin);
     mbar_expect_tx(&bars[3], kTileBytes);
     tma_load_2d(sV, &tmap_v, &bars[3], h * kHd, k_begin);
   }
   for (int kt = 0; kt < num_kt && ok; ++kt) {
-    if (t == 0) {
+    if (leader) {
       if (kt == 0) ok = mbar_wait(&bars[0], 0, abort_word, p.status, kTimeoutTmaFull);
       if (ok) ok = mbar_wait(&bars[1], ph_kv, abort_word, p.status, kTimeoutTmaFull);
       if (ok) {
@@ -108,25 +113,33 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     if (!mbar_wait(&bars[2], ph_mma, abort_word, p.status, kTimeoutTmemFull)) { ok = false; break; }
     ph_mma ^= 1;
     tc_fence_after_sync();
-    if (t == 0 && kt + 1 < num_kt) {       // the MMA that read sK has completed
+    if (leader && kt + 1 < num_kt) {       // the MMA that read sK has completed
       mbar_expect_tx(&bars[1], kTileBytes);
       tma_load_2d(sK, &tmap_k, &bars[1], h * kHd, k_begin + (kt + 1) * kTile);
     }
 
-    // ---- softmax over this key tile: two passes over the 128 score columns of my row -----------
+    // ---- softmax over this key tile: two passes over my 64 of the 128 score columns of my row ---------
     // Scores stay in the base-2 domain (score * scale * log2 e), so one FMA + one ex2 makes a probability.  A tile whose
     // 128 x 128 scores are all inside the sequence (and below the diagonal when causal) skips the per-element masks.
     const int kcols = min(kTile, k_len - kt * kTile);
     const bool full = kcols == kTile && (!p.causal || kt < qt);
     float tile_max = kNegBig;
-#pragma unroll 1
-    for (int c = 0; c < 4; ++c) {
+#pragma unroll
+    for (int cc = 0; cc < 2; ++cc) {
+      const int c = 2 * grp + cc;
       uint32_t r[32];
       tmem_ld32(tS + lane_sel + c * 32, r);
       tmem_ld_wait();
       if (full) {
+        float m0 = __uint_as_float(r[0]), m1 = __uint_as_float(r[1]), m2 = __uint_as_float(r[2]), m3 = __uint_as_float(r[3]);
 #pragma unroll
-        for (int j = 0; j < 32; ++j) tile_max = fmaxf(tile_max, __uint_as_float(r[j]));
+        for (int j = 4; j < 32; j += 4) {
+          m0 = fmaxf(m0, __uint_as_float(r[j]));
+          m1 = fmaxf(m1, __uint_as_float(r[j + 1]));
+          m2 = fmaxf(m2, __uint_as_float(r[j + 2]));
+          m3 = fmaxf(m3, __uint_as_float(r[j + 3]));
+        }
+        tile_max = fmaxf(tile_max, fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)));
       } else {
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
@@ -136,21 +149,33 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         }
       }
     }
+    sRed[grp * kTile + t] = tile_max;
+    __syncthreads();                                            // the other warpgroup's half of the row maximum
+    tile_max = fmaxf(tile_max, sRed[(grp ^ 1) * kTile + t]);
     const float m_new = fmaxf(m_run, tile_max * scale_log2);    // scale > 0: the maximum commutes with the scaling
     const float alpha = ex2_approx(m_run - m_new);
     float row_sum = 0.f;
-#pragma unroll 1
-    for (int c = 0; c < 4; ++c) {
+#pragma unroll
+    for (int cc = 0; cc < 2; ++cc) {
+      const int c = 2 * grp + cc;
       uint32_t r[32];
       tmem_ld32(tS + lane_sel + c * 32, r);
       tmem_ld_wait();
       float pv[32];
       if (full) {
+        float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
+        for (int j = 0; j < 32; j += 4) {
           pv[j] = ex2_approx(fmaf(__uint_as_float(r[j]), scale_log2, -m_new));
-          row_sum += pv[j];
+          pv[j + 1] = ex2_approx(fmaf(__uint_as_float(r[j + 1]), scale_log2, -m_new));
+          pv[j + 2] = ex2_approx(fmaf(__uint_as_float(r[j + 2]), scale_log2, -m_new));
+          pv[j + 3] = ex2_approx(fmaf(__uint_as_float(r[j + 3]), scale_log2, -m_new));
+          s0 += pv[j];
+          s1 += pv[j + 1];
+          s2 += pv[j + 2];
+          s3 += pv[j + 3];
         }
+        row_sum += (s0 + s1) + (s2 + s3);
       } else {
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
@@ -181,7 +206,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     tc_fence_before_sync();
     fence_async_smem();
     __syncthreads();
-    if (t == 0) {
+    if (leader) {
       if (mbar_wait(&bars[3], ph_kv, abort_word, p.status, kTimeoutTmaFull)) {
         tc_fence_after_sync();
         // O_tile = P V : A = P (K-major, two slabs of 4 k-steps), B = V (MN-major, 16 keys per k-step)
@@ -194,34 +219,38 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     if (!mbar_wait(&bars[2], ph_mma, abort_word, p.status, kTimeoutTmemFull)) { ok = false; break; }
     ph_mma ^= 1;
     tc_fence_after_sync();
-    if (t == 0 && kt + 1 < num_kt) {       // the MMA that read sV has completed
+    if (leader && kt + 1 < num_kt) {       // the MMA that read sV has completed
       mbar_expect_tx(&bars[3], kTileBytes);
       tma_load_2d(sV, &tmap_v, &bars[3], h * kHd, k_begin + (kt + 1) * kTile);
     }
-#pragma unroll
-    for (int c = 0; c < 2; ++c) {
+    {
       uint32_t r[32];
-      tmem_ld32(tO + lane_sel + c * 32, r);
+      tmem_ld32(tO + lane_sel + grp * 32, r);
       tmem_ld_wait();
 #pragma unroll
-      for (int j = 0; j < 32; ++j) o_acc[c * 32 + j] = o_acc[c * 32 + j] * alpha + __uint_as_float(r[j]);
+      for (int j = 0; j < 32; ++j) o_acc[j] = o_acc[j] * alpha + __uint_as_float(r[j]);
     }
     tc_fence_before_sync();
     __syncthreads();  // K, V, P shared-memory tiles and both TMEM regions are free again
   }
 
+  // the row sum is the sum of the two warpgroups' halves (both used the same running maximum)
+  sRed[grp * kTile + t] = l_run;
+  __syncthreads();
+  l_run += sRed[(grp ^ 1) * kTile + t];
   if (ok && t < q_rows) {
     const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-    __nv_bfloat16* orow = p.out + static_cast<size_t>(q0 + t) * p.ld_out + h * kHd;
+    __nv_bfloat16* orow = p.out + static_cast<size_t>(q0 + t) * p.ld_out + h * kHd + grp * 32;
 #pragma unroll
-    for (int g = 0; g < 8; ++g) {
+    for (int g = 0; g < 4; ++g) {
       uint4 o;
       __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
 #pragma unroll
       for (int j = 0; j < 4; ++j) o2[j] = __floats2bfloat162_rn(o_acc[g * 8 + 2 * j] * inv, o_acc[g * 8 + 2 * j + 1] * inv);
       reinterpret_cast<uint4*>(orow)[g] = o;
     }
-    if (p.lse) p.lse[static_cast<size_t>(h) * p.lse_stride + q0 + t] = l_run > 0.f ? (m_run + __log2f(l_run)) * 0.6931471805599453f : 0.f;
+    if (p.lse && grp == 0)
+      p.lse[static_cast<size_t>(h) * p.lse_stride + q0 + t] = l_run > 0.f ? (m_run + __log2f(l_run)) * 0.6931471805599453f : 0.f;
   }
   tc_fence_before_sync();
   __syncthreads();
@@ -229,7 +258,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     for (int i = 0; i < 2000; ++i) __nanosleep(1000);
     __syncthreads();
   }
-  if (warp == 0) {
+  if (threadIdx.x < 32) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, 256);
   }
@@ -255,8 +284,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   uint8_t* sP = sDO1 + kTileBytes;
   uint8_t* sDS = sP + kPBytes;
   uint8_t* sDQ = sDS + kPBytes;           // fp32 dQ staging: one [128 x 32] 128-byte-swizzled slab per warpgroup
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sDQ + 2 * kTileBytes);  // [0]=KV [1]=Q,dO buffer 0 [2]=MMA [3]=Q,dO buffer 1
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sDQ + 2 * kTileBytes);  // [0]=KV [1]=Q,dO buffer 0 [2]=dV,dK,dQ MMAs [3]=Q,dO buffer 1 [4]=S,dP MMAs
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 5);
   volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   zero_tail_bwd(p);
@@ -275,6 +304,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     mbar_init(&bars[1], 1);
     mbar_init(&bars[2], 1);
     mbar_init(&bars[3], 1);
+    mbar_init(&bars[4], 1);
     *abort_word = 0;
     mbar_fence_init();
   }
@@ -303,14 +333,29 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
 
   const int num_qt = (q_len + kTile - 1) / kTile;
   const int qt_first = p.causal ? (kt * kTile) / kTile : 0;  // query tiles before the key tile see none of it
-  uint32_t ph_mma = 0;
+  uint32_t ph_mma = 0, ph_s = 0;
   bool ok = true;
   bool first = true;
 
+  // S = Q K^T and dP = dO V^T of query tile i+1 are issued right behind the dV / dK / dQ products of tile i, so they run
+  // while the threads move dQ of tile i out of TMEM; the first pair is issued here.
   if (leader && qt_first < num_qt) {
     mbar_expect_tx(&bars[1], 2 * kTileBytes);
     tma_load_2d(sQ0, &tmap_q, &bars[1], h * kHd, q_begin + qt_first * kTile);
     tma_load_2d(sDO0, &tmap_do, &bars[1], h * kHd, q_begin + qt_first * kTile);
+    ok = mbar_wait(&bars[0], 0, abort_word, p.status, kTimeoutTmaFull);
+    if (ok) ok = mbar_wait(&bars[1], 0, abort_word, p.status, kTimeoutTmaFull);
+    if (ok) {
+      tc_fence_after_sync();
+      umma_steps(tS, smem_u32(sQ0), 16, 32, smem_u32(sK), 16, 32, idesc_s, kHd / 16, false);
+      umma_steps(tDP, smem_u32(sDO0), 16, 32, smem_u32(sV), 16, 32, idesc_s, kHd / 16, false);
+      umma_commit(&bars[4]);
+    }
+  }
+  float nxt_D = 0.f, nxt_lse = 0.f;
+  if (p.delta && qt_first < num_qt && qt_first * kTile + t < q_len) {
+    nxt_D = p.delta[static_cast<size_t>(h) * p.lse_stride + q_begin + qt_first * kTile + t];
+    nxt_lse = p.lse[static_cast<size_t>(h) * p.lse_stride + q_begin + qt_first * kTile + t];
   }
   for (int qt = qt_first; qt < num_qt && ok; ++qt) {
     const int q0 = q_begin + qt * kTile;
@@ -318,48 +363,43 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     const int it = qt - qt_first, buf = it & 1;
     uint8_t* sQ = buf ? sQ1 : sQ0;
     uint8_t* sDO = buf ? sDO1 : sDO0;
-    if (leader) {
-      if (qt + 1 < num_qt) {
-        // the other buffer was last read by the MMAs of the previous iteration, which have completed
-        uint64_t* nb = buf ? &bars[1] : &bars[3];
-        mbar_expect_tx(nb, 2 * kTileBytes);
-        tma_load_2d(buf ? sQ0 : sQ1, &tmap_q, nb, h * kHd, q0 + kTile);
-        tma_load_2d(buf ? sDO0 : sDO1, &tmap_do, nb, h * kHd, q0 + kTile);
-      }
-      if (first) ok = mbar_wait(&bars[0], 0, abort_word, p.status, kTimeoutTmaFull);
-      if (ok) ok = mbar_wait(buf ? &bars[3] : &bars[1], (it >> 1) & 1, abort_word, p.status, kTimeoutTmaFull);
-      if (ok) {
-        tc_fence_after_sync();
-        umma_steps(tS, smem_u32(sQ), 16, 32, smem_u32(sK), 16, 32, idesc_s, kHd / 16, false);
-        umma_steps(tDP, smem_u32(sDO), 16, 32, smem_u32(sV), 16, 32, idesc_s, kHd / 16, false);
-        umma_commit(&bars[2]);
-      }
+    if (leader && qt + 1 < num_qt) {
+      // the other buffer was last read by the MMAs of the previous iteration, which have completed
+      uint64_t* nb = buf ? &bars[1] : &bars[3];
+      mbar_expect_tx(nb, 2 * kTileBytes);
+      tma_load_2d(buf ? sQ0 : sQ1, &tmap_q, nb, h * kHd, q0 + kTile);
+      tma_load_2d(buf ? sDO0 : sDO1, &tmap_do, nb, h * kHd, q0 + kTile);
     }
-    // D = rowsum(dO * O) and the saved log-sum-exp of my query row (overlaps the MMAs)
+    // D = rowsum(dO * O) and the saved log-sum-exp of my query row.  With the precomputed D both are one float per row:
+    // the values of the NEXT tile are requested here and used an iteration later, so their latency is never waited for.
     const bool row_ok = t < q_rows;
     float Drow = 0.f, lse = 0.f;
-    if (row_ok) {
-      if (p.delta) {
-        Drow = p.delta[static_cast<size_t>(h) * p.lse_stride + q0 + t];
-      } else {
-        const uint4* orow = reinterpret_cast<const uint4*>(p.o + static_cast<size_t>(q0 + t) * p.ld_o + h * kHd);
-        const uint4* drow = reinterpret_cast<const uint4*>(p.d_o + static_cast<size_t>(q0 + t) * p.ld_do + h * kHd);
+    if (p.delta) {
+      Drow = nxt_D;
+      lse = nxt_lse;
+      const int nrow = q0 + kTile + t;
+      if (qt + 1 < num_qt && nrow < q_begin + q_len) {
+        nxt_D = p.delta[static_cast<size_t>(h) * p.lse_stride + nrow];
+        nxt_lse = p.lse[static_cast<size_t>(h) * p.lse_stride + nrow];
+      }
+    } else if (row_ok) {
+      const uint4* orow = reinterpret_cast<const uint4*>(p.o + static_cast<size_t>(q0 + t) * p.ld_o + h * kHd);
+      const uint4* drow = reinterpret_cast<const uint4*>(p.d_o + static_cast<size_t>(q0 + t) * p.ld_do + h * kHd);
 #pragma unroll
-        for (int g = 0; g < 8; ++g) {
-          uint4 a = orow[g], d = drow[g];
-          const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&a);
-          const __nv_bfloat162* d2 = reinterpret_cast<const __nv_bfloat162*>(&d);
+      for (int g = 0; g < 8; ++g) {
+        uint4 a = orow[g], d = drow[g];
+        const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&a);
+        const __nv_bfloat162* d2 = reinterpret_cast<const __nv_bfloat162*>(&d);
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            float2 x = __bfloat1622float2(a2[j]), y = __bfloat1622float2(d2[j]);
-            Drow += x.x * y.x + x.y * y.y;
-          }
+        for (int j = 0; j < 4; ++j) {
+          float2 x = __bfloat1622float2(a2[j]), y = __bfloat1622float2(d2[j]);
+          Drow += x.x * y.x + x.y * y.y;
         }
       }
       lse = p.lse[static_cast<size_t>(h) * p.lse_stride + q0 + t];
     }
-    if (!mbar_wait(&bars[2], ph_mma, abort_word, p.status, kTimeoutTmemFull)) { ok = false; break; }
-    ph_mma ^= 1;
+    if (!mbar_wait(&bars[4], ph_s, abort_word, p.status, kTimeoutTmemFull)) { ok = false; break; }
+    ph_s ^= 1;
     tc_fence_after_sync();
 
     const int q_pos = qt * kTile + t;
@@ -426,6 +466,16 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       umma_steps(tDQ, smem_u32(sDS), 16, 32, smem_u32(sK), 8192, 2048, idesc_dq, 4, false);
       umma_steps(tDQ, smem_u32(sDS) + kTileBytes, 16, 32, smem_u32(sK) + 4 * 2048, 8192, 2048, idesc_dq, 4, true);
       umma_commit(&bars[2]);
+      if (qt + 1 < num_qt) {
+        // every thread has read S and dP of this tile (barrier above): the next pair may overwrite them
+        const int nit = it + 1;
+        if (mbar_wait((nit & 1) ? &bars[3] : &bars[1], (nit >> 1) & 1, abort_word, p.status, kTimeoutTmaFull)) {
+          tc_fence_after_sync();
+          umma_steps(tS, smem_u32(buf ? sQ0 : sQ1), 16, 32, smem_u32(sK), 16, 32, idesc_s, kHd / 16, false);
+          umma_steps(tDP, smem_u32(buf ? sDO0 : sDO1), 16, 32, smem_u32(sV), 16, 32, idesc_s, kHd / 16, false);
+          umma_commit(&bars[4]);
+        }
+      }
     }
     first = false;
     if (!mbar_wait(&bars[2], ph_mma, abort_word, p.status, kTimeoutTmemFull)) { ok = false; break; }
@@ -570,7 +620,7 @@ __global__ void attn_dq_convert_kernel(const float* __restrict__ acc, int ld_acc
   }
 }
 
-constexpr int kFwdSmem = 3 * kTileBytes + kPBytes + 64 + 1024;
+constexpr int kFwdSmem = 3 * kTileBytes + kPBytes + 1024 + 64 + 1024;
 constexpr int kBwdSmem = 8 * kTileBytes + 2 * kPBytes + 64 + 1024;
 
 }  // namespace b200
@@ -619,7 +669,7 @@ const char* nmtg_attn_fwd(const AttnDesc* d, cudaStream_t stream) {
     configured = true;
   }
   dim3 grid((d->max_q + kTile - 1) / kTile, d->num_heads, d->batch);
-  attn_fwd_kernel<<<grid, 128, kFwdSmem, stream>>>(tq, tk, tv, a);
+  attn_fwd_kernel<<<grid, 256, kFwdSmem, stream>>>(tq, tk, tv, a);
   cudaError_t ce = cudaGetLastError();
   return ce == cudaSuccess ? nullptr : cudaGetErrorString(ce);
 }
