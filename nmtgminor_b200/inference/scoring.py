@@ -58,6 +58,33 @@ class LanguagePredictor(Translator):
         return model.predict_language(batch).argmax(-1).cpu().tolist()
 
 
+class ClassifierPredictor(Translator):
+    """Labels every input with a trained classifier (``-model classifier`` checkpoints: encoder + pooled linear head).
+    Returns (label index, log-probability of that label) per input; ``label_name`` maps indices through the target
+    dictionary.  Reference: classify.py:179-380 (batching loop, ``get_result``), onmt/inference/predictor.py."""
+
+    def predict(self, src_sents: List[List[str]], batch_size: int = 32):
+        out = []
+        self.model.eval()
+        for i in range(0, len(src_sents), batch_size):
+            batch = self.build_data(src_sents[i:i + batch_size])
+            if self.cuda:
+                batch = batch.cuda(self.device)
+            with torch.no_grad():
+                logits = self.model(batch)["logits"].float()
+            if logits.dim() == 3:                         # per-frame heads: average the frame log-probabilities
+                logits = torch.log_softmax(logits, -1).mean(1)
+            logp = torch.log_softmax(logits, -1)
+            best = logp.argmax(-1)
+            rows = list(zip(best.cpu().tolist(), logp.gather(1, best[:, None]).squeeze(1).cpu().tolist()))
+            out.extend(rows)
+        return out
+
+    def label_name(self, index: int) -> str:
+        d = self.tgt_dict if getattr(self, "tgt_dict", None) is not None else None
+        return d.get_label(index) if d is not None and hasattr(d, "get_label") else str(index)
+
+
 class StreamTranslator(Translator):
     """Translates a document segment by segment.  The tail (``context_tokens``) of the previous segment's output is
     forced as a prefix of the next hypothesis and stripped from the returned text, so lexical choices stay consistent

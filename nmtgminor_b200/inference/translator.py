@@ -109,7 +109,8 @@ class Translator:
                 self.sub_src_dict = dicts.get("src")            # source vocabulary of the first sub-model
             model = build_model(mopt, dicts, remove_pretrain=True)
             load_model_state(model, ckpt["model"])
-            model.renew_buffer(getattr(opt, "max_sent_length", 256) + 2)
+            if hasattr(model, "renew_buffer"):             # classifiers have no decoder position buffers
+                model.renew_buffer(getattr(opt, "max_sent_length", 256) + 2)
             model.eval()
             if self.cuda:
                 FlatParameterStore(model, self.device)        # bf16 working copies for the fused kernels

@@ -158,3 +158,25 @@ def test_translate_distributed_splits_all_line_parallel_inputs(tmp_path):
     a = translate_distributed.split_file(str(src), 2, str(tmp_path), "a")
     b = translate_distributed.split_file(str(past), 2, str(tmp_path), "b")
     assert [len(open(p).readlines()) for p in a] == [len(open(p).readlines()) for p in b] == [3, 2]
+
+
+def test_classify_cli_labels_every_line(tmp_path):
+    import classify as classify_cli
+    from nmtgminor_b200.inference.scoring import ClassifierPredictor
+    torch.manual_seed(0)
+    d, labels = synthetic_dict(40), synthetic_dict(5)
+    opt = default_options(["-model", "classifier"] + COMMON)
+    ck = str(tmp_path / "cls.pt")
+    model = build_model(opt, {"src": d, "tgt": labels})
+    save_checkpoint(ck, model, {"src": d, "tgt": labels}, opt, 1.0)
+    src = tmp_path / "src.txt"
+    src.write_text("w1 w2 w3\nw4 w5\nw6\nw7 w8 w9 w10\nw3\n")
+    out = tmp_path / "pred.txt"
+    classify_cli.main(["-model", ck, "-src", str(src), "-output", str(out), "-gpu", "-1", "-batch_size", "2"])
+    lines = out.read_text().splitlines()
+    assert len(lines) == 5
+    # batching must not change the answer: one call over everything gives the same labels
+    from nmtgminor_b200.options import make_translate_parser
+    p = ClassifierPredictor(make_translate_parser().parse_args(["-model", ck, "-src", str(src), "-gpu", "-1"]))
+    whole = p.predict([l.split() for l in src.read_text().splitlines()], batch_size=8)
+    assert [p.label_name(i) for i, _ in whole] == lines and all(lp <= 0 for _, lp in whole)
