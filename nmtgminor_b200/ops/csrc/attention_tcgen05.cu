@@ -267,10 +267,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
 // ---------------------------------------------------------------------------------------------------
 // backward
 // ---------------------------------------------------------------------------------------------------
-// 512 threads: four warpgroups own the same 128 rows (TMEM lanes) and split the columns of every tile between them (32 of
-// the 128 score columns each; two of them move dQ, one each a half of dK / dV), so each scheduler has four warps to switch
-// between while the others wait on TMEM loads and exponentials.  One CTA per SM (shared memory, TMEM), 128 registers.
-__global__ void __launch_bounds__(512)
+// 256 threads: two warpgroups own the same 128 rows (TMEM lanes) and split the columns of every tile between them, so
+// each scheduler has two warps to switch between while the other waits on TMEM loads and exponentials.
+__global__ void __launch_bounds__(256)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                 const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
                 const __grid_constant__ CUtensorMap tmap_dq, const AttnArgs p) {
@@ -410,7 +409,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     const bool full = q_rows == kTile && k_rows == kTile && (!p.causal || kt < qt);
     const float lse2 = lse * 1.4426950408889634f;
 #pragma unroll 1
-    for (int c = grp; c < grp + 1; ++c) {              // this warpgroup's 32 of the 128 key columns
+    for (int c = 2 * grp; c < 2 * grp + 2; ++c) {      // this warpgroup's 64 of the 128 key columns
       uint32_t rs[32], rd[32];
       tmem_ld32(tS + lane_sel + c * 32, rs);
       tmem_ld32(tDP + lane_sel + c * 32, rd);
@@ -483,7 +482,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     ph_mma ^= 1;
     tc_fence_after_sync();
 #pragma unroll 1
-    for (int c = grp; c < (grp < 2 ? grp + 1 : grp); ++c) {   // warpgroups 0 and 1: 32 of the 64 dQ columns each
+    for (int c = grp; c < grp + 1; ++c) {               // 32 of the 64 dQ columns per warpgroup
       uint32_t r[32];
       tmem_ld32(tDQ + lane_sel + c * 32, r);
       tmem_ld_wait();
@@ -523,7 +522,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     tc_fence_before_sync();
     if (!single_kt && p.dq_tma) fence_async_smem();
     __syncthreads();
-    if (!single_kt && p.dq_tma && t == 0 && grp < 2) {   // one thread per dQ warpgroup: dq_acc[q0 .. q0+127, my 32 columns] += slab
+    if (!single_kt && p.dq_tma && t == 0) {          // one thread per warpgroup: dq_acc[q0 .. q0+127, my 32 columns] += slab
       tma_reduce_add_2d(&tmap_dq, sDQ + grp * kTileBytes, h * kHd + grp * 32, q0);
       tma_store_commit();
     }
@@ -533,12 +532,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   // dK, dV of my key row
   if (ok && !first) {
 #pragma unroll 1
-    for (int which = grp >> 1; which < (grp >> 1) + 1; ++which) {     // warpgroups 0, 1: dK halves; 2, 3: dV halves
+    for (int which = 0; which < 2; ++which) {
       __nv_bfloat16* dst = which == 0 ? p.dk : p.dv;
       const int ld = which == 0 ? p.ld_dk : p.ld_dv;
       const uint32_t tsrc = which == 0 ? tDK : tDV;
 #pragma unroll 1
-      for (int c = grp & 1; c < (grp & 1) + 1; ++c) {
+      for (int c = grp; c < grp + 1; ++c) {
         uint32_t r[32];
         tmem_ld32(tsrc + lane_sel + c * 32, r);
         tmem_ld_wait();
@@ -721,7 +720,7 @@ const char* nmtg_attn_bwd(const AttnDesc* d, cudaStream_t stream) {
       cached_tmap_f32(&tdq, d->dq_acc, d->total_q, width, d->ld_dqacc, kTile, 32))
     a.dq_tma = 1;
   dim3 grid((d->max_k + kTile - 1) / kTile, d->num_heads, d->batch);
-  attn_bwd_kernel<<<grid, 512, kBwdSmem, stream>>>(tq, tk, tv, tdo, tdq, a);
+  attn_bwd_kernel<<<grid, 256, kBwdSmem, stream>>>(tq, tk, tv, tdo, tdq, a);
   cudaError_t ce = cudaGetLastError();
   if (ce != cudaSuccess) return cudaGetErrorString(ce);
   if (d->max_k > kTile) {
@@ -811,7 +810,7 @@ extern "C" int nmtg_attn_bwd_noalloc(const void* q, int ld_q, const void* k, int
   CUtensorMap tdq = tq;       // placeholder when no accumulation buffer is needed
   a.dq_tma = (needs_buffer && cached_tmap_f32(&tdq, scratch, total_q, width, width, kTile, 32)) ? 1 : 0;
   dim3 grid((max_k + kTile - 1) / kTile, num_heads, batch);
-  attn_bwd_kernel<<<grid, 512, kBwdSmem, stream>>>(tq, tk, tv, tdo, tdq, a);
+  attn_bwd_kernel<<<grid, 256, kBwdSmem, stream>>>(tq, tk, tv, tdo, tdq, a);
   ce = cudaGetLastError();
   if (ce != cudaSuccess) return noalloc_fail(3, cudaGetErrorString(ce), err, err_len);
   if (needs_buffer) {
