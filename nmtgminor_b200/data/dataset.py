@@ -194,10 +194,17 @@ def pack_sequences(seqs: Sequence[torch.Tensor], pad: int, capacity: Optional[in
 def collate(src_data, tgt_data, src_lang=None, tgt_lang=None, src_atb=None, tgt_atb=None, src_pad=C.PAD, tgt_pad=C.PAD,
             src_type="text", index_data=None, padded: bool = True, packed: bool = True, capacity_src: Optional[int] = None,
             capacity_tgt: Optional[int] = None, max_batch: Optional[int] = None, round_to: int = 128,
-            create_reverse: bool = False, vocab_mask=None, past_src_data=None) -> Batch:
+            create_reverse: bool = False, vocab_mask=None, past_src_data=None, aux_tgt_data=None) -> Batch:
     """Build a ``Batch`` from lists of per-sentence tensors (targets carry BOS ... EOS).  ``past_src_data``: the previous
-    source sentence of every example (document-context models; keys ``past_source*`` of the reference's batches)."""
+    source sentence of every example (document-context models; keys ``past_source*`` of the reference's batches).
+    ``aux_tgt_data``: a second target per example ("triangle" corpora: e.g. the transcript next to the translation),
+    given as ``aux_target_input`` / ``aux_target_output`` ``[T, B]`` and ``aux_tgt_lengths``."""
     t: TDict = {"src_type": src_type, "vocab_mask": vocab_mask}
+    if aux_tgt_data is not None:
+        aux_bt, aux_lengths = _pad_stack(aux_tgt_data, tgt_pad)
+        t["aux_target_input"] = aux_bt[:, :-1].t().contiguous()
+        t["aux_target_output"] = aux_bt[:, 1:].t().contiguous()
+        t["aux_tgt_lengths"] = torch.tensor([l - 1 for l in aux_lengths], dtype=torch.int64)
     if past_src_data is not None and src_type == "text":
         past_bt, past_lengths = _pad_stack(past_src_data, src_pad)
         t["past_source"] = past_bt.t().contiguous()
@@ -283,8 +290,10 @@ class Dataset(torch.utils.data.Dataset):
                  tgt_atbs=None, batch_size_words=2048, batch_size_frames=10 ** 12, batch_size_sents=10 ** 9, multiplier=1,
                  data_type="text", max_src_len=256, max_tgt_len=256, min_src_len=0, min_tgt_len=0, cleaning=True,
                  sorting=True, src_pad=C.PAD, tgt_pad=C.PAD, padded=True, packed=True, round_to=128, cut_off_size=256000,
-                 smallest_batch_size=4, verbose=False, augmenter=None, create_reverse=False, past_src_data=None, **_ignored):
+                 smallest_batch_size=4, verbose=False, augmenter=None, create_reverse=False, past_src_data=None,
+                 aux_tgt_data=None, **_ignored):
         self.src, self.tgt = src_data, tgt_data
+        self.aux_tgt = aux_tgt_data            # second target per example ("triangle" corpora)
         self.past_src = past_src_data          # previous source sentence per example (document-context models)
         self.src_langs, self.tgt_langs, self.src_atbs, self.tgt_atbs = src_langs, tgt_langs, src_atbs, tgt_atbs
         self.type = data_type
@@ -338,7 +347,7 @@ class Dataset(torch.utils.data.Dataset):
             src = [self.augmenter.augment(s) for s in src]
         return collate(src, pick(self.tgt), lang(self.src_langs), lang(self.tgt_langs), lang(self.src_atbs), lang(self.tgt_atbs),
                        self.src_pad, self.tgt_pad, self.type, ids, self.padded, self.packed, round_to=self.round_to,
-                       create_reverse=self.create_reverse, past_src_data=pick(self.past_src))
+                       create_reverse=self.create_reverse, past_src_data=pick(self.past_src), aux_tgt_data=pick(self.aux_tgt))
 
     __getitem__ = get_batch
 

@@ -46,7 +46,10 @@ def init_vocab(name, files, vocab_file, size, tokenizer, lower=False):
     return make_vocab(name, files, size, tokenizer, lower)
 
 
-def make_data(src_file, tgt_file, src_dict, tgt_dict, opt, tokenizer):
+def make_data(src_file, tgt_file, src_dict, tgt_dict, opt, tokenizer, aux_file=None, aux_dict=None):
+    """Binarises one (source, target[, auxiliary target]) file group and drops the lines whose lengths are out of range.
+    ``-classification``: the target is a label sequence without sentence delimiters (reference: preprocess_classify.py:184).
+    ``aux_file``: a second target side kept aligned with the first (reference: preprocess_triangle.py, ``-aux_train_tgt``)."""
     external = None
     if getattr(opt, "external_tokenizer", ""):
         from nmtgminor_b200.data.binarizer import load_external_tokenizer
@@ -58,18 +61,24 @@ def make_data(src_file, tgt_file, src_dict, tgt_dict, opt, tokenizer):
     else:
         src = binarize_file(src_file, src_dict, tokenizer, None, None, opt.num_threads, external=external) if src_file else None
     # an external tokenizer adds its own sentence delimiters
-    tgt = binarize_file(tgt_file, tgt_dict, tokenizer, None if external else C.BOS_WORD, None if external else C.EOS_WORD,
-                        opt.num_threads, external=external) if tgt_file else None
+    labels = getattr(opt, "classification", False)
+    delim = (None, None) if (external or labels) else (C.BOS_WORD, C.EOS_WORD)
+    tgt = binarize_file(tgt_file, tgt_dict, tokenizer, delim[0], delim[1], opt.num_threads, external=external) if tgt_file else None
+    aux = binarize_file(aux_file, aux_dict, tokenizer, C.BOS_WORD, C.EOS_WORD, opt.num_threads) if aux_file else None
     n = len(src["data"]) if src else len(tgt["data"])
+    if aux is not None:
+        assert len(aux["data"]) == n, "the auxiliary target file has %d lines, the corpus %d" % (len(aux["data"]), n)
     keep = []
     for i in range(n):
         ls = src["sizes"][i] if src else 1
-        lt = tgt["sizes"][i] - 2 if tgt else 1
+        lt = (tgt["sizes"][i] - (0 if labels else 2)) if tgt else 1
         src_ok = ls > 0 if getattr(opt, "asr", False) else 0 < ls <= opt.src_seq_length   # audio is not length-filtered here
         if src_ok and 0 < lt <= opt.tgt_seq_length:
             keep.append(i)
     pick = lambda d: None if d is None else {"data": [d["data"][i] for i in keep], "sizes": [d["sizes"][i] for i in keep]}
     print("Prepared %d sentences (%d ignored due to length)" % (len(keep), n - len(keep)))
+    if aux_file:
+        return pick(src), pick(tgt), pick(aux)
     return pick(src), pick(tgt)
 
 
@@ -128,6 +137,11 @@ def main(argv=None):
         if train_src and not getattr(opt, "asr", False):
             dicts["src"] = init_vocab("source", train_src, opt.src_vocab, opt.src_vocab_size, tokenizer, opt.lower)
         dicts["tgt"] = init_vocab("target", train_tgt, opt.tgt_vocab, opt.tgt_vocab_size, tokenizer, opt.lower)
+    aux_train = opt.aux_train_tgt.split("|") if getattr(opt, "aux_train_tgt", "") else []
+    aux_valid = opt.aux_valid_tgt.split("|") if getattr(opt, "aux_valid_tgt", "") else []
+    if aux_train:
+        dicts["aux_tgt"] = init_vocab("auxiliary target", aux_train, getattr(opt, "aux_tgt_vocab", ""), opt.tgt_vocab_size,
+                                      tokenizer, opt.lower)
     langs = {}
     for l in (getattr(opt, "train_src_lang", "src") or "src").split("|") + (getattr(opt, "train_tgt_lang", "tgt") or "tgt").split("|"):
         langs.setdefault(l, len(langs))
@@ -138,20 +152,23 @@ def main(argv=None):
         return write_multi_dataset(opt, dicts, langs, tokenizer)
 
     sets = {}
-    for split, sfiles, tfiles in (("train", train_src, train_tgt),
-                                  ("valid", opt.valid_src.split("|") if opt.valid_src else [],
-                                   opt.valid_tgt.split("|") if opt.valid_tgt else [])):
-        src_all, tgt_all = {"data": [], "sizes": []}, {"data": [], "sizes": []}
+    for split, sfiles, tfiles, afiles in (("train", train_src, train_tgt, aux_train),
+                                          ("valid", opt.valid_src.split("|") if opt.valid_src else [],
+                                           opt.valid_tgt.split("|") if opt.valid_tgt else [], aux_valid)):
+        src_all, tgt_all, aux_all = {"data": [], "sizes": []}, {"data": [], "sizes": []}, {"data": [], "sizes": []}
         for i in range(max(len(sfiles), len(tfiles))):
-            s, t = make_data(sfiles[i] if i < len(sfiles) else None, tfiles[i] if i < len(tfiles) else None,
-                             dicts.get("src"), dicts["tgt"], opt, tokenizer)
-            for acc, part in ((src_all, s), (tgt_all, t)):
+            parts = make_data(sfiles[i] if i < len(sfiles) else None, tfiles[i] if i < len(tfiles) else None,
+                              dicts.get("src"), dicts["tgt"], opt, tokenizer,
+                              aux_file=afiles[i] if i < len(afiles) else None, aux_dict=dicts.get("aux_tgt"))
+            for acc, part in zip((src_all, tgt_all, aux_all), parts):
                 if part is not None:
                     acc["data"] += part["data"]
                     acc["sizes"] += part["sizes"]
         sets[split] = {"src": src_all["data"] or None, "tgt": tgt_all["data"] or None,
                        "src_sizes": src_all["sizes"] or None, "tgt_sizes": tgt_all["sizes"] or None,
                        "src_lang": [torch.tensor([0])], "tgt_lang": [torch.tensor([1 if len(langs) > 1 else 0])]}
+        if aux_all["data"]:
+            sets[split]["aux_tgt"], sets[split]["aux_tgt_sizes"] = aux_all["data"], aux_all["sizes"]
 
     fmt = getattr(opt, "format", "raw")
     os.makedirs(os.path.dirname(os.path.abspath(opt.save_data)), exist_ok=True)
@@ -171,6 +188,9 @@ def main(argv=None):
                 np.save("%s.%s.%s_sizes.npy" % (opt.save_data, split, side), np.asarray(sets[split][side + "_sizes"]))
             for side in ("src_lang", "tgt_lang"):
                 write_dataset("%s.%s.%s" % (opt.save_data, split, side), sets[split][side], np.int32)
+            if sets[split].get("aux_tgt"):
+                write_dataset("%s.%s.aux_tgt" % (opt.save_data, split), sets[split]["aux_tgt"], best_dtype(dicts["aux_tgt"].size()))
+                np.save("%s.%s.aux_tgt_sizes.npy" % (opt.save_data, split), np.asarray(sets[split]["aux_tgt_sizes"]))
         print("Saved mmap data to %s.*" % opt.save_data)
     elif fmt in ("wav", "scp", "scpmem"):
         # audio: <name>.{wav,scp}_path.pt = {'train': entries, 'valid': entries}; targets memory-mapped; sizes as .npy

@@ -152,3 +152,18 @@ def test_mmap_and_legacy_indexed_roundtrip(tmp_path):
     b.finalize()
     old = IndexedDataset(str(tmp_path / "old"))
     assert all(torch.equal(old[i], items[i]) for i in range(4))
+
+
+def test_auxiliary_target_travels_with_the_batch():
+    from nmtgminor_b200.data.dataset import Dataset
+    src = [torch.arange(4, 4 + n) for n in (3, 5, 2, 4)]
+    tgt = [torch.tensor([2] + [7] * n + [3]) for n in (2, 3, 1, 2)]
+    aux = [torch.tensor([2] + [10 + i] * (i + 1) + [3]) for i in range(4)]
+    ds = Dataset(src, tgt, batch_size_words=10 ** 6, aux_tgt_data=aux, cleaning=False, round_to=1)
+    b = ds.get_batch(0)
+    order = b.get("indices").tolist() if b.get("indices") is not None else list(range(4))
+    inp, out, lens = b.get("aux_target_input"), b.get("aux_target_output"), b.get("aux_tgt_lengths")
+    assert inp.shape == out.shape and inp.shape[1] == 4
+    for col, i in enumerate(order):
+        L = int(lens[col])
+        assert L == i + 2 and inp[:L, col].tolist() == [2] + [10 + i] * (i + 1) and out[L - 1, col] == 3

@@ -43,3 +43,35 @@ def test_speech_benchmark_dry_run(capsys):
         line = [l for l in capsys.readouterr().out.splitlines() if l.startswith("{")][-1]
         out = json.loads(line)
         assert out["value"] > 0 and out["audio_seconds_per_second"] > 0 and out["loss_per_token_after_warmup"] > 0
+
+
+def test_preprocess_triangle_and_classify(tmp_path):
+    import importlib
+    import os
+    import sys
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    tri, cls = importlib.import_module("preprocess_triangle"), importlib.import_module("preprocess_classify")
+    (tmp_path / "s.txt").write_text("a b c\nd e\n" + "x " * 300 + "\nf g h i\n")
+    (tmp_path / "t.txt").write_text("A B\nC\nD\nE F G\n")
+    (tmp_path / "a.txt").write_text("u v w\nx\ny\nz z\n")
+    (tmp_path / "l.txt").write_text("pos\nneg\npos\nneg\n")
+    common = ["-train_src", str(tmp_path / "s.txt"), "-valid_src", str(tmp_path / "s.txt"), "-src_seq_length", "64"]
+    out = str(tmp_path / "tri")
+    tri.main(common + ["-train_tgt", str(tmp_path / "t.txt"), "-valid_tgt", str(tmp_path / "t.txt"),
+                       "-aux_train_tgt", str(tmp_path / "a.txt"), "-aux_valid_tgt", str(tmp_path / "a.txt"), "-save_data", out])
+    data = torch.load(out + ".train.pt", weights_only=False)
+    tr = data["train"]
+    assert len(tr["src"]) == len(tr["tgt"]) == len(tr["aux_tgt"]) == 3            # the 300-word line is dropped on all sides
+    aux = data["dicts"]["aux_tgt"]
+    assert [aux.get_label(int(i)) for i in tr["aux_tgt"][2][1:-1]] == ["z", "z"]     # aligned with the 4th line
+    out2 = str(tmp_path / "cls")
+    cls.main(common + ["-train_tgt", str(tmp_path / "l.txt"), "-valid_tgt", str(tmp_path / "l.txt"), "-save_data", out2])
+    data = torch.load(out2 + ".train.pt", weights_only=False)
+    labels = data["dicts"]["tgt"]
+    assert [t.numel() for t in data["train"]["tgt"]] == [1, 1, 1]                     # bare labels, no delimiters
+    assert [labels.get_label(int(t[0])) for t in data["train"]["tgt"]] == ["pos", "neg", "neg"]
+    try:
+        tri.main(common)
+        raise AssertionError("missing -aux_train_tgt must be refused")
+    except SystemExit:
+        pass

@@ -32,7 +32,7 @@ def _dataset_from(split, opt, dicts, training):
                    batch_size_sents=opt.batch_size_sents if opt.batch_size_sents > 0 else 10 ** 9,
                    multiplier=opt.batch_size_multiplier, data_type=getattr(opt, "encoder_type", "text") if getattr(opt, "encoder_type", "text") != "text" else "text",
                    max_src_len=opt.max_src_length if training else 10 ** 9, max_tgt_len=(opt.max_tgt_length + 2) if training else 10 ** 9,
-                   cleaning=training, verbose=True)
+                   cleaning=training, verbose=True, aux_tgt_data=split.get("aux_tgt"))
 
 
 def load_multi_datasets(opt):
