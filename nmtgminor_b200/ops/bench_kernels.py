@@ -150,7 +150,7 @@ def bench_attention(rows):
     while sum(lens) < 8192 - 100:
         lens.append(int(rng.randint(20, 101)))
     n = sum(lens)
-    cap = (n + 127) // 1216 * 128
+    cap = (n + 127) // 128 * 128
     heads, W = 16, 1024
     cu = torch.zeros(len(lens) + 1, dtype=torch.int32)
     cu[1:] = torch.tensor(lens).cumsum(0)

@@ -143,6 +143,7 @@ attn_fwd_short_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
     const uint32_t lane_sel = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t tS = tmem_base + g * kTile, tO = tmem_base + 256 + g * kHd;
     uint8_t* myP = sP + g * kPBytes;
+    const float scale_log2 = p.scale * 1.4426950408889634f;
     const bool do_drop = p.dropout_p > 0.f;
     const unsigned long long seed = p.seed + ((do_drop && p.seed_dev) ? *p.seed_dev : 0ull);
     int it = 0;
@@ -171,21 +172,33 @@ attn_fwd_short_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
           tmem_ld32(tS + lane_sel + c0 * 32, r0);
           if (c0 + 1 < nchunks) tmem_ld32(tS + lane_sel + (c0 + 1) * 32, r1);
           tmem_ld_wait();
+          // raw-score maximum (scale > 0: scaling commutes with the maximum); a chunk whose 32 key columns all exist
+          // (and no causal mask) needs no per-element test
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int col = c0 * 32 + j;
-            const bool valid = col < w.k_len && (!p.causal || col <= t);
-            row_max = fmaxf(row_max, valid ? __uint_as_float(r0[j]) * p.scale : kNegBig);
-          }
-          if (c0 + 1 < nchunks) {
+          for (int half = 0; half < 2; ++half) {
+            const int c = c0 + half;
+            if (c >= nchunks) break;
+            if (!p.causal && (c + 1) * 32 <= w.k_len) {
+              float m0 = kNegBig, m1 = kNegBig, m2 = kNegBig, m3 = kNegBig;
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const int col = (c0 + 1) * 32 + j;
-              const bool valid = col < w.k_len && (!p.causal || col <= t);
-              row_max = fmaxf(row_max, valid ? __uint_as_float(r1[j]) * p.scale : kNegBig);
+              for (int j = 0; j < 32; j += 4) {
+                m0 = fmaxf(m0, __uint_as_float(half == 0 ? r0[j] : r1[j]));
+                m1 = fmaxf(m1, __uint_as_float(half == 0 ? r0[j + 1] : r1[j + 1]));
+                m2 = fmaxf(m2, __uint_as_float(half == 0 ? r0[j + 2] : r1[j + 2]));
+                m3 = fmaxf(m3, __uint_as_float(half == 0 ? r0[j + 3] : r1[j + 3]));
+              }
+              row_max = fmaxf(row_max, fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)));
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                const int col = c * 32 + j;
+                const bool valid = col < w.k_len && (!p.causal || col <= t);
+                row_max = fmaxf(row_max, valid ? __uint_as_float(half == 0 ? r0[j] : r1[j]) : kNegBig);
+              }
             }
           }
         }
+        row_max *= scale_log2;         // from here on in the base-2 domain: P = 2^(S * scale * log2 e - row_max)
 #pragma unroll 1
         for (int c0 = 0; c0 < nchunks; c0 += 2) {
           uint32_t r0[32], r1[32];
@@ -197,14 +210,30 @@ attn_fwd_short_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
             const int c = c0 + half;
             if (c >= nchunks) break;
             float pv[32];
+            if (!p.causal && (c + 1) * 32 <= w.k_len) {
+              float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const int col = c * 32 + j;
-              const bool valid = col < w.k_len && (!p.causal || col <= t);
-              const float sv = __uint_as_float(half == 0 ? r0[j] : r1[j]);
-              const float e = valid ? __expf(sv * p.scale - row_max) : 0.f;
-              row_sum += e;
-              pv[j] = e;
+              for (int j = 0; j < 32; j += 4) {
+                pv[j] = ex2_approx(fmaf(__uint_as_float(half == 0 ? r0[j] : r1[j]), scale_log2, -row_max));
+                pv[j + 1] = ex2_approx(fmaf(__uint_as_float(half == 0 ? r0[j + 1] : r1[j + 1]), scale_log2, -row_max));
+                pv[j + 2] = ex2_approx(fmaf(__uint_as_float(half == 0 ? r0[j + 2] : r1[j + 2]), scale_log2, -row_max));
+                pv[j + 3] = ex2_approx(fmaf(__uint_as_float(half == 0 ? r0[j + 3] : r1[j + 3]), scale_log2, -row_max));
+                s0 += pv[j];
+                s1 += pv[j + 1];
+                s2 += pv[j + 2];
+                s3 += pv[j + 3];
+              }
+              row_sum += (s0 + s1) + (s2 + s3);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                const int col = c * 32 + j;
+                const bool valid = col < w.k_len && (!p.causal || col <= t);
+                const float sv = __uint_as_float(half == 0 ? r0[j] : r1[j]);
+                const float e = valid ? ex2_approx(fmaf(sv, scale_log2, -row_max)) : 0.f;
+                row_sum += e;
+                pv[j] = e;
+              }
             }
             if (do_drop) apply_dropout32(rng, static_cast<unsigned long long>(w.q0 + t) * p.kstride + c * 32, pv);
 #pragma unroll
@@ -245,7 +274,7 @@ attn_fwd_short_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
             }
             reinterpret_cast<uint4*>(orow)[g4] = o;
           }
-          if (p.lse) p.lse[static_cast<size_t>(w.h) * p.lse_stride + w.q0 + t] = row_sum > 0.f ? row_max + __logf(row_sum) : 0.f;
+          if (p.lse) p.lse[static_cast<size_t>(w.h) * p.lse_stride + w.q0 + t] = row_sum > 0.f ? (row_max + __log2f(row_sum)) * 0.6931471805599453f : 0.f;
         }
       }
       tc_fence_before_sync();
@@ -379,6 +408,7 @@ attn_bwd_short_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
   } else if (warp < 4) {
     const int t = warp * 32 + lane;
     const uint32_t lane_sel = static_cast<uint32_t>(warp * 32) << 16;
+    const float scale_log2 = p.scale * 1.4426950408889634f;
     const bool do_drop = p.dropout_p > 0.f;
     const unsigned long long seed = p.seed + ((do_drop && p.seed_dev) ? *p.seed_dev : 0ull);
     int it = 0;
@@ -411,6 +441,7 @@ attn_bwd_short_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
           }
         }
       }
+      const float lse2 = row_ok ? lse * 1.4426950408889634f : __int_as_float(0x7f800000);
       if (!mbar_wait(sdp_full, ph, abort_word, p.status, kTimeoutTmemFull)) break;
       tc_fence_after_sync();
       const int nchunks = (w.k_len + 31) >> 5;
@@ -432,20 +463,34 @@ attn_bwd_short_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
           for (int half = 0; half < 2; ++half) {
             const int c = c0 + half;
             if (c >= nchunks) break;
-            float kf[32];
-#pragma unroll
-            for (int j = 0; j < 32; ++j) kf[j] = 1.f;
-            if (do_drop) apply_dropout32(rng, static_cast<unsigned long long>(w.q0 + t) * p.kstride + c * 32, kf);
+            // P = 2^(S * scale * log2 e - lse * log2 e); a row past the sequence has lse2 = +inf, so its P is 0 without a
+            // per-element test; dS is kept without the softmax scale (applied when dQ / dK leave TMEM).  A chunk whose 32
+            // key columns all exist (and no causal mask) takes the branch without per-element masks.
             float pd[32], ds[32];
+            const bool chunk_full = !p.causal && (c + 1) * 32 <= w.k_len;
+            if (chunk_full && !do_drop) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const int col = c * 32 + j;
-              const bool valid = row_ok && col < w.k_len && (!p.causal || col <= t);
-              const float sv = __uint_as_float(half == 0 ? rs0[j] : rs1[j]);
-              const float dv = __uint_as_float(half == 0 ? rd0[j] : rd1[j]);
-              const float pr = valid ? __expf(sv * p.scale - lse) : 0.f;
-              pd[j] = pr * kf[j];
-              ds[j] = pr * (dv * kf[j] - Drow) * p.scale;
+              for (int j = 0; j < 32; ++j) {
+                const float sv = __uint_as_float(half == 0 ? rs0[j] : rs1[j]);
+                const float dv = __uint_as_float(half == 0 ? rd0[j] : rd1[j]);
+                pd[j] = ex2_approx(fmaf(sv, scale_log2, -lse2));
+                ds[j] = pd[j] * (dv - Drow);
+              }
+            } else {
+              float kf[32];
+#pragma unroll
+              for (int j = 0; j < 32; ++j) kf[j] = 1.f;
+              if (do_drop) apply_dropout32(rng, static_cast<unsigned long long>(w.q0 + t) * p.kstride + c * 32, kf);
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                const int col = c * 32 + j;
+                const bool valid = chunk_full || (col < w.k_len && (!p.causal || col <= t));
+                const float sv = __uint_as_float(half == 0 ? rs0[j] : rs1[j]);
+                const float dv = __uint_as_float(half == 0 ? rd0[j] : rd1[j]);
+                const float pr = valid ? ex2_approx(fmaf(sv, scale_log2, -lse2)) : 0.f;
+                pd[j] = pr * kf[j];
+                ds[j] = pr * (dv * kf[j] - Drow);
+              }
             }
 #pragma unroll
             for (int g4 = 0; g4 < 4; ++g4) {
@@ -487,7 +532,7 @@ attn_bwd_short_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
               const int e = (g4 & 3) * 8 + 2 * j;
-              o2[j] = __floats2bfloat162_rn(__uint_as_float(g4 < 4 ? r0[e] : r1[e]), __uint_as_float(g4 < 4 ? r0[e + 1] : r1[e + 1]));
+              o2[j] = __floats2bfloat162_rn(__uint_as_float(g4 < 4 ? r0[e] : r1[e]) * p.scale, __uint_as_float(g4 < 4 ? r0[e + 1] : r1[e + 1]) * p.scale);
             }
             reinterpret_cast<uint4*>(drow)[g4] = o;
           }
@@ -499,6 +544,7 @@ attn_bwd_short_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
           __nv_bfloat16* dst = which == 0 ? p.dk : p.dv;
           const int ld = which == 0 ? p.ld_dk : p.ld_dv;
           const uint32_t tsrc = which == 0 ? tDK : tDV;
+          const float osc = which == 0 ? p.scale : 1.f;      // dK carries the softmax scale that dS left out
           uint32_t r0[32], r1[32];
           tmem_ld32(tsrc + lane_sel, r0);
           tmem_ld32(tsrc + lane_sel + 32, r1);
@@ -512,7 +558,7 @@ attn_bwd_short_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
 #pragma unroll
               for (int j = 0; j < 4; ++j) {
                 const int e = (g4 & 3) * 8 + 2 * j;
-                o2[j] = __floats2bfloat162_rn(__uint_as_float(g4 < 4 ? r0[e] : r1[e]), __uint_as_float(g4 < 4 ? r0[e + 1] : r1[e + 1]));
+                o2[j] = __floats2bfloat162_rn(__uint_as_float(g4 < 4 ? r0[e] : r1[e]) * osc, __uint_as_float(g4 < 4 ? r0[e + 1] : r1[e + 1]) * osc);
               }
               reinterpret_cast<uint4*>(drow)[g4] = o;
             }
