@@ -331,10 +331,19 @@ class W2VBertModel(nn.Module):
 
 
 def build_w2vbert_encoder(opt, cfg_json: Optional[dict] = None) -> ConformerShawEncoder:
-    """Encoder for ``-enc_pretrained_model w2vbert*`` / ``xeus``: the ``300m`` preset when the name says so, else ``600m``;
-    keys of an ``-enc_config_file`` JSON (``model_dim``, ``num_encoder_layers``, ...) and the dropout flags override it."""
+    """Encoder for ``-enc_pretrained_model w2vbert*`` / ``xeus``.  A name that carries ``600m`` or ``300m`` selects that
+    preset; any other name builds the architecture at the sizes of the command line (``-model_size``, ``-encoder_layers``
+    or ``-layers``, ``-n_heads``, ``-inner_size``, ``-input_size`` filterbank channels).  Keys of an ``-enc_config_file``
+    JSON (``model_dim``, ``num_encoder_layers``, ...) and the dropout flags override either."""
     name = (getattr(opt, "enc_pretrained_model", "") or "").lower()
-    cfg = w2vbert_arch("300m" if "300m" in name else "600m").encoder
+    if "600m" in name or "300m" in name:
+        cfg = w2vbert_arch("300m" if "300m" in name else "600m").encoder
+    else:
+        n_layers = getattr(opt, "encoder_layers", -1)
+        cfg = ConformerShawConfig(model_dim=opt.model_size, layers=n_layers if n_layers and n_layers > 0 else opt.layers,
+                                  heads=opt.n_heads, ffn_dim=opt.inner_size,
+                                  num_fbank_channels=int(getattr(opt, "input_size", 80) or 80),
+                                  conv_kernel=int(getattr(opt, "conv_kernel", 31) or 31))
     j = cfg_json or {}
     for key, attr in (("model_dim", "model_dim"), ("num_encoder_layers", "layers"), ("num_encoder_attn_heads", "heads"),
                       ("ffn_inner_dim", "ffn_dim"), ("depthwise_conv_kernel_size", "conv_kernel"),

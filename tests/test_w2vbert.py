@@ -95,6 +95,10 @@ def test_pretraining_losses_backward():
 def test_builder_reads_config_file(tmp_path):
     path = tmp_path / "enc.json"
     path.write_text(json.dumps({"model_dim": 48, "num_encoder_layers": 2, "num_encoder_attn_heads": 4, "ffn_inner_dim": 96}))
-    opt = SimpleNamespace(enc_pretrained_model="w2vbert", dropout=0.1, attn_dropout=0.0, death_rate=0.0)
+    opt = SimpleNamespace(enc_pretrained_model="w2vbert", dropout=0.1, attn_dropout=0.0, death_rate=0.0, model_size=32,
+                          layers=1, n_heads=2, inner_size=64, input_size=40)
     enc = build_w2vbert_encoder(opt, json.loads(path.read_text()))
-    assert len(enc.layers) == 2 and enc.dim == 48 and enc.cfg.dropout == 0.1
+    assert len(enc.layers) == 2 and enc.dim == 48 and enc.cfg.dropout == 0.1 and enc.cfg.feature_dim == 80
+    plain = build_w2vbert_encoder(opt)                     # no file: the sizes of the command line
+    assert len(plain.layers) == 1 and plain.dim == 32 and plain.cfg.heads == 2
+    assert w2vbert_arch("300m").encoder.layers == 12       # a name with 300m / 600m selects the preset instead
