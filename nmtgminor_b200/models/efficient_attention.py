@@ -131,3 +131,41 @@ class MaxOut(nn.Module):
 
     def forward(self, x):
         return self.lin(x).view(*x.shape[:-1], self.out_dim, self.pool).amax(-1)
+
+
+def apply_chunking_to_forward(chunk_size: int, chunk_dim: int, forward_fn, *tensors):
+    """Runs ``forward_fn`` on slices of ``chunk_size`` along ``chunk_dim`` and concatenates the results: the same output
+    as one call when ``forward_fn`` treats positions along that dimension independently (a feed-forward block), with the
+    intermediate activations of one slice alive at a time.  ``chunk_size`` 0 = one call.
+    Reference: onmt/legacy/old_models/reformer.py:28-84."""
+    assert tensors and all(t.shape == tensors[0].shape for t in tensors), "inputs must share one shape"
+    if chunk_size <= 0 or tensors[0].shape[chunk_dim] <= chunk_size:
+        return forward_fn(*tensors)
+    pieces = zip(*(t.split(chunk_size, dim=chunk_dim) for t in tensors))      # the last slice may be shorter
+    return torch.cat([forward_fn(*piece) for piece in pieces], dim=chunk_dim)
+
+
+class ReformerEncoderLayer(nn.Module):
+    """Pre-norm encoder layer with bucketed (LSH) self-attention and a feed-forward block evaluated in slices along the
+    time axis; stochastic depth with probability ``death_rate`` (outputs rescaled by ``1 / (1 - death_rate)`` when kept).
+    Reference: onmt/legacy/old_models/reformer.py:87-129 (``ReformerEncoderLayer``)."""
+
+    def __init__(self, dim: int, heads: int, inner: int, dropout: float = 0.1, death_rate: float = 0.0, buckets: int = 8,
+                 rounds: int = 2, ffn_chunk: int = 0, seed: int = 0):
+        super().__init__()
+        self.attn_norm, self.ffn_norm = nn.LayerNorm(dim), nn.LayerNorm(dim)
+        self.self_attention = LSHAttention(dim, heads, buckets, rounds, seed)
+        self.fc1, self.fc2 = nn.Linear(dim, inner), nn.Linear(inner, dim)
+        self.dropout, self.death_rate, self.ffn_chunk = dropout, death_rate, ffn_chunk
+
+    def _ffn(self, x):
+        return self.fc2(F.dropout(F.relu(self.fc1(x)), self.dropout, self.training))
+
+    def forward(self, x, key_padding_mask=None):                  # x [B, T, H]
+        if self.training and self.death_rate > 0 and torch.rand(()).item() < self.death_rate:
+            return x
+        keep = 1.0 / (1.0 - self.death_rate) if (self.training and self.death_rate > 0) else 1.0
+        a = self.self_attention(self.attn_norm(x), key_padding_mask)
+        x = x + F.dropout(a, self.dropout, self.training) * keep
+        f = apply_chunking_to_forward(self.ffn_chunk, 1, self._ffn, self.ffn_norm(x))
+        return x + F.dropout(f, self.dropout, self.training) * keep

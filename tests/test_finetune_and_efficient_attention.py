@@ -113,3 +113,25 @@ def test_distillation_wrapper_trains_through_the_engine():
     assert last < first
     wrapper.eval()
     assert "loss" in wrapper(batch)
+
+
+def test_reformer_layer_and_chunked_forward():
+    from nmtgminor_b200.models.efficient_attention import ReformerEncoderLayer, apply_chunking_to_forward
+    torch.manual_seed(0)
+    lin = torch.nn.Linear(8, 8)
+    x = torch.randn(2, 10, 8)
+    assert torch.allclose(apply_chunking_to_forward(3, 1, lin, x), lin(x), atol=1e-6)       # ragged last slice
+    assert torch.equal(apply_chunking_to_forward(0, 1, lin, x), lin(x))
+    layer = ReformerEncoderLayer(32, 4, 64, dropout=0.0, ffn_chunk=4).eval()
+    whole = ReformerEncoderLayer(32, 4, 64, dropout=0.0, ffn_chunk=0).eval()
+    whole.load_state_dict(layer.state_dict())
+    h = torch.randn(2, 12, 32)
+    assert torch.allclose(layer(h), whole(h), atol=1e-5)
+    pad = torch.zeros(2, 12, dtype=torch.bool)
+    pad[1, 8:] = True
+    out = layer(h, pad)
+    h2 = h.clone()
+    h2[1, 8:] = 0.0
+    assert torch.allclose(out[1, :8], layer(h2, pad)[1, :8], atol=1e-5)                      # padded frames are not attended to
+    drop = ReformerEncoderLayer(32, 4, 64, death_rate=1.0 - 1e-9).train()
+    assert torch.equal(drop(h), h)
