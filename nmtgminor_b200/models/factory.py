@@ -29,7 +29,14 @@ def build_model(opt, dicts, remove_pretrain: bool = False, constants=None):
         return _REGISTRY["transformer_xl_lm"](opt, dicts)
     if name not in _REGISTRY:
         raise NotImplementedError("unknown model %r; registered: %s" % (name, sorted(_REGISTRY)))
-    return _REGISTRY[name](opt, dicts)
+    model = _REGISTRY[name](opt, dicts)
+    aux = dicts.get("aux_tgt") if hasattr(dicts, "get") else None
+    if aux is not None and getattr(model, "ctc_linear", None) is not None:
+        # "triangle" corpora: the CTC head predicts the auxiliary target (the transcript), which has its own vocabulary
+        import torch.nn as nn
+        model.ctc_linear = nn.Linear(model.ctc_linear.in_features, aux.size())
+        model.ctc_on_aux = True
+    return model
 
 
 def build_language_model(opt, dicts):

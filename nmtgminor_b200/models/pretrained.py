@@ -225,7 +225,14 @@ class SpeechToTextModel(Seq2SeqBase):
             context, src = self._uncompressed              # the CTC loss is defined on the frame-level states
         logits = src.pad(self.ctc_linear(context.float()))                   # [T, B, V]
         lengths = (src.cu[1:] - src.cu[:-1]).to(torch.int64)
-        targets = batch.get("target_output").t()                              # [B, U]
+        aux = batch.get("aux_target_output") if getattr(self, "ctc_on_aux", False) else None
+        if aux is not None:
+            # transcript side of a "triangle" corpus; its end-of-sentence symbol is not a CTC label
+            targets = aux.t().clone()                                         # [B, U]
+            last = batch.get("aux_tgt_lengths").to(targets.device) - 1
+            targets[torch.arange(targets.shape[0], device=targets.device), last] = self.pad_idx
+        else:
+            targets = batch.get("target_output").t()                          # [B, U]
         tgt_len = (targets != self.pad_idx).sum(-1)
         lp = F.log_softmax(logits.float(), -1)
         ctc = F.ctc_loss(lp, targets, lengths[:targets.shape[0]], tgt_len, blank=self.pad_idx, reduction="sum", zero_infinity=True)

@@ -195,3 +195,24 @@ def test_model_contract_extras(dicts):
     b.load_encoder_weights({k: torch.zeros_like(v) for k, v in a.state_dict().items()})
     assert float(b.encoder.layers[0].ffn.fc1.weight.abs().sum()) == 0 and float(b.decoder.layers[0].ffn.fc1.weight.abs().sum()) > 0
     assert a.init_stream() is None
+
+
+def test_ctc_head_on_the_auxiliary_target(dicts):
+    from nmtgminor_b200.data.synthetic import synthetic_dict
+    torch.manual_seed(0)
+    aux = synthetic_dict(23)
+    argv = ["-model", "speech_transformer", "-input_size", "40", "-ctc_loss", "0.5"] + COMMON
+    model = build_model(default_options(argv), {**dicts, "aux_tgt": aux})
+    assert model.ctc_linear.out_features == aux.size() and model.ctc_on_aux
+    batch = synthetic_audio_batch(2, 120, "feats", 40, 80, n_feats=40)
+    B = batch.get("target_output").shape[1]
+    full = torch.zeros(B, 6, dtype=torch.long)
+    full[:, 0], full[:, 1:4], full[:, 4] = 2, torch.randint(4, aux.size(), (B, 3)), 3      # BOS w w w EOS pad
+    batch.tensors["aux_target_input"] = full[:, :-1].t().contiguous()
+    batch.tensors["aux_target_output"] = full[:, 1:].t().contiguous()
+    batch.tensors["aux_tgt_lengths"] = torch.full((B,), 4)
+    model.train()
+    out = model(batch)
+    assert torch.isfinite(out["loss"]).all() and out["n_ctc_targets"] == 3 * B          # the EOS is not a CTC label
+    out["loss"].backward()
+    assert model.ctc_linear.weight.grad.abs().sum() > 0
