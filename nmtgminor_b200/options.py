@@ -79,6 +79,7 @@ def make_translate_parser(parser: Optional[argparse.ArgumentParser] = None) -> a
 def make_preprocess_parser(parser: Optional[argparse.ArgumentParser] = None) -> argparse.ArgumentParser:
     parser = parser or argparse.ArgumentParser(description="preprocess")
     _add(parser, PREPROCESS_FLAGS)
+    _md(parser)
     return parser
 
 
