@@ -201,9 +201,38 @@ def checkpoint_name(save_model: str, metric_name: str, value: float, epoch: floa
     return "%s_%s_%.6f_e%.2f.pt" % (save_model, metric_name, value, epoch)
 
 
+def rng_state() -> dict:
+    """Every random stream a training run draws from: Python, NumPy, torch (CPU and the current CUDA device) and the
+    counter-based dropout seed of the fused kernels.  Saved with checkpoints so that a resumed run continues the same
+    sequence of masks and shuffles (reference: whisper/trainers/trainer_pt_utils.py, RNG-state restore on resume)."""
+    import random
+    import numpy as np
+    from .. import ops
+    state = {"python": random.getstate(), "numpy": np.random.get_state(), "torch": torch.get_rng_state(),
+             "dropout": (ops._Rng.seed, ops._Rng.counter)}
+    if torch.cuda.is_available():
+        state["cuda"] = torch.cuda.get_rng_state()
+    return state
+
+
+def restore_rng_state(state: Optional[dict]) -> bool:
+    if not state:
+        return False
+    import random
+    import numpy as np
+    from .. import ops
+    random.setstate(state["python"])
+    np.random.set_state(state["numpy"])
+    torch.set_rng_state(state["torch"])
+    if "cuda" in state and torch.cuda.is_available():
+        torch.cuda.set_rng_state(state["cuda"])
+    ops._Rng.seed, ops._Rng.counter = state["dropout"]
+    return True
+
+
 def save_checkpoint(path: str, model, dicts, opt, epoch: float, optim=None, itr=None, scaler=None, extra: Optional[dict] = None):
     ckpt = {"model": model_state_for_saving(model), "dicts": dicts, "opt": opt, "epoch": epoch, "itr": itr,
-            "optim": optim.state_dict() if optim is not None else None, "scaler": scaler}
+            "optim": optim.state_dict() if optim is not None else None, "scaler": scaler, "rng": rng_state()}
     if extra:
         ckpt.update(extra)
     tmp = path + ".tmp"

@@ -80,6 +80,8 @@ class Trainer:
                 self.optim.load_state_dict(checkpoint["optim"])
             except Exception as exc:  # noqa: BLE001
                 self.log("[WARN] optimiser state not restored: %r" % (exc,))
+            from .checkpoint import restore_rng_state
+            restore_rng_state(checkpoint.get("rng"))      # same dropout masks and shuffles as the uninterrupted run
         self.start_time = time.time()
         # -ema: exponential moving average of the parameters (one vector op on the flat master buffer per update),
         # used for validation and for the saved checkpoints

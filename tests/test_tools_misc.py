@@ -75,3 +75,19 @@ def test_preprocess_triangle_and_classify(tmp_path):
         raise AssertionError("missing -aux_train_tgt must be refused")
     except SystemExit:
         pass
+
+
+def test_rng_state_round_trip():
+    import random
+    import numpy as np
+    from nmtgminor_b200 import ops
+    from nmtgminor_b200.train.checkpoint import restore_rng_state, rng_state
+    ops.manual_seed(77)
+    ops.next_stream()
+    state = rng_state()
+    want = (random.random(), float(np.random.rand()), torch.rand(3), ops.next_stream())
+    random.random(), np.random.rand(), torch.rand(5), ops.manual_seed(5)
+    assert restore_rng_state(state) and not restore_rng_state(None)
+    got = (random.random(), float(np.random.rand()), torch.rand(3), ops.next_stream())
+    assert want[0] == got[0] and want[1] == got[1] and torch.equal(want[2], got[2]) and want[3] == got[3]
+    assert ops._Rng.seed == 77
