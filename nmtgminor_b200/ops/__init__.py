@@ -67,7 +67,7 @@ def extension_available() -> bool:
 
 _KERNEL_CALLS = {"gemm": 1, "layernorm_fwd": 1, "layernorm_bwd": 1, "xent_fused": 1, "dropout_add": 1,
                  "dropout_colsum": 1, "embed_fwd": 1, "embed_bwd": 1, "colsum": 1, "sq_norm": 1, "adamw_flat": 1, "cast_f32_bf16": 1, "attn_fwd": 1,
-                 "attn_bwd": 1, "allreduce_adamw": 1}
+                 "attn_bwd": 1, "update_pieces": 1}
 LAUNCHES = [0]   # kernels of this extension enqueued so far (Python-side count of launcher calls)
 
 
@@ -158,13 +158,21 @@ def advance_device_seed(device=None, by: int = 1) -> None:
 # ---------------------------------------------------------------------------------------------------
 def gemm(a, b, out, *, a_mn_major=False, b_mn_major=False, bias=None, residual=None, aux=None, preact=None, act=0,
          dropout_p=0.0, seed=0, stream_id=0, alpha=1.0, accumulate=False, allow_split_k=False, split_k=0, force_bn=0,
-         mask=None, colsum=None):
+         mask=None, colsum=None, gather=None):
     """out[M,N] = epilogue(alpha * A B^T) on the tcgen05 kernel (see csrc/ops_api.h: GemmDesc).  ``mask`` (int32
     [M, ceil(N/32)]) receives the sign bits of the output, or supplies them when ``act`` is the mask-backward id 8.
-    ``colsum`` (fp32 [N]): the column sums of the bf16 output are added to it by the epilogue (bias gradients)."""
+    ``colsum`` (fp32 [N]): the column sums of the bf16 output are added to it by the epilogue (bias gradients).
+    ``gather``: record of a fully sharded weight (``parallel.fsdp.GatherInfo``) whose pieces this call pulls from
+    their owners into ``b`` before (and while) it multiplies."""
+    g = gather.pending() if gather is not None else None
     ext().gemm(a, a_mn_major, b, b_mn_major, out, bias, residual, aux, preact, int(act), float(dropout_p), int(seed),
-               int(stream_id), float(alpha), bool(accumulate), bool(allow_split_k), int(split_k), int(force_bn), mask, colsum)
+               int(stream_id), float(alpha), bool(accumulate), bool(allow_split_k), int(split_k), int(force_bn), mask, colsum, g)
     return out
+
+
+def _gather_of(weight):
+    """The gather record of a fully sharded weight matrix, or None (replicated parameters)."""
+    return getattr(weight, "_fsdp", None)
 
 
 def empty_rows(rows: int, cols: int, device, dtype=torch.bfloat16):
@@ -194,15 +202,16 @@ class _LinearFn(torch.autograd.Function):
     """y = [residual +] dropout(act(x W^T + b)); weight/bias gradients go to the main_grad buffers."""
 
     @staticmethod
-    def forward(ctx, x, w, bias, residual, gw, gb, act, dropout_p, seed, stream_id, need_input_grad):
+    def forward(ctx, x, w, bias, residual, gw, gb, act, dropout_p, seed, stream_id, need_input_grad, gather=None):
         M, N = x.shape[0], w.shape[0]
         y = empty_rows(M, N, x.device)
         z = empty_rows(M, N, x.device) if act != 0 else None  # pre-activation, needed by act'
         gemm(x, w, y, bias=bias, residual=residual, preact=z, act=act, dropout_p=dropout_p, seed=seed,
-             stream_id=stream_id)
+             stream_id=stream_id, gather=gather)
         ctx.save_for_backward(x, w, z)
         ctx.cfg = (act, dropout_p, seed, stream_id, residual is not None, bias is not None, need_input_grad)
         ctx.gw, ctx.gb = gw, gb
+        ctx.gather = gather
         return y
 
     @staticmethod
@@ -230,8 +239,8 @@ class _LinearFn(torch.autograd.Function):
         dx = None
         if need_dx:
             dx = torch.empty((dy.shape[0], x.shape[1]), dtype=torch.bfloat16, device=dy.device)
-            gemm(dz, w, dx, b_mn_major=True)
-        return dx, None, None, (dy if has_res else None), None, None, None, None, None, None, None
+            gemm(dz, w, dx, b_mn_major=True, gather=ctx.gather)
+        return dx, None, None, (dy if has_res else None), None, None, None, None, None, None, None, None
 
 
 def _colsum_fusable(dy):
@@ -267,8 +276,9 @@ def linear(x, weight, bias=None, act="none", dropout_p=0.0, residual=None, train
         if not torch.is_grad_enabled() or not (need_dx or gw is not None):
             y = empty_rows(x.shape[0], weight.shape[0], x.device)
             return gemm(xin, weight.work, y, bias=b, residual=residual, act=act_id, dropout_p=p, seed=_Rng.seed,
-                        stream_id=sid)
-        return _LinearFn.apply(_track(xin), weight.work, b, residual, gw, gb, act_id, p, _Rng.seed, sid, need_dx)
+                        stream_id=sid, gather=_gather_of(weight))
+        return _LinearFn.apply(_track(xin), weight.work, b, residual, gw, gb, act_id, p, _Rng.seed, sid, need_dx,
+                               _gather_of(weight))
     return ref.linear(x, weight, bias, act_id, p, residual)
 
 
@@ -281,19 +291,20 @@ class _MlpFn(torch.autograd.Function):
     """
 
     @staticmethod
-    def forward(ctx, x, w1, b1, w2, b2, residual, g, act, p1, p2, seed, sid1, sid2):
+    def forward(ctx, x, w1, b1, w2, b2, residual, g, act, p1, p2, seed, sid1, sid2, gather1=None, gather2=None):
         M = x.shape[0]
         h = torch.empty((M, w1.shape[0]), dtype=torch.bfloat16, device=x.device)
         z = torch.empty_like(h) if act != 1 else None
         # ReLU: the epilogue also writes one sign bit per element (ReLU and dropout mask in one), which is all the
         # backward pass needs from h: 1/16 of the bytes of re-reading h
         bits = torch.empty((M, (w1.shape[0] + 31) // 32), dtype=torch.int32, device=x.device) if act == 1 else None
-        gemm(x, w1, h, bias=b1, preact=z, act=act, dropout_p=p1, seed=seed, stream_id=sid1, mask=bits)
+        gemm(x, w1, h, bias=b1, preact=z, act=act, dropout_p=p1, seed=seed, stream_id=sid1, mask=bits, gather=gather1)
         y = torch.empty((M, w2.shape[0]), dtype=torch.bfloat16, device=x.device)
-        gemm(h, w2, y, bias=b2, residual=residual, dropout_p=p2, seed=seed, stream_id=sid2)
+        gemm(h, w2, y, bias=b2, residual=residual, dropout_p=p2, seed=seed, stream_id=sid2, gather=gather2)
         ctx.save_for_backward(x, w1, w2, h, z if z is not None else bits)
         ctx.cfg = (act, p1, p2, seed, sid1, sid2, residual is not None)
         ctx.g = g
+        ctx.gathers = (gather1, gather2)
         return y
 
     @staticmethod
@@ -316,16 +327,18 @@ class _MlpFn(torch.autograd.Function):
         if act == 1:   # the sign bits encode ReLU and the dropout mask; only the keep scale is missing
             # with more than 128 rows the CTA-pair kernel runs, whose epilogue can also sum the columns (fc1 bias gradient)
             fused_gb1 = gb1 is not None and dz2.shape[0] > 128 and dz1.shape[1] % 8 == 0
-            gemm(dz2, w2, dz1, b_mn_major=True, act=8, mask=z, alpha=_keep_scale(p1), colsum=gb1 if fused_gb1 else None)
+            gemm(dz2, w2, dz1, b_mn_major=True, act=8, mask=z, alpha=_keep_scale(p1), colsum=gb1 if fused_gb1 else None,
+                 gather=ctx.gathers[1])
         else:
-            gemm(dz2, w2, dz1, b_mn_major=True, aux=z, act=_ACT_BWD[act], dropout_p=p1, seed=seed, stream_id=sid1)
+            gemm(dz2, w2, dz1, b_mn_major=True, aux=z, act=_ACT_BWD[act], dropout_p=p1, seed=seed, stream_id=sid1,
+                 gather=ctx.gathers[1])
         if gw1 is not None:
             gemm(dz1, x, gw1, a_mn_major=True, b_mn_major=True, accumulate=True, allow_split_k=True)
         if gb1 is not None and not fused_gb1:
             ext().colsum(dz1, gb1)
         dx = torch.empty_like(x)
-        gemm(dz1, w1, dx, b_mn_major=True)
-        return (dx, None, None, None, None, (dy if has_res else None)) + (None,) * 7
+        gemm(dz1, w1, dx, b_mn_major=True, gather=ctx.gathers[0])
+        return (dx, None, None, None, None, (dy if has_res else None)) + (None,) * 9
 
 
 def mlp(x, w1, b1, w2, b2, act="relu", dropout_p=0.0, out_dropout_p=0.0, residual=None, training=True):
@@ -341,11 +354,12 @@ def mlp(x, w1, b1, w2, b2, act="relu", dropout_p=0.0, out_dropout_p=0.0, residua
             g = tuple(getattr(t, "main_grad", None) if (t is not None and t.requires_grad) else None
                       for t in (w1, b1, w2, b2))
             return _MlpFn.apply(_track(xin), w1.work, b1.work if b1 is not None else None, w2.work,
-                                b2.work if b2 is not None else None, residual, g, act_id, p1, p2, _Rng.seed, sid1, sid2)
+                                b2.work if b2 is not None else None, residual, g, act_id, p1, p2, _Rng.seed, sid1, sid2,
+                                _gather_of(w1), _gather_of(w2))
         h = torch.empty((x.shape[0], w1.shape[0]), dtype=torch.bfloat16, device=x.device)
-        gemm(xin, w1.work, h, bias=b1.work if b1 is not None else None, act=act_id)
+        gemm(xin, w1.work, h, bias=b1.work if b1 is not None else None, act=act_id, gather=_gather_of(w1))
         y = torch.empty((x.shape[0], w2.shape[0]), dtype=torch.bfloat16, device=x.device)
-        return gemm(h, w2.work, y, bias=b2.work if b2 is not None else None, residual=residual)
+        return gemm(h, w2.work, y, bias=b2.work if b2 is not None else None, residual=residual, gather=_gather_of(w2))
     h = ref.linear(x, w1, b1, act_id, p1, None)
     return ref.linear(h, w2, b2, 0, p2, residual)
 

@@ -13,14 +13,18 @@
 //     library carries this array from load to process exit, used or not.  A problem with
 //     total_q * heads * 64 above the limit (and max_k > 128, i.e. one that needs the buffer at all) is
 //     rejected with return code 2 and a message in `err`; nothing is launched.
-//   * The first call on each device looks up the device address of the array (cudaGetSymbolAddress) and keeps
-//     it; make that first call outside any stream capture.  Later calls only enqueue work.
+//   * The first call on each device looks up the device address of the array (cudaGetSymbolAddress), raises the
+//     backward kernel's shared-memory limit, and keeps both; make that first call outside any stream capture.
+//     Later calls, from any host thread, only bind the device's context to the thread (cudaSetDevice), build
+//     their descriptors and enqueue work.
 //   * All calls share the one array and it keeps whatever the previous call left in it.  Each call clears the
 //     part it is about to use (an asynchronous memset on `stream`) before its kernels run.  Two calls whose
 //     work can overlap on the GPU (different streams, no dependency between them) would accumulate into the
 //     same memory and corrupt each other: serialise them.
-//   * No cudaMalloc, cudaFree, or other allocating routine is called; tensor-map descriptors are built on the
-//     host stack.  Inputs and outputs are the caller's.
+//   * No cudaMalloc, cudaFree, or other allocating routine is called.  All five tensor-map descriptors (q, k, v,
+//     dO and the fp32 view of the built-in array) are encoded into variables on the caller's stack on every
+//     call; the descriptor cache and its lock, which the regular entry point uses, are not touched.  Inputs
+//     and outputs are the caller's.
 //   * Dropout is supported with the same (seed, stream id) convention as the regular entry point.
 //
 // Returns 0 on success; 1 = bad argument, 2 = problem larger than the built-in buffer, 3 = CUDA error

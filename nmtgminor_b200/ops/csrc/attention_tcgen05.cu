@@ -740,13 +740,14 @@ const char* nmtg_attn_bwd(const AttnDesc* d, cudaStream_t stream) {
 #include <cstdio>
 
 namespace b200 {
-bool make_tmap_bf16_2d(CUtensorMap* out, const void* base, long rows, long cols, long ld, int box_rows, int box_cols);
+bool make_tmap_2d_nobind(CUtensorMap* out, const void* base, long rows, long cols, long ld, int box_rows, int box_cols, bool f32);
 }
 
 // The fp32 dQ accumulation buffer of the no-allocation entry point.  In host code this name is only a handle
 // for cudaGetSymbolAddress, never a pointer that a kernel may receive.
 static __device__ __align__(256) float g_attn_noalloc_scratch[NMTG_ATTN_NOALLOC_MAX_FLOATS];
 static float* g_attn_noalloc_ptr[64] = {};   // device address of the array, per device ordinal
+static bool g_attn_noalloc_smem_set[64] = {}; // the backward kernel's shared-memory limit was raised on this device
 
 static int noalloc_fail(int code, const char* msg, char* err, int err_len) {
   if (err && err_len > 0) snprintf(err, static_cast<size_t>(err_len), "%s", msg);
@@ -778,6 +779,10 @@ extern "C" int nmtg_attn_bwd_noalloc(const void* q, int ld_q, const void* k, int
   int dev = 0;
   cudaError_t ce = cudaGetDevice(&dev);
   if (ce != cudaSuccess || dev < 0 || dev >= 64) return noalloc_fail(3, "cudaGetDevice failed", err, err_len);
+  // Binds the device's primary context to the calling thread (the descriptor encoder below is a driver entry point and
+  // needs one); unlike the regular path's cudaFree(nullptr) this is legal while another thread captures a stream.
+  ce = cudaSetDevice(dev);
+  if (ce != cudaSuccess) return noalloc_fail(3, cudaGetErrorString(ce), err, err_len);
   if (!g_attn_noalloc_ptr[dev]) {   // first call on this device: resolve the array's device address
     float* p = nullptr;
     ce = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_attn_noalloc_scratch);
@@ -790,8 +795,10 @@ extern "C" int nmtg_attn_bwd_noalloc(const void* q, int ld_q, const void* k, int
     if (ce != cudaSuccess) return noalloc_fail(3, cudaGetErrorString(ce), err, err_len);
   }
   CUtensorMap tq, tk, tv, tdo;
-  if (!make_tmap_bf16_2d(&tq, q, total_q, width, ld_q, kTile, kHd) || !make_tmap_bf16_2d(&tk, k, total_k, width, ld_k, kTile, kHd) ||
-      !make_tmap_bf16_2d(&tv, v, total_k, width, ld_v, kTile, kHd) || !make_tmap_bf16_2d(&tdo, d_out, total_q, width, ld_dout, kTile, kHd))
+  if (!make_tmap_2d_nobind(&tq, q, total_q, width, ld_q, kTile, kHd, false) ||
+      !make_tmap_2d_nobind(&tk, k, total_k, width, ld_k, kTile, kHd, false) ||
+      !make_tmap_2d_nobind(&tv, v, total_k, width, ld_v, kTile, kHd, false) ||
+      !make_tmap_2d_nobind(&tdo, d_out, total_q, width, ld_dout, kTile, kHd, false))
     return noalloc_fail(3, "attention: cuTensorMapEncodeTiled failed", err, err_len);
   AttnArgs a = {};
   a.cu_q = cu_q; a.cu_k = cu_k; a.num_heads = num_heads; a.causal = causal; a.scale = scale;
@@ -805,10 +812,13 @@ extern "C" int nmtg_attn_bwd_noalloc(const void* q, int ld_q, const void* k, int
   a.dv = reinterpret_cast<__nv_bfloat16*>(dv); a.ld_dv = ld_dv;
   a.dq_acc = scratch; a.ld_dqacc = width;
   a.total_q = total_q; a.total_k = total_k; a.batch = batch; a.status = status;
-  ce = cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kBwdSmem);
-  if (ce != cudaSuccess) return noalloc_fail(3, cudaGetErrorString(ce), err, err_len);
+  if (!g_attn_noalloc_smem_set[dev]) {   // once per device, like the address look-up above
+    ce = cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kBwdSmem);
+    if (ce != cudaSuccess) return noalloc_fail(3, cudaGetErrorString(ce), err, err_len);
+    g_attn_noalloc_smem_set[dev] = true;
+  }
   CUtensorMap tdq = tq;       // placeholder when no accumulation buffer is needed
-  a.dq_tma = (needs_buffer && cached_tmap_f32(&tdq, scratch, total_q, width, width, kTile, 32)) ? 1 : 0;
+  a.dq_tma = (needs_buffer && make_tmap_2d_nobind(&tdq, scratch, total_q, width, width, kTile, 32, true)) ? 1 : 0;
   dim3 grid((max_k + kTile - 1) / kTile, num_heads, batch);
   attn_bwd_kernel<<<grid, 256, kBwdSmem, stream>>>(tq, tk, tv, tdo, tdq, a);
   ce = cudaGetLastError();

@@ -21,6 +21,7 @@ enum Status : int {
   kTimeoutTmemFull = 3,   // epilogue waited for an accumulator that never completed
   kTimeoutTmemEmpty = 4,  // MMA warp waited for an accumulator that was never drained
   kTimeoutPeerFlag = 5,   // a peer GPU never raised its flag
+  kTimeoutGather = 7,     // the in-kernel gather of a sharded operand never completed a segment
   kBadArgument = 6,
 };
 
@@ -76,6 +77,15 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   *abort_word = 1;
   if (status) atomicCAS(status, 0, code);
   return false;
+}
+
+// generic-proxy accesses (any state space) ordered against the async proxy: global memory written with ordinary
+// stores and then read by a TMA load in the same kernel needs this on both sides of the flag that orders them
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+__device__ __forceinline__ int ld_acquire_gpu(const int* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
 }
 
 // generic-proxy writes to shared memory -> visible to the async proxy (TMA / UMMA reads)

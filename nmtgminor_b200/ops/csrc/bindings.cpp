@@ -62,7 +62,7 @@ Tensor get_seed_tensor(int64_t device) { return seed_tensor(static_cast<int>(dev
 void gemm(const Tensor& a, bool a_mn_major, const Tensor& b, bool b_mn_major, Tensor& out, const OptTensor& bias,
           const OptTensor& residual, const OptTensor& aux, const OptTensor& preact, int64_t act, double dropout_p,
           int64_t seed, int64_t stream_id, double alpha, bool accumulate, bool allow_split_k, int64_t split_k,
-          int64_t force_bn, const OptTensor& mask, const OptTensor& colsum) {
+          int64_t force_bn, const OptTensor& mask, const OptTensor& colsum, const pybind11::object& gather) {
   need_bf16(a, "a"); need_bf16(b, "b");
   need_rowmajor2d(a, "a"); need_rowmajor2d(b, "b"); need_rowmajor2d(out, "out");
   c10::cuda::CUDAGuard guard(a.device());
@@ -111,6 +111,31 @@ void gemm(const Tensor& a, bool a_mn_major, const Tensor& b, bool b_mn_major, Te
   d.split_k = static_cast<int>(split_k); d.allow_split_k = allow_split_k; d.force_bn = static_cast<int>(force_bn);
   d.seed_dev = seed_ptr(a);
   d.status = status_ptr(a);
+  NmtgGather gth = {};
+  if (!gather.is_none()) {
+    // (rank, [shard pointer of every rank], staging buffer, shard_off, piece_len, unit_off, numel, counters): B is a view
+    // of the staging buffer and its pieces are pulled from the owners' shards by this call
+    auto tup = gather.cast<pybind11::tuple>();
+    TORCH_CHECK(tup.size() == 8, "gemm: gather must be an 8-tuple");
+    gth.rank = tup[0].cast<int>();
+    auto shards = tup[1].cast<std::vector<int64_t>>();
+    gth.world = static_cast<int>(shards.size());
+    TORCH_CHECK(gth.world >= 1 && gth.world <= 16, "gemm: gather world size out of range");
+    for (int i = 0; i < gth.world; ++i) gth.shards[i] = reinterpret_cast<const unsigned short*>(shards[i]);
+    const Tensor staging = tup[2].cast<Tensor>();
+    gth.shard_off = tup[3].cast<int64_t>(); gth.piece_len = tup[4].cast<int64_t>(); gth.unit_off = tup[5].cast<int64_t>();
+    const int64_t numel = tup[6].cast<int64_t>();
+    const Tensor counters = tup[7].cast<Tensor>();
+    need_bf16(staging, "gather staging");
+    TORCH_CHECK(counters.is_cuda() && counters.scalar_type() == at::kInt && counters.is_contiguous() && counters.numel() >= 2 + 128,
+                "gemm: gather counters must be int32 [>= 130]");
+    TORCH_CHECK(b.is_contiguous() && b.numel() == numel, "gemm: a gathered operand must be the whole contiguous matrix");
+    TORCH_CHECK(reinterpret_cast<const char*>(b.data_ptr()) == reinterpret_cast<const char*>(staging.data_ptr()) + 2 * gth.unit_off,
+                "gemm: the gathered operand is not at its place in the staging buffer");
+    TORCH_CHECK(gth.unit_off + numel <= gth.piece_len * gth.world, "gemm: gathered operand outside its unit");
+    gth.counters = counters.data_ptr<int>();
+    d.gather = &gth;
+  }
   ck(nmtg_gemm_bf16(&d, cur_stream()));
 }
 
@@ -339,6 +364,8 @@ int64_t ipc_open_handle(const std::string& bytes, int64_t device) {
 
 void ipc_close_handle(int64_t ptr) { cudaIpcCloseMemHandle(reinterpret_cast<void*>(ptr)); }
 
+long long g_peer_timeout_ns = 20LL * 1000 * 1000 * 1000;   // wall-time bound of every cross-GPU wait
+
 NmtgPeerTable make_table(int64_t rank, const std::vector<int64_t>& grads, const std::vector<int64_t>& works,
                          const std::vector<int64_t>& flags, const std::vector<int64_t>& partials, const OptTensor& norm_out) {
   NmtgPeerTable t = {};
@@ -353,52 +380,66 @@ NmtgPeerTable make_table(int64_t rank, const std::vector<int64_t>& grads, const 
     t.partials[i] = reinterpret_cast<float*>(partials[i]);
   }
   t.norm_out = norm_out.has_value() ? norm_out->data_ptr<float>() : nullptr;
+  t.timeout_ns = g_peer_timeout_ns;
   return t;
 }
 
-void allreduce_adamw(int64_t rank, const std::vector<int64_t>& grads, const std::vector<int64_t>& works,
-                     const std::vector<int64_t>& flags, const std::vector<int64_t>& partials, Tensor& reduced, Tensor& sq,
-                     Tensor& nonfinite, Tensor& master, Tensor& m, Tensor& v, const Tensor& hyper, int64_t slice_begin,
-                     int64_t slice_len, int64_t total_len, Tensor& epoch, const OptTensor& norm_out) {
-  need_f32(reduced, "reduced"); need_f32(sq, "sq"); need_f32(master, "master"); need_f32(m, "m"); need_f32(v, "v");
-  need_f32(hyper, "hyper");
-  TORCH_CHECK(reduced.numel() >= slice_len && master.numel() >= slice_len && m.numel() >= slice_len && v.numel() >= slice_len);
-  c10::cuda::CUDAGuard guard(master.device());
-  NmtgPeerTable t = make_table(rank, grads, works, flags, partials, norm_out);
-  ck(nmtg_allreduce_adamw(&t, reduced.data_ptr<float>(), sq.data_ptr<float>(), nonfinite.data_ptr<int>(), master.data_ptr<float>(),
-                          m.data_ptr<float>(), v.data_ptr<float>(), reinterpret_cast<const NmtgAdamHyper*>(hyper.data_ptr<float>()),
-                          slice_begin, slice_len, total_len, epoch.data_ptr<int>(), status_ptr(master), cur_stream()));
+// reduce-scatter of one unit (see ops_api.h); `reduced` is the unit's piece inside the shard-ordered buffer
+void reduce_unit(int64_t rank, const std::vector<int64_t>& grads, const std::vector<int64_t>& flags, int64_t row, Tensor& reduced,
+                 int64_t global_begin, int64_t len, bool accumulate, int64_t zero_begin, int64_t zero_len,
+                 const OptTensor& counter, const Tensor& epoch, int64_t ctas) {
+  need_f32(reduced, "reduced");
+  TORCH_CHECK(reduced.is_contiguous() && reduced.numel() >= len, "reduce_unit: output too small");
+  TORCH_CHECK(epoch.is_cuda() && epoch.scalar_type() == at::kInt);
+  if (counter.has_value()) TORCH_CHECK(counter->is_cuda() && counter->scalar_type() == at::kInt);
+  std::vector<int64_t> zeros(grads.size(), 0);
+  c10::cuda::CUDAGuard guard(reduced.device());
+  NmtgPeerTable t = make_table(rank, grads, zeros, flags, zeros, c10::nullopt);
+  ck(nmtg_reduce_unit(&t, static_cast<int>(row), reduced.data_ptr<float>(), global_begin, len, accumulate ? 1 : 0, zero_begin,
+                      zero_len, counter.has_value() ? counter->data_ptr<int>() : nullptr, epoch.data_ptr<int>(),
+                      status_ptr(reduced), static_cast<int>(ctas), cur_stream()));
 }
 
-void fsdp_gather(int64_t rank, const std::vector<int64_t>& works, Tensor& dst, int64_t shard_off, int64_t piece_len,
-                 int64_t unit_len, int64_t ctas) {
-  need_bf16(dst, "dst");
-  TORCH_CHECK(dst.is_contiguous() && dst.numel() >= unit_len, "fsdp_gather: staging buffer too small");
-  std::vector<int64_t> zeros(works.size(), 0);
-  c10::cuda::CUDAGuard guard(dst.device());
-  NmtgPeerTable t = make_table(rank, zeros, works, zeros, zeros, c10::nullopt);
-  ck(nmtg_fsdp_gather(&t, dst.data_ptr(), shard_off, piece_len, unit_len, static_cast<int>(ctas), cur_stream()));
-}
-
-void fsdp_step(int64_t rank, const std::vector<int64_t>& grads, const std::vector<int64_t>& works, const std::vector<int64_t>& flags,
-               const std::vector<int64_t>& partials, const std::vector<int64_t>& shard_off, const std::vector<int64_t>& global_begin,
-               const std::vector<int64_t>& piece_len, Tensor& reduced, Tensor& sq, Tensor& nonfinite, Tensor& master, Tensor& m,
-               Tensor& v, const Tensor& hyper, int64_t shard_len, int64_t total_len, Tensor& epoch, const OptTensor& norm_out) {
+void update_pieces(int64_t rank, const std::vector<int64_t>& grads, const std::vector<int64_t>& works,
+                   const std::vector<int64_t>& flags, const std::vector<int64_t>& partials, const std::vector<int64_t>& shard_off,
+                   const std::vector<int64_t>& global_begin, const std::vector<int64_t>& piece_len, const Tensor& reduced,
+                   Tensor& master, Tensor& m, Tensor& v, const Tensor& hyper, const Tensor& sq, const Tensor& nonfinite, int64_t mode,
+                   int64_t zero_len, Tensor& epoch, const OptTensor& norm_out) {
   need_f32(reduced, "reduced"); need_f32(sq, "sq"); need_f32(master, "master"); need_f32(m, "m"); need_f32(v, "v");
   need_f32(hyper, "hyper");
-  TORCH_CHECK(reduced.numel() >= shard_len && master.numel() >= shard_len && m.numel() >= shard_len && v.numel() >= shard_len);
-  TORCH_CHECK(shard_off.size() == global_begin.size() && shard_off.size() == piece_len.size() && shard_off.size() <= kFsdpMaxUnits);
+  TORCH_CHECK(shard_off.size() == global_begin.size() && shard_off.size() == piece_len.size() &&
+              shard_off.size() <= static_cast<size_t>(kNmtgMaxUnits), "update_pieces: inconsistent piece lists");
   c10::cuda::CUDAGuard guard(master.device());
   NmtgPeerTable t = make_table(rank, grads, works, flags, partials, norm_out);
-  NmtgFsdpPieces pc = {};
+  NmtgPieces pc = {};
   pc.n = static_cast<int>(shard_off.size());
   for (int u = 0; u < pc.n; ++u) {
     pc.shard_off[u] = shard_off[u]; pc.global_begin[u] = global_begin[u]; pc.len[u] = piece_len[u];
-    TORCH_CHECK(shard_off[u] + piece_len[u] <= shard_len && global_begin[u] + piece_len[u] <= total_len, "fsdp_step: piece out of range");
+    TORCH_CHECK(shard_off[u] + piece_len[u] <= reduced.numel() && shard_off[u] + piece_len[u] <= m.numel() &&
+                shard_off[u] + piece_len[u] <= v.numel(), "update_pieces: piece outside the shard-ordered buffers");
+    TORCH_CHECK((mode == 0 ? global_begin[u] : shard_off[u]) + piece_len[u] <= master.numel(), "update_pieces: piece outside the master weights");
   }
-  ck(nmtg_fsdp_step(&t, &pc, reduced.data_ptr<float>(), sq.data_ptr<float>(), nonfinite.data_ptr<int>(), master.data_ptr<float>(),
-                    m.data_ptr<float>(), v.data_ptr<float>(), reinterpret_cast<const NmtgAdamHyper*>(hyper.data_ptr<float>()), shard_len,
-                    total_len, epoch.data_ptr<int>(), status_ptr(master), cur_stream()));
+  ck(nmtg_update_pieces(&t, &pc, reduced.data_ptr<float>(), master.data_ptr<float>(), m.data_ptr<float>(), v.data_ptr<float>(),
+                        reinterpret_cast<const NmtgAdamHyper*>(hyper.data_ptr<float>()), sq.data_ptr<float>(),
+                        nonfinite.data_ptr<int>(), static_cast<int>(mode), zero_len, epoch.data_ptr<int>(), status_ptr(master),
+                        cur_stream()));
+}
+
+void peer_finish_step(int64_t rank, const std::vector<int64_t>& flags, Tensor& epoch) {
+  std::vector<int64_t> zeros(flags.size(), 0);
+  c10::cuda::CUDAGuard guard(epoch.device());
+  NmtgPeerTable t = make_table(rank, zeros, zeros, flags, zeros, c10::nullopt);
+  ck(nmtg_peer_finish_step(&t, epoch.data_ptr<int>(), status_ptr(epoch), cur_stream()));
+}
+
+void fsdp_gather(int64_t rank, const std::vector<int64_t>& works, Tensor& dst, int64_t shard_off, int64_t piece_len,
+                 int64_t e0, int64_t e1, int64_t ctas) {
+  need_bf16(dst, "dst");
+  TORCH_CHECK(dst.is_contiguous() && dst.numel() >= e1, "fsdp_gather: staging buffer too small");
+  std::vector<int64_t> zeros(works.size(), 0);
+  c10::cuda::CUDAGuard guard(dst.device());
+  NmtgPeerTable t = make_table(rank, zeros, works, zeros, zeros, c10::nullopt);
+  ck(nmtg_fsdp_gather(&t, dst.data_ptr(), shard_off, piece_len, e0, e1, static_cast<int>(ctas), cur_stream()));
 }
 
 void peer_wait_row(int64_t rank, const std::vector<int64_t>& flags, int64_t row, int64_t epoch, const Tensor& like) {
@@ -407,6 +448,10 @@ void peer_wait_row(int64_t rank, const std::vector<int64_t>& flags, int64_t row,
   NmtgPeerTable t = make_table(rank, zeros, zeros, flags, zeros, c10::nullopt);
   ck(nmtg_peer_wait_row(&t, static_cast<int>(row), static_cast<int>(epoch), status_ptr(like), cur_stream()));
 }
+
+void set_peer_timeout_ms(double ms) { g_peer_timeout_ns = static_cast<long long>(ms * 1e6); }
+double get_peer_timeout_ms() { return static_cast<double>(g_peer_timeout_ns) / 1e6; }
+Tensor get_status_tensor(int64_t device) { return status_tensor(static_cast<int>(device)); }
 
 int64_t read_status(int64_t device) {
   Tensor& s = status_tensor(static_cast<int>(device));
@@ -425,7 +470,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         pybind11::arg("bias"), pybind11::arg("residual"), pybind11::arg("aux"), pybind11::arg("preact"), pybind11::arg("act"),
         pybind11::arg("dropout_p"), pybind11::arg("seed"), pybind11::arg("stream_id"), pybind11::arg("alpha"), pybind11::arg("accumulate"),
         pybind11::arg("allow_split_k"), pybind11::arg("split_k"), pybind11::arg("force_bn"), pybind11::arg("mask") = pybind11::none(),
-        pybind11::arg("colsum") = pybind11::none());
+        pybind11::arg("colsum") = pybind11::none(), pybind11::arg("gather") = pybind11::none());
   m.def("set_gemm_variant", [](int64_t v) { nmtg_set_gemm_variant(static_cast<int>(v)); });
   m.def("set_gemm_trace", [](const OptTensor& buf) {
     if (buf.has_value()) {
@@ -455,10 +500,14 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("ipc_get_handle", &ipc_get_handle);
   m.def("ipc_open_handle", &ipc_open_handle);
   m.def("ipc_close_handle", &ipc_close_handle);
-  m.def("allreduce_adamw", &allreduce_adamw);
+  m.def("reduce_unit", &reduce_unit);
+  m.def("update_pieces", &update_pieces);
+  m.def("peer_finish_step", &peer_finish_step);
   m.def("fsdp_gather", &fsdp_gather);
-  m.def("fsdp_step", &fsdp_step);
   m.def("peer_wait_row", &peer_wait_row);
+  m.def("set_peer_timeout_ms", &set_peer_timeout_ms);
+  m.def("get_peer_timeout_ms", &get_peer_timeout_ms);
+  m.def("get_status_tensor", &get_status_tensor);
   m.def("bounds_violations", []() { return static_cast<int64_t>(nmtg_bounds_violations()); });
   m.def("read_status", &read_status);
   m.def("clear_status", &clear_status);

@@ -1,29 +1,33 @@
-// Data-parallel gradient reduction fused with the optimiser, over peer-mapped (NVLink / NVSwitch) memory.
+// Gradient reduction fused with the optimiser over peer-mapped (NVLink / NVSwitch) memory, for data parallelism
+// and for fully sharded parameters.
 //
-// Every rank keeps its flat fp32 gradient buffer and its flat bf16 parameter copy in memory that all other
-// ranks of the node have mapped (CUDA IPC).  Rank r OWNS slice r of the flat parameter space: fp32 master
-// weights and Adam moments exist only for that slice (optimiser state is sharded N ways).  One step is three
-// launches per rank, each ordered after the previous one by the stream:
+// Every rank keeps its fp32 gradients (and, data parallel, its bf16 parameter copy) in memory that all other
+// ranks of the node have mapped (CUDA IPC).  The flat parameter space is cut into UNITS - one per Transformer
+// layer, everything else merged - and every unit into `world` pieces; rank r OWNS piece r of every unit: Adam
+// moments (and, fully sharded, fp32 master weights and bf16 parameters) exist only for owned pieces.
 //
-//   reduce_slice   waits (bounded) until every peer has published "gradients ready", then sums slice r of all
-//                  N gradient buffers with direct 16-byte peer loads (each CTA fetches its own elements; no
-//                  broadcast loads of any kind), writes the fp32 sum to a local buffer, accumulates the
-//                  sum of squares of the slice and flags non-finite values.
-//   update_slice   publishes the slice's sum of squares to every peer, waits (bounded) for all N partials,
-//                  forms the global gradient norm / clip coefficient, applies Adam(W) to the owned slice,
-//                  stores the refreshed bf16 parameters of the slice into EVERY rank's parameter copy with
-//                  peer stores (the all-gather), and clears this rank's whole gradient buffer.
-//   finish_step    publishes "parameters written" and waits (bounded) for all peers, so the next forward
-//                  pass reads a complete parameter copy.
+//   reduce_unit    one launch per unit, enqueued on a communication stream as soon as the backward pass has
+//                  produced the unit's last weight gradient, so the transfer overlaps the backward pass of the
+//                  layers below.  Waits (bounded) until every peer has published "this unit is complete",
+//                  then sums its piece over all N gradient buffers with 16-byte peer loads (each CTA fetches
+//                  its own elements; no broadcast loads of any kind) into the shard-ordered `reduced` buffer.
+//                  With rotating per-layer gradient buffers it also tells the peers when it has finished
+//                  reading and clears its own copy once they all have.
+//   update_pieces  after the last unit: exchanges the squared-norm partials, forms the global gradient norm
+//                  and the clipping coefficient, applies Adam(W) to every owned piece and publishes the
+//                  refreshed bf16 parameters - data parallel: stored into EVERY rank's parameter copy with peer
+//                  stores (the all-gather); fully sharded: into the local shard that the gathers read.
+//   finish_step    closing barrier, so the next forward pass reads complete parameters.
 //
 // Cross-GPU flags are monotonically increasing epochs written with st.release.sys and polled with
-// ld.acquire.sys; a waiter that runs out of polls records kTimeoutPeerFlag in the status word and the
-// kernel returns (the host raises), so a missing peer can never hang a GPU.  Bytes over NVLink per rank and
-// step: (N-1)/N * P * 4 in (gradients) and (N-1)/N * P * 2 out (parameters), against 2 * (N-1)/N * P * 4 for
-// a ring all-reduce followed by a replicated optimiser.
+// ld.acquire.sys; a waiter that runs out of time records kTimeoutPeerFlag in the status word and the kernel
+// returns (the host raises), so a missing peer can never hang a GPU.  Bytes over NVLink per rank and step, data
+// parallel: (N-1)/N * P * 4 in (gradients) and (N-1)/N * P * 2 out (parameters), against 2 * (N-1)/N * P * 4
+// for a ring all-reduce followed by a replicated optimiser.
 //
 // Replaces DistributedDataParallel's bucketed NCCL all-reduce + GradScaler.unscale_ + clip_grad_norm +
-// optimizer.step of the reference (onmt/train_utils/mp_trainer.py:381-387, 895-1016).
+// optimizer.step (onmt/train_utils/mp_trainer.py:381-387, 895-1016) and FSDP's reduce-scatter + sharded
+// optimizer step (onmt/train_utils/mp_trainer.py:314-341) of the reference.
 #include <cuda_runtime.h>
 #include <cuda_bf16.h>
 #include <stdint.h>
@@ -34,48 +38,52 @@ namespace b200 {
 
 int num_sms();
 
-__global__ void __launch_bounds__(512)
-reduce_slice_kernel(const NmtgPeerTable t, float* __restrict__ reduced, float* __restrict__ sq_out, int* __restrict__ nonfinite,
-                    long slice_begin, long slice_len, const int* __restrict__ epoch_ptr, int* status) {
+// 256-thread CTAs at about 40 registers: small enough to share an SM with a resident GEMM CTA (320 threads at up to
+// 168 registers), so the reduction runs beside the backward pass instead of waiting for an SM to drain.
+__global__ void __launch_bounds__(256)
+reduce_unit_kernel(const NmtgPeerTable t, int row, float* __restrict__ reduced, long g0, long len, int accumulate,
+                   long zero_begin, long zero_len, int* __restrict__ counter, const int* __restrict__ epoch_ptr, int* status) {
   const int epoch = *epoch_ptr;
-  if (!peer_barrier(t, 0, epoch, status)) return;
-  __shared__ float red[16];
-  float acc = 0.f;
-  const long n4 = slice_len >> 2;
-  for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < n4; i += static_cast<long>(gridDim.x) * blockDim.x) {
-    float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (!peer_barrier(t, row, epoch, status)) return;
+  const long n4 = len >> 2;
+  const long stride = static_cast<long>(gridDim.x) * blockDim.x;
+  for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < n4; i += stride) {
+    float4 s = accumulate ? reinterpret_cast<const float4*>(reduced)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll 4
     for (int r = 0; r < t.world; ++r) {
       // start with my own buffer, then walk the ring so the peers' links are loaded evenly
       const int src = (t.rank + r) % t.world;
-      const float4 v = reinterpret_cast<const float4*>(t.grads[src] + slice_begin)[i];
+      const float4 v = reinterpret_cast<const float4*>(t.grads[src] + g0)[i];
       s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
     }
     reinterpret_cast<float4*>(reduced)[i] = s;
-    acc += s.x * s.x + s.y * s.y + s.z * s.z + s.w * s.w;
   }
-  const bool bad = !isfinite(acc);
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
-  if (bad) atomicOr(nonfinite, 1);
+  if (zero_len <= 0) return;
+  // Rotating gradient buffers: the LAST CTA of this launch to finish its loads tells every peer "rank `rank` has
+  // read the unit"; everybody then waits for all peers' notices before clearing the local copy.
+  __shared__ int s_last;
   __syncthreads();
-  if (threadIdx.x < 32) {
-    float v = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.f;
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-    if (threadIdx.x == 0) {
-      if (isfinite(v)) atomicAdd(sq_out, v);
-      else atomicOr(nonfinite, 1);
-    }
+  if (threadIdx.x == 0) {
+    __threadfence();
+    s_last = (atomicAdd(counter, 1) == static_cast<int>(gridDim.x) - 1);
   }
+  __syncthreads();
+  if (s_last) {
+    peer_publish(t, row + 1, epoch);
+    if (threadIdx.x == 0) *counter = 0;      // ready for the next launch from this site
+  }
+  if (!peer_barrier(t, row + 1, epoch, status, /*publish=*/false)) return;
+  float4* z = reinterpret_cast<float4*>(t.grads[t.rank] + zero_begin);
+  const long z4 = zero_len >> 2;
+  const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < z4; i += stride) z[i] = zero;
 }
 
 __global__ void __launch_bounds__(512)
-update_slice_kernel(const NmtgPeerTable t, const float* __restrict__ reduced, float* __restrict__ master, float* __restrict__ m,
-                    float* __restrict__ v, const NmtgAdamHyper* __restrict__ hp, const float* __restrict__ sq_local,
-                    const int* __restrict__ nonfinite_local, long slice_begin, long slice_len, long total_len,
-                    const int* __restrict__ epoch_ptr, int* status) {
+update_pieces_kernel(const NmtgPeerTable t, const NmtgPieces pc, const float* __restrict__ reduced, float* __restrict__ master,
+                     float* __restrict__ m, float* __restrict__ v, const NmtgAdamHyper* __restrict__ hp,
+                     const float* __restrict__ sq_local, const int* __restrict__ nonfinite_local, int mode, long zero_len,
+                     const int* __restrict__ epoch_ptr, int* status) {
   const int epoch = *epoch_ptr;
   // publish my partial (sum of squares, non-finite flag as a negative value) to every rank, then gather all
   if (threadIdx.x < t.world) {
@@ -91,7 +99,7 @@ update_slice_kernel(const NmtgPeerTable t, const float* __restrict__ reduced, fl
     int skip = 0;
     for (int r = 0; r < t.world; ++r) {
       const float p = ld_relaxed_sys_f32(&t.partials[t.rank][(epoch & 1) * kMaxRanks + r]);
-      if (p < 0.f) skip = 1;
+      if (p < 0.f || !isfinite(p)) skip = 1;
       total += p;
     }
     float coef = h.grad_scale;
@@ -105,46 +113,54 @@ update_slice_kernel(const NmtgPeerTable t, const float* __restrict__ reduced, fl
   }
   __syncthreads();
   const float coef = s_coef;
-  const bool skip = s_skip != 0;
-  const long n4 = slice_len >> 2;
-  if (!skip) {
-    for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < n4; i += static_cast<long>(gridDim.x) * blockDim.x) {
-      const float4 g4 = reinterpret_cast<const float4*>(reduced)[i];
-      float4 p4 = reinterpret_cast<float4*>(master)[i];
-      float4 m4 = reinterpret_cast<float4*>(m)[i];
-      float4 v4 = reinterpret_cast<float4*>(v)[i];
-      float gg[4] = {g4.x, g4.y, g4.z, g4.w}, pp[4] = {p4.x, p4.y, p4.z, p4.w}, mm[4] = {m4.x, m4.y, m4.z, m4.w},
-            vv[4] = {v4.x, v4.y, v4.z, v4.w};
+  const long stride = static_cast<long>(gridDim.x) * blockDim.x;
+  if (!s_skip) {
+    for (int u = 0; u < pc.n; ++u) {
+      const long n4 = pc.len[u] >> 2;
+      const long so = pc.shard_off[u], g0 = pc.global_begin[u];
+      float* mp = master + (mode == 0 ? g0 : so);
+      for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < n4; i += stride) {
+        const float4 g4 = reinterpret_cast<const float4*>(reduced + so)[i];
+        float4 p4 = reinterpret_cast<float4*>(mp)[i];
+        float4 m4 = reinterpret_cast<float4*>(m + so)[i];
+        float4 v4 = reinterpret_cast<float4*>(v + so)[i];
+        float gg[4] = {g4.x, g4.y, g4.z, g4.w}, pp[4] = {p4.x, p4.y, p4.z, p4.w}, mm[4] = {m4.x, m4.y, m4.z, m4.w},
+              vv[4] = {v4.x, v4.y, v4.z, v4.w};
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        float g = gg[j] * coef;
-        if (!h.decoupled_wd && h.weight_decay != 0.f) g += h.weight_decay * pp[j];
-        mm[j] = h.beta1 * mm[j] + (1.f - h.beta1) * g;
-        vv[j] = h.beta2 * vv[j] + (1.f - h.beta2) * g * g;
-        float upd = (mm[j] / h.bias_correction1) / (sqrtf(vv[j] / h.bias_correction2) + h.eps);
-        if (h.decoupled_wd) upd += h.weight_decay * pp[j];
-        pp[j] -= h.lr * upd;
-      }
-      reinterpret_cast<float4*>(master)[i] = make_float4(pp[0], pp[1], pp[2], pp[3]);
-      reinterpret_cast<float4*>(m)[i] = make_float4(mm[0], mm[1], mm[2], mm[3]);
-      reinterpret_cast<float4*>(v)[i] = make_float4(vv[0], vv[1], vv[2], vv[3]);
-      __nv_bfloat162 lo = __floats2bfloat162_rn(pp[0], pp[1]), hi = __floats2bfloat162_rn(pp[2], pp[3]);
-      uint2 o;
-      o.x = *reinterpret_cast<uint32_t*>(&lo);
-      o.y = *reinterpret_cast<uint32_t*>(&hi);
+        for (int j = 0; j < 4; ++j) {
+          float g = gg[j] * coef;
+          if (!h.decoupled_wd && h.weight_decay != 0.f) g += h.weight_decay * pp[j];
+          mm[j] = h.beta1 * mm[j] + (1.f - h.beta1) * g;
+          vv[j] = h.beta2 * vv[j] + (1.f - h.beta2) * g * g;
+          float upd = (mm[j] / h.bias_correction1) / (sqrtf(vv[j] / h.bias_correction2) + h.eps);
+          if (h.decoupled_wd) upd += h.weight_decay * pp[j];
+          pp[j] -= h.lr * upd;
+        }
+        reinterpret_cast<float4*>(mp)[i] = make_float4(pp[0], pp[1], pp[2], pp[3]);
+        reinterpret_cast<float4*>(m + so)[i] = make_float4(mm[0], mm[1], mm[2], mm[3]);
+        reinterpret_cast<float4*>(v + so)[i] = make_float4(vv[0], vv[1], vv[2], vv[3]);
+        __nv_bfloat162 lo = __floats2bfloat162_rn(pp[0], pp[1]), hi = __floats2bfloat162_rn(pp[2], pp[3]);
+        uint2 o;
+        o.x = *reinterpret_cast<uint32_t*>(&lo);
+        o.y = *reinterpret_cast<uint32_t*>(&hi);
+        if (mode == 0) {
 #pragma unroll 4
-      for (int r = 0; r < t.world; ++r) {
-        const int dst = (t.rank + r) % t.world;
-        reinterpret_cast<uint2*>(t.works[dst] + slice_begin)[i] = o;   // all-gather by peer stores
+          for (int r = 0; r < t.world; ++r) {
+            const int dst = (t.rank + r) % t.world;
+            reinterpret_cast<uint2*>(t.works[dst] + g0)[i] = o;   // all-gather by peer stores
+          }
+        } else {
+          reinterpret_cast<uint2*>(t.works[t.rank] + so)[i] = o;  // the shard that the next step's gathers read
+        }
       }
     }
   }
-  // every peer has finished reading my gradients (they passed the barrier above): clear the whole buffer
-  if (h.zero_grad) {
+  // every peer has finished reading my gradients (they passed the barrier above): clear the local space
+  if (h.zero_grad && zero_len > 0) {
     float4* g = reinterpret_cast<float4*>(t.grads[t.rank]);
-    const long t4 = total_len >> 2;
+    const long t4 = zero_len >> 2;
     const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < t4; i += static_cast<long>(gridDim.x) * blockDim.x) g[i] = z;
+    for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < t4; i += stride) g[i] = z;
   }
   __threadfence_system();
 }
@@ -168,24 +184,36 @@ static const char* err_str() {
   return e == cudaSuccess ? nullptr : cudaGetErrorString(e);
 }
 
-const char* nmtg_allreduce_adamw(const NmtgPeerTable* t, float* reduced, float* sq, int* nonfinite, float* master, float* m,
-                                 float* v, const NmtgAdamHyper* hyper_dev, long slice_begin, long slice_len, long total_len,
-                                 int* epoch_dev, int* status, cudaStream_t stream) {
-  if (t->world < 1 || t->world > kMaxRanks) return "allreduce_adamw: world size out of range";
-  if ((slice_begin % 4) || (slice_len % 4) || (total_len % 4)) return "allreduce_adamw: slices must be multiples of 4 elements";
-  cudaMemsetAsync(sq, 0, sizeof(float), stream);
-  cudaMemsetAsync(nonfinite, 0, sizeof(int), stream);
-  long blocks = (slice_len / 4 + 511) / 512;
-  const long cap = static_cast<long>(num_sms()) * 2;
-  if (blocks > cap) blocks = cap;
+const char* nmtg_reduce_unit(const NmtgPeerTable* t, int row, float* reduced, long global_begin, long len, int accumulate,
+                             long zero_begin, long zero_len, int* counter, const int* epoch_dev, int* status, int ctas,
+                             cudaStream_t stream) {
+  if (t->world < 1 || t->world > kMaxRanks) return "reduce_unit: world size out of range";
+  if (row < 3 || row + 1 >= kNmtgFlagRows) return "reduce_unit: flag row out of range";
+  if ((global_begin % 4) || (len % 4) || (zero_begin % 4) || (zero_len % 4) || len < 0)
+    return "reduce_unit: ranges must be multiples of 4 elements";
+  if (reinterpret_cast<uintptr_t>(reduced) & 15) return "reduce_unit: unaligned output";
+  if (zero_len > 0 && !counter) return "reduce_unit: clearing the unit needs the launch counter";
+  long blocks = (len / 4 + 255) / 256;
+  if (ctas < 1) ctas = 48;
+  if (blocks > ctas) blocks = ctas;
   if (blocks < 1) blocks = 1;
-  reduce_slice_kernel<<<static_cast<int>(blocks), 512, 0, stream>>>(*t, reduced, sq, nonfinite, slice_begin, slice_len, epoch_dev, status);
-  const char* e = err_str();
-  if (e) return e;
-  update_slice_kernel<<<num_sms() * 2, 512, 0, stream>>>(*t, reduced, master, m, v, hyper_dev, sq, nonfinite, slice_begin, slice_len,
-                                                         total_len, epoch_dev, status);
-  if ((e = err_str())) return e;
-  finish_step_kernel<<<1, 32, 0, stream>>>(*t, epoch_dev, status);
+  reduce_unit_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(*t, row, reduced, global_begin, len, accumulate, zero_begin,
+                                                                  zero_len, counter, epoch_dev, status);
+  return err_str();
+}
+
+const char* nmtg_update_pieces(const NmtgPeerTable* t, const NmtgPieces* pieces, const float* reduced, float* master, float* m,
+                               float* v, const NmtgAdamHyper* hyper_dev, const float* sq, const int* nonfinite, int mode,
+                               long zero_len, const int* epoch_dev, int* status, cudaStream_t stream) {
+  if (t->world < 1 || t->world > kMaxRanks) return "update_pieces: world size out of range";
+  if (pieces->n < 1 || pieces->n > kNmtgMaxUnits) return "update_pieces: too many units";
+  if (mode != 0 && mode != 1) return "update_pieces: unknown mode";
+  for (int u = 0; u < pieces->n; ++u)
+    if ((pieces->len[u] % 4) || (pieces->global_begin[u] % 4) || (pieces->shard_off[u] % 4))
+      return "update_pieces: pieces must be multiples of 4 elements";
+  if (zero_len % 4) return "update_pieces: lengths must be multiples of 4 elements";
+  update_pieces_kernel<<<num_sms() * 2, 512, 0, stream>>>(*t, *pieces, reduced, master, m, v, hyper_dev, sq, nonfinite, mode,
+                                                         zero_len, epoch_dev, status);
   return err_str();
 }
 

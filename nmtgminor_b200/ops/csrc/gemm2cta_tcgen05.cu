@@ -73,7 +73,7 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar_cluster_addr) {
 template <int BN, bool kTrace, uint32_t kFeat>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                 const __grid_constant__ CUtensorMap tmap_out, const GemmArgs p) {
+                 const __grid_constant__ CUtensorMap tmap_out, const GemmArgs p, const GatherArgs g) {
   using S = PairSmem<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -154,10 +154,35 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       bool ok = true;
       long cursor = first_work;
       int mn, kb_begin, kb_end;
+      // Sharded B operand: segments of the matrix that are known to have arrived in the local staging buffer
+      // (K-major B: segment = BN / 2 rows, i.e. one CTA's half tile; MN-major B: segment = one 64-row k-block).
+      uint32_t seg_seen[kGatherMaxSegs / 32] = {};
+      auto seg_ready = [&](int sgm) -> bool {
+        if (g.n_seg == 0 || sgm >= g.n_seg || ((seg_seen[sgm >> 5] >> (sgm & 31)) & 1u)) return true;
+        const long left = g.units - static_cast<long>(sgm) * g.seg_units;
+        const int need = left < g.seg_units ? static_cast<int>(left) : g.seg_units;
+        const int* ctr = g.counters + 2 + sgm;
+        for (uint32_t i = 0; i < B200_WAIT_POLLS; ++i) {
+          if (ld_acquire_gpu(ctr) >= need) {
+            fence_proxy_async_all();     // the copies were ordinary stores; the loads below go through the async proxy
+            seg_seen[sgm >> 5] |= 1u << (sgm & 31);
+            return true;
+          }
+          if (i > 16) {
+            if (*abort_word) return false;
+            __nanosleep(i > 4096 ? 256 : 32);
+          }
+        }
+        *abort_word = 1;
+        if (p.status) atomicCAS(p.status, 0, kTimeoutGather);
+        return false;
+      };
       while (ok && next_work(cursor, mn, kb_begin, kb_end)) {
         const int m0 = (mn % num_m) * (2 * BM) + static_cast<int>(rank) * BM;   // my 128 rows of the pair tile
         const int n0 = (mn / num_m) * BN + static_cast<int>(rank) * (BN / 2);   // my half of the B tile
+        if (!p.b_mn_major && !seg_ready(n0 / (BN / 2))) { ok = false; break; }
         for (int kb = kb_begin; kb < kb_end; ++kb) {
+          if (p.b_mn_major && !seg_ready(kb)) { ok = false; break; }
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_word, p.status, kTimeoutSmemEmpty)) { ok = false; break; }
           uint8_t* sa = smem + stage * S::kStageBytes;
           uint8_t* sb = sa + S::kABytes;
@@ -242,6 +267,39 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     }
   } else {
     // ------------------------------- epilogue (8 warps, both CTAs) ---------------------------
+    if (g.n_seg > 0) {
+      // ---- gather of the sharded B operand: these warps have nothing to do until the first accumulator is complete.
+      // The matrix is a run of 4 KB blocks.  The CTAs that are running claim four consecutive blocks at a time from a
+      // shared cursor (so a CTA that has not been scheduled yet holds nobody up and the segments complete in order);
+      // each thread moves 16 bytes of every claimed block (four peer loads in flight), then the blocks' segment
+      // counters are raised.  Element e of the unit lives in rank e / piece_len's shard; a 16-byte group never
+      // straddles two owners (pieces are multiples of 64 elements).
+      __shared__ int s_claim;
+      const int t = threadIdx.x - 64;
+      for (;;) {
+        if (t == 0) s_claim = atomicAdd(g.counters + 1, 4);
+        asm volatile("bar.sync 1, %0;" ::"n"(32 * kEpilogueWarps) : "memory");
+        const long u0 = s_claim;
+        if (u0 >= g.units) break;
+        uint4 v[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          if (u0 + j < g.units) {
+            const long e = g.unit_off + (u0 + j) * (kGatherBlockBytes / 2) + t * 8;
+            const int owner = static_cast<int>(e / g.piece_len);
+            const long within = e - owner * g.piece_len;
+            v[j] = *reinterpret_cast<const uint4*>(g.shards[owner] + g.shard_off + within);
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (u0 + j < g.units) *reinterpret_cast<uint4*>(g.dst + (u0 + j) * (kGatherBlockBytes / 2) + t * 8) = v[j];
+        fence_proxy_async_all();
+        __threadfence();
+        asm volatile("bar.sync 1, %0;" ::"n"(32 * kEpilogueWarps) : "memory");
+        if (t < 4 && u0 + t < g.units) atomicAdd(g.counters + 2 + static_cast<int>((u0 + t) / g.seg_units), 1);
+      }
+    }
     const int q = warp & 3;
     const int chunk_par = (warp - 2) >> 2;
     const bool do_drop = p.dropout_p > 0.f;
@@ -349,18 +407,29 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     tc_fence_after_sync();
     asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * BN) : "memory");
   }
+  if (g.n_seg > 0 && threadIdx.x == 0) {
+    // the last CTA to leave puts the counters back to zero for the next launch that uses them (every CTA has
+    // finished its tiles by now, so nobody polls them any more)
+    __threadfence();
+    if (atomicAdd(g.counters, 1) == static_cast<int>(gridDim.x) - 1) {
+      for (int i = 0; i < g.n_seg; ++i) g.counters[2 + i] = 0;
+      g.counters[0] = 0;
+      g.counters[1] = 0;
+      __threadfence();
+    }
+  }
 }
 
 template <int BN, bool kTrace, uint32_t kFeat>
 static const char* launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmArgs& args, int grid,
-                               cudaStream_t stream) {
+                               cudaStream_t stream, const GatherArgs& g) {
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel<BN, kTrace, kFeat>, cudaFuncAttributeMaxDynamicSharedMemorySize, PairSmem<BN>::kTotal);
     if (e != cudaSuccess) return cudaGetErrorString(e);
     configured = true;
   }
-  gemm_pair_kernel<BN, kTrace, kFeat><<<grid, kPairThreads, PairSmem<BN>::kTotal, stream>>>(ta, tb, tc, args);
+  gemm_pair_kernel<BN, kTrace, kFeat><<<grid, kPairThreads, PairSmem<BN>::kTotal, stream>>>(ta, tb, tc, args, g);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? nullptr : cudaGetErrorString(e);
 }
@@ -369,7 +438,61 @@ static const char* launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, con
 int g_pair_generic_epilogue = 0;   // gemm variant 31: always run the general epilogue (30 = specialised, default)
 int g_pair_tma_store = 1;     // set to 0 (gemm variant 20) to force per-thread global stores, for A/B measurements
 
+// True when the CTA-pair kernel can gather this B operand itself (see GatherArgs); fills `g`.
+bool plan_pair_gather(const GemmDesc* d, int bn, GatherArgs* g) {
+  *g = GatherArgs{};
+  const NmtgGather* src = d->gather;
+  if (!src) return false;
+  const long row_len = d->b_mn_major ? d->N : d->K;          // contiguous matrix: ldb == row length
+  const long rows = d->b_mn_major ? d->K : d->N;
+  if (d->ldb != row_len) return false;
+  const long bytes = rows * row_len * 2;
+  const long seg_rows = d->b_mn_major ? BK : bn / 2;
+  const long seg_bytes = seg_rows * row_len * 2;
+  if (bytes % kGatherBlockBytes || seg_bytes % kGatherBlockBytes) return false;
+  const long n_seg = (rows + seg_rows - 1) / seg_rows;
+  if (n_seg > kGatherMaxSegs || src->world < 1 || src->world > 16 || (src->piece_len % 64) || (src->unit_off % 8) ||
+      (src->shard_off % 8) || !src->counters)
+    return false;
+  g->n_seg = static_cast<int>(n_seg);
+  g->rank = src->rank; g->world = src->world;
+  for (int i = 0; i < src->world; ++i) g->shards[i] = src->shards[i];
+  g->shard_off = src->shard_off; g->piece_len = src->piece_len; g->unit_off = src->unit_off;
+  g->dst = reinterpret_cast<unsigned short*>(const_cast<void*>(d->b));
+  g->units = bytes / kGatherBlockBytes;
+  g->seg_units = static_cast<int>(seg_bytes / kGatherBlockBytes);
+  g->counters = src->counters;
+  return true;
+}
+
+// Stand-alone copy of a sharded B operand into its staging place, for the GEMM paths that cannot gather in-kernel.
+__global__ void __launch_bounds__(256) gather_copy_kernel(const NmtgGather g, unsigned short* __restrict__ dst, long n8) {
+  for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < n8; i += static_cast<long>(gridDim.x) * blockDim.x) {
+    const long e = g.unit_off + i * 8;
+    const int owner = static_cast<int>(e / g.piece_len);
+    const long within = e - owner * g.piece_len;
+    reinterpret_cast<uint4*>(dst)[i] = *reinterpret_cast<const uint4*>(g.shards[owner] + g.shard_off + within);
+  }
+}
+
+const char* launch_gather_copy(const GemmDesc* d, cudaStream_t stream) {
+  const NmtgGather* g = d->gather;
+  const long row_len = d->b_mn_major ? d->N : d->K, rows = d->b_mn_major ? d->K : d->N;
+  if (d->ldb != row_len) return "gemm: a sharded operand must be contiguous";
+  const long n = rows * row_len;
+  if ((n % 8) || (g->unit_off % 8) || (g->piece_len % 8) || (g->shard_off % 8) || g->world < 1 || g->world > 16)
+    return "gemm: sharded operand offsets must be multiples of 8 elements";
+  long blocks = (n / 8 + 255) / 256;
+  if (blocks > 2L * num_sms()) blocks = 2L * num_sms();
+  gather_copy_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(*g, reinterpret_cast<unsigned short*>(const_cast<void*>(d->b)), n / 8);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? nullptr : cudaGetErrorString(e);
+}
+
 const char* launch_gemm_pair(const GemmDesc* d, const GemmArgs& a, int bn, cudaStream_t stream) {
+  GatherArgs g;
+  if (d->gather && !plan_pair_gather(d, bn, &g)) return "gemm: this sharded operand cannot be gathered inside the kernel";
+  if (!d->gather) g = GatherArgs{};
   CUtensorMap ta, tb;
   bool ok;
   if (!d->a_mn_major) ok = cached_tmap(&ta, d->a, d->M, d->K, d->lda, BM, BK);
@@ -390,8 +513,8 @@ const char* launch_gemm_pair(const GemmDesc* d, const GemmArgs& a, int bn, cudaS
   const long tiles = static_cast<long>((d->M + 2 * BM - 1) / (2 * BM)) * ((d->N + bn - 1) / bn) * a.split_k;
   const int max_clusters = num_sms() / 2;
   const int clusters = a.stream_k ? max_clusters : static_cast<int>(tiles < max_clusters ? tiles : max_clusters);
-  if (bn != 256) return launch_pair<128, false, kEpiAll>(ta, tb, tc, args, clusters * 2, stream);
-  if (args.trace != nullptr) return launch_pair<256, true, kEpiAll>(ta, tb, tc, args, clusters * 2, stream);
+  if (bn != 256) return launch_pair<128, false, kEpiAll>(ta, tb, tc, args, clusters * 2, stream, g);
+  if (args.trace != nullptr) return launch_pair<256, true, kEpiAll>(ta, tb, tc, args, clusters * 2, stream, g);
   // the specialised epilogues of the shapes a training step is made of; anything else takes the general kernel
   constexpr uint32_t kPlain = kEpiBf16;
   constexpr uint32_t kFc1 = kEpiBf16 | kEpiBias | kEpiActFwd | kEpiDrop | kEpiMaskOut;
@@ -403,14 +526,14 @@ const char* launch_gemm_pair(const GemmDesc* d, const GemmArgs& a, int bn, cudaS
   constexpr uint32_t kDgradAct = kEpiBf16 | kEpiActBwd | kEpiDrop;
   const uint32_t need = g_pair_generic_epilogue ? kEpiAll : gemm_epilogue_features(args);
   const int grid = clusters * 2;
-  if ((need & ~kPlain) == 0) return launch_pair<256, false, kPlain>(ta, tb, tc, args, grid, stream);
-  if ((need & ~kAccum) == 0) return launch_pair<256, false, kAccum>(ta, tb, tc, args, grid, stream);
-  if ((need & ~kDgradMask) == 0) return launch_pair<256, false, kDgradMask>(ta, tb, tc, args, grid, stream);
-  if ((need & ~kOutRes) == 0) return launch_pair<256, false, kOutRes>(ta, tb, tc, args, grid, stream);
-  if ((need & ~kFc1) == 0) return launch_pair<256, false, kFc1>(ta, tb, tc, args, grid, stream);
-  if ((need & ~kFc1Preact) == 0) return launch_pair<256, false, kFc1Preact>(ta, tb, tc, args, grid, stream);
-  if ((need & ~kDgradAct) == 0) return launch_pair<256, false, kDgradAct>(ta, tb, tc, args, grid, stream);
-  return launch_pair<256, false, kEpiAll>(ta, tb, tc, args, grid, stream);
+  if ((need & ~kPlain) == 0) return launch_pair<256, false, kPlain>(ta, tb, tc, args, grid, stream, g);
+  if ((need & ~kAccum) == 0) return launch_pair<256, false, kAccum>(ta, tb, tc, args, grid, stream, g);
+  if ((need & ~kDgradMask) == 0) return launch_pair<256, false, kDgradMask>(ta, tb, tc, args, grid, stream, g);
+  if ((need & ~kOutRes) == 0) return launch_pair<256, false, kOutRes>(ta, tb, tc, args, grid, stream, g);
+  if ((need & ~kFc1) == 0) return launch_pair<256, false, kFc1>(ta, tb, tc, args, grid, stream, g);
+  if ((need & ~kFc1Preact) == 0) return launch_pair<256, false, kFc1Preact>(ta, tb, tc, args, grid, stream, g);
+  if ((need & ~kDgradAct) == 0) return launch_pair<256, false, kDgradAct>(ta, tb, tc, args, grid, stream, g);
+  return launch_pair<256, false, kEpiAll>(ta, tb, tc, args, grid, stream, g);
 }
 
 }  // namespace b200

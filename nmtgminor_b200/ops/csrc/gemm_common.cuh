@@ -40,6 +40,23 @@ struct GemmArgs {
   long long* trace;        // profiling aid: when set, the CTA-pair kernel writes up to 16 cycle counters per cluster (see gemm2cta_tcgen05.cu)
 };
 
+// In-kernel gather of the B operand (fully sharded parameters), CTA-pair kernel.  The matrix is `units` blocks of
+// 4 KB, claimed four at a time through the cursor counters[1]; block u belongs to segment u / seg_units, and the TMA
+// producer loads tiles of a segment only after counters[2 + segment] has reached the segment's block count.
+// n_seg == 0: no gather.
+constexpr int kGatherBlockBytes = 4096;
+constexpr int kGatherMaxSegs = 128;
+struct GatherArgs {
+  int n_seg;
+  int rank, world;
+  const unsigned short* shards[16];
+  long shard_off, piece_len, unit_off;
+  unsigned short* dst;      // local staging address of the matrix
+  long units;               // 4 KB blocks in the matrix
+  int seg_units;            // blocks per segment (the last segment may have fewer)
+  int* counters;            // [0]: CTAs that have left the kernel, [1]: next unclaimed block, [2 + s]: finished blocks of segment s
+};
+
 __device__ __forceinline__ float gelu_f(float x) { return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f)); }
 __device__ __forceinline__ float gelu_grad(float x) {
   float cdf = 0.5f * (1.0f + erff(x * 0.70710678118654752f));

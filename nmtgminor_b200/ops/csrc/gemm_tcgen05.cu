@@ -235,19 +235,25 @@ static EncodeTiledFn get_encode_fn() {
 
 // 2-D bf16 row-major tensor [rows, cols] with leading dimension ld (elements); box = [box_rows, box_cols].
 static bool make_tmap_2d(CUtensorMap* out, const void* base, long rows, long cols, long ld, int box_rows, int box_cols,
-                         bool f32);
+                         bool f32, bool bind_context = true);
 bool make_tmap_bf16_2d(CUtensorMap* out, const void* base, long rows, long cols, long ld, int box_rows,
                        int box_cols) {
   return make_tmap_2d(out, base, rows, cols, ld, box_rows, box_cols, false);
 }
-static bool make_tmap_2d(CUtensorMap* out, const void* base, long rows, long cols, long ld, int box_rows, int box_cols,
+// Descriptor built straight into `out`: no cache, no lock, and no runtime call of its own.  The calling thread must
+// already have a current context (cudaSetDevice binds the primary one).
+bool make_tmap_2d_nobind(CUtensorMap* out, const void* base, long rows, long cols, long ld, int box_rows, int box_cols,
                          bool f32) {
+  return make_tmap_2d(out, base, rows, cols, ld, box_rows, box_cols, f32, false);
+}
+static bool make_tmap_2d(CUtensorMap* out, const void* base, long rows, long cols, long ld, int box_rows, int box_cols,
+                         bool f32, bool bind_context) {
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) return false;
   // The encoder is a driver entry point and needs a current context.  A thread that has issued no runtime call yet
   // (autograd's backward thread when the first thing it does is build a descriptor) has none: bind the primary one.
   static thread_local bool context_bound = false;
-  if (!context_bound) {
+  if (bind_context && !context_bound) {
     cudaFree(nullptr);
     context_bound = true;
   }
@@ -351,10 +357,13 @@ static const char* launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, con
 
 namespace b200 {
 const char* launch_gemm_pair(const GemmDesc* d, const GemmArgs& a, int bn, cudaStream_t stream);
+const char* launch_gather_copy(const GemmDesc* d, cudaStream_t stream);
+bool plan_pair_gather(const GemmDesc* d, int bn, GatherArgs* g);
 }
 using namespace b200;
 
 static int g_gemm_variant = 0;   // 0 = automatic, 1 = single-CTA kernel only, 2 = CTA-pair kernel whenever M > 128
+static int g_fused_gather = 1;   // 0 (variant 50): sharded operands are always copied by a launch of their own (A/B baseline)
 static long long* g_gemm_trace = nullptr;   // see nmtg_set_gemm_trace
 static int g_stream_k = 1;       // gemm variant 40 switches the equal-run work split of weight gradients off, 41 on
 static int g_gemm_ablate = 0;    // profiling aid, see GemmArgs::ablate; variants 10 / 11 / 12 select ablation 0 / 1 / 2
@@ -365,7 +374,8 @@ extern int g_pair_generic_epilogue;
 void nmtg_set_gemm_trace(long long* buf) { g_gemm_trace = buf; }
 
 void nmtg_set_gemm_variant(int v) {
-  if (v == 40 || v == 41) g_stream_k = v - 40;
+  if (v == 50 || v == 51) g_fused_gather = v - 50;
+  else if (v == 40 || v == 41) g_stream_k = v - 40;
   else if (v == 30 || v == 31) b200::g_pair_generic_epilogue = v - 30;
   else if (v == 20 || v == 21) b200::g_pair_tma_store = v - 20;   // 20: per-thread stores, 21: TMA-store epilogue (default)
   else if (v >= 10) g_gemm_ablate = v - 10;
@@ -398,6 +408,16 @@ const char* nmtg_gemm_bf16(const GemmDesc* d, cudaStream_t stream) {
   a.act = d->act; a.dropout_p = d->dropout_p; a.seed = d->seed; a.stream_id = d->stream_id; a.seed_dev = d->seed_dev;
   a.status = d->status;
 
+  // A sharded B operand (d->gather) is pulled in by the CTA-pair kernel itself; every other path copies it first.
+  GemmDesc unfused;
+  auto gather_first = [&]() -> const char* {
+    const char* e = launch_gather_copy(d, stream);
+    if (e) return e;
+    unfused = *d;
+    unfused.gather = nullptr;
+    d = &unfused;
+    return nullptr;
+  };
   const int sms = num_sms();
   const int num_kb = (d->K + BK - 1) / BK;
   auto fix_split = [&](int split) {   // largest split <= requested whose last part is not empty
@@ -410,6 +430,7 @@ const char* nmtg_gemm_bf16(const GemmDesc* d, cudaStream_t stream) {
   // down to 64 columns
   const bool skinny = g_gemm_variant == 0 && d->M <= 512 && !d->out_fp32 && d->force_bn == 0 && d->split_k <= 1 && !d->colsum;
   if (skinny) {
+    if (d->gather) { const char* e = gather_first(); if (e) return e; }
     const int num_m = (d->M + BM - 1) / BM;
     int bn = 64;
     if (static_cast<long>(num_m) * ((d->N + 255) / 256) >= sms) bn = 256;
@@ -448,6 +469,10 @@ const char* nmtg_gemm_bf16(const GemmDesc* d, cudaStream_t stream) {
   if ((g_gemm_variant != 1 || d->colsum) && d->M > BM) {
     int bn = (d->N > 128) ? 256 : 128;
     if (d->force_bn == 128 || d->force_bn == 256) bn = d->force_bn;
+    if (d->gather) {
+      GatherArgs probe;
+      if (g_fused_gather == 0 || !plan_pair_gather(d, bn, &probe)) { const char* e = gather_first(); if (e) return e; }
+    }
     const long tiles = static_cast<long>((d->M + 2 * BM - 1) / (2 * BM)) * ((d->N + bn - 1) / bn);
     int split = 1;
     if (d->split_k > 0) split = d->split_k;
@@ -472,6 +497,7 @@ const char* nmtg_gemm_bf16(const GemmDesc* d, cudaStream_t stream) {
     return launch_gemm_pair(d, a, bn, stream);
   }
   // ---- single-CTA kernel: tile width 256 when it does not waste a wave, else 128 -------------------
+  if (d->gather) { const char* e = gather_first(); if (e) return e; }
   const int num_m = (d->M + BM - 1) / BM;
   int bn = 256;
   if (d->N <= 128 || ((d->N % 256) != 0 && (d->N % 128) == 0)) bn = 128;

@@ -15,6 +15,18 @@ enum NmtgAct : int {
   kActMaskBwd = 8,  // out = acc * bit(mask)              (mask = sign bits written by a forward epilogue)
 };
 
+// Where the pieces of a sharded B operand live (fully sharded parameters).  The unit that contains the matrix is
+// cut into `world` pieces of `piece_len` elements; rank p keeps its piece at shards[p] + shard_off.  The matrix starts
+// `unit_off` elements into the unit and must be contiguous (ldb equal to its row length); `GemmDesc::b` is its place
+// in the local staging buffer.  The CTA-pair kernel pulls the pieces itself (idle epilogue warps, peer loads) and
+// its TMA producer waits for per-segment completion counters; other paths run a copy launch first.
+struct NmtgGather {
+  int rank, world;
+  const unsigned short* shards[16];
+  long shard_off, piece_len, unit_off;
+  int* counters;     // device ints, [2 + 128], all zero; the kernel that used them leaves them zero
+};
+
 struct GemmDesc {
   // C[M,N] = epilogue(alpha * sum_k A(m,k) B(n,k)).  K-major operand: row index = M/N, leading dimension
   // ld over K.  MN-major operand (x_mn_major = 1): stored [K, M/N] with ld over M/N.
@@ -41,6 +53,7 @@ struct GemmDesc {
   int allow_split_k;
   int force_bn;           // 0 = automatic, 128 or 256
   int* status;            // device int, 0 = ok
+  const NmtgGather* gather;  // optional: B is gathered from its owners by this call (see NmtgGather)
 };
 
 const char* nmtg_gemm_bf16(const GemmDesc* d, cudaStream_t stream);
@@ -133,43 +146,52 @@ const char* nmtg_attn_bwd(const AttnDesc* d, cudaStream_t stream);
 // 0 = choose automatically (persistent single-tile kernels when max_q, max_k <= 128), 1 = general kernels only
 void nmtg_set_attention_variant(int v);
 
-// ---- peer-memory data parallelism ------------------------------------------------------------------------
+// ---- peer-memory data parallelism and fully sharded parameters ---------------------------------------------
 // Pointers of every rank's symmetric buffers as seen from THIS process (own buffers: local pointers; peers:
-// pointers obtained by opening their IPC handles).  flags[r]: int [3][16] epochs, partials[r]: float [2][16].
+// pointers obtained by opening their IPC handles).  flags[r]: int [kNmtgFlagRows][16] epochs, partials[r]:
+// float [2][16].
+constexpr int kNmtgFlagRows = 256;
+constexpr int kNmtgMaxUnits = 96;
 struct NmtgPeerTable {
   int rank, world;
-  float* grads[16];
-  unsigned short* works[16];   // bf16 parameter copies
+  float* grads[16];            // fp32 gradient space of every rank
+  unsigned short* works[16];   // bf16 parameters: full copies (data parallel) or shards (fully sharded)
   int* flags[16];
   float* partials[16];
   float* norm_out;             // optional local float: global gradient norm of the step (-1 when skipped)
+  long long timeout_ns;        // wall-time bound of every cross-GPU wait
 };
-// reduce-scatter of slice [slice_begin, slice_begin + slice_len) + Adam(W) on it + all-gather of the bf16
-// parameters + clearing of the local gradient buffer; reduced / sq / nonfinite are local scratch buffers.
-// *epoch_dev (device int, starts at 1) is the barrier epoch; the last kernel of the step advances it.
-const char* nmtg_allreduce_adamw(const NmtgPeerTable* t, float* reduced, float* sq, int* nonfinite, float* master, float* m,
-                                 float* v, const NmtgAdamHyper* hyper_dev, long slice_begin, long slice_len, long total_len,
-                                 int* epoch_dev, int* status, cudaStream_t stream);
-// the closing barrier of a step (row 2) + epoch advance, shared by the data-parallel and the fully sharded step
-const char* nmtg_peer_finish_step(const NmtgPeerTable* t, int* epoch_dev, int* status, cudaStream_t stream);
-
-// ---- fully sharded data parallelism ----------------------------------------------------------------------------
-// Unit u of the flat parameter space is cut into `world` pieces; this rank's piece is `len[u]` elements at
-// `global_begin[u]` of the flat space and at `shard_off[u]` of the shard-ordered buffers (bf16 parameters in
-// works[rank], fp32 master / moments / reduced gradients).
-constexpr int kFsdpMaxUnits = 96;
-struct NmtgFsdpPieces {
+// The flat parameter space is cut into UNITS (one per Transformer layer, the rest merged); unit u is cut into
+// `world` equal pieces and this rank owns piece `rank` of every unit: `len[u]` elements at `global_begin[u]` of the
+// gradient space and at `shard_off[u]` of the shard-ordered buffers (reduced gradients, Adam moments, and - fully
+// sharded mode - fp32 master weights and bf16 parameters).
+struct NmtgPieces {
   int n;
-  long shard_off[kFsdpMaxUnits];
-  long global_begin[kFsdpMaxUnits];
-  long len[kFsdpMaxUnits];
+  long shard_off[kNmtgMaxUnits];
+  long global_begin[kNmtgMaxUnits];   // offset in the gradient space (every rank's buffer has the same layout); in
+                                      // data-parallel mode this is also the offset in the flat parameter space
+  long len[kNmtgMaxUnits];
 };
-// dst[0:unit_len] (bf16) <- the unit's pieces pulled from every rank's shard (works[p] + shard_off, piece_len each)
-const char* nmtg_fsdp_gather(const NmtgPeerTable* t, void* dst, long shard_off, long piece_len, long unit_len, int ctas,
+// Reduce-scatter of ONE unit: waits (bounded) on flag row `row` until every peer has published "gradients of this
+// unit are complete", then sums this rank's piece over all ranks' gradient buffers with peer loads into
+// reduced[0:len) (added to the old contents when accumulate != 0).  With zero_len > 0 the kernel then waits on row
+// `row + 1` until every peer has finished reading and clears its OWN gradients [zero_begin, zero_begin + zero_len)
+// (rotating per-layer gradient buffers).  `counter` is one device int per launch site, zero between launches.
+const char* nmtg_reduce_unit(const NmtgPeerTable* t, int row, float* reduced, long global_begin, long len, int accumulate,
+                             long zero_begin, long zero_len, int* counter, const int* epoch_dev, int* status, int ctas,
                              cudaStream_t stream);
-// reduce-scatter of the full gradient buffers into shard order + Adam(W) on the shard + closing barrier
-const char* nmtg_fsdp_step(const NmtgPeerTable* t, const NmtgFsdpPieces* pieces, float* reduced, float* sq, int* nonfinite,
-                           float* master, float* m, float* v, const NmtgAdamHyper* hyper_dev, long shard_len, long total_len,
-                           int* epoch_dev, int* status, cudaStream_t stream);
+// After all units are reduced: exchange of the squared-norm partials (flag row 1), clipping coefficient, Adam(W)
+// on every owned piece, refreshed bf16 parameters.  mode 0 (data parallel): master weights are indexed in the flat
+// space and the bf16 values are stored into EVERY rank's full copy (the all-gather); mode 1 (fully sharded): master
+// weights and bf16 parameters are shard-ordered and local.  zero_len > 0 clears the local gradient space
+// [0, zero_len) afterwards (every peer has passed row 1, i.e. finished reading it).
+const char* nmtg_update_pieces(const NmtgPeerTable* t, const NmtgPieces* pieces, const float* reduced, float* master, float* m,
+                               float* v, const NmtgAdamHyper* hyper_dev, const float* sq, const int* nonfinite, int mode,
+                               long zero_len, const int* epoch_dev, int* status, cudaStream_t stream);
+// the closing barrier of a step (row 2) + epoch advance
+const char* nmtg_peer_finish_step(const NmtgPeerTable* t, int* epoch_dev, int* status, cudaStream_t stream);
+// dst[e0:e1) of a unit (bf16) <- pulled from the owners' shards (works[p] + shard_off, piece_len elements each)
+const char* nmtg_fsdp_gather(const NmtgPeerTable* t, void* dst, long shard_off, long piece_len, long e0, long e1, int ctas,
+                             cudaStream_t stream);
 // waits (bounded) on one flag row; used to exercise the timeout path
 const char* nmtg_peer_wait_row(const NmtgPeerTable* t, int row, int epoch, int* status, cudaStream_t stream);

@@ -22,6 +22,8 @@ EXTRA_TRAIN_FLAGS = [
     ("fused_ddp", "flag", False, {}),            # peer-memory all-reduce fused with the optimiser step
     ("nccl_ddp", "flag", False, {}),             # baseline switch: NCCL all-reduce of the flat gradient buffer
     ("watchdog_timeout", "float", 0.0, {}),      # seconds without a heartbeat before a rank is declared dead
+    ("peer_timeout", "float", 0.0, {}),          # milliseconds a kernel waits for a peer GPU before giving up (0: 120 s)
+    ("no_cuda_graph", "flag", False, {}),        # run the training step kernel by kernel instead of replaying a graph
     ("trace_nvtx", "flag", False, {}),           # NVTX ranges around layers / buckets
     ("generator_chunk_rows", "int", 0, {}),      # output projection + loss this many rows at a time (logits stay in L2)
     ("fused_conv", "flag", False, {}),

@@ -68,7 +68,8 @@ class FlatParameterStore:
             with torch.no_grad():
                 view.copy_(p.data.to(self.device, torch.float32))
             p.data = view
-            p.main_grad = self.grad[o:o + n].view(p.shape)
+            if self.grad is not None:
+                p.main_grad = self.grad[o:o + n].view(p.shape)
             if self.work is not None:
                 p.work = self.work[o:o + n].view(p.shape)
         # buffers that enter the fused kernels as bf16 operands get a working copy too
@@ -88,7 +89,13 @@ class FlatParameterStore:
             self.work.copy_(self.master)
 
     def zero_grad(self) -> None:
-        self.grad.zero_()
+        if self.grad is not None:
+            self.grad.zero_()
+        else:     # gradients live in buffers owned by the fully sharded step
+            for p in self.params:
+                g = getattr(p, "main_grad", None)
+                if g is not None:
+                    g.zero_()
 
     def gather_autograd_grads(self) -> None:
         """Add ``p.grad`` tensors (from unfused / CPU ops) into the flat gradient buffer and drop them."""
@@ -98,6 +105,8 @@ class FlatParameterStore:
                 p.grad = None
 
     def zero_frozen_grads(self) -> None:
+        if self.grad is None:
+            return
         for o, n in self.frozen_ranges:
             self.grad[o:o + n].zero_()
 

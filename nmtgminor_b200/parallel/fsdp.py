@@ -1,161 +1,191 @@
 """Fully sharded data parallelism (``-fsdp``) over peer-mapped memory on one NVSwitch node.
 
-Parameters are grouped into UNITS: every module of ``model.encoder.layers`` / ``model.decoder.layers`` is one unit,
-everything else (embeddings, final norms, output projection) forms the resident unit.  Rank r keeps piece r of every
-unit: bf16 parameters (in the symmetric heap, where peers read them), fp32 master weights and Adam moments.  Full
-bf16 weights of a layer exist only while the layer needs them, in one of two staging buffers:
+Units and pieces are those of ``sharded.UnitShardedStep``: every encoder / decoder layer is a unit, everything else
+(embeddings, final norms, output projection) forms resident units, and rank r keeps piece r of every unit.  What a
+rank holds between steps is, per parameter, 1/N of: the bf16 value (in the symmetric heap, where peers read it), the
+fp32 master weight, the two Adam moments and the reduced fp32 gradient - 18/N bytes.  Nothing of full size survives
+a step except the buffers below:
 
-* forward: a pre-forward hook on layer i makes the compute stream wait for the gather of unit i and enqueues the
-  gather of unit i + 1 into the other buffer on a side stream, so the peer loads overlap layer i's GEMMs;
-* backward: a pre-backward hook does the same in reverse order (the weights are gathered again rather than kept);
-* after backward one launch sequence reduce-scatters the gradients straight into shard order, applies Adam(W) to the
-  shard and refreshes the bf16 shard that the next step's gathers read (``ops.ext().fsdp_step``).
+* **parameter staging**: two rotating buffers, each as large as the largest layer, plus one buffer per resident
+  unit.  A layer's weight MATRICES are pulled from their owners by the GEMM that consumes them: the kernel
+  (``csrc/gemm2cta_tcgen05.cu``) is told where every piece of the matrix lives, its otherwise idle epilogue warps
+  copy the pieces with peer loads into the staging buffer in the order the tiles need them, and its TMA producer
+  waits for a segment's completion counter before it loads tiles from that segment - gather and matrix product
+  are one launch, the transfer hidden under the tiles already in flight.  Forward uses the weight as a K-major
+  operand (``x W^T``), backward as an MN-major one (``dy W``); both gather.  The small parameters of a layer
+  (biases, LayerNorm) arrive through one stand-alone copy launch when the layer is entered.  ``fused_gather=False``
+  (or ``NMTG_FSDP_FUSED_GATHER=0``) moves everything through the copy kernel one layer ahead on a side stream, the
+  unfused baseline.
+* **gradient staging**: three rotating fp32 buffers of layer size plus one per resident unit, all in the symmetric
+  heap.  When the backward pass leaves a layer, that unit's ``reduce_unit`` launch (communication stream, overlapped
+  with the layers below) reduce-scatters the buffer into the owned piece of ``reduced``, tells the peers that it has
+  finished reading, and clears the buffer once all peers have; the layer three positions further down then reuses it.
+* the fp32 master weights that back ``param.data`` are released after the shards are cut (``param.data`` becomes a
+  stride-0 view of a NaN scalar, so an op that bypasses the fused path is noticed immediately) and are
+  re-materialised by ``gather_master`` only while a checkpoint is written.
 
-The gather kernels need no flags (shards only change inside the step barrier); every cross-GPU wait is bounded and
-reports through the status word.  The fp32 master copy that backs ``param.data`` stays full-size on every rank for
-checkpointing and is refreshed by ``gather_master``; gradients are accumulated full-size and reduced once per step.
+The gather kernels need no flags (shards only change inside ``update_pieces``, which every rank enters after the
+step's last gather, and the step ends with a barrier); every cross-GPU wait is bounded and reports through the
+status word.
 
-Reference behaviour: FSDP wrapping of the encoder / decoder layers, onmt/train_utils/mp_trainer.py:330-350.
+Reference behaviour: FSDP wrapping of the encoder / decoder layers, onmt/train_utils/mp_trainer.py:314-341, and
+whisper/train_whisper.py:597-600.
 """
 from __future__ import annotations
 
+import os
 from typing import List, Optional
 
 import torch
 import torch.distributed as dist
 
 from .. import ops
-from .symmetric import FLAG_INTS, PARTIAL_FLOATS, SymmetricHeap
+from .sharded import Unit, UnitShardedStep, _round_up, plan_units
+from .symmetric import SymmetricHeap
+
+GRAD_SLOTS = 3
+MIN_FUSED_ELEMS = 1 << 16     # smaller matrices travel with the layer's small parameters
 
 
-def _round_up(x: int, m: int) -> int:
-    return (x + m - 1) // m * m
+class GatherInfo:
+    """Where the pieces of one weight matrix live; attached to the parameter as ``_fsdp`` and handed to the GEMM."""
+
+    __slots__ = ("owner", "unit", "offset", "numel", "valid_key", "used")
+
+    def __init__(self, owner, unit: Unit, offset: int, numel: int):
+        self.owner, self.unit, self.offset, self.numel = owner, unit, offset, numel
+        self.valid_key = None     # (slot occupancy stamp) for which the staging copy is current
+        self.used = False         # some GEMM asked for this matrix during the first step
+
+    def pending(self):
+        """Gather arguments if the staging copy of this matrix is stale, else None (marks it current)."""
+        return self.owner._claim(self)
 
 
-class Unit:
-    def __init__(self, name: str, begin: int, end: int, module=None):
-        self.name, self.begin, self.end, self.module = name, begin, end, module
-        self.piece = 0          # elements per rank (multiple of 8)
-        self.shard_off = 0      # offset of this unit's piece in shard-ordered buffers
-        self.slot = -1          # staging buffer (0 / 1) or -1 for the resident unit
+class FullyShardedAdam(UnitShardedStep):
+    """Sharded parameters + gradients + optimiser state with gather-on-demand staging; plugs into
+    ``Optim.attach_distributed``."""
 
-    @property
-    def length(self):
-        return self.end - self.begin
+    mode = 1
 
-
-def plan_units(model, store, world: int) -> List[Unit]:
-    """Contiguous flat ranges: one per encoder / decoder layer, the rest merged into resident units."""
-    index = {id(p): i for i, p in enumerate(store.params)}
-    claimed = {}
-    layer_units = []
-    for stack_name in ("encoder", "decoder"):
-        stack = getattr(model, stack_name, None)
-        layers = getattr(stack, "layers", None)
-        if layers is None:
-            continue
-        for li, layer in enumerate(layers):
-            ids = sorted(index[id(p)] for p in layer.parameters() if id(p) in index and index[id(p)] not in claimed)
-            if not ids or ids != list(range(ids[0], ids[-1] + 1)):
-                continue              # parameters shared with other modules or not contiguous: leave them resident
-            for i in ids:
-                claimed[i] = True
-            begin = store.offsets[ids[0]]
-            end = store.offsets[ids[-1] + 1] if ids[-1] + 1 < len(store.offsets) else store.total
-            layer_units.append(Unit("%s.layers.%d" % (stack_name, li), begin, end, layer))
-    layer_units.sort(key=lambda u: u.begin)
-    units: List[Unit] = []
-    cursor = 0
-    for u in layer_units:
-        if u.begin > cursor:
-            units.append(Unit("resident%d" % len(units), cursor, u.begin))
-        units.append(u)
-        cursor = u.end
-    if cursor < store.total:
-        units.append(Unit("resident%d" % len(units), cursor, store.total))
-    off = 0
-    n_layer = 0
-    for u in units:
-        u.piece = _round_up(-(-u.length // world), 8)
-        u.shard_off = off
-        off += u.piece
-        if u.module is not None:
-            u.slot = n_layer % 2
-            n_layer += 1
-    return units
-
-
-class FullyShardedAdam:
-    """Sharded parameters + optimiser state with gather-on-demand staging; plugs into ``Optim.attach_distributed``."""
-
-    fused_optimizer = True
-
-    def __init__(self, model, store, optim, heap: SymmetricHeap, grad_ptrs, gather_ctas: int = 32):
-        assert store.work is None, "the flat store must be built without a full bf16 copy"
-        self.model, self.store, self.optim, self.heap = model, store, optim, heap
-        self.rank, self.world = heap.rank, heap.world
-        dev = store.master.device
-        self.units = plan_units(model, store, self.world)
-        assert len(self.units) <= 96, "too many units"
-        self.shard_len = sum(u.piece for u in self.units)
+    def __init__(self, model, store, optim, heap: SymmetricHeap, grad_ptrs=None, gather_ctas: int = 32,
+                 fused_gather: Optional[bool] = None, overlap: bool = True):
+        assert store.work is None and store.grad is None, "the flat store must be built without full bf16 / gradient buffers"
+        world = heap.world
+        dev = store.device
+        units = plan_units(model, store, world)
+        layer_units = [u for u in units if u.slot >= 0]
+        # gradient space: [resident units ... | GRAD_SLOTS rotating layer buffers]
+        off = 0
+        for u in units:
+            if u.slot < 0:
+                u.grad_base = off
+                off += _round_up(u.piece * world, 64)
+        self.slot_len = _round_up(max([u.piece * world for u in layer_units], default=64), 64)
+        self.gslot_base = [off + i * self.slot_len for i in range(GRAD_SLOTS)]
+        for i, u in enumerate(reversed(layer_units)):      # backward order
+            u.gslot = i % GRAD_SLOTS
+            u.grad_base = self.gslot_base[u.gslot]
+        self.grad_len = off + GRAD_SLOTS * self.slot_len if layer_units else max(off, 64)
+        self.grad_space, grad_ptrs = heap.alloc(self.grad_len, torch.float32)
+        self.shard_len_ = sum(u.piece for u in units)
+        self.shard, shard_ptrs = heap.alloc(self.shard_len_, torch.bfloat16)
+        self._setup(model, store, optim, heap, grad_ptrs, shard_ptrs, units, overlap=overlap)
+        self.shard_ptrs = shard_ptrs
         self.gather_ctas = gather_ctas
-        # symmetric buffers: bf16 shard (peers read it), flags, norm partials
-        self.shard, self.shard_ptrs = heap.alloc(self.shard_len, torch.bfloat16)
-        self.flags, self.flag_ptrs = heap.alloc(FLAG_INTS, torch.int32)
-        self.partials, self.partial_ptrs = heap.alloc(PARTIAL_FLOATS, torch.float32)
-        self.grad_ptrs = grad_ptrs
-        f32 = dict(dtype=torch.float32, device=dev)
-        self.master_shard = torch.zeros(self.shard_len, **f32)
-        self.exp_avg = torch.zeros(self.shard_len, **f32)
-        self.exp_avg_sq = torch.zeros(self.shard_len, **f32)
-        self.reduced = torch.zeros(self.shard_len, **f32)
-        self.sq = torch.zeros(1, **f32)
-        self.nonfinite = torch.zeros(1, dtype=torch.int32, device=dev)
-        self.norm = torch.zeros(1, **f32)
-        self.epoch = torch.ones(1, dtype=torch.int32, device=dev)
-        # this rank's piece of every unit, in the flat space
-        self.pieces = []
-        for u in self.units:
-            g0 = u.begin + self.rank * u.piece
-            n = max(0, min(u.piece, u.end - g0))
-            n -= n % 4
-            self.pieces.append((u.shard_off, g0, n))
+        if fused_gather is None:
+            fused_gather = os.environ.get("NMTG_FSDP_FUSED_GATHER", "1") != "0"
+        self.fused_gather = bool(fused_gather)
+        self.master_shard = torch.zeros(self.shard_len, dtype=torch.float32, device=dev)
         self._init_shards()
         # staging: two rotating buffers for layer units, one persistent buffer per resident unit
-        layer_units = [u for u in self.units if u.slot >= 0]
-        max_len = max([u.piece * self.world for u in layer_units], default=8)
-        self.staging = [torch.zeros(max_len, dtype=torch.bfloat16, device=dev) for _ in range(2)]
-        self.resident = {u.name: torch.zeros(u.piece * self.world, dtype=torch.bfloat16, device=dev) for u in self.units if u.slot < 0}
-        self._point_work_views()
+        self.staging = [torch.zeros(self.slot_len, dtype=torch.bfloat16, device=dev) for _ in range(2)]
+        self.resident = {u.name: torch.zeros(_round_up(u.piece * world, 64), dtype=torch.bfloat16, device=dev)
+                         for u in units if u.slot < 0}
+        # per staging buffer: completion counters of the in-kernel gathers (cleared by the kernel that used them)
+        self.gather_counters = torch.zeros(2, 4096 + 8, dtype=torch.int32, device=dev)
+        # First step: every layer is copied whole while the GEMM calls that carry a gather record are noted; matrices
+        # that no such call consumed (a layer type that reads its weights some other way) keep travelling with the
+        # layer's small parameters afterwards.
+        self._learning = self.fused_gather
+        self._point_views()
+        self._release_master()
         self.side = torch.cuda.Stream(device=dev)
         self.slot_unit = [None, None]          # which unit each staging buffer holds (or is being filled with)
-        self.slot_ready = [None, None]         # event: gather into the slot finished
-        self._install_hooks(layer_units)
+        self.slot_stamp = [0, 0]               # bumped whenever a buffer changes hands
+        self.slot_ready = [None, None]         # event: stand-alone gather into the slot finished
+        self.gslot_free = [None] * GRAD_SLOTS  # event: the buffer's previous unit has been reduced and cleared
+        self._layer_units = layer_units
+        self._install_gather_hooks(layer_units)
         if self.world > 1:
             dist.barrier()
 
     # -- set-up ------------------------------------------------------------------------------------------
     def _init_shards(self):
-        for (so, g0, n) in self.pieces:
-            if n > 0:
-                self.master_shard[so:so + n].copy_(self.store.master[g0:g0 + n])
+        for (so, p0, _n), u in zip(self.pieces, self.units):
+            full = max(0, min(u.piece, u.end - p0))
+            if full > 0:
+                self.master_shard[so:so + full].copy_(self.store.master[p0:p0 + full])
         self.shard.copy_(self.master_shard)
 
     def _buffer_of(self, u: Unit):
         return self.staging[u.slot] if u.slot >= 0 else self.resident[u.name]
 
-    def _point_work_views(self):
-        store = self.store
-        bounds = [(u.begin, u.end, u) for u in self.units]
-        for p, off in zip(store.params, store.offsets):
-            for b, e, u in bounds:
-                if b <= off < e:
-                    p.work = self._buffer_of(u)[off - b:off - b + p.numel()].view(p.shape)
-                    break
+    def _unit_of(self, off: int) -> Unit:
+        for u in self.units:
+            if u.begin <= off < u.end:
+                return u
+        raise KeyError(off)
 
-    def _install_hooks(self, layer_units: List[Unit]):
+    def _point_views(self):
+        """``param.work`` -> staging buffer, ``param.main_grad`` -> gradient space, matrices get their gather record."""
+        store = self.store
+        for p, off in zip(store.params, store.offsets):
+            u = self._unit_of(off)
+            d = off - u.begin
+            n = p.numel()
+            p.work = self._buffer_of(u)[d:d + n].view(p.shape)
+            p.main_grad = self.grad_space[u.grad_base + d:u.grad_base + d + n].view(p.shape)
+            fused = (self.fused_gather and u.slot >= 0 and p.dim() == 2 and n >= MIN_FUSED_ELEMS and p.shape[1] % 64 == 0
+                     and p.shape[0] % 64 == 0)
+            p._fsdp = GatherInfo(self, u, d, n) if fused else None
+        self._plan_small_ranges()
+
+    def _plan_small_ranges(self):
+        """Per unit: the element ranges that the stand-alone copy brings in (everything without a gather record)."""
+        store = self.store
+        self._small_ranges = {u.name: [] for u in self.units}
+        for p, off in zip(store.params, store.offsets):
+            if getattr(p, "_fsdp", None) is not None:
+                continue
+            u = self._unit_of(off)
+            d = off - u.begin
+            padded = _round_up(p.numel(), 64)
+            r = self._small_ranges[u.name]
+            if r and r[-1][1] == d:
+                r[-1][1] = d + padded
+            else:
+                r.append([d, d + padded])
+        for u in self.units:
+            lim = _round_up(u.length, 8)
+            self._small_ranges[u.name] = [(a, min(b, lim)) for a, b in self._small_ranges[u.name] if a < lim]
+
+    def _release_master(self):
+        """Drop the full fp32 master buffer; parameters keep their shape through a stride-0 view of one NaN."""
+        self._nan = torch.full((1,), float("nan"), dtype=torch.float32, device=self.device)
+        for p in self.store.params:
+            p.data = self._nan.expand(p.shape)
+        self.store.master = None
+
+    def _materialise_master(self):
+        store = self.store
+        if store.master is None:
+            store.master = torch.zeros(store.total, dtype=torch.float32, device=self.device)
+        for p, off in zip(store.params, store.offsets):
+            p.data = store.master[off:off + p.numel()].view(p.shape)
+
+    def _install_gather_hooks(self, layer_units: List[Unit]):
         order = {u.name: i for i, u in enumerate(layer_units)}
-        self._layer_units = layer_units
 
         def fwd_pre(u):
             def hook(_module, _inputs):
@@ -164,7 +194,7 @@ class FullyShardedAdam:
 
         def bwd_pre(u):
             def hook(_module, _grad_out):
-                self._need(u, prefetch=self._neighbour(order[u.name], -1))
+                self._need(u, prefetch=self._neighbour(order[u.name], -1), backward=True)
             return hook
 
         for u in layer_units:
@@ -177,67 +207,131 @@ class FullyShardedAdam:
         return self._layer_units[j] if 0 <= j < len(self._layer_units) else None
 
     # -- gathers -----------------------------------------------------------------------------------------
-    def _launch_gather(self, u: Unit, stream):
+    def _launch_gather(self, u: Unit, ranges, stream):
+        buf = self._buffer_of(u)
         with torch.cuda.stream(stream):
-            ops.ext().fsdp_gather(self.rank, self.shard_ptrs, self._buffer_of(u), u.shard_off, u.piece, min(u.piece * self.world, _round_up(u.length, 8)),
-                                  self.gather_ctas)
-        ops.LAUNCHES[0] += 1
+            for a, b in ranges:
+                ops.ext().fsdp_gather(self.rank, self.shard_ptrs, buf, u.shard_off, u.piece, a, b, self.gather_ctas)
+                ops.LAUNCHES[0] += 1
 
     def begin_step(self):
         """Resident units (embeddings, norms, output projection) are refreshed once per step on the compute stream."""
         for u in self.units:
             if u.slot < 0:
-                self._launch_gather(u, torch.cuda.current_stream())
+                self._launch_gather(u, [(0, _round_up(u.length, 8))], torch.cuda.current_stream())
         self.slot_unit = [None, None]
+        self.slot_stamp = [s + 1 for s in self.slot_stamp]
 
-    def _gather_into_slot(self, u: Unit):
+    def _take_slot(self, u: Unit, stream_for_small):
+        """Staging buffer ``u.slot`` changes hands: small parameters (or, unfused, everything) are copied in."""
         cur = torch.cuda.current_stream()
-        # everything already enqueued on the compute stream may still read the slot's previous contents
-        self.side.wait_stream(cur)
-        self._launch_gather(u, self.side)
-        ev = torch.cuda.Event()
-        ev.record(self.side)
-        self.slot_unit[u.slot], self.slot_ready[u.slot] = u.name, ev
+        self.slot_unit[u.slot] = u.name
+        self.slot_stamp[u.slot] += 1
+        if self.fused_gather:
+            # matrices arrive inside their GEMMs (compute stream, naturally ordered behind the slot's previous readers)
+            ranges = [(0, _round_up(u.length, 8))] if self._learning else self._small_ranges[u.name]
+            self._launch_gather(u, ranges, cur)
+            self.slot_ready[u.slot] = None
+        else:
+            self.side.wait_stream(cur)        # everything already enqueued may still read the slot's previous contents
+            self._launch_gather(u, [(0, _round_up(u.length, 8))], self.side)
+            ev = torch.cuda.Event()
+            ev.record(self.side)
+            self.slot_ready[u.slot] = ev
 
-    def _need(self, u: Unit, prefetch: Optional[Unit] = None):
+    def _need(self, u: Unit, prefetch: Optional[Unit] = None, backward: bool = False):
         if self.slot_unit[u.slot] != u.name:
-            self._gather_into_slot(u)
-        torch.cuda.current_stream().wait_event(self.slot_ready[u.slot])
-        if prefetch is not None and self.slot_unit[prefetch.slot] != prefetch.name and prefetch.slot != u.slot:
-            self._gather_into_slot(prefetch)
+            self._take_slot(u, None)
+        if self.slot_ready[u.slot] is not None:
+            torch.cuda.current_stream().wait_event(self.slot_ready[u.slot])
+        if backward and u.gslot >= 0 and self.gslot_free[u.gslot] is not None:
+            # the rotating gradient buffer must have been reduced and cleared by its previous user
+            torch.cuda.current_stream().wait_event(self.gslot_free[u.gslot])
+            self.gslot_free[u.gslot] = None
+        if (not self.fused_gather and prefetch is not None and self.slot_unit[prefetch.slot] != prefetch.name
+                and prefetch.slot != u.slot):
+            self._take_slot(prefetch, None)
 
-    # -- optimiser interface -------------------------------------------------------------------------------
-    def __call__(self, flat_grad):
-        return None
+    def _claim(self, info: GatherInfo):
+        u = info.unit
+        if self.slot_unit[u.slot] != u.name:
+            raise RuntimeError("a weight of %s is used outside the layer's forward / backward call (fully sharded parameters "
+                               "are gathered by the layer's hooks)" % u.name)
+        if self._learning:
+            info.used = True
+            return None
+        key = (u.name, self.slot_stamp[u.slot])
+        if info.valid_key == key:
+            return None
+        info.valid_key = key
+        ctr = self.gather_counters[u.slot]
+        return (self.rank, self.shard_ptrs, self.staging[u.slot], u.shard_off, u.piece, info.offset, info.numel, ctr)
+
+    # -- reductions ----------------------------------------------------------------------------------------
+    def _grad_range(self, u: Unit):
+        # every unit's buffer (rotating or resident) is cleared by its own reduction once all peers have read it
+        return u.grad_base + self.rank * u.piece, (u.grad_base, _round_up(u.piece * self.world, 64))
+
+    def _after_reduce(self, u: Unit):
+        if u.gslot >= 0:
+            ev = torch.cuda.Event()
+            ev.record(self.comm)
+            self.gslot_free[u.gslot] = ev
+
+    def _master(self):
+        return self.master_shard
+
+    def _zero_len(self) -> int:
+        return 0                   # every reduce_unit clears its own gradient buffer
+
+    def _finish_learning(self):
+        self._learning = False
+        for p in self.store.params:
+            info = getattr(p, "_fsdp", None)
+            if info is not None and not info.used:
+                p._fsdp = None
+        self._plan_small_ranges()
 
     def launch(self):
-        s = self.store
-        ops.ext().fsdp_step(self.rank, self.grad_ptrs, self.shard_ptrs, self.flag_ptrs, self.partial_ptrs,
-                            [p[0] for p in self.pieces], [p[1] for p in self.pieces], [p[2] for p in self.pieces], self.reduced,
-                            self.sq, self.nonfinite, self.master_shard, self.exp_avg, self.exp_avg_sq, self.optim.hyper,
-                            self.shard_len, s.total, self.epoch, self.norm)
-        ops.LAUNCHES[0] += 3
+        super().launch()
+        if self._learning:
+            self._finish_learning()
         self.slot_unit = [None, None]
+        self.slot_stamp = [s + 1 for s in self.slot_stamp]
 
+    # -- checkpoints -----------------------------------------------------------------------------------------
     def gather_master(self):
-        """Refresh the full fp32 master buffer (``param.data``) on every rank from the owners' pieces."""
+        """Collective: re-materialise the full fp32 master buffer (``param.data``) on every rank from the owners'
+        pieces.  ``release_master`` drops it again."""
+        self._materialise_master()
         if self.world > 1:
             everyone = [torch.empty_like(self.master_shard) for _ in range(self.world)]
             dist.all_gather(everyone, self.master_shard)
         else:
             everyone = [self.master_shard]
         for r, shard in enumerate(everyone):
-            for u in self.units:
-                g0 = u.begin + r * u.piece
-                n = max(0, min(u.piece, u.end - g0))
-                if n > 0:
-                    self.store.master[g0:g0 + n].copy_(shard[u.shard_off:u.shard_off + n])
+            self._shard_to_flat(shard, self.store.master, r)
 
-    def state_dict(self):
-        return {"exp_avg": self.exp_avg.cpu(), "exp_avg_sq": self.exp_avg_sq.cpu(), "begin": -self.rank - 1, "length": self.shard_len}
+    def release_master(self):
+        self._release_master()
+
+    def load_master(self, flat_master: Optional[torch.Tensor] = None):
+        """After ``param.data`` has been (re)loaded into a materialised master buffer: cut the shards again."""
+        src = flat_master if flat_master is not None else self.store.master
+        for (so, p0, _n), u in zip(self.pieces, self.units):
+            full = max(0, min(u.piece, u.end - p0))
+            if full > 0:
+                self.master_shard[so:so + full].copy_(src[p0:p0 + full])
+        self.shard.copy_(self.master_shard)
 
     # memory accounting, bytes per rank
     def memory_report(self):
         total = self.store.total
-        return {"bf16_shard": 2 * self.shard_len, "staging": 2 * sum(b.numel() for b in self.staging) + 2 * sum(b.numel() for b in self.resident.values()),
-                "optimizer_state": 16 * self.shard_len, "replicated_bf16_would_be": 2 * total, "replicated_state_would_be": 16 * total}
+        persistent = 2 * self.shard.numel() + 4 * self.master_shard.numel() + 4 * self.reduced.numel() + 8 * self.exp_avg.numel()
+        staging = 2 * sum(b.numel() for b in self.staging) + 2 * sum(b.numel() for b in self.resident.values())
+        grad_staging = 4 * self.grad_space.numel()
+        return {"bf16_shard": 2 * self.shard.numel(), "master_shard": 4 * self.master_shard.numel(),
+                "reduced_grad_shard": 4 * self.reduced.numel(), "optimizer_state": 8 * self.exp_avg.numel(),
+                "persistent_bytes_per_param": persistent / max(total, 1), "param_staging": staging,
+                "grad_staging": grad_staging, "full_master_resident": self.store.master is not None,
+                "replicated_bf16_would_be": 2 * total, "replicated_state_would_be": 16 * total}

@@ -5,9 +5,10 @@ IPC handles through ``torch.distributed`` (any backend: the exchange is host-sid
 peer's handle; the result is, per buffer, one device pointer per rank.  This is the only use of the process
 group on this path: bootstrap.
 
-``FusedAllReduceAdam`` owns slice ``rank`` of the flat parameter space (fp32 master weights and Adam moments
-exist only for that slice) and performs reduce-scatter + unscale + clip + Adam(W) + all-gather of the bf16
-parameters + gradient clearing with the kernels of ``csrc/comm_p2p.cu`` - no NCCL call on the step.
+``FusedAllReduceAdam`` owns one piece of every layer of the flat parameter space (Adam moments exist only for
+owned pieces) and performs per-layer reduce-scatter overlapped with the backward pass + unscale + clip + Adam(W)
++ all-gather of the bf16 parameters + gradient clearing with the kernels of ``csrc/comm_p2p.cu`` - no NCCL call
+on the step.
 
 ``ShardedAdamReference`` is the same algorithm written with ``torch.distributed`` collectives (reduce-scatter,
 all-gather of the norm partials, all-gather of parameters); it is what CPU / gloo tests run and what the
@@ -21,9 +22,7 @@ import torch
 import torch.distributed as dist
 
 from .. import ops
-
-FLAG_INTS = 3 * 16
-PARTIAL_FLOATS = 2 * 16
+from .sharded import FLAG_INTS, PARTIAL_FLOATS, UnitShardedStep, plan_units  # noqa: F401  (re-exported)
 
 
 def slice_bounds(total: int, world: int, rank: int):
@@ -69,47 +68,36 @@ class SymmetricHeap:
         self._keep = []
 
 
-class FusedAllReduceAdam:
-    """Peer-memory data-parallel step.  ``store.grad`` / ``store.work`` must come from ``heap``."""
+class FusedAllReduceAdam(UnitShardedStep):
+    """Peer-memory data-parallel step.  ``store.grad`` / ``store.work`` must come from ``heap``.
 
-    fused_optimizer = True
+    Every rank keeps full fp32 gradients, a full bf16 parameter copy and the full fp32 master buffer (of which only
+    the owned pieces are current between checkpoints); Adam moments exist only for the owned pieces.  Per step:
+    per-layer ``reduce_unit`` launches overlapped with the backward pass, then one ``update_pieces`` launch whose
+    peer stores refresh every rank's bf16 copy (see ``sharded.UnitShardedStep``)."""
 
-    def __init__(self, store, optim, heap: SymmetricHeap, grad_ptrs, work_ptrs):
-        self.store, self.optim, self.heap = store, optim, heap
-        self.rank, self.world = heap.rank, heap.world
-        self.begin, self.length = slice_bounds(store.total, self.world, self.rank)
-        dev = store.master.device
-        flags, self.flag_ptrs = heap.alloc(FLAG_INTS, torch.int32)
-        partials, self.partial_ptrs = heap.alloc(PARTIAL_FLOATS, torch.float32)
-        self.flags, self.partials = flags, partials
-        self.grad_ptrs, self.work_ptrs = grad_ptrs, work_ptrs
-        self.reduced = torch.zeros(self.length, dtype=torch.float32, device=dev)
-        self.exp_avg = torch.zeros(self.length, dtype=torch.float32, device=dev)
-        self.exp_avg_sq = torch.zeros(self.length, dtype=torch.float32, device=dev)
-        self.sq = torch.zeros(1, dtype=torch.float32, device=dev)
-        self.nonfinite = torch.zeros(1, dtype=torch.int32, device=dev)
-        self.norm = torch.zeros(1, dtype=torch.float32, device=dev)
-        self.epoch = torch.ones(1, dtype=torch.int32, device=dev)
+    mode = 0
+
+    def __init__(self, store, optim, heap: SymmetricHeap, grad_ptrs, work_ptrs, model=None, overlap: bool = True):
+        units = plan_units(model, store, heap.world) if model is not None else plan_units(torch.nn.Module(), store, heap.world)
+        self._setup(model, store, optim, heap, grad_ptrs, work_ptrs, units, overlap=overlap)
         if self.world > 1:
             dist.barrier()      # every rank has zeroed flags and opened every handle before the first step
 
-    def __call__(self, flat_grad):   # the reduction happens inside ``launch`` together with the update
-        return None
-
-    def launch(self):
-        s = self.store
-        ops.ext().allreduce_adamw(self.rank, self.grad_ptrs, self.work_ptrs, self.flag_ptrs, self.partial_ptrs, self.reduced,
-                                  self.sq, self.nonfinite, s.master[self.begin:self.begin + self.length], self.exp_avg,
-                                  self.exp_avg_sq, self.optim.hyper, self.begin, self.length, s.total, self.epoch, self.norm)
-
     def gather_master(self):
-        """Refresh the full fp32 master buffer on every rank from the owners' slices (before saving)."""
-        if self.world > 1:
-            mine = self.store.master[self.begin:self.begin + self.length].clone()
-            dist.all_gather_into_tensor(self.store.master, mine)
-
-    def state_dict(self):
-        return {"exp_avg": self.exp_avg.cpu(), "exp_avg_sq": self.exp_avg_sq.cpu(), "begin": self.begin, "length": self.length}
+        """Refresh the full fp32 master buffer on every rank from the owners' pieces (before saving)."""
+        if self.world <= 1:
+            return
+        mine = torch.zeros(self.shard_len, dtype=torch.float32, device=self.device)
+        for (so, p0, n), u in zip(self.pieces, self.units):
+            full = max(0, min(u.piece, u.end - p0))
+            if full > 0:
+                mine[so:so + full].copy_(self.store.master[p0:p0 + full])
+        everyone = [torch.empty_like(mine) for _ in range(self.world)]
+        dist.all_gather(everyone, mine)
+        for r, shard in enumerate(everyone):
+            if r != self.rank:
+                self._shard_to_flat(shard, self.store.master, r)
 
 
 class ShardedAdamReference:

@@ -212,6 +212,9 @@ def rng_state() -> dict:
              "dropout": (ops._Rng.seed, ops._Rng.counter)}
     if torch.cuda.is_available():
         state["cuda"] = torch.cuda.get_rng_state()
+        if ops.extension_available():
+            # the device-resident word that every training step advances (added to the dropout seed inside the kernels)
+            state["dropout_device_word"] = int(ops.ext().get_seed_tensor(torch.cuda.current_device()).item())
     return state
 
 
@@ -227,6 +230,8 @@ def restore_rng_state(state: Optional[dict]) -> bool:
     if "cuda" in state and torch.cuda.is_available():
         torch.cuda.set_rng_state(state["cuda"])
     ops._Rng.seed, ops._Rng.counter = state["dropout"]
+    if "dropout_device_word" in state and torch.cuda.is_available() and ops.extension_available():
+        ops.ext().get_seed_tensor(torch.cuda.current_device()).fill_(int(state["dropout_device_word"]))
     return True
 
 

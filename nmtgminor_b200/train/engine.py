@@ -91,33 +91,37 @@ class TrainEngine:
                     ptrs[name] = p
                     return t
                 return alloc
-            # fully sharded: no replicated bf16 copy; layers read gathered weights from staging buffers
-            work_alloc = (lambda n, dt: None) if fsdp else symm("work")
-            self.store = FlatParameterStore(model, self.device, allocator={"grad": symm("grad"), "work": work_alloc},
-                                            pad_total_to=256 * world)
+            # fully sharded: no replicated bf16 copy and no full gradient buffer; layers read gathered weights from
+            # staging buffers and write gradients into rotating per-layer buffers owned by the sharded step
+            nothing = lambda n, dt: None
+            self.store = FlatParameterStore(model, self.device, pad_total_to=256 * world,
+                                            allocator={"grad": nothing if fsdp else symm("grad"), "work": nothing if fsdp else symm("work")})
         else:
             self.store = FlatParameterStore(model, self.device, pad_total_to=256 * max(world, 1))
         for b in model.buffers():
             b.data = b.data.to(self.device)
         self.optim = Optim(opt)
-        self.optim.set_parameters(model.parameters(), self.store)
+        self.optim.set_parameters(model.parameters(), self.store, allocate_state=heap is None)
+        from ..parallel.sharded import skips_layers
+        overlap = not skips_layers(opt)
         if fsdp:
             from ..parallel.ddp import broadcast_parameters
             from ..parallel.fsdp import FullyShardedAdam
             if world > 1:
                 broadcast_parameters(self.store)
             assert self.optim.fused, "-fsdp needs the fused Adam(W) path"
-            reducer = FullyShardedAdam(model, self.store, self.optim, heap, ptrs["grad"])
+            reducer = FullyShardedAdam(model, self.store, self.optim, heap, overlap=overlap)
             self.optim.attach_distributed(reducer)
-            cuda_graph = False
         elif world > 1 and reducer is None and ddp is not None:
             from ..parallel.ddp import NcclReducer, broadcast_parameters
             broadcast_parameters(self.store)
             if heap is not None and self.optim.fused:
                 from ..parallel.symmetric import FusedAllReduceAdam
-                reducer = FusedAllReduceAdam(self.store, self.optim, heap, ptrs["grad"], ptrs["work"])
+                reducer = FusedAllReduceAdam(self.store, self.optim, heap, ptrs["grad"], ptrs["work"], model=model, overlap=overlap)
                 self.optim.attach_distributed(reducer)
             else:
+                if heap is not None:     # the fused path was planned but the optimiser is not Adam-like
+                    self.optim.set_parameters(model.parameters(), self.store)
                 reducer = NcclReducer(world)
         self.reducer = reducer            # callable(flat_grad) -> None, data-parallel gradient reduction
         self.grad_scale = grad_scale
@@ -151,8 +155,17 @@ class TrainEngine:
     def _eager_step(self, batch, update: bool = True):
         if self.on_gpu:
             batch = batch.cuda(self.device, hot_only=True)
+            if ops.extension_available():
+                # dropout masks are a function of (seed + device seed word, op index, element): a new word per call gives
+                # every step and every accumulation micro-batch its own masks (a captured graph does the same inside)
+                ops.advance_device_seed(self.device.index)
         n0 = ops.LAUNCHES[0]
+        if hasattr(self.reducer, "active"):
+            # data parallel: micro-batches that do not end in an update accumulate locally, nothing is exchanged
+            self.reducer.active = update or getattr(self.reducer, "mode", 0) == 1
         loss, correct = self._forward_backward(batch)
+        if not update and hasattr(self.reducer, "active") and self.reducer.active:
+            self.reducer(self.store.grad)       # fully sharded: every micro-batch is reduce-scattered into the shard
         if update:
             from ..utils.tracing import nvtx_range
             with nvtx_range("reduce+optimizer", bool(getattr(self.opt, "trace_nvtx", False))):
@@ -162,7 +175,23 @@ class TrainEngine:
             if not self.optim.fused:
                 self.optim.zero_grad()
         self.kernel_launches_per_step = ops.LAUNCHES[0] - n0
+        if update:
+            self._snapshot_status()
         return loss, correct
+
+    def _snapshot_status(self):
+        """Copies the device status word into pinned host memory behind the step (asynchronous; inside a capture it
+        becomes a node of the graph), so ``peek_status`` sees a timed-out wait one step later without synchronising."""
+        if not (self.on_gpu and self.world_size > 1 and ops.extension_available()):
+            return
+        if getattr(self, "_status_host", None) is None:
+            self._status_host = torch.zeros(1, dtype=torch.int32).pin_memory()
+        self._status_host.copy_(ops.ext().get_status_tensor(self.device.index), non_blocking=True)
+
+    def peek_status(self) -> int:
+        """Status word as of the last completed step (no device synchronisation); 0 = every wait was answered."""
+        h = getattr(self, "_status_host", None)
+        return int(h[0]) if h is not None else 0
 
     def _capture(self, batch):
         self._static = _StaticInputs(batch, self.device)
@@ -188,6 +217,7 @@ class TrainEngine:
             if self.reducer is not None:
                 self.reducer(self.store.grad)
             self.optim.launch_fused()
+            self._snapshot_status()
         self.kernel_launches_per_step = ops.LAUNCHES[0] - n0   # every replay re-runs exactly these launches
         self._static_loss, self._static_correct = loss, correct
 
@@ -198,6 +228,8 @@ class TrainEngine:
         self.model.train()
         if not (self.use_graph and self.optim.fused) or not update:
             return self._eager_step(batch, update)
+        if hasattr(self.reducer, "active"):
+            self.reducer.active = True
         if self._graph is None or self._static.signature() != _StaticInputs.signature_of(batch):
             self._capture(batch)
         self._static.load(batch)

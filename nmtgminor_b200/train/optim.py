@@ -70,8 +70,9 @@ class Optim:
         self.params = []
 
     # -- attach -----------------------------------------------------------------------------------
-    def set_parameters(self, params, store: Optional[FlatParameterStore] = None):
-        """Fused flat path when ``store`` lives on a CUDA device and the method is Adam-like."""
+    def set_parameters(self, params, store: Optional[FlatParameterStore] = None, allocate_state: bool = True):
+        """Fused flat path when ``store`` lives on a CUDA device and the method is Adam-like.  ``allocate_state=False``
+        when a sharded step (``attach_distributed``) will own the moments."""
         self.params = [p for p in params if p.requires_grad]
         self.store = store
         fused = store is not None and store.master.is_cuda and self.method in ("adam", "adamw") and ops.extension_available()
@@ -80,8 +81,8 @@ class Optim:
             dev = store.master.device
             # moments only for the trainable prefix of the flat space (frozen parameters sit behind it)
             self.n_update = int(getattr(store, "trainable_total", store.total))
-            self.exp_avg = torch.zeros(self.n_update, dtype=torch.float32, device=dev)
-            self.exp_avg_sq = torch.zeros(self.n_update, dtype=torch.float32, device=dev)
+            self.exp_avg = torch.zeros(self.n_update, dtype=torch.float32, device=dev) if allocate_state else None
+            self.exp_avg_sq = torch.zeros(self.n_update, dtype=torch.float32, device=dev) if allocate_state else None
             self.grad_sq = torch.zeros(1, dtype=torch.float32, device=dev)
             self.nonfinite = torch.zeros(1, dtype=torch.int32, device=dev)
             self.hyper = torch.zeros(16, dtype=torch.float32, device=dev)
@@ -190,9 +191,24 @@ class Optim:
             self.store.zero_grad()
 
     # -- state ------------------------------------------------------------------------------------
+    def prepare_state_dict(self):
+        """Collective part of ``state_dict``: with a sharded step every rank has to call this (the moments of all
+        pieces are gathered into the flat layout on rank 0); a no-op otherwise."""
+        d = getattr(self, "distributed", None)
+        if self.fused and d is not None:
+            self._gathered_moments = d.gather_moments()
+
     def state_dict(self):
-        if self.fused and getattr(self, "distributed", None) is not None:
-            sd = {"fused": True, "sharded": self.distributed.state_dict()}
+        d = getattr(self, "distributed", None)
+        if self.fused and d is not None:
+            got = getattr(self, "_gathered_moments", None)
+            if got is None:
+                if d.world > 1:
+                    raise RuntimeError("Optim.prepare_state_dict() must be called on every rank before state_dict()")
+                got = d.gather_moments()
+            self._gathered_moments = None
+            # flat-ordered moments: the file does not depend on the world size or on the sharding mode that wrote it
+            sd = {"fused": True, "exp_avg": got[0], "exp_avg_sq": got[1]}
         elif self.fused:
             sd = {"fused": True, "exp_avg": self.exp_avg.cpu(), "exp_avg_sq": self.exp_avg_sq.cpu()}
         else:
@@ -206,18 +222,15 @@ class Optim:
         self._step = sd.pop("_step", 0)
         self._epoch_decay = sd.pop("_epoch_decay", 1.0)
         if self.fused and getattr(self, "distributed", None) is not None:
-            sh = sd.get("sharded")
-            d = self.distributed
-            if sh is not None and sh["begin"] == d.begin and sh["length"] == d.length:
-                d.exp_avg.copy_(sh["exp_avg"])
-                d.exp_avg_sq.copy_(sh["exp_avg_sq"])
-            elif "exp_avg" in sd:
-                d.exp_avg.copy_(sd["exp_avg"][d.begin:d.begin + d.length])
-                d.exp_avg_sq.copy_(sd["exp_avg_sq"][d.begin:d.begin + d.length])
+            if "exp_avg" not in sd:
+                raise RuntimeError("the checkpoint holds no flat-ordered Adam moments (keys: %s); a sharded run cannot restore "
+                                   "its optimiser state from it - resume with -reset_optim" % sorted(sd.keys()))
+            self.distributed.load_moments(sd["exp_avg"], sd["exp_avg_sq"])
         elif self.fused:
             if sd.get("fused") and "exp_avg" in sd:
-                self.exp_avg.copy_(sd["exp_avg"])
-                self.exp_avg_sq.copy_(sd["exp_avg_sq"])
+                n = min(self.exp_avg.numel(), sd["exp_avg"].numel())
+                self.exp_avg[:n].copy_(sd["exp_avg"][:n])
+                self.exp_avg_sq[:n].copy_(sd["exp_avg_sq"][:n])
             elif "state" in sd:
                 # a torch.optim state dict (per-parameter moments): scatter into the flat buffers
                 for i, p in enumerate(self.params):

@@ -79,6 +79,8 @@ class Trainer:
             try:
                 self.optim.load_state_dict(checkpoint["optim"])
             except Exception as exc:  # noqa: BLE001
+                if getattr(self.optim, "distributed", None) is not None:
+                    raise       # a sharded run with some ranks restored and others not would diverge silently
                 self.log("[WARN] optimiser state not restored: %r" % (exc,))
             from .checkpoint import restore_rng_state
             restore_rng_state(checkpoint.get("rng"))      # same dropout masks and shuffles as the uninterrupted run
@@ -93,6 +95,10 @@ class Trainer:
         if lora_rank > 0:
             raise RuntimeError("apply LoRA before building the trainer: use nmtgminor_b200.train.finetune.apply_lora on the model "
                                "returned by build_model (see finetune_whisper.py)")
+        if self.cuda and ops.extension_available():
+            # bound of every device-side wait for a peer: minutes in production (a slow data loader or a long validation
+            # pass on one rank must not abort the run), short in tests
+            ops.ext().set_peer_timeout_ms(float(getattr(opt, "peer_timeout", 0) or os.environ.get("NMTG_PEER_TIMEOUT_MS", 120000)))
         self.watchdog = None
         if getattr(opt, "watchdog_timeout", 0) and self.world_size > 1:
             from ..utils.watchdog import Heartbeat
@@ -144,17 +150,26 @@ class Trainer:
     def save(self, epoch: float, valid_ppl: float, itr=None, accuracy: float = 0.0):
         dist_opt = getattr(self.optim, "distributed", None)
         if dist_opt is not None:
-            dist_opt.gather_master()      # collective: every rank refreshes its full fp32 copy from the slice owners
-        if not self.is_main():
-            return None
-        opt = self.opt
-        if self.ema is not None:
-            self.ema.swap_in()
+            dist_opt.gather_master()         # collective: every rank refreshes its full fp32 copy from the piece owners
+            self.optim.prepare_state_dict()  # collective: Adam moments of all pieces -> flat layout on rank 0
+        name = None
         try:
-            return self._save_checkpoint_file(epoch, valid_ppl, itr, accuracy)
+            if self.is_main():
+                if self.ema is not None:
+                    self.ema.swap_in()
+                try:
+                    name = self._save_checkpoint_file(epoch, valid_ppl, itr, accuracy)
+                finally:
+                    if self.ema is not None:
+                        self.ema.swap_out()
         finally:
-            if self.ema is not None:
-                self.ema.swap_out()
+            if dist_opt is not None and hasattr(dist_opt, "release_master"):
+                dist_opt.release_master()
+            # the other ranks wait here while rank 0 writes the file: without this they would run ahead into the next
+            # step's gradient exchange and sit in a device-side wait (which is bounded, and would abort the run)
+            if self.world_size > 1 and dist.is_initialized():
+                dist.barrier()
+        return name
 
     def _save_checkpoint_file(self, epoch: float, valid_ppl: float, itr=None, accuracy: float = 0.0):
         opt = self.opt
@@ -215,6 +230,10 @@ class Trainer:
             report["sents"] += batch.size
             if update:
                 counter, acc_words = 0, 0
+                if self.world_size > 1 and self.engine.peek_status():
+                    torch.cuda.synchronize()
+                    raise RuntimeError("a device kernel gave up waiting for a peer (status %d); aborting the run"
+                                       % (ops.check_status() or self.engine.peek_status()))
                 if self.ema is not None:
                     self.ema.update(self.optim._step)
                 if self.watchdog is not None:

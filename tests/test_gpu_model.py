@@ -166,3 +166,33 @@ def test_lora_adapters_train_on_the_fused_path_and_leave_frozen_weights_alone():
     assert ops.check_status() == 0
     assert torch.equal(store.master[store.trainable_total:], frozen_before)      # no update, no weight decay
     assert losses[-1] < losses[0]
+
+
+@pytest.mark.parametrize("graph", [False, True])
+def test_every_step_draws_new_dropout_masks(graph):
+    """With a learning rate of zero the parameters never move, so two steps on the same batch differ only through
+    their dropout masks: equal losses would mean the masks repeat from step to step."""
+    torch.manual_seed(1)
+    d = synthetic_dict(2000)
+    opt = _opt(["-dropout", "0.3", "-attn_dropout", "0.1", "-learning_rate", "0.0"])
+    model = Transformer(opt, {"src": d, "tgt": d})
+    eng = TrainEngine(model, opt, device="cuda", cuda_graph=graph)
+    batch = token_budget_batches(2000, 5, 40, 1024, 1, seed=5, static=True, padded=False)[0].pin_memory()
+    losses = [eng.train_step(batch)[0].item() for _ in range(4)]
+    assert len(set(losses)) == len(losses), "dropout masks repeat: %r" % (losses,)
+    # accumulation micro-batches get their own masks too
+    a = eng.train_step(batch, update=False)[0].item()
+    b = eng.train_step(batch, update=True)[0].item()
+    assert a != b
+
+
+def test_rng_state_round_trip_restores_the_device_seed_word():
+    from nmtgminor_b200.train.checkpoint import restore_rng_state, rng_state
+    word = ops.ext().get_seed_tensor(torch.cuda.current_device())
+    ops.advance_device_seed(by=5)
+    saved = rng_state()
+    want = int(word.item())
+    ops.advance_device_seed(by=3)
+    assert int(word.item()) == want + 3
+    restore_rng_state(saved)
+    assert int(word.item()) == want
