@@ -73,13 +73,13 @@ def transformer_big_argv(tiny=False):
 class ReferenceRunner:
     """Builds the reference model / loss / optimiser once and exposes ``step(host_batch)``."""
 
-    def __init__(self, vocab_size, device, rank=0, world_size=1, tiny=False):
+    def __init__(self, vocab_size, device, rank=0, world_size=1, tiny=False, argv_extra=()):
         onmt, options = import_reference()
         self.onmt = onmt
         from onmt.model_factory import build_model, init_model_parameters, optimize_model
         from onmt.modules.loss import NMTLossFunc
         from onmt.constants import add_tokenidx
-        self.opt = opt = make_opt(options, transformer_big_argv(tiny))
+        self.opt = opt = make_opt(options, transformer_big_argv(tiny) + list(argv_extra))     # later flags win
         d = onmt.Dict(["<blank>", "<unk>", "<s>", "</s>"])
         for i in range(vocab_size - 4):
             d.add("w%d" % i)

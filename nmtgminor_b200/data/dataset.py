@@ -191,14 +191,41 @@ def pack_sequences(seqs: Sequence[torch.Tensor], pad: int, capacity: Optional[in
     return PackedSeqs(toks, pos, cu, int(lengths.max()) if len(seqs) else 0, lengths)
 
 
+def bucket_capacity(n: int, per_octave: int = 8, floor: int = 128) -> int:
+    """Round a packed token count up to one of ``per_octave`` sizes per power of two (at most 1 / per_octave of the
+    rows are padding).  Batches whose rounded sizes agree share one captured CUDA graph of the training step."""
+    n = max(int(n), 1)
+    if n <= floor:
+        return floor
+    step = max(floor, 1 << max(0, n.bit_length() - 1 - max(per_octave.bit_length() - 1, 0)))
+    return (n + step - 1) // step * step
+
+
+def bucket_max_len(n: int) -> int:
+    """Upper bound on the sequence length that the attention kernels size their grids with: 128 (the single-tile
+    kernels) or the next multiple of 128."""
+    return 128 if n <= 128 else (n + 127) // 128 * 128
+
+
 def collate(src_data, tgt_data, src_lang=None, tgt_lang=None, src_atb=None, tgt_atb=None, src_pad=C.PAD, tgt_pad=C.PAD,
             src_type="text", index_data=None, padded: bool = True, packed: bool = True, capacity_src: Optional[int] = None,
             capacity_tgt: Optional[int] = None, max_batch: Optional[int] = None, round_to: int = 128,
-            create_reverse: bool = False, vocab_mask=None, past_src_data=None, aux_tgt_data=None) -> Batch:
+            create_reverse: bool = False, vocab_mask=None, past_src_data=None, aux_tgt_data=None,
+            static_shapes: bool = False) -> Batch:
     """Build a ``Batch`` from lists of per-sentence tensors (targets carry BOS ... EOS).  ``past_src_data``: the previous
     source sentence of every example (document-context models; keys ``past_source*`` of the reference's batches).
     ``aux_tgt_data``: a second target per example ("triangle" corpora: e.g. the transcript next to the translation),
-    given as ``aux_target_input`` / ``aux_target_output`` ``[T, B]`` and ``aux_tgt_lengths``."""
+    given as ``aux_target_input`` / ``aux_target_output`` ``[T, B]`` and ``aux_tgt_lengths``.
+    ``static_shapes``: round the packed capacities, the sentence count and the length bounds to a small set of sizes
+    (``bucket_capacity``), so that the batches of a token-budget data set fall into a handful of shape classes."""
+    if static_shapes and packed and src_type == "text":
+        n_sent = len(src_data) if src_data is not None else len(tgt_data)
+        if capacity_src is None and src_data is not None:
+            capacity_src = bucket_capacity(sum(int(s.shape[0]) for s in src_data))
+        if capacity_tgt is None and tgt_data is not None:
+            capacity_tgt = bucket_capacity(sum(int(s.shape[0]) - 1 for s in tgt_data))
+        if max_batch is None:
+            max_batch = bucket_capacity(n_sent, per_octave=4, floor=8)
     t: TDict = {"src_type": src_type, "vocab_mask": vocab_mask}
     if aux_tgt_data is not None:
         aux_bt, aux_lengths = _pad_stack(aux_tgt_data, tgt_pad)
@@ -268,6 +295,10 @@ def collate(src_data, tgt_data, src_lang=None, tgt_lang=None, src_atb=None, tgt_
                 assert extra >= 0, "batch of %d sentences exceeds the static capacity %d" % (ps.batch_size, max_batch)
                 if extra:
                     ps.cu = torch.cat([ps.cu, ps.cu[-1:].expand(extra)])
+    if static_shapes and packed:
+        for k in ("packed_source", "packed_target_input"):
+            if k in t:
+                t[k].max_len = bucket_max_len(t[k].max_len)
     for name, data in (("source_lang", src_lang), ("target_lang", tgt_lang), ("source_atbs", src_atb), ("target_atbs", tgt_atb)):
         if data is not None:
             t[name] = torch.cat([d.view(-1) for d in data]).long()
@@ -291,7 +322,7 @@ class Dataset(torch.utils.data.Dataset):
                  data_type="text", max_src_len=256, max_tgt_len=256, min_src_len=0, min_tgt_len=0, cleaning=True,
                  sorting=True, src_pad=C.PAD, tgt_pad=C.PAD, padded=True, packed=True, round_to=128, cut_off_size=256000,
                  smallest_batch_size=4, verbose=False, augmenter=None, create_reverse=False, past_src_data=None,
-                 aux_tgt_data=None, **_ignored):
+                 aux_tgt_data=None, static_shapes=False, **_ignored):
         self.src, self.tgt = src_data, tgt_data
         self.aux_tgt = aux_tgt_data            # second target per example ("triangle" corpora)
         self.past_src = past_src_data          # previous source sentence per example (document-context models)
@@ -300,6 +331,7 @@ class Dataset(torch.utils.data.Dataset):
         self.src_pad, self.tgt_pad = src_pad, tgt_pad
         self.padded, self.packed, self.round_to = padded, packed, round_to
         self.create_reverse = create_reverse
+        self.static_shapes = static_shapes     # round batch shapes so that training steps replay a few captured graphs
         self.augmenter = augmenter
         n = len(src_data) if src_data is not None else len(tgt_data)
         self.full_size = n
@@ -347,7 +379,8 @@ class Dataset(torch.utils.data.Dataset):
             src = [self.augmenter.augment(s) for s in src]
         return collate(src, pick(self.tgt), lang(self.src_langs), lang(self.tgt_langs), lang(self.src_atbs), lang(self.tgt_atbs),
                        self.src_pad, self.tgt_pad, self.type, ids, self.padded, self.packed, round_to=self.round_to,
-                       create_reverse=self.create_reverse, past_src_data=pick(self.past_src), aux_tgt_data=pick(self.aux_tgt))
+                       create_reverse=self.create_reverse, past_src_data=pick(self.past_src), aux_tgt_data=pick(self.aux_tgt),
+                       static_shapes=self.static_shapes)
 
     __getitem__ = get_batch
 

@@ -221,6 +221,10 @@ class FullyShardedAdam(UnitShardedStep):
                 self._launch_gather(u, [(0, _round_up(u.length, 8))], torch.cuda.current_stream())
         self.slot_unit = [None, None]
         self.slot_stamp = [s + 1 for s in self.slot_stamp]
+        # events never cross a step boundary (the streams joined when the last backward pass ended); a captured step
+        # must not wait on an event that was recorded outside its capture
+        self.slot_ready = [None, None]
+        self.gslot_free = [None] * GRAD_SLOTS
 
     def _take_slot(self, u: Unit, stream_for_small):
         """Staging buffer ``u.slot`` changes hands: small parameters (or, unfused, everything) are copied in."""
@@ -277,6 +281,11 @@ class FullyShardedAdam(UnitShardedStep):
             ev = torch.cuda.Event()
             ev.record(self.comm)
             self.gslot_free[u.gslot] = ev
+
+    def __call__(self, flat_grad=None):
+        out = super().__call__(flat_grad)
+        self.gslot_free = [None] * GRAD_SLOTS      # the streams have joined: nothing is pending any more
+        return out
 
     def _master(self):
         return self.master_shard

@@ -3,10 +3,10 @@
 One ``TrainEngine.train_step(batch)`` call performs: async host-to-device copy of the packed integer
 tensors from pinned memory, forward through the fused kernels, backward (weight gradients accumulate
 straight into the flat fp32 buffer), optional data-parallel reduction of that buffer, and the flat
-Adam(W) update.  With ``cuda_graph=True`` and batches of static packed capacity, forward + backward +
-update are captured ONCE into a CUDA graph and replayed per step (inputs are copied into static buffers,
-per-step scalars live in device memory, dropout masks advance through a device-resident seed word), which
-removes per-kernel launch and Python overhead from the step.
+Adam(W) update.  With ``cuda_graph=True`` forward + backward + update are captured into a CUDA graph once per SHAPE CLASS
+of batches (packed capacities rounded to a few sizes) and replayed per step (inputs are copied into static
+buffers, per-step scalars live in device memory, dropout masks advance through a device-resident seed
+word), which removes per-kernel launch and Python overhead from the step.
 
 The reference's equivalent loop is ``Trainer.train_epoch`` (onmt/train_utils/mp_trainer.py:743-1016):
 ``Batch.cuda`` -> autocast forward -> loss -> ``GradScaler.scale(loss).backward()`` (DDP all-reduce inside)
@@ -127,10 +127,10 @@ class TrainEngine:
         self.grad_scale = grad_scale
         self.loss_weight = 1.0            # weight of the next batch's gradient (replay weighting in continual learning)
         self.use_graph = bool(cuda_graph) and self.on_gpu
-        self._graph = None
-        self._static: Optional[_StaticInputs] = None
-        self._static_loss = None
-        self._static_correct = None
+        self._graphs = {}                 # shape class -> [graph, static inputs, launches per replay, last use]
+        self._pool = None
+        self._tick = 0
+        self.max_graphs = 24
         self.kernel_launches_per_step = 0
 
     # ---------------------------------------------------------------------------------------------
@@ -193,50 +193,82 @@ class TrainEngine:
         h = getattr(self, "_status_host", None)
         return int(h[0]) if h is not None else 0
 
-    def _capture(self, batch):
-        self._static = _StaticInputs(batch, self.device)
-        self._static.load(batch)
+    def local_only_mode(self):
+        """Measurement aid: from now on every rank updates its own full parameter copy from its own gradients (gradient
+        norm + flat Adam(W), what a single GPU does) and nothing is exchanged.  The difference between a step before and
+        after this call is the part of the gradient exchange that the backward pass did not hide.  The ranks' parameters
+        diverge afterwards, so this is the last thing a benchmark does with the engine."""
+        if getattr(self.optim, "distributed", None) is None or getattr(self.reducer, "mode", 0) != 0:
+            return
         torch.cuda.synchronize()
-        side = torch.cuda.Stream()
-        side.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(side):
-            for _ in range(2):      # warm-up outside capture: allocator pools, tensor-map cache, lazy inits
-                self._forward_backward(self._static)
-                if self.reducer is not None:
-                    self.reducer(self.store.grad)
-                self.optim._step += 1
-                self.optim.write_hyper(self.grad_scale)
-                self.optim.launch_fused()
-        torch.cuda.current_stream().wait_stream(side)
+        self._graphs = {}
+        self.reducer = None
+        self.optim.distributed = None
+        n = self.optim.n_update
+        self.optim.exp_avg = torch.zeros(n, dtype=torch.float32, device=self.device)
+        self.optim.exp_avg_sq = torch.zeros(n, dtype=torch.float32, device=self.device)
+        self.store.zero_grad()
+
+    def _capture(self, batch, sig):
+        """Capture forward + backward + reduction + update for batches of this shape class.  Nothing is executed here:
+        the caller has just run the same step eagerly (which also warmed the allocator pools, the tensor-map cache and
+        every lazy initialisation), and with several ranks a capture must not add or remove a step from the sequence of
+        collective steps that the peers see."""
+        static = _StaticInputs(batch, self.device)
+        if self._pool is None:
+            self._pool = torch.cuda.graph_pool_handle()     # all shape classes share one private memory pool
+            self._loss_out = torch.zeros(1, dtype=torch.float32, device=self.device)
+            self._correct_out = torch.zeros(1, dtype=torch.float32, device=self.device)
         torch.cuda.synchronize()
-        self._graph = torch.cuda.CUDAGraph()
+        graph = torch.cuda.CUDAGraph()
         n0 = ops.LAUNCHES[0]
-        with torch.cuda.graph(self._graph):
+        step_before = self.optim._step
+        with torch.cuda.graph(graph, pool=self._pool):
             ops.advance_device_seed(self.device.index)
-            loss, correct = self._forward_backward(self._static)
+            loss, correct = self._forward_backward(static)
             if self.reducer is not None:
                 self.reducer(self.store.grad)
             self.optim.launch_fused()
             self._snapshot_status()
-        self.kernel_launches_per_step = ops.LAUNCHES[0] - n0   # every replay re-runs exactly these launches
-        self._static_loss, self._static_correct = loss, correct
+            # results leave the pool: the next replay (of any shape class) may reuse the pool's memory
+            self._loss_out.copy_(loss.reshape(1))
+            self._correct_out.copy_(correct.reshape(1).float())
+        self.optim._step = step_before
+        launches = ops.LAUNCHES[0] - n0               # every replay re-runs exactly these launches
+        if len(self._graphs) >= self.max_graphs:      # drop the least recently used shape class
+            oldest = min(self._graphs, key=lambda k: self._graphs[k][3])
+            del self._graphs[oldest]
+        self._graphs[sig] = [graph, static, launches, self._tick]
+        return self._graphs[sig]
 
     def train_step(self, batch, update: bool = True):
         """Forward + backward on ``batch`` (host tensors, ideally pinned) and, when ``update`` is set, gradient
         reduction + one optimiser update (``update=False`` only accumulates gradients).  Returns (loss_sum,
-        n_correct) as 1-element device tensors; reading them is the only synchronisation point."""
+        n_correct) as 1-element device tensors; reading them is the only synchronisation point.
+
+        With ``cuda_graph`` the first batch of every shape class (packed capacities, sentence count, length bounds: see
+        ``data.dataset.bucket_capacity``) runs kernel by kernel and is then captured; later batches of the class replay
+        the graph.  The returned tensors are overwritten by the next step."""
         self.model.train()
         if not (self.use_graph and self.optim.fused) or not update:
             return self._eager_step(batch, update)
         if hasattr(self.reducer, "active"):
             self.reducer.active = True
-        if self._graph is None or self._static.signature() != _StaticInputs.signature_of(batch):
-            self._capture(batch)
-        self._static.load(batch)
+        self._tick += 1
+        sig = _StaticInputs.signature_of(batch)
+        entry = self._graphs.get(sig)
+        if entry is None:
+            out = self._eager_step(batch, True)
+            self._capture(batch, sig)
+            return out
+        graph, static, launches, _ = entry
+        entry[3] = self._tick
+        static.load(batch)
         self.optim._step += 1
         self.optim.write_hyper(self.grad_scale)
-        self._graph.replay()
-        return self._static_loss, self._static_correct
+        graph.replay()
+        self.kernel_launches_per_step = launches
+        return self._loss_out, self._correct_out
 
     @torch.no_grad()
     def eval_step(self, batch):
