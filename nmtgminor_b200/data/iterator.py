@@ -128,8 +128,13 @@ class DataIterator:
         self._resume_offset = 0
         ds = _BatchIndexDataset(self.dataset, order[start:])
         pin = self.pin_memory and torch.cuda.is_available()
+        # a generator of its own: the loader draws its base seed when iteration starts, and taking that draw from the
+        # global generator would shift every later dropout mask (a resumed run creates the loader at a different point
+        # of the random stream than the run it continues)
+        gen = torch.Generator()
+        gen.manual_seed(int(self.seed) * 1000003 + int(self.epoch))
         loader = torch.utils.data.DataLoader(ds, batch_size=None, shuffle=False, num_workers=self.num_workers,
-                                             collate_fn=None, pin_memory=False)
+                                             collate_fn=None, pin_memory=False, generator=gen)
         it = (b.pin_memory() if pin else b for b in loader)
         if self.buffer_size > 0:
             it = BufferedIterator(it, self.buffer_size)

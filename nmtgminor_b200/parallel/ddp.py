@@ -4,10 +4,10 @@ Two reducers share one interface (``reducer(flat_grad)`` enqueues work on the cu
 
 * ``nccl``  - ``torch.distributed.all_reduce`` on the flat fp32 buffer (the baseline path; also what the CPU
   tests run with the gloo backend);
-* ``fused`` - the peer-memory kernel of ``parallel/symmetric.py`` (reduce-scatter by direct loads from
-  every peer's gradient buffer, fused with the Adam(W) update of the owned slice and the write-back of the
-  updated parameters to every peer), when the symmetric heap could be set up; otherwise it degrades to
-  ``nccl`` and says so once.
+* ``fused`` - the peer-memory kernels of ``parallel/symmetric.py`` (per-layer reduce-scatter by direct loads
+  from every peer's gradient buffer, overlapped with the backward pass and followed by the Adam(W) update of
+  the owned pieces and the write-back of the updated parameters to every peer); ``train.engine.TrainEngine``
+  builds it when the symmetric heap can be set up.
 
 Gradients are summed, not averaged: the reference trains on token-summed losses and normalises (or not)
 with ``-normalize_gradient`` afterwards (onmt/train_utils/mp_trainer.py:965-979).  The reference itself relies
@@ -40,21 +40,3 @@ class NcclReducer:
             return
         for off in range(0, flat_grad.numel(), self.bucket_elems):
             dist.all_reduce(flat_grad[off:off + self.bucket_elems])
-
-
-_warned = [False]
-
-
-def make_reducer(world_size: int, mode: str = "fused", store=None, optim=None):
-    if world_size <= 1:
-        return None
-    if mode == "fused":
-        try:
-            from .symmetric import FusedAllReduceAdam
-            if store is not None and optim is not None:
-                return FusedAllReduceAdam(store, optim)
-        except Exception as exc:  # noqa: BLE001
-            if not _warned[0] and (not dist.is_initialized() or dist.get_rank() == 0):
-                print("[ddp] fused peer-memory reducer unavailable (%r); using NCCL all-reduce" % (exc,), flush=True)
-                _warned[0] = True
-    return NcclReducer(world_size)

@@ -169,7 +169,15 @@ class TrainEngine:
         if update:
             from ..utils.tracing import nvtx_range
             with nvtx_range("reduce+optimizer", bool(getattr(self.opt, "trace_nvtx", False))):
-                if self.reducer is not None:
+                if self.reducer is not None and not self.optim.fused:
+                    # torch.optim path (CPU / gloo ranks, optimisers without a flat kernel): autograd left the gradients
+                    # in p.grad; move them into the flat buffer, reduce that, and hand the optimiser views of it
+                    self.store.gather_autograd_grads()
+                    self.reducer(self.store.grad)
+                    for p in self.store.params:
+                        if p.requires_grad:
+                            p.grad = p.main_grad
+                elif self.reducer is not None:
                     self.reducer(self.store.grad)
                 self.optim.step(self.grad_scale)
             if not self.optim.fused:
