@@ -13,6 +13,13 @@ PAD, UNK, BOS, EOS = 0, 1, 2, 3
 PAD_WORD, UNK_WORD, BOS_WORD, EOS_WORD = "<blank>", "<unk>", "<s>", "</s>"
 
 
+# the options that name the special tokens of each dictionary (mBART / DeltaLM vocabularies use <pad>, </s>, ...)
+_SPECIAL_WORD_OPTIONS = {
+    "src": {"pad": "src_pad_word", "unk": "src_unk_word", "bos": "src_bos_word", "eos": "src_eos_word"},
+    "tgt": {"pad": "tgt_pad_word", "unk": "tgt_unk_word", "bos": "tgt_bos_word", "eos": "tgt_eos_word"},
+}
+
+
 @dataclass
 class Constants:
     PAD: int = PAD
@@ -46,8 +53,9 @@ class Constants:
             d = dicts.get(side) if isinstance(dicts, dict) else None
             if d is None or not hasattr(d, "lookup"):
                 continue
+            words = _SPECIAL_WORD_OPTIONS[side]
             for tok, default_word in (("pad", PAD_WORD), ("unk", UNK_WORD), ("bos", BOS_WORD), ("eos", EOS_WORD)):
-                word = getattr(opt, "%s_%s_word" % (side, tok), default_word)
+                word = getattr(opt, words[tok], default_word)
                 idx = d.lookup(word)
                 if idx is not None:
                     setattr(c, "%s_%s" % (key, tok.upper()), idx)

@@ -2,8 +2,9 @@
 
 A registry maps the reference's model names (onmt/model_factory.py:102-731) to builder functions so that
 families can be added without touching a central if-chain.  ``build_model`` is the single entry point used
-by trainers and translators; ``init_model_parameters`` and ``optimize_model`` exist for API parity (models
-initialise themselves and are born with fused projections).
+by trainers and translators: it validates the options, builds the model, applies ``-init`` / ``-init_embedding``,
+loads pretrained sub-modules (``-enc_state_dict``, ``-dec_state_dict``, ``-wav2vec2_pretrained_model``) and freezes
+what the ``-freeze_*`` options name.  ``optimize_model`` exists for API parity (projections are born fused).
 """
 from __future__ import annotations
 
@@ -29,7 +30,13 @@ def build_model(opt, dicts, remove_pretrain: bool = False, constants=None):
         return _REGISTRY["transformer_xl_lm"](opt, dicts)
     if name not in _REGISTRY:
         raise NotImplementedError("unknown model %r; registered: %s" % (name, sorted(_REGISTRY)))
+    from ..options import validate_model_options
+    validate_model_options(opt)
     model = _REGISTRY[name](opt, dicts)
+    init_model_parameters(model, opt)
+    if not remove_pretrain:          # a full checkpoint is about to be loaded: its weights replace the pretrained ones
+        load_pretrained_parts(model, opt, dicts)
+    apply_freeze_options(model, opt)
     aux = dicts.get("aux_tgt") if hasattr(dicts, "get") else None
     if aux is not None and getattr(model, "ctc_linear", None) is not None:
         # "triangle" corpora: the CTC head predicts the auxiliary target (the transcript), which has its own vocabulary
@@ -50,13 +57,94 @@ def build_classifier(opt, dicts):
 
 
 def init_model_parameters(model, opt):
-    """Models of this framework initialise their own weights at construction; kept for API parity."""
+    """Re-initialise a freshly built model the way ``-init`` / ``-init_embedding`` / ``-param_init`` ask for
+    (reference: onmt/model_factory.py:734-872): ``-init normal`` draws matrices from N(0, 2 / (fan_in + fan_out)),
+    ``-init uniform`` uses Xavier-uniform (or U(-param_init, param_init) when ``-param_init`` is set below 0.1 on
+    purpose); embeddings are N(0, d^-0.5) (``normal``), N(0, 0.01) (``fixed``) or U(-d^-0.5, d^-0.5) (``uniform``);
+    biases start at zero and LayerNorm at (1, 0).  With the default options the models' own construction-time
+    initialisation already is this scheme, so the call only acts when an option departs from its default."""
+    import math
+    import torch
+    import torch.nn as nn
+    from .layers import Embedding, LayerNorm, Linear
+    init = getattr(opt, "init", "normal")
+    init_emb = getattr(opt, "init_embedding", "normal")
+    param_init = float(getattr(opt, "param_init", 0.1))
+    if init == "normal" and init_emb == "normal" and param_init == 0.1:
+        return model
+    d = int(getattr(opt, "model_size", 512))
+    std_emb = d ** -0.5 if not getattr(opt, "rezero", False) else 0.05
+    with torch.no_grad():
+        for m in model.modules():
+            if isinstance(m, (Linear, nn.Linear)):
+                w = m.weight
+                if init == "uniform":
+                    if param_init != 0.1:
+                        nn.init.uniform_(w, -param_init, param_init)
+                    else:
+                        nn.init.xavier_uniform_(w)
+                else:
+                    nn.init.normal_(w, 0.0, math.sqrt(2.0 / (w.shape[0] + w.shape[1])))
+                if getattr(m, "bias", None) is not None:
+                    m.bias.zero_()
+            elif isinstance(m, (Embedding, nn.Embedding)):
+                if init_emb == "normal":
+                    nn.init.normal_(m.weight, 0.0, std_emb)
+                elif init_emb == "fixed":
+                    nn.init.normal_(m.weight, 0.0, 0.01)
+                else:
+                    nn.init.uniform_(m.weight, -std_emb, std_emb)
+            elif isinstance(m, (LayerNorm, nn.LayerNorm)):
+                m.weight.fill_(1.0)
+                m.bias.zero_()
     return model
 
 
 def optimize_model(model, distributed: bool = False):
     """Projections are created fused (qkv / kv); nothing to convert."""
     return model
+
+
+_FREEZE_RULES = (
+    # option, (substrings of parameter names that it freezes; "enc:" / "dec:" restrict to one side)
+    ("freeze_encoder", ("enc:",)),
+    ("freeze_decoder", ("dec:",)),
+    ("freeze_embedding", ("embed.", "generator.", "word_lut")),
+    ("freeze_encoder_self_attn", ("enc:.attn.", "enc:.attn_norm.")),
+    ("freeze_encoder_ffn", ("enc:.ffn.", "enc:.ffn_norm.", "enc:.mcr_ffn.")),
+    ("freeze_decoder_self_attn", ("dec:.self_attn.", "dec:.self_norm.")),
+    ("freeze_decoder_ffn", ("dec:.ffn.", "dec:.ffn_norm.", "dec:.mid_ffn.", "dec:.mcr_ffn.")),
+    ("freeze_cross_attention", ("dec:.cross_attn.", "dec:.cross_norm.")),
+)
+
+
+def apply_freeze_options(model, opt) -> int:
+    """``-freeze_encoder``, ``-freeze_decoder``, ``-freeze_embedding`` and the per-sub-layer variants: switch off the
+    gradients of the named parameter groups (reference: onmt/model_factory.py:333-377 and the ``freeze_*`` checks in
+    the wav2vec2 / mBART wrappers).  Returns the number of parameters frozen."""
+    frozen = 0
+    for flag, patterns in _FREEZE_RULES:
+        if not getattr(opt, flag, False):
+            continue
+        for name, p in model.named_parameters():
+            side = "enc:" if name.startswith("encoder.") else ("dec:" if name.startswith("decoder.") else "")
+            for pat in patterns:
+                if pat.startswith(("enc:", "dec:")):
+                    if side != pat[:4] or pat[4:] not in name:
+                        continue
+                elif pat not in name:
+                    continue
+                if p.requires_grad:
+                    p.requires_grad_(False)
+                    frozen += p.numel()
+                break
+    return frozen
+
+
+def load_pretrained_parts(model, opt, dicts=None):
+    """Pretrained sub-modules named on the command line (see ``models/pretrained_io.py``)."""
+    from .pretrained_io import load_pretrained_parts as _load
+    return _load(model, opt, dicts)
 
 
 _loaded = [False]

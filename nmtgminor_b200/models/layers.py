@@ -290,16 +290,25 @@ def _cached_attention(q, k, v, heads, key_pad_mask):
 
 
 class FeedForward(nn.Module):
-    """``residual + D(fc2(D(act(fc1(x)))))`` executed as two GEMMs with fused epilogues."""
+    """``residual + D(fc2(D(act(fc1(x)))))`` executed as two GEMMs with fused epilogues.  ``glu`` (``-ffn_glu``): fc1 is
+    twice as wide and the hidden state is ``act(first half) * second half`` (reference:
+    onmt/modules/optimized/feed_forward.py:181-184)."""
 
-    def __init__(self, dim: int, inner: int, dropout: float = 0.0, activation: str = "relu"):
+    def __init__(self, dim: int, inner: int, dropout: float = 0.0, activation: str = "relu", glu: bool = False):
         super().__init__()
-        self.fc1 = Linear(dim, inner)
+        self.fc1 = Linear(dim, inner * (2 if glu else 1))
         self.fc2 = Linear(inner, dim)
         self.dropout = dropout
         self.activation = activation
+        self.glu = glu
 
     def forward(self, x, residual=None, dropout_p: float = 0.0):
+        if self.glu:
+            h, gate = self.fc1(x).chunk(2, dim=-1)
+            from ..ops.reference import _act
+            h = (_act(h.float(), ops.ACT_IDS[self.activation]) * gate.float()).to(x.dtype)
+            h = ops.dropout_add(h.contiguous(), None, self.dropout, self.training)
+            return self.fc2(h, dropout_p=dropout_p, residual=residual)
         return ops.mlp(x, self.fc1.weight, self.fc1.bias, self.fc2.weight, self.fc2.bias, self.activation, self.dropout,
                        dropout_p, residual, self.training)
 
@@ -314,41 +323,79 @@ def _sub(layer, fn, inp, residual, p, seqs, *args):
     return fn(inp, *args, residual=residual, dropout_p=p)
 
 
-class EncoderLayer(nn.Module):
+def _scaled_sub(layer, fn, inp, residual, p, seqs, *args, scale=None):
+    """``residual + scale * D(fn(inp))`` with ``scale`` a float (the half steps of a macaron block) or a learned scalar
+    (``-rezero``: starts at zero, no LayerNorm in front).  Outside the fused residual epilogue, which cannot scale."""
+    y = fn(inp, *args, residual=None, dropout_p=p)
+    return residual + (y.float() * scale).to(y.dtype)
+
+
+class _LayerOptions:
+    """Structure switches shared by encoder and decoder layers (reference: onmt/models/transformer_layers.py:83-351):
+    ``post_norm`` LayerNorm after the residual sum, ``rezero`` learned residual gates instead of LayerNorm
+    (pre_post_processing.py:77-80), ``macaron`` an extra feed-forward half step in front of the attention with both
+    feed-forward blocks scaled by 1/2, ``glu`` gated feed-forward."""
+
+    def _init_options(self, dim, inner, fd, activation, post_norm, rezero, macaron, glu):
+        self.post_norm, self.rezero, self.macaron = post_norm, rezero, macaron
+        self.ffn_scale = 0.5 if macaron else None
+        if macaron:
+            self.mcr_norm = LayerNorm(dim)
+            self.mcr_ffn = FeedForward(dim, inner, fd, activation, glu=glu)
+        if rezero:
+            # one residual gate per sub-layer: 0 self-attention, 1 feed-forward, 2 macaron feed-forward,
+            # 3 encoder-decoder attention, 4 interleaved feed-forward (unused entries stay at zero)
+            self.gates = nn.Parameter(torch.zeros(5))
+
+    def _block(self, idx, norm, fn, x, p, seqs, *args, scale=None):
+        """One residual sub-layer under the layer's structure switches; ``idx`` picks the rezero gate."""
+        if self.rezero:
+            g = self.gates[idx] if scale is None else self.gates[idx] * scale
+            return _scaled_sub(self, fn, x, x, p, seqs, *args, scale=g)
+        if self.post_norm:
+            y = _sub(self, fn, x, x, p, seqs, *args) if scale is None else _scaled_sub(self, fn, x, x, p, seqs, *args, scale=scale)
+            return norm(y)
+        x, h = norm.with_residual(x)
+        if scale is None:
+            return _sub(self, fn, h, x, p, seqs, *args)
+        return _scaled_sub(self, fn, h, x, p, seqs, *args, scale=scale)
+
+
+class EncoderLayer(nn.Module, _LayerOptions):
     """Self-attention + FFN block.  Pre-LN: x += D(Attn(LN(x))); x += D(FFN(LN(x))).  Post-LN (``post_norm``):
-    x = LN(x + D(Attn(x))); x = LN(x + D(FFN(x))).  Optional stochastic depth (``death_rate``)."""
+    x = LN(x + D(Attn(x))); x = LN(x + D(FFN(x))).  Optional stochastic depth (``death_rate``), ``rezero``, ``macaron``
+    and gated feed-forward (``glu``)."""
 
     def __init__(self, dim, heads, inner, dropout=0.1, attn_dropout=0.1, activation="relu", attn_bias=False,
-                 death_rate=0.0, ffn_dropout=None, post_norm=False):
+                 death_rate=0.0, ffn_dropout=None, post_norm=False, rezero=False, macaron=False, glu=False):
         super().__init__()
+        fd = dropout if ffn_dropout is None else ffn_dropout
         self.attn_norm = LayerNorm(dim)
         self.attn = SelfAttention(dim, heads, attn_dropout, bias=attn_bias)
         self.ffn_norm = LayerNorm(dim)
-        self.ffn = FeedForward(dim, inner, dropout if ffn_dropout is None else ffn_dropout, activation)
+        self.ffn = FeedForward(dim, inner, fd, activation, glu=glu)
         self.dropout = dropout
         self.death_rate = death_rate
-        self.post_norm = post_norm
+        self._init_options(dim, inner, fd, activation, post_norm, rezero, macaron, glu)
 
     def forward(self, x, seqs: PackedSeqs):
         if self.training and self.death_rate > 0 and torch.rand(1).item() < self.death_rate:
             return x
         p = self.dropout
-        if self.post_norm:
-            x = self.attn_norm(_sub(self, self.attn, x, x, p, seqs, seqs))
-            return self.ffn_norm(_sub(self, self.ffn, x, x, p, seqs))
-        x, h = self.attn_norm.with_residual(x)
-        x = _sub(self, self.attn, h, x, p, seqs, seqs)
-        x, h = self.ffn_norm.with_residual(x)
-        return _sub(self, self.ffn, h, x, p, seqs)
+        if self.macaron:
+            x = self._block(2, self.mcr_norm, self.mcr_ffn, x, p, seqs, scale=0.5)
+        x = self._block(0, self.attn_norm, self.attn, x, p, seqs, seqs)
+        return self._block(1, self.ffn_norm, self.ffn, x, p, seqs, scale=self.ffn_scale)
 
 
-class DecoderLayer(nn.Module):
+class DecoderLayer(nn.Module, _LayerOptions):
     """Causal self-attention, encoder-decoder attention and FFN (pre- or post-LN).  ``interleaved_ffn`` adds a
-    second FFN between the two attentions (the DeltaLM decoder layout)."""
+    second FFN between the two attentions (the DeltaLM decoder layout); ``rezero`` / ``macaron`` / ``glu`` as in the
+    encoder layer."""
 
     def __init__(self, dim, heads, inner, dropout=0.1, attn_dropout=0.1, activation="relu", attn_bias=False,
                  death_rate=0.0, ffn_dropout=None, ignore_source=False, post_norm=False, interleaved_ffn=False,
-                 kv_dim=None):
+                 kv_dim=None, rezero=False, macaron=False, glu=False):
         super().__init__()
         fd = dropout if ffn_dropout is None else ffn_dropout
         self.self_norm = LayerNorm(dim)
@@ -356,40 +403,33 @@ class DecoderLayer(nn.Module):
         self.ignore_source = ignore_source
         if interleaved_ffn:
             self.mid_norm = LayerNorm(dim)
-            self.mid_ffn = FeedForward(dim, inner, fd, activation)
+            self.mid_ffn = FeedForward(dim, inner, fd, activation, glu=glu)
         self.interleaved_ffn = interleaved_ffn
         if not ignore_source:
             self.cross_norm = LayerNorm(dim)
             self.cross_attn = CrossAttention(dim, heads, attn_dropout, bias=attn_bias, kv_dim=kv_dim)
         self.ffn_norm = LayerNorm(dim)
-        self.ffn = FeedForward(dim, inner, fd, activation)
+        self.ffn = FeedForward(dim, inner, fd, activation, glu=glu)
         self.dropout = dropout
         self.death_rate = death_rate
-        self.post_norm = post_norm
+        self._init_options(dim, inner, fd, activation, post_norm, rezero, macaron, glu)
 
     def forward(self, x, seqs: PackedSeqs, memory, mem_seqs: PackedSeqs):
         if self.training and self.death_rate > 0 and torch.rand(1).item() < self.death_rate:
             return x
         p = self.dropout
-        if self.post_norm:
-            x = self.self_norm(_sub(self, self.self_attn, x, x, p, seqs, seqs))
-            if self.interleaved_ffn:
-                x = self.mid_norm(_sub(self, self.mid_ffn, x, x, p, seqs))
-            if not self.ignore_source:
-                x = self.cross_norm(_sub(self, self.cross_attn, x, x, p, seqs, seqs, memory, mem_seqs))
-            return self.ffn_norm(_sub(self, self.ffn, x, x, p, seqs))
-        x, h = self.self_norm.with_residual(x)
-        x = _sub(self, self.self_attn, h, x, p, seqs, seqs)
+        if self.macaron:
+            x = self._block(2, self.mcr_norm, self.mcr_ffn, x, p, seqs, scale=0.5)
+        x = self._block(0, self.self_norm, self.self_attn, x, p, seqs, seqs)
         if self.interleaved_ffn:
-            x, h = self.mid_norm.with_residual(x)
-            x = _sub(self, self.mid_ffn, h, x, p, seqs)
+            x = self._block(4, self.mid_norm, self.mid_ffn, x, p, seqs)
         if not self.ignore_source:
-            x, h = self.cross_norm.with_residual(x)
-            x = _sub(self, self.cross_attn, h, x, p, seqs, seqs, memory, mem_seqs)
-        x, h = self.ffn_norm.with_residual(x)
-        return _sub(self, self.ffn, h, x, p, seqs)
+            x = self._block(3, self.cross_norm, self.cross_attn, x, p, seqs, seqs, memory, mem_seqs)
+        return self._block(1, self.ffn_norm, self.ffn, x, p, seqs, scale=self.ffn_scale)
 
     def step(self, x, cache: dict, mem_mask):
+        if self.rezero or self.macaron:
+            return self._step_general(x, cache, mem_mask)
         if self.post_norm:
             x = self.self_norm(x + self.self_attn.step(x, cache))
             if self.interleaved_ffn:
@@ -403,6 +443,30 @@ class DecoderLayer(nn.Module):
         if not self.ignore_source:
             x = self.cross_attn.step(self.cross_norm(x), cache, mem_mask, residual=x)
         return self.ffn(self.ffn_norm(x), residual=x)
+
+
+def _decoder_step_general(self, x, cache: dict, mem_mask):
+    """Incremental step for the structure switches that the fast paths above do not cover (rezero gates, macaron)."""
+    def blk(idx, norm, fn, x, scale=None):
+        if self.rezero:
+            g = self.gates[idx] if scale is None else self.gates[idx] * scale
+            return x + (fn(x).float() * g).to(x.dtype)
+        if self.post_norm:
+            y = fn(x)
+            return norm(x + (y if scale is None else (y.float() * scale).to(y.dtype)))
+        y = fn(norm(x))
+        return x + (y if scale is None else (y.float() * scale).to(y.dtype))
+    if self.macaron:
+        x = blk(2, self.mcr_norm, lambda h: self.mcr_ffn(h), x, 0.5)
+    x = blk(0, self.self_norm, lambda h: self.self_attn.step(h, cache), x)
+    if self.interleaved_ffn:
+        x = blk(4, self.mid_norm, lambda h: self.mid_ffn(h), x)
+    if not self.ignore_source:
+        x = blk(3, self.cross_norm, lambda h: self.cross_attn.step(h, cache, mem_mask), x)
+    return blk(1, self.ffn_norm, lambda h: self.ffn(h), x, self.ffn_scale)
+
+
+DecoderLayer._step_general = _decoder_step_general
 
 
 def pack_padded(x_bt, lengths, capacity=None):

@@ -61,10 +61,11 @@ def _cfg(cfg, names, default):
 
 class PretrainedStyleDecoder(nn.Module):
     def __init__(self, family: str, vocab: int, dim: int, layers: int, heads: int, ffn: int, dropout=0.1, attn_dropout=0.0,
-                 max_positions=1024, pad_idx=1, layerdrop=0.0, kv_dim=None):
+                 max_positions=1024, pad_idx=1, layerdrop=0.0, kv_dim=None, emb_dropout=None, word_dropout=0.0):
         super().__init__()
         f = FAMILY_DEFAULTS[family]
         self.family = family
+        self.emb_dropout = dropout if emb_dropout is None else emb_dropout
         self.embed = Embedding(vocab, dim, pad_idx, scale=math.sqrt(dim) if f["scale"] else 1.0, max_pos=max_positions,
                                learned_pos=f["learned_pos"], pos_offset=f["pos_offset"])
         self.emb_norm = LayerNorm(dim) if f["emb_norm"] else None
@@ -74,11 +75,12 @@ class PretrainedStyleDecoder(nn.Module):
             for _ in range(layers)])
         self.final_norm = LayerNorm(dim) if f["final_norm"] else None
         self.dropout = dropout
+        self.embed.word_dropout = word_dropout
 
     def _embed(self, seqs: PackedSeqs):
         if self.emb_norm is None:
-            return self.embed(seqs, self.dropout)
-        return ops.dropout_add(self.emb_norm(self.embed(seqs, 0.0)), None, self.dropout, self.training)
+            return self.embed(seqs, self.emb_dropout)
+        return ops.dropout_add(self.emb_norm(self.embed(seqs, 0.0)), None, self.emb_dropout, self.training)
 
     def forward(self, tgt: PackedSeqs, memory, src: PackedSeqs):
         x = self._embed(tgt)
@@ -138,13 +140,19 @@ def _encoder_family(opt) -> str:
 def build_pretrained_decoder(opt, vocab: int, family: Optional[str] = None, kv_dim=None) -> PretrainedStyleDecoder:
     fam = family or _decoder_family(opt)
     cfg = load_json_config(getattr(opt, "dec_config_file", ""))
-    dim = _cfg(cfg, ["d_model", "decoder_embed_dim", "hidden_size"], opt.model_size)
+    dim = _cfg(cfg, ["d_model", "decoder_embed_dim", "hidden_size"],
+               opt.dec_pretrain_hidden_size if getattr(opt, "dec_pretrain_hidden_size", 768) != 768 else opt.model_size)
     return PretrainedStyleDecoder(
         fam, _cfg(cfg, ["vocab_size"], vocab), dim,
         _cfg(cfg, ["decoder_layers", "num_hidden_layers"], opt.layers),
         _cfg(cfg, ["decoder_attention_heads", "num_attention_heads"], opt.n_heads),
         _cfg(cfg, ["decoder_ffn_dim", "decoder_ffn_embed_dim", "intermediate_size"], opt.inner_size),
-        dropout=opt.dropout, attn_dropout=opt.attn_dropout,
+        # -dec_pretrain_hidden_dropout / -dec_pretrain_attn_dropout override the shared rates for a pretrained-style decoder
+        # when they are moved off their defaults (reference: onmt/model_factory.py:636-644)
+        dropout=opt.dec_pretrain_hidden_dropout if getattr(opt, "dec_pretrain_hidden_dropout", 0.1) != 0.1 else opt.dropout,
+        attn_dropout=opt.dec_pretrain_attn_dropout if getattr(opt, "dec_pretrain_attn_dropout", 0.1) != 0.1 else opt.attn_dropout,
+        emb_dropout=getattr(opt, "dec_pretrain_emb_dropout", 0.1) if getattr(opt, "dec_pretrain_emb_dropout", 0.1) != 0.1 else None,
+        word_dropout=float(getattr(opt, "dec_pretrain_word_dropout", 0.0) or 0.0),
         max_positions=_cfg(cfg, ["max_position_embeddings", "max_target_positions"], 1024),
         pad_idx=_cfg(cfg, ["pad_token_id"], getattr(opt, "pad_idx", 1)), layerdrop=getattr(opt, "death_rate", 0.0), kv_dim=kv_dim)
 
@@ -190,7 +198,81 @@ def ctc_compress(context, seqs: PackedSeqs, logits, mode: str = "avg"):
     return out, new_seqs
 
 
-class SpeechToTextModel(Seq2SeqBase):
+class _ReferenceNaming:
+    """Checkpoints of these families are written with the reference's parameter names and its fused-attention layout
+    (``decoder.layers.3.self_attn.proj_weight`` ..., see ``pretrained_io``), and files written by the reference - or
+    pretrained files in Hugging Face / fairseq naming - load back through the same maps."""
+
+    def _io_parts(self):
+        from . import pretrained_io as io
+        enc, dec = self.encoder, self.decoder
+        inter = any(getattr(l, "interleaved_ffn", False) for l in getattr(dec, "layers", []))
+        speech = hasattr(enc, "extractor")
+        # the reference keeps the fairseq model inside a wrapper module (onmt/models/speech_recognizer/wav2vec2.py:165)
+        enc_prefix = "encoder.wav2vec_encoder." if speech else "encoder."
+        return io, enc, dec, inter, speech, enc_prefix
+
+    def to_reference_state_dict(self, sd):
+        io, enc, dec, inter, speech, enc_prefix = self._io_parts()
+        f32 = lambda t: t.detach().float().cpu().clone()
+        sd = {k: f32(v) for k, v in sd.items()}
+        e = {k[len("encoder."):]: v for k, v in sd.items() if k.startswith("encoder.")}
+        d = {k[len("decoder."):]: v for k, v in sd.items() if k.startswith("decoder.")}
+        out = {}
+        if speech:
+            conv = io.wav2vec2_to_reference(e, io._heads_of(enc), getattr(enc.extractor, "mode", "layer_norm") == "layer_norm")
+        else:
+            conv = io.text_encoder_to_reference(e, io._heads_of(enc))
+        covered = set()
+        for k, v in conv.items():
+            out[enc_prefix + k] = v
+        back = io.wav2vec2_to_native(conv, io._heads_of(enc)) if speech else (
+            io.whisper_encoder_to_native(conv, io._heads_of(enc)) if hasattr(enc, "conv1") else io.text_encoder_to_native(conv, io._heads_of(enc)))
+        covered.update("encoder." + k for k in back)
+        dconv = io.decoder_to_reference(d, io._heads_of(dec), inter)
+        for k, v in dconv.items():
+            out["decoder." + k] = v
+        covered.update("decoder." + k for k in io.decoder_to_native(dconv, io._heads_of(dec), inter))
+        if "generator.weight" in sd:
+            out["generator.0.linear.weight"] = sd["generator.weight"]
+            covered.add("generator.weight")
+        if "generator.bias" in sd:
+            out["generator.0.linear.bias"] = sd["generator.bias"]
+            covered.add("generator.bias")
+        for k, v in sd.items():           # anything without a counterpart in the reference keeps its own name
+            if k not in covered and k not in out:
+                out[k] = v
+        return out
+
+    def from_reference_state_dict(self, ref_sd, target_keys=None):
+        io, enc, dec, inter, speech, _ = self._io_parts()
+        out = {}
+        e = {k: v for k, v in ref_sd.items() if k.startswith("encoder.")}
+        d = {k[len("decoder."):]: v for k, v in ref_sd.items() if k.startswith("decoder.")}
+        if speech:
+            e = {k[len("encoder."):]: v for k, v in e.items()}
+            native = io.wav2vec2_to_native(e, io._heads_of(enc))
+        elif hasattr(enc, "conv1"):
+            native = io.whisper_encoder_to_native(e, io._heads_of(enc))
+        else:
+            native = io.text_encoder_to_native(e, io._heads_of(enc))
+        for k, v in native.items():
+            out["encoder." + k] = v
+        for k, v in io.decoder_to_native(d, io._heads_of(dec), inter).items():
+            out["decoder." + k] = v
+        for a, b in (("generator.0.linear.weight", "generator.weight"), ("generator.0.linear.bias", "generator.bias")):
+            if a in ref_sd:
+                out[b] = ref_sd[a]
+        if "generator.weight" not in out and "decoder.embed.weight" in out:
+            out["generator.weight"] = out["decoder.embed.weight"]
+        keys = set(target_keys) if target_keys is not None else None
+        for k, v in ref_sd.items():       # native-named extras (CTC head, adapters ...)
+            if k not in out and (keys is None or k in keys):
+                out[k] = v
+        return out
+
+
+class SpeechToTextModel(Seq2SeqBase, _ReferenceNaming):
     """Audio encoder + text decoder with optional CTC head on the encoder states (``-ctc_loss``)."""
 
     def __init__(self, opt, encoder: nn.Module, decoder: nn.Module, vocab: int, generator_bias: bool = True, tie: bool = True):
@@ -240,7 +322,7 @@ class SpeechToTextModel(Seq2SeqBase):
         return self.ctc_weight * ctc
 
 
-class TextToTextPretrained(Seq2SeqBase):
+class TextToTextPretrained(Seq2SeqBase, _ReferenceNaming):
     """``pretrain_transformer``: pretrained-style text encoder + decoder (mBART, DeltaLM, M2M-100, BART ...)."""
 
     def __init__(self, opt, dicts):
@@ -291,6 +373,7 @@ def _wav2vec_from_opt(opt):
         heads=_cfg(cfg, ["encoder_attention_heads", "num_attention_heads"], 12 if base else 16),
         ffn=_cfg(cfg, ["encoder_ffn_embed_dim", "intermediate_size"], 3072 if base else 4096),
         dropout=getattr(opt, "enc_pretrain_hidden_dropout", opt.dropout) if hasattr(opt, "enc_pretrain_hidden_dropout") else opt.dropout,
+        dropout_input=float(getattr(opt, "enc_pretrain_emb_dropout", 0.0) or 0.0),
         attn_dropout=opt.attn_dropout, layer_norm_first=_cfg(cfg, ["layer_norm_first"], not base),
         extractor_mode=_cfg(cfg, ["extractor_mode"], "default" if base else "layer_norm"),
         conv_bias=_cfg(cfg, ["conv_bias"], not base),

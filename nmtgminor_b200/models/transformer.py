@@ -24,10 +24,63 @@ from ..modules.dropout import checkpointed
 from .layers import DecoderLayer, Embedding, EncoderLayer, LayerNorm, PackedSeqs
 
 
-def _apply_regularisation_options(stack, opt):
+def layer_structure_kwargs(opt) -> dict:
+    """``-post_norm`` / ``-rezero`` / ``-macaron`` / ``-ffn_glu`` as keyword arguments of the shared layer classes."""
+    return dict(post_norm=bool(getattr(opt, "post_norm", False)), rezero=bool(getattr(opt, "rezero", False)),
+                macaron=bool(getattr(opt, "macaron", False)), glu=bool(getattr(opt, "ffn_glu", False)))
+
+
+class LanguageEmbedding(nn.Module):
+    """``-use_language_embedding``: one vector per language id, added to every position of a sentence
+    (``-language_embedding_type sum | all_sum``) or concatenated and projected back (``concat``); reference:
+    onmt/models/transformers.py:196-202 (encoder), :310-327 (decoder)."""
+
+    def __init__(self, n_languages: int, dim: int, kind: str = "sum"):
+        super().__init__()
+        self.table = nn.Embedding(max(int(n_languages), 1), dim)
+        nn.init.normal_(self.table.weight, 0.0, dim ** -0.5)
+        self.kind = kind
+        self.proj = nn.Linear(2 * dim, dim) if kind == "concat" else None
+
+    def forward(self, x, seqs: PackedSeqs, lang_ids):
+        """x ``[tokens, H]``; ``lang_ids`` ``[B]`` (or one id for the whole batch)."""
+        if lang_ids is None:
+            return x
+        lengths = (seqs.cu[1:] - seqs.cu[:-1]).to(torch.int64)
+        ids = lang_ids.to(x.device).view(-1)
+        if ids.numel() == 1:
+            ids = ids.expand(lengths.numel())
+        ids = ids[:lengths.numel()]
+        if ids.numel() < lengths.numel():          # static batch capacity: the extra sentences are empty
+            ids = torch.cat([ids, ids.new_zeros(lengths.numel() - ids.numel())])
+        per_token = torch.repeat_interleave(self.table(ids), lengths, dim=0, output_size=None)
+        if per_token.shape[0] < x.shape[0]:        # rows past the last sentence of a packed buffer
+            per_token = torch.cat([per_token, per_token.new_zeros(x.shape[0] - per_token.shape[0], per_token.shape[1])])
+        if self.kind == "concat":
+            return self.proj(torch.cat([x.float(), per_token.float()], dim=-1)).to(x.dtype)
+        return x + per_token.to(x.dtype)
+
+
+def _n_languages(dicts) -> int:
+    langs = dicts.get("langs") if hasattr(dicts, "get") else None
+    return len(langs) if langs else 1
+
+
+def _embed_with_language(stack, seqs: PackedSeqs, lang_ids):
+    """Embedding (+ language vector) + embedding dropout.  Without language embeddings this is the one fused kernel."""
+    if stack.language_embedding is None or lang_ids is None:
+        return stack.embed(seqs, stack.emb_dropout)
+    x = stack.language_embedding(stack.embed(seqs, 0.0), seqs, lang_ids)
+    return ops.dropout_add(x.contiguous(), None, stack.emb_dropout, stack.training)
+
+
+def _apply_regularisation_options(stack, opt, side: str = "enc"):
     """``-variational_dropout`` (time-shared masks on the residual branches), ``-word_dropout`` (vocabulary-level
-    dropout in the embedding) and ``-checkpointing N`` (recompute the first N layers in backward) for a layer stack."""
+    dropout in the embedding), ``-checkpointing N`` (recompute the first N layers in backward) and
+    ``-enc_gradient_checkpointing`` / ``-dec_gradient_checkpointing`` (recompute every layer of that stack)."""
     stack.checkpointing = int(getattr(opt, "checkpointing", 0) or 0)
+    if getattr(opt, "%s_gradient_checkpointing" % side, False):
+        stack.checkpointing = 10 ** 6
     for layer in stack.layers:
         layer.variational = bool(getattr(opt, "variational_dropout", False))
     stack.embed.word_dropout = float(getattr(opt, "word_dropout", 0.0) or 0.0)
@@ -47,10 +100,12 @@ class TransformerEncoder(nn.Module):
         self.layers = nn.ModuleList([
             EncoderLayer(opt.model_size, opt.n_heads, opt.inner_size, opt.dropout, opt.attn_dropout, opt.ffn_activation,
                          attn_bias=getattr(opt, "attn_bias", False), death_rate=rates[i],
-                         ffn_dropout=opt.ffn_dropout if getattr(opt, "ffn_dropout", -1) >= 0 else None)
+                         ffn_dropout=opt.ffn_dropout if getattr(opt, "ffn_dropout", -1) >= 0 else None,
+                         **layer_structure_kwargs(opt))
             for i in range(n)])
         self.final_norm = LayerNorm(opt.model_size)
-        _apply_regularisation_options(self, opt)
+        self.language_embedding = None
+        _apply_regularisation_options(self, opt, "enc")
         self.reversible = None
         if getattr(opt, "src_reversible", False):
             # activations are reconstructed in backward instead of stored (reference: onmt/reversible_models)
@@ -59,8 +114,8 @@ class TransformerEncoder(nn.Module):
             self.reversible = ReversibleStack(n, opt.model_size, opt.n_heads, opt.inner_size, opt.dropout, opt.attn_dropout,
                                               opt.ffn_activation)
 
-    def forward(self, src: PackedSeqs):
-        x = self.embed(src, self.emb_dropout)
+    def forward(self, src: PackedSeqs, lang_ids=None):
+        x = _embed_with_language(self, src, lang_ids)
         if self.reversible is not None:
             return self.reversible(x, src)
         for i, layer in enumerate(self.layers):
@@ -76,15 +131,18 @@ class TransformerDecoder(nn.Module):
         super().__init__()
         self.embed = embed
         self.emb_dropout = opt.emb_dropout
-        rates = _expected_death_rates(opt.layers, getattr(opt, "death_rate", 0.0))
+        # -death_rate_decoder overrides the shared -death_rate for this stack
+        dr = getattr(opt, "death_rate_decoder", 0.0) or getattr(opt, "death_rate", 0.0)
+        rates = _expected_death_rates(opt.layers, dr)
         self.layers = nn.ModuleList([
             DecoderLayer(opt.model_size, opt.n_heads, opt.inner_size, opt.dropout, opt.attn_dropout, opt.ffn_activation,
                          attn_bias=getattr(opt, "attn_bias", False), death_rate=rates[i],
                          ffn_dropout=opt.ffn_dropout if getattr(opt, "ffn_dropout", -1) >= 0 else None,
-                         ignore_source=ignore_source)
+                         ignore_source=ignore_source, **layer_structure_kwargs(opt))
             for i in range(opt.layers)])
         self.final_norm = LayerNorm(opt.model_size)
-        _apply_regularisation_options(self, opt)
+        self.language_embedding = None
+        _apply_regularisation_options(self, opt, "dec")
         self.reversible = None
         if getattr(opt, "tgt_reversible", False) and not ignore_source:
             from .reversible import ReversibleStack
@@ -94,8 +152,8 @@ class TransformerDecoder(nn.Module):
                                               opt.attn_dropout, opt.ffn_activation, causal=True, cross=True)
             self.layers = self.reversible.layers      # decoding state set-up walks the layers (cross-attention caches)
 
-    def forward(self, tgt: PackedSeqs, memory, src: PackedSeqs):
-        x = self.embed(tgt, self.emb_dropout)
+    def forward(self, tgt: PackedSeqs, memory, src: PackedSeqs, lang_ids=None):
+        x = _embed_with_language(self, tgt, lang_ids)
         if self.reversible is not None:
             return self.reversible(x, tgt, memory, src)
         for i, layer in enumerate(self.layers):
@@ -110,7 +168,10 @@ class TransformerDecoder(nn.Module):
         B = tokens.shape[0]
         seqs = PackedSeqs(tokens, torch.full_like(tokens, position), torch.arange(B + 1, dtype=torch.int32, device=tokens.device), 1)
         self.embed.renew(position + 1)
-        return self.run_layers_step(self.embed(seqs, 0.0), state)
+        x = self.embed(seqs, 0.0)
+        if self.language_embedding is not None and getattr(state, "tgt_lang", None) is not None:
+            x = self.language_embedding(x, seqs, state.tgt_lang)
+        return self.run_layers_step(x, state)
 
     def run_layers_step(self, x, state: "DecodingState"):
         """One new position through the layer stack (subclasses with a different wiring override this)."""
@@ -133,13 +194,18 @@ class TransformerDecoder(nn.Module):
 class Generator(nn.Module):
     """hidden -> vocabulary logits (weight optionally tied to the target embedding)."""
 
-    def __init__(self, dim: int, vocab: int, bias: bool = True):
+    def __init__(self, dim: int, vocab: int, bias: bool = True, fix_norm: bool = False):
         super().__init__()
         self.weight = nn.Parameter(torch.empty(vocab, dim))
         nn.init.normal_(self.weight, 0.0, dim ** -0.5)
         self.bias = nn.Parameter(torch.zeros(vocab)) if bias else None
+        self.fix_norm = fix_norm      # -fix_norm_output_embedding: unit-length output embeddings (base_seq2seq.py:33-41)
 
     def forward(self, hidden, log_softmax: bool = False):
+        if self.fix_norm:
+            w = torch.nn.functional.normalize(self.weight.float(), dim=-1).to(hidden.dtype)
+            logits = torch.nn.functional.linear(hidden, w, None if self.bias is None else self.bias.to(hidden.dtype))
+            return torch.log_softmax(logits.float(), dim=-1) if log_softmax else logits
         logits = ops.linear(hidden, self.weight, self.bias, "none", 0.0, None, False)
         return torch.log_softmax(logits.float(), dim=-1) if log_softmax else logits
 
@@ -233,14 +299,27 @@ class Seq2SeqBase(nn.Module):
         if self.training and self.switchout > 0:
             tgt = self._switchout(tgt, self.generator.weight.shape[0])
         labels = batch.packed_target_output()
-        hidden = self.decoder(tgt, context, src)
+        if getattr(self.decoder, "language_embedding", None) is not None:
+            hidden = self.decoder(tgt, context, src, lang_ids=batch.get("target_lang") if hasattr(batch, "get") else None)
+        else:
+            hidden = self.decoder(tgt, context, src)
         out = {"hidden_packed": hidden, "context_packed": context, "src": src, "tgt": tgt, "target": labels}
-        if compute_loss:
+        if compute_loss and getattr(self.generator, "fix_norm", False):
+            logits = self.generator(hidden)
+            loss, correct, row_loss = ops.cross_entropy(logits if logits.is_contiguous() else logits.contiguous(), labels,
+                                                        self.label_smoothing if self.training else 0.0, self.pad_idx)
+            if grad_scale is not None and torch.is_grad_enabled():
+                from ..ops.reference import scale_gradient
+                gs = grad_scale if isinstance(grad_scale, torch.Tensor) else torch.tensor(float(grad_scale), device=loss.device)
+                loss = scale_gradient(loss, gs.to(loss.device))
+            out.update(loss=loss, correct=correct, row_loss=row_loss)
+        elif compute_loss:
             loss, correct, row_loss = ops.generator_cross_entropy(
                 hidden, self.generator.weight, self.generator.bias, labels,
                 self.label_smoothing if self.training else 0.0, self.pad_idx, grad_scale,
                 chunk_rows=self.generator_chunk_rows if self.training else 0)
             out.update(loss=loss, correct=correct, row_loss=row_loss)
+        if compute_loss:
             aux = self.auxiliary_losses(batch, context, src, out)
             if aux is not None:
                 out["nmt_loss"] = out["loss"]
@@ -292,6 +371,11 @@ class Seq2SeqBase(nn.Module):
         lengths = (src.cu[1:] - src.cu[:-1]).to(torch.int64)
         pad_mask = torch.arange(ctx_padded.shape[1], device=ctx_padded.device)[None, :] >= lengths[:, None]
         state = DecodingState(ctx_padded, pad_mask, len(self.decoder.layers), beam_size)
+        if getattr(self.decoder, "language_embedding", None) is not None and hasattr(batch, "get"):
+            tl = batch.get("target_lang")
+            if tl is not None:
+                tl = tl.to(ctx_padded.device).view(-1)
+                state.tgt_lang = tl.repeat_interleave(beam_size, 0) if (beam_size > 1 and tl.numel() > 1) else tl
         shared = ctx_padded.is_cuda and ctx_padded.dtype == torch.bfloat16 and beam_size > 1
         for i, layer in enumerate(self.decoder.layers):
             if not getattr(layer, "ignore_source", False):
@@ -341,7 +425,11 @@ class Transformer(Seq2SeqBase):
             src_embed = Embedding(src_vocab, opt.model_size, self.pad_idx, max_pos=max_pos)
         self.encoder = TransformerEncoder(opt, src_embed)
         self.decoder = TransformerDecoder(opt, tgt_embed)
-        self.generator = Generator(opt.model_size, tgt_vocab)
+        self.generator = Generator(opt.model_size, tgt_vocab, fix_norm=bool(getattr(opt, "fix_norm_output_embedding", False)))
+        if getattr(opt, "use_language_embedding", False):
+            lang = LanguageEmbedding(_n_languages(dicts), opt.model_size, getattr(opt, "language_embedding_type", "sum"))
+            self.encoder.language_embedding = lang
+            self.decoder.language_embedding = lang       # one table for both sides, as in the reference's factory
         if getattr(opt, "tie_weights", False):
             self.tie_weights()
         self.label_smoothing = getattr(opt, "label_smoothing", 0.0)
@@ -355,4 +443,6 @@ class Transformer(Seq2SeqBase):
         src = batch.packed_source()
         if self.training and self.switchout > 0:
             src = self._switchout(src, self.encoder.embed.weight.shape[0])
+        if self.encoder.language_embedding is not None:
+            return self.encoder(src, lang_ids=batch.get("source_lang") if hasattr(batch, "get") else None), src
         return self.encoder(src), src

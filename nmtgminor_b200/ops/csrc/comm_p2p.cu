@@ -38,37 +38,65 @@ namespace b200 {
 
 int num_sms();
 
-// 256-thread CTAs at about 40 registers: small enough to share an SM with a resident GEMM CTA (320 threads at up to
-// 168 registers), so the reduction runs beside the backward pass instead of waiting for an SM to drain.
-__global__ void __launch_bounds__(256)
+// Sum of element groups i, i + stride, ... of all ranks' buffers; U groups per thread are in flight together.
+template <int U>
+__device__ __forceinline__ void reduce_elements(const NmtgPeerTable& t, float* __restrict__ reduced, long g0, long n4, long first,
+                                                long stride, int accumulate) {
+  for (long i = first; i < n4; i += U * stride) {
+    float4 s[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long j = i + u * stride;
+      s[u] = (accumulate && j < n4) ? reinterpret_cast<const float4*>(reduced)[j] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll 4
+    for (int r = 0; r < t.world; ++r) {
+      // start with my own buffer, then walk the ring so the peers' links are loaded evenly
+      const float* src = t.grads[(t.rank + r) % t.world] + g0;
+      float4 v[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long j = i + u * stride;
+        v[u] = j < n4 ? reinterpret_cast<const float4*>(src)[j] : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) { s[u].x += v[u].x; s[u].y += v[u].y; s[u].z += v[u].z; s[u].w += v[u].w; }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long j = i + u * stride;
+      if (j < n4) reinterpret_cast<float4*>(reduced)[j] = s[u];
+    }
+  }
+}
+
+// 128-thread CTAs at about 40 registers (5 K of the SM's 64 K): small enough to share an SM with a resident GEMM CTA
+// (320 threads at up to 168 registers = 54 K, ~200 KB of shared memory), so the reduction runs beside the backward
+// pass instead of waiting for an SM to drain.
+constexpr int kReduceThreads = 128;
+__global__ void __launch_bounds__(kReduceThreads)
 reduce_unit_kernel(const NmtgPeerTable t, int row, float* __restrict__ reduced, long g0, long len, int accumulate,
                    long zero_begin, long zero_len, int* __restrict__ counter, const int* __restrict__ epoch_ptr, int* status) {
   const int epoch = *epoch_ptr;
   if (!peer_barrier(t, row, epoch, status)) return;
   const long n4 = len >> 2;
   const long stride = static_cast<long>(gridDim.x) * blockDim.x;
-  for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < n4; i += stride) {
-    float4 s = accumulate ? reinterpret_cast<const float4*>(reduced)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 4
-    for (int r = 0; r < t.world; ++r) {
-      // start with my own buffer, then walk the ring so the peers' links are loaded evenly
-      const int src = (t.rank + r) % t.world;
-      const float4 v = reinterpret_cast<const float4*>(t.grads[src] + g0)[i];
-      s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
-    }
-    reinterpret_cast<float4*>(reduced)[i] = s;
-  }
+  const long first = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x;
+  // Peer loads are latency bound: what counts is the number of 16-byte loads a thread has in flight.  Eight ranks give
+  // eight per element; smaller worlds make up for it by working on several elements at once.
+  if (t.world <= 2) reduce_elements<4>(t, reduced, g0, n4, first, stride, accumulate);
+  else if (t.world <= 4) reduce_elements<2>(t, reduced, g0, n4, first, stride, accumulate);
+  else reduce_elements<1>(t, reduced, g0, n4, first, stride, accumulate);
   if (zero_len <= 0) return;
   // Rotating gradient buffers: the LAST CTA of this launch to finish its loads tells every peer "rank `rank` has
   // read the unit"; everybody then waits for all peers' notices before clearing the local copy.
-  __shared__ int s_last;
   __syncthreads();
+  int last = 0;
   if (threadIdx.x == 0) {
     __threadfence();
-    s_last = (atomicAdd(counter, 1) == static_cast<int>(gridDim.x) - 1);
+    last = (atomicAdd(counter, 1) == static_cast<int>(gridDim.x) - 1);
   }
-  __syncthreads();
-  if (s_last) {
+  if (__syncthreads_or(last)) {
     peer_publish(t, row + 1, epoch);
     if (threadIdx.x == 0) *counter = 0;      // ready for the next launch from this site
   }
@@ -193,11 +221,11 @@ const char* nmtg_reduce_unit(const NmtgPeerTable* t, int row, float* reduced, lo
     return "reduce_unit: ranges must be multiples of 4 elements";
   if (reinterpret_cast<uintptr_t>(reduced) & 15) return "reduce_unit: unaligned output";
   if (zero_len > 0 && !counter) return "reduce_unit: clearing the unit needs the launch counter";
-  long blocks = (len / 4 + 255) / 256;
-  if (ctas < 1) ctas = 48;
+  long blocks = (len / 4 + kReduceThreads - 1) / kReduceThreads;
+  if (ctas < 1) ctas = 64;
   if (blocks > ctas) blocks = ctas;
   if (blocks < 1) blocks = 1;
-  reduce_unit_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(*t, row, reduced, global_begin, len, accumulate, zero_begin,
+  reduce_unit_kernel<<<static_cast<int>(blocks), kReduceThreads, 0, stream>>>(*t, row, reduced, global_begin, len, accumulate, zero_begin,
                                                                   zero_len, counter, epoch_dev, status);
   return err_str();
 }

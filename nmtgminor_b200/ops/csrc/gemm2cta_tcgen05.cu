@@ -20,6 +20,7 @@ namespace b200 {
 
 bool cached_tmap(CUtensorMap* out, const void* base, long rows, long cols, long ld, int br, int bc);
 int num_sms();
+int gemm_sms();
 
 constexpr int kPairThreads = 32 * (2 + kEpilogueWarps);
 
@@ -267,39 +268,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     }
   } else {
     // ------------------------------- epilogue (8 warps, both CTAs) ---------------------------
-    if (g.n_seg > 0) {
-      // ---- gather of the sharded B operand: these warps have nothing to do until the first accumulator is complete.
-      // The matrix is a run of 4 KB blocks.  The CTAs that are running claim four consecutive blocks at a time from a
-      // shared cursor (so a CTA that has not been scheduled yet holds nobody up and the segments complete in order);
-      // each thread moves 16 bytes of every claimed block (four peer loads in flight), then the blocks' segment
-      // counters are raised.  Element e of the unit lives in rank e / piece_len's shard; a 16-byte group never
-      // straddles two owners (pieces are multiples of 64 elements).
-      __shared__ int s_claim;
-      const int t = threadIdx.x - 64;
-      for (;;) {
-        if (t == 0) s_claim = atomicAdd(g.counters + 1, 4);
-        asm volatile("bar.sync 1, %0;" ::"n"(32 * kEpilogueWarps) : "memory");
-        const long u0 = s_claim;
-        if (u0 >= g.units) break;
-        uint4 v[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          if (u0 + j < g.units) {
-            const long e = g.unit_off + (u0 + j) * (kGatherBlockBytes / 2) + t * 8;
-            const int owner = static_cast<int>(e / g.piece_len);
-            const long within = e - owner * g.piece_len;
-            v[j] = *reinterpret_cast<const uint4*>(g.shards[owner] + g.shard_off + within);
-          }
-        }
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-          if (u0 + j < g.units) *reinterpret_cast<uint4*>(g.dst + (u0 + j) * (kGatherBlockBytes / 2) + t * 8) = v[j];
-        fence_proxy_async_all();
-        __threadfence();
-        asm volatile("bar.sync 1, %0;" ::"n"(32 * kEpilogueWarps) : "memory");
-        if (t < 4 && u0 + t < g.units) atomicAdd(g.counters + 2 + static_cast<int>((u0 + t) / g.seg_units), 1);
-      }
-    }
     const int q = warp & 3;
     const int chunk_par = (warp - 2) >> 2;
     const bool do_drop = p.dropout_p > 0.f;
@@ -312,12 +280,56 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     long long e_wait = 0, e_last = 0, e_drain = 0, e_chunks = 0, e_issue = 0;
     long cursor = first_work;
     int mn, kb_begin, kb_end;
+    // ---- gather of a sharded B operand (fully sharded parameters), done by these warps WHILE they wait for
+    // accumulators.  The matrix is a run of 4 KB blocks; the CTAs that are running claim four consecutive blocks at
+    // a time from a shared cursor (a CTA that has not been scheduled yet holds nobody up, and the segments complete
+    // in order), each thread moves 16 bytes of every claimed block (four peer loads in flight), then the blocks'
+    // segment counters are raised.  Element e of the unit lives in rank e / piece_len's shard; a 16-byte group never
+    // straddles two owners (pieces are multiples of 64 elements).  One round: thread 0 looks whether the awaited
+    // accumulator is complete (then the epilogue goes first) and otherwise claims blocks; the verdict reaches the
+    // other 255 threads through shared memory and a named barrier.
+    __shared__ int s_claim[2];
+    int claim_slot = 0;
+    bool gather_left = g.n_seg > 0;
+    const int gt = threadIdx.x - 64;
+    auto gather_rounds = [&](uint64_t* wait_bar, uint32_t wait_phase) {
+      while (gather_left) {
+        if (gt == 0) {
+          int c = -1;
+          if (wait_bar == nullptr || !mbar_try_wait(wait_bar, wait_phase)) c = atomicAdd(g.counters + 1, 4);
+          s_claim[claim_slot] = c;
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(32 * kEpilogueWarps) : "memory");
+        const long u0 = s_claim[claim_slot];
+        claim_slot ^= 1;
+        if (u0 < 0) return;                       // the accumulator is ready: epilogue first, gather again later
+        if (u0 >= g.units || *abort_word) { gather_left = false; return; }
+        uint4 v[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          if (u0 + j < g.units) {
+            const long e = g.unit_off + (u0 + j) * (kGatherBlockBytes / 2) + gt * 8;
+            const int owner = static_cast<int>(e / g.piece_len);
+            const long within = e - owner * g.piece_len;
+            v[j] = *reinterpret_cast<const uint4*>(g.shards[owner] + g.shard_off + within);
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (u0 + j < g.units) *reinterpret_cast<uint4*>(g.dst + (u0 + j) * (kGatherBlockBytes / 2) + gt * 8) = v[j];
+        fence_proxy_async_all();
+        __threadfence();
+        asm volatile("bar.sync 1, %0;" ::"n"(32 * kEpilogueWarps) : "memory");
+        if (gt < 4 && u0 + gt < g.units) atomicAdd(g.counters + 2 + static_cast<int>((u0 + gt) / g.seg_units), 1);
+      }
+    };
     for (; next_work(cursor, mn, kb_begin, kb_end); ++it) {
       const int m0 = (mn % num_m) * (2 * BM) + static_cast<int>(rank) * BM;
       const int n0 = (mn / num_m) * BN;
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
       const long long e0 = tracing ? clock64() : 0;
+      gather_rounds(&tmem_full[acc], acc_phase);
       if (!mbar_wait(&tmem_full[acc], acc_phase, abort_word, p.status, kTimeoutTmemFull)) break;
       if (tracing) { e_last = clock64(); e_wait += e_last - e0; }
       tc_fence_after_sync();
@@ -381,6 +393,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       tc_fence_before_sync();
       mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty[acc]), 0));
     }
+    gather_rounds(nullptr, 0);      // blocks that nobody has claimed yet (none, unless this CTA ran out of tiles early)
     if (p.tma_store && lane == 0) tma_store_wait_all();   // staging must outlive the copies that read it
     if (tracing) {
       long long* tr = p.trace + cluster_id * 16;
@@ -511,7 +524,7 @@ const char* launch_gemm_pair(const GemmDesc* d, const GemmArgs& a, int bn, cudaS
   }
   if (a.colsum && !args.tma_store) return "gemm: the column-sum output needs the bf16 TMA-store epilogue (no split-K, no pre-activation)";
   const long tiles = static_cast<long>((d->M + 2 * BM - 1) / (2 * BM)) * ((d->N + bn - 1) / bn) * a.split_k;
-  const int max_clusters = num_sms() / 2;
+  const int max_clusters = gemm_sms() / 2;
   const int clusters = a.stream_k ? max_clusters : static_cast<int>(tiles < max_clusters ? tiles : max_clusters);
   if (bn != 256) return launch_pair<128, false, kEpiAll>(ta, tb, tc, args, clusters * 2, stream, g);
   if (args.trace != nullptr) return launch_pair<256, true, kEpiAll>(ta, tb, tc, args, clusters * 2, stream, g);

@@ -328,6 +328,10 @@ bool cached_tmap_f32(CUtensorMap* out, const void* base, long rows, long cols, l
   return true;
 }
 
+// SMs that the persistent GEMM kernels leave free (for communication kernels that run beside them); even, set
+// through nmtg_set_gemm_variant(60 + n).
+static int g_gemm_sm_reserve = 0;
+int gemm_sms();
 static int g_num_sms = 0;
 int num_sms() {
   if (!g_num_sms) {
@@ -336,6 +340,11 @@ int num_sms() {
     cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
   }
   return g_num_sms;
+}
+
+int gemm_sms() {
+  const int n = num_sms() - g_gemm_sm_reserve;
+  return n < 2 ? 2 : n;
 }
 
 template <int BN, uint32_t kFeat = kEpiAll>
@@ -374,7 +383,8 @@ extern int g_pair_generic_epilogue;
 void nmtg_set_gemm_trace(long long* buf) { g_gemm_trace = buf; }
 
 void nmtg_set_gemm_variant(int v) {
-  if (v == 50 || v == 51) g_fused_gather = v - 50;
+  if (v >= 60 && v < 124) b200::g_gemm_sm_reserve = (v - 60) & ~1;
+  else if (v == 50 || v == 51) g_fused_gather = v - 50;
   else if (v == 40 || v == 41) g_stream_k = v - 40;
   else if (v == 30 || v == 31) b200::g_pair_generic_epilogue = v - 30;
   else if (v == 20 || v == 21) b200::g_pair_tma_store = v - 20;   // 20: per-thread stores, 21: TMA-store epilogue (default)
@@ -418,7 +428,7 @@ const char* nmtg_gemm_bf16(const GemmDesc* d, cudaStream_t stream) {
     d = &unfused;
     return nullptr;
   };
-  const int sms = num_sms();
+  const int sms = gemm_sms();
   const int num_kb = (d->K + BK - 1) / BK;
   auto fix_split = [&](int split) {   // largest split <= requested whose last part is not empty
     if (split > num_kb) split = num_kb;

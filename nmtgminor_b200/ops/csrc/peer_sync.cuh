@@ -45,22 +45,21 @@ __device__ __forceinline__ bool wait_flag(const int* flag, int epoch, long long 
 
 // Thread i < world publishes `epoch` in slot `rank` of peer i's flag row (when `publish` is set), then waits until
 // slot i of the local row reaches `epoch`.  Returns false for the whole CTA when any wait ran out of time (status 5).
+// Uses no shared memory (the verdict travels through the barrier's own OR), so kernels built on it can share an SM
+// with a CTA that owns nearly all of the SM's shared memory.
 __device__ __forceinline__ bool peer_barrier(const NmtgPeerTable& t, int row, int epoch, int* status, bool publish = true) {
-  __shared__ int s_fail;
-  if (threadIdx.x == 0) s_fail = 0;
-  __syncthreads();
+  int fail = 0;
   if (threadIdx.x < t.world) {
     if (publish) {
       __threadfence_system();
       st_release_sys(t.flags[threadIdx.x] + row * kMaxRanks + t.rank, epoch);
     }
     if (!wait_flag(t.flags[t.rank] + row * kMaxRanks + threadIdx.x, epoch, t.timeout_ns)) {
-      s_fail = 1;
+      fail = 1;
       if (status) atomicCAS(status, 0, 5 /* kTimeoutPeerFlag */);
     }
   }
-  __syncthreads();
-  return s_fail == 0;
+  return __syncthreads_or(fail) == 0;
 }
 
 // Publish only (no wait): slot `rank` of every peer's row.

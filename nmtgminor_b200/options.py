@@ -116,3 +116,106 @@ def backward_compatible(opt: argparse.Namespace) -> argparse.Namespace:
     elif getattr(opt, "predict_language", 0) is False:
         opt.predict_language = 0
     return opt
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# what every training flag does here: consumed by code, accepted without effect (and why), or refused
+# ---------------------------------------------------------------------------------------------------------------
+# Flags that select between a fused and an unfused implementation in the reference.  Here the fused kernels are the
+# only path on a GPU and the PyTorch restatement the only path on a CPU, so the switches have nothing to choose.
+ALWAYS_ON_FLAGS = {
+    "fast_xentropy": "the fused label-smoothed cross-entropy kernel is always used on a GPU",
+    "fast_xattention": "encoder-decoder attention always runs on the tcgen05 attention kernels",
+    "fast_self_attention": "self-attention always runs on the tcgen05 attention kernels",
+    "fast_feed_forward": "feed-forward blocks always run as GEMMs with fused epilogues",
+    "fused_ffn": "feed-forward blocks always run as GEMMs with fused epilogues",
+    "flatten_parameters": "parameters always live in one flat buffer (parallel/flat.py)",
+    "zeror_optim": "optimiser state is always sharded across the data-parallel ranks (parallel/sharded.py)",
+}
+
+# Flags that the reference parses and never reads (checked by grepping its sources): accepted for command-line
+# compatibility, without effect there or here.
+NO_EFFECT_IN_REFERENCE = {
+    "dr_alpha", "dr_beta", "attribute_size", "noam_step_interval", "factorizing_step", "input_feature_size",
+    "mfw_atb_rank_scale", "freezing_steps", "debugging", "enc_pretrain_hidden_size", "enc_pretrain_word_dropout",
+    "enc_pretrain_attn_dropout", "mutual_modality_training",
+}
+
+# Flags whose feature is not built: giving one a value other than its default stops the run instead of silently
+# training a different model.
+UNSUPPORTED_FLAGS = {
+    "concat_dataset": "concatenated-sentence data sets",
+    "finalize_only": "the continual-learning finalisation pass",
+    "max_examples_seen": "example-count limits of the continual-learning trainers",
+    "stream_context": "streaming context selection",
+    "rotary_position_encoding": "rotary position encoding in the speech / relative Transformers",
+    "reconstruct": "the reconstruction decoder",
+    "weight_norm": "weight-normalised linear layers",
+    "stochastic_sublayer": "stochastic sub-layer dropping",
+    "activation_layer": "alternative activation-layer layouts (maxout)",
+    "residual_type": "gated / highway residual connections",
+    "extra_context_size": "extra streaming context",
+    "batch_ensemble": "batch-ensemble weights",
+    "no_decoder": "encoder-only sequence models in the translation trainer",
+    "copy_generator": "the copy generator",
+    "favor_attention": "FAVOR+ attention inside the main Transformer (models/efficient_attention.py has the stand-alone layer)",
+    "lm_checkpoint": "language-model fusion",
+    "fusion": "language-model fusion",
+    "reshape_speech": "frame reshaping of speech features (use -concat)",
+    "bottleneck_size": "bottleneck adapters of the legacy speech models",
+    "no_batch_norm": "the Conv2d front end without batch normalisation",
+    "depthwise_conv": "depthwise-convolution feed-forward blocks",
+    "no_ffn": "layers without feed-forward blocks",
+    "fast_factorize": "the fused factorised-weight kernels (the factorised weights run as plain GEMMs)",
+    "flex_factorize": "flexible-rank factorised weights",
+    "mfw_multiplicative": "multiplicative factorised weights",
+    "mfw_activation": "activations on factorised weights",
+    "sub_encoder": "text sub-encoders behind the speech encoder",
+    "weight_drop": "DropConnect on the feed-forward weights",
+    "enc_stacked_pretrained_model": "stacked pretrained encoders",
+    "s4_config_file": "S4 configuration files (the state-space encoder takes its sizes from -enc_config_file)",
+    "load_pretrained_classifier": "pretrained classifier heads",
+    "wav2vec2_quantize": "the wav2vec 2.0 quantiser inside the translation models (models/w2vbert.py has the quantiser)",
+    "wav2vec2_dual_output": "dual-output wav2vec 2.0 encoders",
+    "wav2vec2_relative_attention": "relative attention inside wav2vec 2.0",
+    "wav2vec_adapter": "adapters inside wav2vec 2.0",
+    "decoder_adapter": "adapters inside the pretrained decoders",
+    "contrastive_loss_coeff": "the speech / text contrastive loss",
+    "dataset_factors": "per-data-set sampling factors",
+    "cache_encoder_output": "cached encoder outputs",
+    "use_memory": "the n-gram memory decoder",
+    "freeze_baseline_decoder": "the n-gram memory decoder",
+    "memory_size_max": "the n-gram memory decoder",
+    "encoder_layers_memory": "the n-gram memory decoder",
+    "decoder_layers_memory": "the n-gram memory decoder",
+    "branchformer": "Branchformer cgMLP blocks",
+    "wav2vec_spec_augment": "SpecAugment inside wav2vec 2.0 (time masking is the encoder's mask_prob)",
+}
+
+
+def _flag_defaults():
+    return {row[0]: (row[1], row[2]) for row in list(TRAIN_FLAGS) + list(EXTRA_TRAIN_FLAGS)}
+
+
+def unsupported_flags_in(opt):
+    """[(flag, value, what)] for every unsupported flag that ``opt`` sets to something other than its default."""
+    defaults = _flag_defaults()
+    bad = []
+    for name, what in UNSUPPORTED_FLAGS.items():
+        if not hasattr(opt, name) or name not in defaults:
+            continue
+        kind, default = defaults[name]
+        value = getattr(opt, name)
+        if kind == "flag":
+            if value:
+                bad.append((name, value, what))
+        elif value != default and not (value in (None, "", [], 0, 0.0) and default in (None, "", [], 0, 0.0)):
+            bad.append((name, value, what))
+    return bad
+
+
+def validate_model_options(opt) -> None:
+    """Refuse option values whose feature this build does not have (see ``UNSUPPORTED_FLAGS``)."""
+    bad = unsupported_flags_in(opt)
+    if bad:
+        raise NotImplementedError("not supported by this build: " + "; ".join("-%s %r (%s)" % b for b in bad))

@@ -216,9 +216,11 @@ class FullyShardedAdam(UnitShardedStep):
 
     def begin_step(self):
         """Resident units (embeddings, norms, output projection) are refreshed once per step on the compute stream."""
+        ctas, self.gather_ctas = self.gather_ctas, 296      # nothing runs beside these copies: use every SM
         for u in self.units:
             if u.slot < 0:
                 self._launch_gather(u, [(0, _round_up(u.length, 8))], torch.cuda.current_stream())
+        self.gather_ctas = ctas
         self.slot_unit = [None, None]
         self.slot_stamp = [s + 1 for s in self.slot_stamp]
         # events never cross a step boundary (the streams joined when the last backward pass ended); a captured step

@@ -154,9 +154,15 @@ class UnitShardedStep:
             n = max(0, min(u.piece, min(u.end, limit) - p0))
             n -= n % 4
             self.pieces.append((u.shard_off, p0, n))
-        self.comm = torch.cuda.Stream(device=dev)
-        self.reduce_ctas = int(os.environ.get("NMTG_REDUCE_CTAS", "48"))
+        # high priority: a reduction's small CTAs are placed as soon as an SM has room, ahead of queued GEMM CTAs
+        self.comm = torch.cuda.Stream(device=dev, priority=-1)
+        # CTAs (of 128 threads) of a reduction that runs beside the backward pass, and of one that runs after it
+        self.reduce_ctas = int(os.environ.get("NMTG_REDUCE_CTAS", "1184"))
+        self.tail_ctas = int(os.environ.get("NMTG_REDUCE_TAIL_CTAS", "1184"))
         self.overlap = bool(overlap) and os.environ.get("NMTG_OVERLAP_REDUCE", "1") != "0"
+        reserve = int(os.environ.get("NMTG_GEMM_SM_RESERVE", "0"))
+        if reserve > 0 and self.overlap and self.world > 1:
+            ops.ext().set_gemm_variant(60 + reserve)     # persistent GEMMs leave these SMs to the reductions
         self.active = True          # hooks launch reductions only during a backward pass that ends in an update
         self._done = set()          # units reduced in the current backward pass
         self._last = None           # layer unit whose backward pass is running
@@ -185,7 +191,7 @@ class UnitShardedStep:
         """(offset of this rank's piece in the gradient space, range to clear afterwards or (0, 0))."""
         return u.grad_base + self.rank * u.piece, (0, 0)
 
-    def _reduce(self, u: Unit):
+    def _reduce(self, u: Unit, tail: bool = False):
         if u.index in self._done:
             return
         self._done.add(u.index)
@@ -197,7 +203,7 @@ class UnitShardedStep:
         with torch.cuda.stream(self.comm):
             ops.ext().reduce_unit(self.rank, self.grad_ptrs, self.flag_ptrs, u.row, self.reduced[so:so + max(n, 4)], g0, n,
                                   self._micro > 0 and self.mode == 1, zb, zl, self.counters[u.index:u.index + 1], self.epoch,
-                                  self.reduce_ctas)
+                                  self.tail_ctas if tail else self.reduce_ctas)
             self._after_reduce(u)
         ops.LAUNCHES[0] += 1
 
@@ -210,7 +216,7 @@ class UnitShardedStep:
             self._last = None
             return None
         for u in reversed(self.units):
-            self._reduce(u)
+            self._reduce(u, tail=True)       # nothing left to overlap with: use the whole GPU
         if self._forked:
             torch.cuda.current_stream().wait_stream(self.comm)
             self._forked = False

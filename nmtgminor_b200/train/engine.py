@@ -210,6 +210,8 @@ class TrainEngine:
             return
         torch.cuda.synchronize()
         self._graphs = {}
+        self.reducer.active = False        # its backward hooks stay installed on the layers
+        self.reducer.overlap = False
         self.reducer = None
         self.optim.distributed = None
         n = self.optim.n_update

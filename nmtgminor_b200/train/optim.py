@@ -64,6 +64,8 @@ class Optim:
         self.lr_decay = getattr(opt, "learning_rate_decay", 1.0)
         self.start_decay_at = getattr(opt, "start_decay_at", 99999)
         self._step = 0
+        if int(getattr(opt, "starting_step", -1) or -1) > 0:
+            self._step = int(opt.starting_step)     # -starting_step: continue the schedule of an earlier run
         self._epoch_decay = 1.0
         self.store: Optional[FlatParameterStore] = None
         self.optimizer: Optional[torch.optim.Optimizer] = None
@@ -75,7 +77,10 @@ class Optim:
         when a sharded step (``attach_distributed``) will own the moments."""
         self.params = [p for p in params if p.requires_grad]
         self.store = store
-        fused = store is not None and store.master.is_cuda and self.method in ("adam", "adamw") and ops.extension_available()
+        # -amsgrad keeps a running maximum of the second moment, which the flat kernel does not: torch.optim handles it
+        self.amsgrad = bool(getattr(self.opt, "amsgrad", False))
+        fused = (store is not None and store.master.is_cuda and self.method in ("adam", "adamw") and ops.extension_available()
+                 and not self.amsgrad)
         self.fused = fused
         if fused:
             dev = store.master.device
@@ -93,7 +98,7 @@ class Optim:
         elif self.method in ("adam", "adamw", "fused_adam"):
             cls = torch.optim.AdamW if self.weight_decay > 0 else torch.optim.Adam
             self.optimizer = cls(self.params, lr=self.lr, betas=(self.beta1, self.beta2), eps=self.eps,
-                                 weight_decay=self.weight_decay)
+                                 weight_decay=self.weight_decay, amsgrad=self.amsgrad)
         elif self.method == "adafactor":
             from .adafactor import Adafactor
             self.optimizer = Adafactor(self.params, lr=self.lr if self.lr < 1 else None, weight_decay=self.weight_decay)

@@ -72,7 +72,7 @@ class Trainer:
         if getattr(opt, "fsdp", False) and self.cuda:
             ddp = "fsdp"
         self.engine = TrainEngine(self.model, opt, self.device, reducer=None,
-                                  cuda_graph=getattr(opt, "cuda_graph", False) and getattr(opt, "update_frequency", 1) == 1,
+                                  cuda_graph=self._graph_wanted(opt),
                                   grad_scale=grad_scale, ddp=ddp)
         self.optim = self.engine.optim
         if checkpoint is not None and not getattr(opt, "reset_optim", False) and checkpoint.get("optim") is not None:
@@ -104,6 +104,17 @@ class Trainer:
             from ..utils.watchdog import Heartbeat
             self.watchdog = Heartbeat(self.rank, self.world_size, timeout=opt.watchdog_timeout)
 
+    def _graph_wanted(self, opt) -> bool:
+        """The step is replayed from CUDA graphs (one per shape class of batches) by default on a GPU.  Off with
+        ``-no_cuda_graph``, with gradient accumulation, and for models that skip layers at random (a captured graph
+        would freeze one pattern)."""
+        from ..parallel.sharded import skips_layers
+        if not self.cuda or getattr(opt, "no_cuda_graph", False):
+            return False
+        if int(getattr(opt, "update_frequency", 1) or 1) > 1 or int(getattr(opt, "batch_size_update", -1) or -1) > 0:
+            return False
+        return not skips_layers(opt)
+
     # ------------------------------------------------------------------------------------------
     def is_main(self):
         return self.rank == 0
@@ -118,7 +129,8 @@ class Trainer:
     def _iterator(self, data, epoch, seed_offset=0, shuffle=True):
         kw = dict(seed=getattr(self.opt, "seed", 9999) + seed_offset, num_workers=getattr(self.opt, "num_workers", 0),
                   epoch=epoch, buffer_size=getattr(self.opt, "buffer_size", 0), num_shards=self.world_size,
-                  shard_id=self.rank, split_even=True, pin_memory=self.cuda, shuffle=shuffle)
+                  shard_id=self.rank, split_even=True, pin_memory=self.cuda or bool(getattr(self.opt, "pin_memory", False)),
+                  shuffle=shuffle)
         if _is_list(data):
             return MultiDataIterator(list(data), **kw)
         return DataIterator(data, **kw)
@@ -218,8 +230,11 @@ class Trainer:
         self.model.train()
         for i, batch in enumerate(epoch_itr):
             counter += 1
-            update = counter >= update_frequency or i == n_batches - 1
             acc_words += batch.tgt_size
+            update = counter >= update_frequency or i == n_batches - 1
+            bsu = int(getattr(opt, "batch_size_update", -1) or -1)
+            if bsu > 0:       # -batch_size_update: step once this many target tokens have been accumulated (on this rank)
+                update = acc_words >= bsu or i == n_batches - 1
             if update and getattr(opt, "normalize_gradient", False):
                 total_words = self._all_reduce_scalars([float(acc_words)])[0]
                 self.engine.grad_scale = 1.0 / max(total_words, 1.0)

@@ -26,13 +26,33 @@ from nmtgminor_b200.options import make_parser
 def _dataset_from(split, opt, dicts, training):
     if split is None or (split.get("src") is None and split.get("tgt") is None):
         return None
+    audio = getattr(opt, "encoder_type", "text") != "text"
+    augmenter = None
+    if training and audio and getattr(opt, "augment_speech", False):
+        # -augment_speech: SpecAugment on the feature matrices, widths from -sa_f / -sa_t (reference:
+        # train_distributed.py:186-200 -> onmt/speech/Augmenter.py)
+        from nmtgminor_b200.data.audio import Augmenter
+        augmenter = Augmenter(F=int(getattr(opt, "sa_f", 8)), T=int(getattr(opt, "sa_t", 64)),
+                              input_size=int(getattr(opt, "input_size", 40) or 40), concat=int(getattr(opt, "concat", 1) or 1),
+                              seed=int(getattr(opt, "seed", 9999)))
+    # captured CUDA graphs need batches whose shapes repeat: round packed capacities to a few sizes (text batches)
+    static = training and not audio and _use_cuda_graph(opt)
     return Dataset(split.get("src"), split.get("tgt"), split.get("src_sizes"), split.get("tgt_sizes"), split.get("src_lang"),
                    split.get("tgt_lang"), split.get("src_atb"), split.get("tgt_atb"),
                    batch_size_words=opt.batch_size_words, batch_size_frames=getattr(opt, "batch_size_frames", 10 ** 12),
                    batch_size_sents=opt.batch_size_sents if opt.batch_size_sents > 0 else 10 ** 9,
                    multiplier=opt.batch_size_multiplier, data_type=getattr(opt, "encoder_type", "text") if getattr(opt, "encoder_type", "text") != "text" else "text",
                    max_src_len=opt.max_src_length if training else 10 ** 9, max_tgt_len=(opt.max_tgt_length + 2) if training else 10 ** 9,
-                   cleaning=training, verbose=True, aux_tgt_data=split.get("aux_tgt"))
+                   cleaning=training, verbose=True, aux_tgt_data=split.get("aux_tgt"), augmenter=augmenter, static_shapes=static)
+
+
+def _use_cuda_graph(opt) -> bool:
+    """The training step is replayed from CUDA graphs by default on a GPU; ``-no_cuda_graph``, gradient accumulation
+    (``-update_frequency`` > 1, ``-batch_size_update``) and random layer skipping switch it off."""
+    from nmtgminor_b200.parallel.sharded import skips_layers
+    gpu = bool(getattr(opt, "gpus", None)) and opt.gpus not in ([], [-1]) and torch.cuda.is_available()
+    return (gpu and not getattr(opt, "no_cuda_graph", False) and int(getattr(opt, "update_frequency", 1) or 1) <= 1
+            and int(getattr(opt, "batch_size_update", -1) or -1) <= 0 and not skips_layers(opt))
 
 
 def load_multi_datasets(opt):
@@ -64,8 +84,23 @@ def load_multi_datasets(opt):
                  "src_atb": mm("data.src_atb"), "tgt_atb": mm("data.tgt_atb"),
                  "src_sizes": sizes("data.src_sizes.npy"), "tgt_sizes": sizes("data.tgt_sizes.npy")}
         return _dataset_from(split, opt, dicts, training)
-    train = [one(d, True) for _, d in sorted(found["train"].items())]
-    valid = [one(d, False) for _, d in sorted(found["valid"].items())]
+    # -train_sets / -valid_sets pick data sets by their directory index (all of them when empty); -train_set_orders
+    # gives the order in which the chosen training sets are visited; -dataset_index starts a continual-learning run at
+    # that position of the list (reference: train_distributed.py:470-545)
+    want_train = list(getattr(opt, "train_sets", []) or []) or sorted(found["train"])
+    want_valid = list(getattr(opt, "valid_sets", []) or []) or sorted(found["valid"])
+    orders = list(getattr(opt, "train_set_orders", []) or [])
+    if orders:
+        assert len(orders) == len(want_train), "-train_set_orders needs one position per training set"
+        want_train = [i for _, i in sorted(zip(orders, want_train))]
+    start = int(getattr(opt, "dataset_index", 0) or 0)
+    if start > 0:
+        want_train = want_train[start:]
+    missing = [i for i in want_train if i not in found["train"]] + [i for i in want_valid if i not in found["valid"]]
+    if missing:
+        raise FileNotFoundError("data set directories with index %s not found under %s" % (missing, root))
+    train = [one(found["train"][i], True) for i in want_train]
+    valid = [one(found["valid"][i], False) for i in want_valid]
     return dicts, train, (valid or None)
 
 
@@ -133,6 +168,11 @@ def run_process(rank, opt):
     os.environ.setdefault("MASTER_ADDR", opt.master_addr or "127.0.0.1")
     os.environ.setdefault("MASTER_PORT", str(opt.master_port or 8888))
     dicts, train_data, valid_data = load_data(opt)
+    if getattr(opt, "override_dict_from_checkpoint", False) and getattr(opt, "load_from", ""):
+        # continue with the vocabularies the checkpoint was trained with, whatever the data files say
+        ckpt_dicts = torch.load(opt.load_from, map_location="cpu", weights_only=False).get("dicts")
+        if ckpt_dicts:
+            dicts.update({k: v for k, v in ckpt_dicts.items() if k in ("src", "tgt", "langs", "atbs")})
     if getattr(opt, "patch_vocab_multiplier", 1) > 1 and "tgt" in dicts:
         dicts["tgt"].patch(opt.patch_vocab_multiplier)
     constants = Constants.from_dicts(opt, dicts)
