@@ -57,6 +57,58 @@ class MultilingualLayerNorm(nn.Module):
         return F.layer_norm(x, (x.shape[-1],), self.weight[lang].to(x.dtype), self.bias[lang].to(x.dtype), self.eps)
 
 
+class _Norm(nn.Module):
+    """LayerNorm, shared or per language (``-multilingual_layer_norm``)."""
+
+    def __init__(self, dim, n_languages, per_language):
+        super().__init__()
+        self.norm = MultilingualLayerNorm(dim, n_languages) if per_language else LayerNorm(dim)
+        self.per_language = per_language
+
+    def forward(self, x, lang):
+        return self.norm(x, lang) if self.per_language else self.norm(x)
+
+
+class MFWLayer(nn.Module):
+    """Encoder or decoder layer whose projections are language-factorised (``-multilingual_factorized_weights``):
+    pre-LN self-attention [+ encoder-decoder attention] + feed-forward, every Linear a ``FactorizedLinear`` of rank
+    ``-mfw_rank`` (additive factors, plus multiplicative ones unless switched off).  The attention cores run on the
+    packed attention op; the projections are dense per-language weights applied with plain matrix products.
+    Reference: onmt/models/multilingual_translator/relative_transformer_layers.py, onmt/modules/multilingual_factorized/*."""
+
+    def __init__(self, opt, n_languages: int, decoder: bool):
+        super().__init__()
+        d, inner, r = opt.model_size, opt.inner_size, max(1, int(getattr(opt, "mfw_rank", 1)))
+        bias = not getattr(opt, "mfw_no_bias", False)
+        lin = lambda i, o: FactorizedLinear(i, o, n_languages, rank=r, bias=bias, multiplicative=False)
+        per_lang_norm = bool(getattr(opt, "multilingual_layer_norm", False))
+        self.heads, self.dim, self.decoder = opt.n_heads, d, decoder
+        self.dropout, self.attn_dropout, self.act = opt.dropout, opt.attn_dropout, opt.ffn_activation
+        self.attn_norm, self.qkv, self.out = _Norm(d, n_languages, per_lang_norm), lin(d, 3 * d), lin(d, d)
+        if decoder:
+            self.cross_norm, self.q, self.kv, self.cross_out = _Norm(d, n_languages, per_lang_norm), lin(d, d), lin(d, 2 * d), lin(d, d)
+        self.ffn_norm, self.fc1, self.fc2 = _Norm(d, n_languages, per_lang_norm), lin(d, inner), lin(inner, d)
+
+    def _drop(self, y, residual):
+        return residual + F.dropout(y.float(), self.dropout, self.training).to(residual.dtype)
+
+    def forward(self, x, seqs: PackedSeqs, lang: int, memory=None, mem_seqs=None, mem_lang: int = 0):
+        from .. import ops
+        from ..ops.reference import _act
+        h = self.attn_norm(x, lang)
+        ctx = ops.self_attention(self.qkv(h, lang).contiguous(), seqs.cu, self.heads, seqs.max_len, self.decoder, self.attn_dropout,
+                                 self.training)
+        x = self._drop(self.out(ctx, lang), x)
+        if self.decoder and memory is not None:
+            h = self.cross_norm(x, lang)
+            ctx = ops.cross_attention(self.q(h, lang).contiguous(), self.kv(memory, lang).contiguous(), seqs.cu, mem_seqs.cu, self.heads,
+                                      seqs.max_len, mem_seqs.max_len, self.attn_dropout, self.training)
+            x = self._drop(self.cross_out(ctx, lang), x)
+        h = self.ffn_norm(x, lang)
+        h = F.dropout(_act(self.fc1(h, lang).float(), ops.ACT_IDS[self.act]), self.dropout, self.training).to(x.dtype)
+        return self._drop(self.fc2(h, lang), x)
+
+
 class Adapter(nn.Module):
     """Bottleneck adapter: LayerNorm -> down -> ReLU -> up, added to its input."""
 
@@ -95,6 +147,13 @@ class MultilingualTransformer(Seq2SeqBase):
             src_embed.weight = tgt_embed.weight
         self.encoder = TransformerEncoder(opt, src_embed)
         self.decoder = TransformerDecoder(opt, tgt_embed)
+        # language-factorised layers replace the plain ones on the side(s) that ask for them
+        self.mfw_enc = bool(getattr(opt, "multilingual_factorized_weights", False))
+        self.mfw_dec = self.mfw_enc or bool(getattr(opt, "multilingual_factorized_weights_decoder", False))
+        if self.mfw_enc:
+            self.encoder.layers = nn.ModuleList([MFWLayer(opt, n_lang, decoder=False) for _ in self.encoder.layers])
+        if self.mfw_dec:
+            self.decoder.layers = nn.ModuleList([MFWLayer(opt, n_lang, decoder=True) for _ in self.decoder.layers])
         self.lang_embed = nn.Embedding(n_lang, opt.model_size)
         nn.init.normal_(self.lang_embed.weight, 0, opt.model_size ** -0.5)
         self.generator = Generator(opt.model_size, dicts["tgt"].size())
@@ -117,7 +176,7 @@ class MultilingualTransformer(Seq2SeqBase):
         x = self.encoder.embed(src, self.encoder.emb_dropout)
         x = x + self.lang_embed.weight[lang].to(x.dtype)
         for i, layer in enumerate(self.encoder.layers):
-            x = layer(x, src)
+            x = layer(x, src, lang) if self.mfw_enc else layer(x, src)
             if self.use_adapters:
                 x = self.enc_adapters[i](x, lang)
         return self.encoder.final_norm(x), src
@@ -131,7 +190,7 @@ class MultilingualTransformer(Seq2SeqBase):
         def decoder_forward(tgt, memory, src):
             x = dec.embed(tgt, dec.emb_dropout) + self.lang_embed.weight[lang].to(memory.dtype)
             for i, layer in enumerate(dec.layers):
-                x = layer(x, tgt, memory, src)
+                x = layer(x, tgt, lang, memory, src) if self.mfw_dec else layer(x, tgt, memory, src)
                 if self.use_adapters:
                     x = self.dec_adapters[i](x, lang)
             return dec.final_norm(x)

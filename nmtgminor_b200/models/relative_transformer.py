@@ -116,8 +116,10 @@ class RelativeEncoderLayer(nn.Module):
     def __init__(self, opt, causal=False):
         super().__init__()
         self.attn_norm = LayerNorm(opt.model_size)
+        # -max_pos_length: relative distances beyond it share the outermost learnable position vector
         self.attn = RelativeSelfAttention(opt.model_size, opt.n_heads, opt.attn_dropout, causal,
-                                          getattr(opt, "learnable_position_encoding", False))
+                                          getattr(opt, "learnable_position_encoding", False),
+                                          max_len=int(getattr(opt, "max_pos_length", 512) or 512))
         self.ffn_norm = LayerNorm(opt.model_size)
         self.ffn = FeedForward(opt.model_size, opt.inner_size, opt.dropout, opt.ffn_activation)
         self.dropout = opt.dropout

@@ -79,7 +79,8 @@ def _apply_regularisation_options(stack, opt, side: str = "enc"):
     dropout in the embedding), ``-checkpointing N`` (recompute the first N layers in backward) and
     ``-enc_gradient_checkpointing`` / ``-dec_gradient_checkpointing`` (recompute every layer of that stack)."""
     stack.checkpointing = int(getattr(opt, "checkpointing", 0) or 0)
-    if getattr(opt, "%s_gradient_checkpointing" % side, False):
+    whole_stack = getattr(opt, "enc_gradient_checkpointing", False) if side == "enc" else getattr(opt, "dec_gradient_checkpointing", False)
+    if whole_stack:
         stack.checkpointing = 10 ** 6
     for layer in stack.layers:
         layer.variational = bool(getattr(opt, "variational_dropout", False))

@@ -44,11 +44,26 @@ class Gaussian:
         return (-_LOG_SQRT_2PI - torch.log(s) - (w - self.mu) ** 2 / (2 * s ** 2)).sum()
 
 
+# run-wide prior of the scale mixture, set from the command line by ``configure_prior``
+PRIOR = {"pi": PI, "sigma1": SIGMA_1, "sigma2": SIGMA_2}
+
+
+def configure_prior(opt) -> dict:
+    """``-prior_pi``, ``-neg_log_sigma1``, ``-neg_log_sigma2``: mixture weight and the two standard deviations, given as
+    negative logarithms (reference: onmt/bayesian_factory.py / onmt/modules/bayes_by_backprop: ``sigma = exp(-x)``)."""
+    PRIOR["pi"] = float(getattr(opt, "prior_pi", PI))
+    PRIOR["sigma1"] = math.exp(-float(getattr(opt, "neg_log_sigma1", -math.log(SIGMA_1))))
+    PRIOR["sigma2"] = math.exp(-float(getattr(opt, "neg_log_sigma2", -math.log(SIGMA_2))))
+    return dict(PRIOR)
+
+
 class ScaleMixtureGaussian:
     """Prior ``pi * N(0, sigma1^2) + (1 - pi) * N(0, sigma2^2)`` (Blundell et al. 2015)."""
 
-    def __init__(self, pi: float = PI, sigma1: float = SIGMA_1, sigma2: float = SIGMA_2):
-        self.pi, self.sigma1, self.sigma2 = pi, sigma1, sigma2
+    def __init__(self, pi: Optional[float] = None, sigma1: Optional[float] = None, sigma2: Optional[float] = None):
+        self.pi = PRIOR["pi"] if pi is None else pi
+        self.sigma1 = PRIOR["sigma1"] if sigma1 is None else sigma1
+        self.sigma2 = PRIOR["sigma2"] if sigma2 is None else sigma2
 
     def _component(self, w, sigma):
         return -_LOG_SQRT_2PI - math.log(sigma) - w ** 2 / (2 * sigma ** 2)

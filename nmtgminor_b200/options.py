@@ -190,6 +190,19 @@ UNSUPPORTED_FLAGS = {
     "decoder_layers_memory": "the n-gram memory decoder",
     "branchformer": "Branchformer cgMLP blocks",
     "wav2vec_spec_augment": "SpecAugment inside wav2vec 2.0 (time masking is the encoder's mask_prob)",
+    "multilingual_partitioned_weights": "partitioned (MPW) multilingual weights (the factorised MFW weights are built)",
+    "mpw_factor_size": "partitioned (MPW) multilingual weights",
+    "multilingual_linear_projection": "per-language input projections",
+    "pos_emb_type": "position-embedding variants of the legacy speech Transformer",
+    "absolute_position_encoding": "absolute positions inside the relative speech Transformer",
+    "decoder_late_emb_scale": "late embedding scaling",
+    "encoder_early_emb_scale": "early embedding scaling",
+    "no_input_scale": "unscaled speech inputs of the relative speech Transformer",
+    "transducer_loss": "transducer training of the translation models (ops/sequence.py has the joint and loss kernels)",
+    "ctc_loss_delay": "delayed CTC loss",
+    "char_ctc": "character-level CTC targets",
+    "cache_dir": "cached encoder outputs",
+    "memory_loss_coeff": "the n-gram memory decoder",
 }
 
 

@@ -391,6 +391,44 @@ class OfflineCLTrainer(OCLTrainer):
         return super().train_epoch(datasets, valid_data, epoch, resume_itr_state)
 
 
+class EWCTrainer(OfflineCLTrainer):
+    """The main trainer's elastic-weight-consolidation switches (reference: onmt/train_utils/mp_trainer.py:402-412,
+    1162-1517): ``-estimate_fisher_information`` runs over the training data once, accumulates the squared gradients
+    and writes them with the current weights to ``<checkpoint>.fisher``; ``-load_fisher <file>`` reads such a file
+    and adds the penalty ``ewc_importance / 2 * sum F (w - w*)^2`` to every later update."""
+
+    def __init__(self, *a, **kw):
+        super().__init__(*a, **kw)
+        opt = self.opt
+        if self.ewc is None:
+            self.ewc = EWC(self.flat_params().numel(), self.device, float(getattr(opt, "ewc_importance", 0.0) or 1.0),
+                           getattr(opt, "ewc_normalize", False))
+        path = getattr(opt, "load_fisher", "") or ""
+        if path:
+            self.ewc.load_state_dict(torch.load(path, map_location="cpu", weights_only=False))
+            if self.ewc.anchor is None:
+                self.ewc.anchor = self.flat_params().clone()
+            self.log("[INFO] Fisher information loaded from %s" % path)
+
+    def fisher_path(self) -> str:
+        base = getattr(self.opt, "load_from", "") or (getattr(self.opt, "save_model", "model") + ".pt")
+        return base + ".fisher"
+
+    def run(self, checkpoint=None, train_data=None, valid_data=None):
+        if getattr(self.opt, "estimate_fisher_information", False):
+            data = train_data[0] if _is_list(train_data) else train_data
+            self.estimate_fisher(data, max_batches=10 ** 9)
+            sd = self.ewc.state_dict()
+            if self.is_main():
+                torch.save(sd, self.fisher_path())
+                self.log("[INFO] Fisher information written to %s" % self.fisher_path())
+            return self.fisher_path()
+        return super().run(checkpoint, train_data, valid_data)
+
+    def train_epoch(self, train_data, valid_data, epoch: int, resume_itr_state=None):
+        return OCLTrainer.train_epoch(self, train_data, valid_data, epoch, resume_itr_state)
+
+
 class VATTrainer(OCLTrainer):
     """Virtual adversarial training: besides the supervised loss, the output distribution must not move when the
     source embeddings are perturbed in the direction that changes it most (one power iteration)."""
@@ -459,6 +497,11 @@ class MetaOCLTrainer(OCLTrainer):
 
 class BayesianOCLTrainer(OCLTrainer):
     """Adds ``kl_weight * sum(module.kl_divergence())`` over Bayes-by-backprop layers to every step."""
+
+    def __init__(self, device, dicts, opt, constants=None, **kw):
+        from ..modules.bayesian import configure_prior
+        configure_prior(opt)          # -prior_pi / -neg_log_sigma1 / -neg_log_sigma2 before any Bayesian layer is built
+        super().__init__(device, dicts, opt, constants, **kw)
 
     def train_step(self, batch, dataset_id: int = 0):
         loss, correct = self.engine.train_step(batch, update=False)
@@ -536,4 +579,6 @@ def select_trainer(opt):
         return OfflineCLTrainer
     if getattr(opt, "model", "") in ("classifier", "wav2vec2_classifier") or getattr(opt, "classifier_training", False):
         return ClassifierTrainer
+    if getattr(opt, "estimate_fisher_information", False) or getattr(opt, "load_fisher", ""):
+        return EWCTrainer
     return Trainer

@@ -26,6 +26,11 @@ from nmtgminor_b200.options import make_parser
 def _dataset_from(split, opt, dicts, training):
     if split is None or (split.get("src") is None and split.get("tgt") is None):
         return None
+    if getattr(opt, "model", "") in ("transformer_xl_lm", "TransformerXL") and split.get("src") is None and split.get("tgt") is not None:
+        # language-model training: the target side is one long token stream cut into [-batch_size_sents, -lm_seq_length] blocks
+        from nmtgminor_b200.data.audio import LanguageModelDataset
+        stream = torch.cat([torch.as_tensor(t).view(-1) for t in split["tgt"]])
+        return LanguageModelDataset(stream, opt.batch_size_sents if opt.batch_size_sents > 0 else 32, int(getattr(opt, "lm_seq_length", 128)))
     audio = getattr(opt, "encoder_type", "text") != "text"
     augmenter = None
     if training and audio and getattr(opt, "augment_speech", False):
