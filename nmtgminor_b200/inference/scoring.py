@@ -3,7 +3,7 @@ prediction, and segment-wise (streaming) translation that carries the last targe
 as a forced prefix context.
 
 Reference: onmt/inference/perplexity_scorer.py:15, onmt/Rescorer.py:14, onmt/inference/predictor.py:14,
-onmt/inference/stream_translator.py:13, onmt/inference/global_translator.py:13.
+onmt/inference/stream_translator.py:13 (the document-global beam is ``legacy_search.GlobalStreamTranslator``).
 """
 from __future__ import annotations
 
@@ -110,5 +110,3 @@ class StreamTranslator(Translator):
         self.prev = (self.prev + hyp)[-max(self.context_tokens, 1) * 4:]
         return hyp
 
-
-GlobalStreamTranslator = StreamTranslator
