@@ -13,6 +13,7 @@ Reference behaviour: onmt/models/transformers.py:48-223 (encoder), :226-510 (dec
 """
 from __future__ import annotations
 
+import copy
 import math
 from typing import Dict, Optional
 
@@ -305,7 +306,16 @@ class Seq2SeqBase(nn.Module):
         else:
             hidden = self.decoder(tgt, context, src)
         out = {"hidden_packed": hidden, "context_packed": context, "src": src, "tgt": tgt, "target": labels}
-        if compute_loss and getattr(self.generator, "fix_norm", False):
+        if compute_loss and self.training and getattr(self, "nce", None) is not None:
+            # noise-contrastive training: target and noise scores only, no [rows, V] logits
+            res = self.nce_loss(self.nce(hidden, labels), labels)
+            loss = res["loss"]
+            if grad_scale is not None and torch.is_grad_enabled():
+                from ..ops.reference import scale_gradient
+                gs = grad_scale if isinstance(grad_scale, torch.Tensor) else torch.tensor(float(grad_scale), device=loss.device)
+                loss = scale_gradient(loss, gs.to(loss.device))
+            out.update(loss=loss, correct=None, row_loss=None)
+        elif compute_loss and getattr(self.generator, "fix_norm", False):
             logits = self.generator(hidden)
             loss, correct, row_loss = ops.cross_entropy(logits if logits.is_contiguous() else logits.contiguous(), labels,
                                                         self.label_smoothing if self.training else 0.0, self.pad_idx)
@@ -436,6 +446,83 @@ class Transformer(Seq2SeqBase):
         self.label_smoothing = getattr(opt, "label_smoothing", 0.0)
         self.switchout = float(getattr(opt, "switchout", 0.0) or 0.0)
         self.generator_chunk_rows = int(getattr(opt, "generator_chunk_rows", 0) or 0)
+        # -mirror_loss: a second decoder reads the target right to left; its loss is added and the forward decoder's
+        # states (through a learned map g) are pulled towards the backward decoder's states of the same positions
+        self.mirror_weight = float(getattr(opt, "mirror_loss", 0.0) or 0.0)
+        if self.mirror_weight > 0:
+            self.mirror_decoder = copy.deepcopy(self.decoder)
+            self.mirror_g = nn.Linear(opt.model_size, opt.model_size)
+            self.mirror_generator = Generator(opt.model_size, tgt_vocab)
+            self.mirror_generator.weight = self.decoder.embed.weight
+        # nce_noise > 0 (set by older checkpoints' options): noise-contrastive training of the output layer
+        if int(getattr(opt, "nce_noise", 0) or 0) > 0:
+            from ..modules.nce import NCELinear, NCELoss, build_unigram_noise
+            self.nce = NCELinear(opt.model_size, tgt_vocab, build_unigram_noise(dictionary=dicts["tgt"]), int(opt.nce_noise),
+                                 weight=self.generator.weight, bias=self.generator.bias if self.generator.bias is not None else False)
+            self.nce_loss = NCELoss(opt.model_size, tgt_vocab, int(opt.nce_noise), label_smoothing=self.label_smoothing,
+                                    padding_idx=self.pad_idx)
+        # -reconstruct: a third decoder regenerates the source from the decoder's states
+        self.reconstruct = bool(getattr(opt, "reconstruct", False))
+        if self.reconstruct:
+            rec_embed = Embedding(src_vocab, opt.model_size, self.pad_idx, max_pos=max_pos)
+            rec_embed.weight = self.encoder.embed.weight
+            self.rec_linear = nn.Linear(opt.model_size, opt.model_size)
+            self.rec_decoder = TransformerDecoder(opt, rec_embed)
+            self.rec_generator = Generator(opt.model_size, src_vocab)
+            self.rec_generator.weight = self.encoder.embed.weight
+
+    @staticmethod
+    def _flip_index(seqs: PackedSeqs, rows: int):
+        """Row permutation that reverses every sequence of a packed batch in place (rows of the static padding map to
+        themselves)."""
+        from ..modules.dropout import _sentence_of_row
+        cu = seqs.cu.to(torch.int64)
+        sent = _sentence_of_row(seqs.cu, rows)
+        i = torch.arange(rows, device=cu.device)
+        flipped = cu[sent] + cu[sent + 1] - 1 - i
+        return torch.where(i < cu[-1], flipped, i)
+
+    def auxiliary_losses(self, batch, context, src, out):
+        """Mirror network and source reconstruction (reference: onmt/models/transformers.py:622-666 for the extra
+        decoders, onmt/modules/loss.py:321-391 for the terms).  With the full target ``BOS y1 .. yn EOS`` the backward
+        decoder's input is the per-sentence reversal of the forward labels and its labels are the reversal of the forward
+        inputs; the state of the backward decoder at reversed position t is the regression target (no gradient) of
+        ``g(forward state t)``, summed squared error divided by the model size."""
+        if not self.training or not (self.mirror_weight > 0 or self.reconstruct):
+            return None
+        tgt, hidden, labels = out["tgt"], out["hidden_packed"], out["target"]
+        smoothing = self.label_smoothing
+        total = None
+        if self.mirror_weight > 0:
+            rows = tgt.tokens.shape[0]
+            flip = self._flip_index(tgt, rows)
+            rev_in = PackedSeqs(labels.index_select(0, flip), tgt.positions, tgt.cu, tgt.max_len, tgt.lengths, tgt.extras)
+            rev_labels = tgt.tokens.index_select(0, flip)
+            rev_labels = torch.where(labels == self.pad_idx, torch.full_like(rev_labels, self.pad_idx), rev_labels)
+            rev_hidden = self.mirror_decoder(rev_in, context, src)
+            rev_loss, _, _ = ops.generator_cross_entropy(rev_hidden, self.mirror_generator.weight, self.mirror_generator.bias,
+                                                         rev_labels, smoothing, self.pad_idx)
+            valid = (labels != self.pad_idx).unsqueeze(-1)
+            target_states = rev_hidden.detach().index_select(0, flip)
+            diff = (self.mirror_g(hidden).float() - target_states.float()) * valid
+            mirror = diff.pow(2).sum() / hidden.shape[-1]
+            out["rev_loss"], out["mirror_loss"] = rev_loss.detach(), mirror.detach()
+            total = rev_loss + self.mirror_weight * mirror
+        if self.reconstruct:
+            # input of the reconstruction decoder: the source shifted right behind the target's first symbol (BOS)
+            n = src.tokens.shape[0]
+            cu = src.cu.to(torch.int64)
+            shifted = torch.cat([src.tokens[:1], src.tokens[:-1]])
+            first = torch.zeros(n, dtype=torch.bool, device=src.tokens.device)
+            first[cu[:-1].clamp(max=n - 1)] = True
+            bos = tgt.tokens[tgt.cu[:-1].to(torch.int64)][0]
+            rec_in = PackedSeqs(torch.where(first, bos.expand(n), shifted), src.positions, src.cu, src.max_len, src.lengths, src.extras)
+            rec_hidden = self.rec_decoder(rec_in, self.rec_linear(hidden), tgt)
+            rec_loss, _, _ = ops.generator_cross_entropy(rec_hidden, self.rec_generator.weight, self.rec_generator.bias,
+                                                         src.tokens, smoothing, self.pad_idx)
+            out["rec_loss"] = rec_loss.detach()
+            total = rec_loss if total is None else total + rec_loss
+        return total
 
     def share_enc_dec_embedding(self):
         self.encoder.embed.weight = self.decoder.embed.weight

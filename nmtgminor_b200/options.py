@@ -149,7 +149,6 @@ UNSUPPORTED_FLAGS = {
     "max_examples_seen": "example-count limits of the continual-learning trainers",
     "stream_context": "streaming context selection",
     "rotary_position_encoding": "rotary position encoding in the speech / relative Transformers",
-    "reconstruct": "the reconstruction decoder",
     "weight_norm": "weight-normalised linear layers",
     "stochastic_sublayer": "stochastic sub-layer dropping",
     "activation_layer": "alternative activation-layer layouts (maxout)",

@@ -6,7 +6,7 @@ training path) it is passed through; otherwise the label-smoothed cross-entropy 
 ``outputs['logprobs']`` (logits ``[T, B, V]``) over ALL non-pad target positions (the reference's B×T / T×B mask
 mix-up is not reproduced).  Also here: CTC (``CTCLossFunc``, onmt/modules/loss.py:530, onmt/speech/ctc_loss.py:9-116),
 the combined NMT + CTC loss (:611), masked predictive coding (``MPCLoss`` :411), classification
-(``ClassifierLoss`` :448), language-id cross-entropy (onmt/models/speech_recognizer/lid_loss.py:13) and the
+(``ClassifierLoss`` :448), language-model fusion (``FusionLoss`` :660), language-id cross-entropy (onmt/models/speech_recognizer/lid_loss.py:13) and the
 KL distillation term used by the continual-learning trainers.
 """
 from __future__ import annotations
@@ -40,8 +40,10 @@ class NMTLossFunc(CrossEntropyLossBase):
         if model_outputs.get("loss") is not None:
             loss = model_outputs["loss"].sum()
             total = int((targets != self.padding_idx).sum()) if targets is not None else 0
+            # terms of the mirror / reconstruction decoders are already inside the model's loss; they are reported apart
             return {"loss": loss, "data": loss.detach(), "correct": model_outputs.get("correct"), "total": total,
-                    "rev_loss": None, "mirror_loss": None}
+                    "rev_loss": model_outputs.get("rev_loss"), "mirror_loss": model_outputs.get("mirror_loss"),
+                    "rec_loss": model_outputs.get("rec_loss")}
         logits = model_outputs["logprobs"]
         flat_logits = logits.reshape(-1, logits.shape[-1])
         flat_targets = targets.reshape(-1)
@@ -57,6 +59,37 @@ class NMTLossFunc(CrossEntropyLossBase):
             mirror = ((hid - rev_hid.flip(0)) * mask).float().pow(2).sum()
             out.update(rev_loss=rev, rev_loss_data=rev_data, mirror_loss=mirror)
         return out
+
+
+class FusionLoss(CrossEntropyLossBase):
+    """Loss of a translation model fused with a frozen language model ("simple fusion", pre-norm variant):
+    ``log p = log_softmax(tm_logits + log p_lm)``.  ``model_outputs['tm']['hidden']`` / ``['lm']['hidden']`` are the two
+    decoders' states ``[T, B, H]``, ``model`` gives the two output layers (``model.tm_model.generator``,
+    ``model.lm_model.generator``); a ``model_outputs['logprobs']`` that already holds the fused log-probabilities is used
+    as it is.  Reference: onmt/modules/loss.py:660-737."""
+
+    def forward(self, model_outputs, targets, model=None, backward: bool = False, normalizer: float = 1.0, **_unused):
+        flat_targets = targets.reshape(-1)
+        keep = (flat_targets != self.padding_idx).nonzero(as_tuple=False).squeeze(1)
+        if "tm" in model_outputs and model is not None:
+            tm = model_outputs["tm"]["hidden"]
+            lm = model_outputs["lm"]["hidden"]
+            tm = tm.reshape(-1, tm.shape[-1]).index_select(0, keep)
+            lm = lm.reshape(-1, lm.shape[-1]).index_select(0, keep)
+            tm_logits = model.tm_model.generator(tm).float()
+            with torch.no_grad():
+                log_lm = torch.log_softmax(model.lm_model.generator(lm).float(), -1)
+            dists = torch.log_softmax(tm_logits + log_lm, -1)
+        else:
+            lp = model_outputs["logprobs"]
+            dists = lp.reshape(-1, lp.shape[-1]).float().index_select(0, keep)
+        gold = flat_targets.index_select(0, keep)
+        smoothing = self.label_smoothing if self.training else 0.0
+        nll = -dists.gather(1, gold[:, None]).squeeze(1)
+        loss = ((1.0 - smoothing) * nll - smoothing * dists.mean(-1)).sum() if smoothing > 0 else nll.sum()
+        if backward:
+            (loss / normalizer).backward()
+        return {"loss": loss, "data": float(loss.detach()), "correct": int((dists.argmax(-1) == gold).sum()), "total": int(gold.numel())}
 
 
 class CTCLossFunc(nn.Module):
