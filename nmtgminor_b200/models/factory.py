@@ -34,6 +34,9 @@ def build_model(opt, dicts, remove_pretrain: bool = False, constants=None):
     validate_model_options(opt)
     model = _REGISTRY[name](opt, dicts)
     init_model_parameters(model, opt)
+    if int(getattr(opt, "batch_ensemble", 0) or 0) > 0:
+        from ..modules.batch_ensemble import convert_to_batch_ensemble
+        convert_to_batch_ensemble(model, int(opt.batch_ensemble))
     if not remove_pretrain:          # a full checkpoint is about to be loaded: its weights replace the pretrained ones
         load_pretrained_parts(model, opt, dicts)
     apply_freeze_options(model, opt)

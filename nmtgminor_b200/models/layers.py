@@ -316,17 +316,19 @@ class FeedForward(nn.Module):
 def _sub(layer, fn, inp, residual, p, seqs, *args):
     """Sub-layer output + residual.  Element-wise dropout rides in the producing kernel; with ``layer.variational``
     the mask is shared along time instead and applied outside the kernel."""
+    kw = {"seqs": seqs} if getattr(fn, "wants_seqs", False) else {}    # batch-ensemble blocks pick a member per sentence
     if getattr(layer, "variational", False) and layer.training and p > 0:
         from ..modules.dropout import variational_dropout
-        y = fn(inp, *args, residual=None, dropout_p=0.0)
+        y = fn(inp, *args, residual=None, dropout_p=0.0, **kw)
         return residual + variational_dropout(y, p, True, cu=seqs.cu)
-    return fn(inp, *args, residual=residual, dropout_p=p)
+    return fn(inp, *args, residual=residual, dropout_p=p, **kw)
 
 
 def _scaled_sub(layer, fn, inp, residual, p, seqs, *args, scale=None):
     """``residual + scale * D(fn(inp))`` with ``scale`` a float (the half steps of a macaron block) or a learned scalar
     (``-rezero``: starts at zero, no LayerNorm in front).  Outside the fused residual epilogue, which cannot scale."""
-    y = fn(inp, *args, residual=None, dropout_p=p)
+    kw = {"seqs": seqs} if getattr(fn, "wants_seqs", False) else {}
+    y = fn(inp, *args, residual=None, dropout_p=p, **kw)
     return residual + (y.float() * scale).to(y.dtype)
 
 

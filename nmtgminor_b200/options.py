@@ -154,7 +154,6 @@ UNSUPPORTED_FLAGS = {
     "activation_layer": "alternative activation-layer layouts (maxout)",
     "residual_type": "gated / highway residual connections",
     "extra_context_size": "extra streaming context",
-    "batch_ensemble": "batch-ensemble weights",
     "no_decoder": "encoder-only sequence models in the translation trainer",
     "copy_generator": "the copy generator",
     "favor_attention": "FAVOR+ attention inside the main Transformer (models/efficient_attention.py has the stand-alone layer)",
