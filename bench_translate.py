@@ -35,11 +35,14 @@ def run_reference(args):
     # With a large enough vocabulary the first decoder call then receives four target positions while the Transformer's
     # incremental step builds its masks for one (onmt/modules/attention.py:126 raises "output with shape [.., 1, 1] doesn't
     # match the broadcast shape [.., 1, 4]"), so the stock translator cannot decode a text Transformer at all.  The arm is
-    # reported as unavailable; --force-reference runs it anyway on the CPU to show the error.
+    # reported as unavailable; --force-reference runs it anyway on the CPU to show the error.  The reference's other search,
+    # Translator.translate_batch (onmt/inference/translator.py:331, one Beam object per sentence), was tried on the CPU as
+    # well and stops at the same line ("output with shape [1, 4, 1, 1] doesn't match the broadcast shape [1, 4, 1, 32]").
     if not args.force_reference or torch.cuda.is_available():
         print(json.dumps({"impl": "reference", "unavailable": "the reference's FastTranslator hard-codes the Whisper prompt "
-                          "(token ids up to 50364, decoding from step 3) and fails in the Transformer's incremental attention mask; "
-                          "see the comment in bench_translate.py: run_reference"}))
+                          "(token ids up to 50364, decoding from step 3); it and the legacy Translator.translate_batch both fail in the "
+                          "Transformer's incremental attention mask (onmt/modules/attention.py:126: output with shape [1, 4, 1, 1] "
+                          "doesn't match the broadcast shape [1, 4, 1, 32])"}))
         return
     cuda = torch.cuda.is_available()
     runner = br.ReferenceRunner(args.vocab, "cuda:0" if cuda else "cpu", tiny=args.tiny)
