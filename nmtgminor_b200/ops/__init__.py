@@ -67,7 +67,7 @@ def extension_available() -> bool:
 
 _KERNEL_CALLS = {"gemm": 1, "layernorm_fwd": 1, "layernorm_bwd": 1, "xent_fused": 1, "dropout_add": 1,
                  "dropout_colsum": 1, "embed_fwd": 1, "embed_bwd": 1, "colsum": 1, "sq_norm": 1, "adamw_flat": 1, "cast_f32_bf16": 1, "attn_fwd": 1,
-                 "attn_bwd": 1, "update_pieces": 1}
+                 "attn_bwd": 1, "update_pieces": 1, "act_backward": 1}
 LAUNCHES = [0]   # kernels of this extension enqueued so far (Python-side count of launcher calls)
 
 
@@ -228,10 +228,12 @@ class _LinearFn(torch.autograd.Function):
         fused_gb = want_gb and act == 0 and p > 0.0 and _colsum_fusable(dy)
         if fused_gb:
             dz = ext().dropout_colsum(dy, p, seed, sid, ctx.gb)  # regenerated mask and bias gradient in one pass
+        elif act != 0 and dy.numel() % 8 == 0:
+            dz = ext().act_backward(dy, z, act, p, seed, sid)    # regenerated mask times act'(z) in one pass
         else:
             dz = ext().dropout_add(dy, None, p, seed, sid) if p > 0.0 else dy  # regenerates the forward mask
-        if act != 0:
-            dz = _act_backward(dz, z, act)
+            if act != 0:
+                dz = _act_backward(dz, z, act)
         if ctx.gw is not None:
             gemm(dz, x, ctx.gw, a_mn_major=True, b_mn_major=True, accumulate=True, allow_split_k=True)
         if want_gb and not fused_gb:
@@ -250,7 +252,8 @@ def _colsum_fusable(dy):
 
 
 def _act_backward(dh, z, act):
-    """dz = dh * act'(z) (stand-alone Linear with an activation; the FFN path fuses this into a GEMM)."""
+    """dz = dh * act'(z) in PyTorch ops: the oracle of the ``act_backward`` kernel, and the path for element counts that are
+    not a multiple of 8 (the FFN path fuses this step into a GEMM epilogue)."""
     a = z.float()
     if act == 1:
         g = (a > 0).float()

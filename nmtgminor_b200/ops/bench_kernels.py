@@ -172,6 +172,41 @@ def bench_attention(rows):
         rows.append({"kernel": "attention bwd causal=%s" % causal, "ms": ms, "tflops": 2.5 * fl / ms / 1e9})
 
 
+def bench_attention_ablation(rows):
+    """Short-sequence attention backward with parts of the work switched off (every barrier hand-shake kept): which role
+    bounds the item rate.  Same workload as ``bench_attention``."""
+    import numpy as np
+    rng = np.random.RandomState(0)
+    lens = []
+    while sum(lens) < 8192 - 100:
+        lens.append(int(rng.randint(20, 101)))
+    n = sum(lens)
+    cap = (n + 127) // 128 * 128
+    heads, W = 16, 1024
+    cu = torch.zeros(len(lens) + 1, dtype=torch.int32)
+    cu[1:] = torch.tensor(lens).cumsum(0)
+    cu = cu.cuda()
+    qkv = torch.randn(cap, 3 * W, device="cuda").bfloat16()
+    out = torch.zeros(cap, W, device="cuda", dtype=torch.bfloat16)
+    lse = torch.empty(heads, cap, device="cuda")
+    e = ops.ext()
+    q, k, v = qkv[:, :W], qkv[:, W:2 * W], qkv[:, 2 * W:]
+    e.attn_fwd(q, k, v, out, lse, cu, cu, heads, 100, 100, False, 0.125, 0.1, 1, 1)
+    dqkv = torch.zeros_like(qkv)
+    dout = torch.randn_like(out)
+    names = {0: "everything", 1: "no P/dS math", 2: "no gradient read-out", 4: "no gradient MMAs", 8: "no S/dP MMAs", 16: "no TMA loads",
+             32: "no P/dS stores", 64: "no dropout masks", 3: "no math, no read-out", 19: "no math, no read-out, no loads",
+             31: "barriers only", 12: "no MMAs"}
+    try:
+        for bits, name in names.items():
+            e.set_attn_bwd_ablation(bits)
+            ms = time_ms(lambda: e.attn_bwd(q, k, v, out, lse, dout, dqkv[:, :W], dqkv[:, W:2 * W], dqkv[:, 2 * W:], None, cu, cu,
+                                            heads, 100, 100, False, 0.125, 0.1, 1, 1))
+            rows.append({"kernel": "attention bwd short, %s" % name, "ms": ms, "items_per_cta": len(lens) * heads / 148.0})
+    finally:
+        e.set_attn_bwd_ablation(0)
+
+
 def bench_attention_long(rows):
     """The general multi-tile kernels on speech-length sequences: 8 x 1500 encoder frames with 20 heads (Whisper-large
     encoder self-attention, no dropout) and 8 x 448 causal with dropout 0.1 (decoder self-attention)."""
@@ -294,6 +329,8 @@ def main():
         bench_elementwise(rows)
     if "attn" in which:
         bench_attention(rows)
+    if "attn_ablate" in which:
+        bench_attention_ablation(rows)
     if "attn_long" in which:
         bench_attention_long(rows)
     tf_peak, bw_peak, kind = peaks()

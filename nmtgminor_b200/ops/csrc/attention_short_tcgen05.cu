@@ -8,11 +8,13 @@
 // is what dominates when a sentence has only 20..100 tokens.
 //
 // forward : two softmax groups alternate items (TMEM: S0 S1 | O0 O1), three Q/K/V slots.
-// backward: one group (TMEM: S dP | dQ dK dV), two Q/K/V/dO slots; P and dS are staged once in shared
-//           memory and consumed K-major (dQ = dS K) and MN-major (dV = P^T dO, dK = dS^T Q).
+// backward: a math group (P, D, dS) and an epilogue group (dQ, dK, dV) work on neighbouring items; TMEM holds two sets
+//           (S dP, reused for dV dQ dK), two Q/K/V/dO slots; P and dS are staged once in shared memory and consumed
+//           K-major (dQ = dS K) and MN-major (dV = P^T dO, dK = dS^T Q).
 // MMA reduction lengths are trimmed to the real sequence lengths (multiples of 16).
 // Same numerics, dropout counters and interfaces as the general kernels in attention_tcgen05.cu.
 #include "attention_common.cuh"
+#include "bounds_check.cuh"
 
 namespace b200 {
 
@@ -32,6 +34,9 @@ __device__ __forceinline__ Item get_item(const AttnArgs& p, int item) {
   it.k0 = p.cu_k[b];
   it.k_len = p.cu_k[b + 1] - it.k0;
   it.valid = it.q_len > 0 && it.k_len > 0 && it.q_len <= kTile && it.k_len <= kTile;
+  // a sequence that does not fit one tile (or offsets that run backwards) is skipped by every role of the kernel; the host
+  // dispatch sends such batches to the general kernels, so meeting one here means the offsets are wrong
+  if (!it.valid && (it.q_len < 0 || it.k_len < 0 || it.q_len > kTile || it.k_len > kTile) && threadIdx.x == 0) NMTG_BOUNDS_HIT();
   return it;
 }
 
@@ -296,50 +301,175 @@ attn_fwd_short_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
 // ---------------------------------------------------------------------------------------------------
 // backward
 // ---------------------------------------------------------------------------------------------------
+// Roles (320 threads): warps 0-3 compute P and dS of item i, warps 4-7 write the gradients of item i-1, warp 8 is the
+// TMA producer, warp 9 issues every MMA.  TMEM holds two sets of 256 columns, set = item & 1:
+//   columns   0..127  S  = Q K^T          later  dV (0..63) and dQ (64..127)
+//   columns 128..255  dP = dO V^T         later  dK (128..191)
+// so the S / dP MMAs of item i+1 run while the gradients of item i-1 are still being read out of the other set.
+// P and dS are staged in ONE pair of shared-memory tiles; the math group waits for the gradient MMAs of the previous
+// item (pds_free) only right before its first store, after the exponentials of the new item are done.
+// D = rowsum(dO * O) is not read from memory: it equals rowsum(P_dropped * dP), both of which the math group holds.
 constexpr int kBwdSlots = 2;
 constexpr int kBwdSlotBytes = 4 * kTileBytes;   // Q, K, V, dO
-constexpr int kBwdShortThreads = 192;   // warps 0-3: math group, warp 4: TMA producer, warp 5: MMA issuer
+constexpr int kBwdShortThreads = 320;
 constexpr int kBwdShortSmem = kBwdSlots * kBwdSlotBytes + 2 * kPBytes + 256 + 1024;
+constexpr uint32_t kBwdIssuePolls = 1u << 22;   // polls of the MMA warp without progress before it gives up
+
+// bit j = element (base + j) is kept; base a multiple of 4
+__device__ __forceinline__ uint32_t drop_mask32(const DropRng& rng, unsigned long long base) {
+  uint32_t m = 0;
+#pragma unroll
+  for (int g = 0; g < 8; ++g) {
+    const uint32_t w = rng.word((base >> 2) + g);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) m |= (rng.keep(w, j) ? 1u : 0u) << (g * 4 + j);
+  }
+  return m;
+}
+
+// rs[] : raw scores -> probabilities 2^(S * scale * log2 e - lse * log2 e), 0 outside the sequence / causal triangle.
+// A row past the sequence has lse2 = +inf, so its probabilities are 0 without a per-element test.
+__device__ __forceinline__ void bwd_probs32(uint32_t (&rs)[32], int c, int t, int k_len, bool causal, float scale_log2,
+                                            float lse2) {
+  if (!causal && (c + 1) * 32 <= k_len) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) rs[j] = __float_as_uint(ex2_approx(fmaf(__uint_as_float(rs[j]), scale_log2, -lse2)));
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      const int col = c * 32 + j;
+      const bool valid = col < k_len && (!causal || col <= t);
+      rs[j] = valid ? __float_as_uint(ex2_approx(fmaf(__uint_as_float(rs[j]), scale_log2, -lse2))) : 0u;
+    }
+  }
+}
+
+// sum over the 32 columns of P * dP over the kept elements (the keep scale is applied by the caller)
+__device__ __forceinline__ float bwd_dsum32(const uint32_t (&pr)[32], const uint32_t (&dp)[32], uint32_t keep, bool do_drop) {
+  float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+  if (!do_drop) {
+#pragma unroll
+    for (int j = 0; j < 32; j += 4) {
+      a0 = fmaf(__uint_as_float(pr[j]), __uint_as_float(dp[j]), a0);
+      a1 = fmaf(__uint_as_float(pr[j + 1]), __uint_as_float(dp[j + 1]), a1);
+      a2 = fmaf(__uint_as_float(pr[j + 2]), __uint_as_float(dp[j + 2]), a2);
+      a3 = fmaf(__uint_as_float(pr[j + 3]), __uint_as_float(dp[j + 3]), a3);
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; j += 4) {
+      a0 = fmaf(__uint_as_float(pr[j]), ((keep >> j) & 1u) ? __uint_as_float(dp[j]) : 0.f, a0);
+      a1 = fmaf(__uint_as_float(pr[j + 1]), ((keep >> (j + 1)) & 1u) ? __uint_as_float(dp[j + 1]) : 0.f, a1);
+      a2 = fmaf(__uint_as_float(pr[j + 2]), ((keep >> (j + 2)) & 1u) ? __uint_as_float(dp[j + 2]) : 0.f, a2);
+      a3 = fmaf(__uint_as_float(pr[j + 3]), ((keep >> (j + 3)) & 1u) ? __uint_as_float(dp[j + 3]) : 0.f, a3);
+    }
+  }
+  return (a0 + a1) + (a2 + a3);
+}
+
+// Packs the dropped probabilities and dS = P * (dP_dropped - D) of 32 columns to bf16 and stores them into the two
+// 128-byte-swizzled staging tiles (row t, columns c * 32 ..).  dS is kept without the softmax scale (applied when dQ and
+// dK leave TMEM).
+__device__ __forceinline__ void bwd_emit32(const uint32_t (&pr)[32], const uint32_t (&dp)[32], uint32_t keep, bool do_drop,
+                                           float keep_scale, float Drow, int c, int t, uint8_t* sP, uint8_t* sDS) {
+#pragma unroll
+  for (int g4 = 0; g4 < 4; ++g4) {
+    uint4 o1, o2v;
+    __nv_bfloat162* a2 = reinterpret_cast<__nv_bfloat162*>(&o1);
+    __nv_bfloat162* b2 = reinterpret_cast<__nv_bfloat162*>(&o2v);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float pd[2], ds[2];
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int idx = g4 * 8 + 2 * j + e;
+        const float prob = __uint_as_float(pr[idx]), d = __uint_as_float(dp[idx]);
+        if (do_drop) {
+          const float kf = ((keep >> idx) & 1u) ? keep_scale : 0.f;
+          pd[e] = prob * kf;
+          ds[e] = prob * fmaf(d, kf, -Drow);
+        } else {
+          pd[e] = prob;
+          ds[e] = prob * (d - Drow);
+        }
+      }
+      a2[j] = __floats2bfloat162_rn(pd[0], pd[1]);
+      b2[j] = __floats2bfloat162_rn(ds[0], ds[1]);
+    }
+    const int chunk = c * 4 + g4;
+    const uint32_t off = (chunk >> 3) * kTileBytes + sw128_offset(t, chunk & 7);
+    *reinterpret_cast<uint4*>(sP + off) = o1;
+    *reinterpret_cast<uint4*>(sDS + off) = o2v;
+  }
+}
+
+// One gradient row (64 fp32 accumulator columns of this thread's TMEM lane) scaled, packed to bf16 and stored.
+__device__ __forceinline__ void bwd_store_row(uint32_t taddr, __nv_bfloat16* drow, float osc, bool store) {
+  uint32_t r0[32], r1[32];
+  tmem_ld32(taddr, r0);
+  tmem_ld32(taddr + 32, r1);
+  tmem_ld_wait();
+  if (store) {
+#pragma unroll
+    for (int g4 = 0; g4 < 8; ++g4) {
+      uint4 o;
+      __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int e = (g4 & 3) * 8 + 2 * j;
+        o2[j] = __floats2bfloat162_rn(__uint_as_float(g4 < 4 ? r0[e] : r1[e]) * osc, __uint_as_float(g4 < 4 ? r0[e + 1] : r1[e + 1]) * osc);
+      }
+      reinterpret_cast<uint4*>(drow)[g4] = o;
+    }
+  }
+}
 
 __global__ void __launch_bounds__(kBwdShortThreads, 1)
 attn_bwd_short_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                       const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
-                      const AttnArgs p, const int num_items) {
+                      const AttnArgs p, const int num_items, const int ablate) {
+  // `ablate` (0 in production) switches parts of the work off while keeping every barrier hand-shake, so that a timing run
+  // can tell which role bounds the item rate (results are then meaningless):
+  //   1 no P / dS math   2 no gradient read-out   4 no gradient MMAs   8 no S / dP MMAs   16 no TMA loads
+  //   32 no P / dS shared-memory stores   64 no dropout masks
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sSlots = smem;
   uint8_t* sP = smem + kBwdSlots * kBwdSlotBytes;
   uint8_t* sDS = sP + kPBytes;
   uint64_t* bars = reinterpret_cast<uint64_t*>(sDS + kPBytes);
-  uint64_t* slot_full = bars;        // [2]
-  uint64_t* slot_empty = bars + 2;   // [2]
-  uint64_t* sdp_full = bars + 4;
-  uint64_t* sdp_empty = bars + 5;
-  uint64_t* pds_full = bars + 6;
-  uint64_t* grads_full = bars + 7;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  uint64_t* slot_full = bars;        // [2] TMA -> MMA
+  uint64_t* slot_empty = bars + 2;   // [2] gradient MMAs done -> TMA
+  uint64_t* sdp_full = bars + 4;     // [2] S / dP ready -> math group
+  uint64_t* set_free = bars + 6;     // [2] gradients read out -> MMA may overwrite the set
+  uint64_t* grads_full = bars + 8;   // [2] gradient MMAs done -> epilogue group
+  uint64_t* pds_full = bars + 10;    // P / dS staged -> MMA
+  uint64_t* pds_free = bars + 11;    // gradient MMAs done -> math group may overwrite P / dS
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
   volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   zero_tail_bwd(p);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
-    for (int i = 0; i < 2; ++i) { mbar_init(&slot_full[i], 1); mbar_init(&slot_empty[i], 1); }
-    mbar_init(sdp_full, 1);
-    mbar_init(sdp_empty, 128);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&slot_full[i], 1);
+      mbar_init(&slot_empty[i], 1);
+      mbar_init(&sdp_full[i], 1);
+      mbar_init(&set_free[i], 128);
+      mbar_init(&grads_full[i], 1);
+    }
     mbar_init(pds_full, 128);
-    mbar_init(grads_full, 1);
+    mbar_init(pds_free, 1);
     *abort_word = 0;
     mbar_fence_init();
   }
-  if (warp == 5) tmem_alloc(tmem_slot, 512);
+  if (warp == 9) tmem_alloc(tmem_slot, 512);
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tS = tmem_base, tDP = tmem_base + 128, tDQ = tmem_base + 256, tDK = tmem_base + 320,
-                 tDV = tmem_base + 384;
 
-  if (warp == 4) {
+  if (warp == 8) {
     if (lane == 0) {
       int it = 0;
       for (int item = blockIdx.x; item < num_items; item += gridDim.x) {
@@ -348,69 +478,199 @@ attn_bwd_short_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
         const int slot = it & 1;
         if (!mbar_wait(&slot_empty[slot], ((it >> 1) & 1) ^ 1, abort_word, p.status, kTimeoutSmemEmpty)) break;
         uint8_t* s = sSlots + slot * kBwdSlotBytes;
+        if (ablate & 16) {
+          mbar_arrive(&slot_full[slot]);
+          ++it;
+          continue;
+        }
         mbar_expect_tx(&slot_full[slot], kBwdSlotBytes);
         tma_load_2d(s, &tmap_q, &slot_full[slot], w.h * kHd, w.q0);
         tma_load_2d(s + kTileBytes, &tmap_k, &slot_full[slot], w.h * kHd, w.k0);
-        tma_load_2d(s + 2 * kTileBytes, &tmap_v, &slot_full[slot], w.h * kHd, w.k0);
         tma_load_2d(s + 3 * kTileBytes, &tmap_do, &slot_full[slot], w.h * kHd, w.q0);
+        tma_load_2d(s + 2 * kTileBytes, &tmap_v, &slot_full[slot], w.h * kHd, w.k0);
         ++it;
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == 9) {
     if (lane == 0) {
       const uint32_t idesc_s = make_idesc_bf16(kTile, kTile, 0, 0);
       const uint32_t idesc_dq = make_idesc_bf16(kTile, kHd, 0, 1);
       const uint32_t idesc_dkv = make_idesc_bf16(kTile, kHd, 1, 1);
-      int it = 0;
-      bool have_prev = false, ok = true;
-      int prev_it = 0, prev_q = 0, prev_k = 0;
-      auto issue_grads = [&](int j, int q_len, int k_len) -> bool {
-        const int slot = j & 1;
-        if (!mbar_wait(pds_full, j & 1, abort_word, p.status, kTimeoutTmemEmpty)) return false;
-        tc_fence_after_sync();
-        const uint32_t base = smem_u32(sSlots + slot * kBwdSlotBytes);
-        const uint32_t qa = base, ka = base + kTileBytes, doa = base + 3 * kTileBytes;
-        const uint32_t pa = smem_u32(sP), dsa = smem_u32(sDS);
-        const int nkq = (q_len + 15) >> 4, nkk = (k_len + 15) >> 4;
-        // dV = P^T dO, dK = dS^T Q : A read MN-major (keys = M, two 64-key slabs), reduction over query rows
-        umma_steps(tDV, pa, kTileBytes, 2048, doa, 8192, 2048, idesc_dkv, nkq, false);
-        umma_steps(tDK, dsa, kTileBytes, 2048, qa, 8192, 2048, idesc_dkv, nkq, false);
-        // dQ = dS K : A K-major (slab per 64 keys), B = K tile MN-major, reduction over keys
-        for (int k = 0; k < nkk; ++k) {
-          const uint64_t ad = make_smem_desc_sw128(dsa + (k >> 2) * kTileBytes + (k & 3) * 32, 16, 1024);
-          const uint64_t bd = make_smem_desc_sw128(ka + k * 2048, 8192, 1024);
-          umma_bf16(tDQ, ad, bd, idesc_dq, k > 0 ? 1u : 0u);
+      // Two queues served in whichever order their inputs arrive: S / dP of item s_it (needs its tiles and a free TMEM
+      // set) and the gradients of item g_it (needs P / dS).  Blocking on one would hold back the other: the tiles of item
+      // i + 1 land about a TMA round trip after the gradients of item i - 1 completed.
+      int s_it = 0, g_it = 0;
+      unsigned long long lens = 0;   // (q_len, k_len) bytes of items g_it .. s_it (at most three alive), 16 bits per item
+      int item = blockIdx.x;
+      auto next_valid = [&]() {
+        while (item < num_items) {
+          const Item w = get_item(p, item);
+          if (w.valid) {
+            const int sh = (s_it & 3) * 16;
+            lens = (lens & ~(0xFFFFull << sh)) | (static_cast<unsigned long long>((w.q_len << 8) | w.k_len) << sh);
+            return true;
+          }
+          item += gridDim.x;
         }
-        umma_commit(grads_full);
-        umma_commit(&slot_empty[slot]);
-        return true;
+        return false;
       };
-      for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
-        const Item w = get_item(p, item);
-        if (!w.valid) continue;
-        const int slot = it & 1;
-        if (!mbar_wait(&slot_full[slot], (it >> 1) & 1, abort_word, p.status, kTimeoutTmaFull)) { ok = false; break; }
-        if (!mbar_wait(sdp_empty, (it & 1) ^ 1, abort_word, p.status, kTimeoutTmemEmpty)) { ok = false; break; }
-        tc_fence_after_sync();
-        const uint32_t base = smem_u32(sSlots + slot * kBwdSlotBytes);
-        umma_steps(tS, base, 16, 32, base + kTileBytes, 16, 32, idesc_s, kHd / 16, false);                       // Q K^T
-        umma_steps(tDP, base + 3 * kTileBytes, 16, 32, base + 2 * kTileBytes, 16, 32, idesc_s, kHd / 16, false);  // dO V^T
-        umma_commit(sdp_full);
-        if (have_prev) ok = issue_grads(prev_it, prev_q, prev_k);
-        have_prev = true;
-        prev_it = it;
-        prev_q = w.q_len;
-        prev_k = w.k_len;
-        ++it;
+      bool more = next_valid();
+      uint32_t idle = 0;
+      while (more || g_it < s_it) {
+        bool progressed = false;
+        if (g_it < s_it && mbar_try_wait(pds_full, g_it & 1)) {
+          tc_fence_after_sync();
+          const int s = g_it & 1;
+          const uint32_t set = tmem_base + s * 256;
+          const uint32_t base = smem_u32(sSlots + s * kBwdSlotBytes);
+          const uint32_t qa = base, ka = base + kTileBytes, doa = base + 3 * kTileBytes;
+          const uint32_t pa = smem_u32(sP), dsa = smem_u32(sDS);
+          const uint32_t lw = static_cast<uint32_t>(lens >> ((g_it & 3) * 16)) & 0xFFFFu;
+          const int nkq = ((lw >> 8) + 15) >> 4, nkk = ((lw & 0xFFu) + 15) >> 4;
+          // dV = P^T dO, dK = dS^T Q : A read MN-major (keys = M, two 64-key slabs), reduction over query rows
+          if (!(ablate & 4)) {
+            umma_steps(set, pa, kTileBytes, 2048, doa, 8192, 2048, idesc_dkv, nkq, false);
+            umma_steps(set + 128, dsa, kTileBytes, 2048, qa, 8192, 2048, idesc_dkv, nkq, false);
+          }
+          // dQ = dS K : A K-major (slab per 64 keys), B = K tile MN-major, reduction over keys
+          for (int k = 0; k < ((ablate & 4) ? 0 : nkk); ++k) {
+            const uint64_t ad = make_smem_desc_sw128(dsa + (k >> 2) * kTileBytes + (k & 3) * 32, 16, 1024);
+            const uint64_t bd = make_smem_desc_sw128(ka + k * 2048, 8192, 1024);
+            umma_bf16(set + 64, ad, bd, idesc_dq, k > 0 ? 1u : 0u);
+          }
+          umma_commit(pds_free);
+          umma_commit(&grads_full[s]);
+          umma_commit(&slot_empty[s]);
+          ++g_it;
+          progressed = true;
+        }
+        if (more && s_it - g_it < 2 && mbar_try_wait(&slot_full[s_it & 1], (s_it >> 1) & 1) &&
+            mbar_try_wait(&set_free[s_it & 1], ((s_it >> 1) & 1) ^ 1)) {
+          tc_fence_after_sync();
+          const int s = s_it & 1;
+          const uint32_t set = tmem_base + s * 256;
+          const uint32_t base = smem_u32(sSlots + s * kBwdSlotBytes);
+          if (!(ablate & 8)) {
+            umma_steps(set, base, 16, 32, base + kTileBytes, 16, 32, idesc_s, kHd / 16, false);                              // Q K^T
+            umma_steps(set + 128, base + 3 * kTileBytes, 16, 32, base + 2 * kTileBytes, 16, 32, idesc_s, kHd / 16, false);   // dO V^T
+          }
+          umma_commit(&sdp_full[s]);
+          ++s_it;
+          item += gridDim.x;
+          more = next_valid();
+          progressed = true;
+        }
+        if (progressed) {
+          idle = 0;
+        } else {
+          if (++idle > 64) {
+            if (*abort_word) break;
+            if (idle > kBwdIssuePolls) {
+              *abort_word = 1;
+              if (p.status) atomicCAS(p.status, 0, static_cast<int>(kTimeoutTmemEmpty));
+              break;
+            }
+            __nanosleep(idle > 4096 ? 256 : 32);
+          }
+        }
       }
-      if (ok && have_prev) issue_grads(prev_it, prev_q, prev_k);
     }
   } else if (warp < 4) {
+    // ---- math group: P, D and dS of every item --------------------------------------------------------------------
     const int t = warp * 32 + lane;
     const uint32_t lane_sel = static_cast<uint32_t>(warp * 32) << 16;
     const float scale_log2 = p.scale * 1.4426950408889634f;
-    const bool do_drop = p.dropout_p > 0.f;
+    const bool do_drop = p.dropout_p > 0.f && !(ablate & 64);
     const unsigned long long seed = p.seed + ((do_drop && p.seed_dev) ? *p.seed_dev : 0ull);
+    const float kInf = __int_as_float(0x7f800000);
+    int it = 0;
+    int item = blockIdx.x;
+    Item nxt = item < num_items ? get_item(p, item) : Item{};
+    float lse_nxt = (nxt.valid && t < nxt.q_len) ? p.lse[static_cast<size_t>(nxt.h) * p.lse_stride + nxt.q0 + t] : 0.f;
+    while (item < num_items) {
+      const Item w = nxt;
+      const float lse = lse_nxt;
+      item += gridDim.x;
+      if (item < num_items) {   // the next item's descriptor and log-sum-exp are fetched under this item's work
+        nxt = get_item(p, item);
+        if (nxt.valid && t < nxt.q_len) lse_nxt = p.lse[static_cast<size_t>(nxt.h) * p.lse_stride + nxt.q0 + t];
+      }
+      if (!w.valid) continue;
+      const int s = it & 1;
+      const uint32_t set = tmem_base + s * 256 + lane_sel;
+      const bool row_ok = t < w.q_len;
+      const float lse2 = row_ok ? lse * 1.4426950408889634f : kInf;
+      if (!__all_sync(0xffffffffu, mbar_wait(&sdp_full[s], (it >> 1) & 1, abort_word, p.status, kTimeoutTmemFull))) break;
+      tc_fence_after_sync();
+      const int nchunks = (w.k_len + 31) >> 5;
+      const int q_rows16 = ((w.q_len + 15) >> 4) << 4;   // rows the MN-major MMAs will read
+      const bool warp_writes = warp * 32 < q_rows16 && !(ablate & 1);
+      bool may_store = it == 0, ok = true;
+      if (warp_writes) {
+        const DropRng rng(seed, (p.stream_id << 16) | static_cast<unsigned long long>(w.h), p.dropout_p);
+        const unsigned long long row_base = static_cast<unsigned long long>(w.q0 + t) * p.kstride;
+        const int passes = nchunks > 2 ? 2 : 1;   // up to 64 keys: one round holds the whole row, D needs no second pass
+        float Dacc = 0.f;
+#pragma unroll 1
+        for (int pass = 0; pass < passes && ok; ++pass) {
+          const bool emit = pass == passes - 1;
+#pragma unroll 1
+          for (int c0 = 0; c0 < nchunks; c0 += 2) {
+            const bool two = c0 + 1 < nchunks;
+            uint32_t rs0[32], rd0[32], rs1[32], rd1[32];
+            tmem_ld32(set + c0 * 32, rs0);
+            tmem_ld32(set + 128 + c0 * 32, rd0);
+            if (two) {
+              tmem_ld32(set + (c0 + 1) * 32, rs1);
+              tmem_ld32(set + 128 + (c0 + 1) * 32, rd1);
+            }
+            uint32_t km0 = 0xffffffffu, km1 = 0xffffffffu;
+            if (do_drop) {   // the mask words are hashed while the TMEM loads are in flight
+              km0 = drop_mask32(rng, row_base + c0 * 32);
+              if (two) km1 = drop_mask32(rng, row_base + (c0 + 1) * 32);
+            }
+            tmem_ld_wait();
+            bwd_probs32(rs0, c0, t, w.k_len, p.causal != 0, scale_log2, lse2);
+            if (two) bwd_probs32(rs1, c0 + 1, t, w.k_len, p.causal != 0, scale_log2, lse2);
+            if (pass == 0) {
+              Dacc += bwd_dsum32(rs0, rd0, km0, do_drop);
+              if (two) Dacc += bwd_dsum32(rs1, rd1, km1, do_drop);
+            }
+            if (emit) {
+              if (!may_store) {   // the gradient MMAs of the previous item still read the staging tiles
+                ok = mbar_wait(pds_free, (it - 1) & 1, abort_word, p.status, kTimeoutSmemEmpty);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                may_store = true;
+              }
+              const float Drow = Dacc * rng.scale;
+              if (!(ablate & 32)) {
+                bwd_emit32(rs0, rd0, km0, do_drop, rng.scale, Drow, c0, t, sP, sDS);
+                if (two) bwd_emit32(rs1, rd1, km1, do_drop, rng.scale, Drow, c0 + 1, t, sP, sDS);
+              } else if (Drow == 12345.678f) {
+                sP[t] = static_cast<uint8_t>(rs0[0] + rd0[1] + rs1[2] + rd1[3]);   // keeps the math alive
+              }
+            }
+          }
+        }
+      }
+      if (ok && !may_store) {
+        // A warp with no rows to write must not run ahead either: S / dP are double-buffered, so without this wait it could
+        // reach its arrival for the NEXT item while the other warps still write this one, and complete the phase early.
+        // pds_free(it - 1) implies that phase it - 1 of pds_full is complete.
+        ok = __all_sync(0xffffffffu, mbar_wait(pds_free, (it - 1) & 1, abort_word, p.status, kTimeoutSmemEmpty));
+      }
+      if (!ok) break;
+      tc_fence_before_sync();
+      fence_async_smem();
+      mbar_arrive(pds_full);
+      ++it;
+    }
+  } else if (warp < 8) {
+    // ---- epilogue group: dQ row t (queries), dK / dV row t (keys) of every item ----------------------------------------
+    const int wq = warp - 4;
+    const int t = wq * 32 + lane;
+    const uint32_t lane_sel = static_cast<uint32_t>(wq * 32) << 16;
     int it = 0;
     int item = blockIdx.x;
     Item nxt = item < num_items ? get_item(p, item) : Item{};
@@ -419,153 +679,27 @@ attn_bwd_short_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
       item += gridDim.x;
       if (item < num_items) nxt = get_item(p, item);
       if (!w.valid) continue;
-      const uint32_t ph = it & 1;
+      const int s = it & 1;
+      const uint32_t set = tmem_base + s * 256 + lane_sel;
+      if (!__all_sync(0xffffffffu, mbar_wait(&grads_full[s], (it >> 1) & 1, abort_word, p.status, kTimeoutTmemFull))) break;
+      tc_fence_after_sync();
+      const size_t col = static_cast<size_t>(w.h) * kHd;
+      if (ablate & 2) {
+        tc_fence_before_sync();
+        mbar_arrive(&set_free[s]);
+        ++it;
+        continue;
+      }
+      if (wq * 32 < w.q_len)
+        bwd_store_row(set + 64, p.dq + static_cast<size_t>(w.q0 + t) * p.ld_dq + col, p.scale, t < w.q_len);
+      if (wq * 32 < w.k_len) {
+        // dK carries the softmax scale that dS left out
+        bwd_store_row(set + 128, p.dk + static_cast<size_t>(w.k0 + t) * p.ld_dk + col, p.scale, t < w.k_len);
+        bwd_store_row(set, p.dv + static_cast<size_t>(w.k0 + t) * p.ld_dv + col, 1.f, t < w.k_len);
+      }
+      tc_fence_before_sync();
+      mbar_arrive(&set_free[s]);
       ++it;
-      const bool row_ok = t < w.q_len;
-      float Drow = 0.f, lse = 0.f;
-      if (row_ok) {   // overlaps the S / dP MMAs
-        const uint4* orow = reinterpret_cast<const uint4*>(p.o + static_cast<size_t>(w.q0 + t) * p.ld_o + w.h * kHd);
-        const uint4* drow = reinterpret_cast<const uint4*>(p.d_o + static_cast<size_t>(w.q0 + t) * p.ld_do + w.h * kHd);
-        uint4 a[8], d[8];
-#pragma unroll
-        for (int g4 = 0; g4 < 8; ++g4) { a[g4] = orow[g4]; d[g4] = drow[g4]; }
-        lse = p.lse[static_cast<size_t>(w.h) * p.lse_stride + w.q0 + t];
-#pragma unroll
-        for (int g4 = 0; g4 < 8; ++g4) {
-          const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&a[g4]);
-          const __nv_bfloat162* d2 = reinterpret_cast<const __nv_bfloat162*>(&d[g4]);
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            float2 x = __bfloat1622float2(a2[j]), y = __bfloat1622float2(d2[j]);
-            Drow += x.x * y.x + x.y * y.y;
-          }
-        }
-      }
-      const float lse2 = row_ok ? lse * 1.4426950408889634f : __int_as_float(0x7f800000);
-      if (!mbar_wait(sdp_full, ph, abort_word, p.status, kTimeoutTmemFull)) break;
-      tc_fence_after_sync();
-      const int nchunks = (w.k_len + 31) >> 5;
-      const int q_rows16 = ((w.q_len + 15) >> 4) << 4;   // rows the MN-major MMAs will read
-      const bool warp_writes = warp * 32 < q_rows16;
-      if (warp_writes) {
-        const DropRng rng(seed, (p.stream_id << 16) | static_cast<unsigned long long>(w.h), p.dropout_p);
-#pragma unroll 1
-        for (int c0 = 0; c0 < nchunks; c0 += 2) {
-          uint32_t rs0[32], rd0[32], rs1[32], rd1[32];
-          tmem_ld32(tS + lane_sel + c0 * 32, rs0);
-          tmem_ld32(tDP + lane_sel + c0 * 32, rd0);
-          if (c0 + 1 < nchunks) {
-            tmem_ld32(tS + lane_sel + (c0 + 1) * 32, rs1);
-            tmem_ld32(tDP + lane_sel + (c0 + 1) * 32, rd1);
-          }
-          tmem_ld_wait();
-#pragma unroll
-          for (int half = 0; half < 2; ++half) {
-            const int c = c0 + half;
-            if (c >= nchunks) break;
-            // P = 2^(S * scale * log2 e - lse * log2 e); a row past the sequence has lse2 = +inf, so its P is 0 without a
-            // per-element test; dS is kept without the softmax scale (applied when dQ / dK leave TMEM).  A chunk whose 32
-            // key columns all exist (and no causal mask) takes the branch without per-element masks.
-            float pd[32], ds[32];
-            const bool chunk_full = !p.causal && (c + 1) * 32 <= w.k_len;
-            if (chunk_full && !do_drop) {
-#pragma unroll
-              for (int j = 0; j < 32; ++j) {
-                const float sv = __uint_as_float(half == 0 ? rs0[j] : rs1[j]);
-                const float dv = __uint_as_float(half == 0 ? rd0[j] : rd1[j]);
-                pd[j] = ex2_approx(fmaf(sv, scale_log2, -lse2));
-                ds[j] = pd[j] * (dv - Drow);
-              }
-            } else {
-              float kf[32];
-#pragma unroll
-              for (int j = 0; j < 32; ++j) kf[j] = 1.f;
-              if (do_drop) apply_dropout32(rng, static_cast<unsigned long long>(w.q0 + t) * p.kstride + c * 32, kf);
-#pragma unroll
-              for (int j = 0; j < 32; ++j) {
-                const int col = c * 32 + j;
-                const bool valid = chunk_full || (col < w.k_len && (!p.causal || col <= t));
-                const float sv = __uint_as_float(half == 0 ? rs0[j] : rs1[j]);
-                const float dv = __uint_as_float(half == 0 ? rd0[j] : rd1[j]);
-                const float pr = valid ? ex2_approx(fmaf(sv, scale_log2, -lse2)) : 0.f;
-                pd[j] = pr * kf[j];
-                ds[j] = pr * (dv * kf[j] - Drow);
-              }
-            }
-#pragma unroll
-            for (int g4 = 0; g4 < 4; ++g4) {
-              uint4 o1, o2v;
-              __nv_bfloat162* a2 = reinterpret_cast<__nv_bfloat162*>(&o1);
-              __nv_bfloat162* b2 = reinterpret_cast<__nv_bfloat162*>(&o2v);
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                a2[j] = __floats2bfloat162_rn(pd[g4 * 8 + 2 * j], pd[g4 * 8 + 2 * j + 1]);
-                b2[j] = __floats2bfloat162_rn(ds[g4 * 8 + 2 * j], ds[g4 * 8 + 2 * j + 1]);
-              }
-              const int chunk = c * 4 + g4;
-              const uint32_t off = (chunk >> 3) * kTileBytes + sw128_offset(t, chunk & 7);
-              *reinterpret_cast<uint4*>(sP + off) = o1;
-              *reinterpret_cast<uint4*>(sDS + off) = o2v;
-            }
-          }
-        }
-      }
-      tc_fence_before_sync();
-      fence_async_smem();
-      mbar_arrive(pds_full);
-      mbar_arrive(sdp_empty);
-      if (!mbar_wait(grads_full, ph, abort_word, p.status, kTimeoutTmemFull)) break;
-      tc_fence_after_sync();
-      // dQ row t (queries), dK / dV row t (keys): all TMEM loads of a row are issued before one wait
-      const bool q_warp = warp * 32 < w.q_len, k_warp = warp * 32 < w.k_len;
-      if (q_warp) {
-        uint32_t r0[32], r1[32];
-        tmem_ld32(tDQ + lane_sel, r0);
-        tmem_ld32(tDQ + lane_sel + 32, r1);
-        tmem_ld_wait();
-        if (row_ok) {
-          __nv_bfloat16* drow = p.dq + static_cast<size_t>(w.q0 + t) * p.ld_dq + w.h * kHd;
-#pragma unroll
-          for (int g4 = 0; g4 < 8; ++g4) {
-            uint4 o;
-            __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const int e = (g4 & 3) * 8 + 2 * j;
-              o2[j] = __floats2bfloat162_rn(__uint_as_float(g4 < 4 ? r0[e] : r1[e]) * p.scale, __uint_as_float(g4 < 4 ? r0[e + 1] : r1[e + 1]) * p.scale);
-            }
-            reinterpret_cast<uint4*>(drow)[g4] = o;
-          }
-        }
-      }
-      if (k_warp) {
-#pragma unroll 1
-        for (int which = 0; which < 2; ++which) {
-          __nv_bfloat16* dst = which == 0 ? p.dk : p.dv;
-          const int ld = which == 0 ? p.ld_dk : p.ld_dv;
-          const uint32_t tsrc = which == 0 ? tDK : tDV;
-          const float osc = which == 0 ? p.scale : 1.f;      // dK carries the softmax scale that dS left out
-          uint32_t r0[32], r1[32];
-          tmem_ld32(tsrc + lane_sel, r0);
-          tmem_ld32(tsrc + lane_sel + 32, r1);
-          tmem_ld_wait();
-          if (t < w.k_len) {
-            __nv_bfloat16* drow = dst + static_cast<size_t>(w.k0 + t) * ld + w.h * kHd;
-#pragma unroll
-            for (int g4 = 0; g4 < 8; ++g4) {
-              uint4 o;
-              __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                const int e = (g4 & 3) * 8 + 2 * j;
-                o2[j] = __floats2bfloat162_rn(__uint_as_float(g4 < 4 ? r0[e] : r1[e]) * osc, __uint_as_float(g4 < 4 ? r0[e + 1] : r1[e + 1]) * osc);
-              }
-              reinterpret_cast<uint4*>(drow)[g4] = o;
-            }
-          }
-        }
-      }
-      tc_fence_before_sync();
     }
   }
 
@@ -575,11 +709,14 @@ attn_bwd_short_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
     for (int i = 0; i < 2000; ++i) __nanosleep(1000);
     __syncthreads();
   }
-  if (warp == 5) {
+  if (warp == 9) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, 512);
   }
 }
+
+static int g_attn_bwd_ablate = 0;
+void set_attn_bwd_ablation(int bits) { g_attn_bwd_ablate = bits; }
 
 const char* launch_attn_fwd_short(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttnArgs& a,
                                   int num_items, cudaStream_t stream) {
@@ -604,9 +741,13 @@ const char* launch_attn_bwd_short(const CUtensorMap& tq, const CUtensorMap& tk, 
     configured = true;
   }
   const int grid = num_items < num_sms() ? num_items : num_sms();
-  attn_bwd_short_kernel<<<grid, kBwdShortThreads, kBwdShortSmem, stream>>>(tq, tk, tv, tdo, a, num_items);
+  attn_bwd_short_kernel<<<grid, kBwdShortThreads, kBwdShortSmem, stream>>>(tq, tk, tv, tdo, a, num_items, g_attn_bwd_ablate);
   cudaError_t ce = cudaGetLastError();
   return ce == cudaSuccess ? nullptr : cudaGetErrorString(ce);
 }
 
 }  // namespace b200
+
+NMTG_BOUNDS_READER(nmtg_bounds_attention_short)
+
+void nmtg_set_attn_bwd_ablation(int bits) { b200::set_attn_bwd_ablation(bits); }

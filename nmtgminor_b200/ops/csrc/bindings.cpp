@@ -194,6 +194,16 @@ Tensor dropout_add(const Tensor& x, const OptTensor& residual, double p, int64_t
   return y;
 }
 
+Tensor act_backward(const Tensor& dy, const Tensor& z, int64_t act, double p, int64_t seed, int64_t stream_id) {
+  need_bf16(dy, "dy"); need_bf16(z, "z");
+  TORCH_CHECK(dy.is_contiguous() && z.is_contiguous() && dy.numel() == z.numel());
+  c10::cuda::CUDAGuard guard(dy.device());
+  Tensor dz = torch::empty_like(dy);
+  ck(nmtg_act_backward(dy.data_ptr(), z.data_ptr(), dz.data_ptr(), dy.numel(), static_cast<int>(act), static_cast<float>(p),
+                       static_cast<unsigned long long>(seed), static_cast<unsigned long long>(stream_id), seed_ptr(dy), cur_stream()));
+  return dz;
+}
+
 Tensor dropout_colsum(const Tensor& x, double p, int64_t seed, int64_t stream_id, Tensor& colsum) {
   need_bf16(x, "x"); need_f32(colsum, "colsum");
   TORCH_CHECK(x.dim() == 2 && x.is_contiguous() && colsum.is_contiguous() && colsum.numel() >= x.size(1));
@@ -249,6 +259,26 @@ void sq_norm(const Tensor& g, Tensor& out_sq, Tensor& nonfinite) {
   TORCH_CHECK(g.is_contiguous() && nonfinite.scalar_type() == at::kInt && nonfinite.is_cuda());
   c10::cuda::CUDAGuard guard(g.device());
   ck(nmtg_sq_norm(g.data_ptr<float>(), g.numel(), out_sq.data_ptr<float>(), nonfinite.data_ptr<int>(), cur_stream()));
+}
+
+void loss_scale_prepare(Tensor& hyper, const Tensor& state) {
+  need_f32(state, "state");
+  TORCH_CHECK(hyper.is_cuda() && state.is_cuda() && state.numel() >= 4 && hyper.numel() * hyper.element_size() >= sizeof(NmtgAdamHyper));
+  c10::cuda::CUDAGuard guard(state.device());
+  ck(nmtg_loss_scale_prepare(reinterpret_cast<NmtgAdamHyper*>(hyper.data_ptr()), state.data_ptr<float>(), cur_stream()));
+}
+
+void loss_scale_update(Tensor& state, const OptTensor& nonfinite, const OptTensor& norm, int64_t interval, double growth,
+                       double backoff, double min_scale, double max_scale) {
+  need_f32(state, "state");
+  TORCH_CHECK(state.is_cuda() && state.numel() >= 4);
+  if (nonfinite.has_value()) TORCH_CHECK(nonfinite->scalar_type() == at::kInt && nonfinite->is_cuda());
+  if (norm.has_value()) need_f32(*norm, "norm");
+  c10::cuda::CUDAGuard guard(state.device());
+  ck(nmtg_loss_scale_update(state.data_ptr<float>(), nonfinite.has_value() ? nonfinite->data_ptr<int>() : nullptr,
+                            norm.has_value() ? norm->data_ptr<float>() : nullptr, static_cast<int>(interval),
+                            static_cast<float>(growth), static_cast<float>(backoff), static_cast<float>(min_scale),
+                            static_cast<float>(max_scale), cur_stream()));
 }
 
 void adamw_flat(Tensor& master, const OptTensor& work, Tensor& grad, Tensor& m, Tensor& v, const Tensor& hyper,
@@ -472,6 +502,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         pybind11::arg("allow_split_k"), pybind11::arg("split_k"), pybind11::arg("force_bn"), pybind11::arg("mask") = pybind11::none(),
         pybind11::arg("colsum") = pybind11::none(), pybind11::arg("gather") = pybind11::none());
   m.def("set_gemm_variant", [](int64_t v) { nmtg_set_gemm_variant(static_cast<int>(v)); });
+  m.def("set_attn_bwd_ablation", [](int64_t v) { nmtg_set_attn_bwd_ablation(static_cast<int>(v)); });
   m.def("set_gemm_trace", [](const OptTensor& buf) {
     if (buf.has_value()) {
       TORCH_CHECK(buf->is_cuda() && buf->scalar_type() == at::kLong && buf->is_contiguous() && buf->numel() >= 16 * 128);
@@ -484,12 +515,15 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("layernorm_bwd", &layernorm_bwd);
   m.def("xent_fused", &xent_fused);
   m.def("dropout_add", &dropout_add);
+  m.def("act_backward", &act_backward);
   m.def("dropout_colsum", &dropout_colsum);
   m.def("embed_fwd", &embed_fwd);
   m.def("embed_bwd", &embed_bwd);
   m.def("colsum", &colsum);
   m.def("sq_norm", &sq_norm);
   m.def("adamw_flat", &adamw_flat);
+  m.def("loss_scale_prepare", &loss_scale_prepare);
+  m.def("loss_scale_update", &loss_scale_update);
   m.def("cast_f32_bf16", &cast_f32_bf16);
   m.def("attn_fwd", &attn_fwd);
   m.def("attn_bwd", &attn_bwd);

@@ -200,7 +200,7 @@ void gather_rows(const Tensor& src, Tensor& dst, const Tensor& index, int64_t co
   const long stride = src.numel() / src.size(0) * src.element_size();
   const long copy = copy_elems < 0 ? stride : copy_elems * src.element_size();
   ck(nmtg_gather_rows(src.data_ptr(), dst.data_ptr(), reinterpret_cast<const long*>(index.data_ptr<int64_t>()),
-                      static_cast<int>(rows), stride, copy, dev_int(filled_dev, "filled_dev"), unit_elems * src.element_size(),
+                      static_cast<int>(rows), static_cast<int>(src.size(0)), stride, copy, dev_int(filled_dev, "filled_dev"), unit_elems * src.element_size(),
                       cur_stream()));
 }
 

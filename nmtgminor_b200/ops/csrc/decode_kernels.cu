@@ -7,6 +7,7 @@
 // onmt/inference/search.py:60-140 and the torch.cat caches of onmt/modules/optimized/self_attention_func.py:162-174.
 #include "b200_ptx.cuh"
 #include "seq_api.h"
+#include "bounds_check.cuh"
 
 namespace b200 {
 namespace {
@@ -225,7 +226,8 @@ __global__ void beam_merge_kernel(const float* __restrict__ cand_val, const int*
 }
 
 __global__ void gather_rows_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, const long* __restrict__ index,
-                                   int rows, long stride16, long copy16, const int* __restrict__ filled_dev, long unit16) {
+                                   int rows, int src_rows, long stride16, long copy16, const int* __restrict__ filled_dev,
+                                   long unit16) {
   // filled_dev (optional): number of `unit16`-sized units at the start of every row that hold data, read on the
   // device so that a captured graph copies the right amount at every replay
   if (filled_dev) {
@@ -237,7 +239,8 @@ __global__ void gather_rows_kernel(const uint4* __restrict__ src, uint4* __restr
   for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < total;
        i += static_cast<long>(gridDim.x) * blockDim.x) {
     const long r = i / copy16, c = i % copy16;
-    dst[r * stride16 + c] = src[index[r] * stride16 + c];
+    const long from = checked_range(static_cast<long>(index[r]), 0L, static_cast<long>(src_rows) - 1);
+    dst[r * stride16 + c] = src[from * stride16 + c];
   }
 }
 
@@ -245,7 +248,10 @@ __global__ void cache_append_kernel(const __nv_bfloat16* __restrict__ k_new, con
                                     __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache, int R, int hid,
                                     int cap, int pos, const int* __restrict__ pos_dev) {
   if (pos_dev) pos = *pos_dev;
-  if (pos < 0 || pos >= cap) return;
+  if (pos < 0 || pos >= cap) {
+    if (blockIdx.x == 0 && threadIdx.x == 0) NMTG_BOUNDS_HIT();
+    return;
+  }
   const int n16 = hid >> 3;
   const long total = static_cast<long>(R) * n16;
   for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < total;
@@ -390,13 +396,14 @@ const char* nmtg_beam_topk(const void* logits, long ld, int dtype, const float* 
   return launch_err();
 }
 
-const char* nmtg_gather_rows(const void* src, void* dst, const long* index, int rows, long row_stride_bytes,
+const char* nmtg_gather_rows(const void* src, void* dst, const long* index, int rows, int src_rows, long row_stride_bytes,
                              long copy_bytes, const int* filled_dev, long unit_bytes, cudaStream_t stream) {
   if (filled_dev) {
     if (unit_bytes <= 0 || (unit_bytes % 16)) return "gather_rows: unit size must be a positive multiple of 16 bytes";
     copy_bytes = row_stride_bytes;       // grid sized for the worst case; the kernel reads the real amount
   }
   if (rows <= 0 || copy_bytes <= 0) return nullptr;
+  if (src_rows <= 0) return "gather_rows: the source has no rows";
   if ((row_stride_bytes % 16) || (copy_bytes % 16) || copy_bytes > row_stride_bytes)
     return "gather_rows: sizes must be multiples of 16 bytes with copy <= stride";
   if ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15) return "gather_rows: unaligned pointer";
@@ -404,7 +411,7 @@ const char* nmtg_gather_rows(const void* src, void* dst, const long* index, int 
   long blocks = (total + 255) / 256;
   if (blocks > 148 * 8) blocks = 148 * 8;
   gather_rows_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(static_cast<const uint4*>(src), static_cast<uint4*>(dst),
-                                                                        index, rows, row_stride_bytes / 16, copy_bytes / 16,
+                                                                        index, rows, src_rows, row_stride_bytes / 16, copy_bytes / 16,
                                                                         filled_dev, unit_bytes / 16);
   return launch_err();
 }
@@ -446,3 +453,5 @@ const char* nmtg_cache_append(const void* k_new, const void* v_new, long ld, voi
 }
 
 }  // extern "C"
+
+NMTG_BOUNDS_READER(nmtg_bounds_decode)

@@ -11,6 +11,7 @@
 // dropout.h:21-160) and of the PyTorch embedding/position code in onmt/models/transformers.py:163-207.
 #include "b200_ptx.cuh"
 #include "ops_api.h"
+#include "bounds_check.cuh"
 
 namespace b200 {
 
@@ -18,12 +19,6 @@ int num_sms();
 
 // Debug build (-DNMTG_DEBUG_BOUNDS): out-of-range indices are counted (and still clamped, never trapped) so that a
 // test run can assert that no kernel ever saw one; the release build only clamps.
-#ifdef NMTG_DEBUG_BOUNDS
-__device__ unsigned int g_bounds_violations = 0;
-#define NMTG_BOUNDS_HIT() atomicAdd(&g_bounds_violations, 1u)
-#else
-#define NMTG_BOUNDS_HIT() ((void)0)
-#endif
 
 __device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
   const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
@@ -65,6 +60,43 @@ __global__ void dropout_add_kernel(const __nv_bfloat16* __restrict__ x, const __
       }
       reinterpret_cast<uint4*>(y)[2 * i + h] = pack8(f);
     }
+  }
+}
+
+// dz = dropout-mask(dy) * act'(z): backward of ``dropout(act(z))`` for a stand-alone Linear with an activation, one pass
+// (the mask is the one dropout_add / the GEMM epilogue drew for the same seed and stream).  One thread handles 8
+// consecutive elements (one 16-byte vector, two hash words).  act: 1 ReLU, 2 GELU (erf), 3 SiLU.
+__global__ void act_backward_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ z,
+                                    __nv_bfloat16* __restrict__ dz, long n8, int act, float p, unsigned long long seed,
+                                    unsigned long long stream_id, const unsigned long long* seed_dev) {
+  const bool drop = p > 0.f;
+  const DropRng rng(seed + ((drop && seed_dev) ? *seed_dev : 0ull), stream_id, p);
+  for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < n8;
+       i += static_cast<long>(gridDim.x) * blockDim.x) {
+    float g[8], a[8];
+    unpack8(reinterpret_cast<const uint4*>(dy)[i], g);
+    unpack8(reinterpret_cast<const uint4*>(z)[i], a);
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const uint32_t w = drop ? rng.word(static_cast<unsigned long long>(i) * 2 + h) : 0u;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int e = h * 4 + j;
+        const float x = a[e];
+        float d;
+        if (act == 1) {
+          d = x > 0.f ? 1.f : 0.f;
+        } else if (act == 2) {
+          d = 0.5f * (1.f + erff(x * 0.7071067811865476f)) + x * __expf(-0.5f * x * x) * 0.3989422804014327f;
+        } else {
+          const float sg = 1.f / (1.f + __expf(-x));
+          d = sg * (1.f + x * (1.f - sg));
+        }
+        const float v = drop ? (rng.keep(w, j) ? g[e] * rng.scale : 0.f) : g[e];
+        g[e] = v * d;
+      }
+    }
+    reinterpret_cast<uint4*>(dz)[i] = pack8(g);
   }
 }
 
@@ -279,6 +311,21 @@ const char* nmtg_dropout_add(const void* x, const void* residual, void* y, long 
   return last_err();
 }
 
+const char* nmtg_act_backward(const void* dy, const void* z, void* dz, long n, int act, float p, unsigned long long seed,
+                              unsigned long long stream_id, const unsigned long long* seed_dev, cudaStream_t stream) {
+  if (n <= 0) return nullptr;
+  if (n % 8) return "act_backward: element count must be a multiple of 8";
+  if (act < 1 || act > 3) return "act_backward: activation must be ReLU (1), GELU (2) or SiLU (3)";
+  const long n8 = n / 8;
+  long blocks = (n8 + 255) / 256;
+  const long cap = static_cast<long>(num_sms()) * 8;
+  if (blocks > cap) blocks = cap;
+  act_backward_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(
+      reinterpret_cast<const __nv_bfloat16*>(dy), reinterpret_cast<const __nv_bfloat16*>(z),
+      reinterpret_cast<__nv_bfloat16*>(dz), n8, act, p, seed, stream_id, seed_dev);
+  return last_err();
+}
+
 const char* nmtg_dropout_colsum(const void* x, void* y, float* colsum, int rows, int cols, float p, unsigned long long seed,
                                 unsigned long long stream_id, const unsigned long long* seed_dev, cudaStream_t stream) {
   if (rows <= 0 || cols <= 0) return nullptr;
@@ -351,13 +398,20 @@ const char* nmtg_colsum(const void* x, float* out, int rows, int cols, long ld, 
   return last_err();
 }
 
-// Number of out-of-range indices seen by the kernels of this file since load; -1 when the checks are compiled out.
+NMTG_BOUNDS_READER(nmtg_bounds_elementwise)
+extern "C" long nmtg_bounds_xentropy();
+extern "C" long nmtg_bounds_decode();
+extern "C" long nmtg_bounds_sequence();
+extern "C" long nmtg_bounds_attention_short();
+
+// Number of out-of-range indices corrected by the kernels of this library since load; -1 when the checks are compiled out.
 extern "C" long nmtg_bounds_violations() {
-#ifdef NMTG_DEBUG_BOUNDS
-  unsigned int v = 0;
-  if (cudaMemcpyFromSymbol(&v, b200::g_bounds_violations, sizeof(v)) != cudaSuccess) return -2;
-  return static_cast<long>(v);
-#else
-  return -1;
-#endif
+  long total = 0;
+  const long parts[] = {nmtg_bounds_elementwise(), nmtg_bounds_xentropy(), nmtg_bounds_decode(), nmtg_bounds_sequence(),
+                        nmtg_bounds_attention_short()};
+  for (long v : parts) {
+    if (v < 0) return v;
+    total += v;
+  }
+  return total;
 }

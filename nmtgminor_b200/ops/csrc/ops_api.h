@@ -59,6 +59,8 @@ struct GemmDesc {
 const char* nmtg_gemm_bf16(const GemmDesc* d, cudaStream_t stream);
 // 0 = automatic (CTA-pair kernel when M > 128), 1 = single-CTA kernel only, 2 = same as 0
 void nmtg_set_gemm_variant(int v);
+// Timing aid for the short-sequence attention backward: bit mask of work to leave out (see the kernel); 0 = everything.
+void nmtg_set_attn_bwd_ablation(int bits);
 // Profiling aid: device buffer of 16 int64 per CTA pair (at least 16 * #SMs / 2 entries) that the CTA-pair GEMM fills with
 // cycle counters of its MMA issuer and of one epilogue warp; nullptr switches it off.
 void nmtg_set_gemm_trace(long long* buf);
@@ -86,6 +88,9 @@ const char* nmtg_dropout_colsum(const void* x, void* y, float* colsum, int rows,
                                 unsigned long long stream_id, const unsigned long long* seed_dev, cudaStream_t stream);
 const char* nmtg_dropout_add(const void* x, const void* residual, void* y, long n, float p, unsigned long long seed,
                              unsigned long long stream_id, const unsigned long long* seed_dev, cudaStream_t stream);
+// dz = dropout-mask(dy) * act'(z) over n bf16 elements (n % 8 == 0); act 1 ReLU, 2 GELU, 3 SiLU; p = 0: no mask.
+const char* nmtg_act_backward(const void* dy, const void* z, void* dz, long n, int act, float p, unsigned long long seed,
+                              unsigned long long stream_id, const unsigned long long* seed_dev, cudaStream_t stream);
 // out[r] = dropout(table[tokens[r]] * scale + pos_table[positions[r]])  (pos_table / positions optional)
 const char* nmtg_embed_fwd(const int64_t* tokens, const int64_t* positions, const void* table, const void* pos_table,
                            void* out, int rows, int hidden, int vocab, int max_pos, float scale, float p,
@@ -115,6 +120,12 @@ const char* nmtg_adamw_flat(float* master, void* work_bf16, float* grad, float* 
                             const NmtgAdamHyper* hyper_dev, const float* grad_sq, const int* nonfinite,
                             cudaStream_t stream);
 const char* nmtg_cast_f32_bf16(const float* src, void* dst, long n, cudaStream_t stream);
+// Device-resident dynamic loss scale: state = {scale, clean steps, 1 / scale, skipped steps}.  prepare divides the
+// optimiser's gradient factor by the scale; update backs off after a skipped step (nonfinite flag set, or norm < 0) and
+// grows after `interval` clean ones.  Either of nonfinite / norm may be null.
+const char* nmtg_loss_scale_prepare(NmtgAdamHyper* hyper_dev, const float* state, cudaStream_t stream);
+const char* nmtg_loss_scale_update(float* state, const int* nonfinite, const float* norm, int interval, float growth,
+                                   float backoff, float min_scale, float max_scale, cudaStream_t stream);
 
 // Packed variable-length attention, head_dim 64.  q rows of sequence b are [cu_q[b], cu_q[b+1]) and its
 // key/value rows [cu_k[b], cu_k[b+1]); head h occupies columns [64h, 64h+64) of each tensor.

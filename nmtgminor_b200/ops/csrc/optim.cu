@@ -116,6 +116,38 @@ __global__ void cast_f32_bf16_kernel(const float* __restrict__ src, __nv_bfloat1
   }
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// Dynamic loss scale kept on the device, so that a captured step never asks the host.
+// state = { scale, clean steps since the last change, 1 / scale, skipped steps so far }
+// ---------------------------------------------------------------------------------------------------------
+// Before the update kernels: the gradients carry the loss scale, so the optimiser's gradient factor is divided by it.
+__global__ void loss_scale_prepare_kernel(NmtgAdamHyper* hyper, const float* state) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) hyper->grad_scale = hyper->grad_scale / state[0];
+}
+// After the update kernels: a skipped step (non-finite gradient somewhere: local flag, or the global norm reported as
+// negative by the sharded update) multiplies the scale by `backoff`; `interval` clean steps in a row multiply it by
+// `growth`.  The scale stays within [min_scale, max_scale].
+__global__ void loss_scale_update_kernel(float* state, const int* nonfinite, const float* norm, int interval, float growth,
+                                         float backoff, float min_scale, float max_scale) {
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  const bool skipped = (nonfinite && *nonfinite != 0) || (norm && !(*norm >= 0.f));
+  float scale = state[0], clean = state[1];
+  if (skipped) {
+    scale = fmaxf(scale * backoff, min_scale);
+    clean = 0.f;
+    state[3] += 1.f;
+  } else {
+    clean += 1.f;
+    if (clean >= static_cast<float>(interval)) {
+      scale = fminf(scale * growth, max_scale);
+      clean = 0.f;
+    }
+  }
+  state[0] = scale;
+  state[1] = clean;
+  state[2] = 1.f / scale;
+}
+
 }  // namespace b200
 
 using namespace b200;
@@ -155,5 +187,17 @@ const char* nmtg_cast_f32_bf16(const float* src, void* dst, long n, cudaStream_t
   const long cap = static_cast<long>(num_sms()) * 8;
   if (blocks > cap) blocks = cap;
   cast_f32_bf16_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(src, reinterpret_cast<__nv_bfloat16*>(dst), n);
+  return last_err2();
+}
+
+const char* nmtg_loss_scale_prepare(NmtgAdamHyper* hyper_dev, const float* state, cudaStream_t stream) {
+  loss_scale_prepare_kernel<<<1, 32, 0, stream>>>(hyper_dev, state);
+  return last_err2();
+}
+
+const char* nmtg_loss_scale_update(float* state, const int* nonfinite, const float* norm, int interval, float growth,
+                                   float backoff, float min_scale, float max_scale, cudaStream_t stream) {
+  if (interval < 1) return "loss scale: the growth interval must be at least 1";
+  loss_scale_update_kernel<<<1, 32, 0, stream>>>(state, nonfinite, norm, interval, growth, backoff, min_scale, max_scale);
   return last_err2();
 }

@@ -71,7 +71,7 @@ const char* nmtg_beam_topk(const void* logits, long ld, int dtype, const float* 
 // dst[r, 0:copy_bytes] = src[index[r], 0:copy_bytes] for rows `row_stride_bytes` apart (both multiples of 16).
 // filled_dev (optional device int): copy filled_dev[0] * unit_bytes per row instead of copy_bytes, so that a captured
 // CUDA graph moves the right amount at every replay.
-const char* nmtg_gather_rows(const void* src, void* dst, const long* index, int rows, long row_stride_bytes,
+const char* nmtg_gather_rows(const void* src, void* dst, const long* index, int rows, int src_rows, long row_stride_bytes,
                              long copy_bytes, const int* filled_dev, long unit_bytes, cudaStream_t stream);
 
 // ---- single-query attention over a preallocated cache ------------------------------------------------------

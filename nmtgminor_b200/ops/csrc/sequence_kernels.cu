@@ -12,6 +12,7 @@
 // multihead_attn/softmax_apex.h (softmax / dropout / masked variants).
 #include "b200_ptx.cuh"
 #include "seq_api.h"
+#include "bounds_check.cuh"
 
 namespace b200 {
 namespace {
@@ -145,7 +146,8 @@ __global__ void rnnt_lattice_kernel(const float* __restrict__ x, const int* __re
                                     int blank) {
   extern __shared__ float sm[];
   const int b = blockIdx.x;
-  const int tb = f_len[b], ub = y_len[b] + 1;
+  // lengths beyond the lattice and labels outside the vocabulary are brought into range (and counted in the debug build)
+  const int tb = checked_range(f_len[b], 0, lat.T), ub = checked_range(y_len[b] + 1, 0, lat.U);
   float* prev = sm;
   float* cur = sm + lat.U + 1;
   const int* lab = label + static_cast<long>(b) * (lat.U - 1);
@@ -167,7 +169,7 @@ __global__ void rnnt_lattice_kernel(const float* __restrict__ x, const int* __re
         else {
           float a = -INFINITY, c = -INFINITY;
           if (t > 0) a = prev[u] + x[lat.row(b, t - 1, u, ub) * V + blank];
-          if (u > 0) c = prev[u - 1] + x[lat.row(b, t, u - 1, ub) * V + lab[u - 1]];
+          if (u > 0) c = prev[u - 1] + x[lat.row(b, t, u - 1, ub) * V + checked_range(lab[u - 1], 0, V - 1)];
           v = log_add(a, c);
         }
       } else {
@@ -176,7 +178,7 @@ __global__ void rnnt_lattice_kernel(const float* __restrict__ x, const int* __re
         else {
           float a = -INFINITY, c = -INFINITY;
           if (t < tb - 1) a = prev[u] + x[r + blank];
-          if (u < ub - 1) c = prev[u + 1] + x[r + lab[u]];
+          if (u < ub - 1) c = prev[u + 1] + x[r + checked_range(lab[u], 0, V - 1)];
           v = log_add(a, c);
         }
         if (t == 0 && u == 0) loss[b] = -v;
@@ -196,7 +198,7 @@ __global__ void rnnt_grad_kernel(const float* __restrict__ x, const float* __res
                                  int fuse_softmax) {
   const int b = blockIdx.y;
   const int t = blockIdx.x / lat.U, u = blockIdx.x % lat.U;
-  const int tb = f_len[b], ub = y_len[b] + 1;
+  const int tb = min(max(f_len[b], 0), lat.T), ub = min(max(y_len[b] + 1, 0), lat.U);   // counted once, in the lattice kernel
   const bool valid = t < tb && u < ub;
   if (!valid && lat.packed) return;
   const long r = lat.row(b, t, u, ub) * V;
@@ -207,7 +209,7 @@ __global__ void rnnt_grad_kernel(const float* __restrict__ x, const float* __res
   const float* al = alpha + static_cast<long>(b) * lat.T * lat.U;
   const float* be = beta + static_cast<long>(b) * lat.T * lat.U;
   const float ll = be[0], a = al[static_cast<long>(t) * lat.U + u], g = loss_grad[b];
-  const int lab = u < ub - 1 ? label[static_cast<long>(b) * (lat.U - 1) + u] : -1;
+  const int lab = u < ub - 1 ? min(max(label[static_cast<long>(b) * (lat.U - 1) + u], 0), V - 1) : -1;
   float db = 0.f, dl = 0.f;
   if (t < tb - 1) db = -g * expf(a + be[static_cast<long>(t + 1) * lat.U + u] + x[r + blank] - ll);
   else if (u == ub - 1) db = -g * expf(a + x[r + blank] - ll);
@@ -590,3 +592,5 @@ const char* nmtg_softmax_dropout_bwd(const void* dyd, const void* y, void* dx, i
 }
 
 }  // extern "C"
+
+NMTG_BOUNDS_READER(nmtg_bounds_sequence)

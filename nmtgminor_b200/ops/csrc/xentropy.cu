@@ -14,6 +14,7 @@
 #include <stdint.h>
 #include <float.h>
 #include "ops_api.h"
+#include "bounds_check.cuh"
 
 namespace b200 {
 
@@ -40,6 +41,7 @@ xent_fused_kernel(__nv_bfloat16* __restrict__ logits, const int64_t* __restrict_
   if (row >= rows) return;
   __nv_bfloat16* x = logits + static_cast<size_t>(row) * ld;
   const long label = labels[row];
+  if (label != pad_idx && (label < 0 || label >= vocab)) NMTG_BOUNDS_HIT();   // treated as padding below
   const bool is_pad = (label == pad_idx) || label < 0 || label >= vocab;
   const int nvec = vocab >> 3;  // full 16-byte vectors (row start is 16-byte aligned when ld % 8 == 0)
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -179,3 +181,5 @@ const char* nmtg_xent_fused(void* logits, const int64_t* labels, float* row_loss
   e = cudaGetLastError();
   return e == cudaSuccess ? nullptr : cudaGetErrorString(e);
 }
+
+NMTG_BOUNDS_READER(nmtg_bounds_xentropy)

@@ -126,6 +126,14 @@ class TrainEngine:
         self.reducer = reducer            # callable(flat_grad) -> None, data-parallel gradient reduction
         self.grad_scale = grad_scale
         self.loss_weight = 1.0            # weight of the next batch's gradient (replay weighting in continual learning)
+        # -fp16 without -bf16: the fp16 protocol (dynamic loss scale, skipped steps) on the bf16 kernels; the scale lives
+        # on the device, so the captured step carries it
+        self.scaler = None
+        from .loss_scaler import DynamicLossScaler, wants_loss_scaling
+        if wants_loss_scaling(opt):
+            self.scaler = DynamicLossScaler(self.device, init_scale=float(getattr(opt, "init_loss_scale", 2.0 ** 16) or 2.0 ** 16),
+                                            growth_interval=int(getattr(opt, "loss_scale_window", 2000) or 2000))
+            self.optim.loss_scaler = self.scaler
         self.use_graph = bool(cuda_graph) and self.on_gpu
         self._graphs = {}                 # shape class -> [graph, static inputs, launches per replay, last use]
         self._pool = None
@@ -143,7 +151,9 @@ class TrainEngine:
         ops.reset_stream_counter()
         # the loss gradient is written pre-scaled by the kernel (scale 1): no [tokens, V] rescale pass in backward
         with nvtx_range("forward", trace):
-            out = self.model(batch, grad_scale=float(getattr(self, "loss_weight", 1.0)))   # per-step weight of this batch's gradient
+            weight = float(getattr(self, "loss_weight", 1.0))       # per-step weight of this batch's gradient
+            gs = weight if self.scaler is None else (self.scaler.scale if weight == 1.0 else self.scaler.scale * weight)
+            out = self.model(batch, grad_scale=gs)
         with nvtx_range("backward", trace):
             out["loss"].backward()
         if not self.optim.fused:

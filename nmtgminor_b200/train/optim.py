@@ -141,10 +141,22 @@ class Optim:
         self.exp_avg = self.exp_avg_sq = None      # the replicated moments are not needed any more
 
     def launch_fused(self):
-        """Enqueue norm + update kernels (graph-capturable: reads only device-resident scalars)."""
+        """Enqueue norm + update kernels (graph-capturable: reads only device-resident scalars).  With a dynamic loss
+        scale (``self.loss_scaler``) the gradient factor is divided by the scale on the device first, and the scale is
+        adjusted from the step's non-finite flag afterwards."""
+        sc = getattr(self, "loss_scaler", None)
+        if sc is not None:
+            sc.prepare(self.hyper)
         if getattr(self, "distributed", None) is not None:
             self.distributed.launch()
+            if sc is not None:
+                sc.update(norm=self.distributed.norm)
             return
+        self._launch_local()
+        if sc is not None:
+            sc.update(nonfinite=self.nonfinite)
+
+    def _launch_local(self):
         s = self.store
         self.grad_sq.zero_()
         self.nonfinite.zero_()
@@ -168,6 +180,20 @@ class Optim:
         lr = self.current_lr()
         for g in self.optimizer.param_groups:
             g["lr"] = lr
+        sc = getattr(self, "loss_scaler", None)
+        if sc is not None:
+            # torch.optim path (CPU ranks, optimisers without a flat kernel): unscale and test for overflow here
+            inv = sc.prepare(None)
+            bad = torch.zeros(1, dtype=torch.int32, device=inv.device)
+            for p in self.params:
+                if p.grad is not None:
+                    p.grad.mul_(inv.to(p.grad.device, p.grad.dtype))
+                    if not bool(torch.isfinite(p.grad).all()):
+                        bad.fill_(1)
+            sc.update(nonfinite=bad)
+            if int(bad):
+                self._step -= 1          # a skipped step is not counted, as with GradScaler
+                return
         if grad_scale != 1.0:
             for p in self.params:
                 if p.grad is not None:

@@ -84,6 +84,8 @@ class Trainer:
                 self.log("[WARN] optimiser state not restored: %r" % (exc,))
             from .checkpoint import restore_rng_state
             restore_rng_state(checkpoint.get("rng"))      # same dropout masks and shuffles as the uninterrupted run
+            if getattr(self.engine, "scaler", None) is not None and isinstance(checkpoint.get("scaler"), dict):
+                self.engine.scaler.load_state_dict(checkpoint["scaler"])
         self.start_time = time.time()
         # -ema: exponential moving average of the parameters (one vector op on the flat master buffer per update),
         # used for validation and for the saved checkpoints
@@ -189,7 +191,9 @@ class Trainer:
         value = valid_ppl if metric in ("ppl", "perplexity") else (1.0 - accuracy if metric == "accuracy" else valid_ppl)
         name = checkpoint_name(opt.save_model, "ppl", value, epoch)
         os.makedirs(os.path.dirname(os.path.abspath(name)), exist_ok=True)
-        save_checkpoint(name, self.model, self.dicts, opt, epoch, self.optim, itr.state_dict() if itr is not None else None)
+        scaler = getattr(self.engine, "scaler", None)
+        save_checkpoint(name, self.model, self.dicts, opt, epoch, self.optim, itr.state_dict() if itr is not None else None,
+                        scaler=scaler.state_dict() if scaler is not None else None)
         prune_checkpoints(opt.save_model, getattr(opt, "keep_save_files", 5), "ppl")
         self.log("[INFO] Saved checkpoint %s" % name)
         return name
@@ -274,9 +278,11 @@ class Trainer:
                 status = ops.check_status() if self.cuda and ops.extension_available() else 0
                 if status:
                     raise RuntimeError("a device kernel gave up waiting (status %d); aborting the run" % status)
-                self.log("Epoch %2d, %5d/%5d; ppl: %8.2f ; lr: %.7f ; num updates: %7d ; %5.0f src tok/s; %5.0f tgt tok/s; %s elapsed"
+                scaler = getattr(self.engine, "scaler", None)
+                extra = "" if scaler is None else " ; loss scale: %g (%d skipped)" % (scaler.get_scale(), scaler.skipped_steps())
+                self.log("Epoch %2d, %5d/%5d; ppl: %8.2f ; lr: %.7f ; num updates: %7d ; %5.0f src tok/s; %5.0f tgt tok/s; %s elapsed%s"
                          % (epoch, i + 1, n_batches, math.exp(min(vals[0] / max(vals[1], 1.0), 100)), self.optim.current_lr(),
-                            self.optim._step, vals[2] / dt, vals[1] / dt, _fmt_time(time.time() - self.start_time)))
+                            self.optim._step, vals[2] / dt, vals[1] / dt, _fmt_time(time.time() - self.start_time), extra))
                 report = {"loss": 0.0, "tgt": 0.0, "src": 0.0, "sents": 0.0}
                 t_window = time.time()
         return epoch_loss / max(epoch_words, 1.0), iterator
