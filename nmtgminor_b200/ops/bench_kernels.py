@@ -195,7 +195,7 @@ def bench_attention_ablation(rows):
     dqkv = torch.zeros_like(qkv)
     dout = torch.randn_like(out)
     names = {0: "everything", 1: "no P/dS math", 2: "no gradient read-out", 4: "no gradient MMAs", 8: "no S/dP MMAs", 16: "no TMA loads",
-             32: "no P/dS stores", 64: "no dropout masks", 3: "no math, no read-out", 19: "no math, no read-out, no loads",
+             32: "no D / log-sum-exp loads", 64: "no dropout masks", 3: "no math, no read-out", 19: "no math, no read-out, no loads",
              31: "barriers only", 12: "no MMAs"}
     try:
         for bits, name in names.items():

@@ -8,9 +8,10 @@
 // is what dominates when a sentence has only 20..100 tokens.
 //
 // forward : two softmax groups alternate items (TMEM: S0 S1 | O0 O1), three Q/K/V slots.
-// backward: a math group (P, D, dS) and an epilogue group (dQ, dK, dV) work on neighbouring items; TMEM holds two sets
-//           (S dP, reused for dV dQ dK), two Q/K/V/dO slots; P and dS are staged once in shared memory and consumed
-//           K-major (dQ = dS K) and MN-major (dV = P^T dO, dK = dS^T Q).
+// backward: 256 math threads (query row x half of the key columns) on one item, a warpgroup that prepares D / log-sum-exp
+//           of the next item and writes dQ, dK, dV of the previous one; TMEM holds two sets (S dP, reused for dV dQ dK),
+//           two Q/K/V/dO slots; P and dS are staged once in shared memory and consumed K-major (dQ = dS K) and MN-major
+//           (dV = P^T dO, dK = dS^T Q).
 // MMA reduction lengths are trimmed to the real sequence lengths (multiples of 16).
 // Same numerics, dropout counters and interfaces as the general kernels in attention_tcgen05.cu.
 #include "attention_common.cuh"
@@ -301,25 +302,31 @@ attn_fwd_short_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
 // ---------------------------------------------------------------------------------------------------
 // backward
 // ---------------------------------------------------------------------------------------------------
-// Roles (320 threads): warps 0-3 compute P and dS of item i, warps 4-7 write the gradients of item i-1, warp 8 is the
-// TMA producer, warp 9 issues every MMA.  TMEM holds two sets of 256 columns, set = item & 1:
+// Roles (448 threads):
+//   warps 0-3 / 4-7   math: thread = (query row, half); half h owns key columns [32 c + 16 h, 32 c + 16 h + 16) of every
+//                     32-column chunk c, so all 256 threads work on the SAME item and each holds few values at a time
+//                     (the math is issue-bound: with one warp per scheduler and most registers tied up in TMEM chunks the
+//                     compiler could not interleave independent elements, which is what made the one-group version slow)
+//   warps 8-11        D = rowsum(dO * O) and the log-sum-exp of item i+1 into shared memory, then dQ / dK / dV of item i-1
+//   warp 12           TMA producer          warp 13   MMA issuer
+// TMEM holds two sets of 256 columns, set = item & 1:
 //   columns   0..127  S  = Q K^T          later  dV (0..63) and dQ (64..127)
 //   columns 128..255  dP = dO V^T         later  dK (128..191)
 // so the S / dP MMAs of item i+1 run while the gradients of item i-1 are still being read out of the other set.
-// P and dS are staged in ONE pair of shared-memory tiles; the math group waits for the gradient MMAs of the previous
-// item (pds_free) only right before its first store, after the exponentials of the new item are done.
-// D = rowsum(dO * O) is not read from memory: it equals rowsum(P_dropped * dP), both of which the math group holds.
+// P and dS are staged in ONE pair of shared-memory tiles; the math threads wait for the gradient MMAs of the previous
+// item (pds_free) only right before their first store, after the exponentials of the new item are done.
 constexpr int kBwdSlots = 2;
 constexpr int kBwdSlotBytes = 4 * kTileBytes;   // Q, K, V, dO
-constexpr int kBwdShortThreads = 320;
-constexpr int kBwdShortSmem = kBwdSlots * kBwdSlotBytes + 2 * kPBytes + 256 + 1024;
+constexpr int kBwdShortThreads = 448;
+constexpr int kBwdRowBytes = 2 * 2 * kTile * 4; // D and log-sum-exp of two items in flight
+constexpr int kBwdShortSmem = kBwdSlots * kBwdSlotBytes + 2 * kPBytes + kBwdRowBytes + 256 + 1024;
 constexpr uint32_t kBwdIssuePolls = 1u << 22;   // polls of the MMA warp without progress before it gives up
 
 // bit j = element (base + j) is kept; base a multiple of 4
-__device__ __forceinline__ uint32_t drop_mask32(const DropRng& rng, unsigned long long base) {
+__device__ __forceinline__ uint32_t drop_mask16(const DropRng& rng, unsigned long long base) {
   uint32_t m = 0;
 #pragma unroll
-  for (int g = 0; g < 8; ++g) {
+  for (int g = 0; g < 4; ++g) {
     const uint32_t w = rng.word((base >> 2) + g);
 #pragma unroll
     for (int j = 0; j < 4; ++j) m |= (rng.keep(w, j) ? 1u : 0u) << (g * 4 + j);
@@ -327,53 +334,16 @@ __device__ __forceinline__ uint32_t drop_mask32(const DropRng& rng, unsigned lon
   return m;
 }
 
-// rs[] : raw scores -> probabilities 2^(S * scale * log2 e - lse * log2 e), 0 outside the sequence / causal triangle.
-// A row past the sequence has lse2 = +inf, so its probabilities are 0 without a per-element test.
-__device__ __forceinline__ void bwd_probs32(uint32_t (&rs)[32], int c, int t, int k_len, bool causal, float scale_log2,
-                                            float lse2) {
-  if (!causal && (c + 1) * 32 <= k_len) {
+// 16 key columns starting at column c0 of query row t: probabilities from the raw scores, dS = P * (dP_dropped - D), both
+// packed to bf16 and stored into the 128-byte-swizzled staging tiles.  A row past the sequence has lse2 = +inf, so its
+// probabilities are 0 without a per-element test.  dS is kept without the softmax scale (applied when dQ and dK leave
+// TMEM).
+__device__ __forceinline__ void bwd_emit16(const uint32_t (&sc)[16], const uint32_t (&dp)[16], uint32_t keep, bool do_drop,
+                                           float keep_scale, float Drow, float scale_log2, float lse2, int c0, int t, int k_len,
+                                           bool causal, uint8_t* sP, uint8_t* sDS) {
+  const bool full = !causal && c0 + 16 <= k_len;
 #pragma unroll
-    for (int j = 0; j < 32; ++j) rs[j] = __float_as_uint(ex2_approx(fmaf(__uint_as_float(rs[j]), scale_log2, -lse2)));
-  } else {
-#pragma unroll
-    for (int j = 0; j < 32; ++j) {
-      const int col = c * 32 + j;
-      const bool valid = col < k_len && (!causal || col <= t);
-      rs[j] = valid ? __float_as_uint(ex2_approx(fmaf(__uint_as_float(rs[j]), scale_log2, -lse2))) : 0u;
-    }
-  }
-}
-
-// sum over the 32 columns of P * dP over the kept elements (the keep scale is applied by the caller)
-__device__ __forceinline__ float bwd_dsum32(const uint32_t (&pr)[32], const uint32_t (&dp)[32], uint32_t keep, bool do_drop) {
-  float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
-  if (!do_drop) {
-#pragma unroll
-    for (int j = 0; j < 32; j += 4) {
-      a0 = fmaf(__uint_as_float(pr[j]), __uint_as_float(dp[j]), a0);
-      a1 = fmaf(__uint_as_float(pr[j + 1]), __uint_as_float(dp[j + 1]), a1);
-      a2 = fmaf(__uint_as_float(pr[j + 2]), __uint_as_float(dp[j + 2]), a2);
-      a3 = fmaf(__uint_as_float(pr[j + 3]), __uint_as_float(dp[j + 3]), a3);
-    }
-  } else {
-#pragma unroll
-    for (int j = 0; j < 32; j += 4) {
-      a0 = fmaf(__uint_as_float(pr[j]), ((keep >> j) & 1u) ? __uint_as_float(dp[j]) : 0.f, a0);
-      a1 = fmaf(__uint_as_float(pr[j + 1]), ((keep >> (j + 1)) & 1u) ? __uint_as_float(dp[j + 1]) : 0.f, a1);
-      a2 = fmaf(__uint_as_float(pr[j + 2]), ((keep >> (j + 2)) & 1u) ? __uint_as_float(dp[j + 2]) : 0.f, a2);
-      a3 = fmaf(__uint_as_float(pr[j + 3]), ((keep >> (j + 3)) & 1u) ? __uint_as_float(dp[j + 3]) : 0.f, a3);
-    }
-  }
-  return (a0 + a1) + (a2 + a3);
-}
-
-// Packs the dropped probabilities and dS = P * (dP_dropped - D) of 32 columns to bf16 and stores them into the two
-// 128-byte-swizzled staging tiles (row t, columns c * 32 ..).  dS is kept without the softmax scale (applied when dQ and
-// dK leave TMEM).
-__device__ __forceinline__ void bwd_emit32(const uint32_t (&pr)[32], const uint32_t (&dp)[32], uint32_t keep, bool do_drop,
-                                           float keep_scale, float Drow, int c, int t, uint8_t* sP, uint8_t* sDS) {
-#pragma unroll
-  for (int g4 = 0; g4 < 4; ++g4) {
+  for (int g2 = 0; g2 < 2; ++g2) {
     uint4 o1, o2v;
     __nv_bfloat162* a2 = reinterpret_cast<__nv_bfloat162*>(&o1);
     __nv_bfloat162* b2 = reinterpret_cast<__nv_bfloat162*>(&o2v);
@@ -382,8 +352,11 @@ __device__ __forceinline__ void bwd_emit32(const uint32_t (&pr)[32], const uint3
       float pd[2], ds[2];
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
-        const int idx = g4 * 8 + 2 * j + e;
-        const float prob = __uint_as_float(pr[idx]), d = __uint_as_float(dp[idx]);
+        const int idx = g2 * 8 + 2 * j + e;
+        const int col = c0 + idx;
+        const bool valid = full || (col < k_len && (!causal || col <= t));
+        const float prob = valid ? ex2_approx(fmaf(__uint_as_float(sc[idx]), scale_log2, -lse2)) : 0.f;
+        const float d = __uint_as_float(dp[idx]);
         if (do_drop) {
           const float kf = ((keep >> idx) & 1u) ? keep_scale : 0.f;
           pd[e] = prob * kf;
@@ -396,7 +369,7 @@ __device__ __forceinline__ void bwd_emit32(const uint32_t (&pr)[32], const uint3
       a2[j] = __floats2bfloat162_rn(pd[0], pd[1]);
       b2[j] = __floats2bfloat162_rn(ds[0], ds[1]);
     }
-    const int chunk = c * 4 + g4;
+    const int chunk = (c0 >> 3) + g2;     // 16-byte chunk of the row: 8 per 64-key slab
     const uint32_t off = (chunk >> 3) * kTileBytes + sw128_offset(t, chunk & 7);
     *reinterpret_cast<uint4*>(sP + off) = o1;
     *reinterpret_cast<uint4*>(sDS + off) = o2v;
@@ -431,21 +404,25 @@ attn_bwd_short_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
   // `ablate` (0 in production) switches parts of the work off while keeping every barrier hand-shake, so that a timing run
   // can tell which role bounds the item rate (results are then meaningless):
   //   1 no P / dS math   2 no gradient read-out   4 no gradient MMAs   8 no S / dP MMAs   16 no TMA loads
-  //   32 no P / dS shared-memory stores   64 no dropout masks
+  //   32 no D / log-sum-exp loads   64 no dropout masks
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sSlots = smem;
   uint8_t* sP = smem + kBwdSlots * kBwdSlotBytes;
   uint8_t* sDS = sP + kPBytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sDS + kPBytes);
+  float* sD = reinterpret_cast<float*>(sDS + kPBytes);   // [2][128] rowsum(dO * O) of the items in flight
+  float* sL = sD + 2 * kTile;                            // [2][128] log-sum-exp * log2 e (+inf for rows past the sequence)
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sDS + kPBytes + kBwdRowBytes);
   uint64_t* slot_full = bars;        // [2] TMA -> MMA
   uint64_t* slot_empty = bars + 2;   // [2] gradient MMAs done -> TMA
   uint64_t* sdp_full = bars + 4;     // [2] S / dP ready -> math group
   uint64_t* set_free = bars + 6;     // [2] gradients read out -> MMA may overwrite the set
   uint64_t* grads_full = bars + 8;   // [2] gradient MMAs done -> epilogue group
   uint64_t* pds_full = bars + 10;    // P / dS staged -> MMA
-  uint64_t* pds_free = bars + 11;    // gradient MMAs done -> math group may overwrite P / dS
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+  uint64_t* pds_free = bars + 11;    // gradient MMAs done -> math threads may overwrite P / dS
+  uint64_t* d_full = bars + 12;      // [2] D / log-sum-exp rows written -> math threads
+  uint64_t* d_free = bars + 14;      // [2] rows read -> may be overwritten
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
   volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   zero_tail_bwd(p);
@@ -457,19 +434,21 @@ attn_bwd_short_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
       mbar_init(&sdp_full[i], 1);
       mbar_init(&set_free[i], 128);
       mbar_init(&grads_full[i], 1);
+      mbar_init(&d_full[i], 128);
+      mbar_init(&d_free[i], 256);
     }
-    mbar_init(pds_full, 128);
+    mbar_init(pds_full, 256);
     mbar_init(pds_free, 1);
     *abort_word = 0;
     mbar_fence_init();
   }
-  if (warp == 9) tmem_alloc(tmem_slot, 512);
+  if (warp == 13) tmem_alloc(tmem_slot, 512);
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 8) {
+  if (warp == 12) {
     if (lane == 0) {
       int it = 0;
       for (int item = blockIdx.x; item < num_items; item += gridDim.x) {
@@ -491,7 +470,7 @@ attn_bwd_short_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
         ++it;
       }
     }
-  } else if (warp == 9) {
+  } else if (warp == 13) {
     if (lane == 0) {
       const uint32_t idesc_s = make_idesc_bf16(kTile, kTile, 0, 0);
       const uint32_t idesc_dq = make_idesc_bf16(kTile, kHd, 0, 1);
@@ -575,89 +554,68 @@ attn_bwd_short_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
         }
       }
     }
-  } else if (warp < 4) {
-    // ---- math group: P, D and dS of every item --------------------------------------------------------------------
-    const int t = warp * 32 + lane;
-    const uint32_t lane_sel = static_cast<uint32_t>(warp * 32) << 16;
+  } else if (warp < 8) {
+    // ---- math threads: P and dS of every item, 16 of every 32 key columns each ---------------------------------------
+    const int half = warp >> 2;
+    const int t = (warp & 3) * 32 + lane;
+    const uint32_t lane_sel = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const float scale_log2 = p.scale * 1.4426950408889634f;
     const bool do_drop = p.dropout_p > 0.f && !(ablate & 64);
     const unsigned long long seed = p.seed + ((do_drop && p.seed_dev) ? *p.seed_dev : 0ull);
-    const float kInf = __int_as_float(0x7f800000);
     int it = 0;
     int item = blockIdx.x;
     Item nxt = item < num_items ? get_item(p, item) : Item{};
-    float lse_nxt = (nxt.valid && t < nxt.q_len) ? p.lse[static_cast<size_t>(nxt.h) * p.lse_stride + nxt.q0 + t] : 0.f;
     while (item < num_items) {
       const Item w = nxt;
-      const float lse = lse_nxt;
       item += gridDim.x;
-      if (item < num_items) {   // the next item's descriptor and log-sum-exp are fetched under this item's work
-        nxt = get_item(p, item);
-        if (nxt.valid && t < nxt.q_len) lse_nxt = p.lse[static_cast<size_t>(nxt.h) * p.lse_stride + nxt.q0 + t];
-      }
+      if (item < num_items) nxt = get_item(p, item);   // the next item's descriptor is fetched under this item's work
       if (!w.valid) continue;
       const int s = it & 1;
-      const uint32_t set = tmem_base + s * 256 + lane_sel;
-      const bool row_ok = t < w.q_len;
-      const float lse2 = row_ok ? lse * 1.4426950408889634f : kInf;
+      const uint32_t set = tmem_base + s * 256 + lane_sel + half * 16;
+      if (!__all_sync(0xffffffffu, mbar_wait(&d_full[s], (it >> 1) & 1, abort_word, p.status, kTimeoutTmemFull))) break;
+      const float Drow = sD[s * kTile + t], lse2 = sL[s * kTile + t];
+      mbar_arrive(&d_free[s]);
       if (!__all_sync(0xffffffffu, mbar_wait(&sdp_full[s], (it >> 1) & 1, abort_word, p.status, kTimeoutTmemFull))) break;
       tc_fence_after_sync();
       const int nchunks = (w.k_len + 31) >> 5;
       const int q_rows16 = ((w.q_len + 15) >> 4) << 4;   // rows the MN-major MMAs will read
-      const bool warp_writes = warp * 32 < q_rows16 && !(ablate & 1);
+      const bool warp_writes = (warp & 3) * 32 < q_rows16 && !(ablate & 1);
       bool may_store = it == 0, ok = true;
       if (warp_writes) {
         const DropRng rng(seed, (p.stream_id << 16) | static_cast<unsigned long long>(w.h), p.dropout_p);
-        const unsigned long long row_base = static_cast<unsigned long long>(w.q0 + t) * p.kstride;
-        const int passes = nchunks > 2 ? 2 : 1;   // up to 64 keys: one round holds the whole row, D needs no second pass
-        float Dacc = 0.f;
+        const unsigned long long row_base = static_cast<unsigned long long>(w.q0 + t) * p.kstride + half * 16;
+        // two chunks (2 x 16 columns of this thread) per round: four TMEM loads in flight before the single wait
 #pragma unroll 1
-        for (int pass = 0; pass < passes && ok; ++pass) {
-          const bool emit = pass == passes - 1;
-#pragma unroll 1
-          for (int c0 = 0; c0 < nchunks; c0 += 2) {
-            const bool two = c0 + 1 < nchunks;
-            uint32_t rs0[32], rd0[32], rs1[32], rd1[32];
-            tmem_ld32(set + c0 * 32, rs0);
-            tmem_ld32(set + 128 + c0 * 32, rd0);
-            if (two) {
-              tmem_ld32(set + (c0 + 1) * 32, rs1);
-              tmem_ld32(set + 128 + (c0 + 1) * 32, rd1);
-            }
-            uint32_t km0 = 0xffffffffu, km1 = 0xffffffffu;
-            if (do_drop) {   // the mask words are hashed while the TMEM loads are in flight
-              km0 = drop_mask32(rng, row_base + c0 * 32);
-              if (two) km1 = drop_mask32(rng, row_base + (c0 + 1) * 32);
-            }
-            tmem_ld_wait();
-            bwd_probs32(rs0, c0, t, w.k_len, p.causal != 0, scale_log2, lse2);
-            if (two) bwd_probs32(rs1, c0 + 1, t, w.k_len, p.causal != 0, scale_log2, lse2);
-            if (pass == 0) {
-              Dacc += bwd_dsum32(rs0, rd0, km0, do_drop);
-              if (two) Dacc += bwd_dsum32(rs1, rd1, km1, do_drop);
-            }
-            if (emit) {
-              if (!may_store) {   // the gradient MMAs of the previous item still read the staging tiles
-                ok = mbar_wait(pds_free, (it - 1) & 1, abort_word, p.status, kTimeoutSmemEmpty);
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
-                may_store = true;
-              }
-              const float Drow = Dacc * rng.scale;
-              if (!(ablate & 32)) {
-                bwd_emit32(rs0, rd0, km0, do_drop, rng.scale, Drow, c0, t, sP, sDS);
-                if (two) bwd_emit32(rs1, rd1, km1, do_drop, rng.scale, Drow, c0 + 1, t, sP, sDS);
-              } else if (Drow == 12345.678f) {
-                sP[t] = static_cast<uint8_t>(rs0[0] + rd0[1] + rs1[2] + rd1[3]);   // keeps the math alive
-              }
-            }
+        for (int c = 0; c < nchunks; c += 2) {
+          const bool two = c + 1 < nchunks;
+          uint32_t s0[16], d0[16], s1[16], d1[16];
+          tmem_ld16(set + c * 32, s0);
+          tmem_ld16(set + 128 + c * 32, d0);
+          if (two) {
+            tmem_ld16(set + (c + 1) * 32, s1);
+            tmem_ld16(set + 128 + (c + 1) * 32, d1);
           }
+          uint32_t km0 = 0xffffu, km1 = 0xffffu;
+          if (do_drop) {   // the mask words are hashed while the TMEM loads are in flight
+            km0 = drop_mask16(rng, row_base + c * 32);
+            if (two) km1 = drop_mask16(rng, row_base + (c + 1) * 32);
+          }
+          tmem_ld_wait();
+          if (!may_store) {   // the gradient MMAs of the previous item still read the staging tiles
+            ok = __all_sync(0xffffffffu, mbar_wait(pds_free, (it - 1) & 1, abort_word, p.status, kTimeoutSmemEmpty));
+            if (!ok) break;
+            may_store = true;
+          }
+          bwd_emit16(s0, d0, km0, do_drop, rng.scale, Drow, scale_log2, lse2, c * 32 + half * 16, t, w.k_len, p.causal != 0, sP, sDS);
+          if (two)
+            bwd_emit16(s1, d1, km1, do_drop, rng.scale, Drow, scale_log2, lse2, (c + 1) * 32 + half * 16, t, w.k_len, p.causal != 0,
+                       sP, sDS);
         }
       }
       if (ok && !may_store) {
-        // A warp with no rows to write must not run ahead either: S / dP are double-buffered, so without this wait it could
-        // reach its arrival for the NEXT item while the other warps still write this one, and complete the phase early.
-        // pds_free(it - 1) implies that phase it - 1 of pds_full is complete.
+        // No thread may run ahead: S / dP and the D rows are double-buffered, so without this wait a thread with nothing to
+        // write could reach its arrival for the NEXT item while the others still write this one, and complete the phase
+        // early.  pds_free(it - 1) implies that phase it - 1 of pds_full is complete.
         ok = __all_sync(0xffffffffu, mbar_wait(pds_free, (it - 1) & 1, abort_word, p.status, kTimeoutSmemEmpty));
       }
       if (!ok) break;
@@ -666,41 +624,75 @@ attn_bwd_short_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
       mbar_arrive(pds_full);
       ++it;
     }
-  } else if (warp < 8) {
-    // ---- epilogue group: dQ row t (queries), dK / dV row t (keys) of every item ----------------------------------------
-    const int wq = warp - 4;
+  } else if (warp < 12) {
+    // ---- D / log-sum-exp rows of item i, then dQ row t (queries) and dK / dV row t (keys) of item i - 1 --------------
+    const int wq = warp - 8;
     const int t = wq * 32 + lane;
     const uint32_t lane_sel = static_cast<uint32_t>(wq * 32) << 16;
+    const float kInf = __int_as_float(0x7f800000);
     int it = 0;
     int item = blockIdx.x;
     Item nxt = item < num_items ? get_item(p, item) : Item{};
-    while (item < num_items) {
+    Item prev{};
+    bool ok = true;
+    auto read_out = [&](const Item& w, int j) -> bool {
+      const int s = j & 1;
+      const uint32_t set = tmem_base + s * 256 + lane_sel;
+      if (!__all_sync(0xffffffffu, mbar_wait(&grads_full[s], (j >> 1) & 1, abort_word, p.status, kTimeoutTmemFull))) return false;
+      tc_fence_after_sync();
+      if (!(ablate & 2)) {
+        const size_t col = static_cast<size_t>(w.h) * kHd;
+        if (wq * 32 < w.q_len)
+          bwd_store_row(set + 64, p.dq + static_cast<size_t>(w.q0 + t) * p.ld_dq + col, p.scale, t < w.q_len);
+        if (wq * 32 < w.k_len) {
+          // dK carries the softmax scale that dS left out
+          bwd_store_row(set + 128, p.dk + static_cast<size_t>(w.k0 + t) * p.ld_dk + col, p.scale, t < w.k_len);
+          bwd_store_row(set, p.dv + static_cast<size_t>(w.k0 + t) * p.ld_dv + col, 1.f, t < w.k_len);
+        }
+      }
+      tc_fence_before_sync();
+      mbar_arrive(&set_free[s]);
+      return true;
+    };
+    while (item < num_items && ok) {
       const Item w = nxt;
       item += gridDim.x;
       if (item < num_items) nxt = get_item(p, item);
       if (!w.valid) continue;
       const int s = it & 1;
-      const uint32_t set = tmem_base + s * 256 + lane_sel;
-      if (!__all_sync(0xffffffffu, mbar_wait(&grads_full[s], (it >> 1) & 1, abort_word, p.status, kTimeoutTmemFull))) break;
-      tc_fence_after_sync();
-      const size_t col = static_cast<size_t>(w.h) * kHd;
-      if (ablate & 2) {
-        tc_fence_before_sync();
-        mbar_arrive(&set_free[s]);
-        ++it;
-        continue;
+      float Drow = 0.f, lse2 = kInf;
+      if (t < w.q_len && !(ablate & 32)) {
+        const uint4* orow = reinterpret_cast<const uint4*>(p.o + static_cast<size_t>(w.q0 + t) * p.ld_o + w.h * kHd);
+        const uint4* drow = reinterpret_cast<const uint4*>(p.d_o + static_cast<size_t>(w.q0 + t) * p.ld_do + w.h * kHd);
+        uint4 a[8], d[8];
+#pragma unroll
+        for (int g4 = 0; g4 < 8; ++g4) { a[g4] = orow[g4]; d[g4] = drow[g4]; }
+        lse2 = p.lse[static_cast<size_t>(w.h) * p.lse_stride + w.q0 + t] * 1.4426950408889634f;
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int g4 = 0; g4 < 8; ++g4) {
+          const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&a[g4]);
+          const __nv_bfloat162* d2 = reinterpret_cast<const __nv_bfloat162*>(&d[g4]);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 x = __bfloat1622float2(a2[j]), y = __bfloat1622float2(d2[j]);
+            acc[j] = fmaf(x.x, y.x, fmaf(x.y, y.y, acc[j]));
+          }
+        }
+        Drow = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+      } else if (t < w.q_len) {
+        lse2 = 0.f;
       }
-      if (wq * 32 < w.q_len)
-        bwd_store_row(set + 64, p.dq + static_cast<size_t>(w.q0 + t) * p.ld_dq + col, p.scale, t < w.q_len);
-      if (wq * 32 < w.k_len) {
-        // dK carries the softmax scale that dS left out
-        bwd_store_row(set + 128, p.dk + static_cast<size_t>(w.k0 + t) * p.ld_dk + col, p.scale, t < w.k_len);
-        bwd_store_row(set, p.dv + static_cast<size_t>(w.k0 + t) * p.ld_dv + col, 1.f, t < w.k_len);
-      }
-      tc_fence_before_sync();
-      mbar_arrive(&set_free[s]);
+      // the rows of item it - 2 have been read by every math thread
+      if (!__all_sync(0xffffffffu, mbar_wait(&d_free[s], ((it >> 1) & 1) ^ 1, abort_word, p.status, kTimeoutSmemEmpty))) { ok = false; break; }
+      sD[s * kTile + t] = Drow;
+      sL[s * kTile + t] = lse2;
+      mbar_arrive(&d_full[s]);
+      if (it > 0) ok = read_out(prev, it - 1);
+      prev = w;
       ++it;
     }
+    if (ok && it > 0) read_out(prev, it - 1);
   }
 
   tc_fence_before_sync();
@@ -709,7 +701,7 @@ attn_bwd_short_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
     for (int i = 0; i < 2000; ++i) __nanosleep(1000);
     __syncthreads();
   }
-  if (warp == 9) {
+  if (warp == 13) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, 512);
   }
