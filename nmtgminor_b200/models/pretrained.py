@@ -288,6 +288,32 @@ class SpeechToTextModel(Seq2SeqBase, _ReferenceNaming):
         self.ctc_weight = getattr(opt, "ctc_loss", 0.0)
         if self.ctc_weight > 0:
             self.ctc_linear = nn.Linear(encoder.dim, vocab)
+        # -transducer_loss w: an RNN-T branch next to the attention decoder.  The decoder states act as the prediction
+        # network, the joint is relu(f_t + g_u) -> Linear, blank = padding id (reference:
+        # onmt/models/speech_recognizer/wav2vec2.py:557-566 construction, :697-730 loss)
+        self.transducer_weight = float(getattr(opt, "transducer_loss", 0.0) or 0.0)
+        if self.transducer_weight > 0:
+            from ..ops.sequence import TransducerJoint, TransducerLoss
+            if encoder.dim != dim:
+                raise ValueError("-transducer_loss adds encoder and decoder states: their sizes must be equal")
+            self.transducer_joint = TransducerJoint(pack_output=False, relu=True)
+            self.transducer_linear = nn.Linear(dim, vocab)
+            self.transducer_criterion = TransducerLoss(fuse_softmax_backward=False)
+
+    def _transducer_term(self, context, src, out):
+        tgt = out["tgt"]
+        f = src.pad(context, time_first=False).float()                            # [B, T, H]
+        g = tgt.pad(out["hidden_packed"], time_first=False).float()               # [B, U + 1, H]: states after BOS, y1 .. yU
+        f_len = (src.cu[1:] - src.cu[:-1]).int()
+        g_len = (tgt.cu[1:] - tgt.cu[:-1]).int()
+        B = f.shape[0]
+        tokens = tgt.pad(tgt.tokens[:, None].float(), time_first=False).squeeze(-1).long()    # [B, U + 1], BOS first
+        labels = tokens[:, 1:].contiguous()                                        # y1 .. yU
+        joint = self.transducer_joint(f, g, f_len[:B], g_len)
+        logp = torch.log_softmax(self.transducer_linear(joint).float(), -1)       # [B, T, U + 1, V]
+        loss = self.transducer_criterion(logp, labels, f_len[:B], g_len - 1, self.pad_idx)
+        out["transducer_loss"], out["transducer_numel"] = loss.sum().detach(), int((g_len - 1).sum())
+        return loss.sum()
 
     def encode(self, batch):
         context, src = self.encoder(batch.get("source"))
@@ -301,8 +327,19 @@ class SpeechToTextModel(Seq2SeqBase, _ReferenceNaming):
         return context, src
 
     def auxiliary_losses(self, batch, context, src, out):
-        if self.ctc_weight <= 0 or not self.training:
+        if not self.training:
             return None
+        extra = None
+        if self.transducer_weight > 0:
+            if getattr(self, "_uncompressed", None) is not None:
+                raise RuntimeError("-transducer_loss and -ctc_compress cannot be combined (the lattice needs every frame)")
+            extra = self.transducer_weight * self._transducer_term(context, src, out)
+        if self.ctc_weight <= 0:
+            return extra
+        ctc = self._ctc_term(batch, context, src, out)
+        return ctc if extra is None else ctc + extra
+
+    def _ctc_term(self, batch, context, src, out):
         if getattr(self, "_uncompressed", None) is not None:
             context, src = self._uncompressed              # the CTC loss is defined on the frame-level states
         logits = src.pad(self.ctc_linear(context.float()))                   # [T, B, V]

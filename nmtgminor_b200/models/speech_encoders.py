@@ -136,8 +136,9 @@ class GatedRelPosSelfAttention(SelfAttention):
     layer and shared by all) is added to the scores after being scaled, per query position and head, by a gate
     computed from the query: ``g = a * (b * grep_a - 1) + 2`` with ``a, b = sigmoid(sum_4(W q))``.
 
-    The additive bias is not expressible in the packed tensor-core attention kernels, so this sub-layer pads the
-    fused projection and runs PyTorch's scaled-dot-product attention; projections stay on the fused GEMM path.
+    The bias goes into the attention kernels as an additive fp32 operand ``[batch, heads, T, T]`` (``ops.self_attention(...,
+    bias=)``: added to the scaled scores in the softmax, its gradient returned in the same layout), so this sub-layer stays
+    on the packed tensor-core path; on the CPU the PyTorch restatement takes the same argument.
     Reference: onmt/models/speech_recognizer/fairseq_wav2vec2/wavlm_modules.py:128-166 (buckets, bias), :236-256 (gate).
     """
 
@@ -170,20 +171,20 @@ class GatedRelPosSelfAttention(SelfAttention):
         return bias
 
     def forward(self, x, seqs: PackedSeqs, residual=None, dropout_p: float = 0.0):
-        from ..ops.reference import pad_packed, unpad_packed
+        from ..ops.reference import pad_packed
         H, h = self.dim, self.heads
-        qkv, valid = pad_packed(self.qkv(x), seqs.cu, seqs.max_len)               # [B, T, 3H]
-        B, T, _ = qkv.shape
-        q, k, v = (t.view(B, T, h, H // h).transpose(1, 2) for t in qkv.float().split(H, dim=-1))
-        gate = self.grep_linear(q).view(B, h, T, 2, 4).sum(-1)
-        ga, gb = torch.sigmoid(gate).chunk(2, dim=-1)
-        scale = ga * (gb * self.grep_a - 1.0) + 2.0                                 # [B, h, T, 1]
-        bias = scale * self.position_bias(T, x.device, (id(seqs), torch.is_grad_enabled()))[None].float()
-        bias = bias.masked_fill(~valid[:, None, None, :], float("-inf"))
-        ctx = F.scaled_dot_product_attention(q, k, v, attn_mask=bias, dropout_p=self.attn_dropout if self.training else 0.0)
-        ctx = ctx.transpose(1, 2).reshape(B, T, H) * valid.unsqueeze(-1)
-        ctx = unpad_packed(ctx, seqs.cu, x.shape[0]).to(x.dtype)
-        return self.out(ctx, dropout_p=dropout_p, residual=residual)
+        qkv = self.qkv(x)                                                          # packed [N, 3H]
+        T = int(seqs.max_len)
+        # the gate is a function of the query row; only the [B, h, T, T] bias itself needs the padded layout
+        q_rows = qkv[:, :H].float().view(-1, h, H // h)
+        gate = self.grep_linear(q_rows).view(-1, h, 2, 4).sum(-1)
+        ga, gb = torch.sigmoid(gate).chunk(2, dim=-1)                              # [N, h, 1]
+        scale_rows = (ga * (gb * self.grep_a.view(1, h, 1) - 1.0) + 2.0).squeeze(-1)   # [N, h]
+        scale_pad, _ = pad_packed(scale_rows, seqs.cu, T)                          # [B, T, h]
+        table = self.position_bias(T, x.device, (id(seqs), torch.is_grad_enabled())).float()    # [h, T, T]
+        bias = scale_pad.permute(0, 2, 1).unsqueeze(-1) * table[None]               # [B, h, T, T]
+        ctx = ops.self_attention(qkv, seqs.cu, h, T, False, self.attn_dropout, self.training, bias=bias)
+        return self.out(ctx.to(x.dtype), dropout_p=dropout_p, residual=residual)
 
 
 class Wav2Vec2Encoder(nn.Module):

@@ -448,6 +448,9 @@ class Transformer(Seq2SeqBase):
         self.generator_chunk_rows = int(getattr(opt, "generator_chunk_rows", 0) or 0)
         # -mirror_loss: a second decoder reads the target right to left; its loss is added and the forward decoder's
         # states (through a learned map g) are pulled towards the backward decoder's states of the same positions
+        if float(getattr(opt, "transducer_loss", 0.0) or 0.0) > 0:
+            raise NotImplementedError("-transducer_loss is built for the speech models (frames against labels); "
+                                      "the text Transformer has no transducer branch")
         self.mirror_weight = float(getattr(opt, "mirror_loss", 0.0) or 0.0)
         if self.mirror_weight > 0:
             self.mirror_decoder = copy.deepcopy(self.decoder)

@@ -171,18 +171,20 @@ class ShawRelPosSelfAttention(SelfAttention):
         return (pos[None, :] - pos[:, None]).clamp(-self.max_left, self.max_right) + self.max_left     # [T, T]
 
     def forward(self, x, seqs: PackedSeqs, residual=None, dropout_p: float = 0.0):
-        from ..ops.reference import pad_packed, unpad_packed
+        from ..ops.reference import pad_packed
         H, h = self.dim, self.heads
-        qkv, valid = pad_packed(self.qkv(x), seqs.cu, seqs.max_len)
-        B, T, _ = qkv.shape
-        q, k, v = (t.view(B, T, h, H // h).transpose(1, 2) for t in qkv.float().split(H, dim=-1))
+        qkv = self.qkv(x)                                                              # packed [N, 3H]
+        T = int(seqs.max_len)
         scale = (H // h) ** -0.5
-        by_offset = torch.matmul(q, self.rel_k.weight.float().t()) * scale                # [B, h, T, L+R+1]
+        q_rows = qkv[:, :H].float().view(-1, h, H // h)
+        by_offset = torch.matmul(q_rows, self.rel_k.weight.float().t()) * scale         # [N, h, L+R+1]
+        by_offset, _ = pad_packed(by_offset.reshape(by_offset.shape[0], -1), seqs.cu, T)    # [B, T, h * (L+R+1)]
+        B = by_offset.shape[0]
+        by_offset = by_offset.view(B, T, h, -1).transpose(1, 2)                         # [B, h, T, L+R+1]
         bias = by_offset.gather(-1, self.rel_index(T, x.device)[None, None].expand(B, h, T, T))
-        bias = bias.masked_fill(~valid[:, None, None, :], float("-inf"))
-        ctx = F.scaled_dot_product_attention(q, k, v, attn_mask=bias, dropout_p=self.attn_dropout if self.training else 0.0)
-        ctx = ctx.transpose(1, 2).reshape(B, T, H) * valid.unsqueeze(-1)
-        return self.out(unpad_packed(ctx, seqs.cu, x.shape[0]).to(x.dtype), dropout_p=dropout_p, residual=residual)
+        # the relative-key term is an additive operand of the attention kernels (gradient comes back in the same layout)
+        ctx = ops.self_attention(qkv, seqs.cu, h, T, False, self.attn_dropout, self.training, scale=scale, bias=bias)
+        return self.out(ctx.to(x.dtype), dropout_p=dropout_p, residual=residual)
 
 
 class ShawConvolution(nn.Module):

@@ -481,11 +481,69 @@ class _AttnFn(torch.autograd.Function):
         return (da, db) + (None,) * 10
 
 
-def _attn_dispatch(a, b, cu_q, cu_k, heads, max_q, max_k, causal, dropout_p, training, scale):
+class _AttnBiasFn(torch.autograd.Function):
+    """``_AttnFn`` with an additive fp32 score bias ``[batch, heads, max_q, max_k]`` (relative-position terms): the bias is
+    added to the scaled scores inside the kernels, its gradient (dS before the softmax scale) comes back in the same
+    layout.  Always the general multi-tile kernels."""
+
+    @staticmethod
+    def forward(ctx, a, b, bias, cu_q, cu_k, heads, max_q, max_k, causal, scale, p, seed, sid):
+        W = heads * 64
+        if b is None:
+            q, k, v = a[:, :W], a[:, W:2 * W], a[:, 2 * W:]
+        else:
+            q, k, v = a, b[:, :W], b[:, W:]
+        out = torch.empty((q.shape[0], W), dtype=torch.bfloat16, device=q.device)
+        lse = torch.empty((heads, q.shape[0]), dtype=torch.float32, device=q.device)
+        ext().attn_fwd_bias(q, k, v, out, lse, cu_q, cu_k, heads, max_q, max_k, causal, scale, p, seed, sid, bias)
+        LAUNCHES[0] += 1
+        ctx.save_for_backward(a, b, bias, out, lse, cu_q, cu_k)
+        ctx.cfg = (heads, max_q, max_k, causal, scale, p, seed, sid)
+        return out
+
+    @staticmethod
+    def backward(ctx, d_out):
+        a, b, bias, out, lse, cu_q, cu_k = ctx.saved_tensors
+        heads, max_q, max_k, causal, scale, p, seed, sid = ctx.cfg
+        W = heads * 64
+        da = torch.empty_like(a)
+        if b is None:
+            q, k, v = a[:, :W], a[:, W:2 * W], a[:, 2 * W:]
+            dq, dk, dv = da[:, :W], da[:, W:2 * W], da[:, 2 * W:]
+            db = None
+        else:
+            db = torch.empty_like(b)
+            q, k, v = a, b[:, :W], b[:, W:]
+            dq, dk, dv = da, db[:, :W], db[:, W:]
+        dq_acc = torch.zeros((q.shape[0], W), dtype=torch.float32, device=q.device) if max_k > 128 else None
+        dbias = torch.zeros_like(bias) if ctx.needs_input_grad[2] else None      # pairs outside the sequences stay zero
+        ext().attn_bwd_bias(q, k, v, out, lse, d_out.contiguous(), dq, dk, dv, dq_acc, cu_q, cu_k, heads, max_q, max_k, causal,
+                            scale, p, seed, sid, bias, dbias)
+        LAUNCHES[0] += 1
+        return (da, db, dbias) + (None,) * 10
+
+
+def _attn_dispatch(a, b, cu_q, cu_k, heads, max_q, max_k, causal, dropout_p, training, scale, bias=None):
     W = (a.shape[1] // 3) if b is None else a.shape[1]
     d = W // heads
     scale = (1.0 / math.sqrt(d)) if scale is None else scale
     p = float(dropout_p) if training else 0.0
+    if bias is not None and a.is_cuda and d == 64 and a.dtype == torch.bfloat16:
+        sid = next_stream() if p > 0 else 0
+        a = a.contiguous()
+        b = b.contiguous() if b is not None else None
+        bias = bias.float()
+        if bias.stride(-1) != 1:
+            bias = bias.contiguous()
+        if not torch.is_grad_enabled():
+            bias = bias.detach()
+        return _AttnBiasFn.apply(a, b, bias, cu_q, cu_k, heads, int(max_q), int(max_k), bool(causal), scale, p, _Rng.seed, sid)
+    if bias is not None:
+        if b is None:
+            q, k, v = a[:, :W], a[:, W:2 * W], a[:, 2 * W:]
+        else:
+            q, k, v = a, b[:, :W], b[:, W:]
+        return ref.attention(q, k, v, cu_q, cu_k, heads, causal, p, scale, bias=bias)
     if a.is_cuda and d == 64 and a.dtype == torch.bfloat16:
         sid = next_stream() if p > 0 else 0
         a = a.contiguous()
@@ -507,14 +565,16 @@ def _attn_dispatch(a, b, cu_q, cu_k, heads, max_q, max_k, causal, dropout_p, tra
     return ref.attention(q, k, v, cu_q, cu_k, heads, causal, p, scale)
 
 
-def self_attention(qkv, cu, heads, max_len, causal=False, dropout_p=0.0, training=True, scale=None):
-    """Packed self-attention on the fused projection ``qkv [N, 3*heads*d]`` (columns = [q | k | v])."""
-    return _attn_dispatch(qkv, None, cu, cu, heads, max_len, max_len, causal, dropout_p, training, scale)
+def self_attention(qkv, cu, heads, max_len, causal=False, dropout_p=0.0, training=True, scale=None, bias=None):
+    """Packed self-attention on the fused projection ``qkv [N, 3*heads*d]`` (columns = [q | k | v]).  ``bias``: optional
+    additive term ``[batch, heads, >= max_len, >= max_len]`` on the scaled scores (entry ``[b, h, i, j]`` belongs to query
+    ``i`` and key ``j`` of sequence ``b``); differentiable."""
+    return _attn_dispatch(qkv, None, cu, cu, heads, max_len, max_len, causal, dropout_p, training, scale, bias)
 
 
-def cross_attention(q, kv, cu_q, cu_k, heads, max_q, max_k, dropout_p=0.0, training=True, scale=None):
+def cross_attention(q, kv, cu_q, cu_k, heads, max_q, max_k, dropout_p=0.0, training=True, scale=None, bias=None):
     """Packed encoder-decoder attention: ``q [Nq, heads*d]``, fused ``kv [Nk, 2*heads*d]`` (columns = [k | v])."""
-    return _attn_dispatch(q, kv, cu_q, cu_k, heads, max_q, max_k, False, dropout_p, training, scale)
+    return _attn_dispatch(q, kv, cu_q, cu_k, heads, max_q, max_k, False, dropout_p, training, scale, bias)
 
 
 def attention(q, k, v, cu_q, cu_k, heads, max_q, max_k, causal=False, dropout_p=0.0, training=True, scale=None):

@@ -47,7 +47,21 @@ struct AttnArgs {
   int total_k;            // allocated rows of q / k (>= cu[batch]): rows past the last sequence are cleared by the kernels
   int batch;
   int* status;
+  // optional additive score bias [batch, heads, q, k] in natural-log units (k contiguous; element strides below), added
+  // to S * scale before the softmax; dbias (same layout, zero-initialised by the caller) receives its gradient
+  const float* bias; long bias_sb, bias_sh, bias_sq;
+  float* dbias;
 };
+
+// scores of 32 key columns of one query row -> base-2 domain with the bias added: r = r * scale_log2 + bias * log2 e.
+// `brow` points at the bias of the first of the 32 columns (null: the row is outside the sequence), `ncols` of them exist.
+__device__ __forceinline__ void add_bias32(uint32_t (&r)[32], const float* brow, int ncols, float scale_log2) {
+#pragma unroll
+  for (int j = 0; j < 32; ++j) {
+    const float bv = (brow != nullptr && j < ncols) ? __ldg(brow + j) * 1.4426950408889634f : 0.f;
+    r[j] = __float_as_uint(fmaf(__uint_as_float(r[j]), scale_log2, bv));
+  }
+}
 
 // Clears rows [first_row, end_row) of a bf16 matrix (width a multiple of 8 columns, 16-byte aligned rows) with the
 // whole grid.  Those rows belong to no sequence, so nothing else in the kernel touches them and no ordering is

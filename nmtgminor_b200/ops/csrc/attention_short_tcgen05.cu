@@ -334,19 +334,17 @@ __device__ __forceinline__ uint32_t drop_mask16(const DropRng& rng, unsigned lon
   return m;
 }
 
-// 16 key columns starting at column c0 of query row t: probabilities from the raw scores, dS = P * (dP_dropped - D), both
-// packed to bf16 and stored into the 128-byte-swizzled staging tiles.  A row past the sequence has lse2 = +inf, so its
-// probabilities are 0 without a per-element test.  dS is kept without the softmax scale (applied when dQ and dK leave
-// TMEM).
-__device__ __forceinline__ void bwd_emit16(const uint32_t (&sc)[16], const uint32_t (&dp)[16], uint32_t keep, bool do_drop,
-                                           float keep_scale, float Drow, float scale_log2, float lse2, int c0, int t, int k_len,
-                                           bool causal, uint8_t* sP, uint8_t* sDS) {
+// 16 key columns starting at column c0 of query row t: probabilities from the raw scores and dS = P * (dP_dropped - D),
+// both packed to bf16 (two 16-byte vectors each).  A row past the sequence has lse2 = +inf, so its probabilities are 0
+// without a per-element test.  dS is kept without the softmax scale (applied when dQ and dK leave TMEM).
+__device__ __forceinline__ void bwd_compute16(const uint32_t (&sc)[16], const uint32_t (&dp)[16], uint32_t keep, bool do_drop,
+                                              float keep_scale, float Drow, float scale_log2, float lse2, int c0, int t, int k_len,
+                                              bool causal, uint4 (&vp)[2], uint4 (&vds)[2]) {
   const bool full = !causal && c0 + 16 <= k_len;
 #pragma unroll
   for (int g2 = 0; g2 < 2; ++g2) {
-    uint4 o1, o2v;
-    __nv_bfloat162* a2 = reinterpret_cast<__nv_bfloat162*>(&o1);
-    __nv_bfloat162* b2 = reinterpret_cast<__nv_bfloat162*>(&o2v);
+    __nv_bfloat162* a2 = reinterpret_cast<__nv_bfloat162*>(&vp[g2]);
+    __nv_bfloat162* b2 = reinterpret_cast<__nv_bfloat162*>(&vds[g2]);
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       float pd[2], ds[2];
@@ -369,10 +367,16 @@ __device__ __forceinline__ void bwd_emit16(const uint32_t (&sc)[16], const uint3
       a2[j] = __floats2bfloat162_rn(pd[0], pd[1]);
       b2[j] = __floats2bfloat162_rn(ds[0], ds[1]);
     }
+  }
+}
+// the two vectors of bwd_compute16 into the 128-byte-swizzled staging tiles
+__device__ __forceinline__ void bwd_store16(const uint4 (&vp)[2], const uint4 (&vds)[2], int c0, int t, uint8_t* sP, uint8_t* sDS) {
+#pragma unroll
+  for (int g2 = 0; g2 < 2; ++g2) {
     const int chunk = (c0 >> 3) + g2;     // 16-byte chunk of the row: 8 per 64-key slab
     const uint32_t off = (chunk >> 3) * kTileBytes + sw128_offset(t, chunk & 7);
-    *reinterpret_cast<uint4*>(sP + off) = o1;
-    *reinterpret_cast<uint4*>(sDS + off) = o2v;
+    *reinterpret_cast<uint4*>(sP + off) = vp[g2];
+    *reinterpret_cast<uint4*>(sDS + off) = vds[g2];
   }
 }
 
@@ -601,15 +605,19 @@ attn_bwd_short_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
             if (two) km1 = drop_mask16(rng, row_base + (c + 1) * 32);
           }
           tmem_ld_wait();
+          // all of the arithmetic comes before the wait for the staging tiles: it overlaps the previous item's gradient MMAs
+          uint4 p0[2], e0[2], p1[2], e1[2];
+          bwd_compute16(s0, d0, km0, do_drop, rng.scale, Drow, scale_log2, lse2, c * 32 + half * 16, t, w.k_len, p.causal != 0, p0, e0);
+          if (two)
+            bwd_compute16(s1, d1, km1, do_drop, rng.scale, Drow, scale_log2, lse2, (c + 1) * 32 + half * 16, t, w.k_len,
+                          p.causal != 0, p1, e1);
           if (!may_store) {   // the gradient MMAs of the previous item still read the staging tiles
             ok = __all_sync(0xffffffffu, mbar_wait(pds_free, (it - 1) & 1, abort_word, p.status, kTimeoutSmemEmpty));
             if (!ok) break;
             may_store = true;
           }
-          bwd_emit16(s0, d0, km0, do_drop, rng.scale, Drow, scale_log2, lse2, c * 32 + half * 16, t, w.k_len, p.causal != 0, sP, sDS);
-          if (two)
-            bwd_emit16(s1, d1, km1, do_drop, rng.scale, Drow, scale_log2, lse2, (c + 1) * 32 + half * 16, t, w.k_len, p.causal != 0,
-                       sP, sDS);
+          bwd_store16(p0, e0, c * 32 + half * 16, t, sP, sDS);
+          if (two) bwd_store16(p1, e1, (c + 1) * 32 + half * 16, t, sP, sDS);
         }
       }
       if (ok && !may_store) {
@@ -657,7 +665,13 @@ attn_bwd_short_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
     while (item < num_items && ok) {
       const Item w = nxt;
       item += gridDim.x;
-      if (item < num_items) nxt = get_item(p, item);
+      if (item < num_items) {
+        nxt = get_item(p, item);
+        if (nxt.valid && t < nxt.q_len) {   // the rows this thread reads in the next iteration, on their way to L2 now
+          prefetch_l2(p.o + static_cast<size_t>(nxt.q0 + t) * p.ld_o + nxt.h * kHd);
+          prefetch_l2(p.d_o + static_cast<size_t>(nxt.q0 + t) * p.ld_do + nxt.h * kHd);
+        }
+      }
       if (!w.valid) continue;
       const int s = it & 1;
       float Drow = 0.f, lse2 = kInf;

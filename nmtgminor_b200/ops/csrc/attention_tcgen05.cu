@@ -79,6 +79,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
 
   float m_run = kNegBig, l_run = 0.f;          // running maximum in the base-2 domain, running sum of my 64 columns
   const float scale_log2 = p.scale * 1.4426950408889634f;
+  // with an additive bias the scores are brought into the base-2 domain (and the bias added) right after they are read
+  // from TMEM, so the factor that the softmax below applies is 1
+  const float sl2 = p.bias ? 1.f : scale_log2;
+  const float* bias_row = (p.bias && t < q_rows)
+      ? p.bias + static_cast<long>(b) * p.bias_sb + static_cast<long>(h) * p.bias_sh + static_cast<long>(qt * kTile + t) * p.bias_sq
+      : nullptr;
   float o_acc[32];                             // my warpgroup's 32 of the 64 output columns
 #pragma unroll
   for (int j = 0; j < 32; ++j) o_acc[j] = 0.f;
@@ -130,6 +136,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       uint32_t r[32];
       tmem_ld32(tS + lane_sel + c * 32, r);
       tmem_ld_wait();
+      if (p.bias) add_bias32(r, bias_row ? bias_row + kt * kTile + c * 32 : nullptr, kcols - c * 32, scale_log2);
       if (full) {
         float m0 = __uint_as_float(r[0]), m1 = __uint_as_float(r[1]), m2 = __uint_as_float(r[2]), m3 = __uint_as_float(r[3]);
 #pragma unroll
@@ -152,7 +159,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     sRed[grp * kTile + t] = tile_max;
     __syncthreads();                                            // the other warpgroup's half of the row maximum
     tile_max = fmaxf(tile_max, sRed[(grp ^ 1) * kTile + t]);
-    const float m_new = fmaxf(m_run, tile_max * scale_log2);    // scale > 0: the maximum commutes with the scaling
+    const float m_new = fmaxf(m_run, tile_max * sl2);           // scale > 0: the maximum commutes with the scaling
     const float alpha = ex2_approx(m_run - m_new);
     float row_sum = 0.f;
 #pragma unroll
@@ -161,15 +168,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       uint32_t r[32];
       tmem_ld32(tS + lane_sel + c * 32, r);
       tmem_ld_wait();
+      if (p.bias) add_bias32(r, bias_row ? bias_row + kt * kTile + c * 32 : nullptr, kcols - c * 32, scale_log2);
       float pv[32];
       if (full) {
         float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
 #pragma unroll
         for (int j = 0; j < 32; j += 4) {
-          pv[j] = ex2_approx(fmaf(__uint_as_float(r[j]), scale_log2, -m_new));
-          pv[j + 1] = ex2_approx(fmaf(__uint_as_float(r[j + 1]), scale_log2, -m_new));
-          pv[j + 2] = ex2_approx(fmaf(__uint_as_float(r[j + 2]), scale_log2, -m_new));
-          pv[j + 3] = ex2_approx(fmaf(__uint_as_float(r[j + 3]), scale_log2, -m_new));
+          pv[j] = ex2_approx(fmaf(__uint_as_float(r[j]), sl2, -m_new));
+          pv[j + 1] = ex2_approx(fmaf(__uint_as_float(r[j + 1]), sl2, -m_new));
+          pv[j + 2] = ex2_approx(fmaf(__uint_as_float(r[j + 2]), sl2, -m_new));
+          pv[j + 3] = ex2_approx(fmaf(__uint_as_float(r[j + 3]), sl2, -m_new));
           s0 += pv[j];
           s1 += pv[j + 1];
           s2 += pv[j + 2];
@@ -181,7 +189,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         for (int j = 0; j < 32; ++j) {
           const int col = c * 32 + j;
           const bool valid = col < kcols && (!p.causal || kt * kTile + col <= q_pos);
-          const float e = valid ? ex2_approx(fmaf(__uint_as_float(r[j]), scale_log2, -m_new)) : 0.f;
+          const float e = valid ? ex2_approx(fmaf(__uint_as_float(r[j]), sl2, -m_new)) : 0.f;
           row_sum += e;
           pv[j] = e;
         }
@@ -327,6 +335,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   const uint32_t idesc_dkv = make_idesc_bf16(kTile, kHd, 1, 1);    // dK,dV : MN-major A and B, N = 64
 
   const float scale_log2 = p.scale * 1.4426950408889634f;
+  const float sl2 = p.bias ? 1.f : scale_log2;     // with a bias the scores are converted when they are read (add_bias32)
   const bool do_drop = p.dropout_p > 0.f;
   const DropRng rng(p.seed + ((do_drop && p.seed_dev) ? *p.seed_dev : 0ull),
                     (p.stream_id << 16) | static_cast<unsigned long long>(h), p.dropout_p);
@@ -414,8 +423,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       tmem_ld32(tS + lane_sel + c * 32, rs);
       tmem_ld32(tDP + lane_sel + c * 32, rd);
       tmem_ld_wait();
+      const long bias_off = static_cast<long>(b) * p.bias_sb + static_cast<long>(h) * p.bias_sh +
+                            static_cast<long>(q_pos) * p.bias_sq + kt * kTile + c * 32;
+      if (p.bias) add_bias32(rs, row_ok ? p.bias + bias_off : nullptr, k_rows - c * 32, scale_log2);
       float pd[32], ds[32];
-      if (full && !do_drop) {
+      if (full && !do_drop && !p.bias) {
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
           pd[j] = ex2_approx(fmaf(__uint_as_float(rs[j]), scale_log2, -lse2));
@@ -431,9 +443,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         for (int j = 0; j < 32; ++j) {
           const int col = c * 32 + j;
           const bool valid = row_ok && col < k_rows && (!p.causal || kt * kTile + col <= q_pos);
-          const float pr = valid ? ex2_approx(fmaf(__uint_as_float(rs[j]), scale_log2, -lse2)) : 0.f;
+          const float pr = valid ? ex2_approx(fmaf(__uint_as_float(rs[j]), sl2, -lse2)) : 0.f;
           pd[j] = pr * kf[j];
           ds[j] = pr * (__uint_as_float(rd[j]) * kf[j] - Drow);
+          // the gradient of the bias is dS before the softmax scale; every (query, key) pair is visited by one thread
+          if (p.dbias && valid) p.dbias[bias_off + j] = ds[j];
         }
       }
 #pragma unroll
@@ -660,7 +674,8 @@ const char* nmtg_attn_fwd(const AttnDesc* d, cudaStream_t stream) {
   a.out = reinterpret_cast<__nv_bfloat16*>(d->out); a.ld_out = d->ld_out;
   a.lse = d->lse; a.lse_stride = d->lse_stride;
   a.p_debug = nullptr; a.total_q = d->total_q; a.total_k = d->total_k; a.batch = d->batch; a.status = d->status;
-  if (g_attn_variant == 0 && d->max_q <= kTile && d->max_k <= kTile)
+  a.bias = d->bias; a.bias_sb = d->bias_sb; a.bias_sh = d->bias_sh; a.bias_sq = d->bias_sq; a.dbias = nullptr;
+  if (g_attn_variant == 0 && d->max_q <= kTile && d->max_k <= kTile && !d->bias)
     return launch_attn_fwd_short(tq, tk, tv, a, d->batch * d->num_heads, stream);
   static bool configured = false;
   if (!configured) {
@@ -700,7 +715,8 @@ const char* nmtg_attn_bwd(const AttnDesc* d, cudaStream_t stream) {
   a.dv = reinterpret_cast<__nv_bfloat16*>(d->dv); a.ld_dv = d->ld_dv;
   a.dq_acc = d->dq_acc; a.ld_dqacc = d->ld_dqacc;
   a.total_q = d->total_q; a.total_k = d->total_k; a.batch = d->batch; a.status = d->status;
-  if (g_attn_variant == 0 && d->max_q <= kTile && d->max_k <= kTile)
+  a.bias = d->bias; a.bias_sb = d->bias_sb; a.bias_sh = d->bias_sh; a.bias_sq = d->bias_sq; a.dbias = d->dbias;
+  if (g_attn_variant == 0 && d->max_q <= kTile && d->max_k <= kTile && !d->bias)
     return launch_attn_bwd_short(tq, tk, tv, tdo, a, d->batch * d->num_heads, stream);
   static bool configured = false;
   if (!configured) {

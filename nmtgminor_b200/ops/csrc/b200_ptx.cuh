@@ -79,6 +79,8 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   return false;
 }
 
+__device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
+
 // generic-proxy accesses (any state space) ordered against the async proxy: global memory written with ordinary
 // stores and then read by a TMA load in the same kernel needs this on both sides of the flag that orders them
 __device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }

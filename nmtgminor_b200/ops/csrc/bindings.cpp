@@ -328,22 +328,47 @@ void fill_attn(AttnDesc& d, const Tensor& q, const Tensor& k, const Tensor& v, c
   d.status = status_ptr(q);
 }
 
-void attn_fwd(const Tensor& q, const Tensor& k, const Tensor& v, Tensor& out, Tensor& lse, const Tensor& cu_q,
-              const Tensor& cu_k, int64_t num_heads, int64_t max_q, int64_t max_k, bool causal, double scale,
-              double dropout_p, int64_t seed, int64_t stream_id) {
+// bias / dbias: fp32 [batch, heads, >= max_q, >= max_k], last dimension contiguous
+static void fill_attn_bias(AttnDesc& d, const OptTensor& bias, const OptTensor& dbias, int64_t max_q, int64_t max_k) {
+  if (!bias.has_value()) return;
+  const Tensor& b = *bias;
+  need_f32(b, "bias");
+  TORCH_CHECK(b.is_cuda() && b.dim() == 4 && b.stride(3) == 1, "attention bias must be fp32 [batch, heads, q, k] with contiguous keys");
+  TORCH_CHECK(b.size(0) == d.batch && b.size(1) == d.num_heads && b.size(2) >= max_q && b.size(3) >= max_k,
+              "attention bias is smaller than [batch, heads, max_q, max_k]");
+  d.bias = b.data_ptr<float>();
+  d.bias_sb = b.stride(0); d.bias_sh = b.stride(1); d.bias_sq = b.stride(2);
+  if (dbias.has_value()) {
+    need_f32(*dbias, "dbias");
+    TORCH_CHECK(dbias->sizes() == b.sizes() && dbias->strides() == b.strides(), "dbias must have the layout of bias");
+    d.dbias = dbias->data_ptr<float>();
+  }
+}
+
+void attn_fwd_bias(const Tensor& q, const Tensor& k, const Tensor& v, Tensor& out, Tensor& lse, const Tensor& cu_q,
+                   const Tensor& cu_k, int64_t num_heads, int64_t max_q, int64_t max_k, bool causal, double scale,
+                   double dropout_p, int64_t seed, int64_t stream_id, const OptTensor& bias) {
   c10::cuda::CUDAGuard guard(q.device());
   AttnDesc d = {};
   fill_attn(d, q, k, v, out, lse, cu_q, cu_k, num_heads, max_q, max_k, causal, scale, dropout_p, seed, stream_id);
+  fill_attn_bias(d, bias, c10::nullopt, max_q, max_k);
   ck(nmtg_attn_fwd(&d, cur_stream()));
 }
 
-void attn_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& out, const Tensor& lse, const Tensor& d_out,
-              Tensor& dq, Tensor& dk, Tensor& dv, const OptTensor& dq_acc, const Tensor& cu_q, const Tensor& cu_k,
-              int64_t num_heads, int64_t max_q, int64_t max_k, bool causal, double scale, double dropout_p, int64_t seed,
-              int64_t stream_id) {
+void attn_fwd(const Tensor& q, const Tensor& k, const Tensor& v, Tensor& out, Tensor& lse, const Tensor& cu_q,
+              const Tensor& cu_k, int64_t num_heads, int64_t max_q, int64_t max_k, bool causal, double scale,
+              double dropout_p, int64_t seed, int64_t stream_id) {
+  attn_fwd_bias(q, k, v, out, lse, cu_q, cu_k, num_heads, max_q, max_k, causal, scale, dropout_p, seed, stream_id, c10::nullopt);
+}
+
+void attn_bwd_bias(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& out, const Tensor& lse, const Tensor& d_out,
+                   Tensor& dq, Tensor& dk, Tensor& dv, const OptTensor& dq_acc, const Tensor& cu_q, const Tensor& cu_k,
+                   int64_t num_heads, int64_t max_q, int64_t max_k, bool causal, double scale, double dropout_p, int64_t seed,
+                   int64_t stream_id, const OptTensor& bias, const OptTensor& dbias) {
   c10::cuda::CUDAGuard guard(q.device());
   AttnDesc d = {};
   fill_attn(d, q, k, v, out, lse, cu_q, cu_k, num_heads, max_q, max_k, causal, scale, dropout_p, seed, stream_id);
+  fill_attn_bias(d, bias, dbias, max_q, max_k);
   need_bf16(d_out, "d_out"); need_bf16(dq, "dq"); need_bf16(dk, "dk"); need_bf16(dv, "dv");
   need_rowmajor2d(d_out, "d_out"); need_rowmajor2d(dq, "dq"); need_rowmajor2d(dk, "dk"); need_rowmajor2d(dv, "dv");
   d.d_out = d_out.data_ptr(); d.ld_dout = static_cast<int>(d_out.stride(0));
@@ -360,6 +385,14 @@ void attn_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& o
     d.delta = delta.data_ptr<float>();
   }
   ck(nmtg_attn_bwd(&d, cur_stream()));
+}
+
+void attn_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& out, const Tensor& lse, const Tensor& d_out,
+              Tensor& dq, Tensor& dk, Tensor& dv, const OptTensor& dq_acc, const Tensor& cu_q, const Tensor& cu_k,
+              int64_t num_heads, int64_t max_q, int64_t max_k, bool causal, double scale, double dropout_p, int64_t seed,
+              int64_t stream_id) {
+  attn_bwd_bias(q, k, v, out, lse, d_out, dq, dk, dv, dq_acc, cu_q, cu_k, num_heads, max_q, max_k, causal, scale, dropout_p, seed,
+                stream_id, c10::nullopt, c10::nullopt);
 }
 
 // ---- symmetric (IPC-exportable) memory and the peer-memory optimiser step ---------------------------------
@@ -527,6 +560,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("cast_f32_bf16", &cast_f32_bf16);
   m.def("attn_fwd", &attn_fwd);
   m.def("attn_bwd", &attn_bwd);
+  m.def("attn_fwd_bias", &attn_fwd_bias);
+  m.def("attn_bwd_bias", &attn_bwd_bias);
   m.def("set_attention_variant", [](int64_t v) { nmtg_set_attention_variant(static_cast<int>(v)); });
   m.def("batch_allocate", &batch_allocate);
   m.def("get_seed_tensor", &get_seed_tensor);

@@ -151,6 +151,11 @@ struct AttnDesc {
   float* delta;                       // optional scratch, fp32 [heads, lse_stride]: the backward pass of sequences above 128
                                       // keys fills it with rowsum(dO * O) once instead of recomputing it per key tile
   int* status;
+  // optional additive bias on the scaled scores, fp32 [batch, heads, max_q, max_k] (element strides; keys contiguous),
+  // e.g. relative-position terms; dbias (same strides, zero-initialised) receives its gradient in the backward pass.
+  // Calls with a bias always run the general multi-tile kernels.
+  const float* bias; long bias_sb, bias_sh, bias_sq;
+  float* dbias;
 };
 const char* nmtg_attn_fwd(const AttnDesc* d, cudaStream_t stream);
 const char* nmtg_attn_bwd(const AttnDesc* d, cudaStream_t stream);

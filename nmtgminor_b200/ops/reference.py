@@ -74,8 +74,9 @@ def unpad_packed(xp, cu, total_rows):
     return out
 
 
-def attention(q, k, v, cu_q, cu_k, heads, causal, dropout_p, scale=None, return_probs=False):
-    """softmax(scale * Q K^T + masks) V per sequence and head; rows outside every sequence are zero."""
+def attention(q, k, v, cu_q, cu_k, heads, causal, dropout_p, scale=None, return_probs=False, bias=None):
+    """softmax(scale * Q K^T + bias + masks) V per sequence and head; rows outside every sequence are zero.  ``bias``:
+    optional ``[batch, heads, >= max_q, >= max_k]`` additive term."""
     d = q.shape[1] // heads
     scale = (1.0 / math.sqrt(d)) if scale is None else scale
     lq = (cu_q[1:] - cu_q[:-1]).tolist()
@@ -85,6 +86,8 @@ def attention(q, k, v, cu_q, cu_k, heads, causal, dropout_p, scale=None, return_
     kp, km = pad_packed(k.view(k.shape[0], heads, d), cu_k, mk)
     vp, _ = pad_packed(v.view(v.shape[0], heads, d), cu_k, mk)
     s = torch.einsum("bqhd,bkhd->bhqk", qp.float(), kp.float()) * scale
+    if bias is not None:
+        s = s + bias[:, :, :mq, :mk].float()
     s = s.masked_fill(~km[:, None, None, :], float("-inf"))
     if causal:
         tri = torch.ones(mq, mk, dtype=torch.bool, device=q.device).tril()

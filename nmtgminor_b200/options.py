@@ -196,7 +196,6 @@ UNSUPPORTED_FLAGS = {
     "decoder_late_emb_scale": "late embedding scaling",
     "encoder_early_emb_scale": "early embedding scaling",
     "no_input_scale": "unscaled speech inputs of the relative speech Transformer",
-    "transducer_loss": "transducer training of the translation models (ops/sequence.py has the joint and loss kernels)",
     "ctc_loss_delay": "delayed CTC loss",
     "char_ctc": "character-level CTC targets",
     "cache_dir": "cached encoder outputs",

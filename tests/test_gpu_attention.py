@@ -146,3 +146,70 @@ def test_attention_dropout_is_replayed_in_backward(variant):
     lhs = (o_dir.float() * do.float()).sum().item()
     rhs = (dv * dirv.float()).sum().item()
     assert abs(lhs - rhs) <= 3e-2 * max(1.0, abs(lhs)), (lhs, rhs)
+
+
+@pytest.mark.parametrize("lengths", [[5], [100, 37, 64], [129, 200, 77], [300, 17]])
+@pytest.mark.parametrize("causal", [False, True])
+def test_self_attention_with_additive_bias(lengths, causal):
+    """An fp32 bias [batch, heads, T, T] on the scaled scores (relative-position terms): output, input gradients and the
+    gradient of the bias itself against the fp32 padded statement.  The bias tensor is a padded view (row stride larger
+    than the longest sequence), as models hand it over."""
+    torch.manual_seed(3)
+    heads, W = 4, 256
+    n = sum(lengths)
+    T = max(lengths)
+    cap = (n + 127) // 128 * 128
+    qkv = torch.randn(cap, 3 * W, device=DEV).bfloat16().requires_grad_(True)
+    cu = _cu(lengths)
+    store = torch.randn(len(lengths), heads, T + 3, T + 8, device=DEV)
+    bias = store[:, :, :T, :T].detach().requires_grad_(True)
+    _poison()
+    out = ops.self_attention(qkv, cu, heads, T, causal=causal, dropout_p=0.0, training=True, bias=bias)
+    assert ops.check_status() == 0
+    dout = torch.randn(cap, W, device=DEV).bfloat16()
+    dout[n:] = 0
+    out.backward(dout)
+    assert ops.check_status() == 0
+    q32 = qkv.detach().float().requires_grad_(True)
+    b32 = bias.detach().clone().requires_grad_(True)
+    o_ref = ref.attention(q32[:, :W], q32[:, W:2 * W], q32[:, 2 * W:], cu, cu, heads, causal, 0.0, bias=b32)
+    o_ref.backward(dout.float())
+    assert _err(out[:n], o_ref[:n]) < 2e-2
+    g, gr = qkv.grad, q32.grad
+    assert _err(g[:n, :W], gr[:n, :W]) < 3e-2, "dq"
+    assert _err(g[:n, W:2 * W], gr[:n, W:2 * W]) < 3e-2, "dk"
+    assert _err(g[:n, 2 * W:], gr[:n, 2 * W:]) < 3e-2, "dv"
+    assert _err(bias.grad, b32.grad) < 3e-2, "dbias"
+    # pairs outside the sequences get no gradient
+    for i, L in enumerate(lengths):
+        assert bias.grad[i, :, L:, :].abs().max().item() == 0 if L < T else True
+        assert bias.grad[i, :, :, L:].abs().max().item() == 0 if L < T else True
+
+
+def test_wavlm_and_shaw_attention_run_on_the_fused_path():
+    """The two relative-position attention modules of the speech encoders agree between the kernel path (bias operand)
+    and the PyTorch statement of the same module on the CPU."""
+    from nmtgminor_b200.models.layers import PackedSeqs
+    from nmtgminor_b200.models.speech_encoders import GatedRelPosSelfAttention
+    from nmtgminor_b200.models.w2vbert import ShawRelPosSelfAttention
+    from nmtgminor_b200.parallel.flat import FlatParameterStore
+    lengths = [150, 40]
+    n = sum(lengths)
+    cu = torch.zeros(3, dtype=torch.int32)
+    cu[1:] = torch.tensor(lengths).cumsum(0)
+    for cls in (GatedRelPosSelfAttention, ShawRelPosSelfAttention):
+        torch.manual_seed(1)
+        mod = cls(128, 2, 0.0).eval()
+        x = torch.randn(n, 128)
+        seqs = PackedSeqs(torch.zeros(n, dtype=torch.long), torch.zeros(n, dtype=torch.long), cu, max(lengths))
+        with torch.no_grad():
+            want = mod(x, seqs)
+        launches = ops.LAUNCHES[0]
+        gpu = cls(128, 2, 0.0).eval()
+        gpu.load_state_dict(mod.state_dict())
+        gpu = gpu.to(DEV)
+        FlatParameterStore(gpu, torch.device(DEV))
+        with torch.no_grad():
+            got = gpu(x.to(DEV).bfloat16(), seqs.to(DEV))
+        assert ops.LAUNCHES[0] > launches and ops.check_status() == 0
+        assert _err(got.float().cpu(), want) < 4e-2, cls.__name__

@@ -216,3 +216,79 @@ def test_ctc_head_on_the_auxiliary_target(dicts):
     assert torch.isfinite(out["loss"]).all() and out["n_ctc_targets"] == 3 * B          # the EOS is not a CTC label
     out["loss"].backward()
     assert model.ctc_linear.weight.grad.abs().sum() > 0
+
+
+def test_relative_position_attention_modules_match_the_padded_statement():
+    """WavLM's gated bucket bias and Shaw's relative keys, computed on packed rows and handed to the attention op as an
+    additive bias, against the textbook padded computation."""
+    import math
+    import torch.nn.functional as F
+    from nmtgminor_b200.models.layers import PackedSeqs
+    from nmtgminor_b200.models.speech_encoders import GatedRelPosSelfAttention
+    from nmtgminor_b200.models.w2vbert import ShawRelPosSelfAttention
+    from nmtgminor_b200.ops.reference import pad_packed, unpad_packed
+    torch.manual_seed(0)
+    lengths = [9, 4, 6]
+    n, T, H, h = sum(lengths), max(lengths), 32, 2
+    cu = torch.zeros(4, dtype=torch.int32)
+    cu[1:] = torch.tensor(lengths).cumsum(0)
+    seqs = PackedSeqs(torch.zeros(n, dtype=torch.long), torch.zeros(n, dtype=torch.long), cu, T)
+    x = torch.randn(n, H)
+    wav = GatedRelPosSelfAttention(H, h, 0.0, num_buckets=16, max_distance=20).eval()
+    shaw = ShawRelPosSelfAttention(H, h, 0.0, max_left=4, max_right=2).eval()
+    for mod in (wav, shaw):
+        with torch.no_grad():
+            got = mod(x, seqs)
+            qkv, valid = pad_packed(mod.qkv(x), cu, T)
+            B = qkv.shape[0]
+            q, k, v = (t.view(B, T, h, H // h).transpose(1, 2) for t in qkv.float().split(H, dim=-1))
+            if mod is wav:
+                gate = mod.grep_linear(q).view(B, h, T, 2, 4).sum(-1)
+                ga, gb = torch.sigmoid(gate).chunk(2, dim=-1)
+                bias = (ga * (gb * mod.grep_a - 1.0) + 2.0) * mod.position_bias(T, x.device, ("t", 0))[None].float()
+                scale = (H // h) ** -0.5
+            else:
+                scale = (H // h) ** -0.5
+                by_offset = torch.matmul(q, mod.rel_k.weight.float().t()) * scale
+                bias = by_offset.gather(-1, mod.rel_index(T, x.device)[None, None].expand(B, h, T, T))
+            s = torch.matmul(q, k.transpose(-1, -2)) * scale + bias
+            s = s.masked_fill(~valid[:, None, None, :], float("-inf"))
+            ctx = torch.matmul(torch.softmax(s, -1), v).transpose(1, 2).reshape(B, T, H) * valid.unsqueeze(-1)
+            want = mod.out(unpad_packed(ctx, cu, n), dropout_p=0.0, residual=None)
+        assert torch.allclose(got, want, atol=1e-5), type(mod).__name__
+
+
+def test_transducer_branch_of_the_speech_model():
+    """-transducer_loss: the RNN-T term is computed from encoder frames and decoder states through the joint, weighted
+    and added to the attention loss; blank is the padding id."""
+    from nmtgminor_b200.data.dataset import collate
+    from nmtgminor_b200.ops.sequence import transducer_loss_reference
+    torch.manual_seed(0)
+    d = synthetic_dict(30)
+    opt = default_options(["-model", "speech_transformer", "-encoder_type", "audio", "-input_size", "8", "-model_size", "32",
+                           "-layers", "1", "-n_heads", "1", "-inner_size", "64", "-transducer_loss", "0.5", "-dropout", "0",
+                           "-attn_dropout", "0", "-word_dropout", "0", "-emb_dropout", "0"])
+    m = build_model(opt, {"tgt": d}).train()
+    src = [torch.randn(40, 8), torch.randn(28, 8)]
+    tgt = [torch.tensor([2, 11, 12, 13, 3]), torch.tensor([2, 14, 3])]
+    b = collate(src, tgt, src_type="audio", padded=True, packed=True)
+    out = m(b)
+    assert out["transducer_numel"] == 4
+    total, nmt, rnnt = float(out["loss"].sum()), float(out["nmt_loss"].sum()), float(out["transducer_loss"])
+    assert abs(total - (nmt + 0.5 * rnnt)) < 1e-3 * total
+    # the same term from the pieces
+    with torch.no_grad():
+        context, s = m.encode(b)
+        f = s.pad(context, time_first=False).float()
+        g = out["tgt"].pad(out["hidden_packed"], time_first=False).float()
+        f_len = (s.cu[1:] - s.cu[:-1]).int()
+        joint = torch.relu(f[:, :, None, :] + g[:, None, :, :])
+        logp = torch.log_softmax(m.transducer_linear(joint), -1)
+        labels = torch.tensor([[11, 12, 13], [14, 0, 0]])
+        want = transducer_loss_reference(logp, labels, f_len[:2], torch.tensor([3, 1], dtype=torch.int32), 0).sum()
+    assert abs(float(want) - rnnt) < 1e-3 * rnnt
+    out["loss"].sum().backward()
+    assert m.transducer_linear.weight.grad.abs().sum() > 0
+    m.eval()
+    with torch.no_grad():
+        assert "transducer_loss" not in m(b)
