@@ -34,6 +34,11 @@ def build_model(opt, dicts, remove_pretrain: bool = False, constants=None):
     validate_model_options(opt)
     model = _REGISTRY[name](opt, dicts)
     init_model_parameters(model, opt)
+    if int(getattr(opt, "predict_language", 0) or 0) > 0:
+        if not hasattr(model, "enable_language_prediction"):
+            raise NotImplementedError("-predict_language is built for the speech-to-text models")
+        from .transformer import _n_languages
+        model.enable_language_prediction(_n_languages(dicts))
     if int(getattr(opt, "batch_ensemble", 0) or 0) > 0:
         from ..modules.batch_ensemble import convert_to_batch_ensemble
         convert_to_batch_ensemble(model, int(opt.batch_ensemble))

@@ -300,6 +300,47 @@ class SpeechToTextModel(Seq2SeqBase, _ReferenceNaming):
             self.transducer_linear = nn.Linear(dim, vocab)
             self.transducer_criterion = TransducerLoss(fuse_softmax_backward=False)
 
+    # -predict_language: language-id heads on the encoder frames and on the decoder states, trained with a small weight
+    # next to the translation loss (reference: onmt/train_utils/mp_trainer.py:834-846, 0.01 * (encoder + decoder term);
+    # onmt/models/speech_recognizer/lid_loss.py:13)
+    lid_weight = 0.01
+
+    def enable_language_prediction(self, n_languages: int):
+        self.n_languages = int(n_languages)
+        self.enc_lid = nn.Linear(self.encoder.dim, self.n_languages)
+        self.dec_lid = nn.Linear(self.decoder.embed.weight.shape[1], self.n_languages)
+
+    @staticmethod
+    def _per_row_language(lang, seqs, rows: int):
+        """Per-sentence (or single) language ids -> one id per packed row."""
+        from ..modules.dropout import _sentence_of_row
+        lang = lang.view(-1).to(seqs.cu.device)
+        sent = _sentence_of_row(seqs.cu, rows)
+        return lang[sent] if lang.numel() > 1 else lang.expand(rows)
+
+    def _lid_term(self, batch, context, src, out):
+        tgt = out["tgt"]
+        terms = []
+        for head, states, seqs, key in ((self.enc_lid, context, src, "source_lang"), (self.dec_lid, out["hidden_packed"], tgt, "target_lang")):
+            lang = batch.get(key) if hasattr(batch, "get") else None
+            if lang is None:
+                continue
+            n = int(seqs.cu[-1])
+            logits = head(states[:n].float())
+            labels = self._per_row_language(lang, seqs, states.shape[0])[:n]
+            terms.append(F.cross_entropy(logits, labels.long(), reduction="sum"))
+        if not terms:
+            return None
+        out["lid_loss"] = sum(t.detach() for t in terms)
+        return self.lid_weight * sum(terms)
+
+    @torch.no_grad()
+    def predict_language(self, batch):
+        """Per-sentence language logits ``[B, n_languages]``: the encoder head's frame logits averaged over each utterance."""
+        context, src = self.encode(batch)
+        logp = torch.log_softmax(self.enc_lid(context.float()), -1)
+        return src.pad(logp, time_first=False).sum(1) / (src.cu[1:] - src.cu[:-1]).clamp(min=1).unsqueeze(-1).float()
+
     def _transducer_term(self, context, src, out):
         tgt = out["tgt"]
         f = src.pad(context, time_first=False).float()                            # [B, T, H]
@@ -330,10 +371,13 @@ class SpeechToTextModel(Seq2SeqBase, _ReferenceNaming):
         if not self.training:
             return None
         extra = None
+        if getattr(self, "enc_lid", None) is not None:
+            extra = self._lid_term(batch, context, src, out)
         if self.transducer_weight > 0:
             if getattr(self, "_uncompressed", None) is not None:
                 raise RuntimeError("-transducer_loss and -ctc_compress cannot be combined (the lattice needs every frame)")
-            extra = self.transducer_weight * self._transducer_term(context, src, out)
+            rnnt = self.transducer_weight * self._transducer_term(context, src, out)
+            extra = rnnt if extra is None else extra + rnnt
         if self.ctc_weight <= 0:
             return extra
         ctc = self._ctc_term(batch, context, src, out)

@@ -1,5 +1,6 @@
 """Every model family of the factory builds, trains one step and (where it decodes) runs beam search on CPU."""
 import json
+import math
 
 import pytest
 import torch
@@ -292,3 +293,36 @@ def test_transducer_branch_of_the_speech_model():
     m.eval()
     with torch.no_grad():
         assert "transducer_loss" not in m(b)
+
+
+def test_language_prediction_heads_of_the_speech_model():
+    """-predict_language: frame-level and token-level language heads trained next to the translation loss, and the
+    per-utterance prediction used by the language predictor."""
+    from nmtgminor_b200.data.dataset import collate
+    torch.manual_seed(0)
+    d = synthetic_dict(30)
+    dicts = {"tgt": d, "langs": {"en": 0, "de": 1, "vi": 2}}
+    opt = default_options(["-model", "speech_transformer", "-encoder_type", "audio", "-input_size", "8", "-model_size", "32",
+                           "-layers", "1", "-n_heads", "1", "-inner_size", "64", "-predict_language", "1", "-dropout", "0",
+                           "-attn_dropout", "0", "-word_dropout", "0", "-emb_dropout", "0"])
+    m = build_model(opt, dicts).train()
+    assert m.enc_lid.out_features == 3 and m.dec_lid.out_features == 3
+    src = [torch.randn(40, 8), torch.randn(28, 8)]
+    tgt = [torch.tensor([2, 11, 12, 13, 3]), torch.tensor([2, 14, 3])]
+    b = collate(src, tgt, src_type="audio", padded=True, packed=True, src_lang=torch.tensor([0, 2]), tgt_lang=torch.tensor([1, 1]))
+    out = m(b)
+    assert abs(float(out["loss"].sum()) - float(out["nmt_loss"].sum()) - 0.01 * float(out["lid_loss"])) < 1e-3
+    # every encoder frame of utterance 0 is labelled 0 and of utterance 1 is labelled 2; six decoder positions labelled 1
+    n_frames = int(out["src"].cu[-1])
+    uniform = (n_frames + 6) * math.log(3)
+    assert 0.3 * uniform < float(out["lid_loss"]) < 3 * uniform
+    out["loss"].sum().backward()
+    assert m.enc_lid.weight.grad.abs().sum() > 0 and m.dec_lid.weight.grad.abs().sum() > 0
+    opt_sgd = torch.optim.SGD(list(m.enc_lid.parameters()), lr=0.5)
+    for _ in range(60):
+        opt_sgd.zero_grad()
+        m(b)["loss"].sum().backward()
+        opt_sgd.step()
+    m.eval()
+    pred = m.predict_language(b)
+    assert pred.shape == (2, 3) and pred.argmax(-1).tolist() == [0, 2]
