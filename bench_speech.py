@@ -57,8 +57,9 @@ def build(config: str, tiny: bool, tmp: str, want_model: bool = True):
         opt = default_options(["-model", "whisper", "-dec_config_file", cfg, "-model_size", str(dim), "-n_heads", str(heads),
                                "-inner_size", str(ffn), "-layers", str(layers)] + common)
         n_utt = 16 if not tiny else 2
-        make = lambda seed: synthetic_audio_batch(n_utt, vocab, "feats", n_feats=80, fixed_frames=frames, tgt_min=20 if not tiny else 5,
-                                                  tgt_max=448 if not tiny else 12, seed=seed)
+        # 20-448 target tokens counting the start and end symbols (448 is the decoder's last position)
+        make = lambda seed: synthetic_audio_batch(n_utt, vocab, "feats", n_feats=80, fixed_frames=frames, tgt_min=18 if not tiny else 5,
+                                                  tgt_max=446 if not tiny else 12, seed=seed)
         seconds = lambda b: n_utt * frames / 100.0
         name = "whisper-large-v2 32+32 d1280 h20 ffn5120 vocab51865" if not tiny else "whisper (tiny dry run)"
     elif config == "wav2vec2_mbart50":
