@@ -10,6 +10,7 @@
 #include <cuda_bf16.h>
 #include <stdint.h>
 #include <type_traits>
+#include <cstdlib>
 #include "ops_api.h"
 
 namespace b200 {
@@ -93,8 +94,8 @@ ln_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restri
   }
 }
 
-template <int VPL>
-__global__ void __launch_bounds__(kLnWarps * 32, VPL <= 4 ? 4 : 1)
+template <int VPL, int kWarps>
+__global__ void __launch_bounds__(kWarps * 32, VPL <= 4 ? 16 / kWarps : 1)
 ln_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
               const float* __restrict__ mean, const float* __restrict__ rstd,
               const __nv_bfloat16* __restrict__ gamma, const __nv_bfloat16* __restrict__ dres,
@@ -104,7 +105,7 @@ ln_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restr
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
   const int nvec = hidden >> 3;
-  for (int i = threadIdx.x; i < kLnWarps * 2 * hidden; i += blockDim.x) s_acc[i] = 0.f;
+  for (int i = threadIdx.x; i < kWarps * 2 * hidden; i += blockDim.x) s_acc[i] = 0.f;
   __syncthreads();
   float* wg = s_acc + warp * 2 * hidden;  // lanes own disjoint columns: plain read-modify-write
   float* wb = wg + hidden;
@@ -116,7 +117,7 @@ ln_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restr
 #pragma unroll
     for (int j = 0; j < 8; ++j) ag[i][j] = ab[i][j] = 0.f;
 
-  for (int row = blockIdx.x * kLnWarps + warp; row < rows; row += gridDim.x * kLnWarps) {
+  for (int row = blockIdx.x * kWarps + warp; row < rows; row += gridDim.x * kWarps) {
     const uint4* dyr = reinterpret_cast<const uint4*>(dy + static_cast<size_t>(row) * hidden);
     const uint4* xr = reinterpret_cast<const uint4*>(x + static_cast<size_t>(row) * hidden);
     const uint4* rr = dres ? reinterpret_cast<const uint4*>(dres + static_cast<size_t>(row) * hidden) : nullptr;
@@ -210,7 +211,7 @@ ln_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restr
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
     float g = 0.f, b = 0.f;
 #pragma unroll
-    for (int w = 0; w < kLnWarps; ++w) {
+    for (int w = 0; w < kWarps; ++w) {
       g += s_acc[w * 2 * hidden + i];
       b += s_acc[w * 2 * hidden + hidden + i];
     }
@@ -253,31 +254,43 @@ const char* nmtg_layernorm_fwd(const void* x, const void* gamma, const void* bet
   });
 }
 
-const char* nmtg_layernorm_bwd(const void* dy, const void* x, const float* mean, const float* rstd, const void* gamma,
-                               const void* dres, void* dx, float* dgamma, float* dbeta, int rows, int hidden,
-                               cudaStream_t stream) {
-  if (rows <= 0) return nullptr;
-  if (hidden % 8) return "layernorm: hidden size must be a multiple of 8";
-  int grid = (rows + kLnWarps - 1) / kLnWarps;
-  const size_t smem = kLnWarps * 2 * static_cast<size_t>(hidden) * sizeof(float);
+template <int kWarps>
+static const char* launch_ln_bwd(const void* dy, const void* x, const float* mean, const float* rstd, const void* gamma,
+                                 const void* dres, void* dx, float* dgamma, float* dbeta, int rows, int hidden,
+                                 cudaStream_t stream) {
+  int grid = (rows + kWarps - 1) / kWarps;
+  const size_t smem = kWarps * 2 * static_cast<size_t>(hidden) * sizeof(float);
   return dispatch_vpl(hidden, [&](auto vpl) -> const char* {
-    auto kern = ln_bwd_kernel<decltype(vpl)::value>;
+    auto kern = ln_bwd_kernel<decltype(vpl)::value, kWarps>;
     if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     // exactly one wave of resident CTAs: a partial second wave would leave most SMs idle while it runs
     static int resident[16] = {0};
     int& occ = resident[decltype(vpl)::value];
     if (occ == 0) {
       int n = 0;
-      if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, kLnWarps * 32, smem) != cudaSuccess || n < 1) n = 1;
+      if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, kWarps * 32, smem) != cudaSuccess || n < 1) n = 1;
       occ = n;
     }
     const int cap = num_sms() * occ;
     if (grid > cap) grid = cap;
-    kern<<<grid, kLnWarps * 32, smem, stream>>>(
+    kern<<<grid, kWarps * 32, smem, stream>>>(
         reinterpret_cast<const __nv_bfloat16*>(dy), reinterpret_cast<const __nv_bfloat16*>(x), mean, rstd,
         reinterpret_cast<const __nv_bfloat16*>(gamma), reinterpret_cast<const __nv_bfloat16*>(dres),
         reinterpret_cast<__nv_bfloat16*>(dx), dgamma, dbeta, rows, hidden);
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? nullptr : cudaGetErrorString(e);
   });
+}
+
+const char* nmtg_layernorm_bwd(const void* dy, const void* x, const float* mean, const float* rstd, const void* gamma,
+                               const void* dres, void* dx, float* dgamma, float* dbeta, int rows, int hidden,
+                               cudaStream_t stream) {
+  if (rows <= 0) return nullptr;
+  if (hidden % 8) return "layernorm: hidden size must be a multiple of 8";
+  // Eight warps per CTA once there are enough rows: half as many CTAs end with their 2 * hidden atomics on the affine
+  // gradients, the same number of warps per SM is resident (NMTG_LN_BWD_WARPS=4 restores the narrow CTAs for comparison)
+  static const int forced = [] { const char* e = getenv("NMTG_LN_BWD_WARPS"); return e ? atoi(e) : 0; }();
+  const bool wide = forced ? forced == 8 : rows >= 2048;
+  return wide ? launch_ln_bwd<8>(dy, x, mean, rstd, gamma, dres, dx, dgamma, dbeta, rows, hidden, stream)
+              : launch_ln_bwd<4>(dy, x, mean, rstd, gamma, dres, dx, dgamma, dbeta, rows, hidden, stream);
 }
