@@ -21,13 +21,17 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from .. import ops
+from .attention import (SDPA, AttentionWeightStoreHook, ModuleList, NaiveSDPA, RelativePositionalEncoding, RelativePositionSDPA,
+                        ShawRelativePositionSDPA, TorchSDPA, create_default_sdpa, default_sdpa_factory, set_default_sdpa_factory)
 
 __all__ = ["TransformerNormOrder", "StandardEmbedding", "Linear", "TiedProjection", "StandardLayerNorm", "RMSNorm",
            "SinusoidalPositionEncoder", "LearnedPositionEncoder", "RotaryEncoder", "CausalAttentionMaskFactory",
            "ALiBiMaskFactory", "StandardMultiheadAttention", "StandardFeedForwardNetwork", "GLUFeedForwardNetwork",
            "TransformerEmbeddingFrontend", "StandardTransformerEncoderLayer", "StandardTransformerEncoder",
            "StandardTransformerDecoderLayer", "StandardTransformerDecoder", "TransformerModel", "TransformerDecoderModel",
-           "IncrementalState", "padding_mask_from_lengths"]
+           "IncrementalState", "padding_mask_from_lengths", "SDPA", "TorchSDPA", "NaiveSDPA", "RelativePositionSDPA",
+           "RelativePositionalEncoding", "ShawRelativePositionSDPA", "AttentionWeightStoreHook", "ModuleList",
+           "set_default_sdpa_factory", "create_default_sdpa", "default_sdpa_factory"]
 
 
 class TransformerNormOrder(Enum):
@@ -191,8 +195,11 @@ class StandardMultiheadAttention(nn.Module):
     values are appended to ``state['k'] / state['v']`` (self-attention) or computed once (``static_kv``)."""
 
     def __init__(self, model_dim: int, num_heads: int, num_key_value_heads: Optional[int] = None, pos_encoder=None,
-                 bias: bool = True, attn_dropout_p: float = 0.0, static_kv: bool = False):
+                 bias: bool = True, attn_dropout_p: float = 0.0, static_kv: bool = False, sdpa=None):
         super().__init__()
+        from .attention import create_default_sdpa
+        self.sdpa = sdpa if sdpa is not None else create_default_sdpa(attn_dropout_p=attn_dropout_p)
+        self._attn_weight_hooks = {}
         self.num_heads = num_heads
         self.num_kv_heads = num_key_value_heads or num_heads
         assert num_heads % self.num_kv_heads == 0 and model_dim % num_heads == 0
@@ -208,6 +215,18 @@ class StandardMultiheadAttention(nn.Module):
     def _split(self, x, heads):
         B, T, _ = x.shape
         return x.view(B, T, heads, self.head_dim).transpose(1, 2)
+
+    def register_attn_weight_hook(self, hook):
+        """``hook(module, attn, attn_weights)`` runs after every forward pass; returns a handle with ``remove()``.  With a
+        hook registered the attention weights are materialised (the fused PyTorch attention does not return them)."""
+        key = id(hook)
+        self._attn_weight_hooks[key] = hook
+        owner = self
+
+        class _Handle:
+            def remove(self_inner):
+                owner._attn_weight_hooks.pop(key, None)
+        return _Handle()
 
     def forward(self, x, keys=None, values=None, key_padding_mask=None, attn_mask=None, state: Optional[dict] = None):
         keys = x if keys is None else keys
@@ -239,8 +258,9 @@ class StandardMultiheadAttention(nn.Module):
         if key_padding_mask is not None:
             pad = torch.zeros(key_padding_mask.shape, dtype=q.dtype, device=q.device).masked_fill(key_padding_mask, float("-inf"))
             mask = pad[:, None, None, :] if mask is None else mask + pad[:, None, None, :]
-        p = self.attn_dropout_p if self.training else 0.0
-        out = F.scaled_dot_product_attention(q, k, v, attn_mask=mask, dropout_p=p)
+        out, weights = self.sdpa(q, k, v, mask, needs_weights=bool(self._attn_weight_hooks))
+        for hook in list(self._attn_weight_hooks.values()):
+            hook(self, out, weights)
         return self.output_proj(out.transpose(1, 2).reshape(x.shape[0], x.shape[1], -1))
 
 

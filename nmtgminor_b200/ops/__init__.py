@@ -516,7 +516,9 @@ class _AttnBiasFn(torch.autograd.Function):
             q, k, v = a, b[:, :W], b[:, W:]
             dq, dk, dv = da, db[:, :W], db[:, W:]
         dq_acc = torch.zeros((q.shape[0], W), dtype=torch.float32, device=q.device) if max_k > 128 else None
-        dbias = torch.zeros_like(bias) if ctx.needs_input_grad[2] else None      # pairs outside the sequences stay zero
+        # same strides as the bias (it may be a padded view); pairs outside the sequences stay zero
+        dbias = (torch.empty_strided(bias.shape, bias.stride(), dtype=bias.dtype, device=bias.device).zero_()
+                 if ctx.needs_input_grad[2] else None)
         ext().attn_bwd_bias(q, k, v, out, lse, d_out.contiguous(), dq, dk, dv, dq_acc, cu_q, cu_k, heads, max_q, max_k, causal,
                             scale, p, seed, sid, bias, dbias)
         LAUNCHES[0] += 1

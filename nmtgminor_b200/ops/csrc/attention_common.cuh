@@ -112,4 +112,79 @@ __device__ __forceinline__ void apply_dropout32(const DropRng& rng, unsigned lon
   }
 }
 
+// ---------------------------------------------------------------------------------------------------
+// Backward arithmetic on 16 key columns of one query row (shared by the single-tile and the multi-tile kernels).  Working
+// on 16 columns at a time keeps few values live per thread, which is what lets the compiler interleave independent
+// elements: holding whole 32- or 64-column chunks of S, dP, P and dS at once made these loops latency-bound.
+// ---------------------------------------------------------------------------------------------------
+// bit j = element (base + j) is kept; base a multiple of 4
+__device__ __forceinline__ uint32_t drop_mask16(const DropRng& rng, unsigned long long base) {
+  uint32_t m = 0;
+#pragma unroll
+  for (int g = 0; g < 4; ++g) {
+    const uint32_t w = rng.word((base >> 2) + g);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) m |= (rng.keep(w, j) ? 1u : 0u) << (g * 4 + j);
+  }
+  return m;
+}
+
+// Probabilities from the raw scores (P = 2^(sc * sl2 - lse2); sl2 = 1 when the scores were converted already) and
+// dS = P * (dP_dropped - D), packed to bf16 (two 16-byte vectors each).  c0: first column inside the key tile (columns
+// >= k_lim do not exist); causal: key position kpos0 + j must not exceed q_pos.  A row past the sequence has lse2 = +inf,
+// so its probabilities are 0 without a per-element test.  dS is kept without the softmax scale (applied when dQ and dK
+// leave TMEM).  ds_out (optional): the 16 fp32 dS values of the existing pairs, for the gradient of an additive bias.
+__device__ __forceinline__ void bwd_compute16(const uint32_t (&sc)[16], const uint32_t (&dp)[16], uint32_t keep, bool do_drop,
+                                              float keep_scale, float Drow, float sl2, float lse2, int c0, int k_lim,
+                                              bool causal, int kpos0, int q_pos, uint4 (&vp)[2], uint4 (&vds)[2],
+                                              float* ds_out = nullptr) {
+  const bool full = !causal && c0 + 16 <= k_lim;
+#pragma unroll
+  for (int g2 = 0; g2 < 2; ++g2) {
+    __nv_bfloat162* a2 = reinterpret_cast<__nv_bfloat162*>(&vp[g2]);
+    __nv_bfloat162* b2 = reinterpret_cast<__nv_bfloat162*>(&vds[g2]);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float pd[2], ds[2];
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int idx = g2 * 8 + 2 * j + e;
+        const bool valid = full || (c0 + idx < k_lim && (!causal || kpos0 + idx <= q_pos));
+        const float prob = valid ? ex2_approx(fmaf(__uint_as_float(sc[idx]), sl2, -lse2)) : 0.f;
+        const float d = __uint_as_float(dp[idx]);
+        if (do_drop) {
+          const float kf = ((keep >> idx) & 1u) ? keep_scale : 0.f;
+          pd[e] = prob * kf;
+          ds[e] = prob * fmaf(d, kf, -Drow);
+        } else {
+          pd[e] = prob;
+          ds[e] = prob * (d - Drow);
+        }
+        if (ds_out != nullptr && valid) ds_out[idx] = ds[e];
+      }
+      a2[j] = __floats2bfloat162_rn(pd[0], pd[1]);
+      b2[j] = __floats2bfloat162_rn(ds[0], ds[1]);
+    }
+  }
+}
+// the two vectors of bwd_compute16 into the 128-byte-swizzled staging tiles (row t, columns c0 .. c0 + 15 of the tile)
+__device__ __forceinline__ void bwd_store16(const uint4 (&vp)[2], const uint4 (&vds)[2], int c0, int t, uint8_t* sP, uint8_t* sDS) {
+#pragma unroll
+  for (int g2 = 0; g2 < 2; ++g2) {
+    const int chunk = (c0 >> 3) + g2;     // 16-byte chunk of the row: 8 per 64-key slab
+    const uint32_t off = (chunk >> 3) * kTileBytes + sw128_offset(t, chunk & 7);
+    *reinterpret_cast<uint4*>(sP + off) = vp[g2];
+    *reinterpret_cast<uint4*>(sDS + off) = vds[g2];
+  }
+}
+
+// scores of 16 key columns -> base-2 domain with an additive bias: r = r * scale_log2 + bias * log2 e
+__device__ __forceinline__ void add_bias16(uint32_t (&r)[16], const float* brow, int ncols, float scale_log2) {
+#pragma unroll
+  for (int j = 0; j < 16; ++j) {
+    const float bv = (brow != nullptr && j < ncols) ? __ldg(brow + j) * 1.4426950408889634f : 0.f;
+    r[j] = __float_as_uint(fmaf(__uint_as_float(r[j]), scale_log2, bv));
+  }
+}
+
 }  // namespace b200

@@ -322,64 +322,6 @@ constexpr int kBwdRowBytes = 2 * 2 * kTile * 4; // D and log-sum-exp of two item
 constexpr int kBwdShortSmem = kBwdSlots * kBwdSlotBytes + 2 * kPBytes + kBwdRowBytes + 256 + 1024;
 constexpr uint32_t kBwdIssuePolls = 1u << 22;   // polls of the MMA warp without progress before it gives up
 
-// bit j = element (base + j) is kept; base a multiple of 4
-__device__ __forceinline__ uint32_t drop_mask16(const DropRng& rng, unsigned long long base) {
-  uint32_t m = 0;
-#pragma unroll
-  for (int g = 0; g < 4; ++g) {
-    const uint32_t w = rng.word((base >> 2) + g);
-#pragma unroll
-    for (int j = 0; j < 4; ++j) m |= (rng.keep(w, j) ? 1u : 0u) << (g * 4 + j);
-  }
-  return m;
-}
-
-// 16 key columns starting at column c0 of query row t: probabilities from the raw scores and dS = P * (dP_dropped - D),
-// both packed to bf16 (two 16-byte vectors each).  A row past the sequence has lse2 = +inf, so its probabilities are 0
-// without a per-element test.  dS is kept without the softmax scale (applied when dQ and dK leave TMEM).
-__device__ __forceinline__ void bwd_compute16(const uint32_t (&sc)[16], const uint32_t (&dp)[16], uint32_t keep, bool do_drop,
-                                              float keep_scale, float Drow, float scale_log2, float lse2, int c0, int t, int k_len,
-                                              bool causal, uint4 (&vp)[2], uint4 (&vds)[2]) {
-  const bool full = !causal && c0 + 16 <= k_len;
-#pragma unroll
-  for (int g2 = 0; g2 < 2; ++g2) {
-    __nv_bfloat162* a2 = reinterpret_cast<__nv_bfloat162*>(&vp[g2]);
-    __nv_bfloat162* b2 = reinterpret_cast<__nv_bfloat162*>(&vds[g2]);
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      float pd[2], ds[2];
-#pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        const int idx = g2 * 8 + 2 * j + e;
-        const int col = c0 + idx;
-        const bool valid = full || (col < k_len && (!causal || col <= t));
-        const float prob = valid ? ex2_approx(fmaf(__uint_as_float(sc[idx]), scale_log2, -lse2)) : 0.f;
-        const float d = __uint_as_float(dp[idx]);
-        if (do_drop) {
-          const float kf = ((keep >> idx) & 1u) ? keep_scale : 0.f;
-          pd[e] = prob * kf;
-          ds[e] = prob * fmaf(d, kf, -Drow);
-        } else {
-          pd[e] = prob;
-          ds[e] = prob * (d - Drow);
-        }
-      }
-      a2[j] = __floats2bfloat162_rn(pd[0], pd[1]);
-      b2[j] = __floats2bfloat162_rn(ds[0], ds[1]);
-    }
-  }
-}
-// the two vectors of bwd_compute16 into the 128-byte-swizzled staging tiles
-__device__ __forceinline__ void bwd_store16(const uint4 (&vp)[2], const uint4 (&vds)[2], int c0, int t, uint8_t* sP, uint8_t* sDS) {
-#pragma unroll
-  for (int g2 = 0; g2 < 2; ++g2) {
-    const int chunk = (c0 >> 3) + g2;     // 16-byte chunk of the row: 8 per 64-key slab
-    const uint32_t off = (chunk >> 3) * kTileBytes + sw128_offset(t, chunk & 7);
-    *reinterpret_cast<uint4*>(sP + off) = vp[g2];
-    *reinterpret_cast<uint4*>(sDS + off) = vds[g2];
-  }
-}
-
 // One gradient row (64 fp32 accumulator columns of this thread's TMEM lane) scaled, packed to bf16 and stored.
 __device__ __forceinline__ void bwd_store_row(uint32_t taddr, __nv_bfloat16* drow, float osc, bool store) {
   uint32_t r0[32], r1[32];
@@ -607,10 +549,11 @@ attn_bwd_short_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
           tmem_ld_wait();
           // all of the arithmetic comes before the wait for the staging tiles: it overlaps the previous item's gradient MMAs
           uint4 p0[2], e0[2], p1[2], e1[2];
-          bwd_compute16(s0, d0, km0, do_drop, rng.scale, Drow, scale_log2, lse2, c * 32 + half * 16, t, w.k_len, p.causal != 0, p0, e0);
+          bwd_compute16(s0, d0, km0, do_drop, rng.scale, Drow, scale_log2, lse2, c * 32 + half * 16, w.k_len, p.causal != 0,
+                        c * 32 + half * 16, t, p0, e0);
           if (two)
-            bwd_compute16(s1, d1, km1, do_drop, rng.scale, Drow, scale_log2, lse2, (c + 1) * 32 + half * 16, t, w.k_len,
-                          p.causal != 0, p1, e1);
+            bwd_compute16(s1, d1, km1, do_drop, rng.scale, Drow, scale_log2, lse2, (c + 1) * 32 + half * 16, w.k_len,
+                          p.causal != 0, (c + 1) * 32 + half * 16, t, p1, e1);
           if (!may_store) {   // the gradient MMAs of the previous item still read the staging tiles
             ok = __all_sync(0xffffffffu, mbar_wait(pds_free, (it - 1) & 1, abort_word, p.status, kTimeoutSmemEmpty));
             if (!ok) break;

@@ -29,6 +29,7 @@ namespace b200 {
 // ---------------------------------------------------------------------------------------------------
 // 256 threads: two warpgroups own the same 128 query rows (TMEM lanes) and split the 128 score columns and the 64 output
 // columns between them, so every scheduler has four warps (two CTAs per SM) to hide TMEM loads and exponentials behind.
+template <bool kBias>
 __global__ void __launch_bounds__(256, 2)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                 const __grid_constant__ CUtensorMap tmap_v, const AttnArgs p) {
@@ -79,10 +80,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
 
   float m_run = kNegBig, l_run = 0.f;          // running maximum in the base-2 domain, running sum of my 64 columns
   const float scale_log2 = p.scale * 1.4426950408889634f;
-  // with an additive bias the scores are brought into the base-2 domain (and the bias added) right after they are read
-  // from TMEM, so the factor that the softmax below applies is 1
-  const float sl2 = p.bias ? 1.f : scale_log2;
-  const float* bias_row = (p.bias && t < q_rows)
+  // with an additive bias (kBias) the scores are brought into the base-2 domain, and the bias added, right after they are
+  // read from TMEM, so the factor that the softmax below applies is 1
+  const float sl2 = kBias ? 1.f : scale_log2;
+  const float* bias_row = (kBias && t < q_rows)
       ? p.bias + static_cast<long>(b) * p.bias_sb + static_cast<long>(h) * p.bias_sh + static_cast<long>(qt * kTile + t) * p.bias_sq
       : nullptr;
   float o_acc[32];                             // my warpgroup's 32 of the 64 output columns
@@ -136,7 +137,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       uint32_t r[32];
       tmem_ld32(tS + lane_sel + c * 32, r);
       tmem_ld_wait();
-      if (p.bias) add_bias32(r, bias_row ? bias_row + kt * kTile + c * 32 : nullptr, kcols - c * 32, scale_log2);
+      if (kBias) add_bias32(r, bias_row ? bias_row + kt * kTile + c * 32 : nullptr, kcols - c * 32, scale_log2);
       if (full) {
         float m0 = __uint_as_float(r[0]), m1 = __uint_as_float(r[1]), m2 = __uint_as_float(r[2]), m3 = __uint_as_float(r[3]);
 #pragma unroll
@@ -168,7 +169,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       uint32_t r[32];
       tmem_ld32(tS + lane_sel + c * 32, r);
       tmem_ld_wait();
-      if (p.bias) add_bias32(r, bias_row ? bias_row + kt * kTile + c * 32 : nullptr, kcols - c * 32, scale_log2);
+      if (kBias) add_bias32(r, bias_row ? bias_row + kt * kTile + c * 32 : nullptr, kcols - c * 32, scale_log2);
       float pv[32];
       if (full) {
         float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
@@ -277,6 +278,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
 // ---------------------------------------------------------------------------------------------------
 // 256 threads: two warpgroups own the same 128 rows (TMEM lanes) and split the columns of every tile between them, so
 // each scheduler has two warps to switch between while the other waits on TMEM loads and exponentials.
+template <bool kBias>
 __global__ void __launch_bounds__(256)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                 const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
@@ -335,7 +337,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   const uint32_t idesc_dkv = make_idesc_bf16(kTile, kHd, 1, 1);    // dK,dV : MN-major A and B, N = 64
 
   const float scale_log2 = p.scale * 1.4426950408889634f;
-  const float sl2 = p.bias ? 1.f : scale_log2;     // with a bias the scores are converted when they are read (add_bias32)
+  const float sl2 = kBias ? 1.f : scale_log2;      // with a bias the scores are converted when they are read (add_bias32)
   const bool do_drop = p.dropout_p > 0.f;
   const DropRng rng(p.seed + ((do_drop && p.seed_dev) ? *p.seed_dev : 0ull),
                     (p.stream_id << 16) | static_cast<unsigned long long>(h), p.dropout_p);
@@ -423,11 +425,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       tmem_ld32(tS + lane_sel + c * 32, rs);
       tmem_ld32(tDP + lane_sel + c * 32, rd);
       tmem_ld_wait();
-      const long bias_off = static_cast<long>(b) * p.bias_sb + static_cast<long>(h) * p.bias_sh +
-                            static_cast<long>(q_pos) * p.bias_sq + kt * kTile + c * 32;
-      if (p.bias) add_bias32(rs, row_ok ? p.bias + bias_off : nullptr, k_rows - c * 32, scale_log2);
+      const long bias_off = kBias ? static_cast<long>(b) * p.bias_sb + static_cast<long>(h) * p.bias_sh +
+                                        static_cast<long>(q_pos) * p.bias_sq + kt * kTile + c * 32
+                                  : 0;
+      if (kBias) add_bias32(rs, row_ok ? p.bias + bias_off : nullptr, k_rows - c * 32, scale_log2);
       float pd[32], ds[32];
-      if (full && !do_drop && !p.bias) {
+      if (full && !do_drop && !kBias) {
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
           pd[j] = ex2_approx(fmaf(__uint_as_float(rs[j]), scale_log2, -lse2));
@@ -447,7 +450,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           pd[j] = pr * kf[j];
           ds[j] = pr * (__uint_as_float(rd[j]) * kf[j] - Drow);
           // the gradient of the bias is dS before the softmax scale; every (query, key) pair is visited by one thread
-          if (p.dbias && valid) p.dbias[bias_off + j] = ds[j];
+          if (kBias && p.dbias && valid) p.dbias[bias_off + j] = ds[j];
         }
       }
 #pragma unroll
@@ -679,12 +682,14 @@ const char* nmtg_attn_fwd(const AttnDesc* d, cudaStream_t stream) {
     return launch_attn_fwd_short(tq, tk, tv, a, d->batch * d->num_heads, stream);
   static bool configured = false;
   if (!configured) {
-    cudaError_t ce = cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kFwdSmem);
+    cudaError_t ce = cudaFuncSetAttribute(attn_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kFwdSmem);
+    if (ce == cudaSuccess) ce = cudaFuncSetAttribute(attn_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kFwdSmem);
     if (ce != cudaSuccess) return cudaGetErrorString(ce);
     configured = true;
   }
   dim3 grid((d->max_q + kTile - 1) / kTile, d->num_heads, d->batch);
-  attn_fwd_kernel<<<grid, 256, kFwdSmem, stream>>>(tq, tk, tv, a);
+  if (d->bias) attn_fwd_kernel<true><<<grid, 256, kFwdSmem, stream>>>(tq, tk, tv, a);
+  else attn_fwd_kernel<false><<<grid, 256, kFwdSmem, stream>>>(tq, tk, tv, a);
   cudaError_t ce = cudaGetLastError();
   return ce == cudaSuccess ? nullptr : cudaGetErrorString(ce);
 }
@@ -720,7 +725,8 @@ const char* nmtg_attn_bwd(const AttnDesc* d, cudaStream_t stream) {
     return launch_attn_bwd_short(tq, tk, tv, tdo, a, d->batch * d->num_heads, stream);
   static bool configured = false;
   if (!configured) {
-    cudaError_t ce = cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kBwdSmem);
+    cudaError_t ce = cudaFuncSetAttribute(attn_bwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBwdSmem);
+    if (ce == cudaSuccess) ce = cudaFuncSetAttribute(attn_bwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBwdSmem);
     if (ce != cudaSuccess) return cudaGetErrorString(ce);
     configured = true;
   }
@@ -736,7 +742,8 @@ const char* nmtg_attn_bwd(const AttnDesc* d, cudaStream_t stream) {
       cached_tmap_f32(&tdq, d->dq_acc, d->total_q, width, d->ld_dqacc, kTile, 32))
     a.dq_tma = 1;
   dim3 grid((d->max_k + kTile - 1) / kTile, d->num_heads, d->batch);
-  attn_bwd_kernel<<<grid, 256, kBwdSmem, stream>>>(tq, tk, tv, tdo, tdq, a);
+  if (d->bias) attn_bwd_kernel<true><<<grid, 256, kBwdSmem, stream>>>(tq, tk, tv, tdo, tdq, a);
+  else attn_bwd_kernel<false><<<grid, 256, kBwdSmem, stream>>>(tq, tk, tv, tdo, tdq, a);
   cudaError_t ce = cudaGetLastError();
   if (ce != cudaSuccess) return cudaGetErrorString(ce);
   if (d->max_k > kTile) {
@@ -829,14 +836,14 @@ extern "C" int nmtg_attn_bwd_noalloc(const void* q, int ld_q, const void* k, int
   a.dq_acc = scratch; a.ld_dqacc = width;
   a.total_q = total_q; a.total_k = total_k; a.batch = batch; a.status = status;
   if (!g_attn_noalloc_smem_set[dev]) {   // once per device, like the address look-up above
-    ce = cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kBwdSmem);
+    ce = cudaFuncSetAttribute(attn_bwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBwdSmem);
     if (ce != cudaSuccess) return noalloc_fail(3, cudaGetErrorString(ce), err, err_len);
     g_attn_noalloc_smem_set[dev] = true;
   }
   CUtensorMap tdq = tq;       // placeholder when no accumulation buffer is needed
   a.dq_tma = (needs_buffer && make_tmap_2d_nobind(&tdq, scratch, total_q, width, width, kTile, 32, true)) ? 1 : 0;
   dim3 grid((max_k + kTile - 1) / kTile, num_heads, batch);
-  attn_bwd_kernel<<<grid, 256, kBwdSmem, stream>>>(tq, tk, tv, tdo, tdq, a);
+  attn_bwd_kernel<false><<<grid, 256, kBwdSmem, stream>>>(tq, tk, tv, tdo, tdq, a);
   ce = cudaGetLastError();
   if (ce != cudaSuccess) return noalloc_fail(3, cudaGetErrorString(ce), err, err_len);
   if (needs_buffer) {
