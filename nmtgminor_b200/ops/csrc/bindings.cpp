@@ -535,6 +535,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         pybind11::arg("allow_split_k"), pybind11::arg("split_k"), pybind11::arg("force_bn"), pybind11::arg("mask") = pybind11::none(),
         pybind11::arg("colsum") = pybind11::none(), pybind11::arg("gather") = pybind11::none());
   m.def("set_gemm_variant", [](int64_t v) { nmtg_set_gemm_variant(static_cast<int>(v)); });
+  m.def("set_sm_reserve", [](int64_t n) { nmtg_set_sm_reserve(static_cast<int>(n)); });
   m.def("set_attn_bwd_ablation", [](int64_t v) { nmtg_set_attn_bwd_ablation(static_cast<int>(v)); });
   m.def("set_gemm_trace", [](const OptTensor& buf) {
     if (buf.has_value()) {

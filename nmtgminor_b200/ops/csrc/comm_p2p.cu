@@ -73,8 +73,15 @@ __device__ __forceinline__ void reduce_elements(const NmtgPeerTable& t, float* _
 // 128-thread CTAs at about 40 registers (5 K of the SM's 64 K): small enough to share an SM with a resident GEMM CTA
 // (320 threads at up to 168 registers = 54 K, ~200 KB of shared memory), so the reduction runs beside the backward
 // pass instead of waiting for an SM to drain.
+// The wide form (512 threads, launched with a shared-memory request that no SM holding a GEMM or attention CTA can
+// satisfy) is for SMs set aside for communication (nmtg_set_sm_reserve): a few such CTAs keep enough peer loads in flight
+// to finish a layer's reduction long before the backward pass ends, without sharing an SM with the statically
+// scheduled persistent kernels, which any co-resident work slows down as a whole.
 constexpr int kReduceThreads = 128;
-__global__ void __launch_bounds__(kReduceThreads)
+constexpr int kReduceWideThreads = 512;
+constexpr int kReduceWideSmem = 96 * 1024;
+template <int kThreads>
+__global__ void __launch_bounds__(kThreads)
 reduce_unit_kernel(const NmtgPeerTable t, int row, float* __restrict__ reduced, long g0, long len, int accumulate,
                    long zero_begin, long zero_len, int* __restrict__ counter, const int* __restrict__ epoch_ptr, int* status) {
   const int epoch = *epoch_ptr;
@@ -221,12 +228,27 @@ const char* nmtg_reduce_unit(const NmtgPeerTable* t, int row, float* reduced, lo
     return "reduce_unit: ranges must be multiples of 4 elements";
   if (reinterpret_cast<uintptr_t>(reduced) & 15) return "reduce_unit: unaligned output";
   if (zero_len > 0 && !counter) return "reduce_unit: clearing the unit needs the launch counter";
+  if (ctas < 0) {   // -ctas wide CTAs for the SMs that the compute kernels leave free
+    static bool configured = false;
+    if (!configured) {
+      cudaError_t ce = cudaFuncSetAttribute(reduce_unit_kernel<kReduceWideThreads>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                            kReduceWideSmem);
+      if (ce != cudaSuccess) return cudaGetErrorString(ce);
+      configured = true;
+    }
+    long blocks = (len / 4 + kReduceWideThreads - 1) / kReduceWideThreads;
+    if (blocks > -ctas) blocks = -ctas;
+    if (blocks < 1) blocks = 1;
+    reduce_unit_kernel<kReduceWideThreads><<<static_cast<int>(blocks), kReduceWideThreads, kReduceWideSmem, stream>>>(
+        *t, row, reduced, global_begin, len, accumulate, zero_begin, zero_len, counter, epoch_dev, status);
+    return err_str();
+  }
   long blocks = (len / 4 + kReduceThreads - 1) / kReduceThreads;
   if (ctas < 1) ctas = 64;
   if (blocks > ctas) blocks = ctas;
   if (blocks < 1) blocks = 1;
-  reduce_unit_kernel<<<static_cast<int>(blocks), kReduceThreads, 0, stream>>>(*t, row, reduced, global_begin, len, accumulate, zero_begin,
-                                                                  zero_len, counter, epoch_dev, status);
+  reduce_unit_kernel<kReduceThreads><<<static_cast<int>(blocks), kReduceThreads, 0, stream>>>(
+      *t, row, reduced, global_begin, len, accumulate, zero_begin, zero_len, counter, epoch_dev, status);
   return err_str();
 }
 

@@ -333,14 +333,19 @@ bool cached_tmap_f32(CUtensorMap* out, const void* base, long rows, long cols, l
 static int g_gemm_sm_reserve = 0;
 int gemm_sms();
 static int g_num_sms = 0;
+static int g_sm_reserve = 0;   // SMs that every kernel of this library leaves free (nmtg_set_sm_reserve)
+// Number of SMs that the launchers size their grids for: the device's SMs minus the ones set aside for the
+// communication kernels that run beside the backward pass.
 int num_sms() {
   if (!g_num_sms) {
     int dev = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
   }
-  return g_num_sms;
+  const int n = g_num_sms - g_sm_reserve;
+  return n < 2 ? 2 : n;
 }
+void set_sm_reserve(int n) { g_sm_reserve = n < 0 ? 0 : (n & ~1); }
 
 int gemm_sms() {
   const int n = num_sms() - g_gemm_sm_reserve;
@@ -381,6 +386,7 @@ extern int g_pair_tma_store;
 extern int g_pair_generic_epilogue;
 }
 void nmtg_set_gemm_trace(long long* buf) { g_gemm_trace = buf; }
+void nmtg_set_sm_reserve(int n) { b200::set_sm_reserve(n); }
 
 void nmtg_set_gemm_variant(int v) {
   if (v >= 60 && v < 124) b200::g_gemm_sm_reserve = (v - 60) & ~1;

@@ -59,6 +59,9 @@ struct GemmDesc {
 const char* nmtg_gemm_bf16(const GemmDesc* d, cudaStream_t stream);
 // 0 = automatic (CTA-pair kernel when M > 128), 1 = single-CTA kernel only, 2 = same as 0
 void nmtg_set_gemm_variant(int v);
+// n (even) SMs are left free by every launcher of this library: persistent kernels size their grids for the rest, so that
+// communication kernels placed on the free SMs (nmtg_reduce_unit with a negative CTA count) never share one with them.
+void nmtg_set_sm_reserve(int n);
 // Timing aid for the short-sequence attention backward: bit mask of work to leave out (see the kernel); 0 = everything.
 void nmtg_set_attn_bwd_ablation(int bits);
 // Profiling aid: device buffer of 16 int64 per CTA pair (at least 16 * #SMs / 2 entries) that the CTA-pair GEMM fills with

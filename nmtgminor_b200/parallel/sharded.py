@@ -163,6 +163,13 @@ class UnitShardedStep:
         reserve = int(os.environ.get("NMTG_GEMM_SM_RESERVE", "0"))
         if reserve > 0 and self.overlap and self.world > 1:
             ops.ext().set_gemm_variant(60 + reserve)     # persistent GEMMs leave these SMs to the reductions
+        # NMTG_COMM_SMS = n: n SMs are left free by EVERY kernel of the library and the per-layer reductions run there as n
+        # wide CTAs (they cannot share an SM with a GEMM or attention CTA), so the reduce-scatter proceeds under the backward
+        # pass without slowing the statically scheduled persistent kernels.  The reduction after backward uses the whole GPU.
+        self.comm_sms = int(os.environ.get("NMTG_COMM_SMS", "0")) & ~1
+        if self.comm_sms > 0 and self.overlap and self.world > 1:
+            ops.ext().set_sm_reserve(self.comm_sms)
+            self.reduce_ctas = -self.comm_sms
         self.active = True          # hooks launch reductions only during a backward pass that ends in an update
         self._done = set()          # units reduced in the current backward pass
         self._last = None           # layer unit whose backward pass is running

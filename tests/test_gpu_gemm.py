@@ -211,3 +211,25 @@ def test_gemm_column_sums_in_the_epilogue(M, N, K):
     assert torch.equal(out, ref)
     want = ref.float().sum(0) + 0.25
     assert (gb - want).abs().max().item() <= 2e-3 * max(1.0, want.abs().max().item())
+
+
+def test_sm_reserve_only_changes_the_grid():
+    """SMs set aside for communication kernels: every launcher sizes its grid for the rest; results do not change."""
+    torch.manual_seed(9)
+    a = torch.randn(2048, 512, device=DEV).bfloat16()
+    b = torch.randn(1024, 512, device=DEV).bfloat16()
+    want = torch.empty(2048, 1024, device=DEV, dtype=torch.bfloat16)
+    ops.gemm(a, b, want)
+    try:
+        ops.ext().set_sm_reserve(8)
+        got = torch.empty_like(want)
+        ops.gemm(a, b, got)
+        x = torch.randn(4096, 1024, device=DEV).bfloat16()
+        g = torch.ones(1024, device=DEV).bfloat16()
+        y = ops.ext().layernorm_fwd(x, g, torch.zeros_like(g), 1e-5)[0] if hasattr(ops.ext(), "layernorm_fwd") else None
+    finally:
+        ops.ext().set_sm_reserve(0)
+    _status_ok()
+    assert torch.equal(got, want)
+    if y is not None:
+        assert torch.isfinite(y.float()).all()
