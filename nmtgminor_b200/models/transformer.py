@@ -244,6 +244,8 @@ class DecodingState:
         if reorder_context:
             self.context = self.context.index_select(0, index)
             self.src_pad_mask = self.src_pad_mask.index_select(0, index)
+            if getattr(self, "src_tokens", None) is not None:
+                self.src_tokens = self.src_tokens.index_select(0, index)
         for buf in self.buffers:
             if "k_spare" in buf and buf.get("pos_dev") is not None:
                 H = buf["k"].shape[2]
@@ -315,6 +317,21 @@ class Seq2SeqBase(nn.Module):
                 gs = grad_scale if isinstance(grad_scale, torch.Tensor) else torch.tensor(float(grad_scale), device=loss.device)
                 loss = scale_gradient(loss, gs.to(loss.device))
             out.update(loss=loss, correct=None, row_loss=None)
+        elif compute_loss and getattr(self, "copy_generator", None) is not None:
+            # padded, unfused: the copy distribution needs the [B, T, S] attention of every target position over its source
+            logp = self._copy_log_probs(tgt.pad(hidden, time_first=False), context, src)          # [B, T, V]
+            gold = tgt.pad(labels[:, None].float(), time_first=False).squeeze(-1).long()            # [B, T]
+            valid = gold != self.pad_idx
+            nll = -logp.gather(-1, gold.clamp(min=0)[..., None]).squeeze(-1)
+            eps = self.label_smoothing if self.training else 0.0
+            tok = (1.0 - eps) * nll - eps * logp.mean(-1) if eps > 0 else nll
+            loss = (tok * valid).sum().reshape(1)
+            if grad_scale is not None and torch.is_grad_enabled():
+                from ..ops.reference import scale_gradient
+                gs = grad_scale if isinstance(grad_scale, torch.Tensor) else torch.tensor(float(grad_scale), device=loss.device)
+                loss = scale_gradient(loss, gs.to(loss.device))
+            correct = ((logp.argmax(-1) == gold) & valid).sum().float().reshape(1)
+            out.update(loss=loss, correct=correct, row_loss=None)
         elif compute_loss and getattr(self.generator, "fix_norm", False):
             logits = self.generator(hidden)
             loss, correct, row_loss = ops.cross_entropy(logits if logits.is_contiguous() else logits.contiguous(), labels,
@@ -345,6 +362,14 @@ class Seq2SeqBase(nn.Module):
             out["target_mask"] = batch.get("target_input_selfattn_mask") if hasattr(batch, "get") else None
             out["softmaxed"] = False
         return out
+
+    def _copy_log_probs(self, hidden_bt, context, src):
+        ctx = src.pad(context, time_first=False)                                   # [B, S, H]
+        lengths = (src.cu[1:] - src.cu[:-1]).to(torch.int64)
+        pad = torch.arange(ctx.shape[1], device=ctx.device)[None, :] >= lengths[:, None]
+        toks = src.pad(src.tokens[:, None].float(), time_first=False).squeeze(-1).long()
+        B = hidden_bt.shape[0]
+        return self.copy_generator(hidden_bt, ctx[:B], toks[:B], pad[:B])
 
     def load_encoder_weights(self, pretrained, strict: bool = False):
         """Copy the encoder of another model (a module, or a checkpoint's ``model`` state dict) into this one; used to
@@ -382,6 +407,9 @@ class Seq2SeqBase(nn.Module):
         lengths = (src.cu[1:] - src.cu[:-1]).to(torch.int64)
         pad_mask = torch.arange(ctx_padded.shape[1], device=ctx_padded.device)[None, :] >= lengths[:, None]
         state = DecodingState(ctx_padded, pad_mask, len(self.decoder.layers), beam_size)
+        if getattr(self, "copy_generator", None) is not None:
+            toks = src.pad(src.tokens[:, None].float(), time_first=False).squeeze(-1).long()[:ctx_padded.shape[0]]
+            state.src_tokens = toks.repeat_interleave(beam_size, 0) if beam_size > 1 else toks
         if getattr(self.decoder, "language_embedding", None) is not None and hasattr(batch, "get"):
             tl = batch.get("target_lang")
             if tl is not None:
@@ -405,6 +433,10 @@ class Seq2SeqBase(nn.Module):
         (``logits_only``: raw ``logits`` instead, for the fused log-softmax + top-k beam kernel)."""
         tokens = input_t[:, -1].contiguous()
         hidden = self.decoder.step(tokens, input_t.shape[1] - 1, state)
+        if getattr(self, "copy_generator", None) is not None and getattr(state, "src_tokens", None) is not None:
+            state.position += 1
+            logp = self.copy_generator(hidden[:, None, :], state.context, state.src_tokens, state.src_pad_mask).squeeze(1)
+            return {"log_prob": logp, "logits": logp, "hidden": hidden, "coverage": None}
         logits = self.generator(hidden)
         state.position += 1
         if logits_only:
@@ -464,6 +496,14 @@ class Transformer(Seq2SeqBase):
                                  weight=self.generator.weight, bias=self.generator.bias if self.generator.bias is not None else False)
             self.nce_loss = NCELoss(opt.model_size, tgt_vocab, int(opt.nce_noise), label_smoothing=self.label_smoothing,
                                     padding_idx=self.pad_idx)
+        # -copy_generator: output distribution mixed with a copy distribution over the source words (one shared vocabulary)
+        if getattr(opt, "copy_generator", False):
+            if src_vocab != tgt_vocab:
+                raise ValueError("-copy_generator needs one shared vocabulary (-join_vocab): copied source words are target words")
+            from ..modules.copy_generator import CopyGenerator
+            self.copy_generator = CopyGenerator(opt.model_size, tgt_vocab, weight=self.generator.weight,
+                                                fix_norm=bool(getattr(opt, "fix_norm_output_embedding", False)))
+            self.supports_logits_step = False      # decoding goes through the mixed distribution, not raw logits
         # -reconstruct: a third decoder regenerates the source from the decoder's states
         self.reconstruct = bool(getattr(opt, "reconstruct", False))
         if self.reconstruct:

@@ -155,7 +155,6 @@ UNSUPPORTED_FLAGS = {
     "residual_type": "gated / highway residual connections",
     "extra_context_size": "extra streaming context",
     "no_decoder": "encoder-only sequence models in the translation trainer",
-    "copy_generator": "the copy generator",
     "favor_attention": "FAVOR+ attention inside the main Transformer (models/efficient_attention.py has the stand-alone layer)",
     "lm_checkpoint": "language-model fusion",
     "fusion": "language-model fusion",

@@ -56,9 +56,9 @@ def test_an_unsupported_flag_stops_the_run_and_defaults_do_not():
     opt = default_options([])
     assert unsupported_flags_in(opt) == []
     validate_model_options(opt)
-    opt = default_options(["-copy_generator"])
-    assert [b[0] for b in unsupported_flags_in(opt)] == ["copy_generator"]
-    with pytest.raises(NotImplementedError, match="copy_generator"):
+    opt = default_options(["-weight_norm"])
+    assert [b[0] for b in unsupported_flags_in(opt)] == ["weight_norm"]
+    with pytest.raises(NotImplementedError, match="weight_norm"):
         validate_model_options(opt)
     opt = default_options(["-transducer_loss", "0.5"])
     with pytest.raises(NotImplementedError, match="transducer_loss"):
