@@ -243,7 +243,9 @@ class TrainEngine:
         graph = torch.cuda.CUDAGraph()
         n0 = ops.LAUNCHES[0]
         step_before = self.optim._step
-        with torch.cuda.graph(graph, pool=self._pool):
+        # thread-local capture mode: the data loader's worker / pinning threads keep allocating pinned host memory while
+        # this thread captures, which a global-mode capture treats as an error
+        with torch.cuda.graph(graph, pool=self._pool, capture_error_mode="thread_local"):
             ops.advance_device_seed(self.device.index)
             loss, correct = self._forward_backward(static)
             if self.reducer is not None:
