@@ -355,6 +355,9 @@ class Dataset(torch.utils.data.Dataset):
                                         batch_size_sents, multiplier, max_src_len, max_tgt_len, min_src_len, min_tgt_len,
                                         cleaning, unbalanced, cut_off_size, smallest_batch_size)
         self.num_batches = len(self.batches)
+        # static shapes: ONE sentence capacity for the whole data set (empty trailing sequences cost the attention kernels a
+        # few loads each), so that the shape classes of the training step are (source tokens, target tokens) buckets only
+        self.static_max_batch = bucket_capacity(max([len(b) for b in self.batches] + [1]), per_octave=4, floor=8)
         self.cur_index = 0
         self.batch_order = list(range(self.num_batches))
         if verbose:
@@ -380,7 +383,8 @@ class Dataset(torch.utils.data.Dataset):
         return collate(src, pick(self.tgt), lang(self.src_langs), lang(self.tgt_langs), lang(self.src_atbs), lang(self.tgt_atbs),
                        self.src_pad, self.tgt_pad, self.type, ids, self.padded, self.packed, round_to=self.round_to,
                        create_reverse=self.create_reverse, past_src_data=pick(self.past_src), aux_tgt_data=pick(self.aux_tgt),
-                       static_shapes=self.static_shapes)
+                       static_shapes=self.static_shapes,
+                       max_batch=self.static_max_batch if (self.static_shapes and self.packed and self.type == "text") else None)
 
     __getitem__ = get_batch
 

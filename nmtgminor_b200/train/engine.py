@@ -136,9 +136,12 @@ class TrainEngine:
             self.optim.loss_scaler = self.scaler
         self.use_graph = bool(cuda_graph) and self.on_gpu
         self._graphs = {}                 # shape class -> [graph, static inputs, launches per replay, last use]
+        self._seen = {}                   # shape class -> batches met so far (a class is captured at batch number capture_after)
         self._pool = None
         self._tick = 0
-        self.max_graphs = 24
+        self.max_graphs = 64
+        self.capture_after = 1            # trainers that stream a token-budget data set raise this (rare classes stay eager)
+        self.evict_graphs = True          # False: once the cache is full, further classes run kernel by kernel for good
         self.kernel_launches_per_step = 0
 
     # ---------------------------------------------------------------------------------------------
@@ -280,8 +283,13 @@ class TrainEngine:
         sig = _StaticInputs.signature_of(batch)
         entry = self._graphs.get(sig)
         if entry is None:
+            # a capture costs several eager steps (a second pass over the step's launches plus the instantiation of a
+            # graph of a few hundred nodes): classes that a token-budget data set produces once or twice run eagerly
+            seen = self._seen.get(sig, 0) + 1
+            self._seen[sig] = seen
             out = self._eager_step(batch, True)
-            self._capture(batch, sig)
+            if seen >= self.capture_after and (self.evict_graphs or len(self._graphs) < self.max_graphs):
+                self._capture(batch, sig)
             return out
         graph, static, launches, _ = entry
         entry[3] = self._tick

@@ -71,6 +71,31 @@ def test_engine_trains(graph):
     assert last < first - 0.5, "loss did not go down: %.3f -> %.3f" % (first, last)
 
 
+def test_graph_capture_waits_for_the_third_batch_of_a_class_when_asked():
+    """Trainers that stream a token-budget data set capture a shape class at its third batch: rare classes stay eager."""
+    torch.manual_seed(1)
+    d = synthetic_dict(2000)
+    opt = _opt(["-dropout", "0.1", "-attn_dropout", "0.1"])
+    model = Transformer(opt, {"src": d, "tgt": d})
+    eng = TrainEngine(model, opt, device="cuda", cuda_graph=True)
+    eng.capture_after = 3
+    a, b = [x.pin_memory() for x in token_budget_batches(2000, 5, 40, 1024, 2, seed=5, static=True, padded=False)]
+    sizes = []
+    for batch in (a, a, b, a, a, b, b, b):
+        eng.train_step(batch)
+        sizes.append(len(eng._graphs))
+    same_class = eng._seen.keys().__len__() == 1
+    assert sizes == ([0, 0, 1, 1, 1, 1, 1, 1] if same_class else [0, 0, 0, 1, 1, 1, 2, 2])
+    assert ops.check_status() == 0
+    # a full cache that may not evict leaves new classes to the eager path
+    eng.max_graphs, eng.evict_graphs = len(eng._graphs), False
+    c = token_budget_batches(2000, 5, 40, 2048, 1, seed=9, static=True, padded=False)[0].pin_memory()
+    before = len(eng._graphs)
+    for _ in range(4):
+        eng.train_step(c)
+    assert len(eng._graphs) == before
+
+
 def test_checkpointing_replays_fused_dropout_masks():
     """Recomputed layers must regenerate the dropout masks of the first pass: gradients match the plain run."""
     d = synthetic_dict(2000)
