@@ -9,7 +9,7 @@ Writes a synthetic parallel corpus (sentence lengths uniform in [20, 100], vocab
 ``bench.py`` draws its batches from), binarises it with ``preprocess.py``, trains Transformer-big with the trainer's
 defaults for CUDA (bf16, CUDA graphs per batch shape class, peer-memory data parallelism for N > 1) for ``--updates``
 updates, and reports the median target tokens / s of the trainer's own log windows over the second half of the run (a
-shape class is captured at its third batch, so the first epoch runs mostly kernel by kernel).  Rank 0 prints ONE JSON line.
+shape class is captured into a CUDA graph at its eighth batch, so the first epochs run partly kernel by kernel).  Rank 0 prints ONE JSON line.
 """
 from __future__ import annotations
 

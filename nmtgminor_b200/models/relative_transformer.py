@@ -78,6 +78,9 @@ class RelativeSelfAttention(nn.Module):
             ctx = rel_self_attention(qkv_packed, r.to(torch.bfloat16), self.r_w_bias, self.r_r_bias, seqs.cu, h, T, T - 1, self.causal,
                                      self.attn_dropout, self.training)
             return self.out(ctx, dropout_p=dropout_p, residual=residual)
+        if (memory is None or memory.shape[1] == 0) and (getattr(self, "force_bias_path", False) or (
+                qkv_packed.is_cuda and qkv_packed.dtype == torch.bfloat16 and d == 64)):
+            return self.out(self._attend_with_bias(qkv_packed, seqs), dropout_p=dropout_p, residual=residual)
         qkv = seqs.pad(qkv_packed, time_first=False).float()          # [B, T, 3H]
         B, T, _ = qkv.shape
         q, k, v = qkv[..., :H], qkv[..., H:2 * H], qkv[..., 2 * H:]
@@ -110,6 +113,24 @@ class RelativeSelfAttention(nn.Module):
         from ..ops.reference import unpad_packed
         ctx_packed = unpad_packed(ctx, seqs.cu, x.shape[0])
         return self.out(ctx_packed, dropout_p=dropout_p, residual=residual)
+
+
+    def _attend_with_bias(self, qkv_packed, seqs: PackedSeqs):
+        """Sequences longer than one tile on the tensor-core path: everything of the score that is not ``q . k`` - the
+        content bias ``u . k_j`` and the shifted position term ``(q_i + v) . r_{i-j}`` - is one additive operand
+        ``[B, h, T, T]`` of the packed attention kernels; its gradient comes back from the kernels and flows on to the
+        queries, keys, position projection and both biases through these few PyTorch ops."""
+        H, h, d = self.dim, self.heads, self.hd
+        T = int(seqs.max_len)
+        pad = seqs.pad(qkv_packed[:, :2 * H], time_first=False)                    # [B, T, 2H]
+        B = pad.shape[0]
+        q = pad[..., :H].float().view(B, T, h, d)
+        k = pad[..., H:].float().view(B, T, h, d)
+        r = self.pos(self._positions(T, T, qkv_packed.device).to(qkv_packed.dtype)).float().view(-1, h, d)   # [2T - 1, h, d]
+        bd = rel_shift(torch.einsum("bqhd,lhd->bhql", q + self.r_r_bias.float(), r))[..., :T]
+        uk = torch.einsum("hd,bkhd->bhk", self.r_w_bias.float(), k)[:, :, None, :]
+        bias = (bd + uk) * (d ** -0.5)
+        return ops.self_attention(qkv_packed, seqs.cu, h, T, self.causal, self.attn_dropout, self.training, bias=bias)
 
 
 class RelativeEncoderLayer(nn.Module):

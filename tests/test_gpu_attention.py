@@ -213,3 +213,39 @@ def test_wavlm_and_shaw_attention_run_on_the_fused_path():
             got = gpu(x.to(DEV).bfloat16(), seqs.to(DEV))
         assert ops.LAUNCHES[0] > launches and ops.check_status() == 0
         assert _err(got.float().cpu(), want) < 4e-2, cls.__name__
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_relative_self_attention_long_sequences_use_the_bias_operand(causal):
+    """Transformer-XL style attention over sequences longer than one tile: the position term and the content bias enter the
+    tcgen05 kernels as an additive operand; output and gradients against the fp32 padded statement on CPU."""
+    import copy
+    from nmtgminor_b200.models.layers import PackedSeqs
+    from nmtgminor_b200.models.relative_transformer import RelativeSelfAttention
+    torch.manual_seed(11)
+    H, h = 128, 2
+    m32 = RelativeSelfAttention(H, h, 0.0, causal).eval()
+    with torch.no_grad():
+        m32.r_w_bias.normal_(0, 0.2)
+        m32.r_r_bias.normal_(0, 0.2)
+    lengths = [200, 150, 37]
+    n = sum(lengths)
+    cu = torch.zeros(len(lengths) + 1, dtype=torch.int32)
+    cu[1:] = torch.tensor(lengths).cumsum(0)
+    x32 = (torch.randn(n, H) * 0.5).requires_grad_()
+    seqs_cpu = PackedSeqs(torch.zeros(n, dtype=torch.long), torch.zeros(n, dtype=torch.long), cu, max(lengths))
+    want = m32(x32, seqs_cpu)
+    gw = torch.autograd.grad(want.square().sum(), [x32, m32.r_w_bias, m32.r_r_bias])
+    from nmtgminor_b200.parallel.flat import FlatParameterStore
+    m = copy.deepcopy(m32).to(DEV)
+    FlatParameterStore(m, torch.device(DEV))
+    calls = ops.LAUNCHES[0]
+    x = x32.detach().to(DEV).to(torch.bfloat16).requires_grad_()
+    seqs = PackedSeqs(torch.zeros(n, dtype=torch.long, device=DEV), torch.zeros(n, dtype=torch.long, device=DEV), cu.to(DEV), max(lengths))
+    got = m(x, seqs)
+    gg = torch.autograd.grad(got.float().square().sum(), [x, m.r_w_bias, m.r_r_bias])
+    assert ops.LAUNCHES[0] > calls and ops.check_status() == 0
+    assert (got.float().cpu() - want).abs().max() < 0.06 * max(1.0, float(want.abs().max()))
+    for a, b in zip(gg, gw):
+        scale = max(1.0, float(b.abs().max()))
+        assert (a.float().cpu() - b).abs().max() < 0.08 * scale

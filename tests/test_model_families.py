@@ -326,3 +326,33 @@ def test_language_prediction_heads_of_the_speech_model():
     m.eval()
     pred = m.predict_language(b)
     assert pred.shape == (2, 3) and pred.argmax(-1).tolist() == [0, 2]
+
+
+def test_relative_self_attention_bias_operand_path_matches_padded_path():
+    """Sequences that do not fit the one-tile relative kernel go through the packed attention kernels with the position
+    term and the content bias as one additive operand; on CPU the same routing runs on the PyTorch statement."""
+    import torch
+    from nmtgminor_b200.models.layers import PackedSeqs
+    from nmtgminor_b200.models.relative_transformer import RelativeSelfAttention
+    torch.manual_seed(3)
+    for causal in (False, True):
+        m = RelativeSelfAttention(32, 2, 0.0, causal).eval()
+        with torch.no_grad():
+            m.r_w_bias.normal_(0, 0.3)
+            m.r_r_bias.normal_(0, 0.3)
+        lengths = [9, 4, 6]
+        n = sum(lengths)
+        cu = torch.zeros(4, dtype=torch.int32)
+        cu[1:] = torch.tensor(lengths).cumsum(0)
+        seqs = PackedSeqs(torch.zeros(n, dtype=torch.long), torch.zeros(n, dtype=torch.long), cu, max(lengths))
+        x = torch.randn(n, 32, requires_grad=True)
+        a = m(x, seqs)
+        ga = torch.autograd.grad(a.square().sum(), [x] + list(m.parameters()), allow_unused=True)
+        m.force_bias_path = True
+        b = m(x, seqs)
+        gb = torch.autograd.grad(b.square().sum(), [x] + list(m.parameters()), allow_unused=True)
+        assert torch.allclose(a, b, atol=1e-5)
+        for u, v in zip(ga, gb):
+            assert (u is None) == (v is None)
+            if u is not None:
+                assert torch.allclose(u, v, atol=1e-4, rtol=1e-4)
