@@ -28,6 +28,7 @@ import threading
 from typing import Optional
 
 import torch
+import torch.nn.functional as F
 
 from . import reference as ref
 
@@ -530,6 +531,16 @@ def _attn_dispatch(a, b, cu_q, cu_k, heads, max_q, max_k, causal, dropout_p, tra
     d = W // heads
     scale = (1.0 / math.sqrt(d)) if scale is None else scale
     p = float(dropout_p) if training else 0.0
+    if a.is_cuda and a.dtype == torch.bfloat16 and d < 64 and d % 8 == 0:
+        # heads narrower than the kernels' 64 columns: zero columns change neither q . k nor the first d output columns
+        n = a.shape[0]
+
+        def widen(t, parts):
+            return F.pad(t.reshape(t.shape[0], parts, heads, d), (0, 64 - d)).reshape(t.shape[0], parts * heads * 64)
+
+        out = _attn_dispatch(widen(a, 3 if b is None else 1), None if b is None else widen(b, 2), cu_q, cu_k, heads, max_q, max_k,
+                             causal, dropout_p, training, scale, bias)
+        return out.view(n, heads, 64)[..., :d].reshape(n, heads * d)
     if bias is not None and a.is_cuda and d == 64 and a.dtype == torch.bfloat16:
         sid = next_stream() if p > 0 else 0
         a = a.contiguous()

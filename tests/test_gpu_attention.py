@@ -249,3 +249,37 @@ def test_relative_self_attention_long_sequences_use_the_bias_operand(causal):
     for a, b in zip(gg, gw):
         scale = max(1.0, float(b.abs().max()))
         assert (a.float().cpu() - b).abs().max() < 0.08 * scale
+
+
+@pytest.mark.parametrize("hd", [32, 16, 48])
+@pytest.mark.parametrize("cross", [False, True])
+def test_heads_narrower_than_64_run_on_the_kernels(hd, cross):
+    """Head sizes below 64 are zero-padded to the kernels' 64 columns; output and gradients against the fp32 statement."""
+    torch.manual_seed(2)
+    heads = 4
+    W = heads * hd
+    lq, lk = [70, 150, 9], [33, 140, 128]
+    cu_q, cu_k = _cu(lq), _cu(lq if not cross else lk)
+    nq, nk = sum(lq), sum(lq if not cross else lk)
+    launches = ops.LAUNCHES[0]
+    if cross:
+        q = torch.randn(nq, W, device=DEV).bfloat16().requires_grad_(True)
+        kv = torch.randn(nk, 2 * W, device=DEV).bfloat16().requires_grad_(True)
+        out = ops.cross_attention(q, kv, cu_q, cu_k, heads, max(lq), max(lk), 0.0, True)
+        leaves = [q, kv]
+    else:
+        qkv = torch.randn(nq, 3 * W, device=DEV).bfloat16().requires_grad_(True)
+        out = ops.self_attention(qkv, cu_q, heads, max(lq), causal=True, dropout_p=0.0, training=True)
+        leaves = [qkv]
+    assert ops.LAUNCHES[0] > launches and ops.check_status() == 0
+    dout = torch.randn(nq, W, device=DEV).bfloat16()
+    grads = torch.autograd.grad(out, leaves, dout)
+    l32 = [t.detach().float().requires_grad_(True) for t in leaves]
+    if cross:
+        o_ref = ref.attention(l32[0], l32[1][:, :W], l32[1][:, W:], cu_q, cu_k, heads, False, 0.0)
+    else:
+        o_ref = ref.attention(l32[0][:, :W], l32[0][:, W:2 * W], l32[0][:, 2 * W:], cu_q, cu_q, heads, True, 0.0)
+    g_ref = torch.autograd.grad(o_ref, l32, dout.float())
+    assert _err(out, o_ref) < 2e-2
+    for g, gr in zip(grads, g_ref):
+        assert _err(g, gr) < 3e-2
