@@ -42,6 +42,23 @@ def build_model(opt, dicts, remove_pretrain: bool = False, constants=None):
     if int(getattr(opt, "batch_ensemble", 0) or 0) > 0:
         from ..modules.batch_ensemble import convert_to_batch_ensemble
         convert_to_batch_ensemble(model, int(opt.batch_ensemble))
+    if getattr(opt, "rotary_position_encoding", False) and not any(getattr(m, "rotary", False) for m in model.modules()):
+        raise NotImplementedError("-rotary_position_encoding is built for the wav2vec 2.0 family encoders; model '%s' has no "
+                                  "rotary attention" % getattr(opt, "model", "?"))
+    for flag, side in (("wav2vec_adapter", "encoder"), ("decoder_adapter", "decoder")):
+        if int(getattr(opt, flag, 0) or 0) > 0 and getattr(getattr(model, side, None), "adapters", None) is None:
+            raise NotImplementedError("-%s: the %s of model '%s' has no language-adapter slots (built for the wav2vec 2.0 "
+                                      "family encoders and the pretrained-style decoders)" % (flag, side, getattr(opt, "model", "?")))
+    if float(getattr(opt, "weight_drop", 0.0) or 0.0) > 0:
+        from .layers import FeedForward
+        for m in model.modules():
+            if isinstance(m, FeedForward):
+                m.weight_drop = float(opt.weight_drop)
+    if getattr(opt, "stochastic_sublayer", False):
+        from .layers import _LayerOptions
+        for m in model.modules():
+            if isinstance(m, _LayerOptions):
+                m.stochastic_sublayer = True
     if not remove_pretrain:          # a full checkpoint is about to be loaded: its weights replace the pretrained ones
         load_pretrained_parts(model, opt, dicts)
     apply_freeze_options(model, opt)

@@ -20,6 +20,7 @@ from typing import Optional
 
 import torch
 import torch.nn as nn
+import torch.nn.functional as F
 
 from .. import ops
 
@@ -191,8 +192,28 @@ class Embedding(nn.Module):
                              scale, dropout_p, self.training, self.pad_idx, pos_trainable=self.learned_pos)
 
 
+def rotate_queries_and_keys(qkv, positions, heads: int, base: float = 10000.0):
+    """Rotary position encoding on the fused projection ``qkv [N, 3 * heads * d]``: queries and keys of the token at
+    position ``t`` are rotated by the angles ``t / base^(2i/d)`` (half-split layout: column ``i`` pairs with column
+    ``i + d/2``), values are left alone.  Scores then depend on the distance between query and key only."""
+    N, W3 = qkv.shape
+    d = W3 // (3 * heads)
+    inv = 1.0 / (base ** (torch.arange(0, d, 2, device=qkv.device, dtype=torch.float32) / d))
+    ang = positions.to(torch.float32)[:, None] * inv[None, :]                     # [N, d/2]
+    cos = torch.cat([ang.cos(), ang.cos()], -1)[:, None, None, :]
+    sin = torch.cat([ang.sin(), ang.sin()], -1)[:, None, None, :]
+    t = qkv.view(N, 3, heads, d)
+    qk = t[:, :2].float()
+    half = torch.cat([-qk[..., d // 2:], qk[..., :d // 2]], -1)
+    qk = (qk * cos + half * sin).to(qkv.dtype)
+    return torch.cat([qk, t[:, 2:]], 1).view(N, W3)
+
+
 class SelfAttention(nn.Module):
-    """Fused-QKV self-attention sub-layer: ``residual + D(out(attn(qkv(x))))``."""
+    """Fused-QKV self-attention sub-layer: ``residual + D(out(attn(qkv(x))))``.  ``rotary`` (set by
+    ``-rotary_position_encoding`` on encoder stacks) rotates queries and keys by their positions first."""
+
+    rotary = False
 
     def __init__(self, dim: int, heads: int, attn_dropout: float = 0.0, bias: bool = False, causal: bool = False):
         super().__init__()
@@ -201,12 +222,16 @@ class SelfAttention(nn.Module):
         self.out = Linear(dim, dim, bias=bias)
 
     def forward(self, x, seqs: PackedSeqs, residual=None, dropout_p: float = 0.0):
-        ctx = ops.self_attention(self.qkv(x), seqs.cu, self.heads, seqs.max_len, self.causal, self.attn_dropout,
-                                 self.training)
+        qkv = self.qkv(x)
+        if self.rotary:
+            qkv = rotate_queries_and_keys(qkv, seqs.positions, self.heads)
+        ctx = ops.self_attention(qkv, seqs.cu, self.heads, seqs.max_len, self.causal, self.attn_dropout, self.training)
         return self.out(ctx, dropout_p=dropout_p, residual=residual)
 
     # -- incremental decoding: x [B, H] is ONE new position per hypothesis --------------------------
     def step(self, x, cache: dict, residual=None):
+        if self.rotary:
+            raise NotImplementedError("rotary positions are built for encoder stacks (no incremental step)")
         H, h = self.dim, self.heads
         qkv = self.qkv(x)
         q, k, v = qkv[:, :H], qkv[:, H:2 * H], qkv[:, 2 * H:]
@@ -302,7 +327,20 @@ class FeedForward(nn.Module):
         self.activation = activation
         self.glu = glu
 
+    # -weight_drop p: DropConnect - dropout on both weight matrices during training
+    # (reference: onmt/modules/optimized/feed_forward.py:30-40).  The masked weights exist for one step only, so this
+    # path runs as plain matrix products instead of the fused feed-forward.
+    weight_drop = 0.0
+
     def forward(self, x, residual=None, dropout_p: float = 0.0):
+        if self.weight_drop > 0 and self.training:
+            if self.glu:
+                raise NotImplementedError("-weight_drop with -ffn_glu")
+            from ..ops import reference as ref
+            w1 = F.dropout(self.fc1.weight, self.weight_drop, True)
+            w2 = F.dropout(self.fc2.weight, self.weight_drop, True)
+            h = ref.linear(x, w1, self.fc1.bias, ops.ACT_IDS[self.activation], self.dropout, None)
+            return ref.linear(h, w2, self.fc2.bias, 0, dropout_p, residual)
         if self.glu:
             h, gate = self.fc1(x).chunk(2, dim=-1)
             from ..ops.reference import _act
@@ -349,6 +387,19 @@ class _LayerOptions:
             # 3 encoder-decoder attention, 4 interleaved feed-forward (unused entries stay at zero)
             self.gates = nn.Parameter(torch.zeros(5))
 
+    # -stochastic_sublayer: with layer dropping (``death_rate``) every sub-layer tosses its own coin instead of the layer
+    # as a whole (reference: onmt/models/multilingual_translator/relative_transformer_layers.py:136-176)
+    stochastic_sublayer = False
+
+    def _survives(self, sublayer: bool = False) -> bool:
+        """Coin of the layer (``sublayer`` False) or of one sub-layer; always True outside training / without dropping,
+        and for sub-layers when the layer as a whole has already tossed."""
+        if sublayer and not self.stochastic_sublayer:
+            return True
+        if not self.training or self.death_rate <= 0:
+            return True
+        return torch.rand(1).item() >= self.death_rate
+
     def _block(self, idx, norm, fn, x, p, seqs, *args, scale=None):
         """One residual sub-layer under the layer's structure switches; ``idx`` picks the rezero gate."""
         if self.rezero:
@@ -381,13 +432,17 @@ class EncoderLayer(nn.Module, _LayerOptions):
         self._init_options(dim, inner, fd, activation, post_norm, rezero, macaron, glu)
 
     def forward(self, x, seqs: PackedSeqs):
-        if self.training and self.death_rate > 0 and torch.rand(1).item() < self.death_rate:
+        keep = self._survives
+        if not self.stochastic_sublayer and not keep():
             return x
         p = self.dropout
-        if self.macaron:
+        if self.macaron and keep(True):
             x = self._block(2, self.mcr_norm, self.mcr_ffn, x, p, seqs, scale=0.5)
-        x = self._block(0, self.attn_norm, self.attn, x, p, seqs, seqs)
-        return self._block(1, self.ffn_norm, self.ffn, x, p, seqs, scale=self.ffn_scale)
+        if keep(True):
+            x = self._block(0, self.attn_norm, self.attn, x, p, seqs, seqs)
+        if keep(True):
+            x = self._block(1, self.ffn_norm, self.ffn, x, p, seqs, scale=self.ffn_scale)
+        return x
 
 
 class DecoderLayer(nn.Module, _LayerOptions):
@@ -417,17 +472,21 @@ class DecoderLayer(nn.Module, _LayerOptions):
         self._init_options(dim, inner, fd, activation, post_norm, rezero, macaron, glu)
 
     def forward(self, x, seqs: PackedSeqs, memory, mem_seqs: PackedSeqs):
-        if self.training and self.death_rate > 0 and torch.rand(1).item() < self.death_rate:
+        keep = self._survives
+        if not self.stochastic_sublayer and not keep():
             return x
         p = self.dropout
-        if self.macaron:
+        if self.macaron and keep(True):
             x = self._block(2, self.mcr_norm, self.mcr_ffn, x, p, seqs, scale=0.5)
-        x = self._block(0, self.self_norm, self.self_attn, x, p, seqs, seqs)
-        if self.interleaved_ffn:
+        if keep(True):
+            x = self._block(0, self.self_norm, self.self_attn, x, p, seqs, seqs)
+        if self.interleaved_ffn and keep(True):
             x = self._block(4, self.mid_norm, self.mid_ffn, x, p, seqs)
-        if not self.ignore_source:
+        if not self.ignore_source and keep(True):
             x = self._block(3, self.cross_norm, self.cross_attn, x, p, seqs, seqs, memory, mem_seqs)
-        return self._block(1, self.ffn_norm, self.ffn, x, p, seqs, scale=self.ffn_scale)
+        if keep(True):
+            x = self._block(1, self.ffn_norm, self.ffn, x, p, seqs, scale=self.ffn_scale)
+        return x
 
     def step(self, x, cache: dict, mem_mask):
         if self.rezero or self.macaron:

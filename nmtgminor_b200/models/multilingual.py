@@ -22,8 +22,14 @@ from .transformer import Generator, Seq2SeqBase, TransformerDecoder, Transformer
 class FactorizedLinear(nn.Module):
     """Linear layer whose weight is specialised per language by low-rank multiplicative and additive factors."""
 
-    def __init__(self, d_in, d_out, n_languages, rank=1, bias=True, multiplicative=True):
+    def __init__(self, d_in, d_out, n_languages, rank=1, bias=True, multiplicative=True, weight_drop=0.0, activation="none"):
         super().__init__()
+        if activation not in ("none", "gelu", "silu"):
+            raise NotImplementedError("-mfw_activation %s (none | gelu | silu)" % activation)
+        # ``-weight_drop``: dropout on the shared weight (DropConnect); ``-mfw_activation``: non-linearity on the shared
+        # weight after the multiplicative factors and before the additive ones
+        # (reference: onmt/modules/multilingual_factorized/linear.py:70-103)
+        self.weight_drop, self.activation = float(weight_drop), activation
         self.weight = nn.Parameter(torch.empty(d_out, d_in))
         nn.init.xavier_uniform_(self.weight)
         self.bias = nn.Parameter(torch.zeros(d_out)) if bias else None
@@ -38,8 +44,14 @@ class FactorizedLinear(nn.Module):
 
     def weight_for(self, lang: int):
         w = self.weight
+        if self.weight_drop > 0:
+            w = F.dropout(w, self.weight_drop, self.training)
         if self.multiplicative:
             w = w * (self.rm[lang].t() @ self.sm[lang])
+        if self.activation == "gelu":
+            w = F.gelu(w)
+        elif self.activation == "silu":
+            w = F.silu(w)
         return w + self.r[lang].t() @ self.s[lang]
 
     def forward(self, x, lang: int):
@@ -80,7 +92,10 @@ class MFWLayer(nn.Module):
         super().__init__()
         d, inner, r = opt.model_size, opt.inner_size, max(1, int(getattr(opt, "mfw_rank", 1)))
         bias = not getattr(opt, "mfw_no_bias", False)
-        lin = lambda i, o: FactorizedLinear(i, o, n_languages, rank=r, bias=bias, multiplicative=False)
+        lin = lambda i, o: FactorizedLinear(i, o, n_languages, rank=r, bias=bias,
+                                            multiplicative=bool(getattr(opt, "mfw_multiplicative", False)),
+                                            weight_drop=float(getattr(opt, "weight_drop", 0.0) or 0.0),
+                                            activation=str(getattr(opt, "mfw_activation", "none") or "none"))
         per_lang_norm = bool(getattr(opt, "multilingual_layer_norm", False))
         self.heads, self.dim, self.decoder = opt.n_heads, d, decoder
         self.dropout, self.attn_dropout, self.act = opt.dropout, opt.attn_dropout, opt.ffn_activation

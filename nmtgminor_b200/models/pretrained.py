@@ -28,7 +28,7 @@ import torch.nn.functional as F
 from .. import ops
 from .layers import DecoderLayer, Embedding, EncoderLayer, LayerNorm, PackedSeqs
 from .speech_encoders import SpeechTransformerEncoder, Wav2Vec2Encoder, WhisperEncoder
-from .transformer import DecodingState, Generator, Seq2SeqBase
+from .transformer import DecodingState, Generator, Seq2SeqBase, single_language
 
 FAMILY_DEFAULTS = {
     # learned positions, position offset, embedding LayerNorm, final LayerNorm, pre-LN, scale embeddings, activation
@@ -76,16 +76,31 @@ class PretrainedStyleDecoder(nn.Module):
         self.final_norm = LayerNorm(dim) if f["final_norm"] else None
         self.dropout = dropout
         self.embed.word_dropout = word_dropout
+        self.adapters = None
+
+    def add_adapters(self, n_languages: int, location: int = 1, downsample: int = 4):
+        """``-decoder_adapter``: one bottleneck adapter per language behind every decoder layer (``x + adapter_lang(x)``
+        after the feed-forward block), chosen by the batch's target language
+        (reference: pretrain_module/modeling_mbart.py:1039-1051, 1277-1283, 1844-1847)."""
+        from .multilingual import MultilingualAdapter
+        if location != 1:
+            raise NotImplementedError("-decoder_adapter %d: only location 1 (behind each layer) is built" % location)
+        dim = self.embed.weight.shape[1]
+        self.adapters = nn.ModuleList([MultilingualAdapter(dim, dim // downsample, n_languages) for _ in self.layers])
 
     def _embed(self, seqs: PackedSeqs):
         if self.emb_norm is None:
             return self.embed(seqs, self.emb_dropout)
         return ops.dropout_add(self.emb_norm(self.embed(seqs, 0.0)), None, self.emb_dropout, self.training)
 
-    def forward(self, tgt: PackedSeqs, memory, src: PackedSeqs):
+    def forward(self, tgt: PackedSeqs, memory, src: PackedSeqs, lang: Optional[int] = None):
+        if self.adapters is not None and lang is None:
+            raise ValueError("this decoder has language adapters: the batch must carry its target language id")
         x = self._embed(tgt)
-        for layer in self.layers:
+        for i, layer in enumerate(self.layers):
             x = layer(x, tgt, memory, src)
+            if self.adapters is not None:
+                x = self.adapters[i](x, lang)
         return self.final_norm(x) if self.final_norm is not None else x
 
     def step(self, tokens, position: int, state: DecodingState):
@@ -96,6 +111,8 @@ class PretrainedStyleDecoder(nn.Module):
             x = self.emb_norm(x)
         for i, layer in enumerate(self.layers):
             x = layer.step(x, state.buffers[i], state.src_pad_mask)
+            if self.adapters is not None:
+                x = self.adapters[i](x, int(state.tgt_lang.view(-1)[0]))
         return self.final_norm(x) if self.final_norm is not None else x
 
 
@@ -286,6 +303,10 @@ class SpeechToTextModel(Seq2SeqBase, _ReferenceNaming):
         self.pad_idx = decoder.embed.pad_idx
         self.label_smoothing = getattr(opt, "label_smoothing", 0.0)
         self.ctc_weight = getattr(opt, "ctc_loss", 0.0)
+        # -ctc_loss_delay n: the CTC term joins the loss only once more than n updates have been made (the training
+        # engine writes the optimiser's update count here; reference: onmt/train_utils/mp_trainer.py:795)
+        self.ctc_delay = int(getattr(opt, "ctc_loss_delay", -1) if getattr(opt, "ctc_loss_delay", None) is not None else -1)
+        self.num_updates = 0
         if self.ctc_weight > 0:
             self.ctc_linear = nn.Linear(encoder.dim, vocab)
         # -transducer_loss w: an RNN-T branch next to the attention decoder.  The decoder states act as the prediction
@@ -357,7 +378,10 @@ class SpeechToTextModel(Seq2SeqBase, _ReferenceNaming):
         return loss.sum()
 
     def encode(self, batch):
-        context, src = self.encoder(batch.get("source"))
+        if getattr(self.encoder, "adapters", None) is not None:
+            context, src = self.encoder(batch.get("source"), lang=single_language(batch, "source_lang"))
+        else:
+            context, src = self.encoder(batch.get("source"))
         self._uncompressed = None
         mode = str(getattr(self.opt, "ctc_compress", "None") or "None").lower()
         if mode != "none" and self.ctc_weight > 0:
@@ -378,7 +402,7 @@ class SpeechToTextModel(Seq2SeqBase, _ReferenceNaming):
                 raise RuntimeError("-transducer_loss and -ctc_compress cannot be combined (the lattice needs every frame)")
             rnnt = self.transducer_weight * self._transducer_term(context, src, out)
             extra = rnnt if extra is None else extra + rnnt
-        if self.ctc_weight <= 0:
+        if self.ctc_weight <= 0 or self.num_updates <= self.ctc_delay:
             return extra
         ctc = self._ctc_term(batch, context, src, out)
         return ctc if extra is None else ctc + extra
@@ -406,6 +430,11 @@ class SpeechToTextModel(Seq2SeqBase, _ReferenceNaming):
 class TextToTextPretrained(Seq2SeqBase, _ReferenceNaming):
     """``pretrain_transformer``: pretrained-style text encoder + decoder (mBART, DeltaLM, M2M-100, BART ...)."""
 
+    @property
+    def graph_capturable(self):
+        # reads only the packed token views - unless language adapters pick their weights by the batch's language id
+        return getattr(self.decoder, "adapters", None) is None
+
     def __init__(self, opt, dicts):
         super().__init__()
         self.opt = opt
@@ -426,10 +455,25 @@ class TextToTextPretrained(Seq2SeqBase, _ReferenceNaming):
             self.encoder.embed.weight = self.decoder.embed.weight
         self.pad_idx = self.decoder.embed.pad_idx
         self.label_smoothing = getattr(opt, "label_smoothing", 0.0)
+        if int(getattr(opt, "decoder_adapter", 0) or 0) > 0:
+            _add_language_adapters(opt, dicts, None, self.decoder)
 
     def encode(self, batch):
         src = batch.packed_source()
         return self.encoder(src), src
+
+
+def _add_language_adapters(opt, dicts, encoder, decoder):
+    from .transformer import _n_languages
+    n = max(_n_languages(dicts), int(getattr(opt, "n_languages", 0) or 0))
+    if encoder is not None and int(getattr(opt, "wav2vec_adapter", 0) or 0) > 0:
+        if not hasattr(encoder, "add_adapters"):
+            raise NotImplementedError("-wav2vec_adapter: %s has no adapter slots" % type(encoder).__name__)
+        encoder.add_adapters(n, int(opt.wav2vec_adapter))
+    if int(getattr(opt, "decoder_adapter", 0) or 0) > 0:
+        if not hasattr(decoder, "add_adapters"):
+            raise NotImplementedError("-decoder_adapter: %s has no adapter slots" % type(decoder).__name__)
+        decoder.add_adapters(n, int(opt.decoder_adapter))
 
 
 def _wav2vec_from_opt(opt):
@@ -448,7 +492,7 @@ def _wav2vec_from_opt(opt):
         from .w2vbert import build_w2vbert_encoder
         return build_w2vbert_encoder(opt, vars(cfg))
     base = "base" in name
-    return Wav2Vec2Encoder(
+    enc = Wav2Vec2Encoder(
         dim=_cfg(cfg, ["encoder_embed_dim", "hidden_size"], 768 if base else 1024),
         layers=_cfg(cfg, ["encoder_layers", "num_hidden_layers"], 12 if base else 24),
         heads=_cfg(cfg, ["encoder_attention_heads", "num_attention_heads"], 12 if base else 16),
@@ -463,6 +507,14 @@ def _wav2vec_from_opt(opt):
         freeze_extractor=not getattr(opt, "unfreeze_feature_extractor", False),
         gated_relative_position="wavlm" in name,
         num_buckets=_cfg(cfg, ["num_buckets"], 320), max_distance=_cfg(cfg, ["max_distance"], 800))
+    if getattr(opt, "rotary_position_encoding", False):
+        # queries and keys of every encoder layer are rotated by their frame positions
+        # (reference: onmt/models/speech_recognizer/wav2vec2.py:251-254 -> add_rotary_attention)
+        if "wavlm" in name:
+            raise NotImplementedError("-rotary_position_encoding and WavLM's relative-position bias exclude each other")
+        for layer in enc.layers:
+            layer.attn.rotary = True
+    return enc
 
 
 def _whisper_sizes(opt):
@@ -479,6 +531,7 @@ def register_builders(register):
     def _wav2vec_bert(opt, dicts):
         enc = _wav2vec_from_opt(opt)
         dec = build_pretrained_decoder(opt, dicts["tgt"].size(), kv_dim=enc.dim)
+        _add_language_adapters(opt, dicts, enc, dec)
         return SpeechToTextModel(opt, enc, dec, dec.embed.weight.shape[0], generator_bias=False)
 
     @register("wav2vec2_transformer")

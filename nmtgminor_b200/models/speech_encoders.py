@@ -219,8 +219,20 @@ class Wav2Vec2Encoder(nn.Module):
                 layer.attn = GatedRelPosSelfAttention(dim, heads, attn_dropout, num_buckets, max_distance, table_owner=owner)
                 owner = owner or layer.attn
         self.dim = dim
+        self.adapters = None
 
-    def forward(self, source) -> Tuple[torch.Tensor, PackedSeqs]:
+    def add_adapters(self, n_languages: int, location: int = 1, downsample: int = 4):
+        """``-wav2vec_adapter``: one bottleneck adapter per language in front of every Transformer layer (location 1; the
+        layer's input becomes ``x + adapter_lang(x)``), chosen by the batch's source language
+        (reference: onmt/models/speech_recognizer/fairseq_wav2vec2/wav2vec2.py:1112-1115, 1262-1280, 1494-1500)."""
+        from .multilingual import MultilingualAdapter
+        if location != 1:
+            raise NotImplementedError("-wav2vec_adapter %d: only location 1 (in front of each layer) is built" % location)
+        self.adapters = nn.ModuleList([MultilingualAdapter(self.dim, self.dim // downsample, n_languages) for _ in self.layers])
+
+    def forward(self, source, lang: Optional[int] = None) -> Tuple[torch.Tensor, PackedSeqs]:
+        if self.adapters is not None and lang is None:
+            raise ValueError("this encoder has language adapters: the batch must carry its source language id")
         feats, lengths = split_audio_batch(source)
         wav = feats[:, :, 0].float()
         if self.freeze_extractor:
@@ -243,7 +255,9 @@ class Wav2Vec2Encoder(nn.Module):
         packed = packed.to(torch.bfloat16) if (packed.is_cuda and ops.fused_param(self.input_norm.weight)) else packed
         if not self.layer_norm_first:
             packed = self.input_norm(packed)
-        for layer in self.layers:
+        for i, layer in enumerate(self.layers):
+            if self.adapters is not None:
+                packed = self.adapters[i](packed, lang)
             packed = layer(packed, seqs)
         if self.layer_norm_first:
             packed = self.input_norm(packed)

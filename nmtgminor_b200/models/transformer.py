@@ -67,6 +67,14 @@ def _n_languages(dicts) -> int:
     return len(langs) if langs else 1
 
 
+def single_language(batch, key: str) -> Optional[int]:
+    """The one language id of a batch (batches of the multilingual data sets hold one language pair each), or None."""
+    t = batch.get(key) if hasattr(batch, "get") else None
+    if t is None or not torch.is_tensor(t) or t.numel() == 0:
+        return None
+    return int(t.view(-1)[0])
+
+
 def _embed_with_language(stack, seqs: PackedSeqs, lang_ids):
     """Embedding (+ language vector) + embedding dropout.  Without language embeddings this is the one fused kernel."""
     if stack.language_embedding is None or lang_ids is None:
@@ -283,6 +291,11 @@ class Seq2SeqBase(nn.Module):
     label_smoothing = 0.0
     generator_chunk_rows = 0      # > 0: output projection + loss over this many rows at a time (no [rows, V] logits)
 
+    # A captured training step reads nothing but the packed token views of a batch from fixed device buffers.  A model
+    # whose forward pass depends on anything else of the batch (language ids, audio features, auxiliary targets) or on
+    # state carried between steps must leave this False; the engine then runs it kernel by kernel.
+    graph_capturable = False
+
     def encode(self, batch):
         raise NotImplementedError
 
@@ -305,6 +318,8 @@ class Seq2SeqBase(nn.Module):
         labels = batch.packed_target_output()
         if getattr(self.decoder, "language_embedding", None) is not None:
             hidden = self.decoder(tgt, context, src, lang_ids=batch.get("target_lang") if hasattr(batch, "get") else None)
+        elif getattr(self.decoder, "adapters", None) is not None:
+            hidden = self.decoder(tgt, context, src, lang=single_language(batch, "target_lang"))
         else:
             hidden = self.decoder(tgt, context, src)
         out = {"hidden_packed": hidden, "context_packed": context, "src": src, "tgt": tgt, "target": labels}
@@ -410,7 +425,8 @@ class Seq2SeqBase(nn.Module):
         if getattr(self, "copy_generator", None) is not None:
             toks = src.pad(src.tokens[:, None].float(), time_first=False).squeeze(-1).long()[:ctx_padded.shape[0]]
             state.src_tokens = toks.repeat_interleave(beam_size, 0) if beam_size > 1 else toks
-        if getattr(self.decoder, "language_embedding", None) is not None and hasattr(batch, "get"):
+        if (getattr(self.decoder, "language_embedding", None) is not None
+                or getattr(self.decoder, "adapters", None) is not None) and hasattr(batch, "get"):
             tl = batch.get("target_lang")
             if tl is not None:
                 tl = tl.to(ctx_padded.device).view(-1)
@@ -452,6 +468,11 @@ class Seq2SeqBase(nn.Module):
 
 class Transformer(Seq2SeqBase):
     """``NMTModel`` for text-to-text translation."""
+
+    @property
+    def graph_capturable(self):
+        # language embeddings read the batch's language ids, which the static buffers of a captured step do not carry
+        return getattr(self.decoder, "language_embedding", None) is None
 
     def __init__(self, opt, dicts):
         super().__init__()

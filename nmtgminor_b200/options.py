@@ -139,6 +139,13 @@ NO_EFFECT_IN_REFERENCE = {
     "dr_alpha", "dr_beta", "attribute_size", "noam_step_interval", "factorizing_step", "input_feature_size",
     "mfw_atb_rank_scale", "freezing_steps", "debugging", "enc_pretrain_hidden_size", "enc_pretrain_word_dropout",
     "enc_pretrain_attn_dropout", "mutual_modality_training",
+    # the trainers add opt.contrastive_loss_coeff * outputs['contrastive_loss'], but no model of the reference ever puts
+    # that key into its outputs (the speech models set the term to 0 and leave the assignment commented out)
+    "contrastive_loss_coeff",
+    # parsed into a per-data-set dictionary and handed to Dataset(dataset_factor=...), which never reads it
+    "dataset_factors",
+    # written to onmt.constants.residual_type; every reader of that constant is commented out
+    "residual_type",
 }
 
 # Flags whose feature is not built: giving one a value other than its default stops the run instead of silently
@@ -148,11 +155,8 @@ UNSUPPORTED_FLAGS = {
     "finalize_only": "the continual-learning finalisation pass",
     "max_examples_seen": "example-count limits of the continual-learning trainers",
     "stream_context": "streaming context selection",
-    "rotary_position_encoding": "rotary position encoding in the speech / relative Transformers",
     "weight_norm": "weight-normalised linear layers",
-    "stochastic_sublayer": "stochastic sub-layer dropping",
     "activation_layer": "alternative activation-layer layouts (maxout)",
-    "residual_type": "gated / highway residual connections",
     "extra_context_size": "extra streaming context",
     "no_decoder": "encoder-only sequence models in the translation trainer",
     "favor_attention": "FAVOR+ attention inside the main Transformer (models/efficient_attention.py has the stand-alone layer)",
@@ -165,20 +169,13 @@ UNSUPPORTED_FLAGS = {
     "no_ffn": "layers without feed-forward blocks",
     "fast_factorize": "the fused factorised-weight kernels (the factorised weights run as plain GEMMs)",
     "flex_factorize": "flexible-rank factorised weights",
-    "mfw_multiplicative": "multiplicative factorised weights",
-    "mfw_activation": "activations on factorised weights",
     "sub_encoder": "text sub-encoders behind the speech encoder",
-    "weight_drop": "DropConnect on the feed-forward weights",
     "enc_stacked_pretrained_model": "stacked pretrained encoders",
     "s4_config_file": "S4 configuration files (the state-space encoder takes its sizes from -enc_config_file)",
     "load_pretrained_classifier": "pretrained classifier heads",
     "wav2vec2_quantize": "the wav2vec 2.0 quantiser inside the translation models (models/w2vbert.py has the quantiser)",
     "wav2vec2_dual_output": "dual-output wav2vec 2.0 encoders",
     "wav2vec2_relative_attention": "relative attention inside wav2vec 2.0",
-    "wav2vec_adapter": "adapters inside wav2vec 2.0",
-    "decoder_adapter": "adapters inside the pretrained decoders",
-    "contrastive_loss_coeff": "the speech / text contrastive loss",
-    "dataset_factors": "per-data-set sampling factors",
     "cache_encoder_output": "cached encoder outputs",
     "use_memory": "the n-gram memory decoder",
     "freeze_baseline_decoder": "the n-gram memory decoder",
@@ -195,7 +192,6 @@ UNSUPPORTED_FLAGS = {
     "decoder_late_emb_scale": "late embedding scaling",
     "encoder_early_emb_scale": "early embedding scaling",
     "no_input_scale": "unscaled speech inputs of the relative speech Transformer",
-    "ctc_loss_delay": "delayed CTC loss",
     "char_ctc": "character-level CTC targets",
     "cache_dir": "cached encoder outputs",
     "memory_loss_coeff": "the n-gram memory decoder",

@@ -134,7 +134,8 @@ class TrainEngine:
             self.scaler = DynamicLossScaler(self.device, init_scale=float(getattr(opt, "init_loss_scale", 2.0 ** 16) or 2.0 ** 16),
                                             growth_interval=int(getattr(opt, "loss_scale_window", 2000) or 2000))
             self.optim.loss_scaler = self.scaler
-        self.use_graph = bool(cuda_graph) and self.on_gpu
+        # only models that declare it: a captured step sees nothing of a batch but its packed token views
+        self.use_graph = bool(cuda_graph) and self.on_gpu and bool(getattr(model, "graph_capturable", False))
         self._graphs = {}                 # shape class -> [graph, static inputs, launches per replay, last use]
         self._seen = {}                   # shape class -> batches met so far (a class is captured at batch number capture_after)
         self._pool = None
@@ -152,6 +153,8 @@ class TrainEngine:
             from ..utils.tracing import install_nvtx_hooks
             self._nvtx_hooks = install_nvtx_hooks(self.model)
         ops.reset_stream_counter()
+        if hasattr(self.model, "num_updates"):
+            self.model.num_updates = int(self.optim._step)      # schedules inside the model (delayed CTC weight)
         # the loss gradient is written pre-scaled by the kernel (scale 1): no [tokens, V] rescale pass in backward
         with nvtx_range("forward", trace):
             weight = float(getattr(self, "loss_weight", 1.0))       # per-step weight of this batch's gradient

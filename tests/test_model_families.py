@@ -356,3 +356,154 @@ def test_relative_self_attention_bias_operand_path_matches_padded_path():
             assert (u is None) == (v is None)
             if u is not None:
                 assert torch.allclose(u, v, atol=1e-4, rtol=1e-4)
+
+
+def test_language_adapters_in_the_speech_encoder_and_the_pretrained_decoder(dicts, tmp_path):
+    """``-wav2vec_adapter 1 -decoder_adapter 1``: one adapter per language and layer; a batch trains the adapters of its
+    own source / target language only, and decoding takes the same path."""
+    torch.manual_seed(5)
+    enc = _cfg(tmp_path, "enc.json", encoder_embed_dim=64, encoder_layers=2, encoder_attention_heads=2, encoder_ffn_embed_dim=128)
+    dec = _cfg(tmp_path, "dec.json", d_model=64, decoder_layers=2, decoder_attention_heads=2, decoder_ffn_dim=128, vocab_size=120, pad_token_id=0)
+    argv = ["-model", "wav2vec2_bert", "-enc_config_file", enc, "-dec_config_file", dec, "-dec_pretrained_model", "mbart50",
+            "-wav2vec_adapter", "1", "-decoder_adapter", "1"]
+    model = build_model(default_options(argv + COMMON), dicts)
+    assert len(model.encoder.adapters) == 2 and len(model.encoder.adapters[0].adapters) == 2
+    assert len(model.decoder.adapters) == 2 and len(model.decoder.adapters[0].adapters) == 2
+    batch = synthetic_audio_batch(2, 120, "wav", 3000, 6000)
+    with pytest.raises(ValueError, match="language"):
+        model(batch)
+    batch.tensors["source_lang"] = torch.tensor([0])
+    batch.tensors["target_lang"] = torch.tensor([1])
+    # the up-projection starts at zero (identity adapter): move it so that the adapters matter
+    with torch.no_grad():
+        for stack in (model.encoder.adapters, model.decoder.adapters):
+            for per_layer in stack:
+                for a in per_layer.adapters:
+                    a.up.weight.normal_(0, 0.05)
+    out = model(batch)
+    out["loss"].backward()
+
+    def touched(adapter):
+        return adapter.up.weight.grad is not None and float(adapter.up.weight.grad.abs().sum()) > 0
+    assert touched(model.encoder.adapters[0].adapters[0]) and not touched(model.encoder.adapters[0].adapters[1])
+    assert touched(model.decoder.adapters[1].adapters[1]) and not touched(model.decoder.adapters[1].adapters[0])
+    # another target language gives another loss; decoding runs through the adapters too
+    model.eval()
+    with torch.no_grad():
+        a = float(model(batch)["loss"])
+        batch.tensors["target_lang"] = torch.tensor([0])
+        b = float(model(batch)["loss"])
+    assert abs(a - b) > 1e-6
+    hyps = beam_search(model, batch, BeamConfig(beam_size=2, max_len=4))
+    assert len(hyps) == 2
+
+
+def test_ctc_loss_delay_switches_the_term_on_after_the_given_number_of_updates(dicts, tmp_path):
+    torch.manual_seed(6)
+    enc = _cfg(tmp_path, "enc.json", encoder_embed_dim=64, encoder_layers=1, encoder_attention_heads=2, encoder_ffn_embed_dim=128)
+    dec = _cfg(tmp_path, "dec.json", d_model=64, decoder_layers=1, decoder_attention_heads=2, decoder_ffn_dim=128, vocab_size=120, pad_token_id=0)
+    argv = ["-model", "wav2vec2_bert", "-enc_config_file", enc, "-dec_config_file", dec, "-dec_pretrained_model", "mbart50",
+            "-ctc_loss", "0.3", "-ctc_loss_delay", "2"]
+    model = build_model(default_options(argv + COMMON), dicts)
+    batch = synthetic_audio_batch(2, 120, "wav", 3000, 6000)
+    for step, expected in ((0, False), (2, False), (3, True)):
+        model.num_updates = step
+        out = model(batch)
+        assert ("ctc_loss" in out) == expected, step
+
+
+def test_stochastic_sublayer_tosses_one_coin_per_sublayer(dicts):
+    """With ``-stochastic_sublayer`` a layer can keep its attention and drop its feed-forward block (or the other way
+    round); without it the layer is kept or dropped as a whole."""
+    from nmtgminor_b200.models.layers import EncoderLayer
+    torch.manual_seed(0)
+    model = build_model(default_options(["-model", "transformer", "-death_rate", "0.5", "-stochastic_sublayer"] + COMMON), dicts)
+    layers = [m for m in model.modules() if isinstance(m, EncoderLayer)]
+    assert layers and all(l.stochastic_sublayer for l in layers)
+    layer = layers[-1]
+    layer.death_rate = 0.5
+    layer.train()
+    calls = {"attn": 0, "ffn": 0}
+    layer.attn.register_forward_hook(lambda *a: calls.__setitem__("attn", calls["attn"] + 1))
+    layer.ffn.register_forward_hook(lambda *a: calls.__setitem__("ffn", calls["ffn"] + 1))
+    batch = token_budget_batches(120, 4, 10, 60, 1, static=False, padded=True)[0]
+    seqs = batch.packed_source()
+    x = torch.randn(seqs.tokens.shape[0], layer.attn_norm.weight.shape[0])
+    patterns = set()
+    for _ in range(40):
+        before = dict(calls)
+        layer(x, seqs)
+        patterns.add((calls["attn"] - before["attn"], calls["ffn"] - before["ffn"]))
+    assert {(1, 0), (0, 1)} & patterns, patterns          # mixed patterns occur
+    layer.stochastic_sublayer = False
+    patterns = set()
+    for _ in range(40):
+        before = dict(calls)
+        layer(x, seqs)
+        patterns.add((calls["attn"] - before["attn"], calls["ffn"] - before["ffn"]))
+    assert patterns <= {(0, 0), (1, 1)}, patterns
+
+
+def test_rotary_positions_make_attention_depend_on_distance_only(dicts, tmp_path):
+    from nmtgminor_b200.models.layers import PackedSeqs, SelfAttention, rotate_queries_and_keys
+    torch.manual_seed(7)
+    heads, d, n = 2, 8, 6
+    qkv = torch.randn(n, 3 * heads * d)
+    a = rotate_queries_and_keys(qkv, torch.arange(n), heads).view(n, 3, heads, d)
+    b = rotate_queries_and_keys(qkv, torch.arange(n) + 11, heads).view(n, 3, heads, d)
+    sa = torch.einsum("ihd,jhd->hij", a[:, 0], a[:, 1])
+    sb = torch.einsum("ihd,jhd->hij", b[:, 0], b[:, 1])
+    assert torch.allclose(sa, sb, atol=1e-4)                       # a common shift changes no score
+    assert torch.equal(a[:, 2], qkv.view(n, 3, heads, d)[:, 2])    # values untouched
+    plain = torch.einsum("ihd,jhd->hij", qkv.view(n, 3, heads, d)[:, 0], qkv.view(n, 3, heads, d)[:, 1])
+    assert not torch.allclose(sa, plain, atol=1e-3)
+    # the module: with rotary on, the output changes and still backpropagates
+    att = SelfAttention(16, 2).eval()
+    cu = torch.tensor([0, 4, 6], dtype=torch.int32)
+    seqs = PackedSeqs(torch.ones(6, dtype=torch.long), torch.tensor([0, 1, 2, 3, 0, 1]), cu, 4)
+    x = torch.randn(6, 16, requires_grad=True)
+    y0 = att(x, seqs)
+    att.rotary = True
+    y1 = att(x, seqs)
+    assert not torch.allclose(y0, y1, atol=1e-4)
+    y1.sum().backward()
+    assert x.grad is not None
+    # the flag reaches the wav2vec 2.0 encoder layers
+    enc = _cfg(tmp_path, "enc.json", encoder_embed_dim=64, encoder_layers=2, encoder_attention_heads=2, encoder_ffn_embed_dim=128)
+    dec = _cfg(tmp_path, "dec.json", d_model=64, decoder_layers=1, decoder_attention_heads=2, decoder_ffn_dim=128, vocab_size=120, pad_token_id=0)
+    model = build_model(default_options(["-model", "wav2vec2_bert", "-enc_config_file", enc, "-dec_config_file", dec, "-dec_pretrained_model",
+                                         "mbart50", "-rotary_position_encoding"] + COMMON), dicts)
+    assert all(l.attn.rotary for l in model.encoder.layers)
+    out = model(synthetic_audio_batch(2, 120, "wav", 3000, 6000))
+    assert torch.isfinite(out["loss"]).all()
+
+
+def test_weight_drop_and_factorised_weight_options(dicts):
+    """``-weight_drop`` masks the feed-forward weights in training only; ``-mfw_multiplicative`` / ``-mfw_activation`` change
+    the per-language weight as the formula says."""
+    from nmtgminor_b200.models.layers import FeedForward
+    from nmtgminor_b200.models.multilingual import FactorizedLinear
+    torch.manual_seed(8)
+    model = build_model(default_options(["-model", "transformer", "-weight_drop", "0.5"] + COMMON), dicts)
+    ffns = [m for m in model.modules() if isinstance(m, FeedForward)]
+    assert ffns and all(f.weight_drop == 0.5 for f in ffns)
+    f = ffns[0]
+    f.dropout = 0.0
+    x = torch.randn(5, f.fc1.weight.shape[1])
+    f.eval()
+    assert torch.allclose(f(x), f(x))
+    f.train()
+    a, b = f(x), f(x)
+    assert not torch.allclose(a, b)                        # two different weight masks
+    a.sum().backward()
+    assert f.fc1.weight.grad is not None and float((f.fc1.weight.grad == 0).float().mean()) > 0.2   # dropped entries get no gradient
+    lin = FactorizedLinear(6, 4, n_languages=2, rank=1, multiplicative=True, activation="silu").eval()
+    with torch.no_grad():
+        lin.rm.uniform_(0.5, 1.5)
+        lin.sm.uniform_(0.5, 1.5)
+    want = torch.nn.functional.silu(lin.weight * (lin.rm[1].t() @ lin.sm[1])) + lin.r[1].t() @ lin.s[1]
+    assert torch.allclose(lin.weight_for(1), want, atol=1e-6)
+    ml = build_model(default_options(["-model", "multilingual_translator", "-multilingual_factorized_weights", "-mfw_multiplicative",
+                                      "-mfw_activation", "gelu"] + COMMON), dicts)
+    fl = [m for m in ml.modules() if isinstance(m, FactorizedLinear)]
+    assert fl and all(m.multiplicative and m.activation == "gelu" for m in fl)
