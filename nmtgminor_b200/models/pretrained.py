@@ -507,6 +507,15 @@ def _wav2vec_from_opt(opt):
         freeze_extractor=not getattr(opt, "unfreeze_feature_extractor", False),
         gated_relative_position="wavlm" in name,
         num_buckets=_cfg(cfg, ["num_buckets"], 320), max_distance=_cfg(cfg, ["max_distance"], 800))
+    if getattr(opt, "wav2vec2_relative_attention", False) or getattr(opt, "add_relative_attention", False):
+        # Transformer-XL style attention (sinusoidal relative positions, content and position biases) in every encoder
+        # layer; its projections start from scratch next to the pretrained feed-forward blocks
+        # (reference: onmt/models/speech_recognizer/wav2vec2.py:246-249 -> add_relative_attention)
+        if "wavlm" in name or getattr(opt, "rotary_position_encoding", False):
+            raise NotImplementedError("-wav2vec2_relative_attention excludes WavLM's bias and rotary positions")
+        from .relative_transformer import RelativeSelfAttention
+        for layer in enc.layers:
+            layer.attn = RelativeSelfAttention(enc.dim, layer.attn.heads, opt.attn_dropout, causal=False)
     if getattr(opt, "rotary_position_encoding", False):
         # queries and keys of every encoder layer are rotated by their frame positions
         # (reference: onmt/models/speech_recognizer/wav2vec2.py:251-254 -> add_rotary_attention)

@@ -175,7 +175,6 @@ UNSUPPORTED_FLAGS = {
     "load_pretrained_classifier": "pretrained classifier heads",
     "wav2vec2_quantize": "the wav2vec 2.0 quantiser inside the translation models (models/w2vbert.py has the quantiser)",
     "wav2vec2_dual_output": "dual-output wav2vec 2.0 encoders",
-    "wav2vec2_relative_attention": "relative attention inside wav2vec 2.0",
     "cache_encoder_output": "cached encoder outputs",
     "use_memory": "the n-gram memory decoder",
     "freeze_baseline_decoder": "the n-gram memory decoder",

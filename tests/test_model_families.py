@@ -507,3 +507,16 @@ def test_weight_drop_and_factorised_weight_options(dicts):
                                       "-mfw_activation", "gelu"] + COMMON), dicts)
     fl = [m for m in ml.modules() if isinstance(m, FactorizedLinear)]
     assert fl and all(m.multiplicative and m.activation == "gelu" for m in fl)
+
+
+def test_relative_attention_inside_the_wav2vec_encoder(dicts, tmp_path):
+    from nmtgminor_b200.models.relative_transformer import RelativeSelfAttention
+    torch.manual_seed(9)
+    enc = _cfg(tmp_path, "enc.json", encoder_embed_dim=64, encoder_layers=2, encoder_attention_heads=2, encoder_ffn_embed_dim=128)
+    dec = _cfg(tmp_path, "dec.json", d_model=64, decoder_layers=1, decoder_attention_heads=2, decoder_ffn_dim=128, vocab_size=120, pad_token_id=0)
+    model = build_model(default_options(["-model", "wav2vec2_bert", "-enc_config_file", enc, "-dec_config_file", dec, "-dec_pretrained_model",
+                                         "mbart50", "-wav2vec2_relative_attention"] + COMMON), dicts)
+    assert all(isinstance(l.attn, RelativeSelfAttention) for l in model.encoder.layers)
+    out = model(synthetic_audio_batch(2, 120, "wav", 3000, 6000))
+    out["loss"].backward()
+    assert model.encoder.layers[0].attn.r_r_bias.grad is not None
