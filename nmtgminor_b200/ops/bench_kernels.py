@@ -207,6 +207,48 @@ def bench_attention_ablation(rows):
         e.set_attn_bwd_ablation(0)
 
 
+def bench_attention_long_ablation(rows):
+    """The pipelined multi-tile backward (8 x 1500 frames, 20 heads) with parts of the work switched off, every barrier
+    hand-shake kept: which role bounds the tile rate."""
+    e = ops.ext()
+    L, heads, B = 1500, 20, 8
+    W = heads * 64
+    n = B * L
+    cu = (torch.arange(B + 1, dtype=torch.int32) * L).cuda()
+    qkv = torch.randn(n, 3 * W, device="cuda").bfloat16()
+    q, k, v = qkv[:, :W], qkv[:, W:2 * W], qkv[:, 2 * W:]
+    out = torch.empty(n, W, device="cuda", dtype=torch.bfloat16)
+    lse = torch.empty(heads, n, device="cuda")
+    e.attn_fwd(q, k, v, out, lse, cu, cu, heads, L, L, False, 0.125, 0.0, 1, 0)
+    dqkv = torch.empty_like(qkv)
+    dq_acc = torch.empty(n, W, device="cuda", dtype=torch.float32)
+    dout = torch.randn_like(out)
+    names = {0: "everything", 1: "no P/dS math", 2: "no dQ read-out", 32: "dQ staged, not added", 4: "no gradient MMAs", 8: "no S/dP MMAs",
+             12: "no MMAs", 3: "no math, no read-out", 15: "barriers only"}
+    try:
+        for bits, name in names.items():
+            e.set_attn_bwd_ablation(bits)
+
+            def run():
+                dq_acc.zero_()
+                e.attn_bwd(q, k, v, out, lse, dout, dqkv[:, :W], dqkv[:, W:2 * W], dqkv[:, 2 * W:], dq_acc, cu, cu, heads, L, L, False,
+                           0.125, 0.0, 1, 0)
+            rows.append({"kernel": "attention bwd 8 x 1500 pipelined, %s" % name, "ms": time_ms(run)})
+        # time line of the first CTA (SM clocks relative to its first stamp), one row per query tile
+        e.set_attn_bwd_ablation(128)
+        run()
+        torch.cuda.synchronize()
+        tr = e.attn_ws_trace()[:12]
+        t0 = int(tr[tr > 0].min())
+        names = ["Slo rdy", "Slo ld", "lo cmp", "lo st", "Shi rdy", "Shi ld", "hi cmp", "hi st", "iss Slo", "iss Shi", "iss G", "G done",
+                 "dQ stg", "dQ out", "TMA iss"]
+        print("time line of CTA 0 (SM clocks): " + " ".join("%8s" % n for n in names))
+        for i in range(12):
+            print("  tile %2d                      " % i + " ".join("%8d" % (int(v) - t0 if int(v) > 0 else -1) for v in tr[i][:15]))
+    finally:
+        e.set_attn_bwd_ablation(0)
+
+
 def bench_attention_long(rows):
     """The general multi-tile kernels on speech-length sequences: 8 x 1500 encoder frames with 20 heads (Whisper-large
     encoder self-attention, no dropout) and 8 x 448 causal with dropout 0.1 (decoder self-attention)."""
@@ -333,6 +375,8 @@ def main():
         bench_attention_ablation(rows)
     if "attn_long" in which:
         bench_attention_long(rows)
+    if "attn_long_ablate" in which:
+        bench_attention_long_ablation(rows)
     tf_peak, bw_peak, kind = peaks()
     for r in rows:
         line = "%-48s %8.3f ms" % (r["kernel"], r["ms"])

@@ -134,11 +134,14 @@ __device__ __forceinline__ uint32_t drop_mask16(const DropRng& rng, unsigned lon
 // >= k_lim do not exist); causal: key position kpos0 + j must not exceed q_pos.  A row past the sequence has lse2 = +inf,
 // so its probabilities are 0 without a per-element test.  dS is kept without the softmax scale (applied when dQ and dK
 // leave TMEM).  ds_out (optional): the 16 fp32 dS values of the existing pairs, for the gradient of an additive bias.
-__device__ __forceinline__ void bwd_compute16(const uint32_t (&sc)[16], const uint32_t (&dp)[16], uint32_t keep, bool do_drop,
-                                              float keep_scale, float Drow, float sl2, float lse2, int c0, int k_lim,
-                                              bool causal, int kpos0, int q_pos, uint4 (&vp)[2], uint4 (&vds)[2],
-                                              float* ds_out = nullptr) {
-  const bool full = !causal && c0 + 16 <= k_lim;
+// kMasked / kDrop are compile-time so that the common case (a tile inside both sequences, below the diagonal, no dropout)
+// carries no per-element predicate: with run-time flags the compiler evaluated the validity test and both dropout variants
+// for every element, which doubled the instruction count of the loop.
+template <bool kMasked, bool kDrop>
+__device__ __forceinline__ void bwd_compute16_t(const uint32_t (&sc)[16], const uint32_t (&dp)[16], uint32_t keep,
+                                                float keep_scale, float Drow, float sl2, float lse2, int c0, int k_lim,
+                                                bool causal, int kpos0, int q_pos, uint4 (&vp)[2], uint4 (&vds)[2],
+                                                float* ds_out) {
 #pragma unroll
   for (int g2 = 0; g2 < 2; ++g2) {
     __nv_bfloat162* a2 = reinterpret_cast<__nv_bfloat162*>(&vp[g2]);
@@ -149,10 +152,14 @@ __device__ __forceinline__ void bwd_compute16(const uint32_t (&sc)[16], const ui
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
         const int idx = g2 * 8 + 2 * j + e;
-        const bool valid = full || (c0 + idx < k_lim && (!causal || kpos0 + idx <= q_pos));
-        const float prob = valid ? ex2_approx(fmaf(__uint_as_float(sc[idx]), sl2, -lse2)) : 0.f;
+        float prob = ex2_approx(fmaf(__uint_as_float(sc[idx]), sl2, -lse2));
+        bool valid = true;
+        if (kMasked) {
+          valid = c0 + idx < k_lim && (!causal || kpos0 + idx <= q_pos);
+          prob = valid ? prob : 0.f;
+        }
         const float d = __uint_as_float(dp[idx]);
-        if (do_drop) {
+        if (kDrop) {
           const float kf = ((keep >> idx) & 1u) ? keep_scale : 0.f;
           pd[e] = prob * kf;
           ds[e] = prob * fmaf(d, kf, -Drow);
@@ -165,6 +172,19 @@ __device__ __forceinline__ void bwd_compute16(const uint32_t (&sc)[16], const ui
       a2[j] = __floats2bfloat162_rn(pd[0], pd[1]);
       b2[j] = __floats2bfloat162_rn(ds[0], ds[1]);
     }
+  }
+}
+__device__ __forceinline__ void bwd_compute16(const uint32_t (&sc)[16], const uint32_t (&dp)[16], uint32_t keep, bool do_drop,
+                                              float keep_scale, float Drow, float sl2, float lse2, int c0, int k_lim,
+                                              bool causal, int kpos0, int q_pos, uint4 (&vp)[2], uint4 (&vds)[2],
+                                              float* ds_out = nullptr) {
+  const bool full = !causal && c0 + 16 <= k_lim;
+  if (!do_drop) {
+    if (full) bwd_compute16_t<false, false>(sc, dp, keep, keep_scale, Drow, sl2, lse2, c0, k_lim, causal, kpos0, q_pos, vp, vds, ds_out);
+    else bwd_compute16_t<true, false>(sc, dp, keep, keep_scale, Drow, sl2, lse2, c0, k_lim, causal, kpos0, q_pos, vp, vds, ds_out);
+  } else {
+    if (full) bwd_compute16_t<false, true>(sc, dp, keep, keep_scale, Drow, sl2, lse2, c0, k_lim, causal, kpos0, q_pos, vp, vds, ds_out);
+    else bwd_compute16_t<true, true>(sc, dp, keep, keep_scale, Drow, sl2, lse2, c0, k_lim, causal, kpos0, q_pos, vp, vds, ds_out);
   }
 }
 // the two vectors of bwd_compute16 into the 128-byte-swizzled staging tiles (row t, columns c0 .. c0 + 15 of the tile)

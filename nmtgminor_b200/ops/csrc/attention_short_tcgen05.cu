@@ -443,7 +443,7 @@ attn_bwd_short_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
       uint32_t idle = 0;
       while (more || g_it < s_it) {
         bool progressed = false;
-        if (g_it < s_it && mbar_try_wait(pds_full, g_it & 1)) {
+        if (g_it < s_it && mbar_test_wait(pds_full, g_it & 1)) {
           tc_fence_after_sync();
           const int s = g_it & 1;
           const uint32_t set = tmem_base + s * 256;
@@ -469,8 +469,8 @@ attn_bwd_short_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
           ++g_it;
           progressed = true;
         }
-        if (more && s_it - g_it < 2 && mbar_try_wait(&slot_full[s_it & 1], (s_it >> 1) & 1) &&
-            mbar_try_wait(&set_free[s_it & 1], ((s_it >> 1) & 1) ^ 1)) {
+        if (more && s_it - g_it < 2 && mbar_test_wait(&slot_full[s_it & 1], (s_it >> 1) & 1) &&
+            mbar_test_wait(&set_free[s_it & 1], ((s_it >> 1) & 1) ^ 1)) {
           tc_fence_after_sync();
           const int s = s_it & 1;
           const uint32_t set = tmem_base + s * 256;
@@ -488,14 +488,14 @@ attn_bwd_short_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
         if (progressed) {
           idle = 0;
         } else {
-          if (++idle > 64) {
+          if (++idle > 4096) {        // a few microseconds of plain polling first: a sleep here delays every waiter
             if (*abort_word) break;
             if (idle > kBwdIssuePolls) {
               *abort_word = 1;
               if (p.status) atomicCAS(p.status, 0, static_cast<int>(kTimeoutTmemEmpty));
               break;
             }
-            __nanosleep(idle > 4096 ? 256 : 32);
+            __nanosleep(idle > 65536 ? 256 : 32);
           }
         }
       }
@@ -666,6 +666,7 @@ attn_bwd_short_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
 
 static int g_attn_bwd_ablate = 0;
 void set_attn_bwd_ablation(int bits) { g_attn_bwd_ablate = bits; }
+int get_attn_bwd_ablation() { return g_attn_bwd_ablate; }
 
 const char* launch_attn_fwd_short(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttnArgs& a,
                                   int num_items, cudaStream_t stream) {

@@ -647,11 +647,14 @@ const char* launch_attn_fwd_short(const CUtensorMap& tq, const CUtensorMap& tk, 
                                   int num_items, cudaStream_t stream);
 const char* launch_attn_bwd_short(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tdo,
                                   const AttnArgs& a, int num_items, cudaStream_t stream);
+const char* launch_attn_bwd_ws(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tdo,
+                               const CUtensorMap& tdq, const AttnArgs& a, dim3 grid, cudaStream_t stream);
 }  // namespace b200
 
 using namespace b200;
 
-static int g_attn_variant = 0;   // 0 = automatic, 1 = always the general multi-tile kernels
+// 0 = automatic, 1 = always the general multi-tile kernels, 2 = the general kernels without the warp-specialised backward
+static int g_attn_variant = 0;
 void nmtg_set_attention_variant(int v) { g_attn_variant = v; }
 
 static const char* check_ptr(const void* p, int ld) {
@@ -742,10 +745,16 @@ const char* nmtg_attn_bwd(const AttnDesc* d, cudaStream_t stream) {
       cached_tmap_f32(&tdq, d->dq_acc, d->total_q, width, d->ld_dqacc, kTile, 32))
     a.dq_tma = 1;
   dim3 grid((d->max_k + kTile - 1) / kTile, d->num_heads, d->batch);
-  if (d->bias) attn_bwd_kernel<true><<<grid, 256, kBwdSmem, stream>>>(tq, tk, tv, tdo, tdq, a);
-  else attn_bwd_kernel<false><<<grid, 256, kBwdSmem, stream>>>(tq, tk, tv, tdo, tdq, a);
-  cudaError_t ce = cudaGetLastError();
-  if (ce != cudaSuccess) return cudaGetErrorString(ce);
+  cudaError_t ce = cudaSuccess;
+  if (!d->bias && a.delta && a.dq_tma && g_attn_variant != 2) {
+    // sequences of several key tiles: the warp-specialised, pipelined kernel (attention_bwd_ws_tcgen05.cu)
+    if ((e = launch_attn_bwd_ws(tq, tk, tv, tdo, tdq, a, grid, stream))) return e;
+  } else {
+    if (d->bias) attn_bwd_kernel<true><<<grid, 256, kBwdSmem, stream>>>(tq, tk, tv, tdo, tdq, a);
+    else attn_bwd_kernel<false><<<grid, 256, kBwdSmem, stream>>>(tq, tk, tv, tdo, tdq, a);
+    ce = cudaGetLastError();
+    if (ce != cudaSuccess) return cudaGetErrorString(ce);
+  }
   if (d->max_k > kTile) {
     dim3 g2(64, d->batch);
     attn_dq_convert_kernel<<<g2, 256, 0, stream>>>(d->dq_acc, d->ld_dqacc, reinterpret_cast<__nv_bfloat16*>(d->dq), d->ld_dq,

@@ -60,6 +60,21 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
+// Non-blocking test of a phase.  mbarrier.try_wait may suspend the thread for a system-dependent time when the phase is not
+// complete, which is what a single waiter wants; a thread that polls SEVERAL barriers must use this one, or an incomplete
+// barrier delays its reaction to the others.
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
 // Bounded wait.  `abort_word` lives in shared memory and is raised by the first waiter that gives up;
 // every other waiter of the CTA then returns at its next poll.  Returns false on abort.
 #ifndef B200_WAIT_POLLS

@@ -537,6 +537,12 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("set_gemm_variant", [](int64_t v) { nmtg_set_gemm_variant(static_cast<int>(v)); });
   m.def("set_sm_reserve", [](int64_t n) { nmtg_set_sm_reserve(static_cast<int>(n)); });
   m.def("set_attn_bwd_ablation", [](int64_t v) { nmtg_set_attn_bwd_ablation(static_cast<int>(v)); });
+  m.def("attn_ws_trace", []() {
+    Tensor t = torch::zeros({512}, torch::kInt64);
+    const int n = nmtg_attn_ws_trace(reinterpret_cast<long long*>(t.data_ptr<int64_t>()), 512);
+    TORCH_CHECK(n >= 0, "attn_ws_trace: copy from the device failed");
+    return t.view({32, 16});
+  });
   m.def("set_gemm_trace", [](const OptTensor& buf) {
     if (buf.has_value()) {
       TORCH_CHECK(buf->is_cuda() && buf->scalar_type() == at::kLong && buf->is_contiguous() && buf->numel() >= 16 * 128);

@@ -9,9 +9,10 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda"
 
 
-@pytest.fixture(params=[0, 1], ids=["auto", "general"])
+@pytest.fixture(params=[0, 1, 2], ids=["auto", "general", "general_no_ws"])
 def variant(request):
-    """0 = automatic choice (persistent single-tile kernels up to 128 tokens), 1 = general kernels only."""
+    """0 = automatic choice (persistent single-tile kernels up to 128 tokens), 1 = general kernels only, 2 = general kernels
+    without the warp-specialised backward."""
     ops.ext().set_attention_variant(request.param)
     yield request.param
     ops.ext().set_attention_variant(0)
@@ -283,3 +284,70 @@ def test_heads_narrower_than_64_run_on_the_kernels(hd, cross):
     assert _err(out, o_ref) < 2e-2
     for g, gr in zip(grads, g_ref):
         assert _err(g, gr) < 3e-2
+
+
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("ws", [1, 2], ids=["ws", "no_ws"])
+def test_long_sequences_walk_many_tiles(causal, ws):
+    """Sequences of up to six 128-token tiles: every double buffer of the pipelined backward is reused several times."""
+    torch.manual_seed(13)
+    ops.ext().set_attention_variant(ws)
+    try:
+        heads, W = 2, 128
+        lengths = [700, 333, 129, 5]
+        n = sum(lengths)
+        cu = _cu(lengths)
+        qkv = (torch.randn(n, 3 * W, device=DEV) * 0.7).bfloat16().requires_grad_(True)
+        out = ops.self_attention(qkv, cu, heads, max(lengths), causal=causal, dropout_p=0.0, training=True)
+        dout = torch.randn(n, W, device=DEV).bfloat16()
+        out.backward(dout)
+        assert ops.check_status() == 0
+        q32 = qkv.detach().float().requires_grad_(True)
+        o_ref = ref.attention(q32[:, :W], q32[:, W:2 * W], q32[:, 2 * W:], cu, cu, heads, causal, 0.0)
+        o_ref.backward(dout.float())
+        assert _err(out, o_ref) < 2e-2
+        g, gr = qkv.grad, q32.grad
+        assert _err(g[:, :W], gr[:, :W]) < 3e-2, "dq"
+        assert _err(g[:, W:2 * W], gr[:, W:2 * W]) < 3e-2, "dk"
+        assert _err(g[:, 2 * W:], gr[:, 2 * W:]) < 3e-2, "dv"
+        # encoder-decoder shape: 300 queries over 650 keys, and the dropout mask of the forward pass replayed
+        lq, lk = [300, 40], [650, 200]
+        cq, ck = _cu(lq), _cu(lk)
+        q = (torch.randn(sum(lq), W, device=DEV) * 0.7).bfloat16().requires_grad_(True)
+        kv = (torch.randn(sum(lk), 2 * W, device=DEV) * 0.7).bfloat16().requires_grad_(True)
+        o = ops.cross_attention(q, kv, cq, ck, heads, max(lq), max(lk), 0.0, True)
+        do = torch.randn_like(o)
+        o.backward(do)
+        assert ops.check_status() == 0
+        q3, kv3 = q.detach().float().requires_grad_(True), kv.detach().float().requires_grad_(True)
+        o3 = ref.attention(q3, kv3[:, :W], kv3[:, W:], cq, ck, heads, False, 0.0)
+        o3.backward(do.float())
+        assert _err(o, o3) < 2e-2 and _err(q.grad, q3.grad) < 3e-2 and _err(kv.grad, kv3.grad) < 3e-2
+    finally:
+        ops.ext().set_attention_variant(0)
+
+
+def test_pipelined_backward_replays_the_dropout_mask_on_long_sequences():
+    """dV = P_drop^T dO checked through the linearity of the forward pass in V, on four key tiles."""
+    torch.manual_seed(3)
+    heads, W = 1, 64
+    lengths = [500, 260]
+    n = sum(lengths)
+    cu = _cu(lengths)
+    qkv = (torch.randn(n, 3 * W, device=DEV) * 0.5).bfloat16()
+    ops.manual_seed(11)
+    x = qkv.clone().requires_grad_(True)
+    ops.reset_stream_counter()
+    o = ops.self_attention(x, cu, heads, 500, dropout_p=0.2, training=True)
+    do = torch.randn_like(o)
+    o.backward(do)
+    assert ops.check_status() == 0
+    dv = x.grad[:, 2 * W:].float()
+    dirv = torch.randn(n, W, device=DEV).bfloat16()
+    x2 = qkv.clone()
+    x2[:, 2 * W:] = dirv
+    ops.reset_stream_counter()
+    o_dir = ops.self_attention(x2, cu, heads, 500, dropout_p=0.2, training=True)
+    lhs = (o_dir.float() * do.float()).sum().item()
+    rhs = (dv * dirv.float()).sum().item()
+    assert abs(lhs - rhs) <= 3e-2 * max(1.0, abs(lhs)), (lhs, rhs)
