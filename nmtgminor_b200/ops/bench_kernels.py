@@ -234,8 +234,21 @@ def bench_attention_long_ablation(rows):
                 e.attn_bwd(q, k, v, out, lse, dout, dqkv[:, :W], dqkv[:, W:2 * W], dqkv[:, 2 * W:], dq_acc, cu, cu, heads, L, L, False,
                            0.125, 0.0, 1, 0)
             rows.append({"kernel": "attention bwd 8 x 1500 pipelined, %s" % name, "ms": time_ms(run)})
-        # time line of the first CTA (SM clocks relative to its first stamp), one row per query tile
+        for bits, name in ((0, "taking turns at the exponentials"), (256, "no turns")):
+            e.set_attn_bwd_ablation(bits)
+            rows.append({"kernel": "attention fwd 8 x 1500 pipelined, %s" % name,
+                         "ms": time_ms(lambda: e.attn_fwd(q, k, v, out, lse, cu, cu, heads, L, L, False, 0.125, 0.0, 1, 0))})
+        # time lines of the first CTA (SM clocks relative to its first stamp), one row per key / query tile
         e.set_attn_bwd_ablation(128)
+        e.attn_fwd(q, k, v, out, lse, cu, cu, heads, L, L, False, 0.125, 0.0, 1, 0)
+        torch.cuda.synchronize()
+        tr = e.attn_fws_trace()[:12]
+        t0 = int(tr[tr > 0].min())
+        names = ["S rdy", "loaded", "max", "exps", "packed", "pv done", "staged", "-", "iss S0", "iss PV0", "iss S1", "iss PV1", "PV0 beg", "PV0 end",
+                 "S0 beg", "S0 end"]
+        print("forward, CTA 0 (SM clocks):     " + " ".join("%8s" % n for n in names))
+        for i in range(12):
+            print("  key tile %2d                  " % i + " ".join("%8d" % (int(v) - t0 if int(v) > 0 else -1) for v in tr[i][:16]))
         run()
         torch.cuda.synchronize()
         tr = e.attn_ws_trace()[:12]
@@ -276,6 +289,15 @@ def bench_attention_long(rows):
                        causal, 0.125, p, 1, 1)
         ms = time_ms(bwd)
         rows.append({"kernel": "attention bwd (incl. clearing the dQ accumulator)", "ms": ms, "tflops": 2.5 * fl / ms / 1e9})
+        # the kernels without warp specialisation (one role per CTA), for comparison
+        e.set_attention_variant(2)
+        try:
+            ms = time_ms(lambda: e.attn_fwd(q, k, v, out, lse, cu, cu, heads, L, L, causal, 0.125, p, 1, 1))
+            rows.append({"kernel": "  fwd, kernel without warp specialisation", "ms": ms, "tflops": fl / ms / 1e9})
+            ms = time_ms(bwd)
+            rows.append({"kernel": "  bwd, kernel without warp specialisation", "ms": ms, "tflops": 2.5 * fl / ms / 1e9})
+        finally:
+            e.set_attention_variant(0)
         # the library kernels on the same problem (padded [B, H, L, 64] layout, which favours them: no packing work)
         import torch.nn.functional as F
         qs, ks, vs = (torch.randn(B, heads, L, 64, device="cuda", dtype=torch.bfloat16, requires_grad=True) for _ in range(3))

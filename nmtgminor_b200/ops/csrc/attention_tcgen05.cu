@@ -647,13 +647,15 @@ const char* launch_attn_fwd_short(const CUtensorMap& tq, const CUtensorMap& tk, 
                                   int num_items, cudaStream_t stream);
 const char* launch_attn_bwd_short(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tdo,
                                   const AttnArgs& a, int num_items, cudaStream_t stream);
+const char* launch_attn_fwd_ws(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttnArgs& a, int max_q,
+                               cudaStream_t stream);
 const char* launch_attn_bwd_ws(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tdo,
                                const CUtensorMap& tdq, const AttnArgs& a, dim3 grid, cudaStream_t stream);
 }  // namespace b200
 
 using namespace b200;
 
-// 0 = automatic, 1 = always the general multi-tile kernels, 2 = the general kernels without the warp-specialised backward
+// 0 = automatic, 1 = always the general multi-tile kernels, 2 = the general kernels without their warp-specialised variants
 static int g_attn_variant = 0;
 void nmtg_set_attention_variant(int v) { g_attn_variant = v; }
 
@@ -683,6 +685,11 @@ const char* nmtg_attn_fwd(const AttnDesc* d, cudaStream_t stream) {
   a.bias = d->bias; a.bias_sb = d->bias_sb; a.bias_sh = d->bias_sh; a.bias_sq = d->bias_sq; a.dbias = nullptr;
   if (g_attn_variant == 0 && d->max_q <= kTile && d->max_k <= kTile && !d->bias)
     return launch_attn_fwd_short(tq, tk, tv, a, d->batch * d->num_heads, stream);
+  // Long sequences without attention dropout: the warp-specialised kernel (attention_fwd_ws_tcgen05.cu), two query tiles
+  // per CTA.  Measured against the kernel below: 0.233 / 0.264 ms on 8 x 1500 x 20 heads, but 0.070 / 0.053 ms on
+  // 8 x 448 causal (too few CTAs of 256 queries for 148 SMs), hence the length threshold; variant 1 ignores it (tests).
+  if (!d->bias && d->dropout_p <= 0.f && g_attn_variant != 2 && d->max_q > (g_attn_variant == 1 ? kTile : 4 * kTile))
+    return launch_attn_fwd_ws(tq, tk, tv, a, d->max_q, stream);
   static bool configured = false;
   if (!configured) {
     cudaError_t ce = cudaFuncSetAttribute(attn_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kFwdSmem);
@@ -746,8 +753,9 @@ const char* nmtg_attn_bwd(const AttnDesc* d, cudaStream_t stream) {
     a.dq_tma = 1;
   dim3 grid((d->max_k + kTile - 1) / kTile, d->num_heads, d->batch);
   cudaError_t ce = cudaSuccess;
-  if (!d->bias && a.delta && a.dq_tma && g_attn_variant != 2) {
-    // sequences of several key tiles: the warp-specialised, pipelined kernel (attention_bwd_ws_tcgen05.cu)
+  if (!d->bias && a.delta && a.dq_tma && g_attn_variant != 2 && (g_attn_variant == 1 || d->max_k > 4 * kTile)) {
+    // long sequences: the warp-specialised, pipelined kernel (attention_bwd_ws_tcgen05.cu); 0.587 / 0.664 ms on 8 x 1500 x 20
+    // heads and 0.313 / 0.336 ms on 8 x 1000 x 16 heads against the kernel below, level with it at 448 tokens
     if ((e = launch_attn_bwd_ws(tq, tk, tv, tdo, tdq, a, grid, stream))) return e;
   } else {
     if (d->bias) attn_bwd_kernel<true><<<grid, 256, kBwdSmem, stream>>>(tq, tk, tv, tdo, tdq, a);

@@ -537,6 +537,12 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("set_gemm_variant", [](int64_t v) { nmtg_set_gemm_variant(static_cast<int>(v)); });
   m.def("set_sm_reserve", [](int64_t n) { nmtg_set_sm_reserve(static_cast<int>(n)); });
   m.def("set_attn_bwd_ablation", [](int64_t v) { nmtg_set_attn_bwd_ablation(static_cast<int>(v)); });
+  m.def("attn_fws_trace", []() {
+    Tensor t = torch::zeros({512}, torch::kInt64);
+    const int n = nmtg_attn_fws_trace(reinterpret_cast<long long*>(t.data_ptr<int64_t>()), 512);
+    TORCH_CHECK(n >= 0, "attn_fws_trace: copy from the device failed");
+    return t.view({32, 16});
+  });
   m.def("attn_ws_trace", []() {
     Tensor t = torch::zeros({512}, torch::kInt64);
     const int n = nmtg_attn_ws_trace(reinterpret_cast<long long*>(t.data_ptr<int64_t>()), 512);

@@ -11,8 +11,9 @@ DEV = "cuda"
 
 @pytest.fixture(params=[0, 1, 2], ids=["auto", "general", "general_no_ws"])
 def variant(request):
-    """0 = automatic choice (persistent single-tile kernels up to 128 tokens), 1 = general kernels only, 2 = general kernels
-    without the warp-specialised backward."""
+    """0 = automatic choice (persistent single-tile kernels up to 128 tokens, warp-specialised multi-tile kernels for long
+    sequences), 1 = multi-tile kernels only, warp-specialised wherever they apply, 2 = multi-tile kernels without warp
+    specialisation."""
     ops.ext().set_attention_variant(request.param)
     yield request.param
     ops.ext().set_attention_variant(0)
