@@ -64,8 +64,9 @@ void nmtg_set_gemm_variant(int v);
 void nmtg_set_sm_reserve(int n);
 // Timing aid for the short-sequence attention backward: bit mask of work to leave out (see the kernel); 0 = everything.
 void nmtg_set_attn_bwd_ablation(int bits);
+// time stamps of one CTA of the pipelined attention backward / forward kernels (timing aids, see the kernels)
 int nmtg_attn_ws_trace(long long* out, int capacity);
-int nmtg_attn_fws_trace(long long* out, int capacity);   // time stamps of the pipelined attention backward (a timing aid)
+int nmtg_attn_fws_trace(long long* out, int capacity);
 // Profiling aid: device buffer of 16 int64 per CTA pair (at least 16 * #SMs / 2 entries) that the CTA-pair GEMM fills with
 // cycle counters of its MMA issuer and of one epilogue warp; nullptr switches it off.
 void nmtg_set_gemm_trace(long long* buf);
