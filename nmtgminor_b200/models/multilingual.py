@@ -10,6 +10,7 @@ pretrain_module/adapter.py:10,58.
 from __future__ import annotations
 
 import math
+from typing import Optional
 
 import torch
 import torch.nn as nn
@@ -58,6 +59,31 @@ class FactorizedLinear(nn.Module):
         return F.linear(x, self.weight_for(lang).to(x.dtype), self.bias.to(x.dtype) if self.bias is not None else None)
 
 
+class PartitionedLinear(nn.Module):
+    """Linear layer with partitioned weights (``-multilingual_partitioned_weights``): ``factor_size`` shared weight
+    matrices, mixed per language by that language's factor vector - ``W(lang) = sum_f factor[lang, f] * W_f`` (and the
+    same for the bias).  The factor table (an ``nn.Embedding(n_languages, factor_size)``) belongs to the model and is
+    shared by every layer.  Reference: onmt/modules/multilingual_partitioned/linear.py:6-49, factor table in
+    onmt/model_factory.py:480-482."""
+
+    def __init__(self, d_in, d_out, factors: nn.Embedding):
+        super().__init__()
+        f = factors.embedding_dim
+        self.d_in, self.d_out = d_in, d_out
+        self.shared_weight = nn.Parameter(torch.empty(d_out * d_in, f))
+        self.shared_bias = nn.Parameter(torch.zeros(d_out, f))
+        nn.init.normal_(self.shared_weight, 0.0, (2.0 / (d_in + d_out)) ** 0.5)
+        object.__setattr__(self, "_factors", factors)        # not a sub-module: the table is registered once, on the model
+
+    def weight_for(self, lang: int):
+        return torch.mv(self.shared_weight, self._factors.weight[lang]).view(self.d_out, self.d_in)
+
+    def forward(self, x, lang: int):
+        f = self._factors.weight[lang]
+        w = torch.mv(self.shared_weight, f).view(self.d_out, self.d_in)
+        return F.linear(x, w.to(x.dtype), torch.mv(self.shared_bias, f).to(x.dtype))
+
+
 class MultilingualLayerNorm(nn.Module):
     def __init__(self, dim, n_languages, eps=1e-5):
         super().__init__()
@@ -88,11 +114,11 @@ class MFWLayer(nn.Module):
     packed attention op; the projections are dense per-language weights applied with plain matrix products.
     Reference: onmt/models/multilingual_translator/relative_transformer_layers.py, onmt/modules/multilingual_factorized/*."""
 
-    def __init__(self, opt, n_languages: int, decoder: bool):
+    def __init__(self, opt, n_languages: int, decoder: bool, factors: Optional[nn.Embedding] = None):
         super().__init__()
         d, inner, r = opt.model_size, opt.inner_size, max(1, int(getattr(opt, "mfw_rank", 1)))
         bias = not getattr(opt, "mfw_no_bias", False)
-        lin = lambda i, o: FactorizedLinear(i, o, n_languages, rank=r, bias=bias,
+        lin = (lambda i, o: PartitionedLinear(i, o, factors)) if factors is not None else lambda i, o: FactorizedLinear(i, o, n_languages, rank=r, bias=bias,
                                             multiplicative=bool(getattr(opt, "mfw_multiplicative", False)),
                                             weight_drop=float(getattr(opt, "weight_drop", 0.0) or 0.0),
                                             activation=str(getattr(opt, "mfw_activation", "none") or "none"))
@@ -165,10 +191,16 @@ class MultilingualTransformer(Seq2SeqBase):
         # language-factorised layers replace the plain ones on the side(s) that ask for them
         self.mfw_enc = bool(getattr(opt, "multilingual_factorized_weights", False))
         self.mfw_dec = self.mfw_enc or bool(getattr(opt, "multilingual_factorized_weights_decoder", False))
+        factors = None
+        if getattr(opt, "multilingual_partitioned_weights", False):
+            # partitioned weights: every projection of both stacks is a per-language mixture of shared matrices
+            self.factor_embeddings = nn.Embedding(n_lang, int(getattr(opt, "mpw_factor_size", 8) or 8))
+            factors = self.factor_embeddings
+            self.mfw_enc = self.mfw_dec = True
         if self.mfw_enc:
-            self.encoder.layers = nn.ModuleList([MFWLayer(opt, n_lang, decoder=False) for _ in self.encoder.layers])
+            self.encoder.layers = nn.ModuleList([MFWLayer(opt, n_lang, decoder=False, factors=factors) for _ in self.encoder.layers])
         if self.mfw_dec:
-            self.decoder.layers = nn.ModuleList([MFWLayer(opt, n_lang, decoder=True) for _ in self.decoder.layers])
+            self.decoder.layers = nn.ModuleList([MFWLayer(opt, n_lang, decoder=True, factors=factors) for _ in self.decoder.layers])
         self.lang_embed = nn.Embedding(n_lang, opt.model_size)
         nn.init.normal_(self.lang_embed.weight, 0, opt.model_size ** -0.5)
         self.generator = Generator(opt.model_size, dicts["tgt"].size())
@@ -196,25 +228,57 @@ class MultilingualTransformer(Seq2SeqBase):
                 x = self.enc_adapters[i](x, lang)
         return self.encoder.final_norm(x), src
 
+    def _decode_prefix(self, tgt: PackedSeqs, memory, src: PackedSeqs, lang: int):
+        """The decoder stack with everything that depends on the target language: language embedding, factorised or
+        partitioned weights, adapters."""
+        dec = self.decoder
+        x = dec.embed(tgt, dec.emb_dropout if self.training else 0.0) + self.lang_embed.weight[lang].to(memory.dtype)
+        for i, layer in enumerate(dec.layers):
+            x = layer(x, tgt, lang, memory, src) if self.mfw_dec else layer(x, tgt, memory, src)
+            if self.use_adapters:
+                x = self.dec_adapters[i](x, lang)
+        return dec.final_norm(x)
+
     def forward(self, batch, **kw):
         lang = self._lang(batch, "target_lang", min(1, self.lang_embed.num_embeddings - 1))
         dec = self.decoder
-        if not hasattr(self, "_plain_decoder_forward"):
-            self._plain_decoder_forward = True
-
-        def decoder_forward(tgt, memory, src):
-            x = dec.embed(tgt, dec.emb_dropout) + self.lang_embed.weight[lang].to(memory.dtype)
-            for i, layer in enumerate(dec.layers):
-                x = layer(x, tgt, lang, memory, src) if self.mfw_dec else layer(x, tgt, memory, src)
-                if self.use_adapters:
-                    x = self.dec_adapters[i](x, lang)
-            return dec.final_norm(x)
         original = dec.forward
-        dec.forward = decoder_forward
+        dec.forward = lambda tgt, memory, src: self._decode_prefix(tgt, memory, src, lang)
         try:
             return super().forward(batch, **kw)
         finally:
             dec.forward = original
+
+    # Decoding.  The incremental caches of the plain layers know nothing of the language embedding, the per-language
+    # weights and the adapters, so every step runs the decoder over the whole prefix of every hypothesis with the same
+    # code as training: quadratic in the output length, and exactly the model that was trained.
+    supports_logits_step = False
+
+    @torch.no_grad()
+    def create_decoder_state(self, batch, beam_size: int = 1, **_unused):
+        from .transformer import DecodingState
+        context, src = self.encode(batch)
+        ctx_padded = src.pad(context, time_first=False)
+        lengths = (src.cu[1:] - src.cu[:-1]).to(torch.int64)[:ctx_padded.shape[0]]
+        pad_mask = torch.arange(ctx_padded.shape[1], device=ctx_padded.device)[None, :] >= lengths[:, None]
+        state = DecodingState(ctx_padded, pad_mask, 0, beam_size)
+        state.tgt_lang_id = self._lang(batch, "target_lang", min(1, self.lang_embed.num_embeddings - 1))
+        return state
+
+    @torch.no_grad()
+    def step(self, input_t, state, logits_only: bool = False):
+        from .layers import pack_padded
+        rows, t = input_t.shape
+        dev = input_t.device
+        tgt = PackedSeqs(input_t.reshape(-1), torch.arange(t, device=dev).repeat(rows),
+                         (torch.arange(rows + 1, device=dev, dtype=torch.int32) * t), t)
+        memory, src = pack_padded(state.context, (~state.src_pad_mask).sum(-1))
+        hidden = self._decode_prefix(tgt, memory, src, state.tgt_lang_id).view(rows, t, -1)[:, -1]
+        logits = self.generator(hidden)
+        state.position += 1
+        if logits_only:
+            return {"logits": logits, "hidden": hidden, "coverage": None}
+        return {"log_prob": torch.log_softmax(logits.float(), dim=-1), "hidden": hidden, "coverage": None}
 
 
 def register_builders(register):

@@ -183,8 +183,6 @@ UNSUPPORTED_FLAGS = {
     "decoder_layers_memory": "the n-gram memory decoder",
     "branchformer": "Branchformer cgMLP blocks",
     "wav2vec_spec_augment": "SpecAugment inside wav2vec 2.0 (time masking is the encoder's mask_prob)",
-    "multilingual_partitioned_weights": "partitioned (MPW) multilingual weights (the factorised MFW weights are built)",
-    "mpw_factor_size": "partitioned (MPW) multilingual weights",
     "multilingual_linear_projection": "per-language input projections",
     "pos_emb_type": "position-embedding variants of the legacy speech Transformer",
     "absolute_position_encoding": "absolute positions inside the relative speech Transformer",

@@ -520,3 +520,56 @@ def test_relative_attention_inside_the_wav2vec_encoder(dicts, tmp_path):
     out = model(synthetic_audio_batch(2, 120, "wav", 3000, 6000))
     out["loss"].backward()
     assert model.encoder.layers[0].attn.r_r_bias.grad is not None
+
+
+def test_partitioned_multilingual_weights(dicts):
+    """``-multilingual_partitioned_weights``: every projection is a per-language mixture of shared matrices, mixed by one
+    factor table that all layers share; a batch trains its own language's factor row only."""
+    from nmtgminor_b200.models.multilingual import PartitionedLinear
+    torch.manual_seed(10)
+    model = build_model(default_options(["-model", "multilingual_translator", "-multilingual_partitioned_weights", "-mpw_factor_size", "3"]
+                                        + COMMON), dicts)
+    lins = [m for m in model.modules() if isinstance(m, PartitionedLinear)]
+    assert lins and all(m._factors is model.factor_embeddings for m in lins)
+    assert model.factor_embeddings.weight.shape == (2, 3)
+    assert sum(1 for n, _ in model.named_parameters() if "factor_embeddings" in n) == 1       # registered once
+    lin = lins[0]
+    want = sum(model.factor_embeddings.weight[1, f] * lin.shared_weight[:, f] for f in range(3)).view(lin.d_out, lin.d_in)
+    assert torch.allclose(lin.weight_for(1), want, atol=1e-6)
+    batch = token_budget_batches(120, 4, 10, 60, 1, static=False, padded=True)[0]
+    batch.tensors["source_lang"] = torch.tensor([0])
+    batch.tensors["target_lang"] = torch.tensor([0])
+    out = model(batch)
+    out["loss"].backward()
+    g = model.factor_embeddings.weight.grad
+    assert g is not None and float(g[0].abs().sum()) > 0 and float(g[1].abs().sum()) == 0
+    model.eval()
+    hyps = beam_search(model, batch, BeamConfig(beam_size=2, max_len=4))
+    assert len(hyps) == batch.size
+
+
+@pytest.mark.parametrize("extra", [["-multilingual_adapter", "-adapter_bottleneck_size", "16"],
+                                   ["-multilingual_factorized_weights", "-mfw_rank", "2"],
+                                   ["-multilingual_partitioned_weights", "-mpw_factor_size", "3"]])
+def test_multilingual_decoding_matches_the_training_forward(dicts, extra):
+    """Step-by-step decoding of the multilingual model gives the distributions of the teacher-forced forward pass: the
+    language embedding, per-language weights and adapters all take part in decoding."""
+    torch.manual_seed(12)
+    model = build_model(default_options(["-model", "multilingual_translator"] + extra + COMMON), dicts).eval()
+    with torch.no_grad():
+        for m in model.modules():                      # adapters start as the identity: move them so that they matter
+            if hasattr(m, "up") and hasattr(m, "down"):
+                m.up.weight.normal_(0, 0.1)
+    batch = token_budget_batches(120, 4, 10, 60, 1, static=False, padded=True)[0]
+    batch.tensors["source_lang"] = torch.tensor([0])
+    batch.tensors["target_lang"] = torch.tensor([1])
+    with torch.no_grad():
+        out = model(batch, return_logits=True)
+        want = torch.log_softmax(out["logprobs"].float(), -1)          # [T, B, V]
+        tgt_in = batch.get("target_input")                              # [T, B]
+        lengths = batch.get("tgt_lengths")
+        state = model.create_decoder_state(batch, 1)
+        for t in range(min(4, tgt_in.shape[0])):
+            lp = model.step(tgt_in[:t + 1].t().contiguous(), state)["log_prob"]     # [B, V]
+            rows = (lengths > t).nonzero().squeeze(1) if lengths is not None else torch.arange(lp.shape[0])
+            assert torch.allclose(lp[rows], want[t][rows], atol=2e-4), (t, float((lp[rows] - want[t][rows]).abs().max()))
