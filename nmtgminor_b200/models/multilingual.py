@@ -201,6 +201,11 @@ class MultilingualTransformer(Seq2SeqBase):
             self.encoder.layers = nn.ModuleList([MFWLayer(opt, n_lang, decoder=False, factors=factors) for _ in self.encoder.layers])
         if self.mfw_dec:
             self.decoder.layers = nn.ModuleList([MFWLayer(opt, n_lang, decoder=True, factors=factors) for _ in self.decoder.layers])
+        # Where the language vector meets the sqrt(d) scaling of the word embeddings: the encoder scales the sum unless
+        # -encoder_early_emb_scale, the decoder scales the words only unless -decoder_late_emb_scale
+        # (reference: onmt/models/multilingual_translator/relative_transformer.py:113-152, 259-311)
+        self.enc_lang_scale = 1.0 if getattr(opt, "encoder_early_emb_scale", False) else math.sqrt(opt.model_size)
+        self.dec_lang_scale = math.sqrt(opt.model_size) if getattr(opt, "decoder_late_emb_scale", False) else 1.0
         self.lang_embed = nn.Embedding(n_lang, opt.model_size)
         nn.init.normal_(self.lang_embed.weight, 0, opt.model_size ** -0.5)
         self.generator = Generator(opt.model_size, dicts["tgt"].size())
@@ -221,7 +226,7 @@ class MultilingualTransformer(Seq2SeqBase):
         src = batch.packed_source()
         lang = self._lang(batch, "source_lang", 0)
         x = self.encoder.embed(src, self.encoder.emb_dropout)
-        x = x + self.lang_embed.weight[lang].to(x.dtype)
+        x = x + (self.lang_embed.weight[lang] * self.enc_lang_scale).to(x.dtype)
         for i, layer in enumerate(self.encoder.layers):
             x = layer(x, src, lang) if self.mfw_enc else layer(x, src)
             if self.use_adapters:
@@ -232,7 +237,7 @@ class MultilingualTransformer(Seq2SeqBase):
         """The decoder stack with everything that depends on the target language: language embedding, factorised or
         partitioned weights, adapters."""
         dec = self.decoder
-        x = dec.embed(tgt, dec.emb_dropout if self.training else 0.0) + self.lang_embed.weight[lang].to(memory.dtype)
+        x = dec.embed(tgt, dec.emb_dropout if self.training else 0.0) + (self.lang_embed.weight[lang] * self.dec_lang_scale).to(memory.dtype)
         for i, layer in enumerate(dec.layers):
             x = layer(x, tgt, lang, memory, src) if self.mfw_dec else layer(x, tgt, memory, src)
             if self.use_adapters:

@@ -310,8 +310,10 @@ class SpeechTransformerEncoder(nn.Module):
         self.cnn = bool(getattr(opt, "cnn_downsampling", False))
         self.channels = getattr(opt, "upsampling", 1) if False else 1
         if self.cnn:
-            self.conv = nn.Sequential(nn.Conv2d(1, 32, 3, stride=2, padding=1), nn.ReLU(), nn.BatchNorm2d(32),
-                                      nn.Conv2d(32, 32, 3, stride=2, padding=1), nn.ReLU(), nn.BatchNorm2d(32))
+            # -no_batch_norm: the two convolutions without BatchNorm2d (reference: onmt/models/transformers.py:100-105)
+            bn = (lambda: [nn.BatchNorm2d(32)]) if not getattr(opt, "no_batch_norm", False) else (lambda: [])
+            self.conv = nn.Sequential(nn.Conv2d(1, 32, 3, stride=2, padding=1), nn.ReLU(), *bn(),
+                                      nn.Conv2d(32, 32, 3, stride=2, padding=1), nn.ReLU(), *bn())
             feat = ((input_size + 1) // 2 + 1) // 2 * 32
             self.proj = nn.Linear(feat, dim)
         else:
@@ -323,6 +325,9 @@ class SpeechTransformerEncoder(nn.Module):
         self.final_norm = LayerNorm(dim)
         self.emb_dropout = opt.emb_dropout
         self.dim = dim
+        # -no_input_scale: projected frames are not multiplied by sqrt(model size) before the positions are added
+        # (reference: onmt/models/speech_recognizer/relative_transformer.py:49, 167)
+        self.input_scale = 1.0 if getattr(opt, "no_input_scale", False) else math.sqrt(dim)
 
     def forward(self, source):
         feats, lengths = split_audio_batch(source)
@@ -332,7 +337,7 @@ class SpeechTransformerEncoder(nn.Module):
             lengths = torch.div(torch.div(lengths + 1, 2, rounding_mode="floor") + 1, 2, rounding_mode="floor")
         else:
             x = feats.float()
-        x = self.proj(x) * math.sqrt(self.dim)
+        x = self.proj(x) * self.input_scale
         if x.shape[1] > self.positions.shape[0]:
             self.positions = sinusoidal_table(x.shape[1], self.dim).to(x.device)
         x = x + self.positions[:x.shape[1]].to(x.dtype)

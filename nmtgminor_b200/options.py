@@ -164,7 +164,6 @@ UNSUPPORTED_FLAGS = {
     "fusion": "language-model fusion",
     "reshape_speech": "frame reshaping of speech features (use -concat)",
     "bottleneck_size": "bottleneck adapters of the legacy speech models",
-    "no_batch_norm": "the Conv2d front end without batch normalisation",
     "depthwise_conv": "depthwise-convolution feed-forward blocks",
     "no_ffn": "layers without feed-forward blocks",
     "fast_factorize": "the fused factorised-weight kernels (the factorised weights run as plain GEMMs)",
@@ -186,9 +185,6 @@ UNSUPPORTED_FLAGS = {
     "multilingual_linear_projection": "per-language input projections",
     "pos_emb_type": "position-embedding variants of the legacy speech Transformer",
     "absolute_position_encoding": "absolute positions inside the relative speech Transformer",
-    "decoder_late_emb_scale": "late embedding scaling",
-    "encoder_early_emb_scale": "early embedding scaling",
-    "no_input_scale": "unscaled speech inputs of the relative speech Transformer",
     "char_ctc": "character-level CTC targets",
     "cache_dir": "cached encoder outputs",
     "memory_loss_coeff": "the n-gram memory decoder",

@@ -573,3 +573,22 @@ def test_multilingual_decoding_matches_the_training_forward(dicts, extra):
             lp = model.step(tgt_in[:t + 1].t().contiguous(), state)["log_prob"]     # [B, V]
             rows = (lengths > t).nonzero().squeeze(1) if lengths is not None else torch.arange(lp.shape[0])
             assert torch.allclose(lp[rows], want[t][rows], atol=2e-4), (t, float((lp[rows] - want[t][rows]).abs().max()))
+
+
+def test_small_structure_switches(dicts):
+    """``-no_batch_norm`` / ``-no_input_scale`` on the filterbank encoder, ``-encoder_early_emb_scale`` /
+    ``-decoder_late_emb_scale`` on the multilingual model."""
+    import math
+    import torch.nn as nn
+    args = ["-model", "speech_transformer", "-input_size", "40", "-cnn_downsampling"]
+    a = build_model(default_options(args + COMMON), dicts)
+    b = build_model(default_options(args + ["-no_batch_norm", "-no_input_scale"] + COMMON), dicts)
+    assert any(isinstance(m, nn.BatchNorm2d) for m in a.encoder.conv) and not any(isinstance(m, nn.BatchNorm2d) for m in b.encoder.conv)
+    assert a.encoder.input_scale == math.sqrt(a.encoder.dim) and b.encoder.input_scale == 1.0
+    out = b(synthetic_audio_batch(2, 120, "feats", 40, 80, n_feats=40))
+    assert torch.isfinite(out["loss"]).all()
+    m0 = build_model(default_options(["-model", "multilingual_translator"] + COMMON), dicts)
+    m1 = build_model(default_options(["-model", "multilingual_translator", "-encoder_early_emb_scale", "-decoder_late_emb_scale"] + COMMON), dicts)
+    d = m0.lang_embed.embedding_dim
+    assert (m0.enc_lang_scale, m0.dec_lang_scale) == (math.sqrt(d), 1.0)
+    assert (m1.enc_lang_scale, m1.dec_lang_scale) == (1.0, math.sqrt(d))
