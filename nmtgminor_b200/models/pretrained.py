@@ -505,6 +505,7 @@ def _wav2vec_from_opt(opt):
         mask_prob=getattr(opt, "wav2vec_spec_augment_mask_prob", 0.0) if hasattr(opt, "wav2vec_spec_augment_mask_prob") else 0.0,
         layerdrop=getattr(opt, "death_rate", 0.0) / 2,
         freeze_extractor=not getattr(opt, "unfreeze_feature_extractor", False),
+        mask_channel_prob=0.2 if getattr(opt, "wav2vec_spec_augment", False) else 0.0,
         gated_relative_position="wavlm" in name,
         num_buckets=_cfg(cfg, ["num_buckets"], 320), max_distance=_cfg(cfg, ["max_distance"], 800))
     if getattr(opt, "wav2vec2_relative_attention", False) or getattr(opt, "add_relative_attention", False):

@@ -195,8 +195,12 @@ class Wav2Vec2Encoder(nn.Module):
     def __init__(self, dim=1024, layers=24, heads=16, ffn=4096, dropout=0.1, attn_dropout=0.1, activation="gelu",
                  layer_norm_first=True, extractor_mode="layer_norm", conv_layers=W2V_LARGE_CONV, conv_bias=False,
                  mask_prob=0.0, mask_length=10, layerdrop=0.0, freeze_extractor=True, pos_kernel=128, pos_groups=16,
-                 dropout_input=0.0, gated_relative_position=False, num_buckets=320, max_distance=800):
+                 dropout_input=0.0, gated_relative_position=False, num_buckets=320, max_distance=800,
+                 mask_channel_prob=0.0, mask_channel_length=64):
         super().__init__()
+        # -wav2vec_spec_augment: spans of feature channels are zeroed per utterance during training (probability 0.2, span
+        # 64; reference: onmt/models/speech_recognizer/wav2vec2.py:188-190 -> fairseq's mask_channel_*)
+        self.mask_channel_prob, self.mask_channel_length = mask_channel_prob, mask_channel_length
         self.extractor = ConvFeatureExtractor(conv_layers, extractor_mode, conv_bias)
         self.freeze_extractor = freeze_extractor
         if freeze_extractor:
@@ -249,6 +253,10 @@ class Wav2Vec2Encoder(nn.Module):
         if self.training and self.mask_prob > 0:
             m = compute_mask_spans(B, T, out_len.cpu(), self.mask_prob, self.mask_length).to(x.device)
             x = torch.where(m.unsqueeze(-1), self.mask_emb.to(x.dtype).expand_as(x), x)
+        if self.training and self.mask_channel_prob > 0:
+            full = torch.full((B,), x.shape[2], dtype=torch.long)
+            cm = compute_mask_spans(B, x.shape[2], full, self.mask_channel_prob, self.mask_channel_length).to(x.device)
+            x = x.masked_fill(cm.unsqueeze(1), 0.0)
         x = x * valid.unsqueeze(-1)
         x = x + self.pos_conv(x)
         packed, seqs = pack_padded(x, out_len)

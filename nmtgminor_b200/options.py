@@ -181,7 +181,6 @@ UNSUPPORTED_FLAGS = {
     "encoder_layers_memory": "the n-gram memory decoder",
     "decoder_layers_memory": "the n-gram memory decoder",
     "branchformer": "Branchformer cgMLP blocks",
-    "wav2vec_spec_augment": "SpecAugment inside wav2vec 2.0 (time masking is the encoder's mask_prob)",
     "multilingual_linear_projection": "per-language input projections",
     "pos_emb_type": "position-embedding variants of the legacy speech Transformer",
     "absolute_position_encoding": "absolute positions inside the relative speech Transformer",

@@ -592,3 +592,24 @@ def test_small_structure_switches(dicts):
     d = m0.lang_embed.embedding_dim
     assert (m0.enc_lang_scale, m0.dec_lang_scale) == (math.sqrt(d), 1.0)
     assert (m1.enc_lang_scale, m1.dec_lang_scale) == (1.0, math.sqrt(d))
+
+
+def test_wav2vec_channel_masking(dicts, tmp_path):
+    """``-wav2vec_spec_augment``: spans of feature channels are zeroed in training and left alone in evaluation."""
+    torch.manual_seed(14)
+    enc = _cfg(tmp_path, "enc.json", encoder_embed_dim=512, encoder_layers=1, encoder_attention_heads=8, encoder_ffn_embed_dim=128)
+    dec = _cfg(tmp_path, "dec.json", d_model=64, decoder_layers=1, decoder_attention_heads=2, decoder_ffn_dim=128, vocab_size=120, pad_token_id=0)
+    model = build_model(default_options(["-model", "wav2vec2_bert", "-enc_config_file", enc, "-dec_config_file", dec, "-dec_pretrained_model",
+                                         "mbart50", "-wav2vec_spec_augment"] + COMMON), dicts)
+    assert model.encoder.mask_channel_prob == 0.2 and model.encoder.mask_channel_length == 64
+    batch = synthetic_audio_batch(2, 120, "wav", 3000, 6000)
+    seen = {}
+    model.encoder.pos_conv.register_forward_hook(lambda mod, inp, out: seen.__setitem__("x", inp[0].detach()))
+    model.train()
+    model(batch)
+    zero_cols = (seen["x"].abs().sum(1) == 0).sum(-1)                  # per utterance: channels that are zero at every frame
+    assert int(zero_cols.max()) >= 1
+    model.eval()
+    with torch.no_grad():
+        model(batch)
+    assert int((seen["x"].abs().sum(1) == 0).sum()) == 0
