@@ -275,7 +275,7 @@ class MultilingualTransformer(Seq2SeqBase):
         from .layers import pack_padded
         rows, t = input_t.shape
         dev = input_t.device
-        tgt = PackedSeqs(input_t.reshape(-1), torch.arange(t, device=dev).repeat(rows),
+        tgt = PackedSeqs(input_t.reshape(-1).long().contiguous(), torch.arange(t, device=dev).repeat(rows),
                          (torch.arange(rows + 1, device=dev, dtype=torch.int32) * t), t)
         memory, src = pack_padded(state.context, (~state.src_pad_mask).sum(-1))
         hidden = self._decode_prefix(tgt, memory, src, state.tgt_lang_id).view(rows, t, -1)[:, -1]

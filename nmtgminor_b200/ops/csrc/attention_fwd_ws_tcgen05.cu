@@ -5,8 +5,8 @@
 //
 //   warps 0-3   softmax of query tile 0: thread = query row (TMEM lane), all 128 key columns of the tile
 //   warps 4-7   softmax of query tile 1
-//   warp 8      TMA producer: Q tiles once, K and V tiles through rings of three stages each
-//   warps 9, 10 MMA issuers, one per query tile: S_g = Q_g K^T as soon as the softmax warps have read the previous S_g,
+//   warp 10     TMA producer: Q tiles once, K and V tiles through rings of three stages each
+//   warps 8, 9  MMA issuers, one per query tile: S_g = Q_g K^T as soon as the softmax warps have read the previous S_g,
 //               and O_g += P_g V as soon as P_g is stored
 //
 // TMEM (512 columns): S of tile 0 | S of tile 1 | O of tile 0 | O of tile 1 | P of tile 0 | P of tile 1 (64 columns each:
@@ -31,7 +31,6 @@ namespace b200 {
 constexpr int kFwsThreads = 352;
 constexpr int kFwsStages = 3;
 constexpr int kFwsSmem = 2 * kTileBytes + 2 * kFwsStages * kTileBytes + 512 + 1024;
-constexpr uint32_t kFwsIssuePolls = 1u << 22;
 
 // Time stamps (SM clock) of CTA (0, 0, 0) when ablation bit 128 is set: [key tile][16] = softmax warp 0: S ready, row
 // loaded, maximum, exponentials, packed, previous product done, staged | MMA warp: S of tile 0 issued, P V of tile 0
@@ -61,8 +60,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
   uint64_t* s_free = bars + 15;      // [2] S_g read -> MMA
   uint64_t* p_full = bars + 17;      // [2] P_g stored in tensor memory -> MMA
   uint64_t* pv_done = bars + 19;     // [2] P_g V of a key tile done: P_g may be overwritten, O_g may be touched
-  uint64_t* xu_turn = bars + 21;     // [2] the other query tile's warps are through their exponentials
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 23);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 21);
   volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   zero_tail_fwd(p);
@@ -82,7 +80,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     nkt[g] = q_rows[g] > 0 ? (p.causal ? min(total_kt, ((qt0 + g) * kTile + q_rows[g] + kTile - 1) / kTile) : total_kt) : 0;
   }
   const int nkt_max = max(nkt[0], nkt[1]);
-  const bool trace = (ablate & 128) && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 && (warp == 0 || warp == 9 || warp == 10);
+  const bool trace = (ablate & 128) && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 && (warp == 0 || warp == 8 || warp == 9);
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
@@ -97,7 +95,6 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
       mbar_init(&s_free[i], 128);
       mbar_init(&p_full[i], 128);
       mbar_init(&pv_done[i], 1);
-      mbar_init(&xu_turn[i], 128);
     }
     *abort_word = 0;
     mbar_fence_init();
@@ -108,7 +105,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 8) {
+  if (warp == 10) {
     // ---- TMA producer --------------------------------------------------------------------------------------------
     if (lane == 0 && nkt_max > 0) {
       mbar_expect_tx(q_full, (q_rows[1] > 0 ? 2 : 1) * kTileBytes);
@@ -125,69 +122,59 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         tma_load_2d(sV + st * kTileBytes, &tmap_v, &v_full[st], h * kHd, k_begin + kt * kTile);
       }
     }
-  } else if (warp == 9 || warp == 10) {
+  } else if (warp == 8 || warp == 9) {
     // ---- MMA issuers: one warp per query tile ------------------------------------------------------------------------
     // An MMA of these shapes is 32 to 64 clocks of tensor-core work, less than it costs a single thread that shares its
     // scheduler with two softmax warps to issue it; with one issuer per query tile the two chains S_g -> P_g V are issued
     // side by side.  K and V stages are released by both issuers (two arrivals each).
-    const int g = warp - 9;
+    const int g = warp - 8;
     const int n = g ? nkt[1] : nkt[0], n_other = g ? nkt[0] : nkt[1];
     if (lane == 0 && n > 0 && mbar_wait(q_full, 0, abort_word, p.status, kTimeoutTmaFull)) {
       const uint32_t idesc_s = make_idesc_bf16(kTile, kTile, 0, 0);
       const uint32_t idesc_o = make_idesc_bf16(kTile, kHd, 0, 1);
       const uint32_t tS = tmem_base + g * kTile, tO = tmem_base + 256 + g * 64, tP = tmem_base + 384 + g * 64;
       const uint32_t qa = smem_u32(sQ + g * kTileBytes);
-      int s_it = 0, pv_it = 0;
-      uint32_t idle = 0;
-      while (pv_it < n) {
-        bool progressed = false;
-        // S_g of key tile s_it: its K tile has landed and the softmax warps have read the previous S_g
-        if (s_it < n) {
-          const int kt = s_it, st = kt % kFwsStages;
-          if (mbar_test_wait(&k_full[st], (kt / kFwsStages) & 1) && (kt == 0 || mbar_test_wait(&s_free[g], (kt - 1) & 1))) {
-            tc_fence_after_sync();
-            if (g == 0) FWS_STAMP(kt, 14);
-            umma_steps(tS, qa, 16, 32, smem_u32(sK + st * kTileBytes), 16, 32, idesc_s, kHd / 16, false);
-            if (g == 0) FWS_STAMP(kt, 15);
-            umma_commit(&s_full[g]);
-            umma_commit(&k_free[st]);
-            if (kt >= n_other) umma_commit(&k_free[st]);     // the other query tile never reads this key tile
-            FWS_STAMP(kt, 8 + 2 * g);
-            ++s_it;
-            progressed = true;
-          }
-        }
-        // O_g += P_g V of key tile pv_it
-        if (pv_it < s_it) {
-          const int kt = pv_it, st = kt % kFwsStages;
-          if (mbar_test_wait(&p_full[g], kt & 1) && mbar_test_wait(&v_full[st], (kt / kFwsStages) & 1)) {
-            tc_fence_after_sync();
-            // A = P from tensor memory (8 columns per 16 keys), B = V (MN-major, 16 keys = 2048 bytes per k-step)
-            const uint64_t vdesc = make_smem_desc_sw128(smem_u32(sV + st * kTileBytes), 8192, 1024);
-            if (g == 0) FWS_STAMP(kt, 12);
+      // The events of one query tile come in a fixed order - S of key tile k read (s_free) before P of key tile k stored
+      // (p_full) - so the issuer blocks on them one after the other.  A blocked mbarrier wait costs no issue slots; an
+      // issuer that polls its barriers in a loop shares a scheduler with two softmax warps and slowed them down enough
+      // for them to finish thousands of clocks after the rest of their warpgroup.
+      bool ok = true;
+      auto issue_s = [&](int kt) -> bool {
+        const int st = kt % kFwsStages;
+        if (!mbar_wait(&k_full[st], (kt / kFwsStages) & 1, abort_word, p.status, kTimeoutTmaFull)) return false;
+        if (kt > 0 && !mbar_wait(&s_free[g], (kt - 1) & 1, abort_word, p.status, kTimeoutTmemEmpty)) return false;
+        tc_fence_after_sync();
+        if (g == 0) FWS_STAMP(kt, 14);
+        umma_steps(tS, qa, 16, 32, smem_u32(sK + st * kTileBytes), 16, 32, idesc_s, kHd / 16, false);
+        if (g == 0) FWS_STAMP(kt, 15);
+        umma_commit(&s_full[g]);
+        umma_commit(&k_free[st]);
+        if (kt >= n_other) umma_commit(&k_free[st]);     // the other query tile never reads this key tile
+        FWS_STAMP(kt, 8 + 2 * g);
+        return true;
+      };
+      ok = issue_s(0);
+      for (int kt = 0; kt < n && ok; ++kt) {
+        if (kt + 1 < n) ok = issue_s(kt + 1);
+        if (!ok) break;
+        const int st = kt % kFwsStages;
+        // O_g += P_g V of key tile kt
+        ok = mbar_wait(&p_full[g], kt & 1, abort_word, p.status, kTimeoutTmemEmpty) &&
+             mbar_wait(&v_full[st], (kt / kFwsStages) & 1, abort_word, p.status, kTimeoutTmaFull);
+        if (!ok) break;
+        if (g == 0) FWS_STAMP(kt, 7);
+        tc_fence_after_sync();
+        // A = P from tensor memory (8 columns per 16 keys), B = V (MN-major, 16 keys = 2048 bytes per k-step)
+        const uint64_t vdesc = make_smem_desc_sw128(smem_u32(sV + st * kTileBytes), 8192, 1024);
+        if (g == 0) FWS_STAMP(kt, 12);
 #pragma unroll
-            for (int k = 0; k < 8; ++k)
-              umma_bf16_ts(tO, tP + k * 8, vdesc + static_cast<uint64_t>((k * 2048) >> 4), idesc_o, (kt > 0 || k > 0) ? 1u : 0u);
-            if (g == 0) FWS_STAMP(kt, 13);
-            umma_commit(&pv_done[g]);
-            umma_commit(&v_free[st]);
-            if (kt >= n_other) umma_commit(&v_free[st]);
-            FWS_STAMP(kt, 9 + 2 * g);
-            ++pv_it;
-            progressed = true;
-          }
-        }
-        if (progressed) {
-          idle = 0;
-        } else if (++idle > 4096) {
-          if (*abort_word) break;
-          if (idle > kFwsIssuePolls) {
-            *abort_word = 1;
-            if (p.status) atomicCAS(p.status, 0, static_cast<int>(kTimeoutTmemEmpty));
-            break;
-          }
-          __nanosleep(idle > 65536 ? 256 : 32);
-        }
+        for (int k = 0; k < 8; ++k)
+          umma_bf16_ts(tO, tP + k * 8, vdesc + static_cast<uint64_t>((k * 2048) >> 4), idesc_o, (kt > 0 || k > 0) ? 1u : 0u);
+        if (g == 0) FWS_STAMP(kt, 13);
+        umma_commit(&pv_done[g]);
+        umma_commit(&v_free[st]);
+        if (kt >= n_other) umma_commit(&v_free[st]);
+        FWS_STAMP(kt, 9 + 2 * g);
       }
     }
   } else {
@@ -205,11 +192,6 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     const float scale_log2 = p.scale * 1.4426950408889634f;
     float m_run = kNegBig, l_run = 0.f;     // reference maximum (base-2 domain) and the row sum taken against it
     bool ok = true;
-    // The exponentials of one key tile keep the special-function units of the SM busy for about a thousand clocks.  When
-    // both query tiles walk over the same number of key tiles their warps take turns at them, which puts the two groups
-    // half a tile out of phase: one group's loads, maxima, packing and stores then run under the other's exponentials
-    // instead of both queueing for the same units at the same time.
-    const bool take_turns = nkt[0] == nkt[1] && !(ablate & 256);
 
     for (int kt = 0; kt < n && ok; ++kt) {
       ok = __all_sync(0xffffffffu, mbar_wait(&s_full[g], kt & 1, abort_word, p.status, kTimeoutTmemFull));
@@ -255,10 +237,6 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
       }
       const bool rescale = kt > 0 && __any_sync(0xffffffffu, alpha != 1.f);
       FWS_STAMP(kt, 2);
-      if (take_turns && (g == 1 || kt > 0)) {
-        ok = __all_sync(0xffffffffu, mbar_wait(&xu_turn[g], (g == 1 ? kt : kt - 1) & 1, abort_word, p.status, kTimeoutTmemFull));
-        if (!ok) break;
-      }
       // probabilities against the reference maximum, in place; masked scores (-1e30 * scale) give exactly 0
       float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
 #pragma unroll
@@ -277,7 +255,6 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         r3[j] = __float_as_uint(e3);
       }
       l_run = l_run * alpha + ((s0 + s1) + (s2 + s3));
-      if (take_turns) mbar_arrive(&xu_turn[g ^ 1]);
       FWS_STAMP(kt, 3);
       // bf16 packing first (the 128 fp32 values die here), then the wait for the previous product
       uint32_t pk0[32], pk1[32];     // keys 0..63 and 64..127 of the row, two bf16 per word
