@@ -329,6 +329,67 @@ class _SoftmaxFn(torch.autograd.Function):
         return _k("softmax_dropout_bwd")(dyd.contiguous(), y, scale, p, seed, stream), None, None, None, None, None, None
 
 
+class _SoftmaxRecomputeFn(torch.autograd.Function):
+    """Same result as ``_SoftmaxFn`` but nothing of size ``x`` is kept for backward except ``x`` itself: the softmax is
+    recomputed from the input there (the reference's "recompute" backward variants, softmax_apex.h: dispatch_*_backward_recompute)."""
+
+    @staticmethod
+    def forward(ctx, x, pad_mask, rows_per_mask, scale, p, seed, stream):
+        yd, y = _k("softmax_dropout_fwd")(x.contiguous(), pad_mask, rows_per_mask, scale, p, seed, stream)
+        ctx.save_for_backward(x, pad_mask) if pad_mask is not None else ctx.save_for_backward(x)
+        ctx.cfg = (rows_per_mask, scale, p, seed, stream, pad_mask is not None)
+        return yd
+
+    @staticmethod
+    def backward(ctx, dyd):
+        rows_per_mask, scale, p, seed, stream, has_mask = ctx.cfg
+        x = ctx.saved_tensors[0]
+        pad_mask = ctx.saved_tensors[1] if has_mask else None
+        yd, y = _k("softmax_dropout_fwd")(x.contiguous(), pad_mask, rows_per_mask, scale, p, seed, stream)
+        y = y if p > 0 else yd
+        return _k("softmax_dropout_bwd")(dyd.contiguous(), y, scale, p, seed, stream), None, None, None, None, None, None
+
+
+def time_mask_from_lengths(lengths: torch.Tensor, cols: int) -> torch.Tensor:
+    """Key mask (nonzero = masked) ``[len(lengths), cols]`` for rows that may look at their first ``lengths[i]`` columns."""
+    return (torch.arange(cols, device=lengths.device)[None, :] >= lengths.to(torch.int64)[:, None]).to(torch.uint8)
+
+
+def masked_softmax_dropout(x, *, pad_mask: Optional[torch.Tensor] = None, additive_mask: Optional[torch.Tensor] = None,
+                           lengths: Optional[torch.Tensor] = None, rows_per_mask: int = 1, scale: float = 1.0, p: float = 0.0,
+                           drop_mask: Optional[torch.Tensor] = None, recompute: bool = False, training: bool = True):
+    """The softmax family of the reference's attention extensions (softmax_apex.h: plain, + dropout, + presampled dropout,
+    additive-masked, time-masked, backward from the saved output or recomputed from the input) behind one call:
+
+    * ``pad_mask`` (nonzero = masked, one row per ``rows_per_mask`` rows of ``x``) or ``lengths`` (time mask: row group i
+      sees its first ``lengths[i]`` columns) or ``additive_mask`` (float, broadcastable to ``x``, added to the scaled scores);
+    * ``p``: dropout drawn by the kernel from its counters, or ``drop_mask`` (presampled, already scaled by 1 / (1 - p));
+    * ``recompute``: keep only ``x`` for backward and recompute the probabilities there.
+
+    Returns the (dropped) probabilities.  On a GPU everything but the additive mask and the presampled dropout mask (one
+    element-wise PyTorch op each) runs in the warp-per-row kernels."""
+    cols = x.shape[-1]
+    if lengths is not None:
+        if pad_mask is not None:
+            raise ValueError("give either pad_mask or lengths")
+        pad_mask = time_mask_from_lengths(lengths, cols)
+    if additive_mask is not None:
+        x = x + (additive_mask / scale if scale != 1.0 else additive_mask).to(x.dtype)
+    p_kernel = 0.0 if drop_mask is not None else (p if training else 0.0)
+    if not x.is_cuda:
+        drop = drop_mask
+        if drop is None and p_kernel > 0:
+            drop = (torch.rand(x.shape) >= p_kernel).float() / (1 - p_kernel)
+        return softmax_dropout_reference(x, pad_mask, rows_per_mask, scale, drop)[0]
+    if pad_mask is not None:
+        pad_mask = pad_mask.to(torch.uint8).contiguous()
+    if recompute:
+        out = _SoftmaxRecomputeFn.apply(x, pad_mask, rows_per_mask, scale, p_kernel, _Rng.seed, next_stream())
+    else:
+        out = _SoftmaxFn.apply(x, pad_mask, rows_per_mask, scale, p_kernel, _Rng.seed, next_stream())[0]
+    return out * drop_mask.to(out.dtype) if drop_mask is not None else out
+
+
 def softmax_dropout(x, pad_mask: Optional[torch.Tensor] = None, rows_per_mask: int = 1, scale: float = 1.0, p: float = 0.0,
                     training: bool = True):
     """Returns ``(dropout(softmax(scale * x + mask)), softmax(...))`` over the last axis; ``pad_mask`` (nonzero = masked)

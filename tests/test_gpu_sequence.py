@@ -152,3 +152,43 @@ def test_softmax_mask_dropout(dtype):
     g = kept.float() * 2.0
     expect = y2 * (g - (g * y2).sum(-1, keepdim=True))
     assert torch.allclose(x2.grad, expect, atol=1e-5)
+
+
+def test_softmax_family_variants_on_the_kernels():
+    """Time mask, additive mask, presampled dropout and the recompute backward against the fp32 PyTorch formulas."""
+    torch.manual_seed(6)
+    dev = _dev()
+    B, H, Tq, Tk = 2, 3, 5, 90
+    x = torch.randn(B, H, Tq, Tk, device=dev, requires_grad=True)
+    lengths = torch.tensor([90, 41], device=dev)
+    w = torch.randn(B, H, Tq, Tk, device=dev)
+
+    def plain(xx, add=None, drop=None):
+        s = xx * 0.5
+        if add is not None:
+            s = s + add
+        s = s.masked_fill((torch.arange(Tk, device=dev)[None, :] >= lengths[:, None])[:, None, None, :], float("-inf"))
+        y = torch.softmax(s, -1)
+        return y * drop if drop is not None else y
+
+    add = torch.randn(B, 1, 1, Tk, device=dev)
+    drop = (torch.rand(B, H, Tq, Tk, device=dev) > 0.3).float() / 0.7
+    for recompute in (False, True):
+        xr = x.detach().clone().requires_grad_()
+        got = S.masked_softmax_dropout(x, lengths=lengths, rows_per_mask=H * Tq, scale=0.5, additive_mask=add, drop_mask=drop,
+                                       recompute=recompute)
+        want = plain(xr, add, drop)
+        assert torch.allclose(got, want, atol=1e-5), recompute
+        x.grad = None
+        (got * w).sum().backward()
+        (want * w).sum().backward()
+        assert torch.allclose(x.grad, xr.grad, atol=1e-5), recompute
+    # kernel-drawn dropout with the recompute backward: the mask of the forward pass is regenerated
+    x2 = torch.randn(32, 128, device=dev, requires_grad=True)
+    yd = S.masked_softmax_dropout(x2, p=0.5, recompute=True)
+    kept = yd != 0
+    y = torch.softmax(x2.detach(), -1)
+    assert torch.allclose(yd[kept], y[kept] * 2.0, rtol=1e-4)
+    yd.sum().backward()
+    g = kept.float() * 2.0
+    assert torch.allclose(x2.grad, y * (g - (g * y).sum(-1, keepdim=True)), atol=1e-5)

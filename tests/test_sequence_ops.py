@@ -73,3 +73,23 @@ def test_cauchy_and_softmax_reference():
     mask = torch.tensor([[0, 0, 0, 1, 1], [0, 0, 0, 0, 0]], dtype=torch.bool)
     yd, y = S.softmax_dropout(x, mask, rows_per_mask=3)
     assert torch.allclose(y.sum(-1), torch.ones(6)) and y[:3, 3:].abs().sum() == 0
+
+
+def test_softmax_family_variants_on_the_reference_path():
+    """Time mask, additive mask, presampled dropout and the recompute switch give the plain formulas (CPU statement)."""
+    import torch
+    from nmtgminor_b200.ops import sequence as S
+    torch.manual_seed(0)
+    x = torch.randn(2, 3, 5, 7)                               # [batch, heads, queries, keys]
+    lengths = torch.tensor([7, 4])
+    got = S.masked_softmax_dropout(x, lengths=lengths, rows_per_mask=15, scale=0.5)
+    want = torch.softmax((x * 0.5).masked_fill((torch.arange(7)[None, :] >= lengths[:, None])[:, None, None, :], float("-inf")), -1)
+    assert torch.allclose(got, want, atol=1e-6)
+    add = torch.randn(2, 1, 1, 7)
+    got = S.masked_softmax_dropout(x, additive_mask=add, scale=0.5)
+    assert torch.allclose(got, torch.softmax(x * 0.5 + add, -1), atol=1e-6)
+    drop = (torch.rand_like(x) > 0.3).float() / 0.7
+    got = S.masked_softmax_dropout(x, drop_mask=drop)
+    assert torch.allclose(got, torch.softmax(x, -1) * drop, atol=1e-6)
+    assert torch.allclose(S.masked_softmax_dropout(x, recompute=True), torch.softmax(x, -1), atol=1e-6)
+    assert S.time_mask_from_lengths(lengths, 7).tolist()[1] == [0, 0, 0, 0, 1, 1, 1]
