@@ -416,14 +416,14 @@ class _LayerNormResidualFn(torch.autograd.Function):
 def layer_norm_residual(x, weight, bias, eps=1e-5):
     """``(x, LN(x))`` for a pre-norm residual block ``x + f(LN(x))``: pass the first result as the residual."""
     if (fused_param(weight) and x.is_cuda and x.dim() == 2 and x.dtype == torch.bfloat16 and x.is_contiguous()
-            and x.shape[-1] <= 2048 and x.shape[-1] % 8 == 0 and torch.is_grad_enabled() and x.requires_grad):
+            and x.shape[-1] <= 16384 and x.shape[-1] % 8 == 0 and torch.is_grad_enabled() and x.requires_grad):
         return _LayerNormResidualFn.apply(x, weight.work, bias.work, getattr(weight, "main_grad", None),
                                           getattr(bias, "main_grad", None), eps)
     return x, layer_norm(x, weight, bias, eps)
 
 
 def layer_norm(x, weight, bias, eps=1e-5):
-    if fused_param(weight) and x.is_cuda and x.shape[-1] <= 2048 and x.shape[-1] % 8 == 0:
+    if fused_param(weight) and x.is_cuda and x.shape[-1] <= 16384 and x.shape[-1] % 8 == 0:
         shp = x.shape
         x2 = x.reshape(-1, shp[-1]).contiguous()
         if x2.dtype != torch.bfloat16:

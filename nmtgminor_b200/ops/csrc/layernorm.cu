@@ -2,7 +2,7 @@
 // registers between the statistics pass and the normalisation pass, fp32 statistics saved for backward.
 // Backward writes dx (optionally adding an incoming residual gradient) and accumulates the affine
 // gradients of all rows of a CTA in shared memory before one fp32 atomic add per column into the
-// (fp32, accumulating) gradient buffers.  Hidden size: any multiple of 8 up to 2048.
+// (fp32, accumulating) gradient buffers.  Hidden size: any multiple of 8 up to 16384 (a warp per row up to 2048, a CTA per row above).
 //
 // Covers what the reference's fast_layer_norm_cuda does (onmt/modules/extensions/layer_norm/
 // ln_fwd_kernels.cuh:7-108, ln_bwd_kernels.cuh:6-323) without the per-hidden-size kernel table.
@@ -220,6 +220,167 @@ ln_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restr
   }
 }
 
+// ---------------------------------------------------------------------------------------------------
+// Rows longer than 2048 elements (up to 16384): one CTA of 256 threads per row, rows dealt round-robin over the grid.
+// Thread t owns the 16-byte vectors t, t + 256, ... of every row, so its slice of the affine gradients stays in
+// registers over all the rows of the CTA and costs one atomic per column and CTA at the end.
+// ---------------------------------------------------------------------------------------------------
+constexpr int kWideThreads = 256;
+constexpr int kWideVec = 8;   // 8 vectors x 8 elements x 256 threads = 16384 elements
+
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float t = 0.f;
+#pragma unroll
+  for (int w = 0; w < kWideThreads / 32; ++w) t += red[w];
+  __syncthreads();       // red may be written again right away
+  return t;
+}
+
+__global__ void __launch_bounds__(kWideThreads)
+ln_fwd_wide_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ gamma,
+                   const __nv_bfloat16* __restrict__ beta, __nv_bfloat16* __restrict__ y, float* __restrict__ mean,
+                   float* __restrict__ rstd, int rows, int hidden, float eps) {
+  __shared__ float red[kWideThreads / 32];
+  const int nvec = hidden >> 3;
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + static_cast<size_t>(row) * hidden);
+    float v[kWideVec][8];
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < kWideVec; ++i) {
+      const int vi = threadIdx.x + i * kWideThreads;
+      if (vi < nvec) {
+        const uint4 u = xr[vi];
+        const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = __bfloat1622float2(u2[j]);
+          v[i][2 * j] = f.x;
+          v[i][2 * j + 1] = f.y;
+          s += f.x + f.y;
+        }
+      }
+    }
+    const float mu = block_sum(s, red) / hidden;
+    float sq = 0.f;
+#pragma unroll
+    for (int i = 0; i < kWideVec; ++i)
+      if (threadIdx.x + i * kWideThreads < nvec) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) sq += (v[i][j] - mu) * (v[i][j] - mu);
+      }
+    const float rs = rsqrtf(block_sum(sq, red) / hidden + eps);
+    if (threadIdx.x == 0) {
+      if (mean) mean[row] = mu;
+      if (rstd) rstd[row] = rs;
+    }
+    uint4* yr = reinterpret_cast<uint4*>(y + static_cast<size_t>(row) * hidden);
+#pragma unroll
+    for (int i = 0; i < kWideVec; ++i) {
+      const int vi = threadIdx.x + i * kWideThreads;
+      if (vi < nvec) {
+        const uint4 g = __ldg(reinterpret_cast<const uint4*>(gamma) + vi), b = __ldg(reinterpret_cast<const uint4*>(beta) + vi);
+        const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&g);
+        const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&b);
+        uint4 o;
+        __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 gf = __bfloat1622float2(g2[j]), bf = __bfloat1622float2(b2[j]);
+          o2[j] = __floats2bfloat162_rn((v[i][2 * j] - mu) * rs * gf.x + bf.x, (v[i][2 * j + 1] - mu) * rs * gf.y + bf.y);
+        }
+        yr[vi] = o;
+      }
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kWideThreads)
+ln_bwd_wide_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x, const float* __restrict__ mean,
+                   const float* __restrict__ rstd, const __nv_bfloat16* __restrict__ gamma,
+                   const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dx, float* __restrict__ dgamma,
+                   float* __restrict__ dbeta, int rows, int hidden) {
+  __shared__ float red[kWideThreads / 32];
+  const int nvec = hidden >> 3;
+  float ag[kWideVec][8], ab[kWideVec][8];
+#pragma unroll
+  for (int i = 0; i < kWideVec; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) ag[i][j] = ab[i][j] = 0.f;
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const uint4* dyr = reinterpret_cast<const uint4*>(dy + static_cast<size_t>(row) * hidden);
+    const uint4* xr = reinterpret_cast<const uint4*>(x + static_cast<size_t>(row) * hidden);
+    const uint4* rr = dres ? reinterpret_cast<const uint4*>(dres + static_cast<size_t>(row) * hidden) : nullptr;
+    const float mu = mean[row], rs = rstd[row];
+    uint4 av[kWideVec], bv[kWideVec];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int i = 0; i < kWideVec; ++i) {
+      const int vi = threadIdx.x + i * kWideThreads;
+      av[i] = bv[i] = make_uint4(0u, 0u, 0u, 0u);
+      if (vi < nvec) {
+        av[i] = dyr[vi];
+        bv[i] = xr[vi];
+        const uint4 g = __ldg(reinterpret_cast<const uint4*>(gamma) + vi);
+        const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&av[i]);
+        const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&bv[i]);
+        const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&g);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 d = __bfloat1622float2(a2[j]), xv = __bfloat1622float2(b2[j]), gf = __bfloat1622float2(g2[j]);
+          const float xh0 = (xv.x - mu) * rs, xh1 = (xv.y - mu) * rs;
+          ag[i][2 * j] += d.x * xh0;
+          ag[i][2 * j + 1] += d.y * xh1;
+          ab[i][2 * j] += d.x;
+          ab[i][2 * j + 1] += d.y;
+          const float t0 = d.x * gf.x, t1 = d.y * gf.y;
+          s1 += t0 + t1;
+          s2 += t0 * xh0 + t1 * xh1;
+        }
+      }
+    }
+    s1 = block_sum(s1, red) / hidden;
+    s2 = block_sum(s2, red) / hidden;
+    uint4* dxr = reinterpret_cast<uint4*>(dx + static_cast<size_t>(row) * hidden);
+#pragma unroll
+    for (int i = 0; i < kWideVec; ++i) {
+      const int vi = threadIdx.x + i * kWideThreads;
+      if (vi < nvec) {
+        const uint4 g = __ldg(reinterpret_cast<const uint4*>(gamma) + vi);
+        const uint4 r = rr ? rr[vi] : make_uint4(0u, 0u, 0u, 0u);
+        const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&av[i]);
+        const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&bv[i]);
+        const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&g);
+        const __nv_bfloat162* r2 = reinterpret_cast<const __nv_bfloat162*>(&r);
+        uint4 o;
+        __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 d = __bfloat1622float2(a2[j]), xv = __bfloat1622float2(b2[j]), gf = __bfloat1622float2(g2[j]);
+          const float2 add = __bfloat1622float2(r2[j]);
+          const float xh0 = (xv.x - mu) * rs, xh1 = (xv.y - mu) * rs;
+          o2[j] = __floats2bfloat162_rn(rs * (d.x * gf.x - s1 - xh0 * s2) + add.x, rs * (d.y * gf.y - s1 - xh1 * s2) + add.y);
+        }
+        dxr[vi] = o;
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < kWideVec; ++i) {
+    const int vi = threadIdx.x + i * kWideThreads;
+    if (vi < nvec) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        if (dgamma) atomicAdd(dgamma + vi * 8 + j, ag[i][j]);
+        if (dbeta) atomicAdd(dbeta + vi * 8 + j, ab[i][j]);
+      }
+    }
+  }
+}
+
 template <typename F>
 static const char* dispatch_vpl(int hidden, F&& f) {
   const int need = (hidden / 8 + 31) / 32;
@@ -228,7 +389,7 @@ static const char* dispatch_vpl(int hidden, F&& f) {
   if (need <= 4) return f(std::integral_constant<int, 4>());
   if (need <= 5) return f(std::integral_constant<int, 5>());
   if (need <= 8) return f(std::integral_constant<int, 8>());
-  return "layernorm: hidden size above 2048 is not supported by the register-resident kernel";
+  return "layernorm: hidden size above 2048 belongs to the one-CTA-per-row kernels";
 }
 
 int num_sms();
@@ -241,6 +402,15 @@ const char* nmtg_layernorm_fwd(const void* x, const void* gamma, const void* bet
                                int rows, int hidden, float eps, cudaStream_t stream) {
   if (rows <= 0) return nullptr;
   if (hidden % 8) return "layernorm: hidden size must be a multiple of 8";
+  if (hidden > kWideVec * 8 * kWideThreads) return "layernorm: hidden size above 16384 is not supported";
+  if (hidden > 2048) {
+    const int g = rows < num_sms() * 4 ? rows : num_sms() * 4;
+    ln_fwd_wide_kernel<<<g, kWideThreads, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(x), reinterpret_cast<const __nv_bfloat16*>(gamma),
+                                                       reinterpret_cast<const __nv_bfloat16*>(beta), reinterpret_cast<__nv_bfloat16*>(y),
+                                                       mean, rstd, rows, hidden, eps);
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? nullptr : cudaGetErrorString(e);
+  }
   int grid = (rows + kLnWarps - 1) / kLnWarps;
   const int cap = num_sms() * 16;
   if (grid > cap) grid = cap;
@@ -287,6 +457,16 @@ const char* nmtg_layernorm_bwd(const void* dy, const void* x, const float* mean,
                                cudaStream_t stream) {
   if (rows <= 0) return nullptr;
   if (hidden % 8) return "layernorm: hidden size must be a multiple of 8";
+  if (hidden > kWideVec * 8 * kWideThreads) return "layernorm: hidden size above 16384 is not supported";
+  if (hidden > 2048) {
+    const int g = rows < num_sms() * 2 ? rows : num_sms() * 2;
+    ln_bwd_wide_kernel<<<g, kWideThreads, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(dy), reinterpret_cast<const __nv_bfloat16*>(x),
+                                                       mean, rstd, reinterpret_cast<const __nv_bfloat16*>(gamma),
+                                                       reinterpret_cast<const __nv_bfloat16*>(dres), reinterpret_cast<__nv_bfloat16*>(dx),
+                                                       dgamma, dbeta, rows, hidden);
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? nullptr : cudaGetErrorString(e);
+  }
   // Eight warps per CTA once there are enough rows: half as many CTAs end with their 2 * hidden atomics on the affine
   // gradients, the same number of warps per SM is resident (NMTG_LN_BWD_WARPS=4 restores the narrow CTAs for comparison)
   static const int forced = [] { const char* e = getenv("NMTG_LN_BWD_WARPS"); return e ? atoi(e) : 0; }();

@@ -18,7 +18,8 @@ def _close(a, b, atol, rtol, what):
     assert torch.allclose(a, b, atol=atol, rtol=rtol), "%s: max abs err %g (ref max %g)" % (what, err, b.abs().max().item())
 
 
-@pytest.mark.parametrize("rows,hidden", [(7, 256), (300, 512), (1000, 1024), (513, 1280), (64, 2048), (33, 264)])
+@pytest.mark.parametrize("rows,hidden", [(7, 256), (300, 512), (1000, 1024), (513, 1280), (64, 2048), (33, 264),
+                                         (40, 4096), (700, 5120), (9, 2056), (5, 16384)])
 def test_layernorm_fwd_bwd(rows, hidden):
     torch.manual_seed(0)
     x = (torch.randn(rows, hidden, device=DEV) * 2 + 0.5).bfloat16()
