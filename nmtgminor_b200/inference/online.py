@@ -96,23 +96,77 @@ class _BatchingWorker(threading.Thread):
                 s.done.set()
 
 
+def parse_request_fields(content_type: str, body: bytes) -> dict:
+    """Fields of a POST body: JSON, or ``multipart/form-data`` (values as bytes; file parts included) as the clients of
+    the reference's Flask servers send it (``pcm_s16le``, ``text``, ``prefix``, ``priority``)."""
+    ctype = (content_type or "").lower()
+    if ctype.startswith("multipart/form-data"):
+        from email.parser import BytesParser
+        msg = BytesParser().parsebytes(b"Content-Type: " + content_type.encode() + b"\r\n\r\n" + body)
+        return {part.get_param("name", header="content-disposition"): part.get_payload(decode=True) for part in msg.get_payload()
+                if part.get_param("name", header="content-disposition")}
+    if body:
+        try:
+            return json.loads(body)
+        except ValueError:
+            from urllib.parse import parse_qs
+            return {k: v[0] for k, v in parse_qs(body.decode("utf-8", "replace")).items()}
+    return {}
+
+
 def serve(config_path: str, host: str = "127.0.0.1", port: int = 5000, max_batch: int = 16):
-    worker = _BatchingWorker(OnlineTranslator(config_path), max_batch)
+    """HTTP server with request batching.  Routes: ``POST /`` with JSON ``{"text": ...}`` / ``{"texts": [...]}``; and the
+    routes of the reference's Flask servers (flask_mt.py / flask_online.py:163-215):
+    ``POST /predictions/<input_language>,<output_language>`` with the fields ``text`` (machine translation) or
+    ``pcm_s16le`` (raw 16-bit mono audio for speech models) and optionally ``prefix`` -> ``{"hypo": ...}``, and
+    ``GET /models/<input_language>,<output_language>`` -> the configuration the server runs."""
+    translator = OnlineTranslator(config_path)
+    worker = _BatchingWorker(translator, max_batch)
     worker.start()
+    with open(config_path) as fh:
+        config_text = fh.read()
 
     class Handler(BaseHTTPRequestHandler):
-        def do_POST(self):
-            body = json.loads(self.rfile.read(int(self.headers.get("Content-Length", 0)) or 0) or b"{}")
-            texts = body.get("texts") or [body.get("text", "")]
-            slots = [worker.submit(t) for t in texts]
-            for s in slots:
-                s.done.wait()
-            out = json.dumps({"translations": [s.result for s in slots]}).encode()
-            self.send_response(200)
+        def _reply(self, obj, code=200):
+            out = json.dumps(obj).encode()
+            self.send_response(code)
             self.send_header("Content-Type", "application/json")
             self.send_header("Content-Length", str(len(out)))
             self.end_headers()
             self.wfile.write(out)
+
+        def do_GET(self):
+            if self.path.startswith("/models/"):
+                return self._reply({"version": config_text})
+            self._reply({"error": "unknown route"}, 404)
+
+        def do_POST(self):
+            raw = self.rfile.read(int(self.headers.get("Content-Length", 0)) or 0)
+            body = parse_request_fields(self.headers.get("Content-Type", ""), raw)
+            if self.path.startswith("/predictions/"):
+                langs = self.path[len("/predictions/"):].split(",")
+                if len(langs) == 2:
+                    translator.set_language(langs[0], langs[1])
+                text = lambda v: v.decode("utf-8", "replace") if isinstance(v, (bytes, bytearray)) else v
+                prefix = text(body.get("prefix")) or None
+                try:
+                    if body.get("pcm_s16le") is not None:
+                        import numpy as np
+                        import torch
+                        wav = torch.from_numpy(np.frombuffer(body["pcm_s16le"], dtype="<i2").astype("float32") / 32768.0)
+                        with translator.lock:
+                            pred, *_ = translator.translator.translate([wav.view(-1, 1)], prefix=[prefix.split()] if prefix else None)
+                        hypo = " ".join(pred[0][0])
+                    else:
+                        hypo = translator.translate(text(body.get("text", "")), prefix)
+                    return self._reply({"hypo": hypo})
+                except Exception as exc:      # a bad request must not take the server down
+                    return self._reply({"hypo": "", "status": 400, "error": str(exc)}, 400)
+            texts = body.get("texts") or [body.get("text", "")]
+            slots = [worker.submit(t) for t in texts]
+            for s in slots:
+                s.done.wait()
+            self._reply({"translations": [s.result for s in slots]})
 
         def log_message(self, *a):
             pass

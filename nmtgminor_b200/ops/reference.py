@@ -85,9 +85,10 @@ def attention(q, k, v, cu_q, cu_k, heads, causal, dropout_p, scale=None, return_
     qp, qm = pad_packed(q.view(q.shape[0], heads, d), cu_q, mq)
     kp, km = pad_packed(k.view(k.shape[0], heads, d), cu_k, mk)
     vp, _ = pad_packed(v.view(v.shape[0], heads, d), cu_k, mk)
-    s = torch.einsum("bqhd,bkhd->bhqk", qp.float(), kp.float()) * scale
+    wt = torch.float64 if q.dtype == torch.float64 else torch.float32        # fp64 inputs (gradient checks) stay in fp64
+    s = torch.einsum("bqhd,bkhd->bhqk", qp.to(wt), kp.to(wt)) * scale
     if bias is not None:
-        s = s + bias[:, :, :mq, :mk].float()
+        s = s + bias[:, :, :mq, :mk].to(wt)
     s = s.masked_fill(~km[:, None, None, :], float("-inf"))
     if causal:
         tri = torch.ones(mq, mk, dtype=torch.bool, device=q.device).tril()
@@ -96,7 +97,7 @@ def attention(q, k, v, cu_q, cu_k, heads, causal, dropout_p, scale=None, return_
     p = torch.nan_to_num(p, nan=0.0)
     if dropout_p > 0:
         p = F.dropout(p, dropout_p, True)
-    o = torch.einsum("bhqk,bkhd->bqhd", p, vp.float()).to(q.dtype)
+    o = torch.einsum("bhqk,bkhd->bqhd", p, vp.to(wt)).to(q.dtype)
     out = unpad_packed(o.reshape(o.shape[0], o.shape[1], heads * d), cu_q, q.shape[0])
     if return_probs:
         return out, p

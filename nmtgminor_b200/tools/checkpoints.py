@@ -64,6 +64,35 @@ def extend_vocabulary(state: Dict[str, torch.Tensor], keys: List[str], new_size:
     return state
 
 
+def extend_pretrained_vocab(weights: Dict[str, torch.Tensor], keys: List[str], base_size: int, extra: int, seed: int = 0):
+    """Embedding tables of a pre-trained model (DeltaLM, mBART) grown for ``extra`` new symbols, e.g. speech units: the
+    first ``base_size`` rows are kept (rows past them, the pre-training mask tokens, are dropped) and every new row
+    starts as a copy of a randomly chosen kept row, so that it lies inside the distribution the model was trained
+    with.  (reference: tools/extend_deltalm_vocab.py:17-72)"""
+    gen = torch.Generator().manual_seed(seed)
+    for k in keys:
+        if k not in weights:
+            continue
+        w = weights[k]
+        if w.shape[0] < base_size:
+            raise ValueError("%s has %d rows, fewer than the base vocabulary of %d" % (k, w.shape[0], base_size))
+        picks = torch.randint(0, base_size, (extra,), generator=gen)
+        weights[k] = torch.cat([w[:base_size], w[:base_size].index_select(0, picks)], 0).contiguous()
+    return weights
+
+
+def extend_vocab_file(path: str, extra: int, output: str = "") -> str:
+    """Appends ``__0__ .. __<extra-1>__`` with the next free ids to a ``<token> <id>`` vocabulary file."""
+    output = output or path + ".extend"
+    with open(path) as fh:
+        lines = fh.readlines()
+    with open(output, "w") as out:
+        out.writelines(l if l.endswith("\n") else l + "\n" for l in lines)
+        for i in range(extra):
+            out.write("__%d__ %d\n" % (i, len(lines) + i))
+    return output
+
+
 def rematch_embeddings(weight_old: torch.Tensor, dict_old, dict_new, init: torch.Tensor = None) -> torch.Tensor:
     """Rows of ``weight_old`` are copied to the ids the same token strings have in ``dict_new``."""
     out = init.clone() if init is not None else torch.zeros(dict_new.size(), weight_old.shape[1], dtype=weight_old.dtype).normal_(0, 0.02)
@@ -87,7 +116,20 @@ def main(argv=None):
     b.add_argument("-prefix", required=True)
     b.add_argument("-top", type=int, default=5)
     b.add_argument("-output", default="")
+    c = sub.add_parser("extend-vocab", help="grow the embedding tables of a pre-trained checkpoint for new symbols")
+    c.add_argument("-input", required=True, help="checkpoint with its tensors under 'weights', 'model' or at the top level")
+    c.add_argument("-vocab", required=True, help="'<token> <id>' vocabulary file")
+    c.add_argument("-extra", type=int, default=5946, help="number of new symbols (e.g. k-means units)")
+    c.add_argument("-base_size", type=int, default=250054)
+    c.add_argument("-keys", nargs="+", default=["tgt_embedding.embed_tokens.weight", "src_embedding.embed_tokens.weight"])
     args = ap.parse_args(argv)
+    if args.cmd == "extend-vocab":
+        ckpt = torch.load(args.input, map_location="cpu", weights_only=False)
+        holder = ckpt["weights"] if "weights" in ckpt else ckpt["model"] if "model" in ckpt else ckpt
+        extend_pretrained_vocab(holder, args.keys, args.base_size, args.extra)
+        torch.save(ckpt, args.input + ".extend")
+        print(args.input + ".extend", extend_vocab_file(args.vocab, args.extra))
+        return
     if args.cmd == "average":
         print(average_checkpoints(args.models, args.output, args.method))
     else:

@@ -21,7 +21,7 @@ from typing import Iterable, Iterator, List, Optional, Sequence, Tuple
 import numpy as np
 import torch
 
-from ..data.audio import read_wav, write_ark_matrix
+from ..data.audio import read_ark_matrix, read_scp, read_wav, write_ark_matrix
 
 
 def read_wav_list(path: str) -> Iterator[Tuple[str, torch.Tensor]]:
@@ -142,6 +142,30 @@ def extract_tdnn(model_path: str, wav_list: str, ark_path: str, scp_path: str, b
     return n
 
 
+def verify_tdnn(model_path: str, wav_list: str, scp_path: str, batch_samples: int = 16000 * 60, layer: Optional[int] = None,
+                device="cpu", atol: float = 1e-5, rtol: float = 1e-5) -> Tuple[int, float]:
+    """Recomputes the features of every recording of ``wav_list`` and compares them with the matrices ``scp_path`` points
+    to (written earlier by ``extract_tdnn``): a check that a dump is still what the checkpoint produces, e.g. after the
+    model or the audio pipeline changed.  Returns (utterances checked, largest absolute difference); raises
+    ``AssertionError`` naming the first utterance outside the tolerance.  (reference: verify_wav2vec2_feat.py:91-114)"""
+    enc, _ = load_speech_encoder(model_path, device)
+    stored = read_scp(scp_path)
+    n, worst = 0, 0.0
+    for utts, waves in _batches(read_wav_list(wav_list), batch_samples):
+        for utt, f in zip(utts, encoder_frames(enc, waves, layer, device)):
+            if utt not in stored:
+                raise AssertionError("utterance %s is not in %s" % (utt, scp_path))
+            ref = torch.from_numpy(np.asarray(read_ark_matrix(*stored[utt]), dtype=np.float32))
+            if ref.shape != f.shape:
+                raise AssertionError("utterance %s: stored %s, recomputed %s" % (utt, tuple(ref.shape), tuple(f.shape)))
+            diff = (ref - f).abs()
+            worst = max(worst, float(diff.max()) if diff.numel() else 0.0)
+            if not bool((diff <= atol + rtol * ref.abs()).all()):
+                raise AssertionError("utterance %s differs from the stored features (max |diff| %.3g)" % (utt, float(diff.max())))
+            n += 1
+    return n, worst
+
+
 @torch.no_grad()
 def frame_codes(enc, quant, waves: Sequence[torch.Tensor], kmeans=None, layer: Optional[int] = None, device="cpu") -> List[List[str]]:
     """Per utterance one symbol per frame: ``"g0:g1"`` code indices of the product quantiser, or the k-means cluster."""
@@ -181,6 +205,7 @@ def main(argv=None, mode: str = "tdnn"):
     ap.add_argument("-model", required=True, help="checkpoint of this framework or a fairseq wav2vec 2.0 checkpoint")
     ap.add_argument("-src", required=True, help="list of recordings: <utt> <wav> [<start> <end>]")
     ap.add_argument("-scp_output", default="output.scp")
+    ap.add_argument("-scp", default="output.scp", help="verify mode: the scp file of the stored features")
     ap.add_argument("-ark_output", default="output.ark")
     ap.add_argument("-output", default="output.codes", help="codebook mode: text file with one utterance per line")
     ap.add_argument("-kmeans", default="", help="codebook mode: k-means model to label the frames with")
@@ -190,6 +215,10 @@ def main(argv=None, mode: str = "tdnn"):
     ap.add_argument("-fp16", action="store_true", help="accepted for command-line compatibility; extraction runs in fp32 / bf16")
     a = ap.parse_args(argv)
     dev = torch.device("cuda", a.gpu) if a.gpu >= 0 and torch.cuda.is_available() else torch.device("cpu")
+    if mode == "verify":
+        n, worst = verify_tdnn(a.model, a.src, a.scp, a.batch_size * 16000, a.layer, dev)
+        print("%d utterances match the stored features (largest difference %.3g)" % (n, worst))
+        return n
     if mode == "tdnn":
         n = extract_tdnn(a.model, a.src, a.ark_output, a.scp_output, a.batch_size * 16000, a.layer, dev)
     else:

@@ -1,5 +1,6 @@
 """wav2vec 2.0 feature / code extraction tools: wav list -> Kaldi ark / scp and per-frame discrete units."""
 import numpy as np
+import pytest
 import torch
 
 from nmtgminor_b200.data.audio import read_ark_matrix, read_scp, write_wav
@@ -72,6 +73,22 @@ def test_tdnn_features_to_ark_scp(tmp_path):
         direct = ref_enc.extractor(waves["utt1"][None])[0]
     assert torch.allclose(alone, direct[:alone.shape[0]], atol=1e-4)
     assert abs(waves["utt_seg"].numel() - 1600) <= 2
+    # the dump verifies against a recomputation with other batch boundaries; a changed model does not
+    from nmtgminor_b200.tools.extract import verify_tdnn
+    checked, worst = verify_tdnn(ck, lst, scp, batch_samples=100000, atol=1e-4)
+    assert checked == 4 and worst < 1e-4
+    import subprocess, sys, os
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, os.path.join(root, "verify_wav2vec2_feat.py"), "-model", ck, "-src", lst, "-scp", scp],
+                       capture_output=True, text=True)
+    assert r.returncode == 0 and "4 utterances match" in r.stdout, r.stdout + r.stderr
+    other = str(tmp_path / "w2v_other.pt")
+    state = torch.load(ck, weights_only=False)
+    k = next(k for k in state["model"] if "feature_extractor" in k and state["model"][k].dim() == 3)
+    state["model"][k] = state["model"][k] * 1.5
+    torch.save(state, other)
+    with pytest.raises(AssertionError, match="differs from the stored features"):
+        verify_tdnn(other, lst, scp)
     # states after one Transformer layer
     n = extract_tdnn(ck, lst, ark, scp, layer=1)
     path, off = read_scp(scp)["utt0"]

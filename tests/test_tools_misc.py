@@ -91,3 +91,28 @@ def test_rng_state_round_trip():
     got = (random.random(), float(np.random.rand()), torch.rand(3), ops.next_stream())
     assert want[0] == got[0] and want[1] == got[1] and torch.equal(want[2], got[2]) and want[3] == got[3]
     assert ops._Rng.seed == 77
+
+
+def test_reversible_stacks_pass_a_numerical_gradient_check():
+    from nmtgminor_b200.tools.grad_check import check_reversible
+    assert check_reversible(8, 2, 1, decoder=False)
+    assert check_reversible(8, 1, 2, decoder=True)
+
+
+def test_nbest_picker_and_pretrained_vocab_extension(tmp_path):
+    import torch
+    from nmtgminor_b200.tools.checkpoints import main as ckpt_main
+    from nmtgminor_b200.tools.nbest import pick_best
+    lines = ["a b ||| -1.0 2.0", "c d ||| -0.5 0.0", "e ||| -3.0 1.0", "f g ||| -2.0 9.0"]
+    assert list(pick_best(lines, 2, [1.0, 0.0])) == ["c d", "f g"]
+    assert list(pick_best(lines, 2, [1.0, 1.0])) == ["a b", "f g"]
+    w = {"weights": {"src_embedding.embed_tokens.weight": torch.randn(12, 4), "tgt_embedding.embed_tokens.weight": torch.randn(12, 4),
+                     "other": torch.randn(3)}}
+    kept = w["weights"]["src_embedding.embed_tokens.weight"][:10].clone()
+    torch.save(w, tmp_path / "d.pt")
+    (tmp_path / "v.txt").write_text("".join("t%d %d\n" % (i, i) for i in range(10)))
+    ckpt_main(["extend-vocab", "-input", str(tmp_path / "d.pt"), "-vocab", str(tmp_path / "v.txt"), "-extra", "5", "-base_size", "10"])
+    out = torch.load(str(tmp_path / "d.pt") + ".extend", weights_only=False)["weights"]["src_embedding.embed_tokens.weight"]
+    assert out.shape == (15, 4) and torch.equal(out[:10], kept)
+    assert all(any(torch.equal(r, k) for k in kept) for r in out[10:])
+    assert open(str(tmp_path / "v.txt") + ".extend").read().splitlines()[-1] == "__4__ 14"
