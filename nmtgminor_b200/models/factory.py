@@ -32,6 +32,8 @@ def build_model(opt, dicts, remove_pretrain: bool = False, constants=None):
         raise NotImplementedError("unknown model %r; registered: %s" % (name, sorted(_REGISTRY)))
     from ..options import validate_model_options
     validate_model_options(opt)
+    if getattr(opt, "fusion", False):
+        return build_fusion(opt, dicts, remove_pretrain)
     model = _REGISTRY[name](opt, dicts)
     init_model_parameters(model, opt)
     if int(getattr(opt, "predict_language", 0) or 0) > 0:
@@ -54,6 +56,17 @@ def build_model(opt, dicts, remove_pretrain: bool = False, constants=None):
         for m in model.modules():
             if isinstance(m, FeedForward):
                 m.weight_drop = float(opt.weight_drop)
+    if getattr(opt, "no_ffn", False) or getattr(opt, "depthwise_conv", False):
+        from .layers import EncoderLayer
+        layers = [m for m in getattr(model, "encoder", model).modules() if isinstance(m, EncoderLayer)]
+        if not layers:
+            raise NotImplementedError("-no_ffn / -depthwise_conv change the standard encoder layers; the encoder of model "
+                                      "'%s' is not built from them" % getattr(opt, "model", "?"))
+        for m in layers:
+            if getattr(opt, "depthwise_conv", False):
+                m.add_depthwise_conv(int(getattr(opt, "conv_kernel", 31) or 31))
+            if getattr(opt, "no_ffn", False):
+                m.drop_ffn()
     if getattr(opt, "stochastic_sublayer", False):
         from .layers import _LayerOptions
         for m in model.modules():
@@ -69,6 +82,32 @@ def build_model(opt, dicts, remove_pretrain: bool = False, constants=None):
         model.ctc_linear = nn.Linear(model.ctc_linear.in_features, aux.size())
         model.ctc_on_aux = True
     return model
+
+
+def build_fusion(opt, dicts, remove_pretrain: bool = False):
+    """``-fusion -lm_checkpoint lm.pt``: the translation model the other options describe, fused with the frozen language
+    model of the checkpoint (built from the checkpoint's own options over this run's target vocabulary); the fused
+    distribution is ``log_softmax(tm_logits + log p_lm)`` in training, scoring and search.
+    (reference: onmt/model_factory.py:913-935, onmt/legacy/FusionNetwork/Models.py:10-72)"""
+    import copy
+
+    import torch
+
+    from ..options import backward_compatible
+    from ..train.checkpoint import load_model_state
+    from .legacy import FusionNetwork
+    path = getattr(opt, "lm_checkpoint", "")
+    if not path:
+        raise ValueError("-fusion needs -lm_checkpoint (a checkpoint written by train_language_model.py)")
+    ckpt = torch.load(path, map_location="cpu", weights_only=False)
+    lm_opt = backward_compatible(ckpt["opt"])
+    lm_name = getattr(lm_opt, "model", "transformer_xl_lm")
+    lm = _REGISTRY[lm_name if lm_name in ("lstm_lm",) else "transformer_xl_lm"](lm_opt, dicts)
+    load_model_state(lm, ckpt["model"])
+    tm_opt = copy.copy(opt)
+    tm_opt.fusion = False
+    tm = build_model(tm_opt, dicts, remove_pretrain)
+    return FusionNetwork(tm, lm)
 
 
 def build_language_model(opt, dicts):

@@ -414,6 +414,34 @@ class _LayerOptions:
         return _scaled_sub(self, fn, h, x, p, seqs, *args, scale=scale)
 
 
+class PackedConvolution(nn.Module):
+    """Conformer convolution module on packed sequences: pointwise conv + GLU, depthwise conv over time (padding frames
+    zeroed so that no sequence sees its neighbour or its padding), per-frame LayerNorm over the channels (a batch of one
+    sequence and a padded batch give the same frames), SiLU, pointwise conv; called like the other
+    sub-layers (``residual`` / ``dropout_p`` keywords)."""
+
+    def __init__(self, dim: int, kernel: int = 31):
+        super().__init__()
+        if kernel % 2 == 0:
+            raise ValueError("-conv_kernel must be odd (got %d)" % kernel)
+        self.pw1 = nn.Conv1d(dim, 2 * dim, 1)
+        self.dw = nn.Conv1d(dim, dim, kernel, padding=kernel // 2, groups=dim)
+        self.norm = nn.LayerNorm(dim)
+        self.pw2 = nn.Conv1d(dim, dim, 1)
+
+    def forward(self, x, seqs: PackedSeqs, residual=None, dropout_p: float = 0.0):
+        from ..ops.reference import unpad_packed
+        padded = seqs.pad(x, time_first=False).float()                            # [B, T, C]
+        lengths = (seqs.cu[1:] - seqs.cu[:-1]).to(torch.int64)
+        valid = (torch.arange(padded.shape[1], device=x.device)[None, :] < lengths[:, None]).to(padded.dtype)
+        h = F.glu(self.pw1((padded * valid.unsqueeze(-1)).transpose(1, 2)), dim=1) * valid.unsqueeze(1)
+        h = F.silu(self.norm(self.dw(h).transpose(1, 2)))                          # [B, T, C]
+        h = self.pw2(h.transpose(1, 2)).transpose(1, 2)
+        y = unpad_packed(h.to(x.dtype), seqs.cu, x.shape[0])
+        y = F.dropout(y, dropout_p, self.training) if dropout_p > 0 else y
+        return y if residual is None else residual + y
+
+
 class EncoderLayer(nn.Module, _LayerOptions):
     """Self-attention + FFN block.  Pre-LN: x += D(Attn(LN(x))); x += D(FFN(LN(x))).  Post-LN (``post_norm``):
     x = LN(x + D(Attn(x))); x = LN(x + D(FFN(x))).  Optional stochastic depth (``death_rate``), ``rezero``, ``macaron``
@@ -429,7 +457,21 @@ class EncoderLayer(nn.Module, _LayerOptions):
         self.ffn = FeedForward(dim, inner, fd, activation, glu=glu)
         self.dropout = dropout
         self.death_rate = death_rate
+        self.conv = None
         self._init_options(dim, inner, fd, activation, post_norm, rezero, macaron, glu)
+
+    def drop_ffn(self):
+        """``-no_ffn``: the layer is attention (and the convolution block, if any) only.
+        (reference: onmt/models/speech_recognizer/relative_transformer_layers.py:49, 89-96)"""
+        self.ffn = self.ffn_norm = None
+
+    def add_depthwise_conv(self, kernel: int = 31):
+        """``-depthwise_conv``: a Conformer convolution block (pointwise GLU, depthwise convolution of ``kernel`` taps,
+        normalisation, SiLU, pointwise) between the attention and the feed-forward block, with its own LayerNorm and
+        residual.  (reference: onmt/models/speech_recognizer/relative_transformer_layers.py:136-143, 209-222)"""
+        dim = self.attn_norm.weight.shape[0]
+        self.conv_norm = LayerNorm(dim)
+        self.conv = PackedConvolution(dim, kernel)
 
     def forward(self, x, seqs: PackedSeqs):
         keep = self._survives
@@ -440,7 +482,9 @@ class EncoderLayer(nn.Module, _LayerOptions):
             x = self._block(2, self.mcr_norm, self.mcr_ffn, x, p, seqs, scale=0.5)
         if keep(True):
             x = self._block(0, self.attn_norm, self.attn, x, p, seqs, seqs)
-        if keep(True):
+        if self.conv is not None and keep(True):
+            x = self._block(4, self.conv_norm, self.conv, x, p, seqs, seqs)
+        if self.ffn is not None and keep(True):
             x = self._block(1, self.ffn_norm, self.ffn, x, p, seqs, scale=self.ffn_scale)
         return x
 

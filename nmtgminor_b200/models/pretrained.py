@@ -378,7 +378,7 @@ class SpeechToTextModel(Seq2SeqBase, _ReferenceNaming):
         return loss.sum()
 
     def encode(self, batch):
-        if getattr(self.encoder, "adapters", None) is not None:
+        if getattr(self.encoder, "adapters", None) is not None or getattr(self.encoder, "linear_proj", None) is not None:
             context, src = self.encoder(batch.get("source"), lang=single_language(batch, "source_lang"))
         else:
             context, src = self.encoder(batch.get("source"))
@@ -485,6 +485,8 @@ def _wav2vec_from_opt(opt):
     name = (getattr(opt, "enc_pretrained_model", "") or "wav2vec2").lower()
     if "s4" in name:
         from .mssm import build_stacked_mh_s4
+        if getattr(opt, "s4_config_file", ""):          # -s4_config_file: the state-space sizes have a file of their own
+            cfg = load_json_config(opt.s4_config_file)
         return build_stacked_mh_s4(getattr(opt, "input_size", 80), _cfg(cfg, ["encoder_embed_dim"], opt.model_size),
                                    _cfg(cfg, ["encoder_layers"], opt.layers), _cfg(cfg, ["num_heads"], 4),
                                    _cfg(cfg, ["state_dim"], 32), opt.dropout)
@@ -566,7 +568,8 @@ def register_builders(register):
 
     @register("speech_transformer", "hybrid_transformer")
     def _speech_transformer(opt, dicts):
-        from .transformer import TransformerDecoder
+        from .transformer import TransformerDecoder, _n_languages
+        opt.n_languages = max(_n_languages(dicts), int(getattr(opt, "n_languages", 0) or 0))
         enc = SpeechTransformerEncoder(opt, getattr(opt, "input_size", 40))
         embed = Embedding(dicts["tgt"].size(), opt.model_size, getattr(opt, "pad_idx", 0))
         dec = TransformerDecoder(opt, embed)

@@ -232,8 +232,11 @@ class RelativeTransformer(Seq2SeqBase):
         super().__init__()
         self.opt = opt
         pad = getattr(opt, "pad_idx", 0)
-        tgt_embed = Embedding(dicts["tgt"].size(), opt.model_size, pad, use_pos=False)
-        src_embed = Embedding(dicts["src"].size(), opt.model_size, pad, use_pos=False)
+        # -absolute_position_encoding: sinusoidal absolute positions are added to the embeddings on top of the relative
+        # attention (reference: onmt/models/multilingual_translator/relative_transformer.py:43, 54)
+        absolute = bool(getattr(opt, "absolute_position_encoding", False))
+        tgt_embed = Embedding(dicts["tgt"].size(), opt.model_size, pad, use_pos=absolute)
+        src_embed = Embedding(dicts["src"].size(), opt.model_size, pad, use_pos=absolute)
         if getattr(opt, "join_embedding", False):
             src_embed.weight = tgt_embed.weight
         self.encoder = RelativeTransformerEncoder(opt, src_embed)
@@ -285,6 +288,21 @@ class TransformerXLLanguageModel(nn.Module):
                                                               self.label_smoothing if self.training else 0.0, self.pad_idx,
                                                               grad_scale)
         return {"loss": loss, "correct": correct, "row_loss": row_loss, "hidden_packed": hidden, "tgt": tgt}
+
+
+def _xl_log_probs(self, tokens_tb):
+    """Next-token log-probabilities ``[T, B, V]`` of a prefix matrix ``[T, B]`` (every column is a full-length prefix);
+    what ``FusionNetwork`` asks of its language model."""
+    T, B = tokens_tb.shape
+    seqs = PackedSeqs.from_padded(tokens_tb.t().contiguous(), torch.full((B,), T, dtype=torch.int64, device=tokens_tb.device),
+                                  pad_idx=self.pad_idx)
+    with torch.no_grad():
+        hidden = self.decoder(seqs, None, None, None)
+        logits = self.generator(hidden).float()
+    return torch.log_softmax(logits, -1).view(B, T, -1).transpose(0, 1)
+
+
+TransformerXLLanguageModel.log_probs = _xl_log_probs
 
 
 def register_builders(register):

@@ -336,8 +336,14 @@ class SpeechTransformerEncoder(nn.Module):
         # -no_input_scale: projected frames are not multiplied by sqrt(model size) before the positions are added
         # (reference: onmt/models/speech_recognizer/relative_transformer.py:49, 167)
         self.input_scale = 1.0 if getattr(opt, "no_input_scale", False) else math.sqrt(dim)
+        # -multilingual_linear_projection: the encoder output goes through one square matrix per source language
+        # (reference: onmt/models/speech_recognizer/relative_transformer.py:72-76, 232-237)
+        self.linear_proj = None
+        if getattr(opt, "multilingual_linear_projection", False):
+            n = max(1, int(getattr(opt, "n_languages", 1) or 1))
+            self.linear_proj = nn.Parameter(torch.randn(n, dim, dim) * math.sqrt(2.0 / (dim + dim)))
 
-    def forward(self, source):
+    def forward(self, source, lang=None):
         feats, lengths = split_audio_batch(source)
         if self.cnn:
             x = self.conv(feats.unsqueeze(1).float())                     # [B, 32, T/4, F/4]
@@ -354,4 +360,9 @@ class SpeechTransformerEncoder(nn.Module):
         packed = packed.to(torch.bfloat16) if (packed.is_cuda and ops.fused_param(self.final_norm.weight)) else packed
         for layer in self.layers:
             packed = layer(packed, seqs)
-        return self.final_norm(packed), seqs
+        out = self.final_norm(packed)
+        if self.linear_proj is not None:
+            if lang is None:
+                raise ValueError("-multilingual_linear_projection needs the source language id of the batch")
+            out = out @ self.linear_proj[int(lang)].to(out.dtype)
+        return out, seqs

@@ -142,6 +142,8 @@ NO_EFFECT_IN_REFERENCE = {
     # the trainers add opt.contrastive_loss_coeff * outputs['contrastive_loss'], but no model of the reference ever puts
     # that key into its outputs (the speech models set the term to 0 and leave the assignment commented out)
     "contrastive_loss_coeff",
+    # parsed by the training script but never handed to a data set (frames are stacked at preprocessing, or with -concat)
+    "reshape_speech",
     # parsed into a per-data-set dictionary and handed to Dataset(dataset_factor=...), which never reads it
     "dataset_factors",
     # written to onmt.constants.residual_type; every reader of that constant is commented out
@@ -160,17 +162,11 @@ UNSUPPORTED_FLAGS = {
     "extra_context_size": "extra streaming context",
     "no_decoder": "encoder-only sequence models in the translation trainer",
     "favor_attention": "FAVOR+ attention inside the main Transformer (models/efficient_attention.py has the stand-alone layer)",
-    "lm_checkpoint": "language-model fusion",
-    "fusion": "language-model fusion",
-    "reshape_speech": "frame reshaping of speech features (use -concat)",
     "bottleneck_size": "bottleneck adapters of the legacy speech models",
-    "depthwise_conv": "depthwise-convolution feed-forward blocks",
-    "no_ffn": "layers without feed-forward blocks",
     "fast_factorize": "the fused factorised-weight kernels (the factorised weights run as plain GEMMs)",
     "flex_factorize": "flexible-rank factorised weights",
     "sub_encoder": "text sub-encoders behind the speech encoder",
     "enc_stacked_pretrained_model": "stacked pretrained encoders",
-    "s4_config_file": "S4 configuration files (the state-space encoder takes its sizes from -enc_config_file)",
     "load_pretrained_classifier": "pretrained classifier heads",
     "wav2vec2_quantize": "the wav2vec 2.0 quantiser inside the translation models (models/w2vbert.py has the quantiser)",
     "wav2vec2_dual_output": "dual-output wav2vec 2.0 encoders",
@@ -181,9 +177,7 @@ UNSUPPORTED_FLAGS = {
     "encoder_layers_memory": "the n-gram memory decoder",
     "decoder_layers_memory": "the n-gram memory decoder",
     "branchformer": "Branchformer cgMLP blocks",
-    "multilingual_linear_projection": "per-language input projections",
     "pos_emb_type": "position-embedding variants of the legacy speech Transformer",
-    "absolute_position_encoding": "absolute positions inside the relative speech Transformer",
     "char_ctc": "character-level CTC targets",
     "cache_dir": "cached encoder outputs",
     "memory_loss_coeff": "the n-gram memory decoder",

@@ -31,8 +31,22 @@ def _ln(ref_prefix):
 
 
 def transformer_to_reference(sd: Dict[str, torch.Tensor]) -> "OrderedDict[str, torch.Tensor]":
-    """State dict of ``models.transformer.Transformer`` -> reference key names."""
+    """State dict of ``models.transformer.Transformer`` -> reference key names.  Parameters the reference layout has no
+    name for here (residual gates of ``-rezero``, added convolution blocks, adapters ...) keep their own names, so that
+    nothing a structure switch added is lost between saving and loading."""
     out = OrderedDict()
+    native = sd
+
+    class _Tracked(dict):
+        def __init__(self, d):
+            super().__init__(d)
+            self.used = set()
+
+        def __getitem__(self, k):
+            self.used.add(k)
+            return super().__getitem__(k)
+
+    sd = _Tracked(native)
 
     def put(k, v):
         out[k] = v.detach().clone().float().cpu()
@@ -73,8 +87,13 @@ def transformer_to_reference(sd: Dict[str, torch.Tensor]) -> "OrderedDict[str, t
         n, r = "encoder.layers.%d" % i, "encoder.layer_modules.%d" % i
         norm(n + ".attn_norm", r + ".preprocess_attn")
         attn(n + ".attn", r + ".multihead", True)
-        norm(n + ".ffn_norm", r + ".preprocess_ffn")
-        ffn(n + ".ffn", r + ".feedforward")
+        if n + ".ffn_norm.weight" in sd:
+            norm(n + ".ffn_norm", r + ".preprocess_ffn")
+        if n + ".ffn.fc1.bias" in sd and n + ".ffn.fc2.bias" in sd:
+            ffn(n + ".ffn", r + ".feedforward")
+        if n + ".mcr_norm.weight" in sd:
+            norm(n + ".mcr_norm", r + ".preprocess_mcr_ffn")
+            ffn(n + ".mcr_ffn", r + ".mcr_feedforward")
     norm("encoder.final_norm", "encoder.postprocess_layer")
     put("decoder.word_lut.weight", sd["decoder.embed.weight"])
     n_dec = 1 + max([int(m.group(1)) for k in sd for m in [re.match(r"decoder\.layers\.(\d+)\.", k)] if m] + [-1])
@@ -86,11 +105,18 @@ def transformer_to_reference(sd: Dict[str, torch.Tensor]) -> "OrderedDict[str, t
             norm(n + ".cross_norm", r + ".preprocess_src_attn")
             attn(n + ".cross_attn", r + ".multihead_src", False)
         norm(n + ".ffn_norm", r + ".preprocess_ffn")
-        ffn(n + ".ffn", r + ".feedforward")
+        if n + ".ffn.fc1.bias" in sd and n + ".ffn.fc2.bias" in sd:
+            ffn(n + ".ffn", r + ".feedforward")
+        if n + ".mcr_norm.weight" in sd:
+            norm(n + ".mcr_norm", r + ".preprocess_mcr_ffn")
+            ffn(n + ".mcr_ffn", r + ".mcr_feedforward")
     norm("decoder.final_norm", "decoder.postprocess_layer")
     put("generator.0.linear.weight", sd["generator.weight"])
     if "generator.bias" in sd:
         put("generator.0.linear.bias", sd["generator.bias"])
+    for k, v in native.items():
+        if k not in sd.used:
+            put(k, v)
     return out
 
 
@@ -141,6 +167,8 @@ def transformer_from_reference(ref_sd: Dict[str, torch.Tensor], target_keys) -> 
         attn(n + ".attn", r + ".multihead", True)
         norm(n + ".ffn_norm", r + ".preprocess_ffn")
         ffn(n + ".ffn", r + ".feedforward")
+        norm(n + ".mcr_norm", r + ".preprocess_mcr_ffn")
+        ffn(n + ".mcr_ffn", r + ".mcr_feedforward")
     norm("encoder.final_norm", "encoder.postprocess_layer")
     for i in layer_ids("decoder"):
         n, r = "decoder.layers.%d" % i, "decoder.layer_modules.%d" % i
@@ -150,9 +178,14 @@ def transformer_from_reference(ref_sd: Dict[str, torch.Tensor], target_keys) -> 
         attn(n + ".cross_attn", r + ".multihead_src", False)
         norm(n + ".ffn_norm", r + ".preprocess_ffn")
         ffn(n + ".ffn", r + ".feedforward")
+        norm(n + ".mcr_norm", r + ".preprocess_mcr_ffn")
+        ffn(n + ".mcr_ffn", r + ".mcr_feedforward")
     norm("decoder.final_norm", "decoder.postprocess_layer")
     set_if("generator.weight", get("generator.0.linear.weight"))
     set_if("generator.bias", get("generator.0.linear.bias"))
+    for k, v in ref_sd.items():          # parameters saved under their own names (no reference name exists for them)
+        if k in target_keys and k not in out:
+            out[k] = v
     return out
 
 

@@ -117,3 +117,35 @@ def test_fusion_network_adds_a_frozen_language_model(dicts):
     assert torch.allclose(step0, expect[0], atol=2e-4)
     hyps = beam_search(fusion, batch, BeamConfig(beam_size=2, max_len=5))
     assert len(hyps) == batch.size
+
+
+@pytest.mark.parametrize("lm_name", ["transformer_xl_lm", "lstm_lm"])
+def test_fusion_flags_build_a_fused_model_from_a_language_model_checkpoint(dicts, tmp_path, lm_name):
+    """``-fusion -lm_checkpoint``: the factory loads the language model with its own options and freezes it."""
+    torch.manual_seed(4)
+    lm_opt = default_options(["-model", lm_name, "-model_size", "32", "-layers", "1", "-n_heads", "2", "-inner_size", "64",
+                              "-dropout", "0.0", "-attn_dropout", "0.0"])
+    lm = build_model(lm_opt, dicts)
+    ckpt = str(tmp_path / "lm.pt")
+    torch.save({"model": lm.state_dict(), "opt": lm_opt, "dicts": dicts}, ckpt)
+    with pytest.raises(ValueError, match="lm_checkpoint"):
+        build_model(default_options(["-model", "transformer", "-fusion"] + COMMON), dicts)
+    fused = build_model(default_options(["-model", "transformer", "-fusion", "-lm_checkpoint", ckpt] + COMMON), dicts)
+    assert isinstance(fused, FusionNetwork) and all(not p.requires_grad for p in fused.lm_model.parameters())
+    for (k, a), b in zip(lm.state_dict().items(), fused.lm_model.state_dict().values()):
+        assert torch.equal(a, b), k
+    batch = _batch()
+    out = fused(batch)
+    out["loss"].backward()
+    assert torch.isfinite(out["loss"]) and any(p.grad is not None and p.grad.abs().sum() > 0 for p in fused.tm_model.parameters())
+    fused.eval()
+    with torch.no_grad():
+        # the language model's prefix distribution equals its training-time forward pass
+        log_lm = fused.lm_model.log_probs(batch.get("target_input"))
+        tm_logits = fused.tm_model(batch, return_logits=True, compute_loss=False)["logprobs"].float()
+        state = fused.create_decoder_state(batch, 1)
+        step0 = fused.step(batch.get("target_input")[:1].t().contiguous(), state)["log_prob"]
+    assert torch.allclose(log_lm.exp().sum(-1), torch.ones_like(log_lm[..., 0]), atol=1e-4)
+    assert torch.allclose(step0, torch.log_softmax(tm_logits + log_lm, -1)[0], atol=2e-4)
+    hyps = beam_search(fused, batch, BeamConfig(beam_size=2, max_len=5))
+    assert len(hyps) == batch.size

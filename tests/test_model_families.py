@@ -613,3 +613,77 @@ def test_wav2vec_channel_masking(dicts, tmp_path):
     with torch.no_grad():
         model(batch)
     assert int((seen["x"].abs().sum(1) == 0).sum()) == 0
+
+
+def test_no_ffn_and_depthwise_conv_change_the_encoder_layers_and_survive_a_checkpoint(dicts):
+    from nmtgminor_b200.models.layers import EncoderLayer, PackedConvolution
+    from nmtgminor_b200.train.checkpoint import load_model_state, model_state_for_saving
+    torch.manual_seed(0)
+    flags = ["-model", "transformer", "-depthwise_conv", "-conv_kernel", "5", "-no_ffn", "-macaron"] + COMMON
+    model = build_model(default_options(flags), dicts)
+    enc_layers = [m for m in model.encoder.modules() if isinstance(m, EncoderLayer)]
+    assert enc_layers and all(isinstance(m.conv, PackedConvolution) and m.ffn is None for m in enc_layers)
+    assert not any(".ffn." in k for k in model.encoder.state_dict()) and any(".ffn." in k for k in model.decoder.state_dict())
+    from nmtgminor_b200.models.layers import PackedSeqs
+    batch = token_budget_batches(120, 4, 10, 60, 1, static=False, padded=True)[0]
+    out = model(batch)
+    out["loss"].backward()
+    assert torch.isfinite(out["loss"]) and enc_layers[0].conv.dw.weight.grad.abs().sum() > 0
+    # a sentence's encoding does not depend on what it is batched with (the convolution never reads across sequences)
+    model.eval()
+    with torch.no_grad():
+        src = batch.packed_source()
+        full = model.encoder(src)
+        n0 = int(src.cu[1])
+        first = PackedSeqs(src.tokens[:n0], src.positions[:n0], src.cu[:2], n0)
+        assert torch.allclose(model.encoder(first), full[:n0], atol=1e-5)
+    # structure switches add parameters; all of them come back from a saved state (also the macaron block and the gates)
+    with torch.no_grad():
+        for p in model.parameters():
+            p.add_(torch.randn_like(p) * 0.05)
+    saved = model_state_for_saving(model)
+    fresh = build_model(default_options(flags), dicts)
+    missing, unexpected = load_model_state(fresh, saved)
+    assert not missing and not unexpected
+    assert all(torch.allclose(a, b) for a, b in zip(model.state_dict().values(), fresh.state_dict().values()))
+    gated = build_model(default_options(["-model", "transformer", "-rezero"] + COMMON), dicts)
+    with torch.no_grad():
+        for m in gated.modules():
+            if hasattr(m, "gates"):
+                m.gates.fill_(0.3)
+    again = build_model(default_options(["-model", "transformer", "-rezero"] + COMMON), dicts)
+    assert load_model_state(again, model_state_for_saving(gated))[0] == []
+    assert float(again.encoder.layers[0].gates[0]) == pytest.approx(0.3)
+    with pytest.raises(NotImplementedError, match="no_ffn"):
+        build_model(default_options(["-model", "LSTM", "-no_ffn"] + COMMON), dicts)
+
+
+def test_per_language_output_projection_and_absolute_positions(dicts):
+    torch.manual_seed(0)
+    flags = ["-model", "speech_transformer", "-input_size", "40", "-multilingual_linear_projection"] + COMMON
+    model = build_model(default_options(flags), dicts).eval()
+    assert model.encoder.linear_proj.shape == (2, 64, 64)
+    batch = synthetic_audio_batch(3, 120, "feats", 40, 80, n_feats=40)
+    batch.tensors["source_lang"] = torch.tensor([1])
+    batch.tensors["target_lang"] = torch.tensor([0])
+    with torch.no_grad():
+        ctx1, _ = model.encode(batch)
+        model.encoder.linear_proj[1].copy_(torch.eye(64))
+        plain, _ = model.encode(batch)
+        model.encoder.linear_proj[1].mul_(2.0)
+        doubled, _ = model.encode(batch)
+        model.encoder.linear_proj[0].zero_()                      # another language's matrix is not read
+        assert torch.allclose(model.encode(batch)[0], doubled)
+    assert torch.allclose(doubled, 2 * plain, atol=1e-5) and not torch.allclose(ctx1, plain)
+    model.train()
+    model(batch)["loss"].backward()
+    g = model.encoder.linear_proj.grad
+    assert g[1].abs().sum() > 0 and g[0].abs().sum() == 0
+    # absolute positions on top of relative attention: the embedding now adds the sinusoidal table
+    rel = build_model(default_options(["-model", "relative_transformer"] + COMMON), dicts).eval()
+    both = build_model(default_options(["-model", "relative_transformer", "-absolute_position_encoding"] + COMMON), dicts).eval()
+    both.load_state_dict(rel.state_dict(), strict=False)
+    text = token_budget_batches(120, 4, 10, 60, 1, static=False, padded=True)[0]
+    with torch.no_grad():
+        a, b = rel.encode(text)[0], both.encode(text)[0]
+    assert a.shape == b.shape and not torch.allclose(a, b, atol=1e-3)
