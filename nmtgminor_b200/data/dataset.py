@@ -322,8 +322,15 @@ class Dataset(torch.utils.data.Dataset):
                  data_type="text", max_src_len=256, max_tgt_len=256, min_src_len=0, min_tgt_len=0, cleaning=True,
                  sorting=True, src_pad=C.PAD, tgt_pad=C.PAD, padded=True, packed=True, round_to=128, cut_off_size=256000,
                  smallest_batch_size=4, verbose=False, augmenter=None, create_reverse=False, past_src_data=None,
-                 aux_tgt_data=None, static_shapes=False, **_ignored):
+                 aux_tgt_data=None, static_shapes=False, concat=False, concat_seed=1234, **_ignored):
         self.src, self.tgt = src_data, tgt_data
+        # ``concat``: every training example is extended with randomly drawn other examples, sources joined along time
+        # and targets joined into one sentence, up to ``max_src_len`` (reference: onmt/data/dataset.py:863-865, 923-930,
+        # 1285-1340 ``collater_concat``, :25-130 ``merge_concat_data``)
+        self.concat = bool(concat)
+        self.concat_max_len = int(max_src_len)
+        concat_seed = int(concat_seed) % (2 ** 32)
+        self.concat_rng = np.random.RandomState(concat_seed)
         self.aux_tgt = aux_tgt_data            # second target per example ("triangle" corpora)
         self.past_src = past_src_data          # previous source sentence per example (document-context models)
         self.src_langs, self.tgt_langs, self.src_atbs, self.tgt_atbs = src_langs, tgt_langs, src_atbs, tgt_atbs
@@ -343,6 +350,14 @@ class Dataset(torch.utils.data.Dataset):
         else:
             lengths = self.src_sizes if self.src_sizes is not None else self.tgt_sizes
         order = np.arange(n, dtype=np.int64)
+        if self.concat:
+            # examples grow to about max_src_len each: a fixed number of them per batch, in random order
+            order = np.random.RandomState(concat_seed).permutation(n).astype(np.int64)
+            sorting = False
+            per_batch = max(1, int(batch_size_frames // max(1, max_src_len))) if batch_size_frames < 10 ** 12 else \
+                max(1, int(batch_size_words // max(1, max_src_len)))
+            batch_size_sents = min(batch_size_sents, per_batch)
+            batch_size_words = batch_size_frames = 10 ** 12
         if sorting:
             keys = []
             if self.tgt_sizes is not None:
@@ -355,6 +370,7 @@ class Dataset(torch.utils.data.Dataset):
                                         batch_size_sents, multiplier, max_src_len, max_tgt_len, min_src_len, min_tgt_len,
                                         cleaning, unbalanced, cut_off_size, smallest_batch_size)
         self.num_batches = len(self.batches)
+        self.kept_ids = np.asarray(sorted({int(i) for b in self.batches for i in b}), dtype=np.int64)   # survived the length filters
         # static shapes: ONE sentence capacity for the whole data set (empty trailing sequences cost the attention kernels a
         # few loads each), so that the shape classes of the training step are (source tokens, target tokens) buckets only
         self.static_max_batch = bucket_capacity(max([len(b) for b in self.batches] + [1]), per_octave=4, floor=8)
@@ -373,8 +389,46 @@ class Dataset(torch.utils.data.Dataset):
     def batch_sizes(self) -> List[int]:
         return [len(b) for b in self.batches]
 
+    def _concat_groups(self, ids, retries: int = 20):
+        """For every example of the batch, the list of examples joined behind it: up to ``retries`` random candidates,
+        shortest first, each taken if the joined source still fits and no example of the batch uses it already."""
+        used = set(int(i) for i in ids)
+        pool = self.kept_ids
+        groups = []
+        for i in ids:
+            group, length = [int(i)], int(self.src_sizes[i])
+            cand = pool[self.concat_rng.randint(0, len(pool), size=retries)]
+            for c in sorted((int(c) for c in cand), key=lambda c: int(self.src_sizes[c])):
+                L = int(self.src_sizes[c])
+                if c not in used and length + L <= self.concat_max_len:
+                    group.append(c)
+                    used.add(c)
+                    length += L
+            groups.append(group)
+        return groups
+
+    def _get_concat_batch(self, ids) -> Batch:
+        groups = self._concat_groups(ids)
+        src = [torch.cat([torch.as_tensor(self.src[j]) for j in g], 0) for g in groups]
+
+        def join_targets(g):
+            # one sentence: the first example keeps its BOS, the last its EOS, everything in between loses both
+            parts = [torch.as_tensor(self.tgt[j]) for j in g]
+            inner = [p[(0 if k == 0 else 1):(len(p) if k == len(parts) - 1 else len(p) - 1)] for k, p in enumerate(parts)]
+            return torch.cat(inner, 0)
+
+        tgt = [join_targets(g) for g in groups]
+        if self.augmenter is not None and self.type != "text":
+            src = [self.augmenter.augment(s) for s in src]
+        lang = lambda d: None if d is None else [(d[g[0]] if len(d) > 1 else d[0]) for g in groups]
+        return collate(src, tgt, lang(self.src_langs), lang(self.tgt_langs), lang(self.src_atbs), lang(self.tgt_atbs),
+                       self.src_pad, self.tgt_pad, self.type, [g[0] for g in groups], self.padded, self.packed,
+                       round_to=self.round_to, create_reverse=self.create_reverse)
+
     def get_batch(self, index: int) -> Batch:
         ids = self.batches[index]
+        if self.concat and self.src is not None and self.tgt is not None:
+            return self._get_concat_batch(ids)
         pick = lambda d: None if d is None else [d[i] for i in ids]
         lang = lambda d: None if d is None else [(d[i] if len(d) > 1 else d[0]) for i in ids]
         src = pick(self.src)

@@ -67,6 +67,14 @@ def build_model(opt, dicts, remove_pretrain: bool = False, constants=None):
                 m.add_depthwise_conv(int(getattr(opt, "conv_kernel", 31) or 31))
             if getattr(opt, "no_ffn", False):
                 m.drop_ffn()
+    if getattr(opt, "favor_attention", False):
+        from .layers import SelfAttention
+        mods = [m for m in getattr(model, "encoder", model).modules() if isinstance(m, SelfAttention) and not m.causal]
+        if not mods:
+            raise NotImplementedError("-favor_attention replaces the encoder's self-attention; the encoder of model '%s' has "
+                                      "none of the standard attention blocks" % getattr(opt, "model", "?"))
+        for i, m in enumerate(mods):
+            m.enable_favor(seed=int(getattr(opt, "seed", 0) or 0) + i)
     if getattr(opt, "stochastic_sublayer", False):
         from .layers import _LayerOptions
         for m in model.modules():

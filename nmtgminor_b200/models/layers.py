@@ -218,13 +218,44 @@ class SelfAttention(nn.Module):
     def __init__(self, dim: int, heads: int, attn_dropout: float = 0.0, bias: bool = False, causal: bool = False):
         super().__init__()
         self.dim, self.heads, self.attn_dropout, self.causal = dim, heads, attn_dropout, causal
+        self.register_buffer("favor_projection", None, persistent=False)
         self.qkv = Linear(dim, 3 * dim, bias=bias)
         self.out = Linear(dim, dim, bias=bias)
+
+    def enable_favor(self, nb_features: int = 0, seed: int = 0):
+        """``-favor_attention``: softmax attention is replaced by its FAVOR+ estimate (positive orthogonal random
+        features, cost linear in the sequence length); the projections keep their weights.
+        (reference: onmt/models/speech_recognizer/wav2vec2.py:192-197, fairseq_wav2vec2 ``favor=``)"""
+        if self.causal:
+            raise NotImplementedError("-favor_attention is built for encoder (bidirectional) attention")
+        from .efficient_attention import gaussian_orthogonal_random_matrix
+        d = self.dim // self.heads
+        m = nb_features or max(1, int(d * math.log(d)))
+        self.favor_projection = gaussian_orthogonal_random_matrix(m, d, torch.Generator().manual_seed(seed)).to(self.qkv.weight.device)
+
+    def _favor_attend(self, qkv, seqs: PackedSeqs):
+        from ..ops.reference import unpad_packed
+        from .efficient_attention import softmax_kernel
+        h, d = self.heads, self.dim // self.heads
+        padded = seqs.pad(qkv, time_first=False).float()                              # [B, T, 3H], zero rows past each length
+        B, T, _ = padded.shape
+        q, k, v = padded.view(B, T, 3, h, d).permute(2, 0, 3, 1, 4)                   # [B, h, T, d]
+        lengths = (seqs.cu[1:] - seqs.cu[:-1]).to(torch.int64)
+        keep = (torch.arange(T, device=qkv.device)[None, :] < lengths[:, None])[:, None, :, None].float()
+        qf = softmax_kernel(q, self.favor_projection, True)
+        kf = softmax_kernel(k, self.favor_projection, False) * keep
+        kv = torch.einsum("bhtm,bhtd->bhmd", kf, v * keep)
+        num = torch.einsum("bhtm,bhmd->bhtd", qf, kv)
+        den = torch.einsum("bhtm,bhm->bht", qf, kf.sum(2))
+        ctx = (num / den.clamp_min(1e-6)[..., None]).transpose(1, 2).reshape(B, T, self.dim)
+        return unpad_packed(ctx.to(qkv.dtype), seqs.cu, qkv.shape[0])
 
     def forward(self, x, seqs: PackedSeqs, residual=None, dropout_p: float = 0.0):
         qkv = self.qkv(x)
         if self.rotary:
             qkv = rotate_queries_and_keys(qkv, seqs.positions, self.heads)
+        if self.favor_projection is not None:
+            return self.out(self._favor_attend(qkv, seqs), dropout_p=dropout_p, residual=residual)
         ctx = ops.self_attention(qkv, seqs.cu, self.heads, seqs.max_len, self.causal, self.attn_dropout, self.training)
         return self.out(ctx, dropout_p=dropout_p, residual=residual)
 

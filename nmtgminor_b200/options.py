@@ -131,6 +131,7 @@ ALWAYS_ON_FLAGS = {
     "fused_ffn": "feed-forward blocks always run as GEMMs with fused epilogues",
     "flatten_parameters": "parameters always live in one flat buffer (parallel/flat.py)",
     "zeror_optim": "optimiser state is always sharded across the data-parallel ranks (parallel/sharded.py)",
+    "fast_factorize": "factorised weights always go through the GEMM kernels (the same product as the reference's fused form)",
 }
 
 # Flags that the reference parses and never reads (checked by grepping its sources): accepted for command-line
@@ -144,6 +145,8 @@ NO_EFFECT_IN_REFERENCE = {
     "contrastive_loss_coeff",
     # parsed by the training script but never handed to a data set (frames are stacked at preprocessing, or with -concat)
     "reshape_speech",
+    # only named in commented-out code of the relative Transformer layers
+    "bottleneck_size",
     # parsed into a per-data-set dictionary and handed to Dataset(dataset_factor=...), which never reads it
     "dataset_factors",
     # written to onmt.constants.residual_type; every reader of that constant is commented out
@@ -153,17 +156,11 @@ NO_EFFECT_IN_REFERENCE = {
 # Flags whose feature is not built: giving one a value other than its default stops the run instead of silently
 # training a different model.
 UNSUPPORTED_FLAGS = {
-    "concat_dataset": "concatenated-sentence data sets",
-    "finalize_only": "the continual-learning finalisation pass",
-    "max_examples_seen": "example-count limits of the continual-learning trainers",
     "stream_context": "streaming context selection",
     "weight_norm": "weight-normalised linear layers",
     "activation_layer": "alternative activation-layer layouts (maxout)",
     "extra_context_size": "extra streaming context",
     "no_decoder": "encoder-only sequence models in the translation trainer",
-    "favor_attention": "FAVOR+ attention inside the main Transformer (models/efficient_attention.py has the stand-alone layer)",
-    "bottleneck_size": "bottleneck adapters of the legacy speech models",
-    "fast_factorize": "the fused factorised-weight kernels (the factorised weights run as plain GEMMs)",
     "flex_factorize": "flexible-rank factorised weights",
     "sub_encoder": "text sub-encoders behind the speech encoder",
     "enc_stacked_pretrained_model": "stacked pretrained encoders",

@@ -390,6 +390,60 @@ class OfflineCLTrainer(OCLTrainer):
             datasets = datasets[1:]
         return super().train_epoch(datasets, valid_data, epoch, resume_itr_state)
 
+    def finalize(self, train_data, valid_data):
+        """The closing pass of a round (``-finalize_only``): the round's saved checkpoints are averaged into the model,
+        the replay memory is filled from the round's training data, the averaged model is validated and written with
+        the memory as ``<save_model>_final.pt`` - the file the next round starts from.
+        (reference: onmt/train_utils/offline_cl_trainer.py:3411-3431, :2648-2700)"""
+        import math
+        import os
+
+        from ..tools.checkpoints import average_state_dicts, best_checkpoints
+        from .checkpoint import load_model_state, model_state_for_saving
+        opt = self.opt
+        files = best_checkpoints(opt.save_model, top=10 ** 6)
+        if files and self.is_main():
+            self.log("[INFO] Averaging %d checkpoints of this round" % len(files))
+        if files:
+            states = [torch.load(f, map_location="cpu", weights_only=False)["model"] for f in files]
+            load_model_state(self.model, average_state_dicts(states))
+            store = getattr(self.engine, "store", None)
+            if store is not None:
+                store.sync_work()                 # the bf16 working copy follows the fp32 parameters just loaded
+        for ds in (list(train_data) if _is_list(train_data) else [train_data]):
+            for batch in self._iterator(ds, 1, shuffle=True).next_epoch_itr():
+                self.reservoir.add_sample((0, batch))
+        vloss, vacc = self.eval(valid_data)
+        vppl = math.exp(min(vloss, 100)) if vloss == vloss else float("nan")
+        self.log("[INFO] Validation perplexity: %g  accuracy: %.4f" % (vppl, vacc))
+        name = opt.save_model + "_final.pt"
+        if self.is_main():
+            os.makedirs(os.path.dirname(os.path.abspath(name)), exist_ok=True)
+            torch.save({"model": model_state_for_saving(self.model), "dicts": self.dicts, "opt": opt, "epoch": -1,
+                        "reservoir": self.reservoir.state_dict(), "valid_ppl": vppl}, name)
+            self.log("[INFO] Saved checkpoint %s" % name)
+        return name
+
+    def run(self, checkpoint=None, train_data=None, valid_data=None):
+        opt = self.opt
+        loaded = checkpoint if checkpoint is not None else getattr(self, "_resume_checkpoint", None)
+        if loaded is not None and loaded.get("reservoir") is not None:
+            self.reservoir.load_state_dict(loaded["reservoir"])            # a *_final.pt of the previous round
+        if getattr(opt, "finalize_only", False):
+            self.log("[INFO] Skipping the training and validation part. Only finalizing the models")
+            return self.finalize(train_data, valid_data)
+        budget = int(getattr(opt, "max_examples_seen", 0) or 0)
+        if budget > 0:
+            # the budget counts minibatches; it is turned into whole epochs (reference: offline_cl_trainer.py:2636-2639)
+            sets = list(train_data) if _is_list(train_data) else [train_data]
+            per_epoch = max(1, sum(len(d) for d in sets))
+            opt.epochs = budget // per_epoch
+            self.log("[INFO] Max epoch: %d" % opt.epochs)
+            if opt.epochs == 0:
+                raise ValueError("No training is done (-max_examples_seen %d is less than one epoch of %d minibatches). "
+                                 "Use -finalize_only." % (budget, per_epoch))
+        return super().run(checkpoint, train_data, valid_data)
+
 
 class EWCTrainer(OfflineCLTrainer):
     """The main trainer's elastic-weight-consolidation switches (reference: onmt/train_utils/mp_trainer.py:402-412,

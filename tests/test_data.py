@@ -167,3 +167,36 @@ def test_auxiliary_target_travels_with_the_batch():
     for col, i in enumerate(order):
         L = int(lens[col])
         assert L == i + 2 and inp[:L, col].tolist() == [2] + [10 + i] * (i + 1) and out[L - 1, col] == 3
+
+
+def test_concat_dataset_joins_random_examples_up_to_the_length_limit():
+    """``concat=True``: sources are joined along time, targets become one sentence with a single BOS and EOS, no
+    example is used twice inside a batch, and no joined source exceeds the limit."""
+    import torch
+    from nmtgminor_b200.data.dataset import Dataset
+    rng = np.random.RandomState(0)
+    n = 60
+    src = [torch.full((int(rng.randint(5, 30)), 1), float(i)) for i in range(n)]           # audio-like [T, 1], value = id
+    tgt = [torch.tensor([2] + [10 + i] * int(rng.randint(1, 4)) + [3]) for i in range(n)]
+    data = Dataset(src, tgt, batch_size_frames=400, max_src_len=100, max_tgt_len=200, data_type="audio", concat=True,
+                   concat_seed=5, padded=True, packed=True, round_to=1)
+    assert all(len(b) <= 4 for b in data.batches) and sum(len(b) for b in data.batches) == n
+    joined_any = False
+    for bi in range(len(data)):
+        batch = data.get_batch(bi)
+        source = batch.get("source")                                                       # [T, B, 1 + 1] with a validity column
+        tgt_out, tgt_in = batch.get("target_output"), batch.get("target_input")
+        used = []
+        for b in range(source.shape[1]):
+            valid = source[:, b, 0] > 0
+            ids = source[valid, b, 1].long().tolist()
+            assert len(ids) <= 100
+            order = [k for k, _ in __import__("itertools").groupby(ids)]
+            used += order
+            joined_any |= len(order) > 1
+            assert sum(len(src[k]) for k in order) == len(ids)
+            full = [int(tgt_in[0, b])] + [int(t) for t in tgt_out[:, b] if int(t) != 0]
+            expect = [2] + [t for k in order for t in tgt[k][1:-1].tolist()] + [3]
+            assert full == expect
+        assert len(used) == len(set(used))
+    assert joined_any

@@ -687,3 +687,32 @@ def test_per_language_output_projection_and_absolute_positions(dicts):
     with torch.no_grad():
         a, b = rel.encode(text)[0], both.encode(text)[0]
     assert a.shape == b.shape and not torch.allclose(a, b, atol=1e-3)
+
+
+def test_favor_attention_estimates_softmax_attention_in_the_encoder(dicts):
+    """``-favor_attention``: with many random features the encoder output approaches the exact-attention output, and
+    it does not depend on the padding of the batch."""
+    from nmtgminor_b200.models.layers import PackedSeqs, SelfAttention
+    torch.manual_seed(0)
+    exact = build_model(default_options(["-model", "transformer"] + COMMON), dicts).eval()
+    favor = build_model(default_options(["-model", "transformer", "-favor_attention"] + COMMON), dicts).eval()
+    favor.load_state_dict(exact.state_dict(), strict=False)
+    attn = [m for m in favor.encoder.modules() if isinstance(m, SelfAttention)]
+    assert attn and all(m.favor_projection is not None for m in attn)
+    assert all(m.favor_projection is None for m in favor.decoder.modules() if isinstance(m, SelfAttention))
+    for i, m in enumerate(attn):
+        m.enable_favor(nb_features=4096, seed=i)
+    batch = token_budget_batches(120, 4, 10, 60, 1, static=False, padded=True)[0]
+    with torch.no_grad():
+        src = batch.packed_source()
+        a, b = exact.encoder(src), favor.encoder(src)
+        n0 = int(src.cu[1])
+        alone = favor.encoder(PackedSeqs(src.tokens[:n0], src.positions[:n0], src.cu[:2], n0))
+    assert float((a - b).abs().mean()) < 0.1 * float(a.abs().mean())
+    assert torch.allclose(alone, b[:n0], atol=1e-4)
+    favor.train()
+    out = favor(batch)
+    out["loss"].backward()
+    assert torch.isfinite(out["loss"]) and attn[0].qkv.weight.grad.abs().sum() > 0
+    with pytest.raises(NotImplementedError, match="favor_attention"):
+        build_model(default_options(["-model", "LSTM", "-favor_attention"] + COMMON), dicts)

@@ -1,4 +1,5 @@
 """Continual-learning trainers and their building blocks on CPU."""
+import pytest
 import torch
 
 from nmtgminor_b200.data.synthetic import synthetic_dataset, synthetic_dict
@@ -112,3 +113,35 @@ def test_dual_primal_learning_moves_the_memory_multipliers():
     fresh = R.Reservoir(8)
     fresh.load_state_dict(sd)
     assert fresh.lambdas == tr.reservoir.lambdas
+
+
+def test_offline_trainer_example_budget_and_finalisation(tmp_path):
+    """``-max_examples_seen`` becomes whole epochs; ``-finalize_only`` averages the round's checkpoints, fills the replay
+    memory and writes ``*_final.pt``, from which the next round restores the memory."""
+    torch.manual_seed(0)
+    d = synthetic_dict(40)
+    dicts = {"src": d, "tgt": d}
+    save = str(tmp_path / "r1" / "model")
+    data, valid = _data(3), _data(4)
+    n_batches = len(data)
+    common = ["-offline_cl_training", "-save_model", save, "-save_every", "100000"]
+    tr = R.OfflineCLTrainer(-1, dicts, _opt(common + ["-max_examples_seen", str(2 * n_batches + 1)]), init_distributed=False)
+    tr.run(None, data, valid)
+    assert tr.opt.epochs == 2 and tr.optim._step == 2 * n_batches
+    import glob
+    files = sorted(glob.glob(save + "_ppl_*.pt"))
+    assert len(files) == 2
+    with pytest.raises(ValueError, match="finalize_only"):
+        R.OfflineCLTrainer(-1, dicts, _opt(common + ["-max_examples_seen", "1"]), init_distributed=False).run(None, data, valid)
+    fin = R.OfflineCLTrainer(-1, dicts, _opt(common + ["-finalize_only"]), init_distributed=False)
+    name = fin.run(None, data, valid)
+    assert name == save + "_final.pt" and fin.optim._step == 0
+    ck = torch.load(name, weights_only=False)
+    a, b = (torch.load(f, weights_only=False)["model"] for f in files)
+    k = next(k for k in ck["model"] if ck["model"][k].dim() == 2)
+    assert torch.allclose(ck["model"][k], (a[k] + b[k]) / 2, atol=1e-6)
+    assert 0 < len(fin.reservoir) <= 8 and ck["reservoir"] is not None
+    nxt = R.OfflineCLTrainer(-1, dicts, _opt(common + ["-finalize_only", "-load_from", name]), init_distributed=False)
+    assert len(nxt.reservoir) == 0
+    nxt.run(nxt._resume_checkpoint, [], valid)
+    assert len(nxt.reservoir) == len(fin.reservoir)

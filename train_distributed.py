@@ -48,7 +48,8 @@ def _dataset_from(split, opt, dicts, training):
                    batch_size_sents=opt.batch_size_sents if opt.batch_size_sents > 0 else 10 ** 9,
                    multiplier=opt.batch_size_multiplier, data_type=getattr(opt, "encoder_type", "text") if getattr(opt, "encoder_type", "text") != "text" else "text",
                    max_src_len=opt.max_src_length if training else 10 ** 9, max_tgt_len=(opt.max_tgt_length + 2) if training else 10 ** 9,
-                   cleaning=training, verbose=True, aux_tgt_data=split.get("aux_tgt"), augmenter=augmenter, static_shapes=static)
+                   cleaning=training, verbose=True, aux_tgt_data=split.get("aux_tgt"), augmenter=augmenter, static_shapes=static,
+                   concat=training and bool(getattr(opt, "concat_dataset", False)), concat_seed=int(getattr(opt, "seed", 1234) or 1234))
 
 
 def _use_cuda_graph(opt) -> bool:
