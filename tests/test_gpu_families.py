@@ -55,6 +55,8 @@ def _step_and_decode(model, batch, decode=True):
     ("discourse_translator", []), ("pretrain_transformer", ["-enc_pretrained_model", "mbart50", "-dec_pretrained_model", "mbart50"]),
     ("pretrain_transformer", ["-enc_pretrained_model", "deltalm", "-dec_pretrained_model", "deltalm"]),
     ("dlcl_transformer", []), ("parallel_transformer", []), ("fctransformer", []), ("unified_transformer", []),
+    ("transformer", ["-depthwise_conv", "-conv_kernel", "5", "-no_ffn", "-macaron"]), ("transformer", ["-favor_attention"]),
+    ("relative_transformer", ["-absolute_position_encoding"]),
 ])
 def test_text_families_on_gpu(dicts, name, extra):
     torch.manual_seed(0)
@@ -82,9 +84,13 @@ def test_speech_families_on_gpu(dicts, tmp_path):
         (["-model", "whisper", "-dec_config_file", wsp], synthetic_audio_batch(2, 120, "feats", n_feats=80, fixed_frames=120)),
         (["-model", "speech_transformer", "-input_size", "40", "-cnn_downsampling"], synthetic_audio_batch(2, 120, "feats", 40, 80, n_feats=40)),
         (["-model", "conformer", "-input_size", "40"], synthetic_audio_batch(2, 120, "feats", 40, 80, n_feats=40)),
+        (["-model", "speech_transformer", "-input_size", "40", "-multilingual_linear_projection", "-depthwise_conv"],
+         synthetic_audio_batch(2, 120, "feats", 40, 80, n_feats=40)),
     ]
     for argv, batch in cases:
         model = build_model(default_options(argv + COMMON), dicts)
+        if "-multilingual_linear_projection" in argv:
+            batch.tensors["source_lang"] = torch.tensor([0])
         _step_and_decode(model, batch)
 
 
