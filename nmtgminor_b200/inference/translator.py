@@ -171,6 +171,9 @@ class Translator:
             batch = batch.cuda(self.device)
             if getattr(batch, "sub_batch", None) is not None:
                 batch.sub_batch = batch.sub_batch.cuda(self.device)
+        if getattr(self.model, "ctc_only", False):
+            # encoder-only CTC models (-no_decoder): best-path decoding, one hypothesis per utterance
+            return [[Hypothesis(tokens, score, [])] for tokens, score in self.model.ctc_greedy(batch)]
         return beam_search(self.model, batch, self.cfg, prefix_tokens, banned_first)
 
     def translate(self, src_sents, tgt_sents: Optional[List[List[str]]] = None, prefix: Optional[List[List[str]]] = None,

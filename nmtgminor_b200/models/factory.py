@@ -36,6 +36,9 @@ def build_model(opt, dicts, remove_pretrain: bool = False, constants=None):
         return build_fusion(opt, dicts, remove_pretrain)
     model = _REGISTRY[name](opt, dicts)
     init_model_parameters(model, opt)
+    if getattr(opt, "no_decoder", False) and not getattr(model, "ctc_only", False):
+        raise NotImplementedError("-no_decoder builds encoder-only CTC models of the wav2vec 2.0 family (wav2vec2_bert, "
+                                  "wav2vec2_transformer); model '%s' keeps its decoder" % name)
     if int(getattr(opt, "predict_language", 0) or 0) > 0:
         if not hasattr(model, "enable_language_prediction"):
             raise NotImplementedError("-predict_language is built for the speech-to-text models")

@@ -427,6 +427,65 @@ class SpeechToTextModel(Seq2SeqBase, _ReferenceNaming):
         return self.ctc_weight * ctc
 
 
+class SpeechCTCModel(nn.Module):
+    """``-no_decoder``: a speech encoder with a CTC output layer and nothing else (the reference builds its wav2vec 2.0
+    models without a decoder under this flag, onmt/model_factory.py:274-276, and trains them on the CTC term alone).
+    Blank is the padding id; the target's end-of-sentence symbol is not a label.  Decoding is the best path: arg-max
+    per frame, repeats merged, blanks removed (``ctc_greedy``; the translator calls it instead of beam search)."""
+
+    graph_capturable = False
+    supports_logits_step = False
+    ctc_only = True
+    decoder = None
+
+    def __init__(self, opt, encoder: nn.Module, vocab: int, pad_idx: int = 0, eos_idx: int = 3):
+        super().__init__()
+        self.opt, self.encoder = opt, encoder
+        self.ctc_linear = nn.Linear(encoder.dim, vocab)
+        self.pad_idx, self.eos_idx = pad_idx, eos_idx
+        self.num_updates = 0
+
+    def encode(self, batch):
+        if getattr(self.encoder, "adapters", None) is not None or getattr(self.encoder, "linear_proj", None) is not None:
+            return self.encoder(batch.get("source"), lang=single_language(batch, "source_lang"))
+        return self.encoder(batch.get("source"))
+
+    def _frame_logits(self, batch):
+        context, src = self.encode(batch)
+        lengths = (src.cu[1:] - src.cu[:-1]).to(torch.int64)
+        return src.pad(self.ctc_linear(context.float())), lengths                 # [T, B, V], [B]
+
+    def forward(self, batch, grad_scale=None, **_unused) -> Dict:
+        logits, lengths = self._frame_logits(batch)
+        targets = batch.get("target_output").t().clone()                          # [B, U] ending in EOS
+        targets[targets == self.eos_idx] = self.pad_idx
+        tgt_len = (targets != self.pad_idx).sum(-1)
+        lp = F.log_softmax(logits.float(), -1)
+        ctc = F.ctc_loss(lp, targets, lengths[:targets.shape[0]], tgt_len, blank=self.pad_idx, reduction="sum", zero_infinity=True)
+        loss = ctc if grad_scale is None else ctc * grad_scale
+        return {"loss": loss, "ctc_loss": ctc.detach(), "n_ctc_targets": int(tgt_len.sum()),
+                "correct": torch.zeros((), device=ctc.device), "row_loss": None}
+
+    @torch.no_grad()
+    def ctc_greedy(self, batch):
+        """Best-path decoding: per utterance ``(token ids, sum of the chosen frames' log-probabilities)``."""
+        logits, lengths = self._frame_logits(batch)
+        lp = F.log_softmax(logits.float(), -1)
+        best_lp, best = lp.max(-1)                                                # [T, B]
+        out = []
+        for b in range(best.shape[1]):
+            n = int(lengths[b])
+            path = best[:n, b]
+            keep = torch.ones(n, dtype=torch.bool, device=path.device)
+            keep[1:] = path[1:] != path[:-1]
+            toks = path[keep & (path != self.pad_idx)]
+            out.append((toks.tolist(), float(best_lp[:n, b].sum())))
+        return out
+
+    def create_decoder_state(self, *a, **kw):
+        raise NotImplementedError("a model built with -no_decoder has no decoder to search with; use ctc_greedy (translate.py does)")
+
+
 class TextToTextPretrained(Seq2SeqBase, _ReferenceNaming):
     """``pretrain_transformer``: pretrained-style text encoder + decoder (mBART, DeltaLM, M2M-100, BART ...)."""
 
@@ -470,7 +529,7 @@ def _add_language_adapters(opt, dicts, encoder, decoder):
         if not hasattr(encoder, "add_adapters"):
             raise NotImplementedError("-wav2vec_adapter: %s has no adapter slots" % type(encoder).__name__)
         encoder.add_adapters(n, int(opt.wav2vec_adapter))
-    if int(getattr(opt, "decoder_adapter", 0) or 0) > 0:
+    if int(getattr(opt, "decoder_adapter", 0) or 0) > 0 and decoder is not None:
         if not hasattr(decoder, "add_adapters"):
             raise NotImplementedError("-decoder_adapter: %s has no adapter slots" % type(decoder).__name__)
         decoder.add_adapters(n, int(opt.decoder_adapter))
@@ -542,6 +601,9 @@ def register_builders(register):
     @register("wav2vec2_bert", "quantize_wav2vec2_bert", "quantize_wav2vec2_mbart50")
     def _wav2vec_bert(opt, dicts):
         enc = _wav2vec_from_opt(opt)
+        if getattr(opt, "no_decoder", False):
+            _add_language_adapters(opt, dicts, enc, None)
+            return SpeechCTCModel(opt, enc, dicts["tgt"].size(), getattr(opt, "pad_idx", 0))
         dec = build_pretrained_decoder(opt, dicts["tgt"].size(), kv_dim=enc.dim)
         _add_language_adapters(opt, dicts, enc, dec)
         return SpeechToTextModel(opt, enc, dec, dec.embed.weight.shape[0], generator_bias=False)
@@ -550,6 +612,8 @@ def register_builders(register):
     def _wav2vec_transformer(opt, dicts):
         from .transformer import TransformerDecoder
         enc = _wav2vec_from_opt(opt)
+        if getattr(opt, "no_decoder", False):
+            return SpeechCTCModel(opt, enc, dicts["tgt"].size(), getattr(opt, "pad_idx", 0))
         embed = Embedding(dicts["tgt"].size(), opt.model_size, getattr(opt, "pad_idx", 0))
         dec = TransformerDecoder(opt, embed)
         if enc.dim != opt.model_size:

@@ -160,7 +160,6 @@ UNSUPPORTED_FLAGS = {
     "weight_norm": "weight-normalised linear layers",
     "activation_layer": "alternative activation-layer layouts (maxout)",
     "extra_context_size": "extra streaming context",
-    "no_decoder": "encoder-only sequence models in the translation trainer",
     "flex_factorize": "flexible-rank factorised weights",
     "sub_encoder": "text sub-encoders behind the speech encoder",
     "enc_stacked_pretrained_model": "stacked pretrained encoders",

@@ -716,3 +716,36 @@ def test_favor_attention_estimates_softmax_attention_in_the_encoder(dicts):
     assert torch.isfinite(out["loss"]) and attn[0].qkv.weight.grad.abs().sum() > 0
     with pytest.raises(NotImplementedError, match="favor_attention"):
         build_model(default_options(["-model", "LSTM", "-favor_attention"] + COMMON), dicts)
+
+
+def test_no_decoder_builds_a_ctc_only_speech_model_that_learns_and_decodes(dicts, tmp_path):
+    from nmtgminor_b200.models.pretrained import SpeechCTCModel
+    torch.manual_seed(0)
+    enc = _cfg(tmp_path, "enc.json", encoder_embed_dim=64, encoder_layers=1, encoder_attention_heads=2, encoder_ffn_embed_dim=128)
+    model = build_model(default_options(["-model", "wav2vec2_transformer", "-enc_config_file", enc, "-no_decoder"] + COMMON), dicts)
+    assert isinstance(model, SpeechCTCModel) and model.decoder is None
+    assert not any(k.startswith("decoder") or k.startswith("generator") for k in model.state_dict())
+    batch = synthetic_audio_batch(2, 120, "wav", 3000, 4000, tgt_min=3, tgt_max=5)
+    opt = torch.optim.Adam(model.parameters(), lr=2e-3)
+    model.train()
+    first = None
+    for _ in range(60):
+        opt.zero_grad()
+        out = model(batch)
+        out["loss"].backward()
+        opt.step()
+        first = first if first is not None else float(out["loss"])
+    assert float(out["loss"]) < 0.2 * first
+    model.eval()
+    hyps = model.ctc_greedy(batch)
+    gold = batch.get("target_output").t()
+    for (tokens, score), row in zip(hyps, gold):
+        assert tokens == [int(t) for t in row if int(t) not in (0, 3)] and score <= 0
+    with pytest.raises(NotImplementedError, match="no_decoder"):
+        build_model(default_options(["-model", "transformer", "-no_decoder"] + COMMON), dicts)
+    # the translator takes the best path instead of searching
+    from nmtgminor_b200.inference.translator import Translator
+    tr = Translator.__new__(Translator)
+    tr.model, tr.cuda, tr.cfg = model, False, None
+    out = tr.translate_batch(batch)
+    assert [h[0].tokens for h in out] == [t for t, _ in hyps]
