@@ -70,6 +70,14 @@ def build_model(opt, dicts, remove_pretrain: bool = False, constants=None):
                 m.add_depthwise_conv(int(getattr(opt, "conv_kernel", 31) or 31))
             if getattr(opt, "no_ffn", False):
                 m.drop_ffn()
+    if getattr(opt, "branchformer", False):
+        from .layers import EncoderLayer
+        layers = [m for m in getattr(model, "encoder", model).modules() if isinstance(m, EncoderLayer)]
+        if not layers:
+            raise NotImplementedError("-branchformer adds a cgMLP branch to the standard encoder layers; the encoder of "
+                                      "model '%s' is not built from them" % getattr(opt, "model", "?"))
+        for m in layers:
+            m.add_branchformer(int(getattr(opt, "conv_kernel", 31) or 31))
     if getattr(opt, "favor_attention", False):
         from .layers import SelfAttention
         mods = [m for m in getattr(model, "encoder", model).modules() if isinstance(m, SelfAttention) and not m.causal]

@@ -473,6 +473,36 @@ class PackedConvolution(nn.Module):
         return y if residual is None else residual + y
 
 
+def _over_time(seqs: PackedSeqs, x, fn):
+    """Runs ``fn`` on the padded ``[B, C, T]`` view of packed rows ``x [N, C]`` (padding frames zero) and packs the result."""
+    from ..ops.reference import unpad_packed
+    padded = seqs.pad(x, time_first=False).float()
+    lengths = (seqs.cu[1:] - seqs.cu[:-1]).to(torch.int64)
+    valid = (torch.arange(padded.shape[1], device=x.device)[None, :] < lengths[:, None]).to(padded.dtype)
+    y = fn((padded * valid.unsqueeze(-1)).transpose(1, 2)).transpose(1, 2)
+    return unpad_packed(y.to(x.dtype).contiguous(), seqs.cu, x.shape[0])
+
+
+class ConvolutionalGatingMLP(nn.Module):
+    """cgMLP branch of a Branchformer layer: Linear(d -> u) + GELU, split into halves (r, g), ``r * GELU(dwconv(LN(g)))``,
+    Linear(u/2 -> d).  The gate's convolution starts near zero with bias one, so the unit starts close to the identity
+    on ``r``.  (reference: onmt/models/speech_recognizer/fairseq_wav2vec2/cgmlp.py:14-117)"""
+
+    def __init__(self, dim: int, units: int, kernel: int = 31):
+        super().__init__()
+        self.proj1 = nn.Linear(dim, units)
+        self.gate_norm = nn.LayerNorm(units // 2)
+        self.gate_conv = nn.Conv1d(units // 2, units // 2, kernel, padding=(kernel - 1) // 2, groups=units // 2)
+        nn.init.normal_(self.gate_conv.weight, std=1e-6)
+        nn.init.ones_(self.gate_conv.bias)
+        self.proj2 = nn.Linear(units // 2, dim)
+
+    def forward(self, x, seqs: PackedSeqs):
+        r, g = F.gelu(self.proj1(x.float())).chunk(2, dim=-1)
+        g = _over_time(seqs, self.gate_norm(g), self.gate_conv)
+        return self.proj2(r * F.gelu(g)).to(x.dtype)
+
+
 class EncoderLayer(nn.Module, _LayerOptions):
     """Self-attention + FFN block.  Pre-LN: x += D(Attn(LN(x))); x += D(FFN(LN(x))).  Post-LN (``post_norm``):
     x = LN(x + D(Attn(x))); x = LN(x + D(FFN(x))).  Optional stochastic depth (``death_rate``), ``rezero``, ``macaron``
@@ -504,6 +534,26 @@ class EncoderLayer(nn.Module, _LayerOptions):
         self.conv_norm = LayerNorm(dim)
         self.conv = PackedConvolution(dim, kernel)
 
+    def add_branchformer(self, cgmlp_kernel: int = 31, merge_kernel: int = 3):
+        """``-branchformer``: next to the attention branch a cgMLP branch reads the same layer input; the two outputs are
+        concatenated, a depthwise convolution over time is added to the concatenation, and a linear layer merges them
+        into the residual.  The feed-forward block follows unchanged.  Pre-LayerNorm layers only.
+        (reference: onmt/models/speech_recognizer/fairseq_wav2vec2/wav2vec2.py:1226-1246, 1504-1566)"""
+        if self.post_norm or self.rezero:
+            raise NotImplementedError("-branchformer is built for pre-LayerNorm layers")
+        dim = self.attn_norm.weight.shape[0]
+        self.cgmlp_norm = LayerNorm(dim)
+        self.cgmlp = ConvolutionalGatingMLP(dim, 2 * dim, cgmlp_kernel)
+        self.merge_conv = nn.Conv1d(2 * dim, 2 * dim, merge_kernel, padding=(merge_kernel - 1) // 2, groups=2 * dim)
+        self.merge_proj = nn.Linear(2 * dim, dim)
+
+    def _branchformer_block(self, x, seqs: PackedSeqs, p: float):
+        a = self.attn(self.attn_norm(x), seqs, residual=None, dropout_p=p)
+        c = F.dropout(self.cgmlp(self.cgmlp_norm(x), seqs), p, self.training)
+        both = torch.cat([a, c], -1)
+        merged = self.merge_proj((both + _over_time(seqs, both, self.merge_conv)).float())
+        return x + F.dropout(merged, p, self.training).to(x.dtype)
+
     def forward(self, x, seqs: PackedSeqs):
         keep = self._survives
         if not self.stochastic_sublayer and not keep():
@@ -511,7 +561,9 @@ class EncoderLayer(nn.Module, _LayerOptions):
         p = self.dropout
         if self.macaron and keep(True):
             x = self._block(2, self.mcr_norm, self.mcr_ffn, x, p, seqs, scale=0.5)
-        if keep(True):
+        if getattr(self, "cgmlp", None) is not None:
+            x = self._branchformer_block(x, seqs, p)
+        elif keep(True):
             x = self._block(0, self.attn_norm, self.attn, x, p, seqs, seqs)
         if self.conv is not None and keep(True):
             x = self._block(4, self.conv_norm, self.conv, x, p, seqs, seqs)

@@ -172,7 +172,6 @@ UNSUPPORTED_FLAGS = {
     "memory_size_max": "the n-gram memory decoder",
     "encoder_layers_memory": "the n-gram memory decoder",
     "decoder_layers_memory": "the n-gram memory decoder",
-    "branchformer": "Branchformer cgMLP blocks",
     "pos_emb_type": "position-embedding variants of the legacy speech Transformer",
     "char_ctc": "character-level CTC targets",
     "cache_dir": "cached encoder outputs",

@@ -84,6 +84,9 @@ def test_speech_families_on_gpu(dicts, tmp_path):
         (["-model", "whisper", "-dec_config_file", wsp], synthetic_audio_batch(2, 120, "feats", n_feats=80, fixed_frames=120)),
         (["-model", "speech_transformer", "-input_size", "40", "-cnn_downsampling"], synthetic_audio_batch(2, 120, "feats", 40, 80, n_feats=40)),
         (["-model", "conformer", "-input_size", "40"], synthetic_audio_batch(2, 120, "feats", 40, 80, n_feats=40)),
+        (["-model", "wav2vec2_transformer", "-enc_config_file", enc, "-branchformer", "-conv_kernel", "7"],
+         synthetic_audio_batch(2, 120, "wav", 3000, 6000)),
+        (["-model", "wav2vec2_transformer", "-enc_config_file", enc, "-no_decoder"], synthetic_audio_batch(2, 120, "wav", 3000, 6000)),
         (["-model", "speech_transformer", "-input_size", "40", "-multilingual_linear_projection", "-depthwise_conv"],
          synthetic_audio_batch(2, 120, "feats", 40, 80, n_feats=40)),
     ]
@@ -91,7 +94,10 @@ def test_speech_families_on_gpu(dicts, tmp_path):
         model = build_model(default_options(argv + COMMON), dicts)
         if "-multilingual_linear_projection" in argv:
             batch.tensors["source_lang"] = torch.tensor([0])
-        _step_and_decode(model, batch)
+        _step_and_decode(model, batch, decode="-no_decoder" not in argv)
+        if "-no_decoder" in argv:
+            hyps = model.eval().ctc_greedy(copy.deepcopy(batch).cuda("cuda"))
+            assert len(hyps) == batch.size and ops.check_status() == 0
 
 
 def test_language_model_and_classifier_on_gpu(dicts):

@@ -749,3 +749,33 @@ def test_no_decoder_builds_a_ctc_only_speech_model_that_learns_and_decodes(dicts
     tr.model, tr.cuda, tr.cfg = model, False, None
     out = tr.translate_batch(batch)
     assert [h[0].tokens for h in out] == [t for t, _ in hyps]
+
+
+def test_branchformer_layers_add_a_cgmlp_branch(dicts, tmp_path):
+    from nmtgminor_b200.models.layers import ConvolutionalGatingMLP, EncoderLayer, PackedSeqs
+    torch.manual_seed(0)
+    enc = _cfg(tmp_path, "enc.json", encoder_embed_dim=64, encoder_layers=2, encoder_attention_heads=2, encoder_ffn_embed_dim=128)
+    model = build_model(default_options(["-model", "wav2vec2_transformer", "-enc_config_file", enc, "-branchformer", "-conv_kernel", "7"]
+                                        + COMMON), dicts)
+    layers = [m for m in model.encoder.modules() if isinstance(m, EncoderLayer)]
+    assert len(layers) == 2 and all(isinstance(m.cgmlp, ConvolutionalGatingMLP) and m.merge_proj.in_features == 128 for m in layers)
+    batch = synthetic_audio_batch(2, 120, "wav", 3000, 6000)
+    out = model(batch)
+    out["loss"].backward()
+    assert torch.isfinite(out["loss"])
+    for name in ("cgmlp.proj1.weight", "cgmlp.gate_conv.weight", "merge_conv.weight", "merge_proj.weight", "attn.qkv.weight"):
+        g = dict(layers[0].named_parameters())[name].grad
+        assert g is not None and g.abs().sum() > 0, name
+    # at initialisation the gate is GELU(1): the cgMLP output is proj2(r * GELU(1)); and sequences do not mix
+    layer = layers[0].eval()
+    seqs = PackedSeqs(torch.zeros(9, dtype=torch.long), torch.arange(9) % 5, torch.tensor([0, 5, 9], dtype=torch.int32), 5)
+    x = torch.randn(9, 64)
+    with torch.no_grad():
+        r, _ = torch.nn.functional.gelu(layer.cgmlp.proj1(x)).chunk(2, -1)
+        expect = layer.cgmlp.proj2(r * torch.nn.functional.gelu(torch.ones(())))
+        assert torch.allclose(layer.cgmlp(x, seqs), expect, atol=1e-4)
+        both = layer(x, seqs)
+        first = layer(x[:5], PackedSeqs(seqs.tokens[:5], seqs.positions[:5], seqs.cu[:2], 5))
+    assert torch.allclose(both[:5], first, atol=1e-5)
+    with pytest.raises(NotImplementedError, match="branchformer"):
+        build_model(default_options(["-model", "LSTM", "-branchformer"] + COMMON), dicts)
