@@ -19,8 +19,11 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 def _sources():
     out = []
+    with open(os.path.join(ROOT, ".gitignore")) as fh:       # scratch and build folders are not sources
+        ignored = {line.strip().strip("/") for line in fh if line.strip() and not line.startswith("#")}
+    skip = ignored | {"baseline", ".git", "tests", "__pycache__", "profiles"}
     for base, dirs, files in os.walk(ROOT):
-        dirs[:] = [d for d in dirs if d not in ("_work", "baseline", ".git", "tests", "gpurun_out", "__pycache__", "profiles")]
+        dirs[:] = [d for d in dirs if d not in skip]
         for f in files:
             if f.endswith(".py") and f not in ("options_spec.py", "options.py"):
                 with open(os.path.join(base, f)) as fh:

@@ -104,7 +104,7 @@ def test_noalloc_entry_point_matches_regular_one_twice_in_a_row():
 
 def test_noalloc_entry_point_on_sequences_of_one_tile():
     """At most 128 keys per sequence: the built-in array is not needed (the regular entry point takes its
-    single-tile kernels here, this one the general kernel), so the fp32 restatement is the judge."""
+    single-tile kernels here, this one the general kernel), so the fp32 restatement is the arbiter."""
     fn = _lib()
     c = _case(3, [100, 64, 128, 1])
     rc, got, status, msg = _noalloc(fn, c)
