@@ -26,8 +26,11 @@ def build_model(opt, dicts, remove_pretrain: bool = False, constants=None):
     from ..options import backward_compatible
     opt = backward_compatible(opt)
     name = getattr(opt, "model", "transformer")
-    if getattr(opt, "model_type", "") == "lm" or name in ("TransformerXL", "transformer_xl_lm"):
+    if getattr(opt, "model_type", "") == "lm" or name in ("TransformerXL", "transformer_xl_lm", "transformer_xl"):
         return _REGISTRY["transformer_xl_lm"](opt, dicts)
+    if (getattr(opt, "activation_layer", "linear_relu_linear") or "linear_relu_linear") != "linear_relu_linear":
+        raise NotImplementedError("-activation_layer %s changes the feed-forward blocks of the Transformer-XL language model "
+                                  "only (as in the reference); model '%s' keeps -ffn_activation" % (opt.activation_layer, name))
     if name not in _REGISTRY:
         raise NotImplementedError("unknown model %r; registered: %s" % (name, sorted(_REGISTRY)))
     from ..options import validate_model_options

@@ -276,6 +276,7 @@ class TransformerXLLanguageModel(nn.Module):
         self.generator.weight = self.decoder.embed.weight
         self.pad_idx, self.label_smoothing = pad, getattr(opt, "label_smoothing", 0.0)
         self.max_memory = getattr(opt, "max_memory_size", 0)
+        apply_activation_layer(self, opt)
 
     def init_stream(self):
         return StreamState(len(self.decoder.layers), self.max_memory)
@@ -288,6 +289,36 @@ class TransformerXLLanguageModel(nn.Module):
                                                               self.label_smoothing if self.training else 0.0, self.pad_idx,
                                                               grad_scale)
         return {"loss": loss, "correct": correct, "row_loss": row_loss, "hidden_packed": hidden, "tgt": tgt}
+
+
+class MaxOutFeedForward(nn.Module):
+    """``-activation_layer maxout``: the feed-forward block becomes one linear layer with ``ceil(inner / model)``
+    candidates per output unit of which the largest is kept (reference: onmt/models/transformer_xl.py:44-46)."""
+
+    def __init__(self, dim: int, inner: int):
+        super().__init__()
+        from .efficient_attention import MaxOut
+        self.maxout = MaxOut(dim, dim, max(1, math.ceil(inner / dim)))
+
+    def forward(self, x, residual=None, dropout_p: float = 0.0):
+        y = self.maxout(x.float()).to(x.dtype)
+        y = F.dropout(y, dropout_p, self.training) if dropout_p > 0 else y
+        return y if residual is None else residual + y
+
+
+def apply_activation_layer(model, opt):
+    """``-activation_layer``: ``linear_relu_linear`` (default), ``linear_swish_linear`` (SiLU between the two linear
+    layers) or ``maxout`` for the feed-forward blocks of the Transformer-XL language model."""
+    kind = getattr(opt, "activation_layer", "linear_relu_linear") or "linear_relu_linear"
+    if kind == "linear_relu_linear":
+        return
+    if kind not in ("linear_swish_linear", "maxout"):
+        raise NotImplementedError("-activation_layer %s (known: linear_relu_linear, linear_swish_linear, maxout)" % kind)
+    for layer in model.decoder.layers:
+        if kind == "maxout":
+            layer.ffn = MaxOutFeedForward(opt.model_size, opt.inner_size)
+        else:
+            layer.ffn = FeedForward(opt.model_size, opt.inner_size, opt.dropout, "silu")
 
 
 def _xl_log_probs(self, tokens_tb):

@@ -158,7 +158,6 @@ NO_EFFECT_IN_REFERENCE = {
 UNSUPPORTED_FLAGS = {
     "stream_context": "streaming context selection",
     "weight_norm": "weight-normalised linear layers",
-    "activation_layer": "alternative activation-layer layouts (maxout)",
     "extra_context_size": "extra streaming context",
     "flex_factorize": "flexible-rank factorised weights",
     "sub_encoder": "text sub-encoders behind the speech encoder",

@@ -779,3 +779,24 @@ def test_branchformer_layers_add_a_cgmlp_branch(dicts, tmp_path):
     assert torch.allclose(both[:5], first, atol=1e-5)
     with pytest.raises(NotImplementedError, match="branchformer"):
         build_model(default_options(["-model", "LSTM", "-branchformer"] + COMMON), dicts)
+
+
+@pytest.mark.parametrize("kind", ["maxout", "linear_swish_linear"])
+def test_activation_layer_variants_of_the_xl_language_model(dicts, kind):
+    from nmtgminor_b200.models.relative_transformer import MaxOutFeedForward
+    torch.manual_seed(0)
+    lm = build_model(default_options(["-model", "transformer_xl_lm", "-activation_layer", kind] + COMMON), dicts)
+    ffn = lm.decoder.layers[0].ffn
+    if kind == "maxout":
+        assert isinstance(ffn, MaxOutFeedForward) and ffn.maxout.pool == 2 and ffn.maxout.lin.out_features == 128
+        x = torch.randn(5, 64)
+        cand = ffn.maxout.lin(x).view(5, 64, 2)
+        assert torch.allclose(ffn(x), cand.max(-1).values)
+    else:
+        assert ffn.activation == "silu"
+    batch = token_budget_batches(120, 4, 10, 60, 1, static=False, padded=True)[0]
+    out = lm(batch)
+    out["loss"].backward()
+    assert torch.isfinite(out["loss"]) and all(p.grad is not None for p in ffn.parameters())
+    with pytest.raises(NotImplementedError, match="activation_layer"):
+        build_model(default_options(["-model", "transformer", "-activation_layer", kind] + COMMON), dicts)
