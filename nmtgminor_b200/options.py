@@ -165,7 +165,8 @@ UNSUPPORTED_FLAGS = {
     "load_pretrained_classifier": "pretrained classifier heads",
     "wav2vec2_quantize": "the wav2vec 2.0 quantiser inside the translation models (models/w2vbert.py has the quantiser)",
     "wav2vec2_dual_output": "dual-output wav2vec 2.0 encoders",
-    "cache_encoder_output": "cached encoder outputs",
+    "cache_encoder_output": "cached encoder outputs (the reference's own caching pass stops at a debugger breakpoint, "
+                            "onmt/train_utils/mp_trainer.py:1549)",
     "use_memory": "the n-gram memory decoder",
     "freeze_baseline_decoder": "the n-gram memory decoder",
     "memory_size_max": "the n-gram memory decoder",
@@ -173,7 +174,7 @@ UNSUPPORTED_FLAGS = {
     "decoder_layers_memory": "the n-gram memory decoder",
     "pos_emb_type": "position-embedding variants of the legacy speech Transformer",
     "char_ctc": "character-level CTC targets",
-    "cache_dir": "cached encoder outputs",
+    "cache_dir": "cached encoder outputs (see -cache_encoder_output)",
     "memory_loss_coeff": "the n-gram memory decoder",
 }
 
